@@ -1,0 +1,422 @@
+// extern "C" surface declared in include/bfb200.h: argument checks, exception -> status mapping,
+// and nothing else. All work happens in the kernel layer (kernels.hpp) and the host layer (host/).
+#include <cstring>
+#include <vector>
+
+#include "common.cuh"
+#include "host/bfb200.hpp"
+#include "host/tp.hpp"
+#include "kernels.hpp"
+#include "pool.hpp"
+
+using bfb::asStream;
+using bfb::guarded;
+using bfb::require;
+
+struct bfb_model {
+    std::unique_ptr<bfb200::Model> model;
+    std::vector<bfb200::Parameter*> params;  // refreshed lazily
+    void refresh() {
+        if (params.empty()) params = model->parameters();
+    }
+};
+
+namespace {
+
+std::optional<bfb200::PrecisionPolicy> toPolicy(const bfb_precision* p) {
+    if (p == nullptr || p->present == 0) return std::nullopt;
+    bfb200::PrecisionPolicy policy;
+    policy.storage = p->storage;
+    policy.compute = p->compute;
+    policy.accumulate = p->accumulate;
+    return policy;
+}
+
+void requireDevice() {
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        bfb::fail(BFB_CUDA_ERROR, "no usable CUDA device (this library has no CPU fallback)");
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* bfb_last_error(void) { return bfb::lastErrorSlot().c_str(); }
+
+int32_t bfb_version(void) { return 100; }
+
+bfb_status bfb_device_count(int32_t* count) {
+    return guarded([&] {
+        require(count != nullptr, "device_count: null pointer");
+        *count = 0;
+        int n = 0;
+        cudaError_t e = cudaGetDeviceCount(&n);
+        if (e != cudaSuccess || n == 0) {
+            cudaGetLastError();
+            bfb::fail(BFB_CUDA_ERROR, "no usable CUDA device");
+        }
+        *count = n;
+    });
+}
+
+bfb_status bfb_set_device(int32_t index) {
+    return guarded([&] {
+        int n = 0;
+        cudaError_t e = cudaGetDeviceCount(&n);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            bfb::fail(BFB_CUDA_ERROR, "no usable CUDA device");
+        }
+        require(index >= 0 && index < n, "set_device: device index out of range");
+        BFB_CUDA(cudaSetDevice(index));
+    });
+}
+
+bfb_status bfb_pool_acquire(size_t bytes, void** d_out) {
+    return guarded([&] {
+        require(d_out != nullptr, "pool_acquire: null result pointer");
+        *d_out = nullptr;
+        if (bytes == 0) return;
+        requireDevice();
+        *d_out = bfb::poolAcquire(bytes);
+    });
+}
+
+bfb_status bfb_pool_release(void* d_ptr, size_t bytes) {
+    bfb::poolRelease(d_ptr, bytes);
+    return BFB_OK;
+}
+
+bfb_status bfb_pool_trim(void) {
+    return guarded([&] { bfb::poolTrim(); });
+}
+
+bfb_status bfb_pool_stats(size_t* cached_bytes, size_t* live_bytes) {
+    return guarded([&] { bfb::poolStats(cached_bytes, live_bytes); });
+}
+
+bfb_status bfb_copy_h2d(void* d_dst, const void* h_src, size_t bytes, void* stream) {
+    return guarded([&] {
+        if (bytes == 0) return;
+        require(d_dst != nullptr && h_src != nullptr, "copy_h2d: null pointer");
+        BFB_CUDA(cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, asStream(stream)));
+        BFB_CUDA(cudaStreamSynchronize(asStream(stream)));
+    });
+}
+
+bfb_status bfb_copy_d2h(void* h_dst, const void* d_src, size_t bytes, void* stream) {
+    return guarded([&] {
+        if (bytes == 0) return;
+        require(h_dst != nullptr && d_src != nullptr, "copy_d2h: null pointer");
+        BFB_CUDA(cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, asStream(stream)));
+        BFB_CUDA(cudaStreamSynchronize(asStream(stream)));
+    });
+}
+
+bfb_status bfb_copy_d2d(void* d_dst, const void* d_src, size_t bytes, void* stream) {
+    return guarded([&] {
+        if (bytes == 0) return;
+        require(d_dst != nullptr && d_src != nullptr, "copy_d2d: null pointer");
+        BFB_CUDA(cudaMemcpyAsync(d_dst, d_src, bytes, cudaMemcpyDeviceToDevice, asStream(stream)));
+    });
+}
+
+bfb_status bfb_memset_zero(void* d_dst, size_t bytes, void* stream) {
+    return guarded([&] {
+        if (bytes == 0) return;
+        require(d_dst != nullptr, "memset_zero: null pointer");
+        BFB_CUDA(cudaMemsetAsync(d_dst, 0, bytes, asStream(stream)));
+    });
+}
+
+bfb_status bfb_stream_synchronize(void* stream) {
+    return guarded([&] { BFB_CUDA(cudaStreamSynchronize(asStream(stream))); });
+}
+
+bfb_status bfb_embed_pos(const float* d_ids, const float* d_table, const float* d_pos, void* d_out, int32_t out_dtype,
+                         int64_t batch, int64_t seq, int64_t vocab, int64_t dim, int64_t max_seq, int64_t pos_offset,
+                         int32_t* d_oob_count, void* stream) {
+    return guarded([&] {
+        bfb::embedPos(d_ids, d_table, d_pos, d_out, out_dtype, batch, seq, vocab, dim, max_seq, pos_offset, d_oob_count,
+                      asStream(stream));
+    });
+}
+
+bfb_status bfb_add_positional(const float* d_in, const float* d_pos, float* d_out, int64_t batch, int64_t seq,
+                              int64_t dim, int64_t max_seq, int64_t pos_offset, void* stream) {
+    return guarded([&] { bfb::addPositional(d_in, d_pos, d_out, batch, seq, dim, max_seq, pos_offset, asStream(stream)); });
+}
+
+bfb_status bfb_rmsnorm(const void* d_x, int32_t x_dtype, void* d_out, int32_t out_dtype, int64_t rows, int64_t dim,
+                       float eps, void* stream) {
+    return guarded([&] { bfb::rmsnorm(d_x, x_dtype, d_out, out_dtype, rows, dim, eps, asStream(stream)); });
+}
+
+bfb_status bfb_softmax(const float* d_x, float* d_out, int64_t rows, int64_t cols, void* stream) {
+    return guarded([&] { bfb::softmaxRows(d_x, d_out, rows, cols, asStream(stream)); });
+}
+
+bfb_status bfb_elementwise(int32_t op, const float* d_a, const float* d_b, const float* d_c, float* d_out, int64_t n,
+                           int64_t cols, void* stream) {
+    return guarded([&] { bfb::elementwise(op, d_a, d_b, d_c, d_out, n, cols, asStream(stream)); });
+}
+
+bfb_status bfb_cast(const void* d_in, int32_t in_dtype, void* d_out, int32_t out_dtype, int64_t n, float scale,
+                    const float* d_scale, void* stream) {
+    return guarded([&] { bfb::castScaled(d_in, in_dtype, d_out, out_dtype, n, scale, d_scale, asStream(stream)); });
+}
+
+bfb_status bfb_amax(const void* d_in, int32_t in_dtype, int64_t n, float* d_amax, void* stream) {
+    return guarded([&] { bfb::amax(d_in, in_dtype, n, d_amax, asStream(stream)); });
+}
+
+bfb_status bfb_fp8_scale_from_amax(const float* d_amax, float* d_scales, void* stream) {
+    return guarded([&] { bfb::fp8ScaleFromAmax(d_amax, d_scales, asStream(stream)); });
+}
+
+bfb_status bfb_weight_prepare(const float* d_w, void* d_out, int32_t out_dtype, int64_t k, int64_t n, float scale,
+                              const float* d_scale, void* stream) {
+    return guarded([&] { bfb::weightPrepare(d_w, d_out, out_dtype, k, n, scale, d_scale, asStream(stream)); });
+}
+
+bfb_status bfb_gemm(const void* d_a, const void* d_b, void* d_c, int64_t m, int64_t n, int64_t k, int32_t ab_dtype,
+                    int32_t b_layout, int32_t c_dtype, int32_t epilogue, const float* d_bias, const void* d_residual,
+                    float alpha, const float* d_alpha, int32_t round_c_bf16, int32_t* d_status, void* stream) {
+    return guarded([&] {
+        bfb::GemmArgs g;
+        g.a = d_a;
+        g.b = d_b;
+        g.c = d_c;
+        g.m = m;
+        g.n = n;
+        g.k = k;
+        g.abDtype = ab_dtype;
+        g.bLayout = b_layout;
+        g.cDtype = c_dtype;
+        g.epilogue = epilogue;
+        g.bias = d_bias;
+        g.residual = d_residual;
+        g.alpha = alpha;
+        g.dAlpha = d_alpha;
+        g.roundCBf16 = round_c_bf16;
+        g.dStatus = d_status;
+        bfb::gemm(g, asStream(stream));
+    });
+}
+
+bfb_status bfb_matmul_transpose_b(const float* d_a, const float* d_b, float* d_c, int64_t m, int64_t n, int64_t k,
+                                  void* stream) {
+    return guarded([&] { bfb::matmulTransposeB(d_a, d_b, d_c, m, n, k, asStream(stream)); });
+}
+
+bfb_status bfb_attention_fwd(const void* d_q, const void* d_k, const void* d_v, void* d_out, float* d_m, float* d_l,
+                             int32_t dtype, int64_t batch, int64_t new_len, int64_t total_len, int64_t num_heads,
+                             int64_t head_dim, int64_t ld_q, int64_t ld_k, int64_t ld_v, int64_t ld_o, float scale,
+                             int64_t old_len, int32_t causal, int32_t* d_status, void* stream) {
+    return guarded([&] {
+        bfb::AttentionArgs a;
+        a.q = d_q;
+        a.k = d_k;
+        a.v = d_v;
+        a.out = d_out;
+        a.m = d_m;
+        a.l = d_l;
+        a.dtype = dtype;
+        a.batch = batch;
+        a.newLen = new_len;
+        a.totalLen = total_len;
+        a.numHeads = num_heads;
+        a.headDim = head_dim;
+        a.ldQ = ld_q;
+        a.ldK = ld_k;
+        a.ldV = ld_v;
+        a.ldO = ld_o;
+        a.scale = scale;
+        a.oldLen = old_len;
+        a.causal = causal;
+        a.dStatus = d_status;
+        bfb::attentionForward(a, asStream(stream));
+    });
+}
+
+// ---- model ----------------------------------------------------------------------------------------------
+
+static bfb_status createModel(const bfb_op_desc* ops, int32_t n_ops, int64_t input_last_dim, uint32_t seed,
+                              const bfb_precision* precision, bool randomInit, bfb_model** out) {
+    return guarded([&] {
+        require(out != nullptr, "model_create: null result pointer");
+        *out = nullptr;
+        require(ops != nullptr && n_ops > 0, "model_create: the model has no pipeline");
+        std::vector<bfb_op_desc> v(ops, ops + n_ops);
+        auto holder = std::make_unique<bfb_model>();
+        holder->model = std::make_unique<bfb200::Model>(v, input_last_dim, seed, toPolicy(precision), randomInit);
+        *out = holder.release();
+    });
+}
+
+bfb_status bfb_model_create(const bfb_op_desc* ops, int32_t n_ops, int64_t input_last_dim, uint32_t seed,
+                            const bfb_precision* precision, bfb_model** out) {
+    return createModel(ops, n_ops, input_last_dim, seed, precision, true, out);
+}
+
+bfb_status bfb_model_create_uninitialised(const bfb_op_desc* ops, int32_t n_ops, int64_t input_last_dim,
+                                          const bfb_precision* precision, bfb_model** out) {
+    return createModel(ops, n_ops, input_last_dim, 0, precision, false, out);
+}
+
+void bfb_model_destroy(bfb_model* model) { delete model; }
+
+bfb_status bfb_model_set_tensor_parallel(bfb_model* model, int32_t rank, int32_t world) {
+    return guarded([&] {
+        require(model != nullptr, "model: null handle");
+        model->model->setTensorParallel(rank, world);
+        model->params.clear();
+    });
+}
+
+// Parameter metadata comes from the structure alone: no device memory is touched, so these work
+// without a GPU.
+int32_t bfb_model_param_count(const bfb_model* model) {
+    if (model == nullptr) return 0;
+    return static_cast<int32_t>(model->model->parameterCount());
+}
+
+const char* bfb_model_param_name(const bfb_model* model, int32_t index) {
+    if (model == nullptr || index < 0 || index >= bfb_model_param_count(model)) return "";
+    return model->model->parameterName(static_cast<std::size_t>(index)).c_str();
+}
+
+int32_t bfb_model_param_rank(const bfb_model* model, int32_t index) {
+    if (model == nullptr || index < 0 || index >= bfb_model_param_count(model)) return 0;
+    return static_cast<int32_t>(model->model->parameterShape(static_cast<std::size_t>(index)).size());
+}
+
+void bfb_model_param_shape(const bfb_model* model, int32_t index, int64_t* shape_out) {
+    if (model == nullptr || shape_out == nullptr || index < 0 || index >= bfb_model_param_count(model)) return;
+    const auto& s = model->model->parameterShape(static_cast<std::size_t>(index));
+    for (std::size_t i = 0; i < s.size(); ++i) shape_out[i] = static_cast<int64_t>(s[i]);
+}
+
+bfb_status bfb_model_param_set(bfb_model* model, int32_t index, const float* h_values) {
+    return guarded([&] {
+        require(model != nullptr, "model: null handle");
+        require(index >= 0, "model: negative parameter index");
+        requireDevice();
+        model->model->setParameter(static_cast<std::size_t>(index), h_values);
+    });
+}
+
+bfb_status bfb_model_param_get(bfb_model* model, int32_t index, float* h_values) {
+    return guarded([&] {
+        require(model != nullptr, "model: null handle");
+        require(index >= 0, "model: negative parameter index");
+        requireDevice();
+        model->model->getParameter(static_cast<std::size_t>(index), h_values);
+    });
+}
+
+bfb_status bfb_model_load_checkpoint(bfb_model* model, const char* path) {
+    return guarded([&] {
+        require(model != nullptr && path != nullptr, "model: null argument");
+        bfb200::loadCheckpoint(*model->model, path);
+    });
+}
+
+bfb_status bfb_model_save_checkpoint(bfb_model* model, const char* path) {
+    return guarded([&] {
+        require(model != nullptr && path != nullptr, "model: null argument");
+        requireDevice();
+        bfb200::saveCheckpoint(*model->model, path);
+    });
+}
+
+bfb_status bfb_model_forward(bfb_model* model, const float* d_input, const int64_t* shape, int32_t rank,
+                             int32_t input_range_trusted, float** d_out, int64_t* out_shape, int32_t* out_rank,
+                             void* stream) {
+    return guarded([&] {
+        require(model != nullptr && d_out != nullptr && out_shape != nullptr && out_rank != nullptr && shape != nullptr,
+                "model_forward: null argument");
+        require(rank >= 1 && rank <= 8, "model_forward: bad rank");
+        requireDevice();
+        std::vector<std::size_t> dims(shape, shape + rank);
+        // borrow the caller's buffer as a DeviceTensor without owning it
+        bfb200::DeviceTensor borrowed = bfb200::DeviceTensor::borrow(const_cast<float*>(d_input), dims);
+        bfb200::DeviceTensor result;
+        try {
+            result = model->model->forward(borrowed, input_range_trusted != 0, stream);
+        } catch (...) {
+            borrowed.releaseOwnership();
+            throw;
+        }
+        borrowed.releaseOwnership();
+        *out_rank = static_cast<int32_t>(result.rank());
+        for (std::size_t i = 0; i < result.rank(); ++i) out_shape[i] = static_cast<int64_t>(result.dim(i));
+        *d_out = result.releaseOwnership();
+    });
+}
+
+bfb_status bfb_model_forward_host(bfb_model* model, const float* h_input, const int64_t* shape, int32_t rank,
+                                  float* h_out, int64_t* out_shape, int32_t* out_rank) {
+    return guarded([&] {
+        require(model != nullptr && h_input != nullptr && shape != nullptr && out_shape != nullptr && out_rank != nullptr,
+                "model_forward_host: null argument");
+        require(rank >= 1 && rank <= 8, "model_forward_host: bad rank");
+        requireDevice();
+        std::vector<std::size_t> dims(shape, shape + rank);
+        std::size_t count = 1;
+        for (std::size_t d : dims) count *= d;
+        bfb200::DeviceTensor in(dims);
+        if (count > 0) BFB_CUDA(cudaMemcpy(in.data(), h_input, count * sizeof(float), cudaMemcpyHostToDevice));
+        bfb200::DeviceTensor result = model->model->forward(in, false, nullptr);
+        *out_rank = static_cast<int32_t>(result.rank());
+        for (std::size_t i = 0; i < result.rank(); ++i) out_shape[i] = static_cast<int64_t>(result.dim(i));
+        if (h_out != nullptr && result.elementCount() > 0) {
+            BFB_CUDA(cudaMemcpy(h_out, result.data(), result.elementCount() * sizeof(float), cudaMemcpyDeviceToHost));
+        }
+    });
+}
+
+int64_t bfb_launch_count(int32_t reset) {
+    int64_t v = bfb::launchCounter();
+    if (reset != 0) bfb::launchCounter() = 0;
+    return v;
+}
+
+bfb_status bfb_synthetic_input(const bfb_op_desc* ops, int32_t n_ops, const int64_t* input_shape, int32_t rank,
+                               int64_t batch, uint32_t seed, float* h_out) {
+    return guarded([&] {
+        require(ops != nullptr && n_ops > 0 && input_shape != nullptr && h_out != nullptr, "synthetic_input: null argument");
+        require(rank >= 1 && rank <= 8 && batch >= 0, "synthetic_input: bad rank or batch");
+        std::vector<bfb_op_desc> v(ops, ops + n_ops);
+        std::vector<int64_t> shape(input_shape, input_shape + rank);
+        bfb200::HostTensor t = bfb200::Executor(seed).makeSyntheticInput(v, shape, static_cast<std::size_t>(batch));
+        std::memcpy(h_out, t.data.data(), t.data.size() * sizeof(float));
+    });
+}
+
+// ---- tensor parallel ------------------------------------------------------------------------------------
+
+bfb_status bfb_tp_unique_id(void* h_id_128) {
+    return guarded([&] { bfb200::tpUniqueId(h_id_128); });
+}
+
+bfb_status bfb_tp_init(const void* h_id_128, int32_t rank, int32_t world) {
+    return guarded([&] {
+        requireDevice();
+        bfb200::tpInit(h_id_128, rank, world);
+    });
+}
+
+bfb_status bfb_tp_allreduce_sum(void* d_buf, int64_t count, int32_t dtype, void* stream) {
+    return guarded([&] { bfb200::tpAllReduceSum(d_buf, count, dtype, stream); });
+}
+
+bfb_status bfb_tp_destroy(void) {
+    return guarded([&] { bfb200::tpDestroy(); });
+}
+
+}  // extern "C"

@@ -1,0 +1,84 @@
+// Shared host-side plumbing for the C ABI: per-thread error text, status mapping, launch counting.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <stdexcept>
+#include <string>
+
+#include "../../include/bfb200.h"
+
+namespace bfb {
+
+// Errors follow the reference's convention so the C++ layer can let them propagate unchanged:
+// argument problems are std::invalid_argument, everything else std::runtime_error (with the BFB_*
+// status attached for the C boundary).
+struct InvalidArgument : std::invalid_argument {
+    using std::invalid_argument::invalid_argument;
+};
+struct RuntimeFailure : std::runtime_error {
+    bfb_status status;
+    RuntimeFailure(bfb_status s, const std::string& t) : std::runtime_error(t), status(s) {}
+};
+
+std::string& lastErrorSlot();
+int64_t& launchCounter();
+
+inline void noteLaunch(int n = 1) { launchCounter() += n; }
+
+[[noreturn]] inline void fail(bfb_status s, const std::string& text) {
+    if (s == BFB_INVALID_ARGUMENT) throw InvalidArgument(text);
+    throw RuntimeFailure(s, text);
+}
+
+inline void require(bool ok, const char* text) {
+    if (!ok) fail(BFB_INVALID_ARGUMENT, text);
+}
+
+inline void cudaCheck(cudaError_t e, const char* what, const char* file, int line) {
+    if (e != cudaSuccess) {
+        fail(BFB_CUDA_ERROR, std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ") at " +
+                                 file + ":" + std::to_string(line));
+    }
+}
+#define BFB_CUDA(expr) ::bfb::cudaCheck((expr), #expr, __FILE__, __LINE__)
+#define BFB_LAUNCH_CHECK() ::bfb::cudaCheck(cudaGetLastError(), "kernel launch", __FILE__, __LINE__)
+
+// Runs `fn`, converting exceptions into a status + last-error text.
+template <typename Fn>
+bfb_status guarded(Fn&& fn) noexcept {
+    try {
+        fn();
+        return BFB_OK;
+    } catch (const RuntimeFailure& e) {
+        lastErrorSlot() = e.what();
+        return e.status;
+    } catch (const std::invalid_argument& e) {
+        lastErrorSlot() = e.what();
+        return BFB_INVALID_ARGUMENT;
+    } catch (const std::exception& e) {
+        lastErrorSlot() = e.what();
+        return BFB_CUDA_ERROR;
+    } catch (...) {
+        lastErrorSlot() = "unknown failure";
+        return BFB_CUDA_ERROR;
+    }
+}
+
+inline cudaStream_t asStream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+inline size_t dtypeBytes(int32_t dtype) {
+    switch (dtype) {
+        case BFB_F32: return 4;
+        case BFB_BF16: return 2;
+        case BFB_FP8_E4M3: return 1;
+        default: fail(BFB_INVALID_ARGUMENT, "unknown element format");
+    }
+}
+
+// Number of SMs of the current device (cached per device).
+int smCount();
+
+}  // namespace bfb

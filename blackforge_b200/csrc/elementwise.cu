@@ -1,0 +1,579 @@
+// HBM-bound kernels of the forward path: token gather + positions, rmsnorm, softmax, elementwise
+// ops, format conversion, amax and the one-off weight transpose. All are single-pass over their
+// inputs, 128-bit vectorised where alignment allows, and sized to a multiple of the SM count.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include <algorithm>
+#include <cmath>
+
+#include "common.cuh"
+#include "kernels.hpp"
+
+namespace bfb {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+inline int gridFor(int64_t work, int perBlock, int wavesCap = 32) {
+    int64_t blocks = (work + perBlock - 1) / perBlock;
+    int64_t cap = static_cast<int64_t>(smCount()) * wavesCap;
+    return static_cast<int>(std::max<int64_t>(1, std::min(blocks, cap)));
+}
+
+__device__ __forceinline__ float bf16Round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__device__ __forceinline__ float warpSum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warpMax(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    return v;
+}
+
+// Block-wide sum / max through one shared array of 32 floats.
+__device__ __forceinline__ float blockSum(float v, float* scratch) {
+    v = warpSum(v);
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    int nw = (blockDim.x + 31) >> 5;
+    float t = (threadIdx.x < nw) ? scratch[threadIdx.x] : 0.0f;
+    if (warp == 0) t = warpSum(t);
+    if (threadIdx.x == 0) scratch[0] = t;
+    __syncthreads();
+    return scratch[0];
+}
+__device__ __forceinline__ float blockMax(float v, float* scratch) {
+    v = warpMax(v);
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    int nw = (blockDim.x + 31) >> 5;
+    float t = (threadIdx.x < nw) ? scratch[threadIdx.x] : -INFINITY;
+    if (warp == 0) t = warpMax(t);
+    if (threadIdx.x == 0) scratch[0] = t;
+    __syncthreads();
+    return scratch[0];
+}
+
+// ---- embedding gather + positional add --------------------------------------------------------
+// One block walks token rows; a row of `dim` floats is copied with float4 loads when dim % 4 == 0.
+template <bool kVec, bool kOutBf16>
+__global__ void embedPosKernel(const float* __restrict__ ids, const float* __restrict__ table,
+                               const float* __restrict__ pos, void* __restrict__ outRaw, int64_t tokens, int64_t seq,
+                               int64_t vocab, int64_t dim, int64_t posOffset, int* oobCount) {
+    for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
+        float idf = ids[t];
+        bool finite = fabsf(idf) < 2147483648.0f;  // false for NaN / inf too
+        long long id = finite ? static_cast<long long>(lroundf(idf)) : -1;
+        bool ok = id >= 0 && id < vocab;
+        if (!ok && threadIdx.x == 0 && oobCount != nullptr) atomicAdd(oobCount, 1);
+        const float* src = table + static_cast<int64_t>(ok ? id : 0) * dim;
+        const float* prow = pos != nullptr ? pos + (posOffset + t % seq) * dim : nullptr;
+        if constexpr (kVec) {
+            int64_t nv = dim >> 2;
+            for (int64_t i = threadIdx.x; i < nv; i += blockDim.x) {
+                float4 v = ok ? __ldg(reinterpret_cast<const float4*>(src) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                if (prow != nullptr) {
+                    float4 p = __ldg(reinterpret_cast<const float4*>(prow) + i);
+                    v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+                }
+                if constexpr (kOutBf16) {
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y);
+                    __nv_bfloat162 hi = __floats2bfloat162_rn(v.z, v.w);
+                    uint2 packed;
+                    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                    reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(outRaw) + t * dim)[i] = packed;
+                } else {
+                    reinterpret_cast<float4*>(static_cast<float*>(outRaw) + t * dim)[i] = v;
+                }
+            }
+        } else {
+            for (int64_t i = threadIdx.x; i < dim; i += blockDim.x) {
+                float v = ok ? src[i] : 0.0f;
+                if (prow != nullptr) v += prow[i];
+                if constexpr (kOutBf16) {
+                    static_cast<__nv_bfloat16*>(outRaw)[t * dim + i] = __float2bfloat16_rn(v);
+                } else {
+                    static_cast<float*>(outRaw)[t * dim + i] = v;
+                }
+            }
+        }
+    }
+}
+
+__global__ void addPositionalKernel(const float* __restrict__ in, const float* __restrict__ pos,
+                                    float* __restrict__ out, int64_t total, int64_t seq, int64_t dim,
+                                    int64_t posOffset) {
+    int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        int64_t tok = i / dim;
+        int64_t d = i - tok * dim;
+        out[i] = in[i] + pos[(posOffset + tok % seq) * dim + d];
+    }
+}
+
+// ---- rmsnorm ----------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+    float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <>
+__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+    uint2 t = *reinterpret_cast<const uint2*>(p);
+    __nv_bfloat162 lo = *reinterpret_cast<__nv_bfloat162*>(&t.x);
+    __nv_bfloat162 hi = *reinterpret_cast<__nv_bfloat162*>(&t.y);
+    v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[3] = __high2float(hi);
+}
+template <typename T>
+__device__ __forceinline__ void store4(T* p, const float (&v)[4]);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 t;
+    t.x = *reinterpret_cast<uint32_t*>(&lo);
+    t.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = t;
+}
+
+// Row held in registers (read once). kGroup threads cooperate on one row: 32 (a warp) or the whole
+// block. Each thread keeps up to kMaxVec groups of 4 elements.
+template <typename TIn, typename TOut, int kMaxVec, bool kBlockPerRow>
+__global__ void rmsnormKernel(const TIn* __restrict__ x, TOut* __restrict__ out, int64_t rows, int64_t dim, float eps) {
+    __shared__ float scratch[32];
+    const int group = kBlockPerRow ? blockDim.x : 32;
+    const int lane = kBlockPerRow ? threadIdx.x : (threadIdx.x & 31);
+    const int64_t rowsPerBlock = kBlockPerRow ? 1 : (blockDim.x >> 5);
+    const int64_t firstRow = static_cast<int64_t>(blockIdx.x) * rowsPerBlock + (kBlockPerRow ? 0 : (threadIdx.x >> 5));
+    const int64_t rowStride = static_cast<int64_t>(gridDim.x) * rowsPerBlock;
+    const int64_t nv = dim >> 2;
+    // Block-per-row: every thread of the block walks the same rows, so barriers stay uniform.
+    for (int64_t row = firstRow; row < rows; row += rowStride) {
+        const TIn* src = x + row * dim;
+        float vals[kMaxVec][4];
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kMaxVec; ++j) {
+            int64_t i = lane + static_cast<int64_t>(j) * group;
+            if (i < nv) {
+                load4<TIn>(src + i * 4, vals[j]);
+                ss += vals[j][0] * vals[j][0] + vals[j][1] * vals[j][1] + vals[j][2] * vals[j][2] +
+                      vals[j][3] * vals[j][3];
+            }
+        }
+        float total = kBlockPerRow ? blockSum(ss, scratch) : warpSum(ss);
+        float rms = sqrtf(total / static_cast<float>(dim) + eps);
+        TOut* dst = out + row * dim;
+#pragma unroll
+        for (int j = 0; j < kMaxVec; ++j) {
+            int64_t i = lane + static_cast<int64_t>(j) * group;
+            if (i < nv) {
+                float o[4] = {vals[j][0] / rms, vals[j][1] / rms, vals[j][2] / rms, vals[j][3] / rms};
+                store4<TOut>(dst + i * 4, o);
+            }
+        }
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ float toFloat(T v);
+template <>
+__device__ __forceinline__ float toFloat<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float toFloat<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T fromFloat(float v);
+template <>
+__device__ __forceinline__ float fromFloat<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 fromFloat<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Any dim, two passes over the row (second pass hits L1/L2).
+template <typename TIn, typename TOut>
+__global__ void rmsnormGenericKernel(const TIn* __restrict__ x, TOut* __restrict__ out, int64_t rows, int64_t dim,
+                                     float eps) {
+    __shared__ float scratch[32];
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const TIn* src = x + row * dim;
+        float ss = 0.0f;
+        for (int64_t i = threadIdx.x; i < dim; i += blockDim.x) {
+            float v = toFloat<TIn>(src[i]);
+            ss += v * v;
+        }
+        float total = blockSum(ss, scratch);
+        float rms = sqrtf(total / static_cast<float>(dim) + eps);
+        for (int64_t i = threadIdx.x; i < dim; i += blockDim.x) {
+            out[row * dim + i] = fromFloat<TOut>(toFloat<TIn>(src[i]) / rms);
+        }
+    }
+}
+
+template <typename TIn, typename TOut>
+void rmsnormDispatch(const TIn* x, TOut* out, int64_t rows, int64_t dim, float eps, cudaStream_t stream) {
+    bool aligned = (dim % 4 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
+                   (reinterpret_cast<uintptr_t>(out) % 16 == 0);
+    if (aligned && dim <= 1024) {
+        int rowsPerBlock = kThreads / 32;
+        int grid = gridFor(rows, rowsPerBlock, 16);
+        rmsnormKernel<TIn, TOut, 8, false><<<grid, kThreads, 0, stream>>>(x, out, rows, dim, eps);
+    } else if (aligned && dim <= 8192) {
+        int grid = gridFor(rows, 1, 16);
+        rmsnormKernel<TIn, TOut, 8, true><<<grid, kThreads, 0, stream>>>(x, out, rows, dim, eps);
+    } else {
+        int grid = gridFor(rows, 1, 16);
+        rmsnormGenericKernel<TIn, TOut><<<grid, kThreads, 0, stream>>>(x, out, rows, dim, eps);
+    }
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
+
+// ---- softmax ----------------------------------------------------------------------------------
+__global__ void softmaxKernel(const float* __restrict__ x, float* __restrict__ out, int64_t rows, int64_t cols) {
+    __shared__ float scratch[32];
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float* src = x + row * cols;
+        float mx = -INFINITY;
+        for (int64_t i = threadIdx.x; i < cols; i += blockDim.x) mx = fmaxf(mx, src[i]);
+        mx = blockMax(mx, scratch);
+        float sum = 0.0f;
+        for (int64_t i = threadIdx.x; i < cols; i += blockDim.x) sum += expf(src[i] - mx);
+        sum = blockSum(sum, scratch);
+        for (int64_t i = threadIdx.x; i < cols; i += blockDim.x) out[row * cols + i] = expf(src[i] - mx) / sum;
+    }
+}
+
+// ---- elementwise ------------------------------------------------------------------------------
+__device__ __forceinline__ float siluF(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float geluF(float x) {
+    float inner = 0.7978845608f * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (1.0f + tanhf(inner));
+}
+
+template <int kOp>
+__global__ void elementwiseKernel(const float* __restrict__ a, const float* __restrict__ b,
+                                  const float* __restrict__ c, float* __restrict__ out, int64_t n, int64_t cols) {
+    int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float v = a[i];
+        if constexpr (kOp == BFB_EW_ADD) v = v + b[i];
+        if constexpr (kOp == BFB_EW_ADD_BIAS) v = v + b[i % cols];
+        if constexpr (kOp == BFB_EW_ADD_BIAS_SILU) v = siluF(v + b[i % cols]);
+        if constexpr (kOp == BFB_EW_ADD_BIAS_RESIDUAL) v = v + b[i % cols] + c[i];
+        if constexpr (kOp == BFB_EW_SILU) v = siluF(v);
+        if constexpr (kOp == BFB_EW_RELU) v = v > 0.0f ? v : 0.0f;
+        if constexpr (kOp == BFB_EW_GELU) v = geluF(v);
+        out[i] = v;
+    }
+}
+
+__global__ void roundBf16Kernel(float* x, int64_t n) {
+    int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float v = x[i];
+        x[i] = isfinite(v) ? bf16Round(v) : v;
+    }
+}
+
+// ---- conversion -------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float loadAs(const void* p, int64_t i);
+template <>
+__device__ __forceinline__ float loadAs<float>(const void* p, int64_t i) { return static_cast<const float*>(p)[i]; }
+template <>
+__device__ __forceinline__ float loadAs<__nv_bfloat16>(const void* p, int64_t i) {
+    return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+}
+template <>
+__device__ __forceinline__ float loadAs<__nv_fp8_e4m3>(const void* p, int64_t i) {
+    return static_cast<float>(static_cast<const __nv_fp8_e4m3*>(p)[i]);
+}
+template <typename T>
+__device__ __forceinline__ void storeAs(void* p, int64_t i, float v);
+template <>
+__device__ __forceinline__ void storeAs<float>(void* p, int64_t i, float v) { static_cast<float*>(p)[i] = v; }
+template <>
+__device__ __forceinline__ void storeAs<__nv_bfloat16>(void* p, int64_t i, float v) {
+    static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ void storeAs<__nv_fp8_e4m3>(void* p, int64_t i, float v) {
+    // saturating round-to-nearest-even conversion (values beyond +-448 clamp)
+    static_cast<__nv_fp8_storage_t*>(p)[i] = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+
+template <typename TIn, typename TOut>
+__global__ void castKernel(const void* __restrict__ in, void* __restrict__ out, int64_t n, float scale,
+                           const float* __restrict__ dScale) {
+    float s = dScale != nullptr ? *dScale : scale;
+    int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        storeAs<TOut>(out, i, loadAs<TIn>(in, i) * s);
+    }
+}
+
+// bf16 -> e4m3, 8 elements per thread (128-bit loads, 64-bit stores): the hot conversion of the fp8 path.
+__global__ void castBf16ToFp8Vec(const uint4* __restrict__ in, uint2* __restrict__ out, int64_t nVec, float scale,
+                                 const float* __restrict__ dScale) {
+    float s = dScale != nullptr ? *dScale : scale;
+    int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nVec; i += stride) {
+        uint4 raw = in[i];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float2 f = __bfloat1622float2(h[j]);
+            __nv_fp8x2_storage_t two = __nv_cvt_float2_to_fp8x2(make_float2(f.x * s, f.y * s), __NV_SATFINITE, __NV_E4M3);
+            packed[j >> 1] |= static_cast<uint32_t>(two) << ((j & 1) * 16);
+        }
+        out[i] = make_uint2(packed[0], packed[1]);
+    }
+}
+
+template <typename TIn>
+__global__ void amaxKernel(const void* __restrict__ in, int64_t n, float* amaxOut) {
+    __shared__ float scratch[32];
+    float m = 0.0f;
+    int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        m = fmaxf(m, fabsf(loadAs<TIn>(in, i)));
+    }
+    m = blockMax(m, scratch);
+    // non-negative floats order like their bit patterns
+    if (threadIdx.x == 0) atomicMax(reinterpret_cast<int*>(amaxOut), __float_as_int(m));
+}
+
+__global__ void fp8ScaleKernel(const float* amaxIn, float* scales) {
+    float a = *amaxIn;
+    float s = a > 0.0f ? 448.0f / a : 1.0f;
+    scales[0] = s;
+    scales[1] = 1.0f / s;
+}
+
+__global__ void fp8ActScaleKernel(const float* amaxIn, float* out, const float* weightInverse) {
+    float a = *amaxIn;
+    float s = a > 0.0f ? 448.0f / a : 1.0f;
+    out[0] = s;
+    out[1] = 1.0f / s;
+    out[2] = (1.0f / s) * (*weightInverse);
+}
+
+// W[K,N] f32 -> W^T[N,K] in TOut, through a padded 32x32 shared tile.
+template <typename TOut>
+__global__ void transposeCastKernel(const float* __restrict__ w, void* __restrict__ out, int64_t k, int64_t n,
+                                    float scale, const float* __restrict__ dScale) {
+    __shared__ float tile[32][33];
+    float s = dScale != nullptr ? *dScale : scale;
+    int64_t tilesN = (n + 31) / 32;
+    int64_t tilesK = (k + 31) / 32;
+    for (int64_t t = blockIdx.x; t < tilesN * tilesK; t += gridDim.x) {
+        int64_t tk = t / tilesN, tn = t % tilesN;
+        __syncthreads();
+        for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+            int64_t kk = tk * 32 + r, nn = tn * 32 + threadIdx.x;
+            tile[r][threadIdx.x] = (kk < k && nn < n) ? w[kk * n + nn] : 0.0f;
+        }
+        __syncthreads();
+        for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+            int64_t nn = tn * 32 + r, kk = tk * 32 + threadIdx.x;
+            if (nn < n && kk < k) storeAs<TOut>(out, nn * k + kk, tile[threadIdx.x][r] * s);
+        }
+    }
+}
+
+}  // namespace
+
+// ---- host entry points ------------------------------------------------------------------------
+
+void embedPos(const float* ids, const float* table, const float* pos, void* out, int outDtype, int64_t batch,
+              int64_t seq, int64_t vocab, int64_t dim, int64_t maxSeq, int64_t posOffset, int* oobCount,
+              cudaStream_t stream) {
+    require(batch >= 0 && seq >= 0 && vocab > 0 && dim > 0, "embed_pos: sizes must be positive");
+    require(outDtype == BFB_F32 || outDtype == BFB_BF16, "embed_pos: output format must be f32 or bf16");
+    if (pos != nullptr) require(posOffset >= 0 && posOffset + seq <= maxSeq, "embed_pos: sequence exceeds maxSeqLen");
+    int64_t tokens = batch * seq;
+    if (tokens == 0) return;
+    require(ids != nullptr && table != nullptr && out != nullptr, "embed_pos: null pointer");
+    bool vec = dim % 4 == 0 && reinterpret_cast<uintptr_t>(table) % 16 == 0 &&
+               reinterpret_cast<uintptr_t>(out) % 16 == 0 && (pos == nullptr || reinterpret_cast<uintptr_t>(pos) % 16 == 0);
+    int threads = static_cast<int>(std::min<int64_t>(256, std::max<int64_t>(32, ((vec ? dim / 4 : dim) + 31) / 32 * 32)));
+    int grid = gridFor(tokens, 1, 16);
+    bool bf = outDtype == BFB_BF16;
+#define BFB_EMBED(V, B) \
+    embedPosKernel<V, B><<<grid, threads, 0, stream>>>(ids, table, pos, out, tokens, seq, vocab, dim, posOffset, oobCount)
+    if (vec && bf) BFB_EMBED(true, true);
+    else if (vec) BFB_EMBED(true, false);
+    else if (bf) BFB_EMBED(false, true);
+    else BFB_EMBED(false, false);
+#undef BFB_EMBED
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
+
+void addPositional(const float* in, const float* pos, float* out, int64_t batch, int64_t seq, int64_t dim,
+                   int64_t maxSeq, int64_t posOffset, cudaStream_t stream) {
+    require(batch >= 0 && seq >= 0 && dim > 0, "add_positional: bad sizes");
+    require(posOffset >= 0 && posOffset + seq <= maxSeq, "add_positional: sequence exceeds maxSeqLen");
+    int64_t total = batch * seq * dim;
+    if (total == 0) return;
+    require(in != nullptr && pos != nullptr && out != nullptr, "add_positional: null pointer");
+    addPositionalKernel<<<gridFor(total, kThreads), kThreads, 0, stream>>>(in, pos, out, total, seq, dim, posOffset);
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
+
+void rmsnorm(const void* x, int xDtype, void* out, int outDtype, int64_t rows, int64_t dim, float eps,
+             cudaStream_t stream) {
+    require(rows >= 0 && dim > 0, "rmsnorm: bad sizes");
+    require((xDtype == BFB_F32 || xDtype == BFB_BF16) && (outDtype == BFB_F32 || outDtype == BFB_BF16),
+            "rmsnorm: formats must be f32 or bf16");
+    if (rows == 0) return;
+    require(x != nullptr && out != nullptr, "rmsnorm: null pointer");
+    using bf = __nv_bfloat16;
+    if (xDtype == BFB_F32 && outDtype == BFB_F32)
+        rmsnormDispatch(static_cast<const float*>(x), static_cast<float*>(out), rows, dim, eps, stream);
+    else if (xDtype == BFB_F32)
+        rmsnormDispatch(static_cast<const float*>(x), static_cast<bf*>(out), rows, dim, eps, stream);
+    else if (outDtype == BFB_F32)
+        rmsnormDispatch(static_cast<const bf*>(x), static_cast<float*>(out), rows, dim, eps, stream);
+    else
+        rmsnormDispatch(static_cast<const bf*>(x), static_cast<bf*>(out), rows, dim, eps, stream);
+}
+
+void softmaxRows(const float* x, float* out, int64_t rows, int64_t cols, cudaStream_t stream) {
+    require(rows >= 0 && cols > 0, "softmax: bad sizes");
+    if (rows == 0) return;
+    require(x != nullptr && out != nullptr, "softmax: null pointer");
+    softmaxKernel<<<gridFor(rows, 1, 16), kThreads, 0, stream>>>(x, out, rows, cols);
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
+
+void elementwise(int op, const float* a, const float* b, const float* c, float* out, int64_t n, int64_t cols,
+                 cudaStream_t stream) {
+    require(n >= 0, "elementwise: negative size");
+    require(op >= BFB_EW_ADD && op <= BFB_EW_GELU, "elementwise: unknown op");
+    if (n == 0) return;
+    require(a != nullptr && out != nullptr, "elementwise: null pointer");
+    bool needsB = op <= BFB_EW_ADD_BIAS_RESIDUAL;
+    if (needsB) require(b != nullptr, "elementwise: second operand missing");
+    if (op == BFB_EW_ADD_BIAS || op == BFB_EW_ADD_BIAS_SILU || op == BFB_EW_ADD_BIAS_RESIDUAL)
+        require(cols > 0 && n % cols == 0, "elementwise: bias length must divide the element count");
+    if (op == BFB_EW_ADD_BIAS_RESIDUAL) require(c != nullptr, "elementwise: residual missing");
+    int grid = gridFor(n, kThreads);
+    switch (op) {
+        case BFB_EW_ADD: elementwiseKernel<BFB_EW_ADD><<<grid, kThreads, 0, stream>>>(a, b, c, out, n, cols); break;
+        case BFB_EW_ADD_BIAS: elementwiseKernel<BFB_EW_ADD_BIAS><<<grid, kThreads, 0, stream>>>(a, b, c, out, n, cols); break;
+        case BFB_EW_ADD_BIAS_SILU: elementwiseKernel<BFB_EW_ADD_BIAS_SILU><<<grid, kThreads, 0, stream>>>(a, b, c, out, n, cols); break;
+        case BFB_EW_ADD_BIAS_RESIDUAL: elementwiseKernel<BFB_EW_ADD_BIAS_RESIDUAL><<<grid, kThreads, 0, stream>>>(a, b, c, out, n, cols); break;
+        case BFB_EW_SILU: elementwiseKernel<BFB_EW_SILU><<<grid, kThreads, 0, stream>>>(a, b, c, out, n, cols); break;
+        case BFB_EW_RELU: elementwiseKernel<BFB_EW_RELU><<<grid, kThreads, 0, stream>>>(a, b, c, out, n, cols); break;
+        default: elementwiseKernel<BFB_EW_GELU><<<grid, kThreads, 0, stream>>>(a, b, c, out, n, cols); break;
+    }
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
+
+void roundBf16InPlace(float* x, int64_t n, cudaStream_t stream) {
+    if (n <= 0) return;
+    roundBf16Kernel<<<gridFor(n, kThreads), kThreads, 0, stream>>>(x, n);
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
+
+void castScaled(const void* in, int inDtype, void* out, int outDtype, int64_t n, float scale, const float* dScale,
+                cudaStream_t stream) {
+    require(n >= 0, "cast: negative size");
+    dtypeBytes(inDtype);
+    dtypeBytes(outDtype);
+    if (n == 0) return;
+    require(in != nullptr && out != nullptr, "cast: null pointer");
+    using bf = __nv_bfloat16;
+    using f8 = __nv_fp8_e4m3;
+    if (inDtype == BFB_BF16 && outDtype == BFB_FP8_E4M3 && n % 8 == 0 && reinterpret_cast<uintptr_t>(in) % 16 == 0 &&
+        reinterpret_cast<uintptr_t>(out) % 8 == 0) {
+        int64_t nv = n / 8;
+        castBf16ToFp8Vec<<<gridFor(nv, kThreads), kThreads, 0, stream>>>(static_cast<const uint4*>(in),
+                                                                          static_cast<uint2*>(out), nv, scale, dScale);
+        BFB_LAUNCH_CHECK();
+        noteLaunch();
+        return;
+    }
+    int grid = gridFor(n, kThreads);
+#define BFB_CAST(TI, TO) castKernel<TI, TO><<<grid, kThreads, 0, stream>>>(in, out, n, scale, dScale)
+    int key = inDtype * 3 + outDtype;
+    switch (key) {
+        case BFB_F32 * 3 + BFB_F32: BFB_CAST(float, float); break;
+        case BFB_F32 * 3 + BFB_BF16: BFB_CAST(float, bf); break;
+        case BFB_F32 * 3 + BFB_FP8_E4M3: BFB_CAST(float, f8); break;
+        case BFB_BF16 * 3 + BFB_F32: BFB_CAST(bf, float); break;
+        case BFB_BF16 * 3 + BFB_BF16: BFB_CAST(bf, bf); break;
+        case BFB_BF16 * 3 + BFB_FP8_E4M3: BFB_CAST(bf, f8); break;
+        case BFB_FP8_E4M3 * 3 + BFB_F32: BFB_CAST(f8, float); break;
+        case BFB_FP8_E4M3 * 3 + BFB_BF16: BFB_CAST(f8, bf); break;
+        default: BFB_CAST(f8, f8); break;
+    }
+#undef BFB_CAST
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
+
+void amax(const void* in, int inDtype, int64_t n, float* dAmax, cudaStream_t stream) {
+    require(n >= 0, "amax: negative size");
+    require(inDtype == BFB_F32 || inDtype == BFB_BF16, "amax: input must be f32 or bf16");
+    require(dAmax != nullptr, "amax: null result pointer");
+    if (n == 0) return;
+    require(in != nullptr, "amax: null pointer");
+    int grid = gridFor(n, kThreads * 8, 4);
+    if (inDtype == BFB_F32) amaxKernel<float><<<grid, kThreads, 0, stream>>>(in, n, dAmax);
+    else amaxKernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(in, n, dAmax);
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
+
+void fp8ScaleFromAmax(const float* dAmax, float* dScales, cudaStream_t stream) {
+    require(dAmax != nullptr && dScales != nullptr, "fp8_scale_from_amax: null pointer");
+    fp8ScaleKernel<<<1, 1, 0, stream>>>(dAmax, dScales);
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
+
+void fp8ActScale(const float* dAmax, float* out, const float* dWeightInverse, cudaStream_t stream) {
+    require(dAmax != nullptr && out != nullptr && dWeightInverse != nullptr, "fp8_act_scale: null pointer");
+    fp8ActScaleKernel<<<1, 1, 0, stream>>>(dAmax, out, dWeightInverse);
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
+
+void weightPrepare(const float* w, void* out, int outDtype, int64_t k, int64_t n, float scale, const float* dScale,
+                   cudaStream_t stream) {
+    require(k > 0 && n > 0, "weight_prepare: bad sizes");
+    require(w != nullptr && out != nullptr, "weight_prepare: null pointer");
+    dtypeBytes(outDtype);
+    int64_t tiles = ((n + 31) / 32) * ((k + 31) / 32);
+    int grid = gridFor(tiles, 1, 32);
+    dim3 block(32, 8);
+    if (outDtype == BFB_F32) transposeCastKernel<float><<<grid, block, 0, stream>>>(w, out, k, n, scale, dScale);
+    else if (outDtype == BFB_BF16) transposeCastKernel<__nv_bfloat16><<<grid, block, 0, stream>>>(w, out, k, n, scale, dScale);
+    else transposeCastKernel<__nv_fp8_e4m3><<<grid, block, 0, stream>>>(w, out, k, n, scale, dScale);
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
+
+}  // namespace bfb

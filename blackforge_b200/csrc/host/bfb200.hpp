@@ -1,0 +1,184 @@
+// C++ host layer: the reference's backend operator interface re-created on top of the B200 kernels.
+//
+// Same names, argument meaning, ownership and error behaviour as blackforge::backend::cuda
+// (include/blackforge/backend/cuda/{device_tensor,ops,fused_attention,model,executor,checkpoint,
+// device_pool}.hpp in the reference project), in namespace bfb200 so both can be linked side by
+// side. Shape / range violations throw std::invalid_argument, CUDA and file problems throw
+// std::runtime_error. Tensors at this boundary are fp32 (DeviceTensor stores fp32 only, as in the
+// reference); reduced-precision formats live inside Model::forward.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <memory>
+#include <optional>
+#include <string>
+#include <vector>
+
+#include "../../../include/bfb200.h"
+
+namespace bfb200 {
+
+// Host tensor: shape + row-major fp32 data (stand-in for blackforge::runtime::Tensor).
+struct HostTensor {
+    std::vector<std::size_t> shape;
+    std::vector<float> data;
+    [[nodiscard]] std::size_t elementCount() const;
+};
+
+// include/blackforge/backend/cuda/device_pool.hpp:47-54
+void* devicePoolAcquire(std::size_t bytes);
+void devicePoolRelease(void* ptr, std::size_t bytes);
+
+// include/blackforge/backend/cuda/device_tensor.hpp:10-75 — move-only RAII fp32 buffer from the pool.
+class DeviceTensor {
+public:
+    DeviceTensor() = default;
+    explicit DeviceTensor(std::vector<std::size_t> shape);
+    ~DeviceTensor();
+    DeviceTensor(const DeviceTensor&) = delete;
+    DeviceTensor& operator=(const DeviceTensor&) = delete;
+    DeviceTensor(DeviceTensor&& other) noexcept;
+    DeviceTensor& operator=(DeviceTensor&& other) noexcept;
+
+    static DeviceTensor fromHost(const HostTensor& host);
+    static DeviceTensor zeros(std::vector<std::size_t> shape);
+    [[nodiscard]] HostTensor toHost() const;
+    [[nodiscard]] DeviceTensor clone() const;
+    [[nodiscard]] DeviceTensor reshaped(std::vector<std::size_t> newShape) &&;
+
+    [[nodiscard]] float* data() { return data_; }
+    [[nodiscard]] const float* data() const { return data_; }
+    [[nodiscard]] const std::vector<std::size_t>& shape() const { return shape_; }
+    [[nodiscard]] std::size_t rank() const { return shape_.size(); }
+    [[nodiscard]] std::size_t dim(std::size_t axis) const { return shape_.at(axis); }
+    [[nodiscard]] std::size_t elementCount() const;
+    // Gives up ownership (for handing a result across the C ABI); release with devicePoolRelease.
+    float* releaseOwnership();
+    // Wraps memory owned by someone else; the caller must call releaseOwnership() before it dies.
+    static DeviceTensor borrow(float* data, std::vector<std::size_t> shape);
+
+private:
+    float* data_ = nullptr;
+    std::vector<std::size_t> shape_;
+};
+
+// ---- include/blackforge/backend/cuda/ops.hpp ------------------------------------------------------
+DeviceTensor add(const DeviceTensor& a, const DeviceTensor& b);
+DeviceTensor addBias(const DeviceTensor& input, const DeviceTensor& bias);
+DeviceTensor addBiasSilu(const DeviceTensor& gemmOutput, const DeviceTensor& bias);
+DeviceTensor addBiasResidual(const DeviceTensor& gemmOutput, const DeviceTensor& bias, const DeviceTensor& residual);
+DeviceTensor matmul(const DeviceTensor& a, const DeviceTensor& b);
+DeviceTensor matmulTransposeB(const DeviceTensor& a, const DeviceTensor& b);
+DeviceTensor matmulBf16(const DeviceTensor& a, const DeviceTensor& b);
+DeviceTensor matmulBf16CachedWeight(const DeviceTensor& a, const DeviceTensor& b);
+void invalidateBf16WeightCache();
+// New: e4m3 operands with per-tensor amax scales, fp32 accumulate (the declared `compute fp8.e4m3`).
+DeviceTensor matmulFp8(const DeviceTensor& a, const DeviceTensor& b);
+DeviceTensor silu(const DeviceTensor& input);
+DeviceTensor relu(const DeviceTensor& input);
+DeviceTensor gelu(const DeviceTensor& input);
+DeviceTensor rmsnorm(const DeviceTensor& input);
+DeviceTensor softmax(const DeviceTensor& input);
+DeviceTensor embeddingLookup(const DeviceTensor& tokenIds, const DeviceTensor& table);
+DeviceTensor embeddingLookupPreValidated(const DeviceTensor& tokenIds, const DeviceTensor& table);
+DeviceTensor addPositionalEmbedding(const DeviceTensor& input, const DeviceTensor& table);
+DeviceTensor addPositionalEmbeddingAt(const DeviceTensor& input, const DeviceTensor& table, std::size_t offset);
+DeviceTensor linear(const DeviceTensor& input, const DeviceTensor& weight, const DeviceTensor& bias);
+DeviceTensor linearBf16(const DeviceTensor& input, const DeviceTensor& weight, const DeviceTensor& bias);
+DeviceTensor feedForward(const DeviceTensor& input, const DeviceTensor& w1, const DeviceTensor& b1,
+                         const DeviceTensor& w2, const DeviceTensor& b2);
+DeviceTensor feedForwardBf16(const DeviceTensor& input, const DeviceTensor& w1, const DeviceTensor& b1,
+                             const DeviceTensor& w2, const DeviceTensor& b2);
+DeviceTensor selfAttention(const DeviceTensor& input, const DeviceTensor& wq, const DeviceTensor& wk,
+                           const DeviceTensor& wv, const DeviceTensor& wout, std::size_t numHeads);
+DeviceTensor selfAttentionBf16(const DeviceTensor& input, const DeviceTensor& wq, const DeviceTensor& wk,
+                               const DeviceTensor& wv, const DeviceTensor& wout, std::size_t numHeads);
+
+// include/blackforge/backend/cuda/fused_attention.hpp:42-57
+struct FusedAttentionForwardResult {
+    DeviceTensor output;
+    DeviceTensor m;
+    DeviceTensor l;
+};
+FusedAttentionForwardResult fusedAttentionForward(const DeviceTensor& q, const DeviceTensor& k, const DeviceTensor& v,
+                                                  std::size_t numHeads, float scaleFactor, std::size_t oldLen);
+// Same contract; operands are rounded to bf16 and run through the tensor-core kernel when head_dim is 128.
+FusedAttentionForwardResult fusedAttentionForwardBf16(const DeviceTensor& q, const DeviceTensor& k,
+                                                      const DeviceTensor& v, std::size_t numHeads, float scaleFactor,
+                                                      std::size_t oldLen);
+
+// ---- model ------------------------------------------------------------------------------------------
+using OpDesc = bfb_op_desc;
+
+struct PrecisionPolicy {  // include/blackforge/ir/module.hpp:44-48, BFB_DT_* codes
+    int storage = BFB_DT_FP32;
+    int compute = BFB_DT_FP32;
+    int accumulate = BFB_DT_FP32;
+};
+
+struct Parameter {  // include/blackforge/backend/cuda/model.hpp:15-19 (gradients belong to training)
+    std::string name;
+    DeviceTensor value;                  // this rank's part (the whole tensor when not tensor-parallel)
+    std::vector<std::size_t> fullShape;  // shape in checkpoints
+};
+
+// include/blackforge/backend/cuda/model.hpp:57-113 (forward side).
+class Model {
+public:
+    Model(const std::vector<OpDesc>& ops, std::int64_t inputLastDim, unsigned int seed = 42,
+          std::optional<PrecisionPolicy> precision = std::nullopt, bool randomInit = true,
+          std::string name = "model");
+    ~Model();
+    Model(const Model&) = delete;
+    Model& operator=(const Model&) = delete;
+
+    // Heads, feed-forward columns and logits columns sharded over `world` ranks; call before any
+    // parameter is set. Outputs of a final linear are this rank's column slice.
+    void setTensorParallel(int rank, int world);
+
+    DeviceTensor forward(const DeviceTensor& input, bool inputRangeTrusted = false, void* stream = nullptr);
+
+    [[nodiscard]] std::vector<Parameter*> parameters();
+    [[nodiscard]] const std::string& name() const { return name_; }
+    // Structure only (no device memory touched): checkpoint order, names, full shapes.
+    [[nodiscard]] std::size_t parameterCount() const;
+    [[nodiscard]] const std::string& parameterName(std::size_t index) const;
+    [[nodiscard]] const std::vector<std::size_t>& parameterShape(std::size_t index) const;
+    void setParameter(std::size_t index, const float* hostFullValues);
+    void getParameter(std::size_t index, float* hostFullValues);
+    // Parameters changed: converted weights are rebuilt at the next forward.
+    void invalidatePreparedWeights();
+    [[nodiscard]] std::optional<std::size_t> firstLayerEmbeddingVocabSize() const;
+
+    struct Impl;
+
+private:
+    std::unique_ptr<Impl> impl_;
+    std::string name_;
+};
+
+// include/blackforge/backend/cuda/checkpoint.hpp:24-27 — BFCKPT1 files.
+void saveCheckpoint(Model& model, const std::string& path);
+void loadCheckpoint(Model& model, const std::string& path);
+
+// include/blackforge/backend/cuda/executor.hpp:20-33 — weights regenerated from the seed on every run.
+class Executor {
+public:
+    explicit Executor(unsigned int seed = 42) : seed_(seed) {}
+    [[nodiscard]] HostTensor makeSyntheticInput(const std::vector<OpDesc>& ops, const std::vector<std::int64_t>& inputShape,
+                                                std::size_t batchSize) const;
+    [[nodiscard]] HostTensor run(const std::vector<OpDesc>& ops, std::int64_t inputLastDim, const HostTensor& input,
+                                 const std::optional<PrecisionPolicy>& precision = std::nullopt) const;
+
+private:
+    unsigned int seed_;
+};
+
+// Seeded default initialisation shared by Model and Executor: uniform(-0.1, 0.1) from std::mt19937
+// (src/backend/cpu/random_init.cpp:7-22) with seedFor(base, valueId, salt) = base ^ (valueId * salt).
+HostTensor randomTensor(std::vector<std::size_t> shape, unsigned int seed);
+HostTensor randomTokenIdTensor(std::vector<std::size_t> shape, std::size_t vocabSize, unsigned int seed);
+unsigned int seedFor(unsigned int base, std::size_t valueId, unsigned int salt);
+
+}  // namespace bfb200

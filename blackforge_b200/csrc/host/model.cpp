@@ -1,0 +1,817 @@
+// Model / Executor / checkpoints: the device side of the IR executor.
+//
+// Model::forward has two routes. Without a precision block (or with `compute fp32`) it interprets
+// the pipeline op by op on fp32 tensors — the exactness route compared against the CPU backend.
+// With `compute bf16` or `compute fp8.e4m3` it runs the planned route: weights converted once to
+// K-major bf16 / e4m3 (Q, K, V fused into one matrix), activations kept in a reusable arena, and
+// per block
+//   rmsnorm -> [QKV GEMM] -> flash attention -> [out-proj GEMM + residual]
+//   rmsnorm -> [GEMM + bias + silu] -> [GEMM + bias + residual]
+// with every bias / activation / residual pass folded into a GEMM epilogue. `storage bf16` keeps
+// the residual stream in bf16 (each op output rounded once, the CPU backend's meaning of storage);
+// otherwise it stays fp32. Results leave as fp32 tensors either way.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <map>
+#include <random>
+#include <stdexcept>
+
+#include "../common.cuh"
+#include "../kernels.hpp"
+#include "../pool.hpp"
+#include "bfb200.hpp"
+#include "tp.hpp"
+
+namespace bfb200 {
+
+using bfb::fail;
+using bfb::require;
+
+// ---- seeded default initialisation --------------------------------------------------------------------
+// Salts per parameter slot (src/backend/cpu/model.cpp:14-26, src/backend/cuda/model.cu:17-28): part of
+// the reproducibility contract of `run` without a checkpoint.
+namespace {
+constexpr unsigned int kWeightSalt = 0x2545F491U;
+constexpr unsigned int kBiasSalt = 0x27D4EB2FU;
+constexpr unsigned int kEmbeddingSalt = 0x85EBCA6BU;
+constexpr unsigned int kPositionalSalt = 0xC2B2AE35U;
+constexpr unsigned int kAttnWqSalt = 0x27D4EB2DU;
+constexpr unsigned int kAttnWkSalt = 0x165667B1U;
+constexpr unsigned int kAttnWvSalt = 0xD3A2646CU;
+constexpr unsigned int kAttnWoutSalt = 0xFD7046C5U;
+constexpr unsigned int kFFW1Salt = 0xB55A4F09U;
+constexpr unsigned int kFFB1Salt = 0x5BD1E995U;
+constexpr unsigned int kFFW2Salt = 0x9E3779B9U;
+constexpr unsigned int kFFB2Salt = 0x1B873593U;
+constexpr unsigned int kInputSalt = 0x9E3779B1U;
+}  // namespace
+
+HostTensor randomTensor(std::vector<std::size_t> shape, unsigned int seed) {
+    std::mt19937 rng(seed);
+    std::uniform_real_distribution<float> dist(-0.1F, 0.1F);
+    HostTensor t;
+    t.shape = std::move(shape);
+    t.data.resize(t.elementCount());
+    for (float& v : t.data) v = dist(rng);
+    return t;
+}
+
+HostTensor randomTokenIdTensor(std::vector<std::size_t> shape, std::size_t vocabSize, unsigned int seed) {
+    std::mt19937 rng(seed);
+    std::uniform_int_distribution<std::size_t> dist(0, vocabSize > 0 ? vocabSize - 1 : 0);
+    HostTensor t;
+    t.shape = std::move(shape);
+    t.data.resize(t.elementCount());
+    for (float& v : t.data) v = static_cast<float>(dist(rng));
+    return t;
+}
+
+unsigned int seedFor(unsigned int base, std::size_t valueId, unsigned int salt) {
+    return base ^ (static_cast<unsigned int>(valueId) * salt);
+}
+
+// ---- Model::Impl ----------------------------------------------------------------------------------------
+
+namespace {
+
+enum class Shard { None, Cols, Rows, Vec };  // how a parameter is split across tensor-parallel ranks
+
+enum class Mode { Fp32, Bf16, Fp8 };
+
+struct DevBuf {
+    void* ptr = nullptr;
+    std::size_t bytes = 0;
+    void reset() {
+        if (ptr != nullptr) bfb::poolRelease(ptr, bytes);
+        ptr = nullptr;
+        bytes = 0;
+    }
+    void ensure(std::size_t need) {
+        if (bytes == need && ptr != nullptr) return;
+        reset();
+        ptr = bfb::poolAcquire(need);
+        bytes = need;
+    }
+};
+
+struct ParamMeta {
+    Shard shard = Shard::None;
+    unsigned int salt = 0;
+    std::size_t valueId = 0;
+};
+
+struct Layer {
+    int kind = 0;
+    std::size_t outputId = 0;
+    std::size_t inFeat = 0, outFeat = 0;
+    std::size_t heads = 0, hidden = 0, vocab = 0, maxSeq = 0;
+    int p[4] = {-1, -1, -1, -1};  // parameter indices in slot order
+    bool shardedLinear = false;
+    // converted weights of the planned route (this rank's part)
+    DevBuf w0, w1;   // attention: fused QKV^T, Wout^T; feed-forward: W1^T, W2^T; linear: W^T
+    DevBuf scales;   // fp8: [0..1] scale/inverse of w0, [2..3] of w1
+};
+
+}  // namespace
+
+struct Model::Impl {
+    std::vector<OpDesc> ops;
+    std::int64_t inputLastDim = 0;
+    unsigned int seed = 42;
+    std::optional<PrecisionPolicy> precision;
+    int tpRank = 0, tpWorld = 1;
+    Mode mode = Mode::Fp32;
+    int streamDtype = BFB_F32;
+    bool storageBf16 = false;
+    bool randomInit = true;
+    bool built = false;
+    bool prepared = false;
+    std::vector<Parameter> params;
+    std::vector<ParamMeta> meta;
+    std::vector<Layer> layers;
+    std::map<std::string, DevBuf> arena;
+    DevBuf fp8Stats;  // per GEMM input: [amax, scale, inverse, alpha]
+    DevBuf status;    // device status word for bounded waits + id range counter
+
+    ~Impl() {
+        for (auto& l : layers) {
+            l.w0.reset();
+            l.w1.reset();
+            l.scales.reset();
+        }
+        for (auto& kv : arena) kv.second.reset();
+        fp8Stats.reset();
+        status.reset();
+    }
+
+    void* buf(const std::string& name, std::size_t bytes) {
+        DevBuf& b = arena[name];
+        b.ensure(bytes);
+        return b.ptr;
+    }
+
+    std::vector<std::size_t> localShape(const std::vector<std::size_t>& full, Shard s) const {
+        std::vector<std::size_t> shape = full;
+        if (tpWorld == 1) return shape;
+        if (s == Shard::Cols) shape[1] /= static_cast<std::size_t>(tpWorld);
+        if (s == Shard::Rows) shape[0] /= static_cast<std::size_t>(tpWorld);
+        if (s == Shard::Vec) shape[0] /= static_cast<std::size_t>(tpWorld);
+        return shape;
+    }
+
+    int addParam(const std::string& name, std::vector<std::size_t> fullShape, Shard shard, unsigned int salt,
+                 std::size_t valueId) {
+        Parameter prm;
+        prm.name = name;
+        prm.fullShape = std::move(fullShape);
+        params.push_back(std::move(prm));
+        meta.push_back(ParamMeta{shard, salt, valueId});
+        return static_cast<int>(params.size()) - 1;
+    }
+
+    void buildStructure();
+    void allocateParams();
+    void setParam(std::size_t index, const float* hostFull);
+    void getParam(std::size_t index, float* hostFull);
+    void prepare(cudaStream_t stream);
+    DeviceTensor forwardFp32(const DeviceTensor& input, bool trusted);
+    DeviceTensor forwardPlanned(const DeviceTensor& input, bool trusted, cudaStream_t stream);
+    void checkStatus(cudaStream_t stream, bool checkIds, std::size_t vocab);
+};
+
+void Model::Impl::buildStructure() {
+    std::size_t feat = inputLastDim > 0 ? static_cast<std::size_t>(inputLastDim) : 0;
+    const std::size_t w = static_cast<std::size_t>(tpWorld);
+    for (std::size_t i = 0; i < ops.size(); ++i) {
+        const OpDesc& op = ops[i];
+        Layer layer;
+        layer.kind = op.kind;
+        layer.outputId = static_cast<std::size_t>(op.output);
+        layer.inFeat = feat;
+        const std::string id = std::to_string(op.output);
+        switch (op.kind) {
+            case BFB_OP_LINEAR: {
+                if (feat == 0) throw std::invalid_argument("Model: linear#" + id + " needs a concrete input width");
+                if (op.linear_out_features <= 0) throw std::invalid_argument("Model: linear#" + id + " needs a positive width");
+                std::size_t out = static_cast<std::size_t>(op.linear_out_features);
+                layer.outFeat = out;
+                layer.shardedLinear = tpWorld > 1 && i + 1 == ops.size();
+                if (layer.shardedLinear && out % w != 0) {
+                    throw std::invalid_argument("Model: output width of the last linear must divide by the tensor-parallel size");
+                }
+                Shard sw = layer.shardedLinear ? Shard::Cols : Shard::None;
+                Shard sb = layer.shardedLinear ? Shard::Vec : Shard::None;
+                layer.p[0] = addParam("linear" + id + ".weight", {feat, out}, sw, kWeightSalt, layer.outputId);
+                layer.p[1] = addParam("linear" + id + ".bias", {out}, sb, kBiasSalt, layer.outputId);
+                feat = out;
+                break;
+            }
+            case BFB_OP_EMBEDDING: {
+                if (op.embedding_vocab_size <= 0 || op.embedding_dim <= 0) {
+                    throw std::invalid_argument("Model: embedding#" + id + " needs positive sizes");
+                }
+                layer.vocab = static_cast<std::size_t>(op.embedding_vocab_size);
+                layer.outFeat = static_cast<std::size_t>(op.embedding_dim);
+                layer.p[0] = addParam("embedding" + id + ".table", {layer.vocab, layer.outFeat}, Shard::None,
+                                      kEmbeddingSalt, layer.outputId);
+                feat = layer.outFeat;
+                break;
+            }
+            case BFB_OP_POSITIONAL_EMBEDDING: {
+                if (feat == 0) throw std::invalid_argument("Model: positional_embedding#" + id + " needs a concrete input width");
+                if (op.positional_max_seq_len <= 0) throw std::invalid_argument("Model: positional_embedding#" + id + " needs a positive length");
+                layer.maxSeq = static_cast<std::size_t>(op.positional_max_seq_len);
+                layer.outFeat = feat;
+                layer.p[0] = addParam("positional_embedding" + id + ".table", {layer.maxSeq, feat}, Shard::None,
+                                      kPositionalSalt, layer.outputId);
+                break;
+            }
+            case BFB_OP_ATTENTION: {
+                if (feat == 0) throw std::invalid_argument("Model: attention#" + id + " needs a concrete input width");
+                std::size_t heads = static_cast<std::size_t>(std::max<std::int64_t>(op.attention_num_heads, 0));
+                if (heads == 0 || feat % heads != 0) {
+                    throw std::invalid_argument("Model: 'attention#" + id + "' requires " + std::to_string(heads) +
+                                                " heads to divide dim=" + std::to_string(feat));
+                }
+                if (tpWorld > 1 && heads % w != 0) {
+                    throw std::invalid_argument("Model: attention heads must divide by the tensor-parallel size");
+                }
+                layer.heads = heads;
+                layer.outFeat = feat;
+                layer.p[0] = addParam("attention" + id + ".wq", {feat, feat}, Shard::Cols, kAttnWqSalt, layer.outputId);
+                layer.p[1] = addParam("attention" + id + ".wk", {feat, feat}, Shard::Cols, kAttnWkSalt, layer.outputId);
+                layer.p[2] = addParam("attention" + id + ".wv", {feat, feat}, Shard::Cols, kAttnWvSalt, layer.outputId);
+                layer.p[3] = addParam("attention" + id + ".wout", {feat, feat}, Shard::Rows, kAttnWoutSalt, layer.outputId);
+                break;
+            }
+            case BFB_OP_FEEDFORWARD: {
+                if (feat == 0) throw std::invalid_argument("Model: feedforward#" + id + " needs a concrete input width");
+                if (op.feedforward_hidden_dim <= 0) throw std::invalid_argument("Model: feedforward#" + id + " needs a positive hidden width");
+                std::size_t hidden = static_cast<std::size_t>(op.feedforward_hidden_dim);
+                if (tpWorld > 1 && hidden % w != 0) {
+                    throw std::invalid_argument("Model: feed-forward width must divide by the tensor-parallel size");
+                }
+                layer.hidden = hidden;
+                layer.outFeat = feat;
+                layer.p[0] = addParam("feedforward" + id + ".w1", {feat, hidden}, Shard::Cols, kFFW1Salt, layer.outputId);
+                layer.p[1] = addParam("feedforward" + id + ".b1", {hidden}, Shard::Vec, kFFB1Salt, layer.outputId);
+                layer.p[2] = addParam("feedforward" + id + ".w2", {hidden, feat}, Shard::Rows, kFFW2Salt, layer.outputId);
+                layer.p[3] = addParam("feedforward" + id + ".b2", {feat}, Shard::None, kFFB2Salt, layer.outputId);
+                break;
+            }
+            case BFB_OP_BIDIRECTIONAL_ATTENTION:
+                throw std::invalid_argument(
+                    "Model: 'bidirectional_attention' is not available on the device backend (CPU only)");
+            case BFB_OP_SILU:
+            case BFB_OP_RELU:
+            case BFB_OP_GELU:
+            case BFB_OP_RMSNORM:
+            case BFB_OP_SOFTMAX:
+                layer.outFeat = feat;
+                break;
+            default:
+                throw std::invalid_argument("Model: unknown operation kind " + std::to_string(op.kind));
+        }
+        layers.push_back(std::move(layer));
+    }
+}
+
+void Model::Impl::allocateParams() {
+    if (built) return;
+    for (std::size_t i = 0; i < params.size(); ++i) {
+        params[i].value = DeviceTensor::zeros(localShape(params[i].fullShape, meta[i].shard));
+    }
+    built = true;
+    if (randomInit) {
+        for (std::size_t i = 0; i < params.size(); ++i) {
+            HostTensor t = randomTensor(params[i].fullShape, seedFor(seed, meta[i].valueId, meta[i].salt));
+            setParam(i, t.data.data());
+        }
+    }
+}
+
+void Model::Impl::setParam(std::size_t index, const float* hostFull) {
+    allocateParams();
+    require(index < params.size(), "Model: parameter index out of range");
+    require(hostFull != nullptr, "Model: null parameter data");
+    Parameter& prm = params[index];
+    const Shard s = tpWorld > 1 ? meta[index].shard : Shard::None;
+    const std::size_t n = prm.value.elementCount();
+    const std::size_t w = static_cast<std::size_t>(tpWorld), r = static_cast<std::size_t>(tpRank);
+    if (s == Shard::None) {
+        BFB_CUDA(cudaMemcpy(prm.value.data(), hostFull, n * sizeof(float), cudaMemcpyHostToDevice));
+    } else if (s == Shard::Rows || s == Shard::Vec) {
+        BFB_CUDA(cudaMemcpy(prm.value.data(), hostFull + r * n, n * sizeof(float), cudaMemcpyHostToDevice));
+    } else {  // column slice of [K, N]
+        const std::size_t k = prm.fullShape[0], nFull = prm.fullShape[1], nLoc = nFull / w;
+        BFB_CUDA(cudaMemcpy2D(prm.value.data(), nLoc * sizeof(float), hostFull + r * nLoc, nFull * sizeof(float),
+                              nLoc * sizeof(float), k, cudaMemcpyHostToDevice));
+    }
+    prepared = false;
+}
+
+void Model::Impl::getParam(std::size_t index, float* hostFull) {
+    allocateParams();
+    require(index < params.size(), "Model: parameter index out of range");
+    require(hostFull != nullptr, "Model: null parameter buffer");
+    if (tpWorld > 1 && meta[index].shard != Shard::None) {
+        fail(BFB_UNSUPPORTED, "Model: reading back a tensor-parallel parameter is not supported");
+    }
+    Parameter& prm = params[index];
+    BFB_CUDA(cudaMemcpy(hostFull, prm.value.data(), prm.value.elementCount() * sizeof(float), cudaMemcpyDeviceToHost));
+}
+
+// Convert weights once for the planned route.
+void Model::Impl::prepare(cudaStream_t stream) {
+    allocateParams();
+    if (prepared || mode == Mode::Fp32) {
+        prepared = true;
+        return;
+    }
+    const int wDtype = mode == Mode::Bf16 ? BFB_BF16 : BFB_FP8_E4M3;
+    const std::size_t eb = mode == Mode::Bf16 ? 2 : 1;
+    // Transposes `count` fp32 [K, N_i] matrices into consecutive row blocks of dst ([sum N_i, K]); for
+    // fp8 one scale is derived from the amax over all of them (the fused Q/K/V matrix counts as one tensor).
+    auto convert = [&](DevBuf& dst, std::initializer_list<const DeviceTensor*> srcs, float* scaleSlot) {
+        std::size_t k = (*srcs.begin())->dim(0), totalN = 0;
+        for (const DeviceTensor* t : srcs) totalN += t->dim(1);
+        dst.ensure(totalN * k * eb);
+        const float* dScale = nullptr;
+        if (mode == Mode::Fp8) {
+            BFB_CUDA(cudaMemsetAsync(scaleSlot, 0, 2 * sizeof(float), stream));
+            // amax lands in scaleSlot[0], then is replaced by {scale, inverse}
+            for (const DeviceTensor* t : srcs) {
+                bfb::amax(t->data(), BFB_F32, static_cast<int64_t>(t->elementCount()), scaleSlot, stream);
+            }
+            bfb::fp8ScaleFromAmax(scaleSlot, scaleSlot, stream);
+            dScale = scaleSlot;
+        }
+        std::size_t rowOff = 0;
+        for (const DeviceTensor* t : srcs) {
+            bfb::weightPrepare(t->data(), static_cast<char*>(dst.ptr) + rowOff * k * eb, wDtype,
+                               static_cast<int64_t>(k), static_cast<int64_t>(t->dim(1)), 1.0f, dScale, stream);
+            rowOff += t->dim(1);
+        }
+    };
+    for (Layer& l : layers) {
+        if (l.kind != BFB_OP_ATTENTION && l.kind != BFB_OP_FEEDFORWARD && l.kind != BFB_OP_LINEAR) continue;
+        l.scales.ensure(4 * sizeof(float));
+        float* sc = static_cast<float*>(l.scales.ptr);
+        if (l.kind == BFB_OP_ATTENTION) {
+            convert(l.w0, {&params[l.p[0]].value, &params[l.p[1]].value, &params[l.p[2]].value}, sc);
+            convert(l.w1, {&params[l.p[3]].value}, sc + 2);
+        } else if (l.kind == BFB_OP_FEEDFORWARD) {
+            convert(l.w0, {&params[l.p[0]].value}, sc);
+            convert(l.w1, {&params[l.p[2]].value}, sc + 2);
+        } else {
+            convert(l.w0, {&params[l.p[0]].value}, sc);
+        }
+    }
+    prepared = true;
+}
+
+void Model::Impl::checkStatus(cudaStream_t stream, bool checkIds, std::size_t vocab) {
+    int host[2] = {0, 0};
+    BFB_CUDA(cudaMemcpyAsync(host, status.ptr, sizeof(host), cudaMemcpyDeviceToHost, stream));
+    BFB_CUDA(cudaStreamSynchronize(stream));
+    if (checkIds && host[1] != 0) {
+        throw std::invalid_argument("embeddingLookup: " + std::to_string(host[1]) +
+                                    " token id(s) outside the vocabulary [0, " + std::to_string(vocab) + ")");
+    }
+    if (host[0] != 0) {
+        fail(BFB_TIMEOUT, "a bounded wait inside a tensor-core kernel ran out (device code " + std::to_string(host[0]) + ")");
+    }
+}
+
+// ---- exactness route: op by op on fp32 tensors ----------------------------------------------------------
+DeviceTensor Model::Impl::forwardFp32(const DeviceTensor& input, bool trusted) {
+    require(tpWorld == 1, "Model: tensor parallelism needs compute bf16 or fp8.e4m3");
+    DeviceTensor current = input.clone();
+    auto roundStorage = [&](DeviceTensor& t) {
+        if (storageBf16) bfb::roundBf16InPlace(t.data(), static_cast<int64_t>(t.elementCount()), nullptr);
+    };
+    for (std::size_t i = 0; i < layers.size(); ++i) {
+        Layer& l = layers[i];
+        switch (l.kind) {
+            case BFB_OP_LINEAR: current = linear(current, params[l.p[0]].value, params[l.p[1]].value); break;
+            case BFB_OP_SILU: current = silu(current); break;
+            case BFB_OP_RELU: current = relu(current); break;
+            case BFB_OP_GELU: current = gelu(current); break;
+            case BFB_OP_RMSNORM: current = rmsnorm(current); break;
+            case BFB_OP_SOFTMAX: current = softmax(current); break;
+            case BFB_OP_EMBEDDING:
+                current = (trusted && i == 0) ? embeddingLookupPreValidated(current, params[l.p[0]].value)
+                                              : embeddingLookup(current, params[l.p[0]].value);
+                break;
+            case BFB_OP_POSITIONAL_EMBEDDING: current = addPositionalEmbedding(current, params[l.p[0]].value); break;
+            case BFB_OP_ATTENTION:
+                current = selfAttention(current, params[l.p[0]].value, params[l.p[1]].value, params[l.p[2]].value,
+                                        params[l.p[3]].value, l.heads);
+                break;
+            case BFB_OP_FEEDFORWARD:
+                current = feedForward(current, params[l.p[0]].value, params[l.p[1]].value, params[l.p[2]].value,
+                                      params[l.p[3]].value);
+                break;
+            default: fail(BFB_UNSUPPORTED, "Model: operation not available on the device");
+        }
+        roundStorage(current);
+    }
+    return current;
+}
+
+// ---- planned route: tensor-core GEMMs + flash attention -------------------------------------------------
+DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted, cudaStream_t stream) {
+    prepare(stream);
+    status.ensure(2 * sizeof(int));
+    BFB_CUDA(cudaMemsetAsync(status.ptr, 0, 2 * sizeof(int), stream));
+    int* dStatus = static_cast<int*>(status.ptr);
+    int* dOob = dStatus + 1;
+    const int S = streamDtype;
+    const std::size_t sb = S == BFB_F32 ? 4 : 2;
+    const int ab = mode == Mode::Bf16 ? BFB_BF16 : BFB_FP8_E4M3;
+    const bool fp8 = mode == Mode::Fp8;
+
+    // running activation: pointer + shape; dtype S except straight after a non-planned op
+    std::vector<std::size_t> shape = input.shape();
+    void* x = nullptr;  // [tokens, feat] in S
+    std::size_t feat = shape.empty() ? 0 : shape.back();
+    auto tokensOf = [&]() {
+        std::size_t n = 1;
+        for (std::size_t i = 0; i + 1 < shape.size(); ++i) n *= shape[i];
+        return n;
+    };
+    bool idsChecked = false;
+    std::size_t vocabForCheck = 0;
+    int fp8Slot = 0;
+    if (fp8) {
+        fp8Stats.ensure(layers.size() * 4 * 4 * sizeof(float));
+        BFB_CUDA(cudaMemsetAsync(fp8Stats.ptr, 0, fp8Stats.bytes, stream));
+    }
+
+    // A-operand of a GEMM from a bf16 activation: the buffer itself (bf16) or an e4m3 copy with a fresh
+    // per-tensor scale; returns the device alpha pointer for fp8 (1 / (scale_a * scale_w)).
+    auto gemmInput = [&](const void* act16, std::size_t count, const std::string& name, const float* wScales,
+                         const float** dAlpha) -> const void* {
+        if (!fp8) {
+            *dAlpha = nullptr;
+            return act16;
+        }
+        float* st = static_cast<float*>(fp8Stats.ptr) + 4 * (fp8Slot++);
+        bfb::amax(act16, BFB_BF16, static_cast<int64_t>(count), st, stream);
+        bfb::fp8ActScale(st, st + 1, wScales + 1, stream);  // st[1]=scale st[2]=inverse st[3]=alpha
+        void* a8 = buf(name, count);
+        bfb::castScaled(act16, BFB_BF16, a8, BFB_FP8_E4M3, static_cast<int64_t>(count), 1.0f, st + 1, stream);
+        *dAlpha = st + 3;
+        return a8;
+    };
+    auto runGemm = [&](const void* a, const void* w, void* c, std::size_t m, std::size_t n, std::size_t k, int cDtype,
+                       int epilogue, const float* bias, const void* residual, const float* dAlpha, int roundC) {
+        bfb::GemmArgs g;
+        g.a = a;
+        g.b = w;
+        g.c = c;
+        g.m = static_cast<int64_t>(m);
+        g.n = static_cast<int64_t>(n);
+        g.k = static_cast<int64_t>(k);
+        g.abDtype = ab;
+        g.bLayout = BFB_B_NK;
+        g.cDtype = cDtype;
+        g.epilogue = epilogue;
+        g.bias = bias;
+        g.residual = residual;
+        g.dAlpha = dAlpha;
+        g.roundCBf16 = roundC;
+        g.dStatus = dStatus;
+        bfb::gemm(g, stream);
+    };
+
+    DeviceTensor result;
+    bool haveResult = false;
+    const std::size_t w = static_cast<std::size_t>(tpWorld);
+
+    for (std::size_t i = 0; i < layers.size(); ++i) {
+        Layer& l = layers[i];
+        const std::size_t tokens = tokensOf();
+        switch (l.kind) {
+            case BFB_OP_EMBEDDING: {
+                require(i == 0, "Model: embedding must be the first operation of the planned route");
+                if (input.rank() != 2) throw std::invalid_argument("embeddingLookup: token ids must be [batch, seq]");
+                const std::size_t batch = shape[0], seq = shape[1];
+                const float* pos = nullptr;
+                std::size_t maxSeq = 0;
+                bool fused = i + 1 < layers.size() && layers[i + 1].kind == BFB_OP_POSITIONAL_EMBEDDING;
+                if (fused) {
+                    maxSeq = layers[i + 1].maxSeq;
+                    if (seq > maxSeq) {
+                        throw std::invalid_argument("addPositionalEmbedding: sequence (" + std::to_string(seq) +
+                                                    ") exceeds maxSeqLen (" + std::to_string(maxSeq) + ")");
+                    }
+                    pos = params[layers[i + 1].p[0]].value.data();
+                }
+                x = buf("x", batch * seq * l.outFeat * sb);
+                bfb::embedPos(input.data(), params[l.p[0]].value.data(), pos, x, S, static_cast<int64_t>(batch),
+                              static_cast<int64_t>(seq), static_cast<int64_t>(l.vocab), static_cast<int64_t>(l.outFeat),
+                              static_cast<int64_t>(maxSeq), 0, trusted ? nullptr : dOob, stream);
+                idsChecked = !trusted;
+                vocabForCheck = l.vocab;
+                shape = {batch, seq, l.outFeat};
+                feat = l.outFeat;
+                if (fused) ++i;
+                break;
+            }
+            case BFB_OP_ATTENTION: {
+                require(x != nullptr, "Model: the planned route must start with an embedding");
+                if (shape.size() != 3) throw std::invalid_argument("selfAttention: input [batch, seq, dim] required");
+                const std::size_t batch = shape[0], seq = shape[1], d = feat, dl = d / w, hl = l.heads / w;
+                const std::size_t hd = d / l.heads;
+                void* normed = buf("normed", tokens * d * 2);
+                bfb::rmsnorm(x, S, normed, BFB_BF16, static_cast<int64_t>(tokens), static_cast<int64_t>(d), 1e-6f, stream);
+                const float* sc = static_cast<const float*>(l.scales.ptr);
+                const float* dAlpha = nullptr;
+                const void* aQkv = gemmInput(normed, tokens * d, "act8_d", sc, &dAlpha);
+                void* qkv = buf("qkv", tokens * 3 * dl * 2);
+                runGemm(aQkv, l.w0.ptr, qkv, tokens, 3 * dl, d, BFB_BF16, BFB_EPI_NONE, nullptr, nullptr, dAlpha, 0);
+                void* ctx = buf("ctx", tokens * dl * 2);
+                bfb::AttentionArgs a;
+                a.q = qkv;
+                a.k = static_cast<char*>(qkv) + dl * 2;
+                a.v = static_cast<char*>(qkv) + 2 * dl * 2;
+                a.out = ctx;
+                a.dtype = BFB_BF16;
+                a.batch = static_cast<int64_t>(batch);
+                a.newLen = a.totalLen = static_cast<int64_t>(seq);
+                a.numHeads = static_cast<int64_t>(hl);
+                a.headDim = static_cast<int64_t>(hd);
+                a.ldQ = a.ldK = a.ldV = static_cast<int64_t>(3 * dl);
+                a.ldO = static_cast<int64_t>(dl);
+                a.scale = 1.0f / std::sqrt(static_cast<float>(hd));
+                a.oldLen = 0;
+                a.causal = 1;
+                a.dStatus = dStatus;
+                bfb::attentionForward(a, stream);
+                const void* aOut = gemmInput(ctx, tokens * dl, "act8_dl", sc + 2, &dAlpha);
+                // x = x + ctx * Wout (in place); under tensor parallelism rank 0 carries the residual
+                const int epi = (tpWorld == 1 || tpRank == 0) ? BFB_EPI_RESIDUAL : BFB_EPI_NONE;
+                runGemm(aOut, l.w1.ptr, x, tokens, d, dl, S, epi, nullptr, x, dAlpha, 0);
+                if (tpWorld > 1) tpAllReduceSum(x, static_cast<int64_t>(tokens * d), S, stream);
+                break;
+            }
+            case BFB_OP_FEEDFORWARD: {
+                require(x != nullptr, "Model: the planned route must start with an embedding");
+                const std::size_t d = feat, fl = l.hidden / w;
+                void* normed = buf("normed", tokens * d * 2);
+                bfb::rmsnorm(x, S, normed, BFB_BF16, static_cast<int64_t>(tokens), static_cast<int64_t>(d), 1e-6f, stream);
+                const float* sc = static_cast<const float*>(l.scales.ptr);
+                const float* dAlpha = nullptr;
+                const void* a1 = gemmInput(normed, tokens * d, "act8_d", sc, &dAlpha);
+                void* hidden = buf("hidden", tokens * fl * 2);
+                runGemm(a1, l.w0.ptr, hidden, tokens, fl, d, BFB_BF16, BFB_EPI_BIAS_SILU, params[l.p[1]].value.data(),
+                        nullptr, dAlpha, 0);
+                const void* a2 = gemmInput(hidden, tokens * fl, "act8_f", sc + 2, &dAlpha);
+                const bool lead = tpWorld == 1 || tpRank == 0;
+                runGemm(a2, l.w1.ptr, x, tokens, d, fl, S, lead ? BFB_EPI_BIAS_RESIDUAL : BFB_EPI_NONE,
+                        lead ? params[l.p[3]].value.data() : nullptr, lead ? x : nullptr, dAlpha, 0);
+                if (tpWorld > 1) tpAllReduceSum(x, static_cast<int64_t>(tokens * d), S, stream);
+                break;
+            }
+            case BFB_OP_LINEAR: {
+                require(x != nullptr, "Model: the planned route must start with an embedding");
+                const std::size_t d = feat, outL = l.shardedLinear ? l.outFeat / w : l.outFeat;
+                const void* a16 = x;
+                if (S == BFB_F32) {
+                    void* t = buf("lin16", tokens * d * 2);
+                    bfb::castScaled(x, BFB_F32, t, BFB_BF16, static_cast<int64_t>(tokens * d), 1.0f, nullptr, stream);
+                    a16 = t;
+                }
+                const float* sc = static_cast<const float*>(l.scales.ptr);
+                const float* dAlpha = nullptr;
+                const void* a = gemmInput(a16, tokens * d, "act8_d", sc, &dAlpha);
+                std::vector<std::size_t> outShape = shape;
+                outShape.back() = outL;
+                const bool last = i + 1 == layers.size();
+                if (last) {
+                    result = DeviceTensor(outShape);
+                    runGemm(a, l.w0.ptr, result.data(), tokens, outL, d, BFB_F32, BFB_EPI_BIAS,
+                            params[l.p[1]].value.data(), nullptr, dAlpha, storageBf16 ? 1 : 0);
+                    haveResult = true;
+                } else {
+                    void* nx = buf("x_alt", tokens * outL * sb);
+                    runGemm(a, l.w0.ptr, nx, tokens, outL, d, S, BFB_EPI_BIAS, params[l.p[1]].value.data(), nullptr,
+                            dAlpha, 0);
+                    std::swap(arena["x"], arena["x_alt"]);
+                    x = arena["x"].ptr;
+                }
+                shape = outShape;
+                feat = outL;
+                break;
+            }
+            default: {
+                // elementwise / norm / softmax / standalone positions: run on an fp32 copy
+                require(x != nullptr, "Model: the planned route must start with an embedding");
+                const std::size_t count = tokens * feat;
+                DeviceTensor tmp(shape);
+                bfb::castScaled(x, S, tmp.data(), BFB_F32, static_cast<int64_t>(count), 1.0f, nullptr, stream);
+                BFB_CUDA(cudaStreamSynchronize(stream));  // the fp32 operator API runs on the default stream
+                DeviceTensor out;
+                switch (l.kind) {
+                    case BFB_OP_SILU: out = silu(tmp); break;
+                    case BFB_OP_RELU: out = relu(tmp); break;
+                    case BFB_OP_GELU: out = gelu(tmp); break;
+                    case BFB_OP_RMSNORM: out = rmsnorm(tmp); break;
+                    case BFB_OP_SOFTMAX: out = softmax(tmp); break;
+                    case BFB_OP_POSITIONAL_EMBEDDING: out = addPositionalEmbedding(tmp, params[l.p[0]].value); break;
+                    default: fail(BFB_UNSUPPORTED, "Model: operation not available on the device");
+                }
+                BFB_CUDA(cudaStreamSynchronize(nullptr));
+                bfb::castScaled(out.data(), BFB_F32, x, S, static_cast<int64_t>(count), 1.0f, nullptr, stream);
+                break;
+            }
+        }
+    }
+    if (!haveResult) {
+        require(x != nullptr, "Model: empty pipeline");
+        result = DeviceTensor(shape);
+        bfb::castScaled(x, S, result.data(), BFB_F32, static_cast<int64_t>(tokensOf() * feat), 1.0f, nullptr, stream);
+    }
+    checkStatus(stream, idsChecked, vocabForCheck);
+    return result;
+}
+
+// ---- Model ------------------------------------------------------------------------------------------------
+
+Model::Model(const std::vector<OpDesc>& ops, std::int64_t inputLastDim, unsigned int seed,
+             std::optional<PrecisionPolicy> precision, bool randomInit, std::string name)
+    : impl_(std::make_unique<Impl>()), name_(std::move(name)) {
+    if (ops.empty()) throw std::invalid_argument("Model: the model '" + name_ + "' has no pipeline");
+    impl_->ops = ops;
+    impl_->inputLastDim = inputLastDim;
+    impl_->seed = seed;
+    impl_->precision = precision;
+    impl_->randomInit = randomInit;
+    if (precision.has_value()) {
+        if (precision->compute == BFB_DT_BF16) impl_->mode = Mode::Bf16;
+        else if (precision->compute == BFB_DT_FP8_E4M3) impl_->mode = Mode::Fp8;
+        impl_->storageBf16 = precision->storage == BFB_DT_BF16;
+    }
+    impl_->streamDtype = (impl_->mode != Mode::Fp32 && impl_->storageBf16) ? BFB_BF16 : BFB_F32;
+    impl_->buildStructure();
+}
+
+Model::~Model() = default;
+
+void Model::setTensorParallel(int rank, int world) {
+    if (world < 1 || rank < 0 || rank >= world) throw std::invalid_argument("Model: bad tensor-parallel rank/size");
+    if (impl_->built) throw std::invalid_argument("Model: tensor parallelism must be set before parameters exist");
+    impl_->tpRank = rank;
+    impl_->tpWorld = world;
+    impl_->params.clear();
+    impl_->meta.clear();
+    impl_->layers.clear();
+    impl_->buildStructure();
+}
+
+DeviceTensor Model::forward(const DeviceTensor& input, bool inputRangeTrusted, void* stream) {
+    impl_->allocateParams();
+    // the planned route needs the pipeline to open with an embedding; everything else is interpreted
+    bool planned = impl_->mode != Mode::Fp32 && !impl_->layers.empty() && impl_->layers.front().kind == BFB_OP_EMBEDDING;
+    if (!planned) {
+        if (impl_->mode != Mode::Fp32) {
+            fail(BFB_UNSUPPORTED, "Model: compute bf16 / fp8.e4m3 needs a pipeline that starts with an embedding");
+        }
+        if (stream != nullptr) BFB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+        return impl_->forwardFp32(input, inputRangeTrusted);
+    }
+    return impl_->forwardPlanned(input, inputRangeTrusted, static_cast<cudaStream_t>(stream));
+}
+
+std::vector<Parameter*> Model::parameters() {
+    impl_->allocateParams();
+    std::vector<Parameter*> out;
+    for (Parameter& p : impl_->params) out.push_back(&p);
+    return out;
+}
+
+std::size_t Model::parameterCount() const { return impl_->params.size(); }
+const std::string& Model::parameterName(std::size_t index) const { return impl_->params.at(index).name; }
+const std::vector<std::size_t>& Model::parameterShape(std::size_t index) const {
+    return impl_->params.at(index).fullShape;
+}
+
+void Model::setParameter(std::size_t index, const float* hostFullValues) { impl_->setParam(index, hostFullValues); }
+void Model::getParameter(std::size_t index, float* hostFullValues) { impl_->getParam(index, hostFullValues); }
+void Model::invalidatePreparedWeights() { impl_->prepared = false; }
+
+std::optional<std::size_t> Model::firstLayerEmbeddingVocabSize() const {
+    if (impl_->layers.empty() || impl_->layers.front().kind != BFB_OP_EMBEDDING) return std::nullopt;
+    return impl_->layers.front().vocab;
+}
+
+// ---- checkpoints (BFCKPT1) --------------------------------------------------------------------------------
+
+namespace {
+constexpr char kMagic[8] = {'B', 'F', 'C', 'K', 'P', 'T', '1', '\0'};
+[[noreturn]] void ioFail(const std::string& text) { fail(BFB_IO_ERROR, text); }
+}  // namespace
+
+void saveCheckpoint(Model& model, const std::string& path) {
+    std::vector<Parameter*> params = model.parameters();
+    std::ofstream out(path, std::ios::binary | std::ios::trunc);
+    if (!out) ioFail("saveCheckpoint: cannot write '" + path + "'");
+    out.write(kMagic, sizeof(kMagic));
+    auto u32 = [&](std::uint32_t v) { out.write(reinterpret_cast<const char*>(&v), sizeof(v)); };
+    auto u64 = [&](std::uint64_t v) { out.write(reinterpret_cast<const char*>(&v), sizeof(v)); };
+    u32(static_cast<std::uint32_t>(params.size()));
+    std::vector<float> host;
+    for (std::size_t i = 0; i < params.size(); ++i) {
+        const Parameter& p = *params[i];
+        u32(static_cast<std::uint32_t>(p.name.size()));
+        out.write(p.name.data(), static_cast<std::streamsize>(p.name.size()));
+        u32(static_cast<std::uint32_t>(p.fullShape.size()));
+        std::size_t count = 1;
+        for (std::size_t d : p.fullShape) {
+            u64(static_cast<std::uint64_t>(d));
+            count *= d;
+        }
+        host.resize(count);
+        model.getParameter(i, host.data());
+        out.write(reinterpret_cast<const char*>(host.data()), static_cast<std::streamsize>(count * sizeof(float)));
+    }
+    if (!out) ioFail("saveCheckpoint: write to '" + path + "' failed");
+}
+
+void loadCheckpoint(Model& model, const std::string& path) {
+    std::ifstream in(path, std::ios::binary);
+    if (!in) ioFail("loadCheckpoint: cannot open '" + path + "'");
+    char magic[8];
+    in.read(magic, sizeof(magic));
+    if (!in || std::memcmp(magic, kMagic, sizeof(kMagic)) != 0) {
+        ioFail("loadCheckpoint: '" + path + "' is not a BlackForge checkpoint");
+    }
+    std::vector<Parameter*> params = model.parameters();
+    std::map<std::string, std::size_t> byName;
+    for (std::size_t i = 0; i < params.size(); ++i) byName[params[i]->name] = i;
+    auto u32 = [&]() {
+        std::uint32_t v = 0;
+        in.read(reinterpret_cast<char*>(&v), sizeof(v));
+        return v;
+    };
+    auto u64 = [&]() {
+        std::uint64_t v = 0;
+        in.read(reinterpret_cast<char*>(&v), sizeof(v));
+        return v;
+    };
+    std::uint32_t count = u32();
+    if (!in) ioFail("loadCheckpoint: '" + path + "' is truncated");
+    std::vector<float> data;
+    for (std::uint32_t i = 0; i < count; ++i) {
+        std::uint32_t nameLen = u32();
+        if (!in || nameLen > (1u << 20)) ioFail("loadCheckpoint: '" + path + "' is truncated or corrupt");
+        std::string name(nameLen, '\0');
+        in.read(name.data(), nameLen);
+        std::uint32_t rank = u32();
+        if (!in || rank > 8) ioFail("loadCheckpoint: '" + path + "' is truncated or corrupt");
+        std::vector<std::size_t> shape(rank);
+        std::size_t elements = 1;
+        for (std::uint32_t d = 0; d < rank; ++d) {
+            shape[d] = static_cast<std::size_t>(u64());
+            elements *= shape[d];
+        }
+        if (!in) ioFail("loadCheckpoint: '" + path + "' is truncated or corrupt");
+        auto it = byName.find(name);
+        if (it == byName.end()) ioFail("loadCheckpoint: the model has no parameter named '" + name + "'");
+        if (params[it->second]->fullShape != shape) ioFail("loadCheckpoint: shape mismatch for '" + name + "'");
+        data.resize(elements);
+        in.read(reinterpret_cast<char*>(data.data()), static_cast<std::streamsize>(elements * sizeof(float)));
+        if (!in) ioFail("loadCheckpoint: '" + path + "' is truncated or corrupt");
+        model.setParameter(it->second, data.data());
+    }
+}
+
+// ---- Executor -----------------------------------------------------------------------------------------------
+
+HostTensor Executor::makeSyntheticInput(const std::vector<OpDesc>& ops, const std::vector<std::int64_t>& inputShape,
+                                        std::size_t batchSize) const {
+    std::vector<std::size_t> shape;
+    for (std::int64_t d : inputShape) shape.push_back(d < 0 ? batchSize : static_cast<std::size_t>(d));
+    if (!ops.empty() && ops.front().kind == BFB_OP_EMBEDDING) {
+        return randomTokenIdTensor(std::move(shape), static_cast<std::size_t>(ops.front().embedding_vocab_size),
+                                   seedFor(seed_, 0, kInputSalt));
+    }
+    return randomTensor(std::move(shape), seedFor(seed_, 0, kInputSalt));
+}
+
+HostTensor Executor::run(const std::vector<OpDesc>& ops, std::int64_t inputLastDim, const HostTensor& input,
+                         const std::optional<PrecisionPolicy>& precision) const {
+    if (ops.empty()) throw std::invalid_argument("the model has no pipeline to run");
+    Model model(ops, inputLastDim, seed_, precision, true, "executor");
+    DeviceTensor out = model.forward(DeviceTensor::fromHost(input));
+    return out.toHost();
+}
+
+}  // namespace bfb200

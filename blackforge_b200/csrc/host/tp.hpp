@@ -1,0 +1,17 @@
+// Tensor-parallel communicator: one NCCL communicator per process (one process per GPU), loaded at
+// run time so the library has no link-time NCCL dependency and shares the copy the launcher's
+// framework may already have loaded.
+#pragma once
+
+#include <cstdint>
+
+namespace bfb200 {
+
+void tpUniqueId(void* hostId128);
+void tpInit(const void* hostId128, int rank, int world);
+// In-place sum over all ranks on `stream`; dtype is BFB_F32 or BFB_BF16.
+void tpAllReduceSum(void* deviceBuffer, std::int64_t count, int dtype, void* stream);
+void tpDestroy();
+bool tpReady();
+
+}  // namespace bfb200

@@ -1,0 +1,80 @@
+// Internal C++ entry points of the kernel layer. The C ABI (capi.cu) and the host-side operator
+// layer (host/*.cpp) both call these; they throw bfb::Error and never fall back to the CPU.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace bfb {
+
+void embedPos(const float* ids, const float* table, const float* pos, void* out, int outDtype, int64_t batch,
+              int64_t seq, int64_t vocab, int64_t dim, int64_t maxSeq, int64_t posOffset, int* oobCount,
+              cudaStream_t stream);
+void addPositional(const float* in, const float* pos, float* out, int64_t batch, int64_t seq, int64_t dim,
+                   int64_t maxSeq, int64_t posOffset, cudaStream_t stream);
+void rmsnorm(const void* x, int xDtype, void* out, int outDtype, int64_t rows, int64_t dim, float eps,
+             cudaStream_t stream);
+void softmaxRows(const float* x, float* out, int64_t rows, int64_t cols, cudaStream_t stream);
+void elementwise(int op, const float* a, const float* b, const float* c, float* out, int64_t n, int64_t cols,
+                 cudaStream_t stream);
+void castScaled(const void* in, int inDtype, void* out, int outDtype, int64_t n, float scale, const float* dScale,
+                cudaStream_t stream);
+void amax(const void* in, int inDtype, int64_t n, float* dAmax, cudaStream_t stream);
+void fp8ScaleFromAmax(const float* dAmax, float* dScales, cudaStream_t stream);
+// out[0] = 448 / amax, out[1] = 1 / out[0], out[2] = out[1] * *dWeightInverse (the GEMM's alpha).
+void fp8ActScale(const float* dAmax, float* out, const float* dWeightInverse, cudaStream_t stream);
+void weightPrepare(const float* w, void* out, int outDtype, int64_t k, int64_t n, float scale, const float* dScale,
+                   cudaStream_t stream);
+// In-place rounding of an f32 buffer to bf16 precision (simulated `storage bf16` for the fp32 path).
+void roundBf16InPlace(float* x, int64_t n, cudaStream_t stream);
+
+struct GemmArgs {
+    const void* a = nullptr;      // [M,K] row-major, abDtype
+    const void* b = nullptr;      // [K,N] (BFB_B_KN) or [N,K] (BFB_B_NK), abDtype
+    void* c = nullptr;            // [M,N], cDtype
+    int64_t m = 0, n = 0, k = 0;
+    int abDtype = 0, bLayout = 0, cDtype = 0, epilogue = 0;
+    const float* bias = nullptr;
+    const void* residual = nullptr;
+    float alpha = 1.0f;
+    const float* dAlpha = nullptr;
+    int roundCBf16 = 0;
+    int* dStatus = nullptr;
+};
+void gemm(const GemmArgs& args, cudaStream_t stream);
+// True when the tcgen05 kernel takes this problem (otherwise the CUDA-core kernel runs).
+bool gemmUsesTensorCores(const GemmArgs& args);
+void matmulTransposeB(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, cudaStream_t stream);
+
+struct AttentionArgs {
+    const void* q = nullptr;
+    const void* k = nullptr;
+    const void* v = nullptr;
+    void* out = nullptr;
+    float* m = nullptr;
+    float* l = nullptr;
+    int dtype = 0;
+    int64_t batch = 0, newLen = 0, totalLen = 0, numHeads = 0, headDim = 0;
+    int64_t ldQ = 0, ldK = 0, ldV = 0, ldO = 0;
+    float scale = 1.0f;
+    int64_t oldLen = 0;
+    int causal = 1;
+    int* dStatus = nullptr;
+};
+void attentionForward(const AttentionArgs& args, cudaStream_t stream);
+bool attentionUsesTensorCores(const AttentionArgs& args);
+
+// Tensor-core kernels (gemm_tc.cu / attention_tc.cu); callers have checked eligibility.
+void gemmTensorCore(const GemmArgs& args, cudaStream_t stream);
+void attentionTensorCore(const AttentionArgs& args, cudaStream_t stream);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda dependency).
+// dims/strides innermost first; strides in bytes for dims 1..rank-1; elemBytes 1 or 2.
+struct TensorMapStorage {
+    alignas(64) unsigned char bytes[128];
+};
+void encodeTensorMap(TensorMapStorage* out, const void* base, int elemBytes, int rank, const uint64_t* dims,
+                     const uint64_t* stridesBytes, const uint32_t* box);
+
+}  // namespace bfb

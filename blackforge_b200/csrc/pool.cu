@@ -1,0 +1,129 @@
+// Device memory pool + process-wide helpers behind the C ABI.
+//
+// The pool keeps the reference's contract (exact-size free lists per device, memory is reused and
+// never handed back to the driver on release, release must not throw) and adds a mutex, statistics
+// and an explicit trim.
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "common.cuh"
+#include "pool.hpp"
+
+namespace bfb {
+
+std::string& lastErrorSlot() {
+    thread_local std::string slot;
+    return slot;
+}
+
+int64_t& launchCounter() {
+    thread_local int64_t counter = 0;
+    return counter;
+}
+
+int smCount() {
+    static std::mutex mu;
+    static std::unordered_map<int, int> cache;
+    int dev = 0;
+    BFB_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(dev);
+    if (it != cache.end()) return it->second;
+    int n = 0;
+    BFB_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    cache[dev] = n;
+    return n;
+}
+
+namespace {
+
+struct DevicePool {
+    std::unordered_map<size_t, std::vector<void*>> freeLists;
+    size_t cachedBytes = 0;
+    size_t liveBytes = 0;
+};
+
+std::mutex gPoolMutex;
+std::unordered_map<int, DevicePool> gPools;
+
+int currentDevice() {
+    int dev = 0;
+    BFB_CUDA(cudaGetDevice(&dev));
+    return dev;
+}
+
+}  // namespace
+
+void* poolAcquire(size_t bytes) {
+    if (bytes == 0) return nullptr;
+    int dev = currentDevice();
+    {
+        std::lock_guard<std::mutex> lock(gPoolMutex);
+        DevicePool& pool = gPools[dev];
+        auto it = pool.freeLists.find(bytes);
+        if (it != pool.freeLists.end() && !it->second.empty()) {
+            void* p = it->second.back();
+            it->second.pop_back();
+            pool.cachedBytes -= bytes;
+            pool.liveBytes += bytes;
+            return p;
+        }
+    }
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) {
+        // one retry after giving cached buffers back, then report
+        cudaGetLastError();
+        poolTrim();
+        e = cudaMalloc(&p, bytes);
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        fail(BFB_CUDA_ERROR, "device pool: cudaMalloc of " + std::to_string(bytes) + " bytes failed: " +
+                                 cudaGetErrorString(e));
+    }
+    std::lock_guard<std::mutex> lock(gPoolMutex);
+    gPools[dev].liveBytes += bytes;
+    return p;
+}
+
+void poolRelease(void* ptr, size_t bytes) noexcept {
+    if (ptr == nullptr || bytes == 0) return;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return;
+    try {
+        std::lock_guard<std::mutex> lock(gPoolMutex);
+        DevicePool& pool = gPools[dev];
+        pool.freeLists[bytes].push_back(ptr);
+        pool.cachedBytes += bytes;
+        pool.liveBytes = pool.liveBytes >= bytes ? pool.liveBytes - bytes : 0;
+    } catch (...) {
+        cudaFree(ptr);
+    }
+}
+
+void poolTrim() {
+    int dev = currentDevice();
+    std::vector<void*> victims;
+    {
+        std::lock_guard<std::mutex> lock(gPoolMutex);
+        DevicePool& pool = gPools[dev];
+        for (auto& kv : pool.freeLists) {
+            for (void* p : kv.second) victims.push_back(p);
+            kv.second.clear();
+        }
+        pool.cachedBytes = 0;
+    }
+    for (void* p : victims) cudaFree(p);
+}
+
+void poolStats(size_t* cached, size_t* live) {
+    int dev = currentDevice();
+    std::lock_guard<std::mutex> lock(gPoolMutex);
+    DevicePool& pool = gPools[dev];
+    if (cached != nullptr) *cached = pool.cachedBytes;
+    if (live != nullptr) *live = pool.liveBytes;
+}
+
+}  // namespace bfb

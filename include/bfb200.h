@@ -1,0 +1,279 @@
+/*
+ * bfb200 — C ABI of the B200 (sm_100a) backend for BlackForge's decoder-only forward path.
+ *
+ * BlackForge has no FFI layer of its own: its boundary is the C++ operator API in namespace
+ * blackforge::backend::cuda (DeviceTensor + free functions + Model/Executor). This header is the
+ * flat C surface a drop-in for that API binds to; each entry point names the reference interface
+ * (path:line inside the BlackForge project) whose work it takes over.
+ *
+ * Conventions
+ *  - Every function returns a bfb_status. On failure bfb_last_error() (per host thread) explains.
+ *    BFB_INVALID_ARGUMENT corresponds to the reference's std::invalid_argument, BFB_CUDA_ERROR and
+ *    BFB_IO_ERROR to its std::runtime_error. Nothing is launched when arguments are rejected.
+ *  - Pointers named d_* are device pointers on the CURRENT device (cudaSetDevice is ambient state,
+ *    as in the reference, src/backend/cuda/device_query.cu:34-40); h_* are host pointers.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream the reference
+ *    uses everywhere).
+ *  - Row-major everywhere. A tensor [batch, seq, dim] keeps attention heads contiguous inside dim
+ *    (include/blackforge/backend/cuda/fused_attention.hpp:48-57).
+ *  - There is no CPU fallback: if no CUDA device/driver is usable the compute entry points fail with
+ *    BFB_CUDA_ERROR.
+ */
+#ifndef BFB200_H
+#define BFB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t bfb_status;
+enum {
+    BFB_OK = 0,
+    BFB_INVALID_ARGUMENT = 1, /* shape / rank / range violations */
+    BFB_CUDA_ERROR = 2,       /* CUDA runtime or driver failure */
+    BFB_TIMEOUT = 3,          /* a bounded device-side wait ran out (kernel unwound cleanly) */
+    BFB_UNSUPPORTED = 4,      /* valid request this build has no kernel for */
+    BFB_IO_ERROR = 5          /* checkpoint file problems */
+};
+
+/* Element formats of device buffers. */
+enum { BFB_F32 = 0, BFB_BF16 = 1, BFB_FP8_E4M3 = 2 };
+
+/* sema::DType codes (include/blackforge/sema/dtype.hpp:12-19), used by precision policies. */
+enum { BFB_DT_FP8_E4M3 = 0, BFB_DT_FP8_E5M2 = 1, BFB_DT_FP16 = 2, BFB_DT_BF16 = 3, BFB_DT_TF32 = 4, BFB_DT_FP32 = 5 };
+
+/* ir::OpKind (include/blackforge/ir/operation.hpp:11-12), same order. */
+enum {
+    BFB_OP_LINEAR = 0, BFB_OP_SILU, BFB_OP_RELU, BFB_OP_GELU, BFB_OP_RMSNORM, BFB_OP_SOFTMAX, BFB_OP_EMBEDDING,
+    BFB_OP_POSITIONAL_EMBEDDING, BFB_OP_ATTENTION, BFB_OP_FEEDFORWARD, BFB_OP_BIDIRECTIONAL_ATTENTION
+};
+
+/* Mirror of ir::Operation (include/blackforge/ir/operation.hpp:23-33). */
+typedef struct bfb_op_desc {
+    int32_t kind;
+    int64_t input;   /* value id of the input */
+    int64_t output;  /* value id of the output: the integer in parameter names */
+    int64_t linear_out_features;
+    int64_t embedding_vocab_size;
+    int64_t embedding_dim;
+    int64_t positional_max_seq_len;
+    int64_t attention_num_heads;
+    int64_t feedforward_hidden_dim;
+} bfb_op_desc;
+
+/* Mirror of ir::PrecisionPolicy (include/blackforge/ir/module.hpp:44-48); BFB_DT_* codes. */
+typedef struct bfb_precision {
+    int32_t present; /* 0 = the program has no precision block */
+    int32_t storage;
+    int32_t compute;
+    int32_t accumulate;
+} bfb_precision;
+
+/* GEMM epilogues: C = epilogue(alpha * A*B). */
+enum {
+    BFB_EPI_NONE = 0,
+    BFB_EPI_BIAS = 1,          /* + bias[col]                 addBias,          ops_elementwise.cu:158-176 */
+    BFB_EPI_BIAS_SILU = 2,     /* silu(. + bias[col])         addBiasSilu,      ops_elementwise.cu:178-193 */
+    BFB_EPI_BIAS_RESIDUAL = 3, /* . + bias[col] + residual    addBiasResidual,  ops_elementwise.cu:195-213 */
+    BFB_EPI_RESIDUAL = 4       /* . + residual                add,              ops_elementwise.cu:147-156 */
+};
+
+/* Layout of the second GEMM operand. */
+enum {
+    BFB_B_KN = 0, /* B[K,N] row-major: the reference's weight layout (src/backend/cuda/model.cu:172-175) */
+    BFB_B_NK = 1  /* B^T[N,K] row-major: produced once by bfb_weight_prepare */
+};
+
+/* Unary / binary elementwise selectors for bfb_elementwise. */
+enum {
+    BFB_EW_ADD = 0,           /* add              ops_elementwise.cu:147-156 */
+    BFB_EW_ADD_BIAS = 1,      /* addBias          ops_elementwise.cu:158-176 */
+    BFB_EW_ADD_BIAS_SILU = 2, /* addBiasSilu      ops_elementwise.cu:178-193 */
+    BFB_EW_ADD_BIAS_RESIDUAL = 3, /* addBiasResidual ops_elementwise.cu:195-213 */
+    BFB_EW_SILU = 4,          /* silu             ops_elementwise.cu:215-223 */
+    BFB_EW_RELU = 5,          /* relu             ops_elementwise.cu:500-507 */
+    BFB_EW_GELU = 6           /* gelu             ops_elementwise.cu:509-515 */
+};
+
+const char* bfb_last_error(void);
+/* Library version (major*10000 + minor*100 + patch). */
+int32_t bfb_version(void);
+/* Number of usable CUDA devices; 0 devices is reported as BFB_CUDA_ERROR.
+ * Replaces enumerateDevices (src/backend/cuda/device_query.cu:9-32). */
+bfb_status bfb_device_count(int32_t* count);
+/* Replaces setActiveDevice (src/backend/cuda/device_query.cu:34-40). */
+bfb_status bfb_set_device(int32_t index);
+
+/* ---- device memory pool ----------------------------------------------------------------------
+ * Replaces devicePoolAcquire / devicePoolRelease (src/backend/cuda/device_pool.cu:29-65): per-device
+ * free lists keyed by exact byte size, buffers are never returned to the driver unless trimmed,
+ * release never fails loudly. bytes == 0 yields a NULL pointer. */
+bfb_status bfb_pool_acquire(size_t bytes, void** d_out);
+bfb_status bfb_pool_release(void* d_ptr, size_t bytes);
+/* Extension: give cached buffers of the current device back to the driver. */
+bfb_status bfb_pool_trim(void);
+/* Extension: bytes currently cached / handed out on the current device. */
+bfb_status bfb_pool_stats(size_t* cached_bytes, size_t* live_bytes);
+
+/* ---- host <-> device copies (DeviceTensor::fromHost / toHost / clone, device_tensor.cu:68-115) */
+bfb_status bfb_copy_h2d(void* d_dst, const void* h_src, size_t bytes, void* stream);
+bfb_status bfb_copy_d2h(void* h_dst, const void* d_src, size_t bytes, void* stream);
+bfb_status bfb_copy_d2d(void* d_dst, const void* d_src, size_t bytes, void* stream);
+bfb_status bfb_memset_zero(void* d_dst, size_t bytes, void* stream);
+bfb_status bfb_stream_synchronize(void* stream);
+
+/* ---- gather + positions -----------------------------------------------------------------------
+ * out[t, :] = table[lround(ids[t]), :] (+ pos[(pos_offset + t % seq), :] when d_pos != NULL).
+ * Replaces embeddingLookup / embeddingLookupPreValidated (ops_elementwise.cu:372-441, kernel :305-326)
+ * fused with addPositionalEmbedding / addPositionalEmbeddingAt (ops_elementwise.cu:443-498).
+ * ids are float32 holding integers. Rows whose id is outside [0, vocab) are zero-filled, as the
+ * reference kernel does, and *d_oob_count (optional, int32 on device) is incremented per bad row:
+ * the host layer turns a non-zero count into BFB_INVALID_ARGUMENT without a D2H copy of the ids.
+ * out_dtype: BFB_F32 (bit-exact with the reference) or BFB_BF16 (storage bf16: rounded once). */
+bfb_status bfb_embed_pos(const float* d_ids, const float* d_table, const float* d_pos, void* d_out, int32_t out_dtype,
+                         int64_t batch, int64_t seq, int64_t vocab, int64_t dim, int64_t max_seq, int64_t pos_offset,
+                         int32_t* d_oob_count, void* stream);
+
+/* out = in + pos[(pos_offset + s), :] on an existing [batch, seq, dim] f32 tensor.
+ * Replaces addPositionalEmbedding(+At) (ops_elementwise.cu:443-498). */
+bfb_status bfb_add_positional(const float* d_in, const float* d_pos, float* d_out, int64_t batch, int64_t seq,
+                              int64_t dim, int64_t max_seq, int64_t pos_offset, void* stream);
+
+/* ---- rmsnorm: y = x / sqrt(mean(x^2) + eps), no gamma ------------------------------------------
+ * Replaces rmsnorm (ops_elementwise.cu:355-370, kernel :102-137); eps is an argument, the reference's
+ * value is 1e-6. x_dtype / out_dtype in {BFB_F32, BFB_BF16}; the row is read once. */
+bfb_status bfb_rmsnorm(const void* d_x, int32_t x_dtype, void* d_out, int32_t out_dtype, int64_t rows, int64_t dim,
+                       float eps, void* stream);
+
+/* Row softmax on f32 (softmax, ops_elementwise.cu:225-243, kernel :249-300). */
+bfb_status bfb_softmax(const float* d_x, float* d_out, int64_t rows, int64_t cols, void* stream);
+
+/* f32 elementwise ops (BFB_EW_*). `cols` is the bias length for the bias forms; d_b is the second
+ * operand (add) or the bias; d_c the residual of BFB_EW_ADD_BIAS_RESIDUAL. */
+bfb_status bfb_elementwise(int32_t op, const float* d_a, const float* d_b, const float* d_c, float* d_out, int64_t n,
+                           int64_t cols, void* stream);
+
+/* ---- format conversion -------------------------------------------------------------------------
+ * out = convert(in * scale). scale comes from *d_scale when non-NULL, else `scale`.
+ * Replaces floatToBf16Kernel (ops_tensorcore.cu:21-26) and adds the fp8 e4m3 (saturating) forms. */
+bfb_status bfb_cast(const void* d_in, int32_t in_dtype, void* d_out, int32_t out_dtype, int64_t n, float scale,
+                    const float* d_scale, void* stream);
+/* *d_amax = max(*d_amax, max|in|) (f32 word on device; zero it first for a fresh maximum).
+ * No counterpart in the reference (its fp8 path is declared only, README.md:68). */
+bfb_status bfb_amax(const void* d_in, int32_t in_dtype, int64_t n, float* d_amax, void* stream);
+/* d_scales[0] = 448 / amax (1 when amax == 0), d_scales[1] = 1 / d_scales[0]; reads *d_amax on device. */
+bfb_status bfb_fp8_scale_from_amax(const float* d_amax, float* d_scales, void* stream);
+/* Weight preparation, done once per weight: W[K,N] f32 (reference layout) -> W^T[N,K] in out_dtype,
+ * multiplied by scale (*d_scale when non-NULL). Takes over the per-call weight cast of
+ * matmulBf16 (ops_tensorcore.cu:316-317) and the cached-weight variant (:98-131). */
+bfb_status bfb_weight_prepare(const float* d_w, void* d_out, int32_t out_dtype, int64_t k, int64_t n, float scale,
+                              const float* d_scale, void* stream);
+
+/* ---- GEMM: C[M,N] = epilogue(alpha * A[M,K] * B) ------------------------------------------------
+ * Replaces matmul (cublasSgemm, ops_gemm.cu:64-93), matmulBf16 / bf16Gemm (cublasLtMatmul,
+ * ops_tensorcore.cu:293-327), linear / linearBf16 (+ addBias) and the fused bias/silu/residual
+ * passes listed at BFB_EPI_*.
+ *  ab_dtype  BFB_F32      fp32 FFMA kernel, fp32 accumulate in k order (the exactness path)
+ *            BFB_BF16     tcgen05 kind::f16 on TMA-fed tiles, fp32 accumulate in TMEM
+ *            BFB_FP8_E4M3 tcgen05 kind::f8f6f4 (B must be BFB_B_NK), fp32 accumulate
+ *  b_layout  BFB_B_KN or BFB_B_NK
+ *  c_dtype   BFB_F32 or BFB_BF16; bias is f32[N]; residual has c_dtype and shape [M,N]
+ *  alpha     multiplies the accumulator; *d_alpha (device f32) is used instead when non-NULL
+ *  round_c_bf16  non-zero: round an f32 result to bf16 precision before storing (`storage bf16`)
+ * Shapes the tensor-core kernel cannot take (K or N not a multiple of 8 for bf16 / 16 for fp8, or
+ * misaligned pointers) run a CUDA-core kernel that rounds operands to ab_dtype: same arithmetic
+ * contract, no alignment demands. d_status (optional int32 on device) receives a non-zero code if a
+ * bounded wait inside the tensor-core kernel ran out. */
+bfb_status bfb_gemm(const void* d_a, const void* d_b, void* d_c, int64_t m, int64_t n, int64_t k, int32_t ab_dtype,
+                    int32_t b_layout, int32_t c_dtype, int32_t epilogue, const float* d_bias, const void* d_residual,
+                    float alpha, const float* d_alpha, int32_t round_c_bf16, int32_t* d_status, void* stream);
+
+/* A * B^T on f32: a[M,K], b[N,K] (matmulTransposeB, ops_gemm.cu:95-110, kernel :20-34). */
+bfb_status bfb_matmul_transpose_b(const float* d_a, const float* d_b, float* d_c, int64_t m, int64_t n, int64_t k,
+                                  void* stream);
+
+/* ---- causal attention core ---------------------------------------------------------------------
+ * Replaces fusedAttentionForward (src/backend/cuda/fused_attention.cu:315-341, kernel :60-157).
+ * q [batch, new_len, H*D] with row stride ld_q elements; k, v [batch, total_len, H*D] with strides
+ * ld_k, ld_v (strides let Q, K, V live interleaved in one [tokens, 3*dim] projection output).
+ * Query row i attends keys j <= old_len + i. out [batch, new_len, H*D] (row stride ld_o); optional
+ * d_m, d_l f32 [batch, H, new_len] receive the online-softmax statistics (row max of scaled scores,
+ * sum of exp) as the reference returns them.
+ *  dtype BFB_BF16: tcgen05 flash kernel for D == 128 (TMA tiles, fp32 online softmax in registers,
+ *                  no materialised scores); other D run the CUDA-core kernel on bf16 data
+ *  dtype BFB_F32 : CUDA-core online-softmax kernel, D <= 256 (the reference's limit, :305-311)
+ * out has the same dtype as the inputs. causal == 0 gives the bidirectional form. */
+bfb_status bfb_attention_fwd(const void* d_q, const void* d_k, const void* d_v, void* d_out, float* d_m, float* d_l,
+                             int32_t dtype, int64_t batch, int64_t new_len, int64_t total_len, int64_t num_heads,
+                             int64_t head_dim, int64_t ld_q, int64_t ld_k, int64_t ld_v, int64_t ld_o, float scale,
+                             int64_t old_len, int32_t causal, int32_t* d_status, void* stream);
+
+/* ---- model: the IR executor's device side ------------------------------------------------------
+ * Replaces cuda::Model (src/backend/cuda/model.cu:139-306: constructor, forward, parameters),
+ * cuda::Executor::run / makeSyntheticInput (src/backend/cuda/executor.cu:26-132) and
+ * cuda::loadCheckpoint / saveCheckpoint (src/backend/cuda/checkpoint.cu:60-130).
+ * A model is built from the pipeline of an ir::ModelIR; default parameters reproduce the
+ * reference's seeded uniform(-0.1, 0.1) initialisation so that `run` without a checkpoint gives the
+ * reference's numbers. */
+typedef struct bfb_model bfb_model;
+
+/* input_last_dim: literal size of the input value's last dimension (0 if symbolic). */
+bfb_status bfb_model_create(const bfb_op_desc* ops, int32_t n_ops, int64_t input_last_dim, uint32_t seed,
+                            const bfb_precision* precision, bfb_model** out);
+void bfb_model_destroy(bfb_model* model);
+/* Skip the default random initialisation (parameters start at zero) — for models that are always
+ * loaded from a checkpoint; call before any parameter access. */
+bfb_status bfb_model_create_uninitialised(const bfb_op_desc* ops, int32_t n_ops, int64_t input_last_dim,
+                                          const bfb_precision* precision, bfb_model** out);
+/* Tensor parallelism over `world` ranks (heads and feed-forward columns sharded, logits columns
+ * sharded); the all-reduce is done by the communicator installed with bfb_tp_init. world == 1 is
+ * the default. Must be called before parameters are set. */
+bfb_status bfb_model_set_tensor_parallel(bfb_model* model, int32_t rank, int32_t world);
+
+int32_t bfb_model_param_count(const bfb_model* model);
+const char* bfb_model_param_name(const bfb_model* model, int32_t index);
+int32_t bfb_model_param_rank(const bfb_model* model, int32_t index);
+void bfb_model_param_shape(const bfb_model* model, int32_t index, int64_t* shape_out);
+/* Full (unsharded) f32 values, host side. */
+bfb_status bfb_model_param_set(bfb_model* model, int32_t index, const float* h_values);
+bfb_status bfb_model_param_get(bfb_model* model, int32_t index, float* h_values);
+
+/* BFCKPT1 (include/blackforge/backend/cpu/checkpoint.hpp:15-24). Load matches by name and shape; an
+ * unknown name, a shape mismatch, a bad magic or a truncated file give BFB_IO_ERROR. */
+bfb_status bfb_model_load_checkpoint(bfb_model* model, const char* path);
+bfb_status bfb_model_save_checkpoint(bfb_model* model, const char* path);
+
+/* forward on device buffers: d_input f32 with `rank` dims (token ids as float for a model that starts
+ * with an embedding). The result is acquired from the pool (f32); release it with bfb_pool_release
+ * (bytes = 4 * product(out_shape)). input_range_trusted != 0 skips the id range check
+ * (Model::forward(input, inputRangeTrusted), model.cu:252). */
+bfb_status bfb_model_forward(bfb_model* model, const float* d_input, const int64_t* shape, int32_t rank,
+                             int32_t input_range_trusted, float** d_out, int64_t* out_shape, int32_t* out_rank,
+                             void* stream);
+/* The `blackforge run` path (src/main.cpp:356-388): host ids in, host logits out, synchronous.
+ * h_out must hold product(out_shape) floats; call once with h_out == NULL to learn the shape. */
+bfb_status bfb_model_forward_host(bfb_model* model, const float* h_input, const int64_t* shape, int32_t rank,
+                                  float* h_out, int64_t* out_shape, int32_t* out_rank);
+/* Number of kernels this library launched on the calling thread since the counter was last reset. */
+int64_t bfb_launch_count(int32_t reset);
+
+/* Executor::makeSyntheticInput (executor.cu:26-42): seeded ids/values, host side. */
+bfb_status bfb_synthetic_input(const bfb_op_desc* ops, int32_t n_ops, const int64_t* input_shape, int32_t rank,
+                               int64_t batch, uint32_t seed, float* h_out);
+
+/* ---- tensor-parallel communicator (NCCL over NVLink) -------------------------------------------
+ * No counterpart in the reference (its only multi-GPU code is host-staged gradient averaging,
+ * src/backend/cuda/multi_gpu_train_runner.cu:275-297). unique_id is the 128-byte ncclUniqueId made
+ * by rank 0 with bfb_tp_unique_id and distributed by the launcher. */
+bfb_status bfb_tp_unique_id(void* h_id_128);
+bfb_status bfb_tp_init(const void* h_id_128, int32_t rank, int32_t world);
+bfb_status bfb_tp_allreduce_sum(void* d_buf, int64_t count, int32_t dtype, void* stream);
+bfb_status bfb_tp_destroy(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BFB200_H */
