@@ -99,6 +99,9 @@ SIGNATURES = {
                                  C.POINTER(_I32), _P]),
     "bfb_model_forward_host": (_I32, [_P, _P, C.POINTER(_I64), _I32, _P, C.POINTER(_I64), C.POINTER(_I32)]),
     "bfb_launch_count": (_I64, [_I32]),
+    "bfb_profile_enable": (_I32, [_I32]),
+    "bfb_profile_reset": (_I32, []),
+    "bfb_profile_read": (_I32, [_I32, C.POINTER(C.c_double), C.POINTER(_I64), C.POINTER(C.c_double)]),
     "bfb_synthetic_input": (_I32, [C.POINTER(OpDesc), _I32, C.POINTER(_I64), _I32, _I64, C.c_uint32, _P]),
     "bfb_tp_unique_id": (_I32, [_P]),
     "bfb_tp_init": (_I32, [_P, _I32, _I32]),

@@ -404,6 +404,10 @@ void attentionTensorCore(const AttentionArgs& a, cudaStream_t stream) {
     const int64_t grid = static_cast<int64_t>(p.numQTiles) * a.batch * a.numHeads;
     require(grid <= 0x7FFFFFFF, "attention: too many query tiles for one launch");
     BFB_CUDA(cudaFuncSetAttribute(attentionTcKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmemBytes));
+    // visible (query, key) pairs per (batch, head): causal rows see old_len + i + 1 keys
+    const double nl = static_cast<double>(a.newLen), tl = static_cast<double>(a.totalLen);
+    const double pairs = a.causal ? nl * static_cast<double>(a.oldLen) + nl * (nl + 1.0) / 2.0 : nl * tl;
+    ProfileScope prof(kProfAttnTc, stream, 4.0 * kD * pairs * static_cast<double>(a.batch * a.numHeads));
     attentionTcKernel<<<static_cast<unsigned>(grid), kAttnThreads, kAttnSmemBytes, stream>>>(
         *reinterpret_cast<CUtensorMap*>(tq.bytes), *reinterpret_cast<CUtensorMap*>(tk.bytes),
         *reinterpret_cast<CUtensorMap*>(tv.bytes), p, a.dStatus);

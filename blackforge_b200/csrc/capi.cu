@@ -386,6 +386,21 @@ int64_t bfb_launch_count(int32_t reset) {
     return v;
 }
 
+bfb_status bfb_profile_enable(int32_t on) {
+    return guarded([&] { bfb::profileEnable(on != 0); });
+}
+
+bfb_status bfb_profile_reset(void) {
+    return guarded([&] { bfb::profileReset(); });
+}
+
+bfb_status bfb_profile_read(int32_t kind, double* milliseconds, int64_t* launches, double* work) {
+    return guarded([&] {
+        require(kind >= 0 && kind < bfb::kProfKindCount, "profile_read: unknown kind");
+        bfb::profileRead(kind, milliseconds, launches, work);
+    });
+}
+
 bfb_status bfb_synthetic_input(const bfb_op_desc* ops, int32_t n_ops, const int64_t* input_shape, int32_t rank,
                                int64_t batch, uint32_t seed, float* h_out) {
     return guarded([&] {

@@ -81,4 +81,30 @@ inline size_t dtypeBytes(int32_t dtype) {
 // Number of SMs of the current device (cached per device).
 int smCount();
 
+// ---- per-kernel device timing (off by default) -----------------------------------------------------
+// When enabled on the calling thread, a ProfileScope brackets one kernel launch with CUDA events on
+// the launching stream and books the elapsed time and the launch's algorithmic work (FLOPs or bytes)
+// under its kind. Reading a kind synchronises on its events.
+enum ProfileKind {
+    kProfGemmTc = 0,   // tcgen05 GEMM, work = 2*M*N*K FLOPs
+    kProfAttnTc = 1,   // tcgen05 attention, work = FLOPs of the visible (query, key) pairs
+    kProfRmsnorm = 2,  // work = bytes read + written
+    kProfEmbed = 3,    // work = bytes read + written
+    kProfCast = 4,     // work = bytes read + written
+    kProfKindCount = 5
+};
+void profileEnable(bool on);
+void profileReset();
+void profileRead(int kind, double* milliseconds, int64_t* launches, double* work);
+struct ProfileScope {
+    ProfileScope(int kind, cudaStream_t stream, double work);
+    ~ProfileScope();
+    ProfileScope(const ProfileScope&) = delete;
+    ProfileScope& operator=(const ProfileScope&) = delete;
+
+private:
+    int slot_ = -1;
+    cudaStream_t stream_ = nullptr;
+};
+
 }  // namespace bfb

@@ -415,6 +415,8 @@ void embedPos(const float* ids, const float* table, const float* pos, void* out,
     int threads = static_cast<int>(std::min<int64_t>(256, std::max<int64_t>(32, ((vec ? dim / 4 : dim) + 31) / 32 * 32)));
     int grid = gridFor(tokens, 1, 16);
     bool bf = outDtype == BFB_BF16;
+    ProfileScope prof(kProfEmbed, stream,
+                      static_cast<double>(tokens) * static_cast<double>(dim) * ((pos != nullptr ? 8.0 : 4.0) + (bf ? 2.0 : 4.0)));
 #define BFB_EMBED(V, B) \
     embedPosKernel<V, B><<<grid, threads, 0, stream>>>(ids, table, pos, out, tokens, seq, vocab, dim, posOffset, oobCount)
     if (vec && bf) BFB_EMBED(true, true);
@@ -446,6 +448,9 @@ void rmsnorm(const void* x, int xDtype, void* out, int outDtype, int64_t rows, i
     if (rows == 0) return;
     require(x != nullptr && out != nullptr, "rmsnorm: null pointer");
     using bf = __nv_bfloat16;
+    ProfileScope prof(kProfRmsnorm, stream,
+                      static_cast<double>(rows) * static_cast<double>(dim) *
+                          static_cast<double>(dtypeBytes(xDtype) + dtypeBytes(outDtype)));
     if (xDtype == BFB_F32 && outDtype == BFB_F32)
         rmsnormDispatch(static_cast<const float*>(x), static_cast<float*>(out), rows, dim, eps, stream);
     else if (xDtype == BFB_F32)
@@ -505,6 +510,8 @@ void castScaled(const void* in, int inDtype, void* out, int outDtype, int64_t n,
     if (n == 0) return;
     require(in != nullptr && out != nullptr, "cast: null pointer");
     using bf = __nv_bfloat16;
+    ProfileScope prof(kProfCast, stream,
+                      static_cast<double>(n) * static_cast<double>(dtypeBytes(inDtype) + dtypeBytes(outDtype)));
     using f8 = __nv_fp8_e4m3;
     if (inDtype == BFB_BF16 && outDtype == BFB_FP8_E4M3 && n % 8 == 0 && reinterpret_cast<uintptr_t>(in) % 16 == 0 &&
         reinterpret_cast<uintptr_t>(out) % 8 == 0) {

@@ -350,6 +350,7 @@ void launchTc(const GemmArgs& g, cudaStream_t stream) {
     auto kernel = gemmTcKernel<kElemBytes, kBMnMajor, TC>;
     // per device, so set on every launch (the process may have switched devices)
     BFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    ProfileScope prof(kProfGemmTc, stream, 2.0 * static_cast<double>(g.m) * static_cast<double>(g.n) * static_cast<double>(g.k));
     kernel<<<grid, kThreads, kSmemBytes, stream>>>(*reinterpret_cast<CUtensorMap*>(ta.bytes),
                                                    *reinterpret_cast<CUtensorMap*>(tb.bytes), ep,
                                                    static_cast<int>(g.m), static_cast<int>(g.n), static_cast<int>(g.k),

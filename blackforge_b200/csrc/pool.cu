@@ -36,6 +36,78 @@ int smCount() {
     return n;
 }
 
+// ---- per-kernel timing -----------------------------------------------------------------------------
+namespace {
+struct ProfileRecord {
+    int kind;
+    cudaEvent_t start, stop;
+    double work;
+};
+struct ProfileState {
+    bool enabled = false;
+    std::vector<ProfileRecord> records;
+    std::vector<cudaEvent_t> spare;
+    cudaEvent_t event() {
+        if (!spare.empty()) {
+            cudaEvent_t e = spare.back();
+            spare.pop_back();
+            return e;
+        }
+        cudaEvent_t e = nullptr;
+        BFB_CUDA(cudaEventCreate(&e));
+        return e;
+    }
+};
+ProfileState& profileState() {
+    thread_local ProfileState state;
+    return state;
+}
+}  // namespace
+
+void profileEnable(bool on) { profileState().enabled = on; }
+
+void profileReset() {
+    ProfileState& st = profileState();
+    for (ProfileRecord& r : st.records) {
+        st.spare.push_back(r.start);
+        st.spare.push_back(r.stop);
+    }
+    st.records.clear();
+}
+
+void profileRead(int kind, double* milliseconds, int64_t* launches, double* work) {
+    ProfileState& st = profileState();
+    double ms = 0.0, w = 0.0;
+    int64_t n = 0;
+    for (ProfileRecord& r : st.records) {
+        if (r.kind != kind) continue;
+        BFB_CUDA(cudaEventSynchronize(r.stop));
+        float t = 0.0f;
+        BFB_CUDA(cudaEventElapsedTime(&t, r.start, r.stop));
+        ms += t;
+        w += r.work;
+        ++n;
+    }
+    if (milliseconds != nullptr) *milliseconds = ms;
+    if (launches != nullptr) *launches = n;
+    if (work != nullptr) *work = w;
+}
+
+ProfileScope::ProfileScope(int kind, cudaStream_t stream, double work) : stream_(stream) {
+    ProfileState& st = profileState();
+    if (!st.enabled) return;
+    ProfileRecord r{kind, st.event(), st.event(), work};
+    BFB_CUDA(cudaEventRecord(r.start, stream));
+    st.records.push_back(r);
+    slot_ = static_cast<int>(st.records.size()) - 1;
+}
+
+ProfileScope::~ProfileScope() {
+    if (slot_ < 0) return;
+    ProfileState& st = profileState();
+    if (slot_ < static_cast<int>(st.records.size())) cudaEventRecord(st.records[slot_].stop, stream_);
+}
+
 namespace {
 
 struct DevicePool {

@@ -260,6 +260,15 @@ bfb_status bfb_model_forward_host(bfb_model* model, const float* h_input, const 
 /* Number of kernels this library launched on the calling thread since the counter was last reset. */
 int64_t bfb_launch_count(int32_t reset);
 
+/* Per-kernel device timing with CUDA events on the launching stream — the per-operation breakdown
+ * the reference's benchmark only has for its CPU backend (include/blackforge/backend/cpu/benchmark.hpp:34-43).
+ * Off by default; state is per host thread. `work` is the algorithmic FLOPs (GEMM, attention) or bytes
+ * (the rest) of the launches booked under a kind. Reading synchronises on the recorded events. */
+enum { BFB_PROF_GEMM_TC = 0, BFB_PROF_ATTENTION_TC = 1, BFB_PROF_RMSNORM = 2, BFB_PROF_EMBED = 3, BFB_PROF_CAST = 4 };
+bfb_status bfb_profile_enable(int32_t on);
+bfb_status bfb_profile_reset(void);
+bfb_status bfb_profile_read(int32_t kind, double* milliseconds, int64_t* launches, double* work);
+
 /* Executor::makeSyntheticInput (executor.cu:26-42): seeded ids/values, host side. */
 bfb_status bfb_synthetic_input(const bfb_op_desc* ops, int32_t n_ops, const int64_t* input_shape, int32_t rank,
                                int64_t batch, uint32_t seed, float* h_out);
