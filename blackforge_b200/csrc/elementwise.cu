@@ -204,6 +204,97 @@ __device__ __forceinline__ float fromFloat<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 fromFloat<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// 16-byte vectors of TIn <-> floats
+template <typename T>
+struct Vec16;
+template <>
+struct Vec16<float> {
+    static constexpr int kN = 4;
+    __device__ static void load(const float* p, float* v) {
+        float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
+};
+template <>
+struct Vec16<__nv_bfloat16> {
+    static constexpr int kN = 8;
+    __device__ static void load(const __nv_bfloat16* p, float* v) {
+        uint4 t = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+};
+template <typename TOut, int kN>
+__device__ __forceinline__ void storeRun(TOut* p, const float* v) {
+    if constexpr (sizeof(TOut) == 4) {
+#pragma unroll
+        for (int i = 0; i < kN; i += 4) *reinterpret_cast<float4*>(p + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    } else if constexpr (kN == 8) {
+        uint4 t;
+        uint32_t* w = reinterpret_cast<uint32_t*>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p) = t;
+    } else {
+        uint2 t;
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(v[2], v[3]);
+        t.x = *reinterpret_cast<uint32_t*>(&lo);
+        t.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = t;
+    }
+}
+
+// One warp per row; every lane issues all of its 16-byte loads before the reduction, so a row of up to
+// 32 * kVecs * 16 bytes is in flight at once and is read exactly once.
+template <typename TIn, typename TOut, int kVecs>
+__global__ void __launch_bounds__(kThreads)
+rmsnormWarpKernel(const TIn* __restrict__ x, TOut* __restrict__ out, int64_t rows, int64_t dim, float eps) {
+    constexpr int kN = Vec16<TIn>::kN;
+    const int lane = threadIdx.x & 31;
+    const int64_t warpsPerGrid = static_cast<int64_t>(gridDim.x) * (kThreads / 32);
+    const int64_t nv = dim / kN;
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5); row < rows;
+         row += warpsPerGrid) {
+        const TIn* src = x + row * dim;
+        float vals[kVecs][kN];
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int64_t i = lane + 32 * j;
+            if (i < nv) Vec16<TIn>::load(src + i * kN, vals[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            if (lane + 32 * j < nv) {
+#pragma unroll
+                for (int e = 0; e < kN; ++e) ss = fmaf(vals[j][e], vals[j][e], ss);
+            }
+        }
+        const float total = warpSum(ss);
+        const float rms = sqrtf(total / static_cast<float>(dim) + eps);
+        TOut* dst = out + row * dim;
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int64_t i = lane + 32 * j;
+            if (i < nv) {
+                float o[kN];
+#pragma unroll
+                for (int e = 0; e < kN; ++e) o[e] = vals[j][e] / rms;
+                storeRun<TOut, kN>(dst + i * kN, o);
+            }
+        }
+    }
+}
+
 // Any dim, two passes over the row (second pass hits L1/L2).
 template <typename TIn, typename TOut>
 __global__ void rmsnormGenericKernel(const TIn* __restrict__ x, TOut* __restrict__ out, int64_t rows, int64_t dim,
@@ -228,7 +319,18 @@ template <typename TIn, typename TOut>
 void rmsnormDispatch(const TIn* x, TOut* out, int64_t rows, int64_t dim, float eps, cudaStream_t stream) {
     bool aligned = (dim % 4 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
                    (reinterpret_cast<uintptr_t>(out) % 16 == 0);
-    if (aligned && dim <= 1024) {
+    constexpr int kEpv = 16 / static_cast<int>(sizeof(TIn));  // elements per 16-byte load
+    const bool wide = aligned && dim % kEpv == 0 && (dim * sizeof(TOut)) % 16 == 0;
+    if (wide && dim <= 32 * 16 * kEpv) {
+        // one warp per row, the whole row in flight as 16-byte loads before anything is reduced
+        const int vecs = static_cast<int>((dim / kEpv + 31) / 32);
+        const int rowsPerBlock = kThreads / 32;
+        const int grid = gridFor(rows, rowsPerBlock, 8);
+        if (vecs <= 2) rmsnormWarpKernel<TIn, TOut, 2><<<grid, kThreads, 0, stream>>>(x, out, rows, dim, eps);
+        else if (vecs <= 4) rmsnormWarpKernel<TIn, TOut, 4><<<grid, kThreads, 0, stream>>>(x, out, rows, dim, eps);
+        else if (vecs <= 8) rmsnormWarpKernel<TIn, TOut, 8><<<grid, kThreads, 0, stream>>>(x, out, rows, dim, eps);
+        else rmsnormWarpKernel<TIn, TOut, 16><<<grid, kThreads, 0, stream>>>(x, out, rows, dim, eps);
+    } else if (aligned && dim <= 1024) {
         int rowsPerBlock = kThreads / 32;
         int grid = gridFor(rows, rowsPerBlock, 16);
         rmsnormKernel<TIn, TOut, 8, false><<<grid, kThreads, 0, stream>>>(x, out, rows, dim, eps);

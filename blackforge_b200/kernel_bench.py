@@ -1,0 +1,131 @@
+"""Times ONE kernel of the library in isolation through the C ABI (CUDA events on the launching stream,
+L2 flushed between iterations) and prints one JSON line. This is what the ncu captures under profiles/
+run, on small cases.
+
+    python -m blackforge_b200.kernel_bench gemm --m 65536 --n 2048 --k 2048 [--dtype bf16|fp8] [--epilogue none]
+    python -m blackforge_b200.kernel_bench attention --batch 16 --heads 16 --seq 2048
+    python -m blackforge_b200.kernel_bench rmsnorm --rows 65536 --dim 2048
+    python -m blackforge_b200.kernel_bench embed --batch 32 --seq 2048 --vocab 32000 --dim 2048
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import numpy as np
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "attention", "rmsnorm", "embed"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=2048)
+    ap.add_argument("--k", type=int, default=2048)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"])
+    ap.add_argument("--cdtype", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--epilogue", default="none")
+    ap.add_argument("--layout", default="nk", choices=["nk", "kn"])
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--rows", type=int, default=65536)
+    ap.add_argument("--dim", type=int, default=2048)
+    ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--stream-dtype", default="bf16", choices=["bf16", "f32"])
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    args = ap.parse_args()
+
+    import torch
+    import blackforge_b200 as bfb
+
+    if not torch.cuda.is_available():
+        raise SystemExit("kernel_bench needs a CUDA device")
+    lib = bfb.lib()
+    rng = np.random.default_rng(0)
+    flush = None if args.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def rand_dev(count, dtype, scale=1.0):
+        """Random device buffer in `dtype` without a host round trip of the full size in fp32."""
+        t = torch.randn(count, device="cuda", dtype=torch.float32) * scale
+        buf = bfb.DeviceBuffer(count * bfb.ELEM_BYTES[dtype])
+        bfb.check(lib.bfb_cast(t.data_ptr(), bfb.F32, buf.ptr, dtype, count, 1.0, None, None))
+        torch.cuda.synchronize()
+        return buf
+
+    status = bfb.DeviceBuffer.zeros(4)
+    if args.kernel == "gemm":
+        ab = bfb.BF16 if args.dtype == "bf16" else bfb.FP8_E4M3
+        cd = bfb.BF16 if args.cdtype == "bf16" else bfb.F32
+        a = rand_dev(args.m * args.k, ab)
+        b = rand_dev(args.n * args.k, ab, 0.05)
+        c = bfb.DeviceBuffer(args.m * args.n * bfb.ELEM_BYTES[cd])
+        bias = rand_dev(args.n, bfb.F32)
+        res = bfb.DeviceBuffer.zeros(args.m * args.n * bfb.ELEM_BYTES[cd])
+        layout = bfb.B_NK if args.layout == "nk" else bfb.B_KN
+        epi = bfb.EPI[args.epilogue]
+
+        def run():
+            bfb.check(lib.bfb_gemm(a.ptr, b.ptr, c.ptr, args.m, args.n, args.k, ab, layout, cd, epi, bias.ptr, res.ptr,
+                                   1.0, None, 0, status.ptr, None))
+        work, unit = 2.0 * args.m * args.n * args.k, "TFLOP/s"
+        desc = {"m": args.m, "n": args.n, "k": args.k, "operands": args.dtype, "c": args.cdtype, "epilogue": args.epilogue,
+                "b_layout": args.layout}
+    elif args.kernel == "attention":
+        dim = args.heads * 128
+        q, k, v = (rand_dev(args.batch * args.seq * dim, bfb.BF16) for _ in range(3))
+        out = bfb.DeviceBuffer(args.batch * args.seq * dim * 2)
+
+        def run():
+            bfb.check(lib.bfb_attention_fwd(q.ptr, k.ptr, v.ptr, out.ptr, None, None, bfb.BF16, args.batch, args.seq,
+                                            args.seq, args.heads, 128, dim, dim, dim, dim, float(128 ** -0.5), 0, 1,
+                                            status.ptr, None))
+        work, unit = 4.0 * 128 * args.batch * args.heads * args.seq * (args.seq + 1) / 2.0, "TFLOP/s"
+        desc = {"batch": args.batch, "heads": args.heads, "seq": args.seq, "head_dim": 128, "flops": "causal"}
+    elif args.kernel == "rmsnorm":
+        sd = bfb.BF16 if args.stream_dtype == "bf16" else bfb.F32
+        x = rand_dev(args.rows * args.dim, sd)
+        out = bfb.DeviceBuffer(args.rows * args.dim * 2)
+
+        def run():
+            bfb.check(lib.bfb_rmsnorm(x.ptr, sd, out.ptr, bfb.BF16, args.rows, args.dim, 1e-6, None))
+        work, unit = float(args.rows * args.dim * (bfb.ELEM_BYTES[sd] + 2)), "GB/s"
+        desc = {"rows": args.rows, "dim": args.dim, "in": args.stream_dtype, "out": "bf16"}
+    else:
+        sd = bfb.BF16 if args.stream_dtype == "bf16" else bfb.F32
+        table = rand_dev(args.vocab * args.dim, bfb.F32)
+        pos = rand_dev(args.seq * args.dim, bfb.F32)
+        ids = bfb.DeviceBuffer.from_numpy(rng.integers(0, args.vocab, size=(args.batch, args.seq)).astype(np.float32))
+        out = bfb.DeviceBuffer(args.batch * args.seq * args.dim * bfb.ELEM_BYTES[sd])
+
+        def run():
+            bfb.check(lib.bfb_embed_pos(ids.ptr, table.ptr, pos.ptr, out.ptr, sd, args.batch, args.seq, args.vocab,
+                                        args.dim, args.seq, 0, None, None))
+        work, unit = float(args.batch * args.seq * args.dim * (8 + bfb.ELEM_BYTES[sd])), "GB/s"
+        desc = {"batch": args.batch, "seq": args.seq, "vocab": args.vocab, "dim": args.dim, "out": args.stream_dtype}
+
+    for _ in range(args.warmup):
+        run()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(args.iters):
+        if flush is not None:
+            flush.zero_()            # 256 MiB write: evicts the 126 MB L2
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        run()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    st = int(status.to_numpy(np.int32, (1,))[0])
+    ms = float(np.median(times))
+    rate = work / (ms / 1e3) / (1e12 if unit == "TFLOP/s" else 1e9)
+    print(json.dumps({"kernel": args.kernel, "case": desc, "ms_median": ms, "ms_min": float(min(times)), "rate": rate,
+                      "unit": unit, "iters": args.iters, "l2_flushed": flush is not None, "device_status": st}))
+    return 0 if st == 0 else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
