@@ -24,6 +24,7 @@ SOURCES = [
     "elementwise.cu",
     "gemm_simt.cu",
     "gemm_tc.cu",
+    "gemm_tc2.cu",
     "attention_simt.cu",
     "attention_tc.cu",
     "capi.cu",

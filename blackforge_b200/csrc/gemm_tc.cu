@@ -16,6 +16,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -70,7 +71,7 @@ struct EpilogueParams {
     int roundCBf16;
 };
 
-__device__ __forceinline__ float siluDev(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float siluDev(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 // kElemBytes: 2 (bf16, kind::f16) or 1 (e4m3, kind::f8f6f4). kBMnMajor: B given as [K,N] row-major.
 template <int kElemBytes, bool kBMnMajor, typename TC>
@@ -398,7 +399,21 @@ bool gemmUsesTensorCores(const GemmArgs& g) {
     return true;
 }
 
+// BFB_GEMM_PAIR=0 in the environment keeps every GEMM on the one-CTA kernel (for A/B measurements).
+static bool pairKernelEnabled() {
+    static const bool enabled = [] {
+        const char* v = std::getenv("BFB_GEMM_PAIR");
+        return v == nullptr || v[0] != '0';
+    }();
+    return enabled;
+}
+
 void gemmTensorCore(const GemmArgs& g, cudaStream_t stream) {
+    // CTA pairs share 256-row tiles: worth it once there is more than one 128-row tile of work
+    if (g.bLayout == BFB_B_NK && g.m > 128 && pairKernelEnabled()) {
+        gemmTensorCorePair(g, stream);
+        return;
+    }
     const bool cf32 = g.cDtype == BFB_F32;
     using bf = __nv_bfloat16;
     if (g.abDtype == BFB_BF16) {

@@ -1,0 +1,340 @@
+// tcgen05 GEMM with CTA pairs (tcgen05.mma.cta_group::2): two CTAs of a cluster share one
+// 256 x 256 output tile. Each CTA stages its own 128 rows of A and one 128-row half of B^T per
+// k-slice (32 KiB instead of 48 KiB per stage, so the ring is 6 deep) and holds the accumulator of
+// its own 128 rows in tensor memory; the leader CTA issues every MMA for both. Against the one-CTA
+// kernel this cuts the bytes pulled from L2 per FLOP by a third and deepens the prefetch.
+//
+// Synchronisation across the pair:
+//   full[s]      lives in the leader; both CTAs' TMA loads book their bytes on it
+//   empty[s]     one per CTA; the leader's tcgen05.commit arrives on both
+//   accFull[b]   one per CTA; same commit form, tells both epilogues the accumulator is complete
+//   accEmpty[b]  lives in the leader; the epilogue threads of both CTAs arrive on it
+// Operands: A [M,K] and B^T [N,K], K contiguous (bf16 or e4m3); C f32 or bf16 with the fused epilogues.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "kernels.hpp"
+#include "ptx_sm100.cuh"
+
+namespace bfb {
+
+namespace {
+
+constexpr int kPairM = 256;          // rows of the pair's tile (128 per CTA)
+constexpr int kPairN = 256;
+constexpr int kHalfN = kPairN / 2;   // B rows staged by each CTA
+constexpr int kRowBytes2 = 128;
+constexpr int kStages2 = 6;
+constexpr int kABytes2 = 128 * kRowBytes2;     // 16 KiB
+constexpr int kBBytes2 = kHalfN * kRowBytes2;  // 16 KiB
+constexpr int kStageBytes2 = kABytes2 + kBBytes2;
+constexpr int kThreads2 = 384;       // producer, MMA, TMEM, spare + 8 epilogue warps
+constexpr int kEpilogueThreads2 = 256;
+constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + 1024 + 256;
+
+struct PairTile {
+    int m, n;
+};
+
+__device__ __forceinline__ PairTile pairTileCoord(int t, int tilesM, int tilesN, int groupN) {
+    int fullGroups = tilesN / groupN;
+    int perGroup = tilesM * groupN;
+    int g = t / perGroup;
+    int width = groupN;
+    int r = t - g * perGroup;
+    if (g >= fullGroups) {
+        g = fullGroups;
+        r = t - fullGroups * perGroup;
+        width = tilesN - fullGroups * groupN;
+    }
+    PairTile c;
+    c.m = r / width;
+    c.n = g * groupN + r % width;
+    return c;
+}
+
+struct PairEpilogue {
+    void* c;
+    const float* bias;
+    const void* residual;
+    float alpha;
+    const float* dAlpha;
+    int epilogue;
+    int roundCBf16;
+};
+
+__device__ __forceinline__ float siluFast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
+template <int kElemBytes, typename TC>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
+gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, PairEpilogue ep,
+               int m, int n, int k, int tilesM, int tilesN, int groupN, int* status) {
+    constexpr int kBlockK = kRowBytes2 / kElemBytes;
+    constexpr int kMmaPerStage = 4;
+    constexpr uint32_t kIdesc = make_idesc(kPairM, kPairN, kElemBytes == 2 ? 1u : 0u, 0u);
+
+    extern __shared__ uint8_t smemRaw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages2 * kStageBytes2);
+    uint64_t* fullBar = bars;
+    uint64_t* emptyBar = bars + kStages2;
+    uint64_t* accFullBar = bars + 2 * kStages2;
+    uint64_t* accEmptyBar = accFullBar + 2;
+    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(accEmptyBar + 2);
+    volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int numK = (k + kBlockK - 1) / kBlockK;
+    const int totalTiles = tilesM * tilesN;
+    const int clusterId = blockIdx.x >> 1;
+    const int numClusters = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages2; ++s) {
+            mbar_init(&fullBar[s], 1);
+            mbar_init(&emptyBar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&accFullBar[b], 1);
+            mbar_init(&accEmptyBar[b], 2 * kEpilogueThreads2);
+        }
+        *abortFlag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmapA);
+        tma_prefetch_desc(&tmapB);
+    }
+    if (warp == 2) {
+        tmem_alloc(tmemSlot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers exist before any remote arrival or copy can reach them
+    tc_fence_after();
+    const uint32_t tmemBase = *tmemSlot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        int stage = 0;
+        uint32_t phase = 0;
+        bool alive = true;
+        for (int t = clusterId; t < totalTiles && alive; t += numClusters) {
+            PairTile tc = pairTileCoord(t, tilesM, tilesN, groupN);
+            const int rowA = tc.m * kPairM + static_cast<int>(rank) * 128;
+            const int rowB = tc.n * kPairN + static_cast<int>(rank) * kHalfN;
+            for (int kb = 0; kb < numK; ++kb) {
+                if (!warp_all(mbar_wait(&emptyBar[stage], phase ^ 1u, abortFlag, status, kDevTimeoutStageEmpty))) {
+                    alive = false;
+                    break;
+                }
+                if (lane == 0) {
+                    uint8_t* sa = smem + stage * kStageBytes2;
+                    uint8_t* sb = sa + kABytes2;
+                    if (leader) mbar_arrive_expect_tx(&fullBar[stage], 2 * kStageBytes2);
+                    const uint32_t fullLeader = mapa_cluster(smem_u32(&fullBar[stage]), 0);
+                    tma_load_2d_pair(sa, &tmapA, fullLeader, kb * kBlockK, rowA);
+                    tma_load_2d_pair(sb, &tmapB, fullLeader, kb * kBlockK, rowB);
+                }
+                __syncwarp();
+                if (++stage == kStages2) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1 && leader) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        int stage = 0;
+        uint32_t phase = 0;
+        int local = 0;
+        bool alive = true;
+        for (int t = clusterId; t < totalTiles && alive; t += numClusters, ++local) {
+            const int buf = local & 1;
+            const uint32_t accPhase = (local >> 1) & 1u;
+            if (!warp_all(mbar_wait(&accEmptyBar[buf], accPhase ^ 1u, abortFlag, status, kDevTimeoutAccEmpty))) break;
+            tc_fence_after();
+            const uint32_t dTmem = tmemBase + static_cast<uint32_t>(buf * kPairN);
+            for (int kb = 0; kb < numK; ++kb) {
+                if (!warp_all(mbar_wait(&fullBar[stage], phase, abortFlag, status, kDevTimeoutTmaFull))) {
+                    alive = false;
+                    break;
+                }
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t aAddr = smem_u32(smem + stage * kStageBytes2);
+                    const uint32_t bAddr = aAddr + kABytes2;
+                    const uint64_t aDesc = make_smem_desc_sw128(aAddr, 0, 1024);
+                    const uint64_t bDesc = make_smem_desc_sw128(bAddr, 0, 1024);
+#pragma unroll
+                    for (int kk = 0; kk < kMmaPerStage; ++kk) {
+                        const uint64_t step = static_cast<uint64_t>((kk * 32) >> 4);
+                        const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
+                        if constexpr (kElemBytes == 2) umma_f16_pair(dTmem, aDesc + step, bDesc + step, kIdesc, acc);
+                        else umma_f8_pair(dTmem, aDesc + step, bDesc + step, kIdesc, acc);
+                    }
+                    umma_commit_pair(&emptyBar[stage]);
+                    if (kb == numK - 1) umma_commit_pair(&accFullBar[buf]);
+                }
+                __syncwarp();
+                if (++stage == kStages2) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp >= 4) {
+        // ---------------- epilogue (both CTAs, 8 warps: lane quarter x column half) ----------------
+        const int quarter = warp & 3;
+        const int colHalf = (warp - 4) >> 2;
+        const float scale = ep.dAlpha != nullptr ? *ep.dAlpha : ep.alpha;
+        const bool hasBias =
+            ep.epilogue == BFB_EPI_BIAS || ep.epilogue == BFB_EPI_BIAS_SILU || ep.epilogue == BFB_EPI_BIAS_RESIDUAL;
+        const bool hasSilu = ep.epilogue == BFB_EPI_BIAS_SILU;
+        const bool hasRes = ep.epilogue == BFB_EPI_BIAS_RESIDUAL || ep.epilogue == BFB_EPI_RESIDUAL;
+        TC* cOut = static_cast<TC*>(ep.c);
+        const TC* res = static_cast<const TC*>(ep.residual);
+        int local = 0;
+        for (int t = clusterId; t < totalTiles; t += numClusters, ++local) {
+            PairTile tc = pairTileCoord(t, tilesM, tilesN, groupN);
+            const int buf = local & 1;
+            const uint32_t accPhase = (local >> 1) & 1u;
+            if (!warp_all(mbar_wait(&accFullBar[buf], accPhase, abortFlag, status, kDevTimeoutAccFull))) break;
+            tc_fence_after();
+            const int row = tc.m * kPairM + static_cast<int>(rank) * 128 + quarter * 32 + lane;
+            const bool rowOk = row < m;
+            const uint32_t tBase = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   static_cast<uint32_t>(buf * kPairN + colHalf * 128);
+#pragma unroll 1
+            for (int chunk = 0; chunk < 4; ++chunk) {
+                const int col0 = tc.n * kPairN + colHalf * 128 + chunk * 32;
+                if (col0 >= n) break;
+                uint32_t raw[32];
+                tmem_ld_32x32(tBase + static_cast<uint32_t>(chunk * 32), raw);
+                tmem_ld_wait();
+                if (rowOk) {
+                    const size_t rowOff = static_cast<size_t>(row) * static_cast<size_t>(n);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const int col = col0 + g * 8;
+                        if (col + 8 > n) break;
+                        float v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(raw[g * 8 + j]) * scale;
+                        if (hasBias) {
+                            const float4 b0 = __ldg(reinterpret_cast<const float4*>(ep.bias + col));
+                            const float4 b1 = __ldg(reinterpret_cast<const float4*>(ep.bias + col + 4));
+                            v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                            v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+                        }
+                        if (hasSilu) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) v[j] = siluFast(v[j]);
+                        }
+                        if constexpr (sizeof(TC) == 4) {
+                            if (hasRes) {
+                                const float4 r0 = *reinterpret_cast<const float4*>(res + rowOff + col);
+                                const float4 r1 = *reinterpret_cast<const float4*>(res + rowOff + col + 4);
+                                v[0] += r0.x; v[1] += r0.y; v[2] += r0.z; v[3] += r0.w;
+                                v[4] += r1.x; v[5] += r1.y; v[6] += r1.z; v[7] += r1.w;
+                            }
+                            if (ep.roundCBf16) {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
+                            }
+                            float4* dst = reinterpret_cast<float4*>(cOut + rowOff + col);
+                            dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+                            dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+                        } else {
+                            if (hasRes) {
+                                const uint4 rr = *reinterpret_cast<const uint4*>(res + rowOff + col);
+                                const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    float2 f = __bfloat1622float2(rh[j]);
+                                    v[2 * j] += f.x;
+                                    v[2 * j + 1] += f.y;
+                                }
+                            }
+                            uint4 packed;
+                            uint32_t* pw = reinterpret_cast<uint32_t*>(&packed);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                                pw[j] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                            *reinterpret_cast<uint4*>(cOut + rowOff + col) = packed;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive_cluster(mapa_cluster(smem_u32(&accEmptyBar[buf]), 0));
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's shared and tensor memory stay alive until the leader's MMAs are done with them
+    if (warp == 2) {
+        if (*abortFlag != 0) {
+            uint64_t t0 = global_timer_ns();
+            while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
+        tc_fence_after();
+        tmem_dealloc(tmemBase, 512);
+    }
+}
+
+template <int kElemBytes, typename TC>
+void launchPair(const GemmArgs& g, cudaStream_t stream) {
+    constexpr int kBlockK = kRowBytes2 / kElemBytes;
+    TensorMapStorage ta, tb;
+    {
+        uint64_t dims[2] = {static_cast<uint64_t>(g.k), static_cast<uint64_t>(g.m)};
+        uint64_t strides[1] = {static_cast<uint64_t>(g.k) * kElemBytes};
+        uint32_t box[2] = {static_cast<uint32_t>(kBlockK), 128u};
+        encodeTensorMap(&ta, g.a, kElemBytes, 2, dims, strides, box);
+    }
+    {
+        uint64_t dims[2] = {static_cast<uint64_t>(g.k), static_cast<uint64_t>(g.n)};
+        uint64_t strides[1] = {static_cast<uint64_t>(g.k) * kElemBytes};
+        uint32_t box[2] = {static_cast<uint32_t>(kBlockK), static_cast<uint32_t>(kHalfN)};
+        encodeTensorMap(&tb, g.b, kElemBytes, 2, dims, strides, box);
+    }
+    const int tilesM = static_cast<int>((g.m + kPairM - 1) / kPairM);
+    const int tilesN = static_cast<int>((g.n + kPairN - 1) / kPairN);
+    const int groups = (tilesN + 15) / 16;
+    const int groupN = (tilesN + groups - 1) / groups;
+    const int clusters = std::max(1, std::min(tilesM * tilesN, smCount() / 2));
+    PairEpilogue ep{g.c, g.bias, g.residual, g.alpha, g.dAlpha, g.epilogue, g.roundCBf16};
+    auto kernel = gemmPairKernel<kElemBytes, TC>;
+    BFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2));
+    ProfileScope prof(kProfGemmTc, stream, 2.0 * static_cast<double>(g.m) * static_cast<double>(g.n) * static_cast<double>(g.k));
+    kernel<<<2 * clusters, kThreads2, kSmemBytes2, stream>>>(*reinterpret_cast<CUtensorMap*>(ta.bytes),
+                                                             *reinterpret_cast<CUtensorMap*>(tb.bytes), ep,
+                                                             static_cast<int>(g.m), static_cast<int>(g.n),
+                                                             static_cast<int>(g.k), tilesM, tilesN, groupN, g.dStatus);
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
+
+}  // namespace
+
+void gemmTensorCorePair(const GemmArgs& g, cudaStream_t stream) {
+    const bool cf32 = g.cDtype == BFB_F32;
+    using bf = __nv_bfloat16;
+    if (g.abDtype == BFB_BF16) {
+        if (cf32) launchPair<2, float>(g, stream); else launchPair<2, bf>(g, stream);
+    } else {
+        if (cf32) launchPair<1, float>(g, stream); else launchPair<1, bf>(g, stream);
+    }
+}
+
+}  // namespace bfb

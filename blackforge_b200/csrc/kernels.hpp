@@ -67,6 +67,8 @@ bool attentionUsesTensorCores(const AttentionArgs& args);
 
 // Tensor-core kernels (gemm_tc.cu / attention_tc.cu); callers have checked eligibility.
 void gemmTensorCore(const GemmArgs& args, cudaStream_t stream);
+// CTA-pair variant (cta_group::2, 256 x 256 tiles); B must be [N,K].
+void gemmTensorCorePair(const GemmArgs& args, cudaStream_t stream);
 void attentionTensorCore(const AttentionArgs& args, cudaStream_t stream);
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda dependency).
