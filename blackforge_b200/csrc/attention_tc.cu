@@ -1,18 +1,20 @@
 // tcgen05 flash attention for sm_100a: head_dim 128, bf16 operands, fp32 online softmax, causal
 // (with a cache offset) or bidirectional. No score matrix is ever written to global memory.
 //
-// One CTA owns one 128-row query tile of one (batch, head). Roles:
-//   warp 4      TMA producer: Q once, then K and V tiles (128 keys x 128 dims, two 64-wide swizzled
+// One CTA owns one 128-row query tile of one (batch, head). Roles (320 threads):
+//   warp 8      TMA producer: Q once, then K and V tiles (128 keys x 128 dims, two 64-wide swizzled
 //               halves each) through a 4-slot shared-memory ring
-//   warp 5      MMA issuer + TMEM owner: S = Q K^T (128x128x16 steps) into one of two S buffers, then
+//   warp 9      MMA issuer + TMEM owner: S = Q K^T (128x128x16 steps) into one of two S buffers, then
 //               O_j = P V into one of two O buffers; S of the next tile is issued before P of the
 //               current one is awaited, so the tensor core works under the softmax
-//   warps 0-3   softmax: one thread per query row reads S from TMEM, keeps the running max and sum in
-//               fp32 (base-2 exponentials with the scale folded in), writes P as bf16 into a
-//               swizzled shared tile for the second MMA, and folds the previous tile's P V product
-//               into a register accumulator with the usual rescaling
+//   warps 0-7   softmax: TWO threads per query row, each owning 64 of the 128 key columns (warp w reads
+//               TMEM lanes 32*(w%4).., columns 64*(w/4)..). A thread reads its half row of S once,
+//               the two halves exchange their maxima through shared memory, probabilities go as bf16
+//               into a swizzled shared tile for the second MMA, and each thread folds its 64 output
+//               columns of the previous tile's P V product into registers (one FMA per element:
+//               acc = acc * alpha_prev + O_prev). Sums stay per half and are combined at the end.
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512). Causal tiles above the diagonal
-// are never visited; only tiles that straddle it are masked. All waits are bounded.
+// are never visited; only tiles that straddle it are masked. All mbarrier waits are bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -36,9 +38,11 @@ constexpr int kQOff = 0;
 constexpr int kKvOff = kTileBytes;
 constexpr int kPOff = kKvOff + kKvSlots * kTileBytes;
 constexpr int kBarOff = kPOff + 2 * kTileBytes;
-constexpr int kAttnSmemBytes = kBarOff + 256 + 1024;
-constexpr int kAttnThreads = 192;
-constexpr int kSoftmaxThreads = 128;
+constexpr int kXchgOff = kBarOff + 256;               // float [2 buffers][2 halves][128 rows]
+constexpr int kAttnSmemBytes = kXchgOff + 2 * 2 * 128 * 4;
+constexpr int kSoftmaxWarps = 8;
+constexpr int kSoftmaxThreads = kSoftmaxWarps * 32;
+constexpr int kAttnThreads = kSoftmaxThreads + 64;
 constexpr uint32_t kIdescQK = make_idesc(kBM, kBN, 1u, 0u);
 constexpr uint32_t kIdescPV = make_idesc(kBM, kD, 1u, 1u);
 
@@ -47,6 +51,9 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+
+// barrier among the softmax warps only (the producer and MMA warps never join it)
+__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory"); }
 
 struct AttnParams {
     __nv_bfloat16* out;
@@ -61,8 +68,7 @@ struct AttnParams {
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_constant__ CUtensorMap tmapK,
                   const __grid_constant__ CUtensorMap tmapV, AttnParams p, int* status) {
-    extern __shared__ uint8_t smemRaw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOff);
     uint64_t* qFull = bars;            // [1]
     uint64_t* kvFull = bars + 1;       // [4]
@@ -74,6 +80,14 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
     uint64_t* oFree = bars + 17;       // [2]
     uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 19);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
+    volatile int* softmaxStop = abortFlag + 1;  // agreed on at the softmax barrier so all eight warps leave together
+    float* xchg = reinterpret_cast<float*>(smem + kXchgOff);
+
+    // The swizzled tiles need a 1024-byte aligned base; refuse to run otherwise (uniform across the CTA).
+    if ((smem_u32(smem) & 1023u) != 0u) {
+        if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, kDevTimeoutOther);
+        return;
+    }
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -103,12 +117,13 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
             mbar_init(&oFree[i], kSoftmaxThreads);
         }
         *abortFlag = 0;
+        *softmaxStop = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmapQ);
         tma_prefetch_desc(&tmapK);
         tma_prefetch_desc(&tmapV);
     }
-    if (warp == 5) {
+    if (warp == 9) {
         tmem_alloc(tmemSlot, 512);
         tmem_relinquish();
     }
@@ -117,7 +132,7 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
     tc_fence_after();
     const uint32_t tmemBase = *tmemSlot;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             mbar_arrive_expect_tx(qFull, kTileBytes);
@@ -125,14 +140,10 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
             tma_load_3d(smem + kQOff + kHalfBytes, &tmapQ, qFull, h * kD + 64, q0, b);
         }
         __syncwarp();
-        bool alive = true;
-        for (int idx = 0; idx < 2 * nKv && alive; ++idx) {
+        for (int idx = 0; idx < 2 * nKv; ++idx) {
             const int slot = idx & (kKvSlots - 1);
             const uint32_t use = static_cast<uint32_t>(idx / kKvSlots);
-            if (!warp_all(mbar_wait(&kvEmpty[slot], (use & 1u) ^ 1u, abortFlag, status, kDevTimeoutStageEmpty))) {
-                alive = false;
-                break;
-            }
+            if (!warp_all(mbar_wait(&kvEmpty[slot], (use & 1u) ^ 1u, abortFlag, status, kDevTimeoutStageEmpty))) break;
             if (lane == 0) {
                 const int j = idx >> 1;
                 const CUtensorMap* map = (idx & 1) ? &tmapV : &tmapK;
@@ -143,7 +154,7 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
             }
             __syncwarp();
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ---------------- MMA issuer ----------------
         const uint32_t qAddr = smem_u32(smem + kQOff);
         const uint32_t kvAddr = smem_u32(smem + kKvOff);
@@ -203,69 +214,79 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
             __syncwarp();
         }
     } else {
-        // ---------------- softmax + accumulation (one thread per query row) ----------------
-        const int r = threadIdx.x;  // 0..127
-        const uint32_t laneBase = static_cast<uint32_t>(warp * 32) << 16;
+        // ---------------- softmax + accumulation: two threads per query row ----------------
+        const int quarter = warp & 3;
+        const int half = warp >> 2;                 // which 64 key columns / 64 output columns
+        const int r = quarter * 32 + lane;          // query row inside the tile
+        const uint32_t laneBase = static_cast<uint32_t>(quarter * 32) << 16;
         const int qPos = p.oldLen + q0 + r;
-        float mRun = -INFINITY, lRun = 0.0f;
-        float oAcc[kD];
+        const int keyLimit = p.causal ? min(qPos, p.totalLen - 1) : p.totalLen - 1;  // last visible key
+        float mRun = -INFINITY, lRun = 0.0f, alphaPrev = 0.0f;
+        float oAcc[64];
 #pragma unroll
-        for (int i = 0; i < kD; ++i) oAcc[i] = 0.0f;
+        for (int i = 0; i < 64; ++i) oAcc[i] = 0.0f;
         bool alive = true;
-        uint8_t* pRowBase = smem + kPOff + r * 128;
+        uint8_t* pRow = smem + kPOff + half * kHalfBytes + r * 128;
         const int sw = r & 7;
 
         for (int j = 0; j < nKv; ++j) {
             const int buf = j & 1;
             const uint32_t use = static_cast<uint32_t>(j >> 1);
-            if (!warp_all(mbar_wait(&sFull[buf], use & 1u, abortFlag, status, kDevTimeoutAccFull))) {
+            // An abandoned wait is published and acted on after the next softmax barrier, where all eight warps
+            // see the same flag: they leave the loop in the same iteration and execute the same barrier count.
+            if (alive && !warp_all(mbar_wait(&sFull[buf], use & 1u, abortFlag, status, kDevTimeoutAccFull))) {
+                alive = false;
+                *softmaxStop = 1;
+            }
+            const uint32_t sAddr = tmemBase + laneBase + static_cast<uint32_t>(buf * kBN + half * 64);
+            const int key0 = j * kBN + half * 64;
+            const bool needMask = (p.causal && j * kBN + kBN - 1 > p.oldLen + q0) || (j * kBN + kBN > p.totalLen);
+
+            // this thread's 64 scores, read once
+            uint32_t s0[32], s1[32];
+            float mx = -INFINITY;
+            if (alive) {
+                tc_fence_after();
+                tmem_ld_32x32(sAddr, s0);
+                tmem_ld_32x32(sAddr + 32u, s1);
+                tmem_ld_wait();
+                tc_fence_before();
+                mbar_arrive(&sFree[buf]);  // S buffer can be refilled while we work from registers
+                if (needMask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (key0 + i > keyLimit) s0[i] = 0xFF800000u;       // -inf
+                        if (key0 + 32 + i > keyLimit) s1[i] = 0xFF800000u;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
+            }
+            float* slotMine = xchg + (buf * 2 + half) * 128 + r;
+            const float* slotOther = xchg + (buf * 2 + (half ^ 1)) * 128 + r;
+            *slotMine = mx;
+            softmax_sync();
+            if (*softmaxStop != 0) {
                 alive = false;
                 break;
             }
-            tc_fence_after();
-            const uint32_t sAddr = tmemBase + laneBase + static_cast<uint32_t>(buf * kBN);
-            const int key0 = j * kBN;
-            const bool needMask = (p.causal && key0 + kBN - 1 > p.oldLen + q0) || (key0 + kBN > p.totalLen);
-            const int keyLimit = p.causal ? min(qPos, p.totalLen - 1) : p.totalLen - 1;  // last visible key
-
-            // pass 1: row maximum
-            float mx = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < kBN / 32; ++c) {
-                uint32_t raw[32];
-                tmem_ld_32x32(sAddr + static_cast<uint32_t>(c * 32), raw);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(raw[i]);
-                    if (needMask && key0 + c * 32 + i > keyLimit) s = -INFINITY;
-                    mx = fmaxf(mx, s);
-                }
-            }
+            mx = fmaxf(mx, *slotOther);
             const float mNew = fmaxf(mRun, mx * p.scaleLog2);
             // a row with no visible key yet keeps everything at zero instead of producing NaN
             const float mUse = (mNew == -INFINITY) ? 0.0f : mNew;
             const float alpha = ex2(mRun - mUse);
 
-            // pass 2: probabilities -> bf16 tile in shared memory, row sum in fp32
             float rowSum = 0.0f;
-            uint8_t* pBuf = pRowBase + buf * kTileBytes;
+            uint8_t* pBuf = pRow + buf * kTileBytes;
 #pragma unroll
-            for (int c = 0; c < kBN / 32; ++c) {
-                uint32_t raw[32];
-                tmem_ld_32x32(sAddr + static_cast<uint32_t>(c * 32), raw);
-                tmem_ld_wait();
+            for (int c = 0; c < 2; ++c) {
+                const uint32_t* sv = c == 0 ? s0 : s1;
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float s0 = __uint_as_float(raw[i]);
-                    float s1 = __uint_as_float(raw[i + 1]);
-                    float p0 = ex2(fmaf(s0, p.scaleLog2, -mUse));
-                    float p1 = ex2(fmaf(s1, p.scaleLog2, -mUse));
-                    if (needMask) {
-                        if (key0 + c * 32 + i > keyLimit) p0 = 0.0f;
-                        if (key0 + c * 32 + i + 1 > keyLimit) p1 = 0.0f;
-                    }
+                    // masked entries hold -inf: ex2(-inf) = 0
+                    const float p0 = ex2(fmaf(__uint_as_float(sv[i]), p.scaleLog2, -mUse));
+                    const float p1 = ex2(fmaf(__uint_as_float(sv[i + 1]), p.scaleLog2, -mUse));
                     rowSum += p0 + p1;
                     __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
                     packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
@@ -273,79 +294,90 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                 // 32 keys = four 16-byte chunks; chunk index inside the 128-byte row is XORed with row % 8
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
-                    const int chunk = c * 4 + g;           // 0..15 over 128 keys
-                    const int half = chunk >> 3;           // which 64-key half
-                    const int cc = (chunk & 7) ^ sw;
-                    *reinterpret_cast<uint4*>(pBuf + half * kHalfBytes + cc * 16) =
+                    const int cc = (c * 4 + g) ^ sw;
+                    *reinterpret_cast<uint4*>(pBuf + cc * 16) =
                         make_uint4(packed[g * 4], packed[g * 4 + 1], packed[g * 4 + 2], packed[g * 4 + 3]);
                 }
             }
-            tc_fence_before();
-            mbar_arrive(&sFree[buf]);
             fence_proxy_async_smem();
             mbar_arrive(&pFull[buf]);
             lRun = lRun * alpha + rowSum;
 
-            // fold the previous tile's P V into the register accumulator, then rescale to the new max
+            // fold the previous tile's P V (relative to the previous maximum) into the accumulator
             if (j > 0) {
                 const int pb = (j - 1) & 1;
                 const uint32_t pUse = static_cast<uint32_t>((j - 1) >> 1);
-                if (!warp_all(mbar_wait(&oFull[pb], pUse & 1u, abortFlag, status, kDevTimeoutAccFull))) {
-                    alive = false;
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t oAddr = tmemBase + laneBase + 256u + static_cast<uint32_t>(pb * kD);
-#pragma unroll
-                for (int c = 0; c < kD / 32; ++c) {
-                    uint32_t raw[32];
-                    tmem_ld_32x32(oAddr + static_cast<uint32_t>(c * 32), raw);
+                if (warp_all(mbar_wait(&oFull[pb], pUse & 1u, abortFlag, status, kDevTimeoutAccFull))) {
+                    tc_fence_after();
+                    const uint32_t oAddr = tmemBase + laneBase + 256u + static_cast<uint32_t>(pb * kD + half * 64);
+                    uint32_t o0[32], o1[32];
+                    tmem_ld_32x32(oAddr, o0);
+                    tmem_ld_32x32(oAddr + 32u, o1);
                     tmem_ld_wait();
+                    tc_fence_before();
+                    mbar_arrive(&oFree[pb]);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) oAcc[c * 32 + i] = (oAcc[c * 32 + i] + __uint_as_float(raw[i])) * alpha;
+                    for (int i = 0; i < 32; ++i) {
+                        oAcc[i] = fmaf(oAcc[i], alphaPrev, __uint_as_float(o0[i]));
+                        oAcc[32 + i] = fmaf(oAcc[32 + i], alphaPrev, __uint_as_float(o1[i]));
+                    }
+                } else {
+                    alive = false;
+                    *softmaxStop = 1;
                 }
-                tc_fence_before();
-                mbar_arrive(&oFree[pb]);
             }
+            alphaPrev = alpha;
             mRun = mNew;
         }
 
-        if (alive) {
+        // last tile's product, normalisation and store. Every softmax warp takes part in the two barriers
+        // below even after an abandoned wait, so none is left behind.
+        bool haveLast = false;
+        uint32_t o0[32], o1[32];
+        if (alive && *softmaxStop == 0) {
             const int pb = (nKv - 1) & 1;
             const uint32_t pUse = static_cast<uint32_t>((nKv - 1) >> 1);
             if (warp_all(mbar_wait(&oFull[pb], pUse & 1u, abortFlag, status, kDevTimeoutAccFull))) {
                 tc_fence_after();
-                const uint32_t oAddr = tmemBase + laneBase + 256u + static_cast<uint32_t>(pb * kD);
-                const float inv = lRun > 0.0f ? 1.0f / lRun : 0.0f;
-                const bool rowOk = q0 + r < p.newLen;
-                __nv_bfloat16* dst =
-                    p.out + (static_cast<int64_t>(b) * p.newLen + q0 + r) * p.ldO + static_cast<int64_t>(h) * kD;
+                const uint32_t oAddr = tmemBase + laneBase + 256u + static_cast<uint32_t>(pb * kD + half * 64);
+                tmem_ld_32x32(oAddr, o0);
+                tmem_ld_32x32(oAddr + 32u, o1);
+                tmem_ld_wait();
+                haveLast = true;
+            }
+        }
+        softmax_sync();  // everyone is done with the maxima of the last tile
+        xchg[half * 128 + r] = lRun;
+        softmax_sync();
+        const float lTotal = lRun + xchg[(half ^ 1) * 128 + r];
+        if (haveLast) {
+            const float inv = lTotal > 0.0f ? 1.0f / lTotal : 0.0f;
+            const bool rowOk = q0 + r < p.newLen;
+            if (rowOk) {
+                __nv_bfloat16* dst = p.out + (static_cast<int64_t>(b) * p.newLen + q0 + r) * p.ldO +
+                                     static_cast<int64_t>(h) * kD + half * 64;
 #pragma unroll
-                for (int c = 0; c < kD / 32; ++c) {
-                    uint32_t raw[32];
-                    tmem_ld_32x32(oAddr + static_cast<uint32_t>(c * 32), raw);
-                    tmem_ld_wait();
-                    if (rowOk) {
+                for (int c = 0; c < 2; ++c) {
+                    const uint32_t* ov = c == 0 ? o0 : o1;
 #pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            uint32_t w[4];
+                    for (int g = 0; g < 4; ++g) {
+                        uint32_t w[4];
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int e = g * 8 + 2 * i;
-                                float a0 = (oAcc[c * 32 + e] + __uint_as_float(raw[e])) * inv;
-                                float a1 = (oAcc[c * 32 + e + 1] + __uint_as_float(raw[e + 1])) * inv;
-                                __nv_bfloat162 hh = __floats2bfloat162_rn(a0, a1);
-                                w[i] = *reinterpret_cast<uint32_t*>(&hh);
-                            }
-                            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                        for (int i = 0; i < 4; ++i) {
+                            const int e = g * 8 + 2 * i;
+                            const float a0 = fmaf(oAcc[c * 32 + e], alphaPrev, __uint_as_float(ov[e])) * inv;
+                            const float a1 = fmaf(oAcc[c * 32 + e + 1], alphaPrev, __uint_as_float(ov[e + 1])) * inv;
+                            __nv_bfloat162 hh = __floats2bfloat162_rn(a0, a1);
+                            w[i] = *reinterpret_cast<uint32_t*>(&hh);
                         }
+                        *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
-                if (rowOk) {
+                if (half == 0) {
                     const int64_t statIdx = (static_cast<int64_t>(b) * p.numHeads + h) * p.newLen + q0 + r;
                     // statistics in natural-log units of the scaled scores, as the reference reports them
                     if (p.mOut != nullptr) p.mOut[statIdx] = mRun * 0.69314718056f;
-                    if (p.lOut != nullptr) p.lOut[statIdx] = lRun;
+                    if (p.lOut != nullptr) p.lOut[statIdx] = lTotal;
                 }
             }
         }
@@ -354,7 +386,7 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
     // ---------------- teardown ----------------
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         if (*abortFlag != 0) {
             uint64_t t0 = global_timer_ns();
             while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -378,6 +410,7 @@ bool attentionUsesTensorCores(const AttentionArgs& a) {
     if (a.ldQ % 8 || a.ldK % 8 || a.ldV % 8 || a.ldO % 8) return false;
     auto aligned16 = [](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
     if (!aligned16(a.q) || !aligned16(a.k) || !aligned16(a.v) || !aligned16(a.out)) return false;
+    if (!(a.scale > 0.0f)) return false;  // masked scores are -inf before scaling
     if (a.batch * a.numHeads > 0x3FFFFF || a.totalLen > 0x3FFFFFFF || a.newLen > 0x3FFFFFFF) return false;
     return true;
 }
