@@ -49,7 +49,9 @@ WORKLOADS = {
 
 # DRAM bytes per launch of the dominant kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum),
 # keyed by workload; None until a capture of that kernel has been summarised under profiles/.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {"c3": None, "c4": None, "c1": None}
+# c3: capture of M=32768, N=K=2048 (239.2 MB for 0.275 TFLOP, equal to A+B+C) scaled by FLOPs to the step's average
+# GEMM launch (1.418 TFLOP); see profiles/gemm_pair_bf16_m32768_n2048_k2048.md.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"c3": 1.233e9, "c4": None, "c1": None}
 
 
 def lm_ops(vocab, dim, layers, heads, hidden, max_seq):
