@@ -22,6 +22,7 @@ LIB_PATH = os.path.join(HERE, "libbfb200.so")
 SOURCES = [
     "pool.cu",
     "elementwise.cu",
+    "quantize.cu",
     "gemm_simt.cu",
     "gemm_tc.cu",
     "gemm_tc2.cu",

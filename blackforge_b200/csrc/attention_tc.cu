@@ -63,6 +63,7 @@ struct AttnParams {
     int64_t ldO;
     float scaleLog2;
     int oldLen, causal, numQTiles;
+    int headsPerGroup;  // (batch, head) pairs whose K + V are kept in L2 together
 };
 
 __global__ void __launch_bounds__(kAttnThreads, 1)
@@ -92,10 +93,22 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    // heaviest query tiles (most key tiles) are scheduled first
+    // Launch order: (batch, head) pairs are taken in groups whose K and V fit in L2 together; inside a group the
+    // heaviest query tiles (most key tiles) go first. All query tiles of a head therefore run close in time and
+    // K/V come from DRAM once.
     const int bhCount = p.batch * p.numHeads;
-    const int qt = p.numQTiles - 1 - static_cast<int>(blockIdx.x) / bhCount;
-    const int bh = static_cast<int>(blockIdx.x) % bhCount;
+    const int perGroup = p.headsPerGroup * p.numQTiles;
+    const int fullGroups = bhCount / p.headsPerGroup;
+    int group = static_cast<int>(blockIdx.x) / perGroup;
+    int rem = static_cast<int>(blockIdx.x) - group * perGroup;
+    int width = p.headsPerGroup;
+    if (group >= fullGroups) {
+        group = fullGroups;
+        rem = static_cast<int>(blockIdx.x) - fullGroups * perGroup;
+        width = bhCount - fullGroups * p.headsPerGroup;
+    }
+    const int qt = p.numQTiles - 1 - rem / width;
+    const int bh = group * p.headsPerGroup + rem % width;
     const int b = bh / p.numHeads;
     const int h = bh % p.numHeads;
     const int q0 = qt * kBM;
@@ -434,6 +447,9 @@ void attentionTensorCore(const AttentionArgs& a, cudaStream_t stream) {
     p.oldLen = static_cast<int>(a.oldLen);
     p.causal = a.causal;
     p.numQTiles = static_cast<int>((a.newLen + kBM - 1) / kBM);
+    // K + V of one (batch, head): 2 * total_len * 128 * 2 bytes; keep about 64 MB of them live in the 126 MB L2
+    const int64_t kvBytes = 2 * a.totalLen * kD * 2;
+    p.headsPerGroup = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(a.batch * a.numHeads, (64ll << 20) / kvBytes)));
     const int64_t grid = static_cast<int64_t>(p.numQTiles) * a.batch * a.numHeads;
     require(grid <= 0x7FFFFFFF, "attention: too many query tiles for one launch");
     BFB_CUDA(cudaFuncSetAttribute(attentionTcKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmemBytes));

@@ -178,6 +178,24 @@ bfb_status bfb_fp8_scale_from_amax(const float* d_amax, float* d_scales, void* s
     return guarded([&] { bfb::fp8ScaleFromAmax(d_amax, d_scales, asStream(stream)); });
 }
 
+bfb_status bfb_quantize_e4m3(const void* d_in, int32_t in_dtype, int64_t n, void* d_out, float* d_scales,
+                             const float* d_weight_inverse, void* stream) {
+    return guarded([&] {
+        require(n >= 0, "quantize_e4m3: negative size");
+        requireDevice();
+        const size_t bytes = static_cast<size_t>(bfb::quantizeScratchFloats(n)) * sizeof(float);
+        float* scratch = static_cast<float*>(bfb::poolAcquire(bytes));
+        try {
+            bfb::quantizeE4m3(d_in, in_dtype, n, d_out, d_scales, d_weight_inverse, scratch, asStream(stream));
+        } catch (...) {
+            bfb::poolRelease(scratch, bytes);
+            throw;
+        }
+        // work on `stream` is ordered before any later use of the buffer on the same stream
+        bfb::poolRelease(scratch, bytes);
+    });
+}
+
 bfb_status bfb_weight_prepare(const float* d_w, void* d_out, int32_t out_dtype, int64_t k, int64_t n, float scale,
                               const float* d_scale, void* stream) {
     return guarded([&] { bfb::weightPrepare(d_w, d_out, out_dtype, k, n, scale, d_scale, asStream(stream)); });

@@ -281,6 +281,9 @@ rmsnormWarpKernel(const TIn* __restrict__ x, TOut* __restrict__ out, int64_t row
         }
         const float total = warpSum(ss);
         const float rms = sqrtf(total / static_cast<float>(dim) + eps);
+        // bf16 results are rounded to 8 bits anyway: one reciprocal per row instead of a division per element;
+        // fp32 results keep the reference's x / rms
+        const float inv = 1.0f / rms;
         TOut* dst = out + row * dim;
 #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
@@ -288,7 +291,7 @@ rmsnormWarpKernel(const TIn* __restrict__ x, TOut* __restrict__ out, int64_t row
             if (i < nv) {
                 float o[kN];
 #pragma unroll
-                for (int e = 0; e < kN; ++e) o[e] = vals[j][e] / rms;
+                for (int e = 0; e < kN; ++e) o[e] = sizeof(TOut) == 2 ? vals[j][e] * inv : vals[j][e] / rms;
                 storeRun<TOut, kN>(dst + i * kN, o);
             }
         }

@@ -462,12 +462,13 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
             *dAlpha = nullptr;
             return act16;
         }
-        float* st = static_cast<float*>(fp8Stats.ptr) + 4 * (fp8Slot++);
-        bfb::amax(act16, BFB_BF16, static_cast<int64_t>(count), st, stream);
-        bfb::fp8ActScale(st, st + 1, wScales + 1, stream);  // st[1]=scale st[2]=inverse st[3]=alpha
+        float* st = static_cast<float*>(fp8Stats.ptr) + 4 * (fp8Slot++);  // [0]=scale [1]=inverse [2]=alpha
         void* a8 = buf(name, count);
-        bfb::castScaled(act16, BFB_BF16, a8, BFB_FP8_E4M3, static_cast<int64_t>(count), 1.0f, st + 1, stream);
-        *dAlpha = st + 3;
+        const int64_t n = static_cast<int64_t>(count);
+        float* scratch = static_cast<float*>(
+            buf("partial_" + name, static_cast<std::size_t>(bfb::quantizeScratchFloats(n)) * sizeof(float)));
+        bfb::quantizeE4m3(act16, BFB_BF16, n, a8, st, wScales + 1, scratch, stream);
+        *dAlpha = st + 2;
         return a8;
     };
     auto runGemm = [&](const void* a, const void* w, void* c, std::size_t m, std::size_t n, std::size_t k, int cDtype,

@@ -26,6 +26,11 @@ void fp8ScaleFromAmax(const float* dAmax, float* dScales, cudaStream_t stream);
 void fp8ActScale(const float* dAmax, float* out, const float* dWeightInverse, cudaStream_t stream);
 void weightPrepare(const float* w, void* out, int outDtype, int64_t k, int64_t n, float scale, const float* dScale,
                    cudaStream_t stream);
+// Per-tensor e4m3 quantisation: dScales[0] = 448 / max|in|, [1] = its inverse, [2] = inverse * *dWeightInverse
+// (1 when null); out = e4m3(in * dScales[0]). `scratch` holds quantizeScratchFloats(n) floats of partial maxima.
+int64_t quantizeScratchFloats(int64_t n);
+void quantizeE4m3(const void* in, int inDtype, int64_t n, void* out, float* dScales, const float* dWeightInverse,
+                  float* scratch, cudaStream_t stream);
 // In-place rounding of an f32 buffer to bf16 precision (simulated `storage bf16` for the fp32 path).
 void roundBf16InPlace(float* x, int64_t n, cudaStream_t stream);
 

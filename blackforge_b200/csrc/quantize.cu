@@ -1,0 +1,128 @@
+// Per-tensor e4m3 quantisation of an activation: scale = 448 / max|x|, out = e4m3(x * scale).
+// Three launches: (1) every block reduces its own 8192-element chunk to one partial maximum in a scratch
+// array, (2) one block folds the partial maxima into {scale, 1/scale, 1/scale * weight inverse},
+// (3) the conversion. No atomics, so the result does not depend on block scheduling.
+#include <cuda_bf16.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "kernels.hpp"
+#include "pool.hpp"
+
+namespace bfb {
+
+namespace {
+
+constexpr int kChunkThreads = 256;
+constexpr int kChunkElems = 8192;  // elements reduced by one block
+
+template <typename T>
+__device__ __forceinline__ float absMax16(const T* p);
+template <>
+__device__ __forceinline__ float absMax16<float>(const float* p) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+}
+template <>
+__device__ __forceinline__ float absMax16<__nv_bfloat16>(const __nv_bfloat16* p) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+    return m;
+}
+template <typename T>
+__device__ __forceinline__ float absOne(const T* p);
+template <>
+__device__ __forceinline__ float absOne<float>(const float* p) { return fabsf(*p); }
+template <>
+__device__ __forceinline__ float absOne<__nv_bfloat16>(const __nv_bfloat16* p) { return fabsf(__bfloat162float(*p)); }
+
+template <typename T>
+__global__ void __launch_bounds__(kChunkThreads)
+partialAmaxKernel(const T* __restrict__ in, int64_t n, float* __restrict__ partial, int vectorised) {
+    __shared__ float warpMax[kChunkThreads / 32];
+    constexpr int kPerVec = 16 / static_cast<int>(sizeof(T));
+    const int64_t begin = static_cast<int64_t>(blockIdx.x) * kChunkElems;
+    const int64_t end = min(begin + static_cast<int64_t>(kChunkElems), n);
+    float m = 0.0f;
+    if (vectorised) {
+        for (int64_t i = begin + static_cast<int64_t>(threadIdx.x) * kPerVec; i + kPerVec <= end;
+             i += static_cast<int64_t>(kChunkThreads) * kPerVec) {
+            m = fmaxf(m, absMax16<T>(in + i));
+        }
+        // tail of the last chunk that is not a whole vector
+        const int64_t tail = begin + ((end - begin) / kPerVec) * kPerVec;
+        for (int64_t i = tail + threadIdx.x; i < end; i += kChunkThreads) m = fmaxf(m, absOne<T>(in + i));
+    } else {
+        for (int64_t i = begin + threadIdx.x; i < end; i += kChunkThreads) m = fmaxf(m, absOne<T>(in + i));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if ((threadIdx.x & 31) == 0) warpMax[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = warpMax[0];
+#pragma unroll
+        for (int w = 1; w < kChunkThreads / 32; ++w) t = fmaxf(t, warpMax[w]);
+        partial[blockIdx.x] = t;
+    }
+}
+
+__global__ void __launch_bounds__(1024)
+finalizeScaleKernel(const float* __restrict__ partial, int64_t count, float* __restrict__ scales,
+                    const float* __restrict__ weightInverse) {
+    __shared__ float warpMax[32];
+    float m = 0.0f;
+    for (int64_t i = threadIdx.x; i < count; i += blockDim.x) m = fmaxf(m, partial[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if ((threadIdx.x & 31) == 0) warpMax[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) t = fmaxf(t, warpMax[w]);
+        const float s = t > 0.0f ? 448.0f / t : 1.0f;
+        scales[0] = s;
+        scales[1] = 1.0f / s;
+        scales[2] = (1.0f / s) * (weightInverse != nullptr ? *weightInverse : 1.0f);
+    }
+}
+
+}  // namespace
+
+int64_t quantizeScratchFloats(int64_t n) { return std::max<int64_t>(1, (n + kChunkElems - 1) / kChunkElems); }
+
+void quantizeE4m3(const void* in, int inDtype, int64_t n, void* out, float* dScales, const float* dWeightInverse,
+                  float* scratch, cudaStream_t stream) {
+    require(n >= 0, "quantize_e4m3: negative size");
+    require(inDtype == BFB_F32 || inDtype == BFB_BF16, "quantize_e4m3: input must be f32 or bf16");
+    require(dScales != nullptr, "quantize_e4m3: null scale pointer");
+    require(scratch != nullptr, "quantize_e4m3: null scratch pointer");
+    if (n > 0) require(in != nullptr && out != nullptr, "quantize_e4m3: null pointer");
+    const int64_t blocks = quantizeScratchFloats(n);
+    require(blocks <= 0x7FFFFFFF, "quantize_e4m3: tensor too large for one launch");
+    const int vectorised = reinterpret_cast<uintptr_t>(in) % 16 == 0 ? 1 : 0;
+    if (n > 0) {
+        if (inDtype == BFB_F32) {
+            partialAmaxKernel<float><<<static_cast<unsigned>(blocks), kChunkThreads, 0, stream>>>(
+                static_cast<const float*>(in), n, scratch, vectorised);
+        } else {
+            partialAmaxKernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), kChunkThreads, 0, stream>>>(
+                static_cast<const __nv_bfloat16*>(in), n, scratch, vectorised);
+        }
+        BFB_LAUNCH_CHECK();
+        noteLaunch();
+    }
+    finalizeScaleKernel<<<1, 1024, 0, stream>>>(scratch, n > 0 ? blocks : 0, dScales, dWeightInverse);
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+    if (n > 0) castScaled(in, inDtype, out, BFB_FP8_E4M3, n, 1.0f, dScales, stream);
+}
+
+}  // namespace bfb

@@ -166,6 +166,13 @@ bfb_status bfb_cast(const void* d_in, int32_t in_dtype, void* d_out, int32_t out
 bfb_status bfb_amax(const void* d_in, int32_t in_dtype, int64_t n, float* d_amax, void* stream);
 /* d_scales[0] = 448 / amax (1 when amax == 0), d_scales[1] = 1 / d_scales[0]; reads *d_amax on device. */
 bfb_status bfb_fp8_scale_from_amax(const float* d_amax, float* d_scales, void* stream);
+/* Per-tensor e4m3 quantisation of an activation in one call: d_scales[0] = 448 / max|in| (1 for an all-zero
+ * tensor), d_scales[1] = 1 / d_scales[0], d_scales[2] = d_scales[1] * *d_weight_inverse (1 when NULL: the alpha
+ * of the following GEMM); d_out = e4m3(in * d_scales[0]), saturating. in_dtype BFB_F32 or BFB_BF16. The partial
+ * maxima (one float per 8192 elements) go through scratch memory taken from the device pool for the duration
+ * of the call. Deterministic (no atomics). No counterpart in the reference (fp8 is declared only). */
+bfb_status bfb_quantize_e4m3(const void* d_in, int32_t in_dtype, int64_t n, void* d_out, float* d_scales,
+                             const float* d_weight_inverse, void* stream);
 /* Weight preparation, done once per weight: W[K,N] f32 (reference layout) -> W^T[N,K] in out_dtype,
  * multiplied by scale (*d_scale when non-NULL). Takes over the per-call weight cast of
  * matmulBf16 (ops_tensorcore.cu:316-317) and the cached-weight variant (:98-131). */

@@ -289,3 +289,28 @@ def test_pool_reuses_exact_sizes(gpu):
     assert cached.value >= 12345
     gpu.check(lib.bfb_pool_acquire(0, C.byref(p1)))
     assert p1.value is None
+
+
+@pytest.mark.parametrize("n,dtype_name", [(8192 * 3 + 77, "f32"), (8192 * 5, "bf16"), (13, "bf16"), (1 << 20, "bf16")])
+def test_quantize_e4m3_one_call(gpu, n, dtype_name):
+    rng = np.random.default_rng(n)
+    x = (rng.standard_normal(n) * 3).astype(np.float32)
+    x[n // 2] = -37.5                                   # the maximum sits in the middle of a chunk
+    dtype = gpu.F32 if dtype_name == "f32" else gpu.BF16
+    if dtype == gpu.BF16:
+        x = O.round_bf16(x)
+    src = gpu.upload(x, dtype)
+    out = gpu.DeviceBuffer(n)
+    scales = gpu.DeviceBuffer.zeros(12)
+    winv = gpu.DeviceBuffer.from_numpy(np.array([0.25], np.float32))
+    gpu.check(gpu.lib().bfb_quantize_e4m3(src.ptr, dtype, n, out.ptr, scales.ptr, winv.ptr, None))
+    s = scales.to_numpy(np.float32, (3,))
+    want_scale = np.float32(448.0) / np.float32(37.5)
+    assert s[0] == want_scale and s[1] == np.float32(1.0) / want_scale and s[2] == s[1] * np.float32(0.25)
+    assert np.array_equal(gpu.download(out, gpu.FP8_E4M3, (n,)), O.e4m3_round_hw(x * want_scale))
+    # all-zero tensor: scale 1, zeros out; empty tensor: scales only
+    zero = gpu.DeviceBuffer.zeros(64 * 4)
+    gpu.check(gpu.lib().bfb_quantize_e4m3(zero.ptr, gpu.F32, 64, out.ptr, scales.ptr, None, None))
+    assert scales.to_numpy(np.float32, (3,)).tolist() == [1.0, 1.0, 1.0]
+    assert gpu.lib().bfb_quantize_e4m3(None, gpu.F32, 0, None, scales.ptr, None, None) == gpu.OK
+    assert gpu.lib().bfb_quantize_e4m3(src.ptr, gpu.FP8_E4M3, n, out.ptr, scales.ptr, None, None) == gpu.INVALID_ARGUMENT
