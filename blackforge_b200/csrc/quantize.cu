@@ -5,6 +5,9 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <mutex>
+#include <string>
+#include <unordered_map>
 
 #include "common.cuh"
 #include "kernels.hpp"
@@ -126,3 +129,47 @@ void quantizeE4m3(const void* in, int inDtype, int64_t n, void* out, float* dSca
 }
 
 }  // namespace bfb
+
+// ---- allocation-free variant ---------------------------------------------------------------------------
+// Some hosts cannot let this library take device memory at call time: an engine that handed every byte of
+// the GPU to its own arena at start-up, or a serving loop that must not reach cudaMalloc because it can
+// stall the whole device. For them the partial maxima live in this fixed array instead of the pool. Every
+// GPU on which the library is used keeps these 256 KiB until the process exits.
+namespace bfb {
+namespace {
+
+constexpr int64_t kStaticScratchFloats = 65536;  // one partial maximum per 8192 elements -> 536 870 912 elements
+__device__ __align__(256) float gQuantStaticScratch[kStaticScratchFloats];
+
+// The array's name is only a host-side handle; kernels need its device address, which differs per device.
+float* staticScratchForCurrentDevice() {
+    static std::mutex mu;
+    static std::unordered_map<int, float*> perDevice;
+    int dev = 0;
+    BFB_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = perDevice.find(dev);
+    if (it != perDevice.end()) return it->second;
+    float* ptr = nullptr;
+    BFB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), gQuantStaticScratch));
+    perDevice[dev] = ptr;
+    return ptr;
+}
+
+}  // namespace
+}  // namespace bfb
+
+extern "C" bfb_status bfb_quantize_e4m3_static(const void* d_in, int32_t in_dtype, int64_t n, void* d_out,
+                                               float* d_scales, const float* d_weight_inverse, void* stream) {
+    return bfb::guarded([&] {
+        bfb::require(n >= 0, "quantize_e4m3_static: negative size");
+        if (bfb::quantizeScratchFloats(n) > bfb::kStaticScratchFloats) {
+            bfb::fail(BFB_INVALID_ARGUMENT,
+                      "quantize_e4m3_static: at most " + std::to_string(bfb::kStaticScratchFloats * 8192) +
+                          " elements fit the built-in scratch array; use bfb_quantize_e4m3 for larger tensors");
+        }
+        float* scratch = bfb::staticScratchForCurrentDevice();
+        // every block writes its own slot before the fold reads it, so nothing has to be cleared between calls
+        bfb::quantizeE4m3(d_in, in_dtype, n, d_out, d_scales, d_weight_inverse, scratch, bfb::asStream(stream));
+    });
+}

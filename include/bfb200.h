@@ -173,6 +173,21 @@ bfb_status bfb_fp8_scale_from_amax(const float* d_amax, float* d_scales, void* s
  * of the call. Deterministic (no atomics). No counterpart in the reference (fp8 is declared only). */
 bfb_status bfb_quantize_e4m3(const void* d_in, int32_t in_dtype, int64_t n, void* d_out, float* d_scales,
                              const float* d_weight_inverse, void* stream);
+/* Same operation and results as bfb_quantize_e4m3, for callers that must not allocate device memory while
+ * they run: a host engine that gave the whole GPU to its own arena at start-up, or a latency-critical
+ * serving loop where a trip into the device allocator can stall every stream. This entry point has no
+ * counterpart in the reference. It calls no allocator at all (not cudaMalloc, not the device pool): the partial
+ * maxima go to a fixed 256 KiB array inside the library, which every GPU that uses the library holds until the
+ * process exits. Limits and rules:
+ *  - n <= 536 870 912 elements (65 536 partial maxima of 8192 elements each); larger n is refused with
+ *    BFB_INVALID_ARGUMENT and nothing is launched.
+ *  - The first call on each device looks up the array's device address (once, with that device current);
+ *    make that first call before starting any stream capture.
+ *  - All calls on a device share the one array. It keeps the previous call's values, which is harmless because
+ *    each call overwrites every slot it later reads; but two calls whose kernels overlap on the GPU (different
+ *    streams) race on it. Keep calls to this entry point on one stream, or order them yourself. */
+bfb_status bfb_quantize_e4m3_static(const void* d_in, int32_t in_dtype, int64_t n, void* d_out, float* d_scales,
+                                    const float* d_weight_inverse, void* stream);
 /* Weight preparation, done once per weight: W[K,N] f32 (reference layout) -> W^T[N,K] in out_dtype,
  * multiplied by scale (*d_scale when non-NULL). Takes over the per-call weight cast of
  * matmulBf16 (ops_tensorcore.cu:316-317) and the cached-weight variant (:98-131). */
