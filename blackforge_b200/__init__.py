@@ -345,3 +345,20 @@ def synthetic_input(ops: Sequence[dict], input_shape: Sequence[int], batch: int,
     out = np.empty(dims, dtype=np.float32)
     check(lib().bfb_synthetic_input(descs, len(ops), shape, len(input_shape), batch, seed, out.ctypes.data))
     return out
+
+
+# ---- tensor-parallel communicator ---------------------------------------------------------------------------
+
+def tp_unique_id() -> bytes:
+    buf = C.create_string_buffer(128)
+    check(lib().bfb_tp_unique_id(buf))
+    return buf.raw
+
+
+def tp_init(unique_id: bytes, rank: int, world: int):
+    assert len(unique_id) == 128
+    check(lib().bfb_tp_init(C.create_string_buffer(unique_id, 128), rank, world))
+
+
+def tp_destroy():
+    check(lib().bfb_tp_destroy())

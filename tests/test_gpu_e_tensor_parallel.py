@@ -1,0 +1,76 @@
+"""Tensor parallelism over two GPUs (heads, feed-forward columns and logits columns sharded, NCCL all-reduce
+after the out-projection and the feed-forward down-projection) against the one-GPU result. Runs as two child
+processes, one per GPU; skipped on a one-GPU box."""
+import ctypes as C
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from oracle import bf_oracle as O
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CFG = dict(vocab=512, dim=512, layers=2, heads=4, hidden=1024, max_seq=160)
+
+WORKER = r"""
+import os, sys, time
+import numpy as np
+sys.path.insert(0, os.environ["BFB_ROOT"])
+import blackforge_b200 as bfb
+from oracle import bf_oracle as O
+rank, world, work = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+cfg = eval(sys.argv[4])
+bfb.check(bfb.lib().bfb_set_device(rank))
+id_path = os.path.join(work, "nccl_id")
+if rank == 0:
+    ident = bfb.tp_unique_id()
+    with open(id_path + ".tmp", "wb") as f:
+        f.write(ident)
+    os.replace(id_path + ".tmp", id_path)
+else:
+    deadline = time.time() + 120
+    while not os.path.exists(id_path):
+        if time.time() > deadline:
+            raise SystemExit("no communicator id from rank 0")
+        time.sleep(0.05)
+    ident = open(id_path, "rb").read()
+bfb.tp_init(ident, rank, world)
+ops = O.lm_ops(**cfg)
+params = O.synth_params(ops, None, seed=21, sigma=0.05, bias_sigma=0.05)
+ids = O.synth_token_ids(2, 160, cfg["vocab"], seed=22)
+m = bfb.Model(ops, precision={"storage": "fp32", "compute": "bf16"}, random_init=False)
+m.set_tensor_parallel(rank, world)
+m.set_params(params)
+out = m.forward_host(ids)
+np.save(os.path.join(work, f"logits_{rank}.npy"), out)
+bfb.tp_destroy()
+print("rank", rank, "ok", out.shape)
+"""
+
+
+def test_two_gpu_tensor_parallel_matches_single_gpu(gpu, tmp_path):
+    n = C.c_int32(0)
+    gpu.check(gpu.lib().bfb_device_count(C.byref(n)))
+    if n.value < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "tp_worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, BFB_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), "2", str(tmp_path), repr(CFG)], env=env,
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    parts = [np.load(tmp_path / f"logits_{r}.npy") for r in range(2)]
+    assert parts[0].shape == (2, 160, CFG["vocab"] // 2)
+    sharded = np.concatenate(parts, axis=-1)
+    ops = O.lm_ops(**CFG)
+    params = O.synth_params(ops, None, seed=21, sigma=0.05, bias_sigma=0.05)
+    ids = O.synth_token_ids(2, 160, CFG["vocab"], seed=22)
+    single = gpu.Model(ops, precision={"storage": "fp32", "compute": "bf16"}, random_init=False)
+    single.set_params(params)
+    want = single.forward_host(ids)
+    # same arithmetic, different summation order across the two partial products
+    assert np.max(np.abs(sharded - want)) / np.max(np.abs(want)) <= 5e-3
