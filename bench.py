@@ -396,6 +396,9 @@ def main():
                "api": "bfb_model_forward_host (fromHost -> Model::forward -> toHost), pinned host buffers"}
         del h_out
 
+    if world > 1:
+        launch.barrier()
+        torch.distributed.destroy_process_group()
     if rank != 0:
         return
 

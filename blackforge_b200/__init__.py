@@ -95,6 +95,8 @@ SIGNATURES = {
     "bfb_model_param_shape": (None, [_P, _I32, C.POINTER(_I64)]),
     "bfb_model_param_set": (_I32, [_P, _I32, _P]),
     "bfb_model_param_get": (_I32, [_P, _I32, _P]),
+    "bfb_model_param_fill_normal": (_I32, [_P, _I32, C.c_uint64, _F]),
+    "bfb_model_release_master_weights": (_I32, [_P]),
     "bfb_model_load_checkpoint": (_I32, [_P, C.c_char_p]),
     "bfb_model_save_checkpoint": (_I32, [_P, C.c_char_p]),
     "bfb_model_forward": (_I32, [_P, _P, C.POINTER(_I64), _I32, _I32, C.POINTER(_P), C.POINTER(_I64),
@@ -298,6 +300,12 @@ class Model:
         out = np.empty(self.param_shape(index), dtype=np.float32)
         check(lib().bfb_model_param_get(self._h, index, out.ctypes.data))
         return out
+
+    def fill_param_normal(self, index: int, seed: int, sigma: float):
+        check(lib().bfb_model_param_fill_normal(self._h, index, seed, sigma))
+
+    def release_master_weights(self):
+        check(lib().bfb_model_release_master_weights(self._h))
 
     def set_params(self, params: Dict[str, np.ndarray]):
         for i, name in enumerate(self.param_names()):

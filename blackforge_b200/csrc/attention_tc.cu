@@ -272,8 +272,16 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                         if (key0 + 32 + i > keyLimit) s1[i] = 0xFF800000u;
                     }
                 }
+                // four independent chains instead of one 32-deep dependency
+                float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
+                for (int i = 0; i < 32; i += 4) {
+                    m0 = fmaxf(m0, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
+                    m1 = fmaxf(m1, fmaxf(__uint_as_float(s0[i + 1]), __uint_as_float(s1[i + 1])));
+                    m2 = fmaxf(m2, fmaxf(__uint_as_float(s0[i + 2]), __uint_as_float(s1[i + 2])));
+                    m3 = fmaxf(m3, fmaxf(__uint_as_float(s0[i + 3]), __uint_as_float(s1[i + 3])));
+                }
+                mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
             }
             float* slotMine = xchg + (buf * 2 + half) * 128 + r;
             const float* slotOther = xchg + (buf * 2 + (half ^ 1)) * 128 + r;
@@ -289,7 +297,10 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
             const float mUse = (mNew == -INFINITY) ? 0.0f : mNew;
             const float alpha = ex2(mRun - mUse);
 
-            float rowSum = 0.0f;
+            // packed fp32 pairs: one FMA / ADD instruction serves two scores
+            const uint64_t scale2 = pack_f32x2(p.scaleLog2, p.scaleLog2);
+            const uint64_t negMax2 = pack_f32x2(-mUse, -mUse);
+            uint64_t sumA = pack_f32x2(0.0f, 0.0f), sumB = sumA;
             uint8_t* pBuf = pRow + buf * kTileBytes;
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
@@ -298,9 +309,14 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     // masked entries hold -inf: ex2(-inf) = 0
-                    const float p0 = ex2(fmaf(__uint_as_float(sv[i]), p.scaleLog2, -mUse));
-                    const float p1 = ex2(fmaf(__uint_as_float(sv[i + 1]), p.scaleLog2, -mUse));
-                    rowSum += p0 + p1;
+                    const uint64_t arg = fma_f32x2(pack_f32x2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])),
+                                                   scale2, negMax2);
+                    float a0, a1;
+                    unpack_f32x2(arg, a0, a1);
+                    const float p0 = ex2(a0);
+                    const float p1 = ex2(a1);
+                    if ((i & 2) == 0) sumA = add_f32x2(sumA, pack_f32x2(p0, p1));
+                    else sumB = add_f32x2(sumB, pack_f32x2(p0, p1));
                     __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
                     packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
                 }
@@ -314,7 +330,9 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
             }
             fence_proxy_async_smem();
             mbar_arrive(&pFull[buf]);
-            lRun = lRun * alpha + rowSum;
+            float sumLo, sumHi;
+            unpack_f32x2(add_f32x2(sumA, sumB), sumLo, sumHi);
+            lRun = lRun * alpha + (sumLo + sumHi);
 
             // fold the previous tile's P V (relative to the previous maximum) into the accumulator
             if (j > 0) {
@@ -329,10 +347,15 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                     tmem_ld_wait();
                     tc_fence_before();
                     mbar_arrive(&oFree[pb]);
+                    const uint64_t alpha2 = pack_f32x2(alphaPrev, alphaPrev);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        oAcc[i] = fmaf(oAcc[i], alphaPrev, __uint_as_float(o0[i]));
-                        oAcc[32 + i] = fmaf(oAcc[32 + i], alphaPrev, __uint_as_float(o1[i]));
+                    for (int i = 0; i < 32; i += 2) {
+                        unpack_f32x2(fma_f32x2(pack_f32x2(oAcc[i], oAcc[i + 1]), alpha2,
+                                               pack_f32x2(__uint_as_float(o0[i]), __uint_as_float(o0[i + 1]))),
+                                     oAcc[i], oAcc[i + 1]);
+                        unpack_f32x2(fma_f32x2(pack_f32x2(oAcc[32 + i], oAcc[33 + i]), alpha2,
+                                               pack_f32x2(__uint_as_float(o1[i]), __uint_as_float(o1[i + 1]))),
+                                     oAcc[32 + i], oAcc[33 + i]);
                     }
                 } else {
                     alive = false;

@@ -1,6 +1,8 @@
 // extern "C" surface declared in include/bfb200.h: argument checks, exception -> status mapping,
 // and nothing else. All work happens in the kernel layer (kernels.hpp) and the host layer (host/).
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -337,6 +339,23 @@ bfb_status bfb_model_param_get(bfb_model* model, int32_t index, float* h_values)
     });
 }
 
+bfb_status bfb_model_param_fill_normal(bfb_model* model, int32_t index, uint64_t seed, float sigma) {
+    return guarded([&] {
+        require(model != nullptr, "model: null handle");
+        require(index >= 0, "model: negative parameter index");
+        requireDevice();
+        model->model->fillParameterNormal(static_cast<std::size_t>(index), seed, sigma);
+    });
+}
+
+bfb_status bfb_model_release_master_weights(bfb_model* model) {
+    return guarded([&] {
+        require(model != nullptr, "model: null handle");
+        requireDevice();
+        model->model->releaseMasterWeights();
+    });
+}
+
 bfb_status bfb_model_load_checkpoint(bfb_model* model, const char* path) {
     return guarded([&] {
         require(model != nullptr && path != nullptr, "model: null argument");
@@ -377,24 +396,84 @@ bfb_status bfb_model_forward(bfb_model* model, const float* d_input, const int64
     });
 }
 
+namespace {
+// Two non-blocking streams per device for the host-buffer path: compute and device-to-host copies.
+struct HostPathStreams {
+    cudaStream_t compute = nullptr;
+    cudaStream_t copy = nullptr;
+};
+HostPathStreams& hostPathStreams() {
+    static std::mutex mu;
+    static std::map<int, HostPathStreams> perDevice;
+    int dev = 0;
+    BFB_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    HostPathStreams& s = perDevice[dev];
+    if (s.compute == nullptr) {
+        BFB_CUDA(cudaStreamCreateWithFlags(&s.compute, cudaStreamNonBlocking));
+        BFB_CUDA(cudaStreamCreateWithFlags(&s.copy, cudaStreamNonBlocking));
+    }
+    return s;
+}
+}  // namespace
+
+// Sequences are independent, so a batch is run in slices: while slice i+1 computes, the logits of slice i
+// travel to the host on a second stream. With pinned host memory the copy (the larger cost for wide
+// vocabularies) hides the compute; with pageable memory the result is the same, only without the overlap.
 bfb_status bfb_model_forward_host(bfb_model* model, const float* h_input, const int64_t* shape, int32_t rank,
                                   float* h_out, int64_t* out_shape, int32_t* out_rank) {
     return guarded([&] {
         require(model != nullptr && h_input != nullptr && shape != nullptr && out_shape != nullptr && out_rank != nullptr,
                 "model_forward_host: null argument");
         require(rank >= 1 && rank <= 8, "model_forward_host: bad rank");
-        requireDevice();
         std::vector<std::size_t> dims(shape, shape + rank);
+        std::vector<std::size_t> outDims = model->model->outputShape(dims);
+        *out_rank = static_cast<int32_t>(outDims.size());
+        for (std::size_t i = 0; i < outDims.size(); ++i) out_shape[i] = static_cast<int64_t>(outDims[i]);
+        if (h_out == nullptr) return;  // shape query only
+        requireDevice();
         std::size_t count = 1;
         for (std::size_t d : dims) count *= d;
         bfb200::DeviceTensor in(dims);
         if (count > 0) BFB_CUDA(cudaMemcpy(in.data(), h_input, count * sizeof(float), cudaMemcpyHostToDevice));
-        bfb200::DeviceTensor result = model->model->forward(in, false, nullptr);
-        *out_rank = static_cast<int32_t>(result.rank());
-        for (std::size_t i = 0; i < result.rank(); ++i) out_shape[i] = static_cast<int64_t>(result.dim(i));
-        if (h_out != nullptr && result.elementCount() > 0) {
-            BFB_CUDA(cudaMemcpy(h_out, result.data(), result.elementCount() * sizeof(float), cudaMemcpyDeviceToHost));
+
+        const std::size_t batch = dims[0];
+        const std::size_t slices = (rank == 2 && batch >= 8) ? 4 : 1;
+        if (slices == 1) {
+            bfb200::DeviceTensor result = model->model->forward(in, false, nullptr);
+            if (result.elementCount() > 0) {
+                BFB_CUDA(cudaMemcpy(h_out, result.data(), result.elementCount() * sizeof(float), cudaMemcpyDeviceToHost));
+            }
+            return;
         }
+        HostPathStreams& st = hostPathStreams();
+        const std::size_t perSeqIn = count / batch;
+        std::size_t outCount = 1;
+        for (std::size_t d : outDims) outCount *= d;
+        const std::size_t perSeqOut = outCount / batch;
+        std::vector<bfb200::DeviceTensor> results;  // kept alive until their copies have finished
+        results.reserve(slices);
+        const std::size_t step = (batch + slices - 1) / slices;
+        for (std::size_t b0 = 0; b0 < batch; b0 += step) {
+            const std::size_t nb = std::min(step, batch - b0);
+            std::vector<std::size_t> sliceDims = dims;
+            sliceDims[0] = nb;
+            bfb200::DeviceTensor view = bfb200::DeviceTensor::borrow(in.data() + b0 * perSeqIn, sliceDims);
+            try {
+                // forward returns after its own work on the compute stream is complete (status read-back)
+                results.push_back(model->model->forward(view, false, st.compute));
+            } catch (...) {
+                view.releaseOwnership();
+                cudaStreamSynchronize(st.copy);
+                throw;
+            }
+            view.releaseOwnership();
+            // the fp32 route works on the default stream, which the non-blocking copy stream does not wait for
+            BFB_CUDA(cudaStreamSynchronize(nullptr));
+            BFB_CUDA(cudaMemcpyAsync(h_out + b0 * perSeqOut, results.back().data(), nb * perSeqOut * sizeof(float),
+                                     cudaMemcpyDeviceToHost, st.copy));
+        }
+        BFB_CUDA(cudaStreamSynchronize(st.copy));
     });
 }
 

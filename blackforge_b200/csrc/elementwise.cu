@@ -479,6 +479,25 @@ __global__ void fp8ActScaleKernel(const float* amaxIn, float* out, const float* 
     out[2] = (1.0f / s) * (*weightInverse);
 }
 
+// Seeded N(0, sigma) fill of a [rows, colsLocal] block of a [*, colsFull] tensor. Every value is a pure
+// function of (seed, position in the FULL tensor), so tensor-parallel ranks that fill only their slice agree
+// with a rank that fills everything.
+__global__ void fillNormalKernel(float* __restrict__ out, int64_t rows, int64_t colsLocal, int64_t colsFull,
+                                 int64_t rowOffset, int64_t colOffset, uint64_t seed, float sigma) {
+    const int64_t total = rows * colsLocal;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t r = i / colsLocal, c = i - r * colsLocal;
+        uint64_t z = seed * 0x9E3779B97F4A7C15ull + static_cast<uint64_t>((r + rowOffset) * colsFull + c + colOffset);
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;  // splitmix64 finaliser
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        z ^= z >> 31;
+        const float u1 = (static_cast<float>(static_cast<uint32_t>(z >> 32)) + 1.0f) * 2.3283064e-10f;  // (0, 1]
+        const float u2 = static_cast<float>(static_cast<uint32_t>(z)) * 2.3283064e-10f;
+        out[i] = sigma * sqrtf(-2.0f * __logf(u1)) * __cosf(6.2831853f * u2);
+    }
+}
+
 // W[K,N] f32 -> W^T[N,K] in TOut, through a padded 32x32 shared tile.
 template <typename TOut>
 __global__ void transposeCastKernel(const float* __restrict__ w, void* __restrict__ out, int64_t k, int64_t n,
@@ -669,6 +688,17 @@ void fp8ScaleFromAmax(const float* dAmax, float* dScales, cudaStream_t stream) {
 void fp8ActScale(const float* dAmax, float* out, const float* dWeightInverse, cudaStream_t stream) {
     require(dAmax != nullptr && out != nullptr && dWeightInverse != nullptr, "fp8_act_scale: null pointer");
     fp8ActScaleKernel<<<1, 1, 0, stream>>>(dAmax, out, dWeightInverse);
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
+
+void fillNormal(float* out, int64_t rows, int64_t colsLocal, int64_t colsFull, int64_t rowOffset, int64_t colOffset,
+                uint64_t seed, float sigma, cudaStream_t stream) {
+    require(rows >= 0 && colsLocal >= 0 && colsFull >= colsLocal, "fill_normal: bad sizes");
+    if (rows * colsLocal == 0) return;
+    require(out != nullptr, "fill_normal: null pointer");
+    fillNormalKernel<<<gridFor(rows * colsLocal, kThreads), kThreads, 0, stream>>>(out, rows, colsLocal, colsFull,
+                                                                                  rowOffset, colOffset, seed, sigma);
     BFB_LAUNCH_CHECK();
     noteLaunch();
 }

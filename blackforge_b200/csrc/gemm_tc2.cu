@@ -1,8 +1,14 @@
-// tcgen05 GEMM with CTA pairs (tcgen05.mma.cta_group::2): two CTAs of a cluster share one
-// 256 x 256 output tile. Each CTA stages its own 128 rows of A and one 128-row half of B^T per
-// k-slice (32 KiB instead of 48 KiB per stage, so the ring is 6 deep) and holds the accumulator of
-// its own 128 rows in tensor memory; the leader CTA issues every MMA for both. Against the one-CTA
-// kernel this cuts the bytes pulled from L2 per FLOP by a third and deepens the prefetch.
+// tcgen05 GEMM with CTA pairs (tcgen05.mma.cta_group::2): two CTAs of a cluster share one output tile
+// of 256 rows x kAccN columns (kAccN = 256 or 512). Each CTA stages its own 128 rows of A and its half of
+// the B^T rows per k-slice and holds the accumulator of its own 128 rows in tensor memory; the leader CTA
+// issues every MMA (256 x 256 x 16 each) for both.
+//
+//   kAccN = 256  32 KiB per stage and CTA, 6-stage ring, two accumulator buffers: the epilogue of one tile
+//                runs under the MMAs of the next.
+//   kAccN = 512  48 KiB per stage, 4-stage ring, the whole tensor memory is one accumulator (two 256-column
+//                halves fed by the same A slice). The epilogue is not hidden, but every byte of A is used for
+//                twice as many FLOPs: 25 % fewer bytes come out of L2 per FLOP, which is what bounds the
+//                256-wide tile (about 10 TB/s of L2 reads whatever the SM clock).
 //
 // Synchronisation across the pair:
 //   full[s]      lives in the leader; both CTAs' TMA loads book their bytes on it
@@ -14,6 +20,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "kernels.hpp"
@@ -23,17 +30,21 @@ namespace bfb {
 
 namespace {
 
-constexpr int kPairM = 256;          // rows of the pair's tile (128 per CTA)
-constexpr int kPairN = 256;
-constexpr int kHalfN = kPairN / 2;   // B rows staged by each CTA
+constexpr int kPairM = 256;  // rows of the pair's tile (128 per CTA)
 constexpr int kRowBytes2 = 128;
-constexpr int kStages2 = 6;
-constexpr int kABytes2 = 128 * kRowBytes2;     // 16 KiB
-constexpr int kBBytes2 = kHalfN * kRowBytes2;  // 16 KiB
-constexpr int kStageBytes2 = kABytes2 + kBBytes2;
-constexpr int kThreads2 = 384;       // producer, MMA, TMEM, spare + 8 epilogue warps
+constexpr int kABytes2 = 128 * kRowBytes2;  // 16 KiB
+constexpr int kThreads2 = 384;              // producer, MMA, TMEM, spare + 8 epilogue warps
 constexpr int kEpilogueThreads2 = 256;
-constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + 1024 + 256;
+
+template <int kAccN>
+struct PairCfg {
+    static constexpr int kBRows = kAccN / 2;                    // B^T rows staged by each CTA per k-slice
+    static constexpr int kBBytes = kBRows * kRowBytes2;
+    static constexpr int kStageBytes = kABytes2 + kBBytes;      // 32 or 48 KiB
+    static constexpr int kStages = kAccN == 256 ? 6 : 4;
+    static constexpr int kBufs = 512 / kAccN;                   // accumulator buffers in the 512 TMEM columns
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
 
 struct PairTile {
     int m, n;
@@ -68,20 +79,25 @@ struct PairEpilogue {
 
 __device__ __forceinline__ float siluFast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
-template <int kElemBytes, typename TC>
+template <int kElemBytes, typename TC, int kAccN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, PairEpilogue ep,
                int m, int n, int k, int tilesM, int tilesN, int groupN, int* status) {
+    using Cfg = PairCfg<kAccN>;
     constexpr int kBlockK = kRowBytes2 / kElemBytes;
     constexpr int kMmaPerStage = 4;
-    constexpr uint32_t kIdesc = make_idesc(kPairM, kPairN, kElemBytes == 2 ? 1u : 0u, 0u);
+    constexpr int kStages = Cfg::kStages;
+    constexpr int kStageBytes = Cfg::kStageBytes;
+    constexpr int kBufs = Cfg::kBufs;
+    constexpr int kHalves = kAccN / 256;  // 256-column MMAs per k-step
+    constexpr uint32_t kIdesc = make_idesc(kPairM, 256, kElemBytes == 2 ? 1u : 0u, 0u);
 
     extern __shared__ uint8_t smemRaw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages2 * kStageBytes2);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
     uint64_t* fullBar = bars;
-    uint64_t* emptyBar = bars + kStages2;
-    uint64_t* accFullBar = bars + 2 * kStages2;
+    uint64_t* emptyBar = bars + kStages;
+    uint64_t* accFullBar = bars + 2 * kStages;
     uint64_t* accEmptyBar = accFullBar + 2;
     uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(accEmptyBar + 2);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
@@ -96,7 +112,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
     const int numClusters = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages2; ++s) {
+        for (int s = 0; s < kStages; ++s) {
             mbar_init(&fullBar[s], 1);
             mbar_init(&emptyBar[s], 1);
         }
@@ -127,22 +143,26 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
         for (int t = clusterId; t < totalTiles && alive; t += numClusters) {
             PairTile tc = pairTileCoord(t, tilesM, tilesN, groupN);
             const int rowA = tc.m * kPairM + static_cast<int>(rank) * 128;
-            const int rowB = tc.n * kPairN + static_cast<int>(rank) * kHalfN;
             for (int kb = 0; kb < numK; ++kb) {
                 if (!warp_all(mbar_wait(&emptyBar[stage], phase ^ 1u, abortFlag, status, kDevTimeoutStageEmpty))) {
                     alive = false;
                     break;
                 }
                 if (lane == 0) {
-                    uint8_t* sa = smem + stage * kStageBytes2;
+                    uint8_t* sa = smem + stage * kStageBytes;
                     uint8_t* sb = sa + kABytes2;
-                    if (leader) mbar_arrive_expect_tx(&fullBar[stage], 2 * kStageBytes2);
+                    if (leader) mbar_arrive_expect_tx(&fullBar[stage], 2 * kStageBytes);
                     const uint32_t fullLeader = mapa_cluster(smem_u32(&fullBar[stage]), 0);
                     tma_load_2d_pair(sa, &tmapA, fullLeader, kb * kBlockK, rowA);
-                    tma_load_2d_pair(sb, &tmapB, fullLeader, kb * kBlockK, rowB);
+                    // each 256-column MMA takes 128 B^T rows from each CTA: this CTA's rows of column half h
+#pragma unroll
+                    for (int h = 0; h < kHalves; ++h) {
+                        tma_load_2d_pair(sb + h * (128 * kRowBytes2), &tmapB, fullLeader, kb * kBlockK,
+                                         tc.n * kAccN + h * 256 + static_cast<int>(rank) * 128);
+                    }
                 }
                 __syncwarp();
-                if (++stage == kStages2) {
+                if (++stage == kStages) {
                     stage = 0;
                     phase ^= 1u;
                 }
@@ -155,11 +175,11 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
         int local = 0;
         bool alive = true;
         for (int t = clusterId; t < totalTiles && alive; t += numClusters, ++local) {
-            const int buf = local & 1;
-            const uint32_t accPhase = (local >> 1) & 1u;
+            const int buf = local % kBufs;
+            const uint32_t accPhase = static_cast<uint32_t>(local / kBufs) & 1u;
             if (!warp_all(mbar_wait(&accEmptyBar[buf], accPhase ^ 1u, abortFlag, status, kDevTimeoutAccEmpty))) break;
             tc_fence_after();
-            const uint32_t dTmem = tmemBase + static_cast<uint32_t>(buf * kPairN);
+            const uint32_t dTmem = tmemBase + static_cast<uint32_t>(buf * kAccN);
             for (int kb = 0; kb < numK; ++kb) {
                 if (!warp_all(mbar_wait(&fullBar[stage], phase, abortFlag, status, kDevTimeoutTmaFull))) {
                     alive = false;
@@ -167,22 +187,26 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
                 }
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t aAddr = smem_u32(smem + stage * kStageBytes2);
+                    const uint32_t aAddr = smem_u32(smem + stage * kStageBytes);
                     const uint32_t bAddr = aAddr + kABytes2;
                     const uint64_t aDesc = make_smem_desc_sw128(aAddr, 0, 1024);
-                    const uint64_t bDesc = make_smem_desc_sw128(bAddr, 0, 1024);
 #pragma unroll
                     for (int kk = 0; kk < kMmaPerStage; ++kk) {
                         const uint64_t step = static_cast<uint64_t>((kk * 32) >> 4);
                         const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
-                        if constexpr (kElemBytes == 2) umma_f16_pair(dTmem, aDesc + step, bDesc + step, kIdesc, acc);
-                        else umma_f8_pair(dTmem, aDesc + step, bDesc + step, kIdesc, acc);
+#pragma unroll
+                        for (int h = 0; h < kHalves; ++h) {
+                            const uint64_t bDesc = make_smem_desc_sw128(bAddr + h * (128 * kRowBytes2), 0, 1024);
+                            const uint32_t d = dTmem + static_cast<uint32_t>(h * 256);
+                            if constexpr (kElemBytes == 2) umma_f16_pair(d, aDesc + step, bDesc + step, kIdesc, acc);
+                            else umma_f8_pair(d, aDesc + step, bDesc + step, kIdesc, acc);
+                        }
                     }
                     umma_commit_pair(&emptyBar[stage]);
                     if (kb == numK - 1) umma_commit_pair(&accFullBar[buf]);
                 }
                 __syncwarp();
-                if (++stage == kStages2) {
+                if (++stage == kStages) {
                     stage = 0;
                     phase ^= 1u;
                 }
@@ -190,6 +214,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
         }
     } else if (warp >= 4) {
         // ---------------- epilogue (both CTAs, 8 warps: lane quarter x column half) ----------------
+        constexpr int kColsPerWarp = kAccN / 2;
         const int quarter = warp & 3;
         const int colHalf = (warp - 4) >> 2;
         const float scale = ep.dAlpha != nullptr ? *ep.dAlpha : ep.alpha;
@@ -202,17 +227,17 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
         int local = 0;
         for (int t = clusterId; t < totalTiles; t += numClusters, ++local) {
             PairTile tc = pairTileCoord(t, tilesM, tilesN, groupN);
-            const int buf = local & 1;
-            const uint32_t accPhase = (local >> 1) & 1u;
+            const int buf = local % kBufs;
+            const uint32_t accPhase = static_cast<uint32_t>(local / kBufs) & 1u;
             if (!warp_all(mbar_wait(&accFullBar[buf], accPhase, abortFlag, status, kDevTimeoutAccFull))) break;
             tc_fence_after();
             const int row = tc.m * kPairM + static_cast<int>(rank) * 128 + quarter * 32 + lane;
             const bool rowOk = row < m;
             const uint32_t tBase = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   static_cast<uint32_t>(buf * kPairN + colHalf * 128);
+                                   static_cast<uint32_t>(buf * kAccN + colHalf * kColsPerWarp);
 #pragma unroll 1
-            for (int chunk = 0; chunk < 4; ++chunk) {
-                const int col0 = tc.n * kPairN + colHalf * 128 + chunk * 32;
+            for (int chunk = 0; chunk < kColsPerWarp / 32; ++chunk) {
+                const int col0 = tc.n * kAccN + colHalf * kColsPerWarp + chunk * 32;
                 if (col0 >= n) break;
                 uint32_t raw[32];
                 tmem_ld_32x32(tBase + static_cast<uint32_t>(chunk * 32), raw);
@@ -292,8 +317,18 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
     }
 }
 
-template <int kElemBytes, typename TC>
+// BFB_GEMM_TILE_N=256 in the environment forces the 256-column tile (for A/B measurements).
+int preferredTileN() {
+    static const int v = [] {
+        const char* e = std::getenv("BFB_GEMM_TILE_N");
+        return (e != nullptr && std::atoi(e) == 256) ? 256 : 512;
+    }();
+    return v;
+}
+
+template <int kElemBytes, typename TC, int kAccN>
 void launchPair(const GemmArgs& g, cudaStream_t stream) {
+    using Cfg = PairCfg<kAccN>;
     constexpr int kBlockK = kRowBytes2 / kElemBytes;
     TensorMapStorage ta, tb;
     {
@@ -305,24 +340,41 @@ void launchPair(const GemmArgs& g, cudaStream_t stream) {
     {
         uint64_t dims[2] = {static_cast<uint64_t>(g.k), static_cast<uint64_t>(g.n)};
         uint64_t strides[1] = {static_cast<uint64_t>(g.k) * kElemBytes};
-        uint32_t box[2] = {static_cast<uint32_t>(kBlockK), static_cast<uint32_t>(kHalfN)};
+        uint32_t box[2] = {static_cast<uint32_t>(kBlockK), 128u};
         encodeTensorMap(&tb, g.b, kElemBytes, 2, dims, strides, box);
     }
     const int tilesM = static_cast<int>((g.m + kPairM - 1) / kPairM);
-    const int tilesN = static_cast<int>((g.n + kPairN - 1) / kPairN);
-    const int groups = (tilesN + 15) / 16;
+    const int tilesN = static_cast<int>((g.n + kAccN - 1) / kAccN);
+    // about 4096 columns of B^T (16 MB at K = 2048) stay L2-resident per group
+    const int maxGroup = 4096 / kAccN;
+    const int groups = (tilesN + maxGroup - 1) / maxGroup;
     const int groupN = (tilesN + groups - 1) / groups;
     const int clusters = std::max(1, std::min(tilesM * tilesN, smCount() / 2));
     PairEpilogue ep{g.c, g.bias, g.residual, g.alpha, g.dAlpha, g.epilogue, g.roundCBf16};
-    auto kernel = gemmPairKernel<kElemBytes, TC>;
-    BFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2));
+    auto kernel = gemmPairKernel<kElemBytes, TC, kAccN>;
+    BFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     ProfileScope prof(kProfGemmTc, stream, 2.0 * static_cast<double>(g.m) * static_cast<double>(g.n) * static_cast<double>(g.k));
-    kernel<<<2 * clusters, kThreads2, kSmemBytes2, stream>>>(*reinterpret_cast<CUtensorMap*>(ta.bytes),
-                                                             *reinterpret_cast<CUtensorMap*>(tb.bytes), ep,
-                                                             static_cast<int>(g.m), static_cast<int>(g.n),
-                                                             static_cast<int>(g.k), tilesM, tilesN, groupN, g.dStatus);
+    kernel<<<2 * clusters, kThreads2, Cfg::kSmemBytes, stream>>>(*reinterpret_cast<CUtensorMap*>(ta.bytes),
+                                                                 *reinterpret_cast<CUtensorMap*>(tb.bytes), ep,
+                                                                 static_cast<int>(g.m), static_cast<int>(g.n),
+                                                                 static_cast<int>(g.k), tilesM, tilesN, groupN, g.dStatus);
     BFB_LAUNCH_CHECK();
     noteLaunch();
+}
+
+template <int kElemBytes, typename TC>
+void launchPairAnyTile(const GemmArgs& g, cudaStream_t stream) {
+    // The 512-column tile pays off once its exposed epilogue is small next to the k loop and there are enough
+    // tiles. Measured at M = 65536: K = 2048 and 5632 lose 4-17 % to the 256-column tile, K = 16384 gains 17 %
+    // (1587 vs 1358 TFLOP/s); BFB_GEMM_WIDE_K overrides the switch-over depth.
+    static const int64_t wideK = [] {
+        const char* e = std::getenv("BFB_GEMM_WIDE_K");
+        return e != nullptr ? static_cast<int64_t>(std::atoll(e)) : static_cast<int64_t>(8192);
+    }();
+    const bool wide = preferredTileN() == 512 && g.n >= 512 && g.k >= wideK &&
+                      ((g.m + 255) / 256) * ((g.n + 511) / 512) >= smCount() / 2;
+    if (wide) launchPair<kElemBytes, TC, 512>(g, stream);
+    else launchPair<kElemBytes, TC, 256>(g, stream);
 }
 
 }  // namespace
@@ -331,9 +383,9 @@ void gemmTensorCorePair(const GemmArgs& g, cudaStream_t stream) {
     const bool cf32 = g.cDtype == BFB_F32;
     using bf = __nv_bfloat16;
     if (g.abDtype == BFB_BF16) {
-        if (cf32) launchPair<2, float>(g, stream); else launchPair<2, bf>(g, stream);
+        if (cf32) launchPairAnyTile<2, float>(g, stream); else launchPairAnyTile<2, bf>(g, stream);
     } else {
-        if (cf32) launchPair<1, float>(g, stream); else launchPair<1, bf>(g, stream);
+        if (cf32) launchPairAnyTile<1, float>(g, stream); else launchPairAnyTile<1, bf>(g, stream);
     }
 }
 

@@ -141,12 +141,19 @@ public:
 
     [[nodiscard]] std::vector<Parameter*> parameters();
     [[nodiscard]] const std::string& name() const { return name_; }
+    // Shape of forward()'s result for an input of this shape, without running anything.
+    [[nodiscard]] std::vector<std::size_t> outputShape(const std::vector<std::size_t>& inputShape) const;
     // Structure only (no device memory touched): checkpoint order, names, full shapes.
     [[nodiscard]] std::size_t parameterCount() const;
     [[nodiscard]] const std::string& parameterName(std::size_t index) const;
     [[nodiscard]] const std::vector<std::size_t>& parameterShape(std::size_t index) const;
     void setParameter(std::size_t index, const float* hostFullValues);
     void getParameter(std::size_t index, float* hostFullValues);
+    // Synthetic weights without a host round trip: seeded N(0, sigma), identical whatever the tensor-parallel split.
+    void fillParameterNormal(std::size_t index, std::uint64_t seed, float sigma);
+    // After conversion to bf16 / e4m3, drop the fp32 copies of the GEMM weights (inference on models whose fp32
+    // weights would not fit next to the converted ones). Those parameters can no longer be read or set.
+    void releaseMasterWeights();
     // Parameters changed: converted weights are rebuilt at the next forward.
     void invalidatePreparedWeights();
     [[nodiscard]] std::optional<std::size_t> firstLayerEmbeddingVocabSize() const;

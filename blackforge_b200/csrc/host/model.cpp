@@ -132,6 +132,7 @@ struct Model::Impl {
     bool randomInit = true;
     bool built = false;
     bool prepared = false;
+    bool mastersReleased = false;  // fp32 copies of the GEMM weights dropped after conversion
     std::vector<Parameter> params;
     std::vector<ParamMeta> meta;
     std::vector<Layer> layers;
@@ -301,6 +302,9 @@ void Model::Impl::setParam(std::size_t index, const float* hostFull) {
     require(index < params.size(), "Model: parameter index out of range");
     require(hostFull != nullptr, "Model: null parameter data");
     Parameter& prm = params[index];
+    if (mastersReleased && prm.value.data() == nullptr) {
+        fail(BFB_UNSUPPORTED, "Model: the fp32 copy of '" + prm.name + "' was released; it can no longer be set");
+    }
     const Shard s = tpWorld > 1 ? meta[index].shard : Shard::None;
     const std::size_t n = prm.value.elementCount();
     const std::size_t w = static_cast<std::size_t>(tpWorld), r = static_cast<std::size_t>(tpRank);
@@ -313,7 +317,7 @@ void Model::Impl::setParam(std::size_t index, const float* hostFull) {
         BFB_CUDA(cudaMemcpy2D(prm.value.data(), nLoc * sizeof(float), hostFull + r * nLoc, nFull * sizeof(float),
                               nLoc * sizeof(float), k, cudaMemcpyHostToDevice));
     }
-    prepared = false;
+    if (!mastersReleased) prepared = false;
 }
 
 void Model::Impl::getParam(std::size_t index, float* hostFull) {
@@ -324,6 +328,9 @@ void Model::Impl::getParam(std::size_t index, float* hostFull) {
         fail(BFB_UNSUPPORTED, "Model: reading back a tensor-parallel parameter is not supported");
     }
     Parameter& prm = params[index];
+    if (mastersReleased && prm.value.data() == nullptr) {
+        fail(BFB_UNSUPPORTED, "Model: the fp32 copy of '" + prm.name + "' was released");
+    }
     BFB_CUDA(cudaMemcpy(hostFull, prm.value.data(), prm.value.elementCount() * sizeof(float), cudaMemcpyDeviceToHost));
 }
 
@@ -698,10 +705,56 @@ std::vector<Parameter*> Model::parameters() {
     return out;
 }
 
+std::vector<std::size_t> Model::outputShape(const std::vector<std::size_t>& inputShape) const {
+    std::vector<std::size_t> shape = inputShape;
+    for (const Layer& l : impl_->layers) {
+        if (l.kind == BFB_OP_EMBEDDING) shape.push_back(l.outFeat);
+        else if (l.kind == BFB_OP_LINEAR && !shape.empty()) {
+            shape.back() = l.shardedLinear ? l.outFeat / static_cast<std::size_t>(impl_->tpWorld) : l.outFeat;
+        }
+    }
+    return shape;
+}
+
 std::size_t Model::parameterCount() const { return impl_->params.size(); }
 const std::string& Model::parameterName(std::size_t index) const { return impl_->params.at(index).name; }
 const std::vector<std::size_t>& Model::parameterShape(std::size_t index) const {
     return impl_->params.at(index).fullShape;
+}
+
+void Model::fillParameterNormal(std::size_t index, std::uint64_t seed, float sigma) {
+    impl_->allocateParams();
+    require(index < impl_->params.size(), "Model: parameter index out of range");
+    Parameter& prm = impl_->params[index];
+    const Shard s = impl_->tpWorld > 1 ? impl_->meta[index].shard : Shard::None;
+    const std::size_t r = static_cast<std::size_t>(impl_->tpRank);
+    const std::size_t rows = prm.value.rank() == 2 ? prm.value.dim(0) : 1;
+    const std::size_t colsLocal = prm.value.rank() == 2 ? prm.value.dim(1) : prm.value.dim(0);
+    const std::size_t colsFull = prm.fullShape.size() == 2 ? prm.fullShape[1] : prm.fullShape[0];
+    std::size_t rowOff = 0, colOff = 0;
+    if (s == Shard::Rows) rowOff = r * rows;
+    if (s == Shard::Cols || s == Shard::Vec) colOff = r * colsLocal;
+    bfb::fillNormal(prm.value.data(), static_cast<int64_t>(rows), static_cast<int64_t>(colsLocal),
+                    static_cast<int64_t>(colsFull), static_cast<int64_t>(rowOff), static_cast<int64_t>(colOff), seed,
+                    sigma, nullptr);
+    if (!impl_->mastersReleased) impl_->prepared = false;
+}
+
+void Model::releaseMasterWeights() {
+    impl_->prepare(nullptr);
+    BFB_CUDA(cudaStreamSynchronize(nullptr));
+    if (impl_->mode == Mode::Fp32) return;  // the fp32 route computes from the masters
+    for (Layer& l : impl_->layers) {
+        if (l.kind != BFB_OP_ATTENTION && l.kind != BFB_OP_FEEDFORWARD && l.kind != BFB_OP_LINEAR) continue;
+        const int weightSlots[3][4] = {{0, 1, 2, 3}, {0, 2, -1, -1}, {0, -1, -1, -1}};
+        const int* slots = l.kind == BFB_OP_ATTENTION ? weightSlots[0] : l.kind == BFB_OP_FEEDFORWARD ? weightSlots[1] : weightSlots[2];
+        for (int i = 0; i < 4; ++i) {
+            if (slots[i] < 0) continue;
+            impl_->params[l.p[slots[i]]].value = DeviceTensor();  // biases and tables stay
+        }
+    }
+    impl_->mastersReleased = true;
+    bfb::poolTrim();
 }
 
 void Model::setParameter(std::size_t index, const float* hostFullValues) { impl_->setParam(index, hostFullValues); }

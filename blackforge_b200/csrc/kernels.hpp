@@ -31,6 +31,10 @@ void weightPrepare(const float* w, void* out, int outDtype, int64_t k, int64_t n
 int64_t quantizeScratchFloats(int64_t n);
 void quantizeE4m3(const void* in, int inDtype, int64_t n, void* out, float* dScales, const float* dWeightInverse,
                   float* scratch, cudaStream_t stream);
+// Seeded N(0, sigma) values for the [rows, colsLocal] block at (rowOffset, colOffset) of a tensor with colsFull
+// columns; a value depends only on the seed and its position in the full tensor.
+void fillNormal(float* out, int64_t rows, int64_t colsLocal, int64_t colsFull, int64_t rowOffset, int64_t colOffset,
+                uint64_t seed, float sigma, cudaStream_t stream);
 // In-place rounding of an f32 buffer to bf16 precision (simulated `storage bf16` for the fp32 path).
 void roundBf16InPlace(float* x, int64_t n, cudaStream_t stream);
 

@@ -263,6 +263,15 @@ void bfb_model_param_shape(const bfb_model* model, int32_t index, int64_t* shape
 bfb_status bfb_model_param_set(bfb_model* model, int32_t index, const float* h_values);
 bfb_status bfb_model_param_get(bfb_model* model, int32_t index, float* h_values);
 
+/* Synthetic weights for benchmarks, generated on the device: parameter `index` becomes seeded N(0, sigma). A value
+ * depends only on (seed, position in the full tensor), so every tensor-parallel rank fills just its slice and
+ * all ranks still agree. No counterpart in the reference (its Executor draws uniform weights on the host). */
+bfb_status bfb_model_param_fill_normal(bfb_model* model, int32_t index, uint64_t seed, float sigma);
+/* Inference-only memory saver: convert the weights now and drop the fp32 copies of the GEMM weights (the
+ * reference keeps fp32 values and gradients for every parameter, model.cu:139-250). Those parameters can no
+ * longer be read, set or saved afterwards. No effect on an fp32-compute model. */
+bfb_status bfb_model_release_master_weights(bfb_model* model);
+
 /* BFCKPT1 (include/blackforge/backend/cpu/checkpoint.hpp:15-24). Load matches by name and shape; an
  * unknown name, a shape mismatch, a bad magic or a truncated file give BFB_IO_ERROR. */
 bfb_status bfb_model_load_checkpoint(bfb_model* model, const char* path);

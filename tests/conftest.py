@@ -10,6 +10,10 @@ if ROOT not in sys.path:
 
 GOLDEN = os.path.join(ROOT, "tests", "golden")
 
+# The GEMM switches to its 512-column tile only for deep reductions (K >= 8192 by default); lower the threshold
+# so that the test sizes reach that kernel too (read once by the library, at its first GEMM).
+os.environ.setdefault("BFB_GEMM_WIDE_K", "1024")
+
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")

@@ -114,6 +114,26 @@ def test_fp8_matches_oracle(gpu, m, n, k):
     assert rel_err(got, want * 0.5) <= ACC_TOL
 
 
+@pytest.mark.parametrize("dtype_name", ["bf16", "fp8"])
+def test_wide_tile_path_with_ragged_edges(gpu, dtype_name):
+    # enough 256 x 512 tiles (>= one per CTA pair) and K >= 1024 select the 512-column accumulator; M and N are
+    # ragged so the last tile row / column is partly outside, and every CTA pair walks more than one tile
+    rng = np.random.default_rng(11)
+    m, n, k = 256 * 12 - 60, 512 * 8 - 248, 1024
+    if dtype_name == "bf16":
+        a, b = operands(rng, m, n, k, scale=0.5)
+        ab = gpu.BF16
+    else:
+        a = O.e4m3_round_hw(rng.standard_normal((m, k)).astype(np.float32) * 2)
+        b = O.e4m3_round_hw(rng.standard_normal((k, n)).astype(np.float32) * 2)
+        ab = gpu.FP8_E4M3
+    bias = rng.standard_normal(n).astype(np.float32)
+    res = O.round_bf16(rng.standard_normal((m, n)).astype(np.float32))
+    want = O.matmul(a, b, exact_order=False) + bias + res
+    got = gemm(gpu, a, np.ascontiguousarray(b.T), ab, gpu.B_NK, gpu.F32, "bias_residual", bias=bias, residual=res)
+    assert rel_err(got, want) <= ACC_TOL
+
+
 def test_fp8_scaled_gemm_definition(gpu):
     # the project's `compute fp8.e4m3` arithmetic end to end: amax -> scale -> e4m3 -> GEMM -> rescale
     rng = np.random.default_rng(6)

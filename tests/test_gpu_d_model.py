@@ -208,3 +208,22 @@ def test_device_forward_reports_launches(gpu):
     # embed + per layer (norm, qkv, attention, out-proj, norm, ff1, ff2) + final linear on a bf16 stream
     assert gpu.lib().bfb_launch_count(0) == 1 + 7 * TC["layers"] + 1
     out.free()
+
+
+@pytest.mark.parametrize("precision", [None, {"storage": "bf16", "compute": "bf16"}])
+def test_host_path_slices_large_batches_without_changing_results(gpu, precision):
+    """bfb_model_forward_host runs batches of 8 or more in slices (copy of one slice overlaps the next slice's
+    compute); every sequence must come out exactly as when it is run alone."""
+    cfg = C1 if precision is None else TC
+    ops = O.lm_ops(**cfg)
+    m = gpu.Model(ops, precision=precision, seed=7)
+    seq = 32 if precision is None else 128
+    ids = O.synth_token_ids(11, seq, cfg["vocab"], seed=5)      # 11: slices of 3, 3, 3, 2
+    whole = m.forward_host(ids)
+    assert whole.shape == (11, seq, cfg["vocab"])
+    for b in (0, 4, 10):
+        assert np.array_equal(whole[b:b + 1], m.forward_host(ids[b:b + 1]))
+    bad = ids.copy()
+    bad[9, 0] = cfg["vocab"]
+    with pytest.raises(gpu.InvalidArgument):
+        m.forward_host(bad)
