@@ -37,7 +37,7 @@ constexpr int kKvSlots = 4;
 constexpr int kQOff = 0;
 constexpr int kKvOff = kTileBytes;
 constexpr int kPOff = kKvOff + kKvSlots * kTileBytes;
-constexpr int kBarOff = kPOff + 2 * kTileBytes;
+constexpr int kBarOff = kPOff;  // probabilities live in tensor memory, not in shared memory
 constexpr int kXchgOff = kBarOff + 256;               // float [2 buffers][2 halves][128 rows]
 constexpr int kAttnSmemBytes = kXchgOff + 2 * 2 * 128 * 4;
 constexpr int kSoftmaxWarps = 8;
@@ -171,7 +171,6 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
         // ---------------- MMA issuer ----------------
         const uint32_t qAddr = smem_u32(smem + kQOff);
         const uint32_t kvAddr = smem_u32(smem + kKvOff);
-        const uint32_t pAddr = smem_u32(smem + kPOff);
         auto issueQK = [&](int j) -> bool {  // S[j&1] = Q K(j)^T
             const int idx = 2 * j;
             const int slot = idx & (kKvSlots - 1);
@@ -211,15 +210,14 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
             tc_fence_after();
             if (lane == 0) {
                 const uint32_t vAddr = kvAddr + slot * kTileBytes;
-                const uint32_t pBuf = pAddr + (j & 1) * kTileBytes;
+                const uint32_t pTmem = tmemBase + static_cast<uint32_t>((j & 1) * kBN);  // P sits where S was
                 const uint32_t dO = tmemBase + 256u + static_cast<uint32_t>((j & 1) * kD);
 #pragma unroll
                 for (int kk = 0; kk < kBN / 16; ++kk) {
-                    // P: K-major over keys (two 64-key halves). V: keys are rows (MN-major B): 8-key groups
-                    // 1024 B apart, the two 64-wide halves of head_dim one half-tile apart.
-                    const uint32_t pOff = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-                    umma_f16(dO, make_smem_desc_sw128(pBuf + pOff, 0, 1024),
-                             make_smem_desc_sw128(vAddr + kk * 2048, kHalfBytes, 1024), kIdescPV, kk > 0 ? 1u : 0u);
+                    // P from tensor memory: 16 keys = 8 packed columns per step. V: keys are rows (MN-major B):
+                    // 8-key groups 1024 B apart, the two 64-wide halves of head_dim one half-tile apart.
+                    umma_f16_ts(dO, pTmem + static_cast<uint32_t>(kk * 8),
+                                make_smem_desc_sw128(vAddr + kk * 2048, kHalfBytes, 1024), kIdescPV, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(&kvEmpty[slot]);
                 umma_commit(&oFull[j & 1]);
@@ -239,8 +237,6 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
 #pragma unroll
         for (int i = 0; i < 64; ++i) oAcc[i] = 0.0f;
         bool alive = true;
-        uint8_t* pRow = smem + kPOff + half * kHalfBytes + r * 128;
-        const int sw = r & 7;
 
         for (int j = 0; j < nKv; ++j) {
             const int buf = j & 1;
@@ -263,8 +259,6 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                 tmem_ld_32x32(sAddr, s0);
                 tmem_ld_32x32(sAddr + 32u, s1);
                 tmem_ld_wait();
-                tc_fence_before();
-                mbar_arrive(&sFree[buf]);  // S buffer can be refilled while we work from registers
                 if (needMask) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
@@ -301,7 +295,6 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
             const uint64_t scale2 = pack_f32x2(p.scaleLog2, p.scaleLog2);
             const uint64_t negMax2 = pack_f32x2(-mUse, -mUse);
             uint64_t sumA = pack_f32x2(0.0f, 0.0f), sumB = sumA;
-            uint8_t* pBuf = pRow + buf * kTileBytes;
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 const uint32_t* sv = c == 0 ? s0 : s1;
@@ -320,16 +313,14 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                     __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
                     packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
                 }
-                // 32 keys = four 16-byte chunks; chunk index inside the 128-byte row is XORed with row % 8
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const int cc = (c * 4 + g) ^ sw;
-                    *reinterpret_cast<uint4*>(pBuf + cc * 16) =
-                        make_uint4(packed[g * 4], packed[g * 4 + 1], packed[g * 4 + 2], packed[g * 4 + 3]);
-                }
+                // P replaces S in tensor memory: two bf16 keys per 32-bit column, so 128 keys take the first 64
+                // columns of the S buffer and this thread's 32 keys of chunk c take 16 of them
+                tmem_st_32x16(tmemBase + laneBase + static_cast<uint32_t>(buf * kBN + half * 32 + c * 16), packed);
             }
-            fence_proxy_async_smem();
-            mbar_arrive(&pFull[buf]);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&pFull[buf]);   // P is in place ...
+            mbar_arrive(&sFree[buf]);   // ... and S has been consumed: the buffer may be overwritten after P V
             float sumLo, sumHi;
             unpack_f32x2(add_f32x2(sumA, sumB), sumLo, sumHi);
             lRun = lRun * alpha + (sumLo + sumHi);
