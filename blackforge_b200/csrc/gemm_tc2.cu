@@ -118,7 +118,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&accFullBar[b], 1);
-            mbar_init(&accEmptyBar[b], 2 * kEpilogueThreads2);
+            mbar_init(&accEmptyBar[b], 2 * (kEpilogueThreads2 / 32));  // one arrival per epilogue warp of both CTAs
         }
         *abortFlag = 0;
         fence_mbar_init();
@@ -299,7 +299,8 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
                 }
             }
             tc_fence_before();
-            mbar_arrive_cluster(mapa_cluster(smem_u32(&accEmptyBar[buf]), 0));
+            __syncwarp();  // one (remote) arrival per warp instead of one per thread
+            if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&accEmptyBar[buf]), 0));
         }
     }
 
