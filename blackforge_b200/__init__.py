@@ -14,7 +14,8 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libbfb200.so")
+# BFB200_LIBRARY points at another build of the same library (e.g. an instrumented one) when set.
+LIB_PATH = os.environ.get("BFB200_LIBRARY") or os.path.join(_HERE, "libbfb200.so")
 
 OK, INVALID_ARGUMENT, CUDA_ERROR, TIMEOUT, UNSUPPORTED, IO_ERROR = range(6)
 F32, BF16, FP8_E4M3 = 0, 1, 2
