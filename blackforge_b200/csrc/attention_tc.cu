@@ -1,23 +1,26 @@
 // tcgen05 flash attention for sm_100a: head_dim 128, bf16 operands, fp32 online softmax, causal
 // (with a cache offset) or bidirectional. No score matrix is ever written to global memory.
 //
-// One CTA owns one 128-row query tile of one (batch, head). With kParts softmax threads per query row
-// (2 or 4) the roles are:
-//   warps 0 .. 4*kParts-1   softmax. Warp w reads TMEM lanes 32*(w%4).. (its 32 query rows) and the
-//               128/kParts key columns of part w/4. A thread reads its slice of S once, the parts of a row
-//               exchange their maxima through shared memory, the probabilities are written back as bf16 INTO
-//               TENSOR MEMORY over the scores they came from (two keys per 32-bit column), and the thread folds
-//               its 128/kParts output columns of the previous tile's P V product into registers with one FMA
-//               per element (acc = acc * alpha_prev + O_prev). Row sums stay per part and are combined at the end.
-//   warp 4*kParts      TMA producer: Q once, then K and V tiles (128 keys x 128 dims, two 64-wide swizzled
-//               halves each) through a 4-slot shared-memory ring
-//   warp 4*kParts+1    MMA issuer + TMEM owner: S = Q K^T (128x128x16 steps, both operands from shared memory)
-//               into one of two S buffers, then O_j = P V with P read from tensor memory and V from shared memory
-//               into one of two O buffers; S of the next tile is issued before P of the current one is awaited,
-//               so the tensor core works under the softmax
-// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_j occupies the first 64 columns of S_j.
-// Causal tiles above the diagonal are never visited; only tiles that straddle it are masked. All mbarrier
-// waits are bounded.
+// Persistent CTAs (one per SM) walk a list of work items; an item is a block of 256 query rows of one
+// (batch, head), handled as two 128-row tiles, side A and side B, that share every K and V tile. Roles:
+//   warps 0-3   softmax of side A, warps 4-7 softmax of side B: ONE thread per query row and no exchange between
+//               threads. A thread reads its row of S (128 scores) from tensor memory, takes the maximum,
+//               exponentiates, and writes the probabilities back as bf16 INTO TENSOR MEMORY over the scores (two
+//               keys per 32-bit column). The two sides are independent, so while one waits for its next scores
+//               the other has the scheduler's exp unit to itself.
+//   warp 8      TMA producer: Q of each item (both sides) into one of two Q buffers, K and V tiles (128 keys x
+//               128 dims, two 64-wide swizzled halves each) through a 3-slot ring. It runs ahead into the next
+//               item, so the pipeline does not drain between items.
+//   warp 9      MMA issuer + TMEM owner. Per key tile and side: O += P V (P from tensor memory, V from shared
+//               memory), then S = Q K^T of that side's NEXT key tile. Tensor-core operations of one thread run in
+//               issue order, so the next scores overwrite P only after P V has read it.
+//   warps 10-11 idle (they complete the warpgroup whose registers are handed to the softmax warps).
+// O stays in tensor memory for the whole item and accumulates across key tiles. The exponent reference of a
+// row follows the running maximum lazily: it moves (and O and the row sum are rescaled) only when the maximum
+// has grown by more than 8 in log2 units, so probabilities stay below 2^8 and almost no tile pays for a rescale.
+// TMEM columns: S_A [0,128) S_B [128,256) O_A [256,384) O_B [384,512); P of a tile occupies the first 64
+// columns of its S region. Key tiles above the causal diagonal are never visited; only tiles that straddle it
+// are masked. All mbarrier waits are bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -33,37 +36,30 @@ namespace bfb {
 namespace {
 
 constexpr int kD = 128;
-constexpr int kBM = 128;
-constexpr int kBN = 128;
+constexpr int kBM = 128;                    // query rows per side
+constexpr int kBN = 128;                    // keys per tile
+constexpr int kItemRows = 2 * kBM;
 constexpr int kHalfBytes = 128 * 128;       // one 64-wide half of a 128-row tile
 constexpr int kTileBytes = 2 * kHalfBytes;  // 32 KiB
-constexpr int kKvSlots = 4;
-constexpr int kQOff = 0;
-constexpr int kKvOff = kTileBytes;
+constexpr int kKvSlots = 3;
+constexpr int kQOff = 0;                    // [2 buffers][2 sides] Q tiles
+constexpr int kKvOff = 4 * kTileBytes;
 constexpr int kBarOff = kKvOff + kKvSlots * kTileBytes;
-constexpr int kXchgOff = kBarOff + 256;     // float [2 buffers][kParts][128 rows]
+constexpr int kSmemBytes = kBarOff + 256;
+constexpr int kSoftmaxWarps = 8;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kThreads = 384;
+constexpr int kSoftmaxRegs = 232;           // 384 threads start with 168 registers each; the last warpgroup gives
+constexpr int kOtherRegs = 40;              // 128 * (168 - 40), the two softmax warpgroups take 2 * 128 * (232 - 168)
+constexpr float kRescaleSlack = 8.0f;       // log2 units the running maximum may lead the exponent reference
 constexpr uint32_t kIdescQK = make_idesc(kBM, kBN, 1u, 0u);
 constexpr uint32_t kIdescPV = make_idesc(kBM, kD, 1u, 1u);
-
-template <int kParts>
-struct AttnCfg {
-    static constexpr int kCols = 128 / kParts;  // key columns (and output columns) per softmax thread
-    static constexpr int kSoftmaxWarps = 4 * kParts;
-    static constexpr int kSoftmaxThreads = kSoftmaxWarps * 32;
-    static constexpr int kThreads = kSoftmaxThreads + 64;
-    static constexpr int kSmemBytes = kXchgOff + 2 * kParts * 128 * 4;
-};
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-}
-
-// barrier among the softmax warps only (the producer and MMA warps never join it)
-template <int kThreads>
-__device__ __forceinline__ void softmax_sync() {
-    asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
 }
 
 struct AttnParams {
@@ -73,34 +69,74 @@ struct AttnParams {
     int batch, newLen, totalLen, numHeads;
     int64_t ldO;
     float scaleLog2;
-    int oldLen, causal, numQTiles;
+    int oldLen, causal, numQBlocks;
     int headsPerGroup;  // (batch, head) pairs whose K + V are kept in L2 together
+    int totalItems;
 };
 
-template <int kParts>
-__global__ void __launch_bounds__(AttnCfg<kParts>::kThreads, 1)
+struct Item {
+    int b, h, q0;
+    int nKv[2];   // key tiles side A / side B visits (0: the side has no query row)
+    int n;        // max of the two
+};
+
+__device__ __forceinline__ int keyTiles(const AttnParams& p, int firstRow) {
+    if (firstRow >= p.newLen) return 0;
+    int lastKey = p.totalLen - 1;
+    if (p.causal) lastKey = min(lastKey, p.oldLen + firstRow + kBM - 1);
+    return lastKey / kBN + 1;
+}
+
+// Item order: (batch, head) pairs are taken in groups whose K and V fit in L2 together; inside a group the
+// heaviest query blocks (most key tiles) come first. All query blocks of a head therefore run close in time and
+// K/V come from DRAM once.
+__device__ __forceinline__ Item decodeItem(const AttnParams& p, int item) {
+    const int bhCount = p.batch * p.numHeads;
+    const int perGroup = p.headsPerGroup * p.numQBlocks;
+    const int fullGroups = bhCount / p.headsPerGroup;
+    int group = item / perGroup;
+    int rem = item - group * perGroup;
+    int width = p.headsPerGroup;
+    if (group >= fullGroups) {
+        group = fullGroups;
+        rem = item - fullGroups * perGroup;
+        width = bhCount - fullGroups * p.headsPerGroup;
+    }
+    const int qb = p.numQBlocks - 1 - rem / width;
+    const int bh = group * p.headsPerGroup + rem % width;
+    Item it;
+    it.b = bh / p.numHeads;
+    it.h = bh % p.numHeads;
+    it.q0 = qb * kItemRows;
+    it.nKv[0] = keyTiles(p, it.q0);
+    it.nKv[1] = keyTiles(p, it.q0 + kBM);
+    it.n = max(it.nKv[0], it.nKv[1]);
+    return it;
+}
+
+// The k-th item of this CTA, or a value >= totalItems when it has none left. Rounds alternate direction
+// (CTA c takes position c in even rounds and grid-1-c in odd ones): with items sorted heaviest first, a CTA
+// that got a heavier item in one round gets a lighter one in the next.
+__device__ __forceinline__ int itemAt(uint32_t k) {
+    const int pos = (k & 1u) ? static_cast<int>(gridDim.x - 1u - blockIdx.x) : static_cast<int>(blockIdx.x);
+    return static_cast<int>(k * gridDim.x) + pos;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
 attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_constant__ CUtensorMap tmapK,
                   const __grid_constant__ CUtensorMap tmapV, AttnParams p, int* status) {
-    using Cfg = AttnCfg<kParts>;
-    constexpr int kCols = Cfg::kCols;
-    constexpr int kChunks = kCols / 32;  // 32-column TMEM accesses per thread
-    constexpr int kProducerWarp = Cfg::kSoftmaxWarps;
-    constexpr int kMmaWarp = Cfg::kSoftmaxWarps + 1;
-
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOff);
-    uint64_t* qFull = bars;            // [1]
-    uint64_t* kvFull = bars + 1;       // [4]
-    uint64_t* kvEmpty = bars + 5;      // [4]
-    uint64_t* sFull = bars + 9;        // [2]
-    uint64_t* sFree = bars + 11;       // [2]
-    uint64_t* pFull = bars + 13;       // [2]
-    uint64_t* oFull = bars + 15;       // [2]
-    uint64_t* oFree = bars + 17;       // [2]
-    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 19);
+    uint64_t* qFull = bars;            // [2 buffers]
+    uint64_t* qEmpty = bars + 2;       // [2]
+    uint64_t* kvFull = bars + 4;       // [3 slots]
+    uint64_t* kvEmpty = bars + 7;      // [3]
+    uint64_t* sFull = bars + 10;       // [2 sides]
+    uint64_t* pFull = bars + 12;       // [2]
+    uint64_t* oFull = bars + 14;       // [2]
+    uint64_t* oFree = bars + 16;       // [2]
+    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 18);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
-    volatile int* softmaxStop = abortFlag + 1;  // agreed on at the softmax barrier so all softmax warps leave together
-    float* xchg = reinterpret_cast<float*>(smem + kXchgOff);
 
     // The swizzled tiles need a 1024-byte aligned base; refuse to run otherwise (uniform across the CTA).
     if ((smem_u32(smem) & 1023u) != 0u) {
@@ -111,44 +147,20 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    // Launch order: (batch, head) pairs are taken in groups whose K and V fit in L2 together; inside a group the
-    // heaviest query tiles (most key tiles) go first. All query tiles of a head therefore run close in time and
-    // K/V come from DRAM once.
-    const int bhCount = p.batch * p.numHeads;
-    const int perGroup = p.headsPerGroup * p.numQTiles;
-    const int fullGroups = bhCount / p.headsPerGroup;
-    int group = static_cast<int>(blockIdx.x) / perGroup;
-    int rem = static_cast<int>(blockIdx.x) - group * perGroup;
-    int width = p.headsPerGroup;
-    if (group >= fullGroups) {
-        group = fullGroups;
-        rem = static_cast<int>(blockIdx.x) - fullGroups * perGroup;
-        width = bhCount - fullGroups * p.headsPerGroup;
-    }
-    const int qt = p.numQTiles - 1 - rem / width;
-    const int bh = group * p.headsPerGroup + rem % width;
-    const int b = bh / p.numHeads;
-    const int h = bh % p.numHeads;
-    const int q0 = qt * kBM;
-    int lastKey = p.totalLen - 1;
-    if (p.causal) lastKey = min(lastKey, p.oldLen + q0 + kBM - 1);
-    const int nKv = lastKey / kBN + 1;
-
     if (threadIdx.x == 0) {
-        mbar_init(qFull, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&qFull[i], 1);
+            mbar_init(&qEmpty[i], 1);
+            mbar_init(&sFull[i], 1);
+            mbar_init(&pFull[i], 4);   // one arrival per softmax warp of the side
+            mbar_init(&oFull[i], 1);
+            mbar_init(&oFree[i], 4);
+        }
         for (int s = 0; s < kKvSlots; ++s) {
             mbar_init(&kvFull[s], 1);
             mbar_init(&kvEmpty[s], 1);
         }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&sFull[i], 1);
-            mbar_init(&sFree[i], Cfg::kSoftmaxWarps);
-            mbar_init(&pFull[i], Cfg::kSoftmaxWarps);
-            mbar_init(&oFull[i], 1);
-            mbar_init(&oFree[i], Cfg::kSoftmaxWarps);
-        }
         *abortFlag = 0;
-        *softmaxStop = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmapQ);
         tma_prefetch_desc(&tmapK);
@@ -164,132 +176,211 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
     const uint32_t tmemBase = *tmemSlot;
 
     if (warp == kProducerWarp) {
-        // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            mbar_arrive_expect_tx(qFull, kTileBytes);
-            tma_load_3d(smem + kQOff, &tmapQ, qFull, h * kD, q0, b);
-            tma_load_3d(smem + kQOff + kHalfBytes, &tmapQ, qFull, h * kD + 64, q0, b);
-        }
-        __syncwarp();
-        for (int idx = 0; idx < 2 * nKv; ++idx) {
-            const int slot = idx & (kKvSlots - 1);
-            const uint32_t use = static_cast<uint32_t>(idx / kKvSlots);
-            if (!warp_all(mbar_wait(&kvEmpty[slot], (use & 1u) ^ 1u, abortFlag, status, kDevTimeoutStageEmpty))) break;
+        // ---------------- TMA producer: runs ahead across items ----------------
+        setmaxnreg_dec<kOtherRegs>();
+        uint32_t it = 0;     // items taken by this CTA so far
+        uint32_t idx = 0;    // K/V tiles loaded so far (K of an item's key tile j, then its V)
+        bool alive = true;
+        for (int item = itemAt(0); item < p.totalItems && alive; item = itemAt(++it)) {
+            const Item w = decodeItem(p, item);
+            const int qb = it & 1u;
+            if (!warp_all(mbar_wait(&qEmpty[qb], ((it >> 1) & 1u) ^ 1u, abortFlag, status, kDevTimeoutStageEmpty))) break;
             if (lane == 0) {
-                const int j = idx >> 1;
-                const CUtensorMap* map = (idx & 1) ? &tmapV : &tmapK;
-                uint8_t* dst = smem + kKvOff + slot * kTileBytes;
-                mbar_arrive_expect_tx(&kvFull[slot], kTileBytes);
-                tma_load_3d(dst, map, &kvFull[slot], h * kD, j * kBN, b);
-                tma_load_3d(dst + kHalfBytes, map, &kvFull[slot], h * kD + 64, j * kBN, b);
+                uint8_t* dst = smem + kQOff + qb * 2 * kTileBytes;
+                const int sides = w.nKv[1] > 0 ? 2 : 1;
+                mbar_arrive_expect_tx(&qFull[qb], sides * kTileBytes);
+                for (int s = 0; s < sides; ++s) {
+                    tma_load_3d(dst + s * kTileBytes, &tmapQ, &qFull[qb], w.h * kD, w.q0 + s * kBM, w.b);
+                    tma_load_3d(dst + s * kTileBytes + kHalfBytes, &tmapQ, &qFull[qb], w.h * kD + 64, w.q0 + s * kBM, w.b);
+                }
             }
             __syncwarp();
+            for (int t = 0; t < 2 * w.n; ++t, ++idx) {
+                const int slot = idx % kKvSlots;
+                const uint32_t use = idx / kKvSlots;
+                if (!warp_all(mbar_wait(&kvEmpty[slot], (use & 1u) ^ 1u, abortFlag, status, kDevTimeoutStageEmpty))) {
+                    alive = false;
+                    break;
+                }
+                if (lane == 0) {
+                    const int j = t >> 1;
+                    const CUtensorMap* map = (t & 1) ? &tmapV : &tmapK;
+                    uint8_t* dst = smem + kKvOff + slot * kTileBytes;
+                    mbar_arrive_expect_tx(&kvFull[slot], kTileBytes);
+                    tma_load_3d(dst, map, &kvFull[slot], w.h * kD, j * kBN, w.b);
+                    tma_load_3d(dst + kHalfBytes, map, &kvFull[slot], w.h * kD + 64, j * kBN, w.b);
+                }
+                __syncwarp();
+            }
         }
     } else if (warp == kMmaWarp) {
         // ---------------- MMA issuer ----------------
-        const uint32_t qAddr = smem_u32(smem + kQOff);
+        setmaxnreg_dec<kOtherRegs>();
         const uint32_t kvAddr = smem_u32(smem + kKvOff);
-        auto issueQK = [&](int j) -> bool {  // S[j&1] = Q K(j)^T
-            const int idx = 2 * j;
-            const int slot = idx & (kKvSlots - 1);
-            const uint32_t use = static_cast<uint32_t>(idx / kKvSlots);
-            const uint32_t sUse = static_cast<uint32_t>(j >> 1);
-            if (!warp_all(mbar_wait(&kvFull[slot], use & 1u, abortFlag, status, kDevTimeoutTmaFull))) return false;
-            // the buffer's previous scores were read and replaced by P, and the P V that reads them was issued
-            // before this point (tensor-core operations of one thread complete in issue order)
-            if (!warp_all(mbar_wait(&sFree[j & 1], (sUse & 1u) ^ 1u, abortFlag, status, kDevTimeoutAccEmpty))) return false;
+        uint32_t tilesDone[2] = {0u, 0u};   // P V products issued per side (phase of pFull / oFull)
+        uint32_t itemsDone[2] = {0u, 0u};   // items whose output the side's softmax warps have taken (phase of oFree)
+
+        auto waitKv = [&](uint32_t idx) -> bool {
+            return warp_all(mbar_wait(&kvFull[idx % kKvSlots], (idx / kKvSlots) & 1u, abortFlag, status, kDevTimeoutTmaFull));
+        };
+        // S_side = Q_side K^T for the key tile in ring entry kIdx
+        auto issueQK = [&](int side, uint32_t itemNo, uint32_t kIdx) {
             tc_fence_after();
             if (lane == 0) {
-                const uint32_t kAddr = kvAddr + slot * kTileBytes;
-                const uint32_t dS = tmemBase + static_cast<uint32_t>((j & 1) * kBN);
+                const uint32_t qAddr = smem_u32(smem + kQOff + ((itemNo & 1u) * 2 + side) * kTileBytes);
+                const uint32_t kAddr = kvAddr + (kIdx % kKvSlots) * kTileBytes;
+                const uint32_t dS = tmemBase + static_cast<uint32_t>(side * kBN);
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
                     umma_f16(dS, make_smem_desc_sw128(qAddr + off, 0, 1024), make_smem_desc_sw128(kAddr + off, 0, 1024),
                              kIdescQK, kk > 0 ? 1u : 0u);
                 }
-                umma_commit(&kvEmpty[slot]);
-                umma_commit(&sFull[j & 1]);
+                umma_commit(&sFull[side]);
             }
             __syncwarp();
-            return true;
         };
-        bool alive = warp_all(mbar_wait(qFull, 0, abortFlag, status, kDevTimeoutTmaFull));
-        if (alive) alive = issueQK(0);
-        for (int j = 0; j < nKv && alive; ++j) {
-            if (j + 1 < nKv) {
-                if (!issueQK(j + 1)) break;
+        // O_side (+)= P_side V for the key tile whose V is ring entry vIdx; `first` starts a new item's sum
+        auto issuePV = [&](int side, uint32_t vIdx, bool first) -> bool {
+            if (!warp_all(mbar_wait(&pFull[side], tilesDone[side] & 1u, abortFlag, status, kDevTimeoutSoftmax))) return false;
+            if (first) {
+                // the previous item's output must have left tensor memory
+                if (!warp_all(mbar_wait(&oFree[side], (itemsDone[side] & 1u) ^ 1u, abortFlag, status, kDevTimeoutAccEmpty)))
+                    return false;
+                ++itemsDone[side];
             }
-            const int idx = 2 * j + 1;
-            const int slot = idx & (kKvSlots - 1);
-            const uint32_t use = static_cast<uint32_t>(idx / kKvSlots);
-            const uint32_t bufUse = static_cast<uint32_t>(j >> 1);
-            if (!warp_all(mbar_wait(&pFull[j & 1], bufUse & 1u, abortFlag, status, kDevTimeoutSoftmax))) break;
-            if (!warp_all(mbar_wait(&kvFull[slot], use & 1u, abortFlag, status, kDevTimeoutTmaFull))) break;
-            if (!warp_all(mbar_wait(&oFree[j & 1], (bufUse & 1u) ^ 1u, abortFlag, status, kDevTimeoutAccEmpty))) break;
             tc_fence_after();
             if (lane == 0) {
-                const uint32_t vAddr = kvAddr + slot * kTileBytes;
-                const uint32_t pTmem = tmemBase + static_cast<uint32_t>((j & 1) * kBN);  // P sits where S was
-                const uint32_t dO = tmemBase + 256u + static_cast<uint32_t>((j & 1) * kD);
+                const uint32_t vAddr = kvAddr + (vIdx % kKvSlots) * kTileBytes;
+                const uint32_t pTmem = tmemBase + static_cast<uint32_t>(side * kBN);  // P sits where S was
+                const uint32_t dO = tmemBase + 256u + static_cast<uint32_t>(side * kD);
 #pragma unroll
                 for (int kk = 0; kk < kBN / 16; ++kk) {
                     // P from tensor memory: 16 keys = 8 packed columns per step. V: keys are rows (MN-major B):
                     // 8-key groups 1024 B apart, the two 64-wide halves of head_dim one half-tile apart.
                     umma_f16_ts(dO, pTmem + static_cast<uint32_t>(kk * 8),
-                                make_smem_desc_sw128(vAddr + kk * 2048, kHalfBytes, 1024), kIdescPV, kk > 0 ? 1u : 0u);
+                                make_smem_desc_sw128(vAddr + kk * 2048, kHalfBytes, 1024), kIdescPV,
+                                (kk > 0 || !first) ? 1u : 0u);
                 }
-                umma_commit(&kvEmpty[slot]);
-                umma_commit(&oFull[j & 1]);
+                umma_commit(&oFull[side]);
             }
             __syncwarp();
-        }
-    } else {
-        // ---------------- softmax + accumulation: kParts threads per query row ----------------
-        const int quarter = warp & 3;
-        const int part = warp >> 2;                 // which kCols key columns / output columns
-        const int r = quarter * 32 + lane;          // query row inside the tile
-        const uint32_t laneBase = static_cast<uint32_t>(quarter * 32) << 16;
-        const int qPos = p.oldLen + q0 + r;
-        const int keyLimit = p.causal ? min(qPos, p.totalLen - 1) : p.totalLen - 1;  // last visible key
-        float mRun = -INFINITY, lRun = 0.0f, alphaPrev = 0.0f;
-        float oAcc[kCols];
+            ++tilesDone[side];
+            return true;
+        };
+        auto waitQ = [&](uint32_t itemNo) -> bool {
+            return warp_all(mbar_wait(&qFull[itemNo & 1u], (itemNo >> 1) & 1u, abortFlag, status, kDevTimeoutTmaFull));
+        };
+        auto commitTo = [&](uint64_t* bar) {
+            if (lane == 0) umma_commit(bar);
+            __syncwarp();
+        };
+
+        int item = itemAt(0);
+        if (item < p.totalItems) {
+            uint32_t it = 0;
+            uint32_t base = 0;   // ring entry of this item's K(0); K(j) is base + 2j, V(j) is base + 2j + 1
+            Item w = decodeItem(p, item);
+            bool alive = waitQ(0) && waitKv(0);
+            if (alive) {
+                issueQK(0, 0, 0);
+                if (w.nKv[1] > 0) issueQK(1, 0, 0);
+                commitTo(&kvEmpty[0]);
+                if (w.n == 1) commitTo(&qEmpty[0]);
+            }
+            while (alive) {
+                // the item that follows, if any: its first scores are issued under this item's last key tile
+                const int nextItem = itemAt(it + 1);
+                const bool haveNextItem = nextItem < p.totalItems;
+                Item nw = w;
+                if (haveNextItem) nw = decodeItem(p, nextItem);
+                const uint32_t nextBase = base + 2u * static_cast<uint32_t>(w.n);
+
+                for (int j = 0; j < w.n && alive; ++j) {
+                    const uint32_t vIdx = base + 2u * j + 1u;
+                    // the key tile whose scores are issued in this round
+                    const bool inItem = j + 1 < w.n;
+                    const bool haveNext = inItem || haveNextItem;
+                    const uint32_t kIdx = inItem ? base + 2u * (j + 1) : nextBase;
+                    const uint32_t kItemNo = inItem ? it : it + 1;
+                    const Item& kw = inItem ? w : nw;
+                    const int kj = inItem ? j + 1 : 0;
+                    bool kReady = false;
+                    if (!waitKv(vIdx)) { alive = false; break; }
 #pragma unroll
-        for (int i = 0; i < kCols; ++i) oAcc[i] = 0.0f;
+                    for (int side = 0; side < 2; ++side) {
+                        if (j < w.nKv[side]) {
+                            if (!issuePV(side, vIdx, j == 0)) { alive = false; break; }
+                        }
+                        if (haveNext && kj < kw.nKv[side]) {
+                            if (!kReady) {
+                                if ((!inItem && !waitQ(kItemNo)) || !waitKv(kIdx)) { alive = false; break; }
+                                kReady = true;
+                            }
+                            issueQK(side, kItemNo, kIdx);
+                        }
+                    }
+                    if (!alive) break;
+                    commitTo(&kvEmpty[vIdx % kKvSlots]);
+                    if (haveNext) {
+                        commitTo(&kvEmpty[kIdx % kKvSlots]);
+                        if (kj == kw.n - 1) commitTo(&qEmpty[kItemNo & 1u]);   // those were the item's last scores
+                    }
+                }
+                if (!alive || !haveNextItem) break;
+                item = nextItem;
+                w = nw;
+                base = nextBase;
+                ++it;
+            }
+        }
+    } else if (warp < kSoftmaxWarps) {
+        // ---------------- softmax: one thread per query row ----------------
+        setmaxnreg_inc<kSoftmaxRegs>();
+        const int side = warp >> 2;
+        const int r = (warp & 3) * 32 + lane;       // query row inside the side's tile
+        const uint32_t laneBase = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t sAddr = tmemBase + laneBase + static_cast<uint32_t>(side * kBN);
+        const uint32_t oAddr = tmemBase + laneBase + 256u + static_cast<uint32_t>(side * kD);
+        uint32_t tiles = 0;                         // key tiles this side has processed (phase of sFull / oFull)
         bool alive = true;
 
-        for (int j = 0; j < nKv; ++j) {
-            const int buf = j & 1;
-            const uint32_t use = static_cast<uint32_t>(j >> 1);
-            // An abandoned wait is published and acted on after the next softmax barrier, where all softmax warps
-            // see the same flag: they leave the loop in the same iteration and execute the same barrier count.
-            if (alive && !warp_all(mbar_wait(&sFull[buf], use & 1u, abortFlag, status, kDevTimeoutAccFull))) {
-                alive = false;
-                *softmaxStop = 1;
-            }
-            const uint32_t sAddr = tmemBase + laneBase + static_cast<uint32_t>(buf * kBN + part * kCols);
-            const int key0 = j * kBN + part * kCols;
-            const bool needMask = (p.causal && j * kBN + kBN - 1 > p.oldLen + q0) || (j * kBN + kBN > p.totalLen);
+        for (uint32_t it = 0; alive; ++it) {
+            const int item = itemAt(it);
+            if (item >= p.totalItems) break;
+            const Item w = decodeItem(p, item);
+            const int nKv = w.nKv[side];
+            if (nKv == 0) continue;
+            const int row = w.q0 + side * kBM + r;
+            const int qPos = p.oldLen + row;
+            const int keyLimit = p.causal ? min(qPos, p.totalLen - 1) : p.totalLen - 1;  // last visible key
+            const int firstRowPos = p.oldLen + w.q0 + side * kBM;
+            float mRef = -INFINITY;    // exponent reference (log2 units); trails the true maximum by at most the slack
+            float mTrue = -INFINITY;   // running maximum
+            float lRun = 0.0f;         // row sum relative to mRef
 
-            // this thread's scores, read once
-            uint32_t s[kChunks][32];
-            float mx = -INFINITY;
-            if (alive) {
+            for (int j = 0; j < nKv; ++j, ++tiles) {
+                if (!warp_all(mbar_wait(&sFull[side], tiles & 1u, abortFlag, status, kDevTimeoutAccFull))) {
+                    alive = false;
+                    break;
+                }
                 tc_fence_after();
+                uint32_t s[4][32];
 #pragma unroll
-                for (int c = 0; c < kChunks; ++c) tmem_ld_32x32(sAddr + static_cast<uint32_t>(c * 32), s[c]);
+                for (int c = 0; c < 4; ++c) tmem_ld_32x32(sAddr + static_cast<uint32_t>(c * 32), s[c]);
                 tmem_ld_wait();
+                const bool needMask = (p.causal && j * kBN + kBN - 1 > firstRowPos) || (j * kBN + kBN > p.totalLen);
                 if (needMask) {
 #pragma unroll
-                    for (int c = 0; c < kChunks; ++c)
+                    for (int c = 0; c < 4; ++c)
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            if (key0 + c * 32 + i > keyLimit) s[c][i] = 0xFF800000u;  // -inf
+                            if (j * kBN + c * 32 + i > keyLimit) s[c][i] = 0xFF800000u;  // -inf
                 }
                 // four independent chains instead of one long dependency
                 float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-                for (int c = 0; c < kChunks; ++c)
+                for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
                         m0 = fmaxf(m0, __uint_as_float(s[c][i]));
@@ -297,142 +388,118 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                         m2 = fmaxf(m2, __uint_as_float(s[c][i + 2]));
                         m3 = fmaxf(m3, __uint_as_float(s[c][i + 3]));
                     }
-                mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-            }
-            float* slots = xchg + buf * kParts * 128 + r;   // [part][row]
-            slots[part * 128] = mx;
-            softmax_sync<Cfg::kSoftmaxThreads>();
-            if (*softmaxStop != 0) {
-                alive = false;
-                break;
-            }
-#pragma unroll
-            for (int q = 0; q < kParts; ++q) mx = fmaxf(mx, slots[q * 128]);
-            const float mNew = fmaxf(mRun, mx * p.scaleLog2);
-            // a row with no visible key yet keeps everything at zero instead of producing NaN
-            const float mUse = (mNew == -INFINITY) ? 0.0f : mNew;
-            const float alpha = ex2(mRun - mUse);
+                const float mTile = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * p.scaleLog2;
+                mTrue = fmaxf(mTrue, mTile);
 
-            // packed fp32 pairs: one FMA / ADD instruction serves two scores
-            const uint64_t scale2 = pack_f32x2(p.scaleLog2, p.scaleLog2);
-            const uint64_t negMax2 = pack_f32x2(-mUse, -mUse);
-            uint64_t sumA = pack_f32x2(0.0f, 0.0f), sumB = sumA;
-#pragma unroll
-            for (int c = 0; c < kChunks; ++c) {
-                uint32_t packed[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    // masked entries hold -inf: ex2(-inf) = 0
-                    const uint64_t arg = fma_f32x2(pack_f32x2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])),
-                                                   scale2, negMax2);
-                    float a0, a1;
-                    unpack_f32x2(arg, a0, a1);
-                    const float p0 = ex2(a0);
-                    const float p1 = ex2(a1);
-                    if ((i & 2) == 0) sumA = add_f32x2(sumA, pack_f32x2(p0, p1));
-                    else sumB = add_f32x2(sumB, pack_f32x2(p0, p1));
-                    __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-                    packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
-                }
-                // P replaces S in tensor memory: two bf16 keys per 32-bit column, so 128 keys take the first 64
-                // columns of the S buffer and this thread's 32 keys of chunk c take 16 of them
-                tmem_st_32x16(tmemBase + laneBase + static_cast<uint32_t>(buf * kBN + (part * kCols + c * 32) / 2), packed);
-            }
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();               // one arrival per warp: 256 per-thread arrivals on one word serialise
-            if (lane == 0) {
-                mbar_arrive(&pFull[buf]);   // P is in place ...
-                mbar_arrive(&sFree[buf]);   // ... and S has been consumed: the buffer may be overwritten after P V
-            }
-            float sumLo, sumHi;
-            unpack_f32x2(add_f32x2(sumA, sumB), sumLo, sumHi);
-            lRun = lRun * alpha + (sumLo + sumHi);
-
-            // fold the previous tile's P V (relative to the previous maximum) into the accumulator
-            if (j > 0) {
-                const int pb = (j - 1) & 1;
-                const uint32_t pUse = static_cast<uint32_t>((j - 1) >> 1);
-                if (warp_all(mbar_wait(&oFull[pb], pUse & 1u, abortFlag, status, kDevTimeoutAccFull))) {
-                    tc_fence_after();
-                    const uint32_t oAddr = tmemBase + laneBase + 256u + static_cast<uint32_t>(pb * kD + part * kCols);
-                    uint32_t o[kChunks][32];
-#pragma unroll
-                    for (int c = 0; c < kChunks; ++c) tmem_ld_32x32(oAddr + static_cast<uint32_t>(c * 32), o[c]);
-                    tmem_ld_wait();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&oFree[pb]);
-                    const uint64_t alpha2 = pack_f32x2(alphaPrev, alphaPrev);
-#pragma unroll
-                    for (int c = 0; c < kChunks; ++c)
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            unpack_f32x2(fma_f32x2(pack_f32x2(oAcc[c * 32 + i], oAcc[c * 32 + i + 1]), alpha2,
-                                                   pack_f32x2(__uint_as_float(o[c][i]), __uint_as_float(o[c][i + 1]))),
-                                         oAcc[c * 32 + i], oAcc[c * 32 + i + 1]);
-                        }
+                if (j == 0) {
+                    mRef = mTile;
                 } else {
-                    alive = false;
-                    *softmaxStop = 1;
-                }
-            }
-            alphaPrev = alpha;
-            mRun = mNew;
-        }
-
-        // last tile's product, normalisation and store. Every softmax warp takes part in the two barriers
-        // below even after an abandoned wait, so none is left behind.
-        bool haveLast = false;
-        uint32_t o[kChunks][32];
-        if (alive && *softmaxStop == 0) {
-            const int pb = (nKv - 1) & 1;
-            const uint32_t pUse = static_cast<uint32_t>((nKv - 1) >> 1);
-            if (warp_all(mbar_wait(&oFull[pb], pUse & 1u, abortFlag, status, kDevTimeoutAccFull))) {
-                tc_fence_after();
-                const uint32_t oAddr = tmemBase + laneBase + 256u + static_cast<uint32_t>(pb * kD + part * kCols);
-#pragma unroll
-                for (int c = 0; c < kChunks; ++c) tmem_ld_32x32(oAddr + static_cast<uint32_t>(c * 32), o[c]);
-                tmem_ld_wait();
-                haveLast = true;
-            }
-        }
-        softmax_sync<Cfg::kSoftmaxThreads>();  // everyone is done with the maxima of the last tile
-        xchg[part * 128 + r] = lRun;
-        softmax_sync<Cfg::kSoftmaxThreads>();
-        float lTotal = 0.0f;
-#pragma unroll
-        for (int q = 0; q < kParts; ++q) lTotal += xchg[q * 128 + r];
-        if (haveLast) {
-            const float inv = lTotal > 0.0f ? 1.0f / lTotal : 0.0f;
-            const bool rowOk = q0 + r < p.newLen;
-            if (rowOk) {
-                __nv_bfloat16* dst = p.out + (static_cast<int64_t>(b) * p.newLen + q0 + r) * p.ldO +
-                                     static_cast<int64_t>(h) * kD + part * kCols;
-#pragma unroll
-                for (int c = 0; c < kChunks; ++c) {
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int e = g * 8 + 2 * i;
-                            const float a0 = fmaf(oAcc[c * 32 + e], alphaPrev, __uint_as_float(o[c][e])) * inv;
-                            const float a1 = fmaf(oAcc[c * 32 + e + 1], alphaPrev, __uint_as_float(o[c][e + 1])) * inv;
-                            __nv_bfloat162 hh = __floats2bfloat162_rn(a0, a1);
-                            w[i] = *reinterpret_cast<uint32_t*>(&hh);
+                    const bool moved = mTile > mRef + kRescaleSlack;
+                    if (__any_sync(0xFFFFFFFFu, moved)) {
+                        // Rare: bring O and the row sum to the new reference. The previous tile's P V must have
+                        // finished; the next one is issued only after this warp reports P below.
+                        if (!warp_all(mbar_wait(&oFull[side], (tiles - 1u) & 1u, abortFlag, status, kDevTimeoutAccFull))) {
+                            alive = false;
+                            break;
                         }
-                        *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                        tc_fence_after();
+                        const float alpha = moved ? ex2(mRef - mTile) : 1.0f;   // 0 when there was no visible key yet
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t o[32];
+                            tmem_ld_32x32(oAddr + static_cast<uint32_t>(c * 32), o);
+                            tmem_ld_wait();
+                            uint32_t lo[16], hi[16];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                lo[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                                hi[i] = __float_as_uint(__uint_as_float(o[i + 16]) * alpha);
+                            }
+                            tmem_st_32x16(oAddr + static_cast<uint32_t>(c * 32), lo);
+                            tmem_st_32x16(oAddr + static_cast<uint32_t>(c * 32 + 16), hi);
+                        }
+                        tmem_st_wait();
+                        lRun *= alpha;
+                        if (moved) mRef = mTile;
                     }
                 }
-                if (part == 0) {
-                    const int64_t statIdx = (static_cast<int64_t>(b) * p.numHeads + h) * p.newLen + q0 + r;
-                    // statistics in natural-log units of the scaled scores, as the reference reports them
-                    if (p.mOut != nullptr) p.mOut[statIdx] = mRun * 0.69314718056f;
-                    if (p.lOut != nullptr) p.lOut[statIdx] = lTotal;
+                // a row with no visible key yet keeps everything at zero instead of producing NaN
+                const float mUse = (mRef == -INFINITY) ? 0.0f : mRef;
+
+                // packed fp32 pairs: one FMA / ADD instruction serves two scores
+                const uint64_t scale2 = pack_f32x2(p.scaleLog2, p.scaleLog2);
+                const uint64_t negRef2 = pack_f32x2(-mUse, -mUse);
+                uint64_t sumA = pack_f32x2(0.0f, 0.0f), sumB = sumA;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        // masked entries hold -inf: ex2(-inf) = 0
+                        const uint64_t arg = fma_f32x2(
+                            pack_f32x2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), scale2, negRef2);
+                        float a0, a1;
+                        unpack_f32x2(arg, a0, a1);
+                        const float p0 = ex2(a0);
+                        const float p1 = ex2(a1);
+                        if ((i & 2) == 0) sumA = add_f32x2(sumA, pack_f32x2(p0, p1));
+                        else sumB = add_f32x2(sumB, pack_f32x2(p0, p1));
+                        __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+                        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+                    }
+                    // P replaces S in tensor memory: two bf16 keys per 32-bit column, so the 32 keys of chunk c take
+                    // 16 columns and the whole tile the first 64 columns of the S region
+                    tmem_st_32x16(sAddr + static_cast<uint32_t>(c * 16), packed);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();               // one arrival per warp: per-thread arrivals on one word serialise
+                if (lane == 0) mbar_arrive(&pFull[side]);
+                float sumLo, sumHi;
+                unpack_f32x2(add_f32x2(sumA, sumB), sumLo, sumHi);
+                lRun += sumLo + sumHi;
+            }
+            if (!alive) break;
+
+            // the item's output: wait for the last P V, normalise, store, hand the O region back
+            if (!warp_all(mbar_wait(&oFull[side], (tiles - 1u) & 1u, abortFlag, status, kDevTimeoutAccFull))) break;
+            tc_fence_after();
+            const float inv = lRun > 0.0f ? 1.0f / lRun : 0.0f;
+            const bool store = row < p.newLen;
+            __nv_bfloat16* dst = p.out + (static_cast<int64_t>(w.b) * p.newLen + row) * p.ldO + static_cast<int64_t>(w.h) * kD;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t o[32];
+                tmem_ld_32x32(oAddr + static_cast<uint32_t>(c * 32), o);
+                tmem_ld_wait();
+                if (c == 3) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&oFree[side]);
+                }
+                if (store) {
+#pragma unroll
+                    for (int gq = 0; gq < 4; ++gq) {
+                        uint32_t wd[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int e = gq * 8 + 2 * i;
+                            __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
+                            wd[i] = *reinterpret_cast<uint32_t*>(&hh);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c * 32 + gq * 8) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+                    }
                 }
             }
+            if (store) {
+                const int64_t statIdx = (static_cast<int64_t>(w.b) * p.numHeads + w.h) * p.newLen + row;
+                // statistics relative to the true running maximum, in natural-log units of the scaled scores
+                if (p.mOut != nullptr) p.mOut[statIdx] = mTrue * 0.69314718056f;
+                if (p.lOut != nullptr) p.lOut[statIdx] = (mTrue == -INFINITY) ? 0.0f : lRun * ex2(mRef - mTrue);
+            }
         }
+    } else {
+        setmaxnreg_dec<kOtherRegs>();  // idle warps of the last warpgroup
     }
 
     // ---------------- teardown ----------------
@@ -453,26 +520,6 @@ void makeMap(TensorMapStorage* out, const void* base, int64_t dim, int64_t len, 
     uint64_t strides[2] = {static_cast<uint64_t>(ld) * 2, static_cast<uint64_t>(ld) * 2 * static_cast<uint64_t>(len)};
     uint32_t box[3] = {64u, 128u, 1u};
     encodeTensorMap(out, base, 2, 3, dims, strides, box);
-}
-
-// BFB_ATTN_PARTS=2 in the environment selects two softmax threads per row instead of four (A/B measurements).
-int softmaxParts() {
-    static const int v = [] {
-        const char* e = std::getenv("BFB_ATTN_PARTS");
-        return (e != nullptr && std::atoi(e) == 2) ? 2 : 4;
-    }();
-    return v;
-}
-
-template <int kParts>
-void launchAttention(const TensorMapStorage& tq, const TensorMapStorage& tk, const TensorMapStorage& tv,
-                     const AttnParams& p, int64_t grid, int* status, cudaStream_t stream) {
-    using Cfg = AttnCfg<kParts>;
-    auto kernel = attentionTcKernel<kParts>;
-    BFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    kernel<<<static_cast<unsigned>(grid), Cfg::kThreads, Cfg::kSmemBytes, stream>>>(
-        *reinterpret_cast<const CUtensorMap*>(tq.bytes), *reinterpret_cast<const CUtensorMap*>(tk.bytes),
-        *reinterpret_cast<const CUtensorMap*>(tv.bytes), p, status);
 }
 
 }  // namespace
@@ -505,18 +552,22 @@ void attentionTensorCore(const AttentionArgs& a, cudaStream_t stream) {
     p.scaleLog2 = a.scale * 1.4426950408889634f;
     p.oldLen = static_cast<int>(a.oldLen);
     p.causal = a.causal;
-    p.numQTiles = static_cast<int>((a.newLen + kBM - 1) / kBM);
+    p.numQBlocks = static_cast<int>((a.newLen + kItemRows - 1) / kItemRows);
     // K + V of one (batch, head): 2 * total_len * 128 * 2 bytes; keep about 64 MB of them live in the 126 MB L2
     const int64_t kvBytes = 2 * a.totalLen * kD * 2;
     p.headsPerGroup = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(a.batch * a.numHeads, (64ll << 20) / kvBytes)));
-    const int64_t grid = static_cast<int64_t>(p.numQTiles) * a.batch * a.numHeads;
-    require(grid <= 0x7FFFFFFF, "attention: too many query tiles for one launch");
+    const int64_t items = static_cast<int64_t>(p.numQBlocks) * a.batch * a.numHeads;
+    require(items <= 0x7FFFFFFF, "attention: too many query blocks for one launch");
+    p.totalItems = static_cast<int>(items);
+    const int grid = static_cast<int>(std::min<int64_t>(items, smCount()));
     // visible (query, key) pairs per (batch, head): causal rows see old_len + i + 1 keys
     const double nl = static_cast<double>(a.newLen), tl = static_cast<double>(a.totalLen);
     const double pairs = a.causal ? nl * static_cast<double>(a.oldLen) + nl * (nl + 1.0) / 2.0 : nl * tl;
     ProfileScope prof(kProfAttnTc, stream, 4.0 * kD * pairs * static_cast<double>(a.batch * a.numHeads));
-    if (softmaxParts() == 2) launchAttention<2>(tq, tk, tv, p, grid, a.dStatus, stream);
-    else launchAttention<4>(tq, tk, tv, p, grid, a.dStatus, stream);
+    BFB_CUDA(cudaFuncSetAttribute(attentionTcKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    attentionTcKernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, stream>>>(
+        *reinterpret_cast<const CUtensorMap*>(tq.bytes), *reinterpret_cast<const CUtensorMap*>(tk.bytes),
+        *reinterpret_cast<const CUtensorMap*>(tv.bytes), p, a.dStatus);
     BFB_LAUNCH_CHECK();
     noteLaunch();
 }
