@@ -391,8 +391,12 @@ def main():
         torch.cuda.synchronize()
         launch.barrier()
         e2e_ms = launch.max_over_ranks(s2.elapsed_time(e2), dev if world > 1 else None) / e2e_steps
+        # bytes the call itself booked for its copies: under storage bf16 part of the logits crosses the link as
+        # 2-byte bf16 and is widened to the caller's fp32 buffer by host threads
+        h2d_bytes, d2h_bytes = bfb.host_transfer_bytes()
         e2e = {"value": world * tokens_per_step / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": int(ids.nbytes), "d2h_bytes_per_step": out_elems * 4, "steps": e2e_steps,
+               "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+               "result_bytes_per_step": out_elems * 4, "steps": e2e_steps,
                "api": "bfb_model_forward_host (fromHost -> Model::forward -> toHost), pinned host buffers"}
         del h_out
 

@@ -103,6 +103,7 @@ SIGNATURES = {
     "bfb_model_forward": (_I32, [_P, _P, C.POINTER(_I64), _I32, _I32, C.POINTER(_P), C.POINTER(_I64),
                                  C.POINTER(_I32), _P]),
     "bfb_model_forward_host": (_I32, [_P, _P, C.POINTER(_I64), _I32, _P, C.POINTER(_I64), C.POINTER(_I32)]),
+    "bfb_host_transfer_bytes": (_I32, [C.POINTER(_I64), C.POINTER(_I64)]),
     "bfb_launch_count": (_I64, [_I32]),
     "bfb_profile_enable": (_I32, [_I32]),
     "bfb_profile_reset": (_I32, []),
@@ -344,6 +345,13 @@ class Model:
         buf.ptr = out_ptr.value or 0
         buf.nbytes = int(np.prod(oshape)) * 4
         return buf, oshape
+
+
+def host_transfer_bytes():
+    """(host-to-device, device-to-host) bytes of this thread's latest Model.forward_host."""
+    a, b = _I64(0), _I64(0)
+    check(lib().bfb_host_transfer_bytes(C.byref(a), C.byref(b)))
+    return int(a.value), int(b.value)
 
 
 def synthetic_input(ops: Sequence[dict], input_shape: Sequence[int], batch: int, seed: int = 42) -> np.ndarray:

@@ -32,6 +32,7 @@ SOURCES = [
     "host/ops.cpp",
     "host/model.cpp",
     "host/tp.cpp",
+    "host/widen.cpp",
 ]
 
 NVCC_FLAGS = [

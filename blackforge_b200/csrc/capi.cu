@@ -1,5 +1,7 @@
 // extern "C" surface declared in include/bfb200.h: argument checks, exception -> status mapping,
 // and nothing else. All work happens in the kernel layer (kernels.hpp) and the host layer (host/).
+#include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -8,6 +10,7 @@
 #include "common.cuh"
 #include "host/bfb200.hpp"
 #include "host/tp.hpp"
+#include "host/widen.hpp"
 #include "kernels.hpp"
 #include "pool.hpp"
 
@@ -397,10 +400,59 @@ bfb_status bfb_model_forward(bfb_model* model, const float* d_input, const int64
 }
 
 namespace {
+// slice size of the bf16 result path for small batches: a quarter of the batch
+std::size_t step4(std::size_t batch) { return (batch + 3) / 4; }
+
+// Host-link bytes of the calling thread's latest host-buffer forward.
+struct HostTransfer {
+    int64_t h2d = 0;
+    int64_t d2h = 0;
+};
+HostTransfer& hostTransfer() {
+    thread_local HostTransfer t;
+    return t;
+}
+
+// Share (percent) of the result slices that the host-buffer path moves as bf16 and widens on host threads when
+// the result is bf16-exact; the rest is copied as fp32. The 2-byte way halves the link time but costs host
+// cores and host memory bandwidth (the fp32 words are written by the CPU on top of the incoming copy). Measured
+// on a 16-core host with a PCIe 5 x16 link, 2 G logits per call: all slices narrow 138 ms, three quarters
+// 148 ms, half 158 ms, none 168-182 ms. So: everything with 12 or more host threads, half with 6 or more, none
+// below (plain fp32 copies). BFB_HOST_NARROW_PCT overrides (0..100).
+int narrowSharePercent() {
+    if (const char* e = std::getenv("BFB_HOST_NARROW_PCT")) return std::max(0, std::min(100, std::atoi(e)));
+    const int threads = bfb200::defaultWidenThreads();
+    return threads >= 12 ? 100 : (threads >= 6 ? 50 : 0);
+}
+
 // Two non-blocking streams per device for the host-buffer path: compute and device-to-host copies.
 struct HostPathStreams {
     cudaStream_t compute = nullptr;
     cudaStream_t copy = nullptr;
+    // bf16 result path: a ring of device slices, pinned host slices and their copy-finished events, kept between
+    // calls (pinning host memory is slow) and grown when a larger slice comes along. Four slots: a slot is busy
+    // from the start of its slice's compute to the end of its widening, about three slice times.
+    static constexpr int kSlots = 4;
+    void* dev16[kSlots] = {};
+    void* pinned16[kSlots] = {};
+    cudaEvent_t copied[kSlots] = {};
+    std::size_t sliceBytes = 0;
+
+    void ensureStaging(std::size_t bytes) {
+        if (bytes <= sliceBytes) return;
+        for (int i = 0; i < kSlots; ++i) {
+            if (dev16[i] != nullptr) BFB_CUDA(cudaFree(dev16[i]));
+            if (pinned16[i] != nullptr) BFB_CUDA(cudaFreeHost(pinned16[i]));
+            dev16[i] = pinned16[i] = nullptr;
+        }
+        sliceBytes = 0;
+        for (int i = 0; i < kSlots; ++i) {
+            BFB_CUDA(cudaMalloc(&dev16[i], bytes));
+            BFB_CUDA(cudaMallocHost(&pinned16[i], bytes));
+            if (copied[i] == nullptr) BFB_CUDA(cudaEventCreateWithFlags(&copied[i], cudaEventDisableTiming));
+        }
+        sliceBytes = bytes;
+    }
 };
 HostPathStreams& hostPathStreams() {
     static std::mutex mu;
@@ -436,6 +488,8 @@ bfb_status bfb_model_forward_host(bfb_model* model, const float* h_input, const 
         for (std::size_t d : dims) count *= d;
         bfb200::DeviceTensor in(dims);
         if (count > 0) BFB_CUDA(cudaMemcpy(in.data(), h_input, count * sizeof(float), cudaMemcpyHostToDevice));
+        hostTransfer().h2d = static_cast<int64_t>(count * sizeof(float));
+        hostTransfer().d2h = 0;
 
         const std::size_t batch = dims[0];
         const std::size_t slices = (rank == 2 && batch >= 8) ? 4 : 1;
@@ -443,6 +497,7 @@ bfb_status bfb_model_forward_host(bfb_model* model, const float* h_input, const 
             bfb200::DeviceTensor result = model->model->forward(in, false, nullptr);
             if (result.elementCount() > 0) {
                 BFB_CUDA(cudaMemcpy(h_out, result.data(), result.elementCount() * sizeof(float), cudaMemcpyDeviceToHost));
+                hostTransfer().d2h = static_cast<int64_t>(result.elementCount() * sizeof(float));
             }
             return;
         }
@@ -451,6 +506,62 @@ bfb_status bfb_model_forward_host(bfb_model* model, const float* h_input, const 
         std::size_t outCount = 1;
         for (std::size_t d : outDims) outCount *= d;
         const std::size_t perSeqOut = outCount / batch;
+        const int narrowPct = model->model->resultIsBf16Exact() ? narrowSharePercent() : 0;
+        if (narrowPct > 0) {
+            // Under `storage bf16` the logits are bf16 numbers. A share of the slices crosses PCIe as 2-byte values
+            // and is widened to the caller's fp32 words by host threads; the rest is copied as fp32 straight into
+            // the caller's buffer. The first kind costs half the PCIe time but host memory bandwidth and cores,
+            // the second only PCIe time, so mixing them keeps both busy. Every slice's copy overlaps the next
+            // slice's compute. The result is bit-identical to copying the fp32 result whole.
+            const std::size_t seqs = batch >= 16 ? std::max<std::size_t>(1, batch / 8) : step4(batch);
+            st.ensureStaging(seqs * perSeqOut * 2);
+            int dev = 0;
+            BFB_CUDA(cudaGetDevice(&dev));
+            bfb200::WidenQueue queue(dev, bfb200::defaultWidenThreads());
+            std::vector<bfb200::DeviceTensor> wide;  // fp32 slices, kept alive until their copies have finished
+            std::size_t slice = 0, narrowCount = 0;
+            std::size_t jobOfSlot[HostPathStreams::kSlots] = {};
+            bool slotUsed[HostPathStreams::kSlots] = {};
+            for (std::size_t b0 = 0; b0 < batch; b0 += seqs, ++slice) {
+                const std::size_t nb = std::min(seqs, batch - b0);
+                // slice s goes the 2-byte way when the running share falls behind the target
+                const bool narrow = (slice + 1) * static_cast<std::size_t>(narrowPct) / 100 > narrowCount;
+                std::vector<std::size_t> sliceDims = dims;
+                sliceDims[0] = nb;
+                bfb200::DeviceTensor view = bfb200::DeviceTensor::borrow(in.data() + b0 * perSeqIn, sliceDims);
+                const int k = static_cast<int>(narrowCount % HostPathStreams::kSlots);
+                try {
+                    // both calls return after their own work on the compute stream is complete (status read-back)
+                    if (narrow) {
+                        if (slotUsed[k]) queue.wait(jobOfSlot[k]);  // the slot has been copied out and widened
+                        model->model->forwardBf16(view, st.dev16[k], false, st.compute);
+                    } else {
+                        wide.push_back(model->model->forward(view, false, st.compute));
+                    }
+                } catch (...) {
+                    view.releaseOwnership();
+                    cudaStreamSynchronize(st.copy);
+                    throw;
+                }
+                view.releaseOwnership();
+                if (narrow) {
+                    BFB_CUDA(cudaMemcpyAsync(st.pinned16[k], st.dev16[k], nb * perSeqOut * 2, cudaMemcpyDeviceToHost, st.copy));
+                    BFB_CUDA(cudaEventRecord(st.copied[k], st.copy));
+                    jobOfSlot[k] = queue.submit(st.copied[k], static_cast<const std::uint16_t*>(st.pinned16[k]),
+                                                h_out + b0 * perSeqOut, nb * perSeqOut);
+                    slotUsed[k] = true;
+                    ++narrowCount;
+                    hostTransfer().d2h += static_cast<int64_t>(nb * perSeqOut * 2);
+                } else {
+                    BFB_CUDA(cudaMemcpyAsync(h_out + b0 * perSeqOut, wide.back().data(), nb * perSeqOut * sizeof(float),
+                                             cudaMemcpyDeviceToHost, st.copy));
+                    hostTransfer().d2h += static_cast<int64_t>(nb * perSeqOut * sizeof(float));
+                }
+            }
+            queue.waitAll();
+            BFB_CUDA(cudaStreamSynchronize(st.copy));
+            return;
+        }
         std::vector<bfb200::DeviceTensor> results;  // kept alive until their copies have finished
         results.reserve(slices);
         const std::size_t step = (batch + slices - 1) / slices;
@@ -472,8 +583,17 @@ bfb_status bfb_model_forward_host(bfb_model* model, const float* h_input, const 
             BFB_CUDA(cudaStreamSynchronize(nullptr));
             BFB_CUDA(cudaMemcpyAsync(h_out + b0 * perSeqOut, results.back().data(), nb * perSeqOut * sizeof(float),
                                      cudaMemcpyDeviceToHost, st.copy));
+            hostTransfer().d2h += static_cast<int64_t>(nb * perSeqOut * sizeof(float));
         }
         BFB_CUDA(cudaStreamSynchronize(st.copy));
+    });
+}
+
+bfb_status bfb_host_transfer_bytes(int64_t* h2d_bytes, int64_t* d2h_bytes) {
+    return guarded([&] {
+        require(h2d_bytes != nullptr && d2h_bytes != nullptr, "host_transfer_bytes: null argument");
+        *h2d_bytes = hostTransfer().h2d;
+        *d2h_bytes = hostTransfer().d2h;
     });
 }
 

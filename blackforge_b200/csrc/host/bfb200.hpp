@@ -138,6 +138,11 @@ public:
     void setTensorParallel(int rank, int world);
 
     DeviceTensor forward(const DeviceTensor& input, bool inputRangeTrusted = false, void* stream = nullptr);
+    // Under `storage bf16` every value of forward()'s result is a bf16 number held in an fp32 word. When the
+    // pipeline runs from an embedding to a final linear, forwardBf16 writes those same numbers as 2-byte bf16
+    // into `deviceOut16` (product(outputShape) elements) instead: half the bytes for a caller that moves them on.
+    [[nodiscard]] bool resultIsBf16Exact() const;
+    void forwardBf16(const DeviceTensor& input, void* deviceOut16, bool inputRangeTrusted = false, void* stream = nullptr);
 
     [[nodiscard]] std::vector<Parameter*> parameters();
     [[nodiscard]] const std::string& name() const { return name_; }

@@ -182,7 +182,8 @@ struct Model::Impl {
     void getParam(std::size_t index, float* hostFull);
     void prepare(cudaStream_t stream);
     DeviceTensor forwardFp32(const DeviceTensor& input, bool trusted);
-    DeviceTensor forwardPlanned(const DeviceTensor& input, bool trusted, cudaStream_t stream);
+    // out16 != nullptr: the final linear writes bf16 there and the returned tensor is empty
+    DeviceTensor forwardPlanned(const DeviceTensor& input, bool trusted, cudaStream_t stream, void* out16);
     void checkStatus(cudaStream_t stream, bool checkIds, std::size_t vocab);
 };
 
@@ -433,7 +434,7 @@ DeviceTensor Model::Impl::forwardFp32(const DeviceTensor& input, bool trusted) {
 }
 
 // ---- planned route: tensor-core GEMMs + flash attention -------------------------------------------------
-DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted, cudaStream_t stream) {
+DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted, cudaStream_t stream, void* out16) {
     prepare(stream);
     status.ensure(2 * sizeof(int));
     BFB_CUDA(cudaMemsetAsync(status.ptr, 0, 2 * sizeof(int), stream));
@@ -603,7 +604,12 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                 std::vector<std::size_t> outShape = shape;
                 outShape.back() = outL;
                 const bool last = i + 1 == layers.size();
-                if (last) {
+                if (last && out16 != nullptr) {
+                    // the caller takes the bf16 values themselves: same rounding as below, half the bytes
+                    runGemm(a, l.w0.ptr, out16, tokens, outL, d, BFB_BF16, BFB_EPI_BIAS, params[l.p[1]].value.data(),
+                            nullptr, dAlpha, 0);
+                    haveResult = true;
+                } else if (last) {
                     result = DeviceTensor(outShape);
                     runGemm(a, l.w0.ptr, result.data(), tokens, outL, d, BFB_F32, BFB_EPI_BIAS,
                             params[l.p[1]].value.data(), nullptr, dAlpha, storageBf16 ? 1 : 0);
@@ -695,7 +701,19 @@ DeviceTensor Model::forward(const DeviceTensor& input, bool inputRangeTrusted, v
         if (stream != nullptr) BFB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
         return impl_->forwardFp32(input, inputRangeTrusted);
     }
-    return impl_->forwardPlanned(input, inputRangeTrusted, static_cast<cudaStream_t>(stream));
+    return impl_->forwardPlanned(input, inputRangeTrusted, static_cast<cudaStream_t>(stream), nullptr);
+}
+
+bool Model::resultIsBf16Exact() const {
+    const bool planned = impl_->mode != Mode::Fp32 && !impl_->layers.empty() && impl_->layers.front().kind == BFB_OP_EMBEDDING;
+    return planned && impl_->storageBf16 && impl_->layers.back().kind == BFB_OP_LINEAR;
+}
+
+void Model::forwardBf16(const DeviceTensor& input, void* deviceOut16, bool inputRangeTrusted, void* stream) {
+    require(deviceOut16 != nullptr, "Model::forwardBf16: null output");
+    require(resultIsBf16Exact(), "Model::forwardBf16: needs storage bf16 and a pipeline from an embedding to a linear");
+    impl_->allocateParams();
+    impl_->forwardPlanned(input, inputRangeTrusted, static_cast<cudaStream_t>(stream), deviceOut16);
 }
 
 std::vector<Parameter*> Model::parameters() {

@@ -288,6 +288,11 @@ bfb_status bfb_model_forward(bfb_model* model, const float* d_input, const int64
  * h_out must hold product(out_shape) floats; call once with h_out == NULL to learn the shape. */
 bfb_status bfb_model_forward_host(bfb_model* model, const float* h_input, const int64_t* shape, int32_t rank,
                                   float* h_out, int64_t* out_shape, int32_t* out_rank);
+/* Bytes the calling thread's most recent bfb_model_forward_host moved over the host link: ids host to device,
+ * result device to host. Under `storage bf16` part of the result travels as 2-byte bf16 and is widened to the
+ * caller's fp32 words by host threads, so d2h can be below 4 * product(out_shape).
+ * No reference counterpart: its run path does not report transfers. */
+bfb_status bfb_host_transfer_bytes(int64_t* h2d_bytes, int64_t* d2h_bytes);
 /* Number of kernels this library launched on the calling thread since the counter was last reset. */
 int64_t bfb_launch_count(int32_t reset);
 

@@ -227,3 +227,30 @@ def test_host_path_slices_large_batches_without_changing_results(gpu, precision)
     bad[9, 0] = cfg["vocab"]
     with pytest.raises(gpu.InvalidArgument):
         m.forward_host(bad)
+
+
+def test_bf16_result_path_equals_device_result(gpu, monkeypatch):
+    """Under storage bf16 the host-buffer call moves part of the logits as 2-byte values and widens them on host
+    threads (six of ten slices here, through a ring of four staging slots), the rest as fp32; the caller must get exactly
+    the fp32 words the device call produces, and the reported device-to-host bytes say which way they went."""
+    monkeypatch.setenv("BFB_HOST_THREADS", "3")
+    monkeypatch.setenv("BFB_HOST_NARROW_PCT", "60")
+    ops = O.lm_ops(**TC)
+    m = gpu.Model(ops, precision={"storage": "bf16", "compute": "bf16"}, seed=11)
+    ids = O.synth_token_ids(19, 96, TC["vocab"], seed=6)
+    whole = m.forward_host(ids)
+    d_ids = gpu.DeviceBuffer.from_numpy(ids)
+    out, shape = m.forward_device(d_ids.ptr, ids.shape)
+    gpu.sync()
+    want = out.to_numpy(np.float32, shape)
+    out.free()
+    assert whole.shape == tuple(shape) and np.array_equal(whole, want)
+    assert np.array_equal(whole, O.round_bf16(whole))
+    h2d, d2h = gpu.host_transfer_bytes()
+    per_seq = 96 * TC["vocab"]
+    # 19 sequences in slices of 2: slices 1, 3, 4, 6, 8, 9 (0-based) go as bf16 (the last one holds one sequence)
+    assert h2d == ids.size * 4 and d2h == (5 * 2 + 1) * per_seq * 2 + 4 * 2 * per_seq * 4
+    monkeypatch.setenv("BFB_HOST_NARROW_PCT", "100")
+    assert np.array_equal(m.forward_host(ids), want) and gpu.host_transfer_bytes()[1] == 19 * per_seq * 2
+    monkeypatch.setenv("BFB_HOST_NARROW_PCT", "0")
+    assert np.array_equal(m.forward_host(ids), want) and gpu.host_transfer_bytes()[1] == 19 * per_seq * 4
