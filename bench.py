@@ -281,7 +281,10 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (invalid as a headline number)")
     ap.add_argument("--e2e-steps", type=int, default=-1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-sample-seq", type=int, default=32)
+    ap.add_argument("--cpu-sample-seq", type=int, default=32,
+                    help="tokens per worker and step of the reference arm's bounded sample")
+    ap.add_argument("--cpu-baseline-seq", type=int, default=192,
+                    help="tokens of the single-thread cpu_baseline sample of the default arm (about 11 s)")
     ap.add_argument("--cpu-workers", type=int, default=32)
     ap.add_argument("--seed", type=int, default=1234)
     args = ap.parse_args()
@@ -413,7 +416,7 @@ def main():
     if "gemm_tcgen05" in kernels:
         k = kernels["gemm_tcgen05"]
         achieved = k["work"] / (k["ms_total"] / 1e3) / 1e12
-        roofline = {"kernel": "gemmTcKernel (tcgen05 128x256 tiles, TMA-fed, TMEM accumulators)", "bound": "tensor",
+        roofline = {"kernel": "gemmPairKernel (tcgen05 cta_group::2, 256x256 tiles per CTA pair, TMA-fed, TMEM accumulators)", "bound": "tensor",
                     "achieved": achieved, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
                     "frac": achieved / peaks["tflops_sustained"], "peak_source": f"of {peaks['source']} (sustained cuBLAS bf16)",
                     "launches": k["launches"], "avg_launch_ms": k["ms_total"] / k["launches"],
@@ -431,7 +434,7 @@ def main():
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         try:
-            cpu = cpu_baseline_inline(cfg, seq, args.cpu_sample_seq)
+            cpu = cpu_baseline_inline(cfg, seq, args.cpu_baseline_seq)
         except Exception as exc:
             cpu = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "unavailable", "sample": repr(exc)}
 
