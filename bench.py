@@ -45,13 +45,19 @@ WORKLOADS = {
            "2B-class decoder (vocab 32000, d 2048, 16 layers, 16x128 heads, ffn 5632) fp8.e4m3 prefill"),
     "c1": (dict(vocab=256, dim=64, layers=2, heads=4, hidden=256, max_seq=32), 4, 32, None,
            "tiny decoder (vocab 256, d 64, 2 layers, 4x16 heads, ffn 256) fp32"),
+    # tensor parallel: every rank runs the SAME 8 sequences on its shard of the heads, feed-forward columns and
+    # logits columns; needs --gpus 2, 4 or 8 (the fp32 master weights alone are 97 GB)
+    "c5": (dict(vocab=32000, dim=8192, layers=32, heads=64, hidden=28672, max_seq=4096), 8, 4096,
+           {"storage": "bf16", "compute": "bf16", "accumulate": "fp32"},
+           "24B-class decoder (vocab 32000, d 8192, 32 layers, 64x128 heads, ffn 28672) bf16 prefill, tensor parallel"),
 }
+TENSOR_PARALLEL = {"c5"}
 
 # DRAM bytes per launch of the dominant kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum),
 # keyed by workload; None until a capture of that kernel has been summarised under profiles/.
 # c3: capture of M=32768, N=K=2048 (239.2 MB for 0.275 TFLOP, equal to A+B+C) scaled by FLOPs to the step's average
 # GEMM launch (1.418 TFLOP); see profiles/gemm_pair_bf16_m32768_n2048_k2048.md.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {"c3": 1.233e9, "c4": None, "c1": None}
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"c3": 1.233e9, "c4": None, "c1": None, "c5": None}
 
 
 def lm_ops(vocab, dim, layers, heads, hidden, max_seq):
@@ -323,8 +329,21 @@ def main():
     # ---- model and inputs --------------------------------------------------------------------------------
     ops = lm_ops(**cfg)
     model = bfb.Model(ops, precision=precision, random_init=False)
-    synth_weights(bfb, model, args.seed, 0.02)
-    rng = np.random.Generator(np.random.PCG64([args.seed, 7919 + rank]))
+    tensor_parallel = args.workload in TENSOR_PARALLEL
+    if tensor_parallel:
+        if world < 2:
+            raise SystemExit(f"workload {args.workload} is tensor parallel: launch it on 2, 4 or 8 GPUs")
+        ident = launch.broadcast_bytes(bfb.tp_unique_id() if rank == 0 else b"", 128, 0, dev)
+        bfb.tp_init(ident, rank, world)
+        model.set_tensor_parallel(rank, world)
+        # weights drawn on the device (N(0, 0.01), the same full matrices whatever the split); the fp32 copies of
+        # the GEMM weights are dropped once the first forward has converted them
+        for i, _name in enumerate(model.param_names()):
+            model.fill_param_normal(i, args.seed * 1000003 + i, 0.01)
+    else:
+        synth_weights(bfb, model, args.seed, 0.02)
+    # batch-sharded ranks draw their own sequences; tensor-parallel ranks must all see the same ones
+    rng = np.random.Generator(np.random.PCG64([args.seed, 7919 + (0 if tensor_parallel else rank)]))
     ids = rng.integers(0, cfg["vocab"], size=(batch, seq)).astype(np.float32)
     d_ids = bfb.DeviceBuffer.from_numpy(ids)
     tokens_per_step = batch * seq
@@ -337,8 +356,11 @@ def main():
     # ---- warm-up (first call converts the weights) -------------------------------------------------------
     sampler = ClockSampler(local) if rank == 0 else None
     out_shape = None
-    for _ in range(max(args.warmup, 1)):
+    for i in range(max(args.warmup, 1)):
         out_shape = step_device()
+        if i == 0 and tensor_parallel:
+            torch.cuda.synchronize()
+            model.release_master_weights()
     torch.cuda.synchronize()
 
     # ---- timed region: K steps, CUDA events on the launching (default) stream ------------------------------
@@ -367,7 +389,8 @@ def main():
             kernels[name] = {"ms_total": ms, "launches": n, "work": work}
     bfb.lib().bfb_profile_reset()
     ms_per_step = elapsed_ms / args.steps
-    value = world * tokens_per_step / (ms_per_step / 1e3)
+    replicas = 1 if tensor_parallel else world   # tensor-parallel ranks share one batch
+    value = replicas * tokens_per_step / (ms_per_step / 1e3)
 
     # ---- end to end through the host-buffer API: ids H2D + logits D2H inside the timed region ---------------
     e2e = None
@@ -397,7 +420,7 @@ def main():
         # bytes the call itself booked for its copies: under storage bf16 part of the logits crosses the link as
         # 2-byte bf16 and is widened to the caller's fp32 buffer by host threads
         h2d_bytes, d2h_bytes = bfb.host_transfer_bytes()
-        e2e = {"value": world * tokens_per_step / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+        e2e = {"value": replicas * tokens_per_step / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                "result_bytes_per_step": out_elems * 4, "steps": e2e_steps,
                "api": "bfb_model_forward_host (fromHost -> Model::forward -> toHost), pinned host buffers"}
@@ -405,6 +428,8 @@ def main():
 
     if world > 1:
         launch.barrier()
+        if tensor_parallel:
+            bfb.tp_destroy()
         torch.distributed.destroy_process_group()
     if rank != 0:
         return
@@ -429,7 +454,8 @@ def main():
         else:
             k["gbs"] = k["work"] / secs / 1e9
         k["share_of_step"] = k["ms_total"] / elapsed_ms
-    model_tflops = (g_flops + a_flops) * tokens_per_step / (ms_per_step / 1e3) / 1e12
+    # per GPU: a tensor-parallel rank does 1/world of the batch's arithmetic
+    model_tflops = (g_flops + a_flops) * tokens_per_step / (ms_per_step / 1e3) / 1e12 / (world if tensor_parallel else 1)
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
@@ -440,13 +466,17 @@ def main():
 
     line = {
         "metric": "prefill tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 1), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": max(args.warmup, 1), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if tensor_parallel else "weak",
         "vs_baseline": None, "dtype": "bf16" if (precision or {}).get("compute") == "bf16" else
         ("fp8.e4m3" if (precision or {}).get("compute") == "fp8.e4m3" else "f32"),
-        "data": "synthetic (seeded uniform token ids, N(0,0.02) weights)",
-        "config": {"workload": label, "global_batch": batch * world, "batch_per_gpu": batch, "seq_len": seq,
-                   "precision": precision, "parallelism": f"batch-sharded x{world}, no data-path collective",
-                   "l2": "per-step working set (weights 1.5 GB + activations) far exceeds the 126 MB L2; no flush needed",
+        "data": f"synthetic (seeded uniform token ids, N(0,{'0.01' if tensor_parallel else '0.02'}) weights)",
+        "config": {"workload": label, "global_batch": batch * replicas, "batch_per_gpu": batch, "seq_len": seq,
+                   "precision": precision,
+                   "parallelism": (f"tensor-parallel x{world}: heads, feed-forward columns and logits columns sharded, "
+                                   "NCCL all-reduce after the out-projection and the feed-forward down-projection"
+                                   if tensor_parallel else f"batch-sharded x{world}, no data-path collective"),
+                   "l2": "per-step working set (weights and activations, GBs) far exceeds the 126 MB L2; no flush needed",
                    "flops_per_token": g_flops + a_flops},
         "model_tflops": model_tflops,
         "model_frac_of_peak": {"measured_sustained": model_tflops / peaks["tflops_sustained"],

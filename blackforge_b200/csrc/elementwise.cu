@@ -298,6 +298,66 @@ rmsnormWarpKernel(const TIn* __restrict__ x, TOut* __restrict__ out, int64_t row
     }
 }
 
+// Rows too long for one warp's registers: four warps share a row, each lane still holds its part in registers
+// (read once, 16-byte accesses), and the four partial sums of squares meet in shared memory.
+template <typename TIn, typename TOut, int kVecs>
+__global__ void __launch_bounds__(kThreads)
+rmsnormQuadKernel(const TIn* __restrict__ x, TOut* __restrict__ out, int64_t rows, int64_t dim, float eps) {
+    constexpr int kN = Vec16<TIn>::kN;
+    constexpr int kGroup = 4;                       // warps per row
+    constexpr int kRowsPerBlock = kThreads / 32 / kGroup;
+    __shared__ float partial[2][kThreads / 32];     // double-buffered by iteration: one barrier per row
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int group = warp / kGroup;
+    const int64_t slot = (warp % kGroup) * 32 + lane;   // position among the 128 lanes of the row
+    const int64_t nv = dim / kN;
+    int parity = 0;
+    // every warp of the block makes the same number of trips, so the barrier below is reached by all
+    for (int64_t base = static_cast<int64_t>(blockIdx.x) * kRowsPerBlock; base < rows;
+         base += static_cast<int64_t>(gridDim.x) * kRowsPerBlock, parity ^= 1) {
+        const int64_t row = base + group;
+        const bool active = row < rows;
+        const TIn* src = x + row * dim;
+        float vals[kVecs][kN];
+        float ss = 0.0f;
+        if (active) {
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                const int64_t i = slot + 128 * j;
+                if (i < nv) Vec16<TIn>::load(src + i * kN, vals[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                if (slot + 128 * j < nv) {
+#pragma unroll
+                    for (int e = 0; e < kN; ++e) ss = fmaf(vals[j][e], vals[j][e], ss);
+                }
+            }
+        }
+        const float mine = warpSum(ss);
+        if (lane == 0) partial[parity][warp] = mine;
+        __syncthreads();
+        if (!active) continue;
+        float total = 0.0f;
+#pragma unroll
+        for (int g = 0; g < kGroup; ++g) total += partial[parity][group * kGroup + g];
+        const float rms = sqrtf(total / static_cast<float>(dim) + eps);
+        const float inv = 1.0f / rms;
+        TOut* dst = out + row * dim;
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int64_t i = slot + 128 * j;
+            if (i < nv) {
+                float o[kN];
+#pragma unroll
+                for (int e = 0; e < kN; ++e) o[e] = sizeof(TOut) == 2 ? vals[j][e] * inv : vals[j][e] / rms;
+                storeRun<TOut, kN>(dst + i * kN, o);
+            }
+        }
+    }
+}
+
 // Any dim, two passes over the row (second pass hits L1/L2).
 template <typename TIn, typename TOut>
 __global__ void rmsnormGenericKernel(const TIn* __restrict__ x, TOut* __restrict__ out, int64_t rows, int64_t dim,
@@ -324,15 +384,20 @@ void rmsnormDispatch(const TIn* x, TOut* out, int64_t rows, int64_t dim, float e
                    (reinterpret_cast<uintptr_t>(out) % 16 == 0);
     constexpr int kEpv = 16 / static_cast<int>(sizeof(TIn));  // elements per 16-byte load
     const bool wide = aligned && dim % kEpv == 0 && (dim * sizeof(TOut)) % 16 == 0;
-    if (wide && dim <= 32 * 16 * kEpv) {
+    if (wide && dim <= 32 * 8 * kEpv) {
         // one warp per row, the whole row in flight as 16-byte loads before anything is reduced
         const int vecs = static_cast<int>((dim / kEpv + 31) / 32);
         const int rowsPerBlock = kThreads / 32;
         const int grid = gridFor(rows, rowsPerBlock, 8);
         if (vecs <= 2) rmsnormWarpKernel<TIn, TOut, 2><<<grid, kThreads, 0, stream>>>(x, out, rows, dim, eps);
         else if (vecs <= 4) rmsnormWarpKernel<TIn, TOut, 4><<<grid, kThreads, 0, stream>>>(x, out, rows, dim, eps);
-        else if (vecs <= 8) rmsnormWarpKernel<TIn, TOut, 8><<<grid, kThreads, 0, stream>>>(x, out, rows, dim, eps);
-        else rmsnormWarpKernel<TIn, TOut, 16><<<grid, kThreads, 0, stream>>>(x, out, rows, dim, eps);
+        else rmsnormWarpKernel<TIn, TOut, 8><<<grid, kThreads, 0, stream>>>(x, out, rows, dim, eps);
+    } else if (wide && dim <= 128 * 8 * kEpv) {
+        const int vecs = static_cast<int>((dim / kEpv + 127) / 128);
+        const int rowsPerBlock = kThreads / 32 / 4;
+        const int grid = gridFor(rows, rowsPerBlock, 8);
+        if (vecs <= 4) rmsnormQuadKernel<TIn, TOut, 4><<<grid, kThreads, 0, stream>>>(x, out, rows, dim, eps);
+        else rmsnormQuadKernel<TIn, TOut, 8><<<grid, kThreads, 0, stream>>>(x, out, rows, dim, eps);
     } else if (aligned && dim <= 1024) {
         int rowsPerBlock = kThreads / 32;
         int grid = gridFor(rows, rowsPerBlock, 16);

@@ -36,7 +36,8 @@ def test_elementwise_against_golden(gpu, golden_ops):
     assert np.max(np.abs(got - O.silu(ab + g["lin_bias"]))) <= 1e-5
 
 
-@pytest.mark.parametrize("shape", [(3, 5, 300), (7, 64), (5, 2048), (2, 8192), (3, 10), (2, 9000)])
+@pytest.mark.parametrize("shape", [(3, 5, 300), (7, 64), (5, 2048), (2, 8192), (3, 10), (2, 9000), (5, 4096), (3, 6144),
+                                   (9, 8192)])
 def test_rmsnorm_matches_oracle(gpu, shape):
     x = (np.random.default_rng(sum(shape)).standard_normal(shape) * 2).astype(np.float32)
     rows, dim = int(np.prod(shape[:-1])), shape[-1]
