@@ -231,6 +231,38 @@ bfb_status bfb_gemm(const void* d_a, const void* d_b, void* d_c, int64_t m, int6
     });
 }
 
+bfb_status bfb_row_sum_squares(const void* d_x, int32_t dtype, float* d_out, int64_t rows, int64_t dim, void* stream) {
+    return guarded([&] { bfb::rowSumSquares(d_x, dtype, d_out, rows, dim, asStream(stream)); });
+}
+
+bfb_status bfb_gemm_rmsnorm(const void* d_a, const void* d_w, void* d_c, int64_t m, int64_t n, int64_t k,
+                            int32_t ab_dtype, int32_t c_dtype, int32_t epilogue, const float* d_bias,
+                            const void* d_residual, const float* d_row_sum_sq, int32_t row_sum_sq_parts, float eps,
+                            float* d_out_sum_sq, int32_t* d_status, void* stream) {
+    return guarded([&] {
+        bfb::GemmArgs g;
+        g.a = d_a;
+        g.b = d_w;
+        g.c = d_c;
+        g.m = m;
+        g.n = n;
+        g.k = k;
+        g.abDtype = ab_dtype;
+        g.bLayout = BFB_B_NK;
+        g.cDtype = c_dtype;
+        g.epilogue = epilogue;
+        g.bias = d_bias;
+        g.residual = d_residual;
+        g.rowSumSq = d_row_sum_sq;
+        g.rowSumSqParts = row_sum_sq_parts;
+        g.rowInvDim = k > 0 ? 1.0f / static_cast<float>(k) : 0.0f;
+        g.rowEps = eps;
+        g.outSumSq = d_out_sum_sq;
+        g.dStatus = d_status;
+        bfb::gemm(g, asStream(stream));
+    });
+}
+
 bfb_status bfb_matmul_transpose_b(const float* d_a, const float* d_b, float* d_c, int64_t m, int64_t n, int64_t k,
                                   void* stream) {
     return guarded([&] { bfb::matmulTransposeB(d_a, d_b, d_c, m, n, k, asStream(stream)); });

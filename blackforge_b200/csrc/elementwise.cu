@@ -298,6 +298,47 @@ rmsnormWarpKernel(const TIn* __restrict__ x, TOut* __restrict__ out, int64_t row
     }
 }
 
+// The statistic of an rmsnorm alone: out[row] = sum of squares of the row. One warp per row, 16-byte loads.
+template <typename TIn, bool kVector>
+__global__ void __launch_bounds__(kThreads)
+rowSumSquaresKernel(const TIn* __restrict__ x, float* __restrict__ out, int64_t rows, int64_t dim) {
+    constexpr int kN = Vec16<TIn>::kN;
+    const int lane = threadIdx.x & 31;
+    const int64_t warpsPerGrid = static_cast<int64_t>(gridDim.x) * (kThreads / 32);
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5); row < rows;
+         row += warpsPerGrid) {
+        const TIn* src = x + row * dim;
+        float s0 = 0.0f, s1 = 0.0f;
+        if constexpr (kVector) {
+            const int64_t nv = dim / kN;
+            int64_t i = lane;
+            for (; i + 32 < nv; i += 64) {   // two loads in flight per lane
+                float a[kN], b[kN];
+                Vec16<TIn>::load(src + i * kN, a);
+                Vec16<TIn>::load(src + (i + 32) * kN, b);
+#pragma unroll
+                for (int e = 0; e < kN; ++e) {
+                    s0 = fmaf(a[e], a[e], s0);
+                    s1 = fmaf(b[e], b[e], s1);
+                }
+            }
+            if (i < nv) {
+                float a[kN];
+                Vec16<TIn>::load(src + i * kN, a);
+#pragma unroll
+                for (int e = 0; e < kN; ++e) s0 = fmaf(a[e], a[e], s0);
+            }
+        } else {
+            for (int64_t i = lane; i < dim; i += 32) {
+                const float v = toFloat<TIn>(src[i]);
+                s0 = fmaf(v, v, s0);
+            }
+        }
+        const float total = warpSum(s0 + s1);
+        if (lane == 0) out[row] = total;
+    }
+}
+
 // Rows too long for one warp's registers: four warps share a row, each lane still holds its part in registers
 // (read once, 16-byte accesses), and the four partial sums of squares meet in shared memory.
 template <typename TIn, typename TOut, int kVecs>
@@ -648,6 +689,28 @@ void rmsnorm(const void* x, int xDtype, void* out, int outDtype, int64_t rows, i
         rmsnormDispatch(static_cast<const bf*>(x), static_cast<float*>(out), rows, dim, eps, stream);
     else
         rmsnormDispatch(static_cast<const bf*>(x), static_cast<bf*>(out), rows, dim, eps, stream);
+}
+
+void rowSumSquares(const void* x, int xDtype, float* out, int64_t rows, int64_t dim, cudaStream_t stream) {
+    require(rows >= 0 && dim > 0, "row_sum_squares: bad sizes");
+    require(xDtype == BFB_F32 || xDtype == BFB_BF16, "row_sum_squares: format must be f32 or bf16");
+    if (rows == 0) return;
+    require(x != nullptr && out != nullptr, "row_sum_squares: null pointer");
+    ProfileScope prof(kProfRmsnorm, stream,
+                      static_cast<double>(rows) * (static_cast<double>(dim) * dtypeBytes(xDtype) + 4.0));
+    const int grid = gridFor(rows, kThreads / 32, 16);
+    if (xDtype == BFB_F32) {
+        const bool vec = dim % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
+        if (vec) rowSumSquaresKernel<float, true><<<grid, kThreads, 0, stream>>>(static_cast<const float*>(x), out, rows, dim);
+        else rowSumSquaresKernel<float, false><<<grid, kThreads, 0, stream>>>(static_cast<const float*>(x), out, rows, dim);
+    } else {
+        using bf = __nv_bfloat16;
+        const bool vec = dim % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
+        if (vec) rowSumSquaresKernel<bf, true><<<grid, kThreads, 0, stream>>>(static_cast<const bf*>(x), out, rows, dim);
+        else rowSumSquaresKernel<bf, false><<<grid, kThreads, 0, stream>>>(static_cast<const bf*>(x), out, rows, dim);
+    }
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
 }
 
 void softmaxRows(const float* x, float* out, int64_t rows, int64_t cols, cudaStream_t stream) {

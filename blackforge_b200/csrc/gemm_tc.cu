@@ -408,9 +408,16 @@ static bool pairKernelEnabled() {
     return enabled;
 }
 
+bool gemmSupportsRowStats(const GemmArgs& g) {
+    return gemmUsesTensorCores(g) && g.bLayout == BFB_B_NK && pairKernelEnabled() && g.rowSumSqParts >= 1;
+}
+
 void gemmTensorCore(const GemmArgs& g, cudaStream_t stream) {
     // CTA pairs share 256-row tiles: worth it once there is more than one 128-row tile of work
-    if (g.bLayout == BFB_B_NK && g.m > 128 && pairKernelEnabled()) {
+    // ... or when row statistics are asked for, which only that kernel has (whatever the number of rows, so that
+    // a sequence gives the same bits alone and inside a batch)
+    const bool stats = g.rowSumSq != nullptr || g.outSumSq != nullptr;
+    if (g.bLayout == BFB_B_NK && (g.m > 128 || stats) && pairKernelEnabled()) {
         gemmTensorCorePair(g, stream);
         return;
     }

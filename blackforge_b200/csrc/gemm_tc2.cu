@@ -75,6 +75,11 @@ struct PairEpilogue {
     const float* dAlpha;
     int epilogue;
     int roundCBf16;
+    const float* rowSumSq;   // [rowSumSqParts][m] partial sums of squares of A's rows, or null
+    int rowSumSqParts;
+    float rowInvDim;         // row scale = 1 / sqrt(sum * rowInvDim + rowEps)
+    float rowEps;
+    float* outSumSq;         // [ceil(n / 128)][m]: sums of squares of the stored values per 128-column part, or null
 };
 
 __device__ __forceinline__ float siluFast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
@@ -233,12 +238,33 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
             tc_fence_after();
             const int row = tc.m * kPairM + static_cast<int>(rank) * 128 + quarter * 32 + lane;
             const bool rowOk = row < m;
+            // an rmsnorm of A's rows, applied to the product's rows instead
+            float rowScale = scale;
+            if (ep.rowSumSq != nullptr && rowOk) {
+                float total = 0.0f;   // parts added in index order: the same sum whoever produced them
+                for (int part = 0; part < ep.rowSumSqParts; ++part)
+                    total += __ldg(ep.rowSumSq + static_cast<size_t>(part) * static_cast<size_t>(m) + row);
+                rowScale = scale / sqrtf(total * ep.rowInvDim + ep.rowEps);
+            }
+            // Sums of squares of what this thread stores, one per 128-column part of the row, each written by
+            // exactly one thread: no atomics, so the figures do not depend on timing or on the tile width.
+            float sumSq = 0.0f;
+            int part = -1;
+            auto flushPart = [&]() {
+                if (ep.outSumSq != nullptr && rowOk && part >= 0)
+                    ep.outSumSq[static_cast<size_t>(part) * static_cast<size_t>(m) + row] = sumSq;
+            };
             const uint32_t tBase = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>(buf * kAccN + colHalf * kColsPerWarp);
 #pragma unroll 1
             for (int chunk = 0; chunk < kColsPerWarp / 32; ++chunk) {
                 const int col0 = tc.n * kAccN + colHalf * kColsPerWarp + chunk * 32;
                 if (col0 >= n) break;
+                if ((col0 >> 7) != part) {
+                    flushPart();
+                    part = col0 >> 7;
+                    sumSq = 0.0f;
+                }
                 uint32_t raw[32];
                 tmem_ld_32x32(tBase + static_cast<uint32_t>(chunk * 32), raw);
                 tmem_ld_wait();
@@ -250,7 +276,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
                         if (col + 8 > n) break;
                         float v[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(raw[g * 8 + j]) * scale;
+                        for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(raw[g * 8 + j]) * rowScale;
                         if (hasBias) {
                             const float4 b0 = __ldg(reinterpret_cast<const float4*>(ep.bias + col));
                             const float4 b1 = __ldg(reinterpret_cast<const float4*>(ep.bias + col + 4));
@@ -275,6 +301,10 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
                             float4* dst = reinterpret_cast<float4*>(cOut + rowOff + col);
                             dst[0] = make_float4(v[0], v[1], v[2], v[3]);
                             dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+                            if (ep.outSumSq != nullptr) {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) sumSq = fmaf(v[j], v[j], sumSq);
+                            }
                         } else {
                             if (hasRes) {
                                 const uint4 rr = *reinterpret_cast<const uint4*>(res + rowOff + col);
@@ -292,6 +322,10 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
                             for (int j = 0; j < 4; ++j) {
                                 __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
                                 pw[j] = *reinterpret_cast<uint32_t*>(&h);
+                                if (ep.outSumSq != nullptr) {
+                                    const float2 f = __bfloat1622float2(h);   // the values as stored
+                                    sumSq = fmaf(f.x, f.x, fmaf(f.y, f.y, sumSq));
+                                }
                             }
                             *reinterpret_cast<uint4*>(cOut + rowOff + col) = packed;
                         }
@@ -301,6 +335,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
             tc_fence_before();
             __syncwarp();  // one (remote) arrival per warp instead of one per thread
             if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&accEmptyBar[buf]), 0));
+            flushPart();
         }
     }
 
@@ -351,7 +386,8 @@ void launchPair(const GemmArgs& g, cudaStream_t stream) {
     const int groups = (tilesN + maxGroup - 1) / maxGroup;
     const int groupN = (tilesN + groups - 1) / groups;
     const int clusters = std::max(1, std::min(tilesM * tilesN, smCount() / 2));
-    PairEpilogue ep{g.c, g.bias, g.residual, g.alpha, g.dAlpha, g.epilogue, g.roundCBf16};
+    PairEpilogue ep{g.c, g.bias, g.residual, g.alpha, g.dAlpha, g.epilogue, g.roundCBf16,
+                    g.rowSumSq, g.rowSumSqParts, g.rowInvDim, g.rowEps, g.outSumSq};
     auto kernel = gemmPairKernel<kElemBytes, TC, kAccN>;
     BFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     ProfileScope prof(kProfGemmTc, stream, 2.0 * static_cast<double>(g.m) * static_cast<double>(g.n) * static_cast<double>(g.k));

@@ -7,7 +7,9 @@
 // per block
 //   rmsnorm -> [QKV GEMM] -> flash attention -> [out-proj GEMM + residual]
 //   rmsnorm -> [GEMM + bias + silu] -> [GEMM + bias + residual]
-// with every bias / activation / residual pass folded into a GEMM epilogue. `storage bf16` keeps
+// with every bias / activation / residual pass folded into a GEMM epilogue. On a bf16 residual stream with
+// bf16 operands the rmsnorm is folded too: the GEMM after it reads x and scales its rows in the epilogue, and
+// the GEMM that writes x delivers the row sums of squares the next norm needs. `storage bf16` keeps
 // the residual stream in bf16 (each op output rounded once, the CPU backend's meaning of storage);
 // otherwise it stays fp32. Results leave as fp32 tensors either way.
 #include <dlfcn.h>
@@ -480,7 +482,8 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
         return a8;
     };
     auto runGemm = [&](const void* a, const void* w, void* c, std::size_t m, std::size_t n, std::size_t k, int cDtype,
-                       int epilogue, const float* bias, const void* residual, const float* dAlpha, int roundC) {
+                       int epilogue, const float* bias, const void* residual, const float* dAlpha, int roundC,
+                       const float* rowSumSq = nullptr, int rowSumSqParts = 1, float* outSumSq = nullptr) {
         bfb::GemmArgs g;
         g.a = a;
         g.b = w;
@@ -497,7 +500,58 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
         g.dAlpha = dAlpha;
         g.roundCBf16 = roundC;
         g.dStatus = dStatus;
+        g.rowSumSq = rowSumSq;
+        g.rowSumSqParts = rowSumSqParts;
+        g.rowInvDim = k > 0 ? 1.0f / static_cast<float>(k) : 0.0f;
+        g.rowEps = 1e-6f;
+        g.outSumSq = outSumSq;
         bfb::gemm(g, stream);
+    };
+
+    // rmsnorm folded into the GEMM that follows it (bf16 residual stream, bf16 operands): an rmsnorm without
+    // weights scales rows, which commutes with the product, so the GEMM reads x itself and its epilogue divides
+    // row i by sqrt(mean(x_i^2) + eps). The sums of squares come from the epilogue of the GEMM that wrote x
+    // (out-projection, feed-forward down-projection) or, where x has another origin (the embedding, a
+    // tensor-parallel all-reduce), from one read-only pass. No normalised copy of x is written or read.
+    // e4m3 operands keep the separate norm: their per-tensor scale is taken from the normalised values.
+    auto fusedNormOk = [&](std::size_t tokens, std::size_t n, std::size_t d, const void* w) {
+        if (fp8 || S != BFB_BF16) return false;
+        bfb::GemmArgs probe;
+        probe.a = x;
+        probe.b = w;
+        probe.c = x;
+        probe.m = static_cast<int64_t>(tokens);
+        probe.n = static_cast<int64_t>(n);
+        probe.k = static_cast<int64_t>(d);
+        probe.abDtype = ab;
+        probe.bLayout = BFB_B_NK;
+        probe.cDtype = BFB_BF16;
+        return bfb::gemmSupportsRowStats(probe);
+    };
+    // Sums of squares of the rows of x as [parts][tokens]: one part from the read-only pass, one per 128 columns
+    // from the epilogue of the GEMM that wrote x. One buffer is enough: by the time a GEMM writes the sums of the
+    // next x, the GEMM that read the previous ones has finished (same stream).
+    float* ss = nullptr;
+    int ssParts = 0;         // 0: ss does not describe the current x
+    auto sumSqBuffer = [&](std::size_t tokens, std::size_t d) {
+        return static_cast<float*>(buf("row_sumsq", ((d + 127) / 128) * tokens * sizeof(float)));
+    };
+    auto needSumSq = [&](std::size_t tokens, std::size_t d) {
+        if (ssParts == 0) {
+            ss = sumSqBuffer(tokens, d);
+            bfb::rowSumSquares(x, S, ss, static_cast<int64_t>(tokens), static_cast<int64_t>(d), stream);
+            ssParts = 1;
+        }
+        return ss;
+    };
+    // where the GEMM that writes the next x puts the next sums (null: it cannot deliver them)
+    auto nextSumSq = [&](std::size_t tokens, std::size_t d) -> float* {
+        if (tpWorld > 1) return nullptr;   // x is completed by an all-reduce: the epilogue only sees a partial sum
+        return sumSqBuffer(tokens, d);
+    };
+    auto producedSumSq = [&](float* produced, std::size_t d) {
+        ss = produced;
+        ssParts = produced != nullptr ? static_cast<int>((d + 127) / 128) : 0;
     };
 
     DeviceTensor result;
@@ -539,13 +593,20 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                 if (shape.size() != 3) throw std::invalid_argument("selfAttention: input [batch, seq, dim] required");
                 const std::size_t batch = shape[0], seq = shape[1], d = feat, dl = d / w, hl = l.heads / w;
                 const std::size_t hd = d / l.heads;
-                void* normed = buf("normed", tokens * d * 2);
-                bfb::rmsnorm(x, S, normed, BFB_BF16, static_cast<int64_t>(tokens), static_cast<int64_t>(d), 1e-6f, stream);
                 const float* sc = static_cast<const float*>(l.scales.ptr);
                 const float* dAlpha = nullptr;
-                const void* aQkv = gemmInput(normed, tokens * d, "act8_d", sc, &dAlpha);
                 void* qkv = buf("qkv", tokens * 3 * dl * 2);
-                runGemm(aQkv, l.w0.ptr, qkv, tokens, 3 * dl, d, BFB_BF16, BFB_EPI_NONE, nullptr, nullptr, dAlpha, 0);
+                const bool fuse = fusedNormOk(tokens, 3 * dl, d, l.w0.ptr);
+                if (fuse) {
+                    const float* sums = needSumSq(tokens, d);
+                    runGemm(x, l.w0.ptr, qkv, tokens, 3 * dl, d, BFB_BF16, BFB_EPI_NONE, nullptr, nullptr, nullptr, 0, sums,
+                            ssParts, nullptr);
+                } else {
+                    void* normed = buf("normed", tokens * d * 2);
+                    bfb::rmsnorm(x, S, normed, BFB_BF16, static_cast<int64_t>(tokens), static_cast<int64_t>(d), 1e-6f, stream);
+                    const void* aQkv = gemmInput(normed, tokens * d, "act8_d", sc, &dAlpha);
+                    runGemm(aQkv, l.w0.ptr, qkv, tokens, 3 * dl, d, BFB_BF16, BFB_EPI_NONE, nullptr, nullptr, dAlpha, 0);
+                }
                 void* ctx = buf("ctx", tokens * dl * 2);
                 bfb::AttentionArgs a;
                 a.q = qkv;
@@ -567,25 +628,36 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                 const void* aOut = gemmInput(ctx, tokens * dl, "act8_dl", sc + 2, &dAlpha);
                 // x = x + ctx * Wout (in place); under tensor parallelism rank 0 carries the residual
                 const int epi = (tpWorld == 1 || tpRank == 0) ? BFB_EPI_RESIDUAL : BFB_EPI_NONE;
-                runGemm(aOut, l.w1.ptr, x, tokens, d, dl, S, epi, nullptr, x, dAlpha, 0);
+                float* produced = fuse && fusedNormOk(tokens, d, dl, l.w1.ptr) ? nextSumSq(tokens, d) : nullptr;
+                runGemm(aOut, l.w1.ptr, x, tokens, d, dl, S, epi, nullptr, x, dAlpha, 0, nullptr, 1, produced);
+                producedSumSq(produced, d);
                 if (tpWorld > 1) tpAllReduceSum(x, static_cast<int64_t>(tokens * d), S, stream);
                 break;
             }
             case BFB_OP_FEEDFORWARD: {
                 require(x != nullptr, "Model: the planned route must start with an embedding");
                 const std::size_t d = feat, fl = l.hidden / w;
-                void* normed = buf("normed", tokens * d * 2);
-                bfb::rmsnorm(x, S, normed, BFB_BF16, static_cast<int64_t>(tokens), static_cast<int64_t>(d), 1e-6f, stream);
                 const float* sc = static_cast<const float*>(l.scales.ptr);
                 const float* dAlpha = nullptr;
-                const void* a1 = gemmInput(normed, tokens * d, "act8_d", sc, &dAlpha);
                 void* hidden = buf("hidden", tokens * fl * 2);
-                runGemm(a1, l.w0.ptr, hidden, tokens, fl, d, BFB_BF16, BFB_EPI_BIAS_SILU, params[l.p[1]].value.data(),
-                        nullptr, dAlpha, 0);
+                const bool fuse = fusedNormOk(tokens, fl, d, l.w0.ptr);
+                if (fuse) {
+                    const float* sums = needSumSq(tokens, d);
+                    runGemm(x, l.w0.ptr, hidden, tokens, fl, d, BFB_BF16, BFB_EPI_BIAS_SILU, params[l.p[1]].value.data(),
+                            nullptr, nullptr, 0, sums, ssParts, nullptr);
+                } else {
+                    void* normed = buf("normed", tokens * d * 2);
+                    bfb::rmsnorm(x, S, normed, BFB_BF16, static_cast<int64_t>(tokens), static_cast<int64_t>(d), 1e-6f, stream);
+                    const void* a1 = gemmInput(normed, tokens * d, "act8_d", sc, &dAlpha);
+                    runGemm(a1, l.w0.ptr, hidden, tokens, fl, d, BFB_BF16, BFB_EPI_BIAS_SILU, params[l.p[1]].value.data(),
+                            nullptr, dAlpha, 0);
+                }
                 const void* a2 = gemmInput(hidden, tokens * fl, "act8_f", sc + 2, &dAlpha);
                 const bool lead = tpWorld == 1 || tpRank == 0;
+                float* produced = fuse && fusedNormOk(tokens, d, fl, l.w1.ptr) ? nextSumSq(tokens, d) : nullptr;
                 runGemm(a2, l.w1.ptr, x, tokens, d, fl, S, lead ? BFB_EPI_BIAS_RESIDUAL : BFB_EPI_NONE,
-                        lead ? params[l.p[3]].value.data() : nullptr, lead ? x : nullptr, dAlpha, 0);
+                        lead ? params[l.p[3]].value.data() : nullptr, lead ? x : nullptr, dAlpha, 0, nullptr, 1, produced);
+                producedSumSq(produced, d);
                 if (tpWorld > 1) tpAllReduceSum(x, static_cast<int64_t>(tokens * d), S, stream);
                 break;
             }
@@ -620,6 +692,7 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                             dAlpha, 0);
                     std::swap(arena["x"], arena["x_alt"]);
                     x = arena["x"].ptr;
+                    ssParts = 0;
                 }
                 shape = outShape;
                 feat = outL;
@@ -644,6 +717,7 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                 }
                 BFB_CUDA(cudaStreamSynchronize(nullptr));
                 bfb::castScaled(out.data(), BFB_F32, x, S, static_cast<int64_t>(count), 1.0f, nullptr, stream);
+                ssParts = 0;
                 break;
             }
         }

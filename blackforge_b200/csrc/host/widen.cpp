@@ -45,8 +45,14 @@ int defaultWidenThreads() {
         const int v = std::atoi(e);
         if (v >= 1) return std::min(v, 256);
     }
-    const unsigned hc = std::thread::hardware_concurrency();
-    return static_cast<int>(std::max(1u, std::min(hc == 0 ? 4u : hc, 16u)));
+    unsigned hc = std::thread::hardware_concurrency();
+    if (hc == 0) hc = 4;
+    // one process per GPU on the same host (LOCAL_WORLD_SIZE as set by torchrun): the ranks share the cores
+    if (const char* e = std::getenv("LOCAL_WORLD_SIZE")) {
+        const int ranks = std::atoi(e);
+        if (ranks > 1) hc = std::max(1u, hc / static_cast<unsigned>(ranks));
+    }
+    return static_cast<int>(std::min(hc, 16u));
 }
 
 WidenQueue::WidenQueue(int device, int threads) : device_(device), threads_(std::max(1, threads)) {

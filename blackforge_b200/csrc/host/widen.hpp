@@ -17,8 +17,9 @@ namespace bfb200 {
 // dst[i] = the fp32 value of bf16 src[i] (exact), one thread.
 void widenBf16(const std::uint16_t* src, float* dst, std::size_t count);
 
-// Number of host threads a WidenQueue uses by default: the machine's hardware threads, at most 16; the
-// environment variable BFB_HOST_THREADS overrides it.
+// Number of host threads a WidenQueue uses by default: the machine's hardware threads divided by the number of
+// processes on this host (LOCAL_WORLD_SIZE, when a launcher set it), at most 16; the environment variable
+// BFB_HOST_THREADS overrides it.
 int defaultWidenThreads();
 
 // Jobs run one at a time, in submission order, on a coordinator thread: wait for the job's CUDA event (the

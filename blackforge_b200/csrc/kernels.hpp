@@ -13,6 +13,8 @@ void embedPos(const float* ids, const float* table, const float* pos, void* out,
               cudaStream_t stream);
 void addPositional(const float* in, const float* pos, float* out, int64_t batch, int64_t seq, int64_t dim,
                    int64_t maxSeq, int64_t posOffset, cudaStream_t stream);
+// out[row] = sum over the row of x^2 (the statistic of rmsnorm; see GemmArgs::rowSumSq).
+void rowSumSquares(const void* x, int xDtype, float* out, int64_t rows, int64_t dim, cudaStream_t stream);
 void rmsnorm(const void* x, int xDtype, void* out, int outDtype, int64_t rows, int64_t dim, float eps,
              cudaStream_t stream);
 void softmaxRows(const float* x, float* out, int64_t rows, int64_t cols, cudaStream_t stream);
@@ -50,8 +52,20 @@ struct GemmArgs {
     const float* dAlpha = nullptr;
     int roundCBf16 = 0;
     int* dStatus = nullptr;
+    // Row statistics (CTA-pair tensor-core kernel only, see gemmSupportsRowStats). With rowSumSq set, row i of
+    // the product is multiplied by 1 / sqrt(s_i * rowInvDim + rowEps) before bias and activation, where s_i is
+    // the sum over p < rowSumSqParts of rowSumSq[p * m + i]: an rmsnorm without weights commutes with the matrix
+    // product, so A can be the un-normalised activation. With outSumSq set, the sums of squares of each stored
+    // row (after rounding to the result format) are written per 128-column part to outSumSq[p * m + i],
+    // p < ceil(n / 128): the next norm's statistic without another pass over C, and without atomics.
+    const float* rowSumSq = nullptr;
+    int rowSumSqParts = 1;
+    float rowInvDim = 0.0f;
+    float rowEps = 0.0f;
+    float* outSumSq = nullptr;
 };
 void gemm(const GemmArgs& args, cudaStream_t stream);
+bool gemmSupportsRowStats(const GemmArgs& args);
 // True when the tcgen05 kernel takes this problem (otherwise the CUDA-core kernel runs).
 bool gemmUsesTensorCores(const GemmArgs& args);
 void matmulTransposeB(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, cudaStream_t stream);

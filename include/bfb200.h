@@ -213,6 +213,20 @@ bfb_status bfb_gemm(const void* d_a, const void* d_b, void* d_c, int64_t m, int6
                     int32_t b_layout, int32_t c_dtype, int32_t epilogue, const float* d_bias, const void* d_residual,
                     float alpha, const float* d_alpha, int32_t round_c_bf16, int32_t* d_status, void* stream);
 
+/* rmsnorm fused into the adjacent linear (no reference counterpart as one call: it stands for
+ * rmsnorm, src/backend/cuda/ops_elementwise.cu:102-137, followed by linearBf16, ops_tensorcore.cu:329-387).
+ * An rmsnorm without weights scales each row by 1 / sqrt(mean(x^2) + eps), which commutes with the matrix
+ * product: C[i,:] = epilogue(A[i,:] W^T / sqrt(s_i / k + eps)) with A the UN-normalised activation and s_i the
+ * sum over p < row_sum_sq_parts of d_row_sum_sq[p * m + i]. bfb_row_sum_squares computes s (one part); a
+ * producing GEMM can also deliver it: with d_out_sum_sq set, the sums of squares of every stored row of C are
+ * written there per 128-column part, d_out_sum_sq[p * m + i] for p < ceil(n / 128) (no atomics: the same bits on
+ * every run). d_row_sum_sq and d_out_sum_sq may be NULL. Weights are [n,k] (BFB_B_NK); needs the tensor-core
+ * formats and 16-byte aligned rows, else BFB_UNSUPPORTED. */
+bfb_status bfb_row_sum_squares(const void* d_x, int32_t dtype, float* d_out, int64_t rows, int64_t dim, void* stream);
+bfb_status bfb_gemm_rmsnorm(const void* d_a, const void* d_w, void* d_c, int64_t m, int64_t n, int64_t k,
+                            int32_t ab_dtype, int32_t c_dtype, int32_t epilogue, const float* d_bias,
+                            const void* d_residual, const float* d_row_sum_sq, int32_t row_sum_sq_parts, float eps,
+                            float* d_out_sum_sq, int32_t* d_status, void* stream);
 /* A * B^T on f32: a[M,K], b[N,K] (matmulTransposeB, ops_gemm.cu:95-110, kernel :20-34). */
 bfb_status bfb_matmul_transpose_b(const float* d_a, const float* d_b, float* d_c, int64_t m, int64_t n, int64_t k,
                                   void* stream);

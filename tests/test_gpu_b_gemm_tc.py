@@ -162,3 +162,97 @@ def test_linearity_at_benchmark_width(gpu):
     rhs = gemm(gpu, a1, wt, gpu.BF16, gpu.B_NK) + gemm(gpu, a2, wt, gpu.BF16, gpu.B_NK)
     assert np.array_equal(lhs, rhs)
     assert np.array_equal(lhs[:4], ((a1 + a2)[:4].astype(np.float64) @ w.astype(np.float64)).astype(np.float32))
+
+
+@pytest.mark.parametrize("m,n,k,epilogue,wide", [
+    (300, 264, 136, "none", False),        # ragged rows and an 8-column N tail
+    (512, 512, 256, "bias_silu", False),
+    (384, 1024, 1024, "bias_residual", True),   # the 512-column tile (tests lower its switch-over depth to K = 1024)
+])
+def test_rmsnorm_folded_into_the_gemm(gpu, m, n, k, epilogue, wide):
+    """C = epilogue(rmsnorm(A) W^T) computed as row-scaled (A W^T): the GEMM reads the un-normalised A and divides
+    row i by sqrt(mean(A_i^2) + eps) in its epilogue. Checked against float64 arithmetic on the same bf16
+    operands; the sums of squares of the stored rows come back for the next norm."""
+    rng = np.random.default_rng(m + n + k)
+    a = O.round_bf16((rng.standard_normal((m, k)) * rng.uniform(0.2, 5.0, size=(m, 1))).astype(np.float32))
+    w = O.round_bf16(rng.standard_normal((n, k)).astype(np.float32) * 0.1)
+    bias = rng.standard_normal(n).astype(np.float32)
+    res = O.round_bf16(rng.standard_normal((m, n)).astype(np.float32))
+    d_a, d_w = gpu.upload(a, gpu.BF16), gpu.upload(w, gpu.BF16)
+    d_bias, d_res = gpu.DeviceBuffer.from_numpy(bias), gpu.upload(res, gpu.BF16)
+    d_ss = gpu.DeviceBuffer(m * 4)
+    gpu.check(gpu.lib().bfb_row_sum_squares(d_a.ptr, gpu.BF16, d_ss.ptr, m, k, None))
+    ss = d_ss.to_numpy(np.float32, (m,))
+    want_ss = np.sum(a.astype(np.float64) ** 2, axis=1)
+    assert np.max(np.abs(ss - want_ss) / want_ss) <= 1e-5
+    d_c = gpu.DeviceBuffer(m * n * 2)
+    parts = (n + 127) // 128
+    d_out_ss = gpu.DeviceBuffer(parts * m * 4)
+    status = gpu.DeviceBuffer.zeros(4)
+    epi = gpu.EPI[epilogue]
+    gpu.check(gpu.lib().bfb_gemm_rmsnorm(d_a.ptr, d_w.ptr, d_c.ptr, m, n, k, gpu.BF16, gpu.BF16, epi,
+                                         d_bias.ptr if epilogue != "none" else None,
+                                         d_res.ptr if epilogue == "bias_residual" else None,
+                                         d_ss.ptr, 1, 1e-6, d_out_ss.ptr, status.ptr, None))
+    got = gpu.download(d_c, gpu.BF16, (m, n))
+    assert status.to_numpy(np.int32, (1,))[0] == 0
+    normed = a.astype(np.float64) / np.sqrt(want_ss / k + 1e-6)[:, None]
+    want = normed @ w.astype(np.float64).T
+    if epilogue != "none":
+        want = want + bias
+    if epilogue == "bias_silu":
+        want = want / (1.0 + np.exp(-want))
+    if epilogue == "bias_residual":
+        want = want + res
+    # one rounding to bf16 on top of fp32 accumulation
+    assert np.max(np.abs(got - want) / (np.abs(want) + 0.05)) <= 2.0 ** -8 + 1e-3
+    out_ss = d_out_ss.to_numpy(np.float32, (parts, m))
+    padded = np.zeros((m, parts * 128))
+    padded[:, :n] = got.astype(np.float64) ** 2
+    stored = padded.reshape(m, parts, 128).sum(axis=2).T          # [parts][m], one figure per 128 columns
+    assert np.max(np.abs(out_ss - stored) / (stored + 1e-30)) <= 1e-5
+    # those parts drive the next GEMM exactly like the one-part sums of a separate pass over C
+    d_c2, d_c3 = gpu.DeviceBuffer(m * 64 * 2), gpu.DeviceBuffer(m * 64 * 2)
+    w2 = O.round_bf16(rng.standard_normal((64, n)).astype(np.float32) * 0.1)
+    d_w2 = gpu.upload(w2, gpu.BF16)
+    gpu.check(gpu.lib().bfb_gemm_rmsnorm(d_c.ptr, d_w2.ptr, d_c2.ptr, m, 64, n, gpu.BF16, gpu.BF16, gpu.EPI["none"], None,
+                                         None, d_out_ss.ptr, parts, 1e-6, None, status.ptr, None))
+    d_one = gpu.DeviceBuffer(m * 4)
+    gpu.check(gpu.lib().bfb_row_sum_squares(d_c.ptr, gpu.BF16, d_one.ptr, m, n, None))
+    gpu.check(gpu.lib().bfb_gemm_rmsnorm(d_c.ptr, d_w2.ptr, d_c3.ptr, m, 64, n, gpu.BF16, gpu.BF16, gpu.EPI["none"], None,
+                                         None, d_one.ptr, 1, 1e-6, None, status.ptr, None))
+    got2, got3 = gpu.download(d_c2, gpu.BF16, (m, 64)), gpu.download(d_c3, gpu.BF16, (m, 64))
+    assert np.max(np.abs(got2 - got3) / (np.abs(got3) + 0.05)) <= 2.0 ** -7
+
+
+def test_row_statistics_need_the_tensor_core_kernel(gpu):
+    # rows of 60 bf16 values are not 16-byte multiples: the CUDA-core kernel would run, and it has no row statistics
+    a = np.ones((64, 60), np.float32)
+    d_a, d_w, d_c = gpu.upload(a, gpu.BF16), gpu.upload(a, gpu.BF16), gpu.DeviceBuffer(64 * 64 * 2)
+    d_ss = gpu.DeviceBuffer.zeros(64 * 4)
+    rc = gpu.lib().bfb_gemm_rmsnorm(d_a.ptr, d_w.ptr, d_c.ptr, 64, 64, 60, gpu.BF16, gpu.BF16, gpu.EPI["none"], None, None,
+                                    d_ss.ptr, 1, 1e-6, None, None, None)
+    assert rc == gpu.UNSUPPORTED
+
+
+def test_folded_rmsnorm_gives_the_same_bits_for_any_number_of_rows(gpu):
+    """A sequence must come out the same alone (few rows) and inside a batch (many rows, other tile shapes)."""
+    rng = np.random.default_rng(77)
+    m, n, k = 640, 512, 1024
+    a = O.round_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    w = O.round_bf16(rng.standard_normal((n, k)).astype(np.float32) * 0.1)
+    d_w = gpu.upload(w, gpu.BF16)
+
+    def run(rows):
+        d_a = gpu.upload(a[:rows], gpu.BF16)
+        d_ss, d_c = gpu.DeviceBuffer(rows * 4), gpu.DeviceBuffer(rows * n * 2)
+        d_out = gpu.DeviceBuffer(4 * rows * 4)
+        gpu.check(gpu.lib().bfb_row_sum_squares(d_a.ptr, gpu.BF16, d_ss.ptr, rows, k, None))
+        gpu.check(gpu.lib().bfb_gemm_rmsnorm(d_a.ptr, d_w.ptr, d_c.ptr, rows, n, k, gpu.BF16, gpu.BF16, gpu.EPI["none"],
+                                             None, None, d_ss.ptr, 1, 1e-6, d_out.ptr, None, None))
+        return gpu.download(d_c, gpu.BF16, (rows, n)), d_out.to_numpy(np.float32, (4, rows))
+
+    whole, whole_ss = run(m)
+    for rows in (1, 100, 128, 300):
+        part, part_ss = run(rows)
+        assert np.array_equal(part, whole[:rows]) and np.array_equal(part_ss, whole_ss[:, :rows])

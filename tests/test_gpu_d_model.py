@@ -205,8 +205,18 @@ def test_device_forward_reports_launches(gpu):
     out, shape = m.forward_device(d_ids.ptr, ids.shape, trusted=True)
     gpu.sync()
     assert shape == (1, 128, TC["vocab"])
-    # embed + per layer (norm, qkv, attention, out-proj, norm, ff1, ff2) + final linear on a bf16 stream
-    assert gpu.lib().bfb_launch_count(0) == 1 + 7 * TC["layers"] + 1
+    # on a bf16 stream the GEMMs take the rmsnorm with them: embed, one pass for the first norm's sums of squares,
+    # per layer (qkv, attention, out-proj, ff1, ff2), final linear
+    assert gpu.lib().bfb_launch_count(0) == 2 + 5 * TC["layers"] + 1
+    out.free()
+    # an fp32 stream keeps the separate norm: embed + per layer (norm, qkv, attention, out-proj, norm, ff1, ff2)
+    # + cast for the final linear + final linear
+    m32 = gpu.Model(ops, precision={"storage": "fp32", "compute": "bf16"})
+    m32.forward_device(d_ids.ptr, ids.shape)[0].free()
+    gpu.lib().bfb_launch_count(1)
+    out, shape = m32.forward_device(d_ids.ptr, ids.shape, trusted=True)
+    gpu.sync()
+    assert gpu.lib().bfb_launch_count(0) == 1 + 7 * TC["layers"] + 2
     out.free()
 
 
