@@ -102,6 +102,10 @@ SIGNATURES = {
     "bfb_model_release_master_weights": (_I32, [_P]),
     "bfb_model_load_checkpoint": (_I32, [_P, C.c_char_p]),
     "bfb_model_save_checkpoint": (_I32, [_P, C.c_char_p]),
+    "bfb_model_forward_incremental": (_I32, [_P, _P, C.POINTER(_I64), _I32, _I32, C.POINTER(_P), C.POINTER(_I64),
+                                              C.POINTER(_I32), _P]),
+    "bfb_model_reset_generation": (_I32, [_P]),
+    "bfb_model_generation_position": (_I32, [_P, C.POINTER(_I64)]),
     "bfb_model_forward": (_I32, [_P, _P, C.POINTER(_I64), _I32, _I32, C.POINTER(_P), C.POINTER(_I64),
                                  C.POINTER(_I32), _P]),
     "bfb_model_forward_host": (_I32, [_P, _P, C.POINTER(_I64), _I32, _P, C.POINTER(_I64), C.POINTER(_I32)]),
@@ -347,6 +351,38 @@ class Model:
         buf.ptr = out_ptr.value or 0
         buf.nbytes = int(np.prod(oshape)) * 4
         return buf, oshape
+
+    def forward_incremental_device(self, d_new_ids: int, shape: Sequence[int], trusted: bool = False, stream=None):
+        """Generation: device ids of the NEW positions in, their device logits out: (DeviceBuffer, shape)."""
+        s = (_I64 * len(shape))(*shape)
+        out_shape = (_I64 * 8)()
+        out_rank = _I32(0)
+        out_ptr = _P()
+        check(lib().bfb_model_forward_incremental(self._h, d_new_ids, s, len(shape), int(trusted), C.byref(out_ptr),
+                                                  out_shape, C.byref(out_rank), stream))
+        oshape = tuple(out_shape[i] for i in range(out_rank.value))
+        buf = DeviceBuffer.__new__(DeviceBuffer)
+        buf.ptr = out_ptr.value or 0
+        buf.nbytes = int(np.prod(oshape)) * 4
+        return buf, oshape
+
+    def forward_incremental(self, new_ids) -> np.ndarray:
+        """Host convenience: ids of the new positions [batch, new_len] in, their logits out."""
+        a = np.ascontiguousarray(new_ids, dtype=np.float32)
+        d = DeviceBuffer.from_numpy(a)
+        out, shape = self.forward_incremental_device(d.ptr, a.shape)
+        res = out.to_numpy(np.float32, shape)
+        out.free()
+        d.free()
+        return res
+
+    def reset_generation(self):
+        check(lib().bfb_model_reset_generation(self._h))
+
+    def generation_position(self) -> int:
+        pos = _I64(0)
+        check(lib().bfb_model_generation_position(self._h, C.byref(pos)))
+        return int(pos.value)
 
 
 def host_transfer_bytes():

@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attentionSimtKernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ out,
                     float* __restrict__ mOut, float* __restrict__ lOut, int64_t batch, int64_t newLen,
                     int64_t totalLen, int64_t numHeads, int64_t headDim, int64_t ldQ, int64_t ldK, int64_t ldV,
-                    int64_t ldO, float scale, int64_t oldLen, int causal) {
+                    int64_t ldO, float scale, int64_t oldLen, int causal, int64_t kvBatchRows) {
     const int lane = threadIdx.x & 31;
     const int64_t rowsTotal = batch * numHeads * newLen;
     const int64_t warpGlobal = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
@@ -58,7 +58,7 @@ attentionSimtKernel(const T* __restrict__ q, const T* __restrict__ k, const T* _
         int64_t lastKey = causal ? (oldLen + i) : (totalLen - 1);
         if (lastKey > totalLen - 1) lastKey = totalLen - 1;
         for (int64_t j = 0; j <= lastKey; ++j) {
-            const T* kRow = k + (b * totalLen + j) * ldK + h * headDim;
+            const T* kRow = k + (b * kvBatchRows + j) * ldK + h * headDim;
             float part = 0.0f;
 #pragma unroll
             for (int e = 0; e < kMaxPerLane; ++e) {
@@ -71,7 +71,7 @@ attentionSimtKernel(const T* __restrict__ q, const T* __restrict__ k, const T* _
             const float mNew = fmaxf(mRun, score);
             const float corr = expf(mRun - mNew);
             const float p = expf(score - mNew);
-            const T* vRow = v + (b * totalLen + j) * ldV + h * headDim;
+            const T* vRow = v + (b * kvBatchRows + j) * ldV + h * headDim;
 #pragma unroll
             for (int e = 0; e < kMaxPerLane; ++e) {
                 int64_t d = lane + 32 * e;
@@ -105,6 +105,8 @@ void attentionForward(const AttentionArgs& a, cudaStream_t stream) {
     require(a.oldLen >= 0 && a.oldLen + a.newLen <= a.totalLen, "attention: old_len + new_len exceeds total_len");
     if (a.batch == 0 || a.newLen == 0) return;
     require(a.totalLen > 0, "attention: no keys");
+    require(a.kvBatchRows == 0 || a.kvBatchRows >= a.totalLen, "attention: kv batch stride below total_len");
+    const int64_t kvRows = a.kvBatchRows > 0 ? a.kvBatchRows : a.totalLen;
     require(a.q != nullptr && a.k != nullptr && a.v != nullptr && a.out != nullptr, "attention: null pointer");
 
     if (attentionUsesTensorCores(a)) {
@@ -118,13 +120,13 @@ void attentionForward(const AttentionArgs& a, cudaStream_t stream) {
         attentionSimtKernel<float><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
             static_cast<const float*>(a.q), static_cast<const float*>(a.k), static_cast<const float*>(a.v),
             static_cast<float*>(a.out), a.m, a.l, a.batch, a.newLen, a.totalLen, a.numHeads, a.headDim, a.ldQ, a.ldK,
-            a.ldV, a.ldO, a.scale, a.oldLen, a.causal);
+            a.ldV, a.ldO, a.scale, a.oldLen, a.causal, kvRows);
     } else {
         using bf = __nv_bfloat16;
         attentionSimtKernel<bf><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
             static_cast<const bf*>(a.q), static_cast<const bf*>(a.k), static_cast<const bf*>(a.v),
             static_cast<bf*>(a.out), a.m, a.l, a.batch, a.newLen, a.totalLen, a.numHeads, a.headDim, a.ldQ, a.ldK,
-            a.ldV, a.ldO, a.scale, a.oldLen, a.causal);
+            a.ldV, a.ldO, a.scale, a.oldLen, a.causal, kvRows);
     }
     BFB_LAUNCH_CHECK();
     noteLaunch();

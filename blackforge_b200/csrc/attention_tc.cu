@@ -515,9 +515,11 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
     }
 }
 
-void makeMap(TensorMapStorage* out, const void* base, int64_t dim, int64_t len, int64_t batch, int64_t ld) {
+// `batchRows`: rows from one batch entry to the next (the length itself when densely packed, the capacity for a cache)
+void makeMap(TensorMapStorage* out, const void* base, int64_t dim, int64_t len, int64_t batch, int64_t ld,
+             int64_t batchRows) {
     uint64_t dims[3] = {static_cast<uint64_t>(dim), static_cast<uint64_t>(len), static_cast<uint64_t>(batch)};
-    uint64_t strides[2] = {static_cast<uint64_t>(ld) * 2, static_cast<uint64_t>(ld) * 2 * static_cast<uint64_t>(len)};
+    uint64_t strides[2] = {static_cast<uint64_t>(ld) * 2, static_cast<uint64_t>(ld) * 2 * static_cast<uint64_t>(batchRows)};
     uint32_t box[3] = {64u, 128u, 1u};
     encodeTensorMap(out, base, 2, 3, dims, strides, box);
 }
@@ -537,9 +539,10 @@ bool attentionUsesTensorCores(const AttentionArgs& a) {
 void attentionTensorCore(const AttentionArgs& a, cudaStream_t stream) {
     const int64_t dim = a.numHeads * a.headDim;
     TensorMapStorage tq, tk, tv;
-    makeMap(&tq, a.q, dim, a.newLen, a.batch, a.ldQ);
-    makeMap(&tk, a.k, dim, a.totalLen, a.batch, a.ldK);
-    makeMap(&tv, a.v, dim, a.totalLen, a.batch, a.ldV);
+    const int64_t kvRows = a.kvBatchRows > 0 ? a.kvBatchRows : a.totalLen;
+    makeMap(&tq, a.q, dim, a.newLen, a.batch, a.ldQ, a.newLen);
+    makeMap(&tk, a.k, dim, a.totalLen, a.batch, a.ldK, kvRows);
+    makeMap(&tv, a.v, dim, a.totalLen, a.batch, a.ldV, kvRows);
     AttnParams p;
     p.out = static_cast<__nv_bfloat16*>(a.out);
     p.mOut = a.m;

@@ -431,6 +431,44 @@ bfb_status bfb_model_forward(bfb_model* model, const float* d_input, const int64
     });
 }
 
+bfb_status bfb_model_forward_incremental(bfb_model* model, const float* d_new_ids, const int64_t* shape, int32_t rank,
+                                         int32_t input_range_trusted, float** d_out, int64_t* out_shape,
+                                         int32_t* out_rank, void* stream) {
+    return guarded([&] {
+        require(model != nullptr && d_out != nullptr && out_shape != nullptr && out_rank != nullptr && shape != nullptr,
+                "model_forward_incremental: null argument");
+        require(rank >= 2 && rank <= 8, "model_forward_incremental: bad rank");
+        requireDevice();
+        std::vector<std::size_t> dims(shape, shape + rank);
+        bfb200::DeviceTensor borrowed = bfb200::DeviceTensor::borrow(const_cast<float*>(d_new_ids), dims);
+        bfb200::DeviceTensor result;
+        try {
+            result = model->model->forwardIncremental(borrowed, input_range_trusted != 0, stream);
+        } catch (...) {
+            borrowed.releaseOwnership();
+            throw;
+        }
+        borrowed.releaseOwnership();
+        *out_rank = static_cast<int32_t>(result.rank());
+        for (std::size_t i = 0; i < result.rank(); ++i) out_shape[i] = static_cast<int64_t>(result.dim(i));
+        *d_out = result.releaseOwnership();
+    });
+}
+
+bfb_status bfb_model_reset_generation(bfb_model* model) {
+    return guarded([&] {
+        require(model != nullptr, "model_reset_generation: null model");
+        model->model->resetGenerationState();
+    });
+}
+
+bfb_status bfb_model_generation_position(bfb_model* model, int64_t* position) {
+    return guarded([&] {
+        require(model != nullptr && position != nullptr, "model_generation_position: null argument");
+        *position = static_cast<int64_t>(model->model->generationPosition());
+    });
+}
+
 namespace {
 // slice size of the bf16 result path for small batches: a quarter of the batch
 std::size_t step4(std::size_t batch) { return (batch + 3) / 4; }

@@ -713,6 +713,59 @@ void rowSumSquares(const void* x, int xDtype, float* out, int64_t rows, int64_t 
     noteLaunch();
 }
 
+// ---- key/value cache append ---------------------------------------------------------------------
+// Copies the K and V columns of freshly projected rows ([batch * newLen, ld], K at column kOff, V at vOff, `width`
+// columns each) behind the `oldLen` rows every batch entry of the caches ([batch, capRows, width]) already holds.
+template <typename V>
+__global__ void appendKvKernel(const V* __restrict__ src, int64_t ldV, int64_t kOffV, int64_t vOffV, V* __restrict__ kCache,
+                               V* __restrict__ vCache, int64_t batch, int64_t newLen, int64_t widthV, int64_t capRows,
+                               int64_t oldLen) {
+    const int64_t total = batch * newLen * widthV * 2;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t col = i % widthV;
+        int64_t r = i / widthV;
+        const int which = static_cast<int>(r & 1);   // 0: K, 1: V
+        r >>= 1;
+        const int64_t t = r % newLen, b = r / newLen;
+        const V value = src[(b * newLen + t) * ldV + (which ? vOffV : kOffV) + col];
+        V* dst = which ? vCache : kCache;
+        dst[(b * capRows + oldLen + t) * widthV + col] = value;
+    }
+}
+
+void appendKv(const void* src, int dtype, int64_t ld, int64_t kOffset, int64_t vOffset, void* kCache, void* vCache,
+              int64_t batch, int64_t newLen, int64_t width, int64_t capRows, int64_t oldLen, cudaStream_t stream) {
+    require(dtype == BFB_F32 || dtype == BFB_BF16, "append_kv: format must be f32 or bf16");
+    require(batch >= 0 && newLen >= 0 && width > 0 && oldLen >= 0 && oldLen + newLen <= capRows, "append_kv: bad sizes");
+    if (batch == 0 || newLen == 0) return;
+    require(src != nullptr && kCache != nullptr && vCache != nullptr, "append_kv: null pointer");
+    const int64_t eb = dtypeBytes(dtype);
+    auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    const bool vec = (width * eb) % 16 == 0 && (ld * eb) % 16 == 0 && (kOffset * eb) % 16 == 0 && (vOffset * eb) % 16 == 0 &&
+                     al16(src) && al16(kCache) && al16(vCache);
+    const int64_t per = vec ? 16 / eb : 1;
+    const int64_t total = batch * newLen * (width / per) * 2;
+    const int grid = static_cast<int>(std::min<int64_t>((total + kThreads - 1) / kThreads, static_cast<int64_t>(smCount()) * 8));
+    if (vec) {
+        appendKvKernel<uint4><<<grid, kThreads, 0, stream>>>(static_cast<const uint4*>(src), ld / per, kOffset / per,
+                                                             vOffset / per, static_cast<uint4*>(kCache),
+                                                             static_cast<uint4*>(vCache), batch, newLen, width / per,
+                                                             capRows, oldLen);
+    } else if (dtype == BFB_F32) {
+        appendKvKernel<float><<<grid, kThreads, 0, stream>>>(static_cast<const float*>(src), ld, kOffset, vOffset,
+                                                             static_cast<float*>(kCache), static_cast<float*>(vCache),
+                                                             batch, newLen, width, capRows, oldLen);
+    } else {
+        using bf = __nv_bfloat16;
+        appendKvKernel<bf><<<grid, kThreads, 0, stream>>>(static_cast<const bf*>(src), ld, kOffset, vOffset,
+                                                          static_cast<bf*>(kCache), static_cast<bf*>(vCache), batch,
+                                                          newLen, width, capRows, oldLen);
+    }
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
+
 void softmaxRows(const float* x, float* out, int64_t rows, int64_t cols, cudaStream_t stream) {
     require(rows >= 0 && cols > 0, "softmax: bad sizes");
     if (rows == 0) return;

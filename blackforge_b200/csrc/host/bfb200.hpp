@@ -95,6 +95,22 @@ DeviceTensor selfAttention(const DeviceTensor& input, const DeviceTensor& wq, co
 DeviceTensor selfAttentionBf16(const DeviceTensor& input, const DeviceTensor& wq, const DeviceTensor& wk,
                                const DeviceTensor& wv, const DeviceTensor& wout, std::size_t numHeads);
 
+// include/blackforge/backend/cuda/ops.hpp:213-241 — autoregressive generation at the operator level. `k` / `v`
+// are [batch, length, dim] and grow by the number of new positions on every call; one instance per layer.
+// The result for the new positions equals what selfAttention() gives for them on the whole sequence so far.
+struct KVCache {
+    DeviceTensor k;
+    DeviceTensor v;
+    std::size_t length = 0;
+};
+DeviceTensor concatSeq(const DeviceTensor& a, const DeviceTensor& b);   // along dimension 1 of [batch, len, dim]
+DeviceTensor selfAttentionIncremental(const DeviceTensor& newInput, const DeviceTensor& wq, const DeviceTensor& wk,
+                                      const DeviceTensor& wv, const DeviceTensor& wout, std::size_t numHeads,
+                                      KVCache& cache);
+DeviceTensor selfAttentionIncrementalBf16(const DeviceTensor& newInput, const DeviceTensor& wq, const DeviceTensor& wk,
+                                          const DeviceTensor& wv, const DeviceTensor& wout, std::size_t numHeads,
+                                          KVCache& cache);
+
 // include/blackforge/backend/cuda/fused_attention.hpp:42-57
 struct FusedAttentionForwardResult {
     DeviceTensor output;
@@ -141,6 +157,15 @@ public:
     // Under `storage bf16` every value of forward()'s result is a bf16 number held in an fp32 word. When the
     // pipeline runs from an embedding to a final linear, forwardBf16 writes those same numbers as 2-byte bf16
     // into `deviceOut16` (product(outputShape) elements) instead: half the bytes for a caller that moves them on.
+    // include/blackforge/backend/cuda/model.hpp (forwardIncremental, resetGenerationState): autoregressive
+    // generation. Each call takes the ids of the NEW positions only, [batch, newLen], and returns their outputs;
+    // keys and values of earlier positions stay in per-layer caches, positions continue where the last call
+    // stopped. The batch size is fixed by the first call after a reset. On the planned route (compute bf16 /
+    // fp8.e4m3) the caches are preallocated bf16 buffers sized for the positional table (grown by doubling when
+    // the pipeline has none), filled in place: no re-copy per token.
+    DeviceTensor forwardIncremental(const DeviceTensor& newTokenIds, bool inputRangeTrusted = false, void* stream = nullptr);
+    void resetGenerationState();
+    [[nodiscard]] std::size_t generationPosition() const;
     [[nodiscard]] bool resultIsBf16Exact() const;
     void forwardBf16(const DeviceTensor& input, void* deviceOut16, bool inputRangeTrusted = false, void* stream = nullptr);
 

@@ -118,6 +118,11 @@ struct Layer {
     // converted weights of the planned route (this rank's part)
     DevBuf w0, w1;   // attention: fused QKV^T, Wout^T; feed-forward: W1^T, W2^T; linear: W^T
     DevBuf scales;   // fp8: [0..1] scale/inverse of w0, [2..3] of w1
+    // generation state of an attention layer: the planned route keeps bf16 caches [batch, cacheRows, dim / ranks]
+    // that are filled in place; the fp32 route keeps the operator-level cache
+    DevBuf kCache, vCache;
+    std::size_t cacheRows = 0;
+    KVCache opCache;
 };
 
 }  // namespace
@@ -139,6 +144,8 @@ struct Model::Impl {
     std::vector<ParamMeta> meta;
     std::vector<Layer> layers;
     std::map<std::string, DevBuf> arena;
+    std::size_t genPosition = 0;   // positions already in the caches
+    std::size_t genBatch = 0;      // batch size the caches were opened with
     DevBuf fp8Stats;  // per GEMM input: [amax, scale, inverse, alpha]
     DevBuf status;    // device status word for bounded waits + id range counter
 
@@ -147,6 +154,8 @@ struct Model::Impl {
             l.w0.reset();
             l.w1.reset();
             l.scales.reset();
+            l.kCache.reset();
+            l.vCache.reset();
         }
         for (auto& kv : arena) kv.second.reset();
         fp8Stats.reset();
@@ -183,9 +192,14 @@ struct Model::Impl {
     void setParam(std::size_t index, const float* hostFull);
     void getParam(std::size_t index, float* hostFull);
     void prepare(cudaStream_t stream);
-    DeviceTensor forwardFp32(const DeviceTensor& input, bool trusted);
+    // incremental: `input` holds the ids of the new positions only; keys and values of earlier ones are cached
+    DeviceTensor forwardFp32(const DeviceTensor& input, bool trusted, bool incremental);
     // out16 != nullptr: the final linear writes bf16 there and the returned tensor is empty
-    DeviceTensor forwardPlanned(const DeviceTensor& input, bool trusted, cudaStream_t stream, void* out16);
+    DeviceTensor forwardPlanned(const DeviceTensor& input, bool trusted, cudaStream_t stream, void* out16,
+                                bool incremental);
+    void ensureCache(Layer& l, std::size_t batch, std::size_t width, std::size_t rowsNeeded, std::size_t rowsHint,
+                     cudaStream_t stream);
+    void resetGeneration();
     void checkStatus(cudaStream_t stream, bool checkIds, std::size_t vocab);
 };
 
@@ -400,7 +414,43 @@ void Model::Impl::checkStatus(cudaStream_t stream, bool checkIds, std::size_t vo
 }
 
 // ---- exactness route: op by op on fp32 tensors ----------------------------------------------------------
-DeviceTensor Model::Impl::forwardFp32(const DeviceTensor& input, bool trusted) {
+void Model::Impl::resetGeneration() {
+    genPosition = 0;
+    genBatch = 0;
+    for (Layer& l : layers) {
+        l.kCache.reset();
+        l.vCache.reset();
+        l.cacheRows = 0;
+        l.opCache = KVCache{};
+    }
+}
+
+// Room for `rowsNeeded` positions per batch entry in the layer's caches; `rowsHint` (the positional table's
+// length, 0 when the pipeline has none) sizes them once, otherwise they double. Growing copies the filled rows.
+void Model::Impl::ensureCache(Layer& l, std::size_t batch, std::size_t width, std::size_t rowsNeeded,
+                              std::size_t rowsHint, cudaStream_t stream) {
+    if (l.cacheRows >= rowsNeeded) return;
+    std::size_t rows = std::max<std::size_t>(rowsHint, 256);
+    while (rows < rowsNeeded) rows *= 2;
+    DevBuf nk, nv;
+    nk.ensure(batch * rows * width * 2);
+    nv.ensure(batch * rows * width * 2);
+    if (l.cacheRows > 0 && genPosition > 0) {
+        const std::size_t filled = genPosition * width * 2;
+        BFB_CUDA(cudaMemcpy2DAsync(nk.ptr, rows * width * 2, l.kCache.ptr, l.cacheRows * width * 2, filled, batch,
+                                   cudaMemcpyDeviceToDevice, stream));
+        BFB_CUDA(cudaMemcpy2DAsync(nv.ptr, rows * width * 2, l.vCache.ptr, l.cacheRows * width * 2, filled, batch,
+                                   cudaMemcpyDeviceToDevice, stream));
+        BFB_CUDA(cudaStreamSynchronize(stream));   // the old buffers go back to the pool below
+    }
+    l.kCache.reset();
+    l.vCache.reset();
+    l.kCache = nk;
+    l.vCache = nv;
+    l.cacheRows = rows;
+}
+
+DeviceTensor Model::Impl::forwardFp32(const DeviceTensor& input, bool trusted, bool incremental) {
     require(tpWorld == 1, "Model: tensor parallelism needs compute bf16 or fp8.e4m3");
     DeviceTensor current = input.clone();
     auto roundStorage = [&](DeviceTensor& t) {
@@ -419,10 +469,15 @@ DeviceTensor Model::Impl::forwardFp32(const DeviceTensor& input, bool trusted) {
                 current = (trusted && i == 0) ? embeddingLookupPreValidated(current, params[l.p[0]].value)
                                               : embeddingLookup(current, params[l.p[0]].value);
                 break;
-            case BFB_OP_POSITIONAL_EMBEDDING: current = addPositionalEmbedding(current, params[l.p[0]].value); break;
+            case BFB_OP_POSITIONAL_EMBEDDING:
+                current = addPositionalEmbeddingAt(current, params[l.p[0]].value, incremental ? genPosition : 0);
+                break;
             case BFB_OP_ATTENTION:
-                current = selfAttention(current, params[l.p[0]].value, params[l.p[1]].value, params[l.p[2]].value,
-                                        params[l.p[3]].value, l.heads);
+                current = incremental
+                              ? selfAttentionIncremental(current, params[l.p[0]].value, params[l.p[1]].value,
+                                                         params[l.p[2]].value, params[l.p[3]].value, l.heads, l.opCache)
+                              : selfAttention(current, params[l.p[0]].value, params[l.p[1]].value, params[l.p[2]].value,
+                                              params[l.p[3]].value, l.heads);
                 break;
             case BFB_OP_FEEDFORWARD:
                 current = feedForward(current, params[l.p[0]].value, params[l.p[1]].value, params[l.p[2]].value,
@@ -432,11 +487,13 @@ DeviceTensor Model::Impl::forwardFp32(const DeviceTensor& input, bool trusted) {
         }
         roundStorage(current);
     }
+    if (incremental) genPosition += input.rank() >= 2 ? input.dim(1) : 0;
     return current;
 }
 
 // ---- planned route: tensor-core GEMMs + flash attention -------------------------------------------------
-DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted, cudaStream_t stream, void* out16) {
+DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted, cudaStream_t stream, void* out16,
+                                          bool incremental) {
     prepare(stream);
     status.ensure(2 * sizeof(int));
     BFB_CUDA(cudaMemsetAsync(status.ptr, 0, 2 * sizeof(int), stream));
@@ -458,6 +515,8 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
     };
     bool idsChecked = false;
     std::size_t vocabForCheck = 0;
+    const std::size_t oldLen = incremental ? genPosition : 0;   // positions already cached
+    std::size_t cacheHint = 0;                                 // the positional table's length, when there is one
     int fp8Slot = 0;
     if (fp8) {
         fp8Stats.ensure(layers.size() * 4 * 4 * sizeof(float));
@@ -571,16 +630,17 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                 bool fused = i + 1 < layers.size() && layers[i + 1].kind == BFB_OP_POSITIONAL_EMBEDDING;
                 if (fused) {
                     maxSeq = layers[i + 1].maxSeq;
-                    if (seq > maxSeq) {
-                        throw std::invalid_argument("addPositionalEmbedding: sequence (" + std::to_string(seq) +
+                    if (oldLen + seq > maxSeq) {
+                        throw std::invalid_argument("addPositionalEmbedding: sequence (" + std::to_string(oldLen + seq) +
                                                     ") exceeds maxSeqLen (" + std::to_string(maxSeq) + ")");
                     }
+                    cacheHint = maxSeq;
                     pos = params[layers[i + 1].p[0]].value.data();
                 }
                 x = buf("x", batch * seq * l.outFeat * sb);
                 bfb::embedPos(input.data(), params[l.p[0]].value.data(), pos, x, S, static_cast<int64_t>(batch),
                               static_cast<int64_t>(seq), static_cast<int64_t>(l.vocab), static_cast<int64_t>(l.outFeat),
-                              static_cast<int64_t>(maxSeq), 0, trusted ? nullptr : dOob, stream);
+                              static_cast<int64_t>(maxSeq), static_cast<int64_t>(oldLen), trusted ? nullptr : dOob, stream);
                 idsChecked = !trusted;
                 vocabForCheck = l.vocab;
                 shape = {batch, seq, l.outFeat};
@@ -610,18 +670,34 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                 void* ctx = buf("ctx", tokens * dl * 2);
                 bfb::AttentionArgs a;
                 a.q = qkv;
-                a.k = static_cast<char*>(qkv) + dl * 2;
-                a.v = static_cast<char*>(qkv) + 2 * dl * 2;
                 a.out = ctx;
                 a.dtype = BFB_BF16;
                 a.batch = static_cast<int64_t>(batch);
-                a.newLen = a.totalLen = static_cast<int64_t>(seq);
+                a.newLen = static_cast<int64_t>(seq);
                 a.numHeads = static_cast<int64_t>(hl);
                 a.headDim = static_cast<int64_t>(hd);
-                a.ldQ = a.ldK = a.ldV = static_cast<int64_t>(3 * dl);
+                a.ldQ = static_cast<int64_t>(3 * dl);
                 a.ldO = static_cast<int64_t>(dl);
                 a.scale = 1.0f / std::sqrt(static_cast<float>(hd));
-                a.oldLen = 0;
+                if (incremental) {
+                    // the new keys and values join the layer's cache; attention reads the cache
+                    ensureCache(l, batch, dl, oldLen + seq, cacheHint, stream);
+                    bfb::appendKv(qkv, BFB_BF16, static_cast<int64_t>(3 * dl), static_cast<int64_t>(dl),
+                                  static_cast<int64_t>(2 * dl), l.kCache.ptr, l.vCache.ptr, static_cast<int64_t>(batch),
+                                  static_cast<int64_t>(seq), static_cast<int64_t>(dl), static_cast<int64_t>(l.cacheRows),
+                                  static_cast<int64_t>(oldLen), stream);
+                    a.k = l.kCache.ptr;
+                    a.v = l.vCache.ptr;
+                    a.ldK = a.ldV = static_cast<int64_t>(dl);
+                    a.kvBatchRows = static_cast<int64_t>(l.cacheRows);
+                    a.totalLen = static_cast<int64_t>(oldLen + seq);
+                } else {
+                    a.k = static_cast<char*>(qkv) + dl * 2;
+                    a.v = static_cast<char*>(qkv) + 2 * dl * 2;
+                    a.ldK = a.ldV = static_cast<int64_t>(3 * dl);
+                    a.totalLen = static_cast<int64_t>(seq);
+                }
+                a.oldLen = static_cast<int64_t>(oldLen);
                 a.causal = 1;
                 a.dStatus = dStatus;
                 bfb::attentionForward(a, stream);
@@ -728,6 +804,7 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
         bfb::castScaled(x, S, result.data(), BFB_F32, static_cast<int64_t>(tokensOf() * feat), 1.0f, nullptr, stream);
     }
     checkStatus(stream, idsChecked, vocabForCheck);
+    if (incremental) genPosition += shape.size() >= 2 ? shape[1] : 0;
     return result;
 }
 
@@ -773,10 +850,32 @@ DeviceTensor Model::forward(const DeviceTensor& input, bool inputRangeTrusted, v
             fail(BFB_UNSUPPORTED, "Model: compute bf16 / fp8.e4m3 needs a pipeline that starts with an embedding");
         }
         if (stream != nullptr) BFB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
-        return impl_->forwardFp32(input, inputRangeTrusted);
+        return impl_->forwardFp32(input, inputRangeTrusted, false);
     }
-    return impl_->forwardPlanned(input, inputRangeTrusted, static_cast<cudaStream_t>(stream), nullptr);
+    return impl_->forwardPlanned(input, inputRangeTrusted, static_cast<cudaStream_t>(stream), nullptr, false);
 }
+
+DeviceTensor Model::forwardIncremental(const DeviceTensor& newTokenIds, bool inputRangeTrusted, void* stream) {
+    impl_->allocateParams();
+    if (newTokenIds.rank() < 2) throw std::invalid_argument("forwardIncremental: input [batch, newLen, ...] required");
+    if (impl_->genPosition > 0 && newTokenIds.dim(0) != impl_->genBatch) {
+        throw std::invalid_argument("forwardIncremental: the batch size changed since the caches were opened (" +
+                                    std::to_string(impl_->genBatch) + " -> " + std::to_string(newTokenIds.dim(0)) + ")");
+    }
+    if (impl_->genPosition == 0) impl_->genBatch = newTokenIds.dim(0);
+    bool planned = impl_->mode != Mode::Fp32 && !impl_->layers.empty() && impl_->layers.front().kind == BFB_OP_EMBEDDING;
+    if (!planned) {
+        if (impl_->mode != Mode::Fp32) {
+            fail(BFB_UNSUPPORTED, "Model: compute bf16 / fp8.e4m3 needs a pipeline that starts with an embedding");
+        }
+        if (stream != nullptr) BFB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+        return impl_->forwardFp32(newTokenIds, inputRangeTrusted, true);
+    }
+    return impl_->forwardPlanned(newTokenIds, inputRangeTrusted, static_cast<cudaStream_t>(stream), nullptr, true);
+}
+
+void Model::resetGenerationState() { impl_->resetGeneration(); }
+std::size_t Model::generationPosition() const { return impl_->genPosition; }
 
 bool Model::resultIsBf16Exact() const {
     const bool planned = impl_->mode != Mode::Fp32 && !impl_->layers.empty() && impl_->layers.front().kind == BFB_OP_EMBEDDING;
@@ -787,7 +886,7 @@ void Model::forwardBf16(const DeviceTensor& input, void* deviceOut16, bool input
     require(deviceOut16 != nullptr, "Model::forwardBf16: null output");
     require(resultIsBf16Exact(), "Model::forwardBf16: needs storage bf16 and a pipeline from an embedding to a linear");
     impl_->allocateParams();
-    impl_->forwardPlanned(input, inputRangeTrusted, static_cast<cudaStream_t>(stream), deviceOut16);
+    impl_->forwardPlanned(input, inputRangeTrusted, static_cast<cudaStream_t>(stream), deviceOut16, false);
 }
 
 std::vector<Parameter*> Model::parameters() {

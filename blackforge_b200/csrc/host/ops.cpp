@@ -304,6 +304,44 @@ DeviceTensor selfAttentionImpl(const DeviceTensor& input, const DeviceTensor& wq
     return gemmOp(attn.output, rows, dim, wout, ab, BFB_EPI_RESIDUAL, nullptr, input.data(), {batch, seq, dim});
 }
 
+DeviceTensor selfAttentionIncrementalImpl(const DeviceTensor& newInput, const DeviceTensor& wq, const DeviceTensor& wk,
+                                          const DeviceTensor& wv, const DeviceTensor& wout, std::size_t numHeads,
+                                          KVCache& cache, bool bf16, const char* name) {
+    if (newInput.rank() != 3) throw std::invalid_argument(std::string(name) + ": input [batch, seq, dim] required");
+    std::size_t batch = newInput.dim(0), newLen = newInput.dim(1), dim = newInput.dim(2);
+    if (numHeads == 0 || dim % numHeads != 0) {
+        throw std::invalid_argument(std::string(name) + ": numHeads must divide dim");
+    }
+    for (const DeviceTensor* w : {&wq, &wk, &wv, &wout}) {
+        if (w->rank() != 2 || w->dim(0) != dim || w->dim(1) != dim) {
+            throw std::invalid_argument(std::string(name) + ": projection weights must be [dim, dim]");
+        }
+    }
+    if (cache.length > 0 && (cache.k.rank() != 3 || cache.k.dim(0) != batch || cache.k.dim(2) != dim ||
+                             cache.k.dim(1) != cache.length)) {
+        throw std::invalid_argument(std::string(name) + ": the cache does not belong to this batch / width");
+    }
+    float scaleFactor = 1.0f / std::sqrt(static_cast<float>(dim / numHeads));
+    int ab = bf16 ? BFB_BF16 : BFB_F32;
+    // the norm is per position, so normalising the new positions alone is exact
+    DeviceTensor normed = rmsnorm(newInput);
+    std::size_t rows = batch * newLen;
+    DeviceTensor q = gemmOp(normed, rows, dim, wq, ab, BFB_EPI_NONE, nullptr, nullptr, {batch, newLen, dim});
+    DeviceTensor kNew = gemmOp(normed, rows, dim, wk, ab, BFB_EPI_NONE, nullptr, nullptr, {batch, newLen, dim});
+    DeviceTensor vNew = gemmOp(normed, rows, dim, wv, ab, BFB_EPI_NONE, nullptr, nullptr, {batch, newLen, dim});
+    const std::size_t oldLen = cache.length;
+    if (oldLen == 0) {
+        cache.k = std::move(kNew);
+        cache.v = std::move(vNew);
+    } else {
+        cache.k = concatSeq(cache.k, kNew);
+        cache.v = concatSeq(cache.v, vNew);
+    }
+    cache.length = oldLen + newLen;
+    FusedAttentionForwardResult attn = attentionImpl(q, cache.k, cache.v, numHeads, scaleFactor, oldLen, bf16);
+    return gemmOp(attn.output, rows, dim, wout, ab, BFB_EPI_RESIDUAL, nullptr, newInput.data(), {batch, newLen, dim});
+}
+
 DeviceTensor feedForwardImpl(const DeviceTensor& input, const DeviceTensor& w1, const DeviceTensor& b1,
                              const DeviceTensor& w2, const DeviceTensor& b2, bool bf16, const char* name) {
     if (input.rank() < 2) throw std::invalid_argument(std::string(name) + ": input of rank >= 2 required");
@@ -534,6 +572,39 @@ DeviceTensor feedForward(const DeviceTensor& input, const DeviceTensor& w1, cons
 DeviceTensor feedForwardBf16(const DeviceTensor& input, const DeviceTensor& w1, const DeviceTensor& b1,
                              const DeviceTensor& w2, const DeviceTensor& b2) {
     return feedForwardImpl(input, w1, b1, w2, b2, true, "feedForwardBf16");
+}
+
+// ops_transformer.cu:159-167 (concatSeq): [batch, la, dim] ++ [batch, lb, dim] -> [batch, la + lb, dim].
+DeviceTensor concatSeq(const DeviceTensor& a, const DeviceTensor& b) {
+    if (a.rank() != 3 || b.rank() != 3 || a.dim(0) != b.dim(0) || a.dim(2) != b.dim(2)) {
+        throw std::invalid_argument("concatSeq: tensors must be [batch, len, dim] with equal batch and dim");
+    }
+    const std::size_t batch = a.dim(0), la = a.dim(1), lb = b.dim(1), dim = a.dim(2);
+    DeviceTensor out({batch, la + lb, dim});
+    if (batch == 0 || dim == 0) return out;
+    const std::size_t pitch = (la + lb) * dim * sizeof(float);
+    // one strided copy per source: each batch entry is a "row" of la * dim (lb * dim) floats
+    if (la > 0) {
+        BFB_CUDA(cudaMemcpy2DAsync(out.data(), pitch, a.data(), la * dim * sizeof(float), la * dim * sizeof(float), batch,
+                                   cudaMemcpyDeviceToDevice, nullptr));
+    }
+    if (lb > 0) {
+        BFB_CUDA(cudaMemcpy2DAsync(out.data() + la * dim, pitch, b.data(), lb * dim * sizeof(float),
+                                   lb * dim * sizeof(float), batch, cudaMemcpyDeviceToDevice, nullptr));
+    }
+    return out;
+}
+
+DeviceTensor selfAttentionIncremental(const DeviceTensor& newInput, const DeviceTensor& wq, const DeviceTensor& wk,
+                                      const DeviceTensor& wv, const DeviceTensor& wout, std::size_t numHeads,
+                                      KVCache& cache) {
+    return selfAttentionIncrementalImpl(newInput, wq, wk, wv, wout, numHeads, cache, false, "selfAttentionIncremental");
+}
+
+DeviceTensor selfAttentionIncrementalBf16(const DeviceTensor& newInput, const DeviceTensor& wq, const DeviceTensor& wk,
+                                          const DeviceTensor& wv, const DeviceTensor& wout, std::size_t numHeads,
+                                          KVCache& cache) {
+    return selfAttentionIncrementalImpl(newInput, wq, wk, wv, wout, numHeads, cache, true, "selfAttentionIncrementalBf16");
 }
 
 DeviceTensor selfAttention(const DeviceTensor& input, const DeviceTensor& wq, const DeviceTensor& wk,

@@ -13,6 +13,10 @@ void embedPos(const float* ids, const float* table, const float* pos, void* out,
               cudaStream_t stream);
 void addPositional(const float* in, const float* pos, float* out, int64_t batch, int64_t seq, int64_t dim,
                    int64_t maxSeq, int64_t posOffset, cudaStream_t stream);
+// Key/value cache append: the K and V column blocks of `src` ([batch * newLen, ld]; K at column kOffset, V at
+// vOffset, `width` columns each) go behind the oldLen rows each batch entry of the caches [batch, capRows, width] holds.
+void appendKv(const void* src, int dtype, int64_t ld, int64_t kOffset, int64_t vOffset, void* kCache, void* vCache,
+              int64_t batch, int64_t newLen, int64_t width, int64_t capRows, int64_t oldLen, cudaStream_t stream);
 // out[row] = sum over the row of x^2 (the statistic of rmsnorm; see GemmArgs::rowSumSq).
 void rowSumSquares(const void* x, int xDtype, float* out, int64_t rows, int64_t dim, cudaStream_t stream);
 void rmsnorm(const void* x, int xDtype, void* out, int outDtype, int64_t rows, int64_t dim, float eps,
@@ -80,6 +84,9 @@ struct AttentionArgs {
     int dtype = 0;
     int64_t batch = 0, newLen = 0, totalLen = 0, numHeads = 0, headDim = 0;
     int64_t ldQ = 0, ldK = 0, ldV = 0, ldO = 0;
+    // rows between one batch entry of K / V and the next; 0 means total_len (densely packed). A key/value cache
+    // with room for more positions than it holds passes its capacity here.
+    int64_t kvBatchRows = 0;
     float scale = 1.0f;
     int64_t oldLen = 0;
     int causal = 1;

@@ -298,6 +298,18 @@ bfb_status bfb_model_save_checkpoint(bfb_model* model, const char* path);
 bfb_status bfb_model_forward(bfb_model* model, const float* d_input, const int64_t* shape, int32_t rank,
                              int32_t input_range_trusted, float** d_out, int64_t* out_shape, int32_t* out_rank,
                              void* stream);
+/* Autoregressive generation (Model::forwardIncremental / resetGenerationState, model.cu:385-431; caller
+ * runGenerate, src/main.cpp:524-627). d_new_ids holds the ids of the NEW positions only, [batch, new_len] as f32;
+ * the result (pool memory, f32, release with bfb_pool_release) is their output, equal to what bfb_model_forward
+ * gives for those positions on the whole sequence so far. Keys and values of earlier positions stay in per-layer
+ * caches; the batch size is fixed by the first call after a reset. Where the reference re-copies the whole cache
+ * for every token (concatSeq, ops_transformer.cu:159-167), the bf16 / e4m3 routes keep preallocated bf16 caches
+ * sized for the positional table and append in place. */
+bfb_status bfb_model_forward_incremental(bfb_model* model, const float* d_new_ids, const int64_t* shape, int32_t rank,
+                                         int32_t input_range_trusted, float** d_out, int64_t* out_shape,
+                                         int32_t* out_rank, void* stream);
+bfb_status bfb_model_reset_generation(bfb_model* model);
+bfb_status bfb_model_generation_position(bfb_model* model, int64_t* position);
 /* The `blackforge run` path (src/main.cpp:356-388): host ids in, host logits out, synchronous.
  * h_out must hold product(out_shape) floats; call once with h_out == NULL to learn the shape. */
 bfb_status bfb_model_forward_host(bfb_model* model, const float* h_input, const int64_t* shape, int32_t rank,
