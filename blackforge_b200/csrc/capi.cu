@@ -485,12 +485,18 @@ HostTransfer& hostTransfer() {
 
 // Share (percent) of the result slices that the host-buffer path moves as bf16 and widens on host threads when
 // the result is bf16-exact; the rest is copied as fp32. The 2-byte way halves the link time but costs host
-// cores and host memory bandwidth (the fp32 words are written by the CPU on top of the incoming copy). Measured
-// on a 16-core host with a PCIe 5 x16 link, 2 G logits per call: all slices narrow 138 ms, three quarters
-// 148 ms, half 158 ms, none 168-182 ms. So: everything with 12 or more host threads, half with 6 or more, none
-// below (plain fp32 copies). BFB_HOST_NARROW_PCT overrides (0..100).
+// cores and twice the host memory traffic (the fp32 words are written by the CPU on top of the incoming copy).
+// Measured with 2 G logits per call: one process on a 16-core host with a PCIe 5 x16 link, all slices narrow
+// 127-138 ms, three quarters 148 ms, half 158 ms, none 168-182 ms (bound by the link); four processes on a 32-core
+// host, half narrow 487 ms per step, because they share the host's memory bandwidth, which is then the limit and
+// which the plain copies load least. So: everything when this process has the host to itself and 12 or more
+// threads, half with 6 or more, none below or when a launcher reports several processes on the host
+// (LOCAL_WORLD_SIZE > 1). BFB_HOST_NARROW_PCT overrides (0..100).
 int narrowSharePercent() {
     if (const char* e = std::getenv("BFB_HOST_NARROW_PCT")) return std::max(0, std::min(100, std::atoi(e)));
+    if (const char* e = std::getenv("LOCAL_WORLD_SIZE")) {
+        if (std::atoi(e) > 1) return 0;
+    }
     const int threads = bfb200::defaultWidenThreads();
     return threads >= 12 ? 100 : (threads >= 6 ? 50 : 0);
 }
