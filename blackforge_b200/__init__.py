@@ -79,6 +79,7 @@ SIGNATURES = {
     "bfb_cast": (_I32, [_P, _I32, _P, _I32, _I64, _F, _P, _P]),
     "bfb_amax": (_I32, [_P, _I32, _I64, _P, _P]),
     "bfb_fp8_scale_from_amax": (_I32, [_P, _P, _P]),
+    "bfb_rmsnorm_quantize_e4m3": (_I32, [_P, _I64, _I64, _F, _P, _P, _P, _P]),
     "bfb_quantize_e4m3": (_I32, [_P, _I32, _I64, _P, _P, _P, _P]),
     "bfb_quantize_e4m3_static": (_I32, [_P, _I32, _I64, _P, _P, _P, _P]),
     "bfb_weight_prepare": (_I32, [_P, _P, _I32, _I64, _I64, _F, _P, _P]),

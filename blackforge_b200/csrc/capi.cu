@@ -201,6 +201,24 @@ bfb_status bfb_quantize_e4m3(const void* d_in, int32_t in_dtype, int64_t n, void
     });
 }
 
+bfb_status bfb_rmsnorm_quantize_e4m3(const void* d_x, int64_t rows, int64_t dim, float eps, void* d_out, float* d_scales,
+                                     const float* d_weight_inverse, void* stream) {
+    return guarded([&] {
+        require(rows >= 0, "rmsnorm_quantize_e4m3: negative size");
+        requireDevice();
+        const size_t bytes = static_cast<size_t>(bfb::rmsnormQuantizeScratchFloats(rows)) * sizeof(float);
+        float* scratch = static_cast<float*>(bfb::poolAcquire(bytes));
+        try {
+            bfb::rmsnormQuantizeE4m3(d_x, rows, dim, eps, d_out, d_scales, d_weight_inverse, scratch, asStream(stream));
+        } catch (...) {
+            bfb::poolRelease(scratch, bytes);
+            throw;
+        }
+        // work on `stream` is ordered before any later use of the buffer on the same stream
+        bfb::poolRelease(scratch, bytes);
+    });
+}
+
 bfb_status bfb_weight_prepare(const float* d_w, void* d_out, int32_t out_dtype, int64_t k, int64_t n, float scale,
                               const float* d_scale, void* stream) {
     return guarded([&] { bfb::weightPrepare(d_w, d_out, out_dtype, k, n, scale, d_scale, asStream(stream)); });

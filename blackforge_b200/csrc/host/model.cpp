@@ -540,6 +540,19 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
         *dAlpha = st + 2;
         return a8;
     };
+    // e4m3 A-operand of the GEMM that follows an rmsnorm, straight from the bf16 residual stream: the norm and
+    // the quantisation in two passes over x, without a normalised copy in between
+    auto normedFp8Input = [&](std::size_t tokens, std::size_t d, const float* wScales, const float** dAlpha) -> const void* {
+        float* st = static_cast<float*>(fp8Stats.ptr) + 4 * (fp8Slot++);
+        void* a8 = buf("act8_d", tokens * d);
+        float* scratch = static_cast<float*>(
+            buf("norm_quant", static_cast<std::size_t>(bfb::rmsnormQuantizeScratchFloats(static_cast<int64_t>(tokens))) *
+                                  sizeof(float)));
+        bfb::rmsnormQuantizeE4m3(x, static_cast<int64_t>(tokens), static_cast<int64_t>(d), 1e-6f, a8, st, wScales + 1,
+                                 scratch, stream);
+        *dAlpha = st + 2;
+        return a8;
+    };
     auto runGemm = [&](const void* a, const void* w, void* c, std::size_t m, std::size_t n, std::size_t k, int cDtype,
                        int epilogue, const float* bias, const void* residual, const float* dAlpha, int roundC,
                        const float* rowSumSq = nullptr, int rowSumSqParts = 1, float* outSumSq = nullptr) {
@@ -661,6 +674,9 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                     const float* sums = needSumSq(tokens, d);
                     runGemm(x, l.w0.ptr, qkv, tokens, 3 * dl, d, BFB_BF16, BFB_EPI_NONE, nullptr, nullptr, nullptr, 0, sums,
                             ssParts, nullptr);
+                } else if (fp8 && S == BFB_BF16) {
+                    const void* aQkv = normedFp8Input(tokens, d, sc, &dAlpha);
+                    runGemm(aQkv, l.w0.ptr, qkv, tokens, 3 * dl, d, BFB_BF16, BFB_EPI_NONE, nullptr, nullptr, dAlpha, 0);
                 } else {
                     void* normed = buf("normed", tokens * d * 2);
                     bfb::rmsnorm(x, S, normed, BFB_BF16, static_cast<int64_t>(tokens), static_cast<int64_t>(d), 1e-6f, stream);
@@ -721,6 +737,10 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                     const float* sums = needSumSq(tokens, d);
                     runGemm(x, l.w0.ptr, hidden, tokens, fl, d, BFB_BF16, BFB_EPI_BIAS_SILU, params[l.p[1]].value.data(),
                             nullptr, nullptr, 0, sums, ssParts, nullptr);
+                } else if (fp8 && S == BFB_BF16) {
+                    const void* a1 = normedFp8Input(tokens, d, sc, &dAlpha);
+                    runGemm(a1, l.w0.ptr, hidden, tokens, fl, d, BFB_BF16, BFB_EPI_BIAS_SILU, params[l.p[1]].value.data(),
+                            nullptr, dAlpha, 0);
                 } else {
                     void* normed = buf("normed", tokens * d * 2);
                     bfb::rmsnorm(x, S, normed, BFB_BF16, static_cast<int64_t>(tokens), static_cast<int64_t>(d), 1e-6f, stream);

@@ -37,6 +37,12 @@ void weightPrepare(const float* w, void* out, int outDtype, int64_t k, int64_t n
 int64_t quantizeScratchFloats(int64_t n);
 void quantizeE4m3(const void* in, int inDtype, int64_t n, void* out, float* dScales, const float* dWeightInverse,
                   float* scratch, cudaStream_t stream);
+// rmsnorm (no weights) of bf16 rows followed by per-tensor e4m3 quantisation, without storing the normalised rows:
+// out = e4m3(bf16(x * r_row) * scale), scale = 448 / max|bf16(x * r_row)|; dScales as for quantizeE4m3. `scratch`
+// holds rmsnormQuantizeScratchFloats(rows) floats.
+int64_t rmsnormQuantizeScratchFloats(int64_t rows);
+void rmsnormQuantizeE4m3(const void* x, int64_t rows, int64_t dim, float eps, void* out, float* dScales,
+                         const float* dWeightInverse, float* scratch, cudaStream_t stream);
 // Seeded N(0, sigma) values for the [rows, colsLocal] block at (rowOffset, colOffset) of a tensor with colsFull
 // columns; a value depends only on the seed and its position in the full tensor.
 void fillNormal(float* out, int64_t rows, int64_t colsLocal, int64_t colsFull, int64_t rowOffset, int64_t colOffset,

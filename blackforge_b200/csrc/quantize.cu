@@ -3,6 +3,7 @@
 // array, (2) one block folds the partial maxima into {scale, 1/scale, 1/scale * weight inverse},
 // (3) the conversion. No atomics, so the result does not depend on block scheduling.
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 
 #include <algorithm>
 #include <mutex>
@@ -97,7 +98,145 @@ finalizeScaleKernel(const float* __restrict__ partial, int64_t count, float* __r
     }
 }
 
+// ---- rmsnorm + quantisation in two passes over x ---------------------------------------------------------
+// Pass 1: one warp per row: r = 1 / sqrt(mean(x^2) + eps) to rowInv[row], and the block's maximum of
+// |bf16(x * r)| (what a separate norm would have stored) to partial[block]. Pass 2: e4m3(bf16(x * r) * scale).
+// x is read twice (2 + 2 bytes per element) and e4m3 written once, against 9 bytes per element for a norm that
+// writes bf16, a maximum pass and a conversion pass.
+constexpr int kNormThreads = 256;
+
+__device__ __forceinline__ float bf16Rounded(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__global__ void __launch_bounds__(kNormThreads)
+normAmaxKernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t dim, float eps, float* __restrict__ rowInv,
+               float* __restrict__ partial, int vectorised) {
+    __shared__ float warpMax[kNormThreads / 32];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int64_t warpsPerGrid = static_cast<int64_t>(gridDim.x) * (kNormThreads / 32);
+    float blockMax = 0.0f;
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * (kNormThreads / 32) + warp; row < rows; row += warpsPerGrid) {
+        const __nv_bfloat16* src = x + row * dim;
+        float ss = 0.0f, mx = 0.0f;   // |x * r| is largest where |x| is: one pass gives both
+        if (vectorised) {
+            for (int64_t i = static_cast<int64_t>(lane) * 8; i < dim; i += 256) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(src + i);
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(h[j]);
+                    ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
+                    mx = fmaxf(mx, fmaxf(fabsf(f.x), fabsf(f.y)));
+                }
+            }
+        } else {
+            for (int64_t i = lane; i < dim; i += 32) {
+                const float v = __bfloat162float(src[i]);
+                ss = fmaf(v, v, ss);
+                mx = fmaxf(mx, fabsf(v));
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+        }
+        const float inv = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps);
+        if (lane == 0) rowInv[row] = inv;
+        // rounding to bf16 is monotonic, so the largest normalised magnitude is that of the largest |x|
+        blockMax = fmaxf(blockMax, bf16Rounded(mx * inv));
+    }
+    if (lane == 0) warpMax[warp] = blockMax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = warpMax[0];
+#pragma unroll
+        for (int w = 1; w < kNormThreads / 32; ++w) t = fmaxf(t, warpMax[w]);
+        partial[blockIdx.x] = t;
+    }
+}
+
+// 8 elements per thread; dim is a multiple of 8, so a vector never straddles two rows.
+__global__ void __launch_bounds__(kNormThreads)
+normQuantizeKernel(const uint4* __restrict__ x, uint2* __restrict__ out, int64_t nVec, int64_t vecsPerRow,
+                   const float* __restrict__ rowInv, const float* __restrict__ scales) {
+    const float scale = scales[0];
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nVec; i += stride) {
+        const float inv = __ldg(rowInv + i / vecsPerRow);
+        const uint4 raw = x[i];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        uint2 packed;
+        __nv_fp8x2_storage_t* o = reinterpret_cast<__nv_fp8x2_storage_t*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            o[j] = __nv_cvt_float2_to_fp8x2(make_float2(bf16Rounded(f.x * inv) * scale, bf16Rounded(f.y * inv) * scale),
+                                            __NV_SATFINITE, __NV_E4M3);
+        }
+        out[i] = packed;
+    }
+}
+
+__global__ void normQuantizeScalarKernel(const __nv_bfloat16* __restrict__ x, __nv_fp8_storage_t* __restrict__ out,
+                                         int64_t n, int64_t dim, const float* __restrict__ rowInv,
+                                         const float* __restrict__ scales) {
+    const float scale = scales[0];
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float v = bf16Rounded(__bfloat162float(x[i]) * rowInv[i / dim]) * scale;
+        out[i] = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+    }
+}
+
+int normAmaxBlocks(int64_t rows) {
+    return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>((rows + kNormThreads / 32 - 1) / (kNormThreads / 32),
+                                                                 static_cast<int64_t>(smCount()) * 8)));
+}
+
 }  // namespace
+
+int64_t rmsnormQuantizeScratchFloats(int64_t rows) { return rows + normAmaxBlocks(rows); }
+
+void rmsnormQuantizeE4m3(const void* x, int64_t rows, int64_t dim, float eps, void* out, float* dScales,
+                         const float* dWeightInverse, float* scratch, cudaStream_t stream) {
+    require(rows >= 0 && dim > 0, "rmsnorm_quantize_e4m3: bad sizes");
+    require(dScales != nullptr && scratch != nullptr, "rmsnorm_quantize_e4m3: null scale or scratch pointer");
+    if (rows > 0) require(x != nullptr && out != nullptr, "rmsnorm_quantize_e4m3: null pointer");
+    float* rowInv = scratch;
+    float* partial = scratch + rows;
+    const int blocks = normAmaxBlocks(rows);
+    const bool vec = dim % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0;
+    const double elems = static_cast<double>(rows) * static_cast<double>(dim);
+    if (rows > 0) {
+        ProfileScope prof(kProfRmsnorm, stream, elems * 2.0);
+        normAmaxKernel<<<blocks, kNormThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, dim, eps, rowInv,
+                                                            partial, vec ? 1 : 0);
+        BFB_LAUNCH_CHECK();
+        noteLaunch();
+    }
+    finalizeScaleKernel<<<1, 1024, 0, stream>>>(partial, rows > 0 ? blocks : 0, dScales, dWeightInverse);
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+    if (rows == 0) return;
+    ProfileScope prof(kProfCast, stream, elems * 3.0);
+    const int64_t n = rows * dim;
+    if (vec) {
+        const int64_t nVec = n / 8;
+        const int grid = static_cast<int>(std::min<int64_t>((nVec + kNormThreads - 1) / kNormThreads,
+                                                            static_cast<int64_t>(smCount()) * 16));
+        normQuantizeKernel<<<grid, kNormThreads, 0, stream>>>(static_cast<const uint4*>(x), static_cast<uint2*>(out), nVec,
+                                                              dim / 8, rowInv, dScales);
+    } else {
+        const int grid = static_cast<int>(std::min<int64_t>((n + kNormThreads - 1) / kNormThreads,
+                                                            static_cast<int64_t>(smCount()) * 16));
+        normQuantizeScalarKernel<<<grid, kNormThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
+                                                                    static_cast<__nv_fp8_storage_t*>(out), n, dim, rowInv,
+                                                                    dScales);
+    }
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
 
 int64_t quantizeScratchFloats(int64_t n) { return std::max<int64_t>(1, (n + kChunkElems - 1) / kChunkElems); }
 

@@ -173,6 +173,13 @@ bfb_status bfb_fp8_scale_from_amax(const float* d_amax, float* d_scales, void* s
  * of the call. Deterministic (no atomics). No counterpart in the reference (fp8 is declared only). */
 bfb_status bfb_quantize_e4m3(const void* d_in, int32_t in_dtype, int64_t n, void* d_out, float* d_scales,
                              const float* d_weight_inverse, void* stream);
+/* rmsnorm (ops_elementwise.cu:102-137, no weights) of bf16 rows and the per-tensor e4m3 quantisation of the result
+ * in one call, without storing the normalised rows: d_out = e4m3(bf16(x * r_row) * d_scales[0]) with
+ * r_row = 1 / sqrt(mean(x_row^2) + eps) and d_scales as for bfb_quantize_e4m3 (the maximum is taken over the
+ * normalised bf16 values). Two passes over x instead of a norm, a maximum pass and a conversion. Scratch
+ * (one float per row and per block) comes from the device pool for the duration of the call. */
+bfb_status bfb_rmsnorm_quantize_e4m3(const void* d_x, int64_t rows, int64_t dim, float eps, void* d_out, float* d_scales,
+                                     const float* d_weight_inverse, void* stream);
 /* Same operation and results as bfb_quantize_e4m3, for callers that must not allocate device memory while
  * they run: a host engine that gave the whole GPU to its own arena at start-up, or a latency-critical
  * serving loop where a trip into the device allocator can stall every stream. This entry point has no

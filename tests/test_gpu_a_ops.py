@@ -315,3 +315,28 @@ def test_quantize_e4m3_one_call(gpu, n, dtype_name):
     assert scales.to_numpy(np.float32, (3,)).tolist() == [1.0, 1.0, 1.0]
     assert gpu.lib().bfb_quantize_e4m3(None, gpu.F32, 0, None, scales.ptr, None, None) == gpu.OK
     assert gpu.lib().bfb_quantize_e4m3(src.ptr, gpu.FP8_E4M3, n, out.ptr, scales.ptr, None, None) == gpu.INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("rows,dim", [(37, 2048), (5, 300), (64, 8192), (3, 8)])
+def test_rmsnorm_quantize_e4m3_equals_norm_then_quantize(gpu, rows, dim):
+    """The fused call must give what rmsnorm to bf16 followed by bfb_quantize_e4m3 gives: same scale, same codes
+    (a last-bit difference in a row's 1/rms may move single values across a rounding boundary)."""
+    rng = np.random.default_rng(rows * dim)
+    x = O.round_bf16((rng.standard_normal((rows, dim)) * rng.uniform(0.1, 4.0, size=(rows, 1))).astype(np.float32))
+    src = gpu.upload(x, gpu.BF16)
+    normed = gpu.DeviceBuffer(x.size * 2)
+    gpu.check(gpu.lib().bfb_rmsnorm(src.ptr, gpu.BF16, normed.ptr, gpu.BF16, rows, dim, 1e-6, None))
+    want_q, want_s = gpu.DeviceBuffer(x.size), gpu.DeviceBuffer.zeros(12)
+    winv = gpu.DeviceBuffer.from_numpy(np.array([0.5], np.float32))
+    gpu.check(gpu.lib().bfb_quantize_e4m3(normed.ptr, gpu.BF16, x.size, want_q.ptr, want_s.ptr, winv.ptr, None))
+    got_q, got_s = gpu.DeviceBuffer(x.size), gpu.DeviceBuffer.zeros(12)
+    gpu.check(gpu.lib().bfb_rmsnorm_quantize_e4m3(src.ptr, rows, dim, 1e-6, got_q.ptr, got_s.ptr, winv.ptr, None))
+    ws, gs = want_s.to_numpy(np.float32, (3,)), got_s.to_numpy(np.float32, (3,))
+    assert np.max(np.abs(ws - gs) / ws) <= 2.0 ** -7            # the maximum may sit one bf16 step apart
+    a = gpu.download(want_q, gpu.FP8_E4M3, x.shape)
+    b = gpu.download(got_q, gpu.FP8_E4M3, x.shape)
+    if np.array_equal(ws, gs):
+        assert np.mean(a != b) <= 2e-3 and np.max(np.abs(a - b) / (np.abs(a) + 2.0 ** -6)) <= 0.13
+    # against the definition: oracle rmsnorm, rounded to bf16, scaled by this call's scale, rounded to e4m3
+    want = O.e4m3_round_hw(O.round_bf16(O.rmsnorm(x)) * gs[0])
+    assert np.mean(b != want) <= 2e-3
