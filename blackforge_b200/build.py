@@ -26,6 +26,7 @@ SOURCES = [
     "gemm_simt.cu",
     "gemm_tc.cu",
     "gemm_tc2.cu",
+    "gemm_skinny.cu",
     "attention_simt.cu",
     "attention_tc.cu",
     "capi.cu",

@@ -281,6 +281,38 @@ bfb_status bfb_gemm_rmsnorm(const void* d_a, const void* d_w, void* d_c, int64_t
     });
 }
 
+bfb_status bfb_gemm_few_rows(const void* d_a, const void* d_w, void* d_c, int64_t m, int64_t n, int64_t k, int32_t ab_dtype,
+                             int32_t c_dtype, int32_t epilogue, const float* d_bias, const void* d_residual, float alpha,
+                             const float* d_row_sum_sq, int32_t row_sum_sq_parts, float eps, float* d_out_sum_sq,
+                             int32_t* d_status, void* stream) {
+    return guarded([&] {
+        bfb::GemmArgs g;
+        g.a = d_a;
+        g.b = d_w;
+        g.c = d_c;
+        g.m = m;
+        g.n = n;
+        g.k = k;
+        g.abDtype = ab_dtype;
+        g.bLayout = BFB_B_NK;
+        g.cDtype = c_dtype;
+        g.epilogue = epilogue;
+        g.bias = d_bias;
+        g.residual = d_residual;
+        g.alpha = alpha;
+        g.rowSumSq = d_row_sum_sq;
+        g.rowSumSqParts = row_sum_sq_parts;
+        g.rowInvDim = k > 0 ? 1.0f / static_cast<float>(k) : 0.0f;
+        g.rowEps = eps;
+        g.outSumSq = d_out_sum_sq;
+        g.dStatus = d_status;
+        g.preferSkinny = 1;
+        bfb::require(bfb::gemmSkinnyEligible(g) || m == 0 || n == 0,
+                     "gemm_few_rows: needs 1..128 rows, k > 0, tensor-core formats and 16-byte aligned rows");
+        bfb::gemm(g, asStream(stream));
+    });
+}
+
 bfb_status bfb_matmul_transpose_b(const float* d_a, const float* d_b, float* d_c, int64_t m, int64_t n, int64_t k,
                                   void* stream) {
     return guarded([&] { bfb::matmulTransposeB(d_a, d_b, d_c, m, n, k, asStream(stream)); });

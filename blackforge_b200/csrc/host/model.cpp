@@ -577,6 +577,8 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
         g.rowInvDim = k > 0 ? 1.0f / static_cast<float>(k) : 0.0f;
         g.rowEps = 1e-6f;
         g.outSumSq = outSumSq;
+        // a generation step has a handful of rows: stream the weights through every SM instead of tiling C
+        g.preferSkinny = incremental && m <= 128 ? 1 : 0;
         bfb::gemm(g, stream);
     };
 

@@ -73,9 +73,18 @@ struct GemmArgs {
     float rowInvDim = 0.0f;
     float rowEps = 0.0f;
     float* outSumSq = nullptr;
+    // Few rows (a generation step): stream the weights through as many SMs as possible instead of tiling C (see
+    // gemm_skinny.cu). Takes effect for 1..128 rows with [N,K] weights in a tensor-core format; has the row
+    // statistics. `workspace` (gemmSkinnyWorkspaceBytes) is optional: without it the pool lends the memory.
+    int preferSkinny = 0;
+    void* workspace = nullptr;
+    size_t workspaceBytes = 0;
 };
 void gemm(const GemmArgs& args, cudaStream_t stream);
 bool gemmSupportsRowStats(const GemmArgs& args);
+bool gemmSkinnyEligible(const GemmArgs& args);
+int64_t gemmSkinnyWorkspaceBytes(const GemmArgs& args);
+void gemmSkinny(const GemmArgs& args, cudaStream_t stream);
 // True when the tcgen05 kernel takes this problem (otherwise the CUDA-core kernel runs).
 bool gemmUsesTensorCores(const GemmArgs& args);
 void matmulTransposeB(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, cudaStream_t stream);

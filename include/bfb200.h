@@ -234,6 +234,16 @@ bfb_status bfb_gemm_rmsnorm(const void* d_a, const void* d_w, void* d_c, int64_t
                             int32_t ab_dtype, int32_t c_dtype, int32_t epilogue, const float* d_bias,
                             const void* d_residual, const float* d_row_sum_sq, int32_t row_sum_sq_parts, float eps,
                             float* d_out_sum_sq, int32_t* d_status, void* stream);
+/* The linear of a generation step (few rows, all of W): C[m,n] = epilogue(alpha * A[m,k] W^T [* row scale]) for
+ * 1 <= m <= 128, W [n,k], bf16 or e4m3 operands. It stands for the same reference calls as bfb_gemm
+ * (matmulBf16 / linearBf16, ops_tensorcore.cu:308-387) in the shape Model::forwardIncremental produces. The weight
+ * rows take the MMA's M side and K is split over CTAs so that every SM streams part of W; the partial products are
+ * added in a fixed order (same bits on every run). Row statistics as for bfb_gemm_rmsnorm (d_row_sum_sq and
+ * d_out_sum_sq may be NULL). */
+bfb_status bfb_gemm_few_rows(const void* d_a, const void* d_w, void* d_c, int64_t m, int64_t n, int64_t k, int32_t ab_dtype,
+                             int32_t c_dtype, int32_t epilogue, const float* d_bias, const void* d_residual, float alpha,
+                             const float* d_row_sum_sq, int32_t row_sum_sq_parts, float eps, float* d_out_sum_sq,
+                             int32_t* d_status, void* stream);
 /* A * B^T on f32: a[M,K], b[N,K] (matmulTransposeB, ops_gemm.cu:95-110, kernel :20-34). */
 bfb_status bfb_matmul_transpose_b(const float* d_a, const float* d_b, float* d_c, int64_t m, int64_t n, int64_t k,
                                   void* stream);

@@ -256,3 +256,80 @@ def test_folded_rmsnorm_gives_the_same_bits_for_any_number_of_rows(gpu):
     for rows in (1, 100, 128, 300):
         part, part_ss = run(rows)
         assert np.array_equal(part, whole[:rows]) and np.array_equal(part_ss, whole_ss[:, :rows])
+
+
+@pytest.mark.parametrize("m,n,k,epilogue,c_dtype", [
+    (1, 264, 136, "none", "bf16"),              # one row, N tail of 8 columns, K tail
+    (7, 2048, 2048, "residual", "bf16"),        # 16 column tiles x 8 K-splits
+    (32, 2048, 5632, "bias_residual", "bf16"),
+    (100, 512, 320, "bias_silu", "bf16"),
+    (128, 1000, 512, "bias", "f32"),
+    (33, 6144, 2048, "none", "bf16"),
+])
+def test_few_rows_gemm_matches_oracle(gpu, m, n, k, epilogue, c_dtype):
+    """The generation-step GEMM (weights on the MMA's M side, K split across CTAs, partial products added in a
+    fixed order) against float64 arithmetic on the same bf16 operands, with the folded rmsnorm and its statistics."""
+    rng = np.random.default_rng(m * 3 + n + k)
+    a = O.round_bf16((rng.standard_normal((m, k)) * rng.uniform(0.3, 3.0, size=(m, 1))).astype(np.float32))
+    w = O.round_bf16(rng.standard_normal((n, k)).astype(np.float32) * 0.1)
+    bias = rng.standard_normal(n).astype(np.float32)
+    cd = gpu.BF16 if c_dtype == "bf16" else gpu.F32
+    res = rng.standard_normal((m, n)).astype(np.float32)
+    if cd == gpu.BF16:
+        res = O.round_bf16(res)
+    d_a, d_w = gpu.upload(a, gpu.BF16), gpu.upload(w, gpu.BF16)
+    d_bias, d_res = gpu.DeviceBuffer.from_numpy(bias), gpu.upload(res, cd)
+    d_ss = gpu.DeviceBuffer(m * 4)
+    gpu.check(gpu.lib().bfb_row_sum_squares(d_a.ptr, gpu.BF16, d_ss.ptr, m, k, None))
+    parts = (n + 127) // 128
+    d_c = gpu.DeviceBuffer(m * n * (2 if cd == gpu.BF16 else 4))
+    d_out_ss = gpu.DeviceBuffer(parts * m * 4)
+    status = gpu.DeviceBuffer.zeros(4)
+    has_bias, has_res = epilogue.startswith("bias"), epilogue.endswith("residual")
+    for run in range(2):
+        gpu.check(gpu.lib().bfb_gemm_few_rows(d_a.ptr, d_w.ptr, d_c.ptr, m, n, k, gpu.BF16, cd, gpu.EPI[epilogue],
+                                              d_bias.ptr if has_bias else None, d_res.ptr if has_res else None, 1.0,
+                                              d_ss.ptr, 1, 1e-6, d_out_ss.ptr, status.ptr, None))
+        got = gpu.download(d_c, cd, (m, n))
+        if run == 0:
+            first = got.copy()
+    assert np.array_equal(first, got)                      # no atomics: the same bits every time
+    assert status.to_numpy(np.int32, (1,))[0] == 0
+    ssq = np.sum(a.astype(np.float64) ** 2, axis=1)
+    want = (a.astype(np.float64) / np.sqrt(ssq / k + 1e-6)[:, None]) @ w.astype(np.float64).T
+    if has_bias:
+        want = want + bias
+    if epilogue == "bias_silu":
+        want = want / (1.0 + np.exp(-want))
+    if has_res:
+        want = want + res
+    tol = 2.0 ** -8 + 1e-3 if cd == gpu.BF16 else 1e-4
+    assert np.max(np.abs(got - want) / (np.abs(want) + 0.05)) <= tol
+    out_ss = d_out_ss.to_numpy(np.float32, (parts, m))
+    padded = np.zeros((m, parts * 128))
+    padded[:, :n] = got.astype(np.float64) ** 2
+    stored = padded.reshape(m, parts, 128).sum(axis=2).T
+    assert np.max(np.abs(out_ss - stored) / (stored + 1e-30)) <= 1e-5
+    # a row gives the same bits whatever rows sit beside it
+    if m > 1:
+        d_c1 = gpu.DeviceBuffer(n * (2 if cd == gpu.BF16 else 4))
+        gpu.check(gpu.lib().bfb_gemm_few_rows(d_a.ptr, d_w.ptr, d_c1.ptr, 1, n, k, gpu.BF16, cd, gpu.EPI[epilogue],
+                                              d_bias.ptr if has_bias else None, d_res.ptr if has_res else None, 1.0,
+                                              d_ss.ptr, 1, 1e-6, None, status.ptr, None))
+        assert np.array_equal(gpu.download(d_c1, cd, (1, n)), got[:1])
+
+
+def test_few_rows_gemm_e4m3_and_limits(gpu):
+    rng = np.random.default_rng(5)
+    m, n, k = 24, 384, 512
+    a = O.e4m3_round_hw(rng.standard_normal((m, k)).astype(np.float32))
+    w = O.e4m3_round_hw(rng.standard_normal((n, k)).astype(np.float32))
+    d_a, d_w = gpu.upload(a, gpu.FP8_E4M3), gpu.upload(w, gpu.FP8_E4M3)
+    d_c = gpu.DeviceBuffer(m * n * 4)
+    gpu.check(gpu.lib().bfb_gemm_few_rows(d_a.ptr, d_w.ptr, d_c.ptr, m, n, k, gpu.FP8_E4M3, gpu.F32, gpu.EPI["none"], None,
+                                          None, 0.5, None, 1, 0.0, None, None, None))
+    want = 0.5 * (a.astype(np.float64) @ w.astype(np.float64).T)
+    assert rel_err(gpu.download(d_c, gpu.F32, (m, n)), want) <= ACC_TOL
+    rc = gpu.lib().bfb_gemm_few_rows(d_a.ptr, d_w.ptr, d_c.ptr, 129, n, k, gpu.FP8_E4M3, gpu.F32, gpu.EPI["none"], None, None,
+                                     1.0, None, 1, 0.0, None, None, None)
+    assert rc == gpu.INVALID_ARGUMENT
