@@ -112,6 +112,7 @@ SIGNATURES = {
                                  C.POINTER(_I32), _P]),
     "bfb_model_forward_host": (_I32, [_P, _P, C.POINTER(_I64), _I32, _P, C.POINTER(_I64), C.POINTER(_I32)]),
     "bfb_host_transfer_bytes": (_I32, [C.POINTER(_I64), C.POINTER(_I64)]),
+    "bfb_host_widen_bf16": (_I32, [_P, _P, _I64, _I32]),
     "bfb_launch_count": (_I64, [_I32]),
     "bfb_profile_enable": (_I32, [_I32]),
     "bfb_profile_reset": (_I32, []),

@@ -5,6 +5,7 @@
 #include <cstring>
 #include <map>
 #include <mutex>
+#include <thread>
 #include <vector>
 
 #include "common.cuh"
@@ -712,6 +713,22 @@ bfb_status bfb_model_forward_host(bfb_model* model, const float* h_input, const 
             hostTransfer().d2h += static_cast<int64_t>(nb * perSeqOut * sizeof(float));
         }
         BFB_CUDA(cudaStreamSynchronize(st.copy));
+    });
+}
+
+bfb_status bfb_host_widen_bf16(const uint16_t* h_src, float* h_dst, int64_t count, int32_t threads) {
+    return guarded([&] {
+        require(count >= 0 && threads >= 1 && threads <= 256, "host_widen_bf16: bad count or thread number");
+        if (count == 0) return;
+        require(h_src != nullptr && h_dst != nullptr, "host_widen_bf16: null pointer");
+        const std::size_t n = static_cast<std::size_t>(count), parts = static_cast<std::size_t>(threads);
+        const std::size_t chunk = ((n + parts - 1) / parts + 7) / 8 * 8;
+        std::vector<std::thread> helpers;
+        for (std::size_t t = 1; t < parts && t * chunk < n; ++t) {
+            helpers.emplace_back([=] { bfb200::widenBf16(h_src + t * chunk, h_dst + t * chunk, std::min(chunk, n - t * chunk)); });
+        }
+        bfb200::widenBf16(h_src, h_dst, std::min(chunk, n));
+        for (std::thread& h : helpers) h.join();
     });
 }
 

@@ -336,6 +336,9 @@ bfb_status bfb_model_forward_host(bfb_model* model, const float* h_input, const 
  * caller's fp32 words by host threads, so d2h can be below 4 * product(out_shape).
  * No reference counterpart: its run path does not report transfers. */
 bfb_status bfb_host_transfer_bytes(int64_t* h2d_bytes, int64_t* d2h_bytes);
+/* The host half of that path on its own (no device needed): h_dst[i] = the fp32 value of bf16 h_src[i], exact,
+ * with `threads` host threads and streaming stores. No reference counterpart. */
+bfb_status bfb_host_widen_bf16(const uint16_t* h_src, float* h_dst, int64_t count, int32_t threads);
 /* Number of kernels this library launched on the calling thread since the counter was last reset. */
 int64_t bfb_launch_count(int32_t reset);
 

@@ -102,3 +102,21 @@ def test_bf16_bit_helpers_round_to_nearest_even(bfb):
     x = np.array([1.0, 1.00390625, 1.01171875, -2.5, 3.4e38, 1e-40], dtype=np.float32)
     back = bfb.bf16_bits_to_f32(bfb.f32_to_bf16_bits(x))
     assert np.array_equal(back, O.round_bf16(x))
+
+
+@pytest.mark.parametrize("count,threads,offset", [(0, 1, 0), (1, 1, 0), (7, 3, 0), (64, 1, 1), (100003, 4, 3), (4096, 16, 0)])
+def test_host_widening_is_exact(count, threads, offset):
+    """The host half of the bf16 result path runs without a device: every bf16 pattern, finite or not, must come out
+    as the fp32 word with the same upper 16 bits, whatever the alignment of the destination and the thread split."""
+    import blackforge_b200 as bfb
+    rng = np.random.default_rng(count + threads)
+    src = rng.integers(0, 1 << 16, size=count, dtype=np.uint16)
+    if count >= 4:
+        src[:4] = [0x7F80, 0xFF80, 0x7FC1, 0x8000]       # +inf, -inf, a NaN, -0
+    backing = np.zeros(count + offset + 1, dtype=np.float32)
+    dst = backing[offset:offset + count]
+    rc = bfb.lib().bfb_host_widen_bf16(src.ctypes.data if count else None, dst.ctypes.data if count else None, count, threads)
+    assert rc == bfb.OK
+    assert np.array_equal(dst.view(np.uint32), src.astype(np.uint32) << 16)
+    assert backing[:offset].tolist() == [0.0] * offset and backing[-1] == 0.0
+    assert bfb.lib().bfb_host_widen_bf16(src.ctypes.data, dst.ctypes.data, count, 0) == bfb.INVALID_ARGUMENT
