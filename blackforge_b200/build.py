@@ -29,6 +29,7 @@ SOURCES = [
     "gemm_skinny.cu",
     "attention_simt.cu",
     "attention_tc.cu",
+    "attention_decode.cu",
     "capi.cu",
     "host/ops.cpp",
     "host/model.cpp",

@@ -109,6 +109,10 @@ void attentionForward(const AttentionArgs& a, cudaStream_t stream) {
     const int64_t kvRows = a.kvBatchRows > 0 ? a.kvBatchRows : a.totalLen;
     require(a.q != nullptr && a.k != nullptr && a.v != nullptr && a.out != nullptr, "attention: null pointer");
 
+    if (attentionDecodeEligible(a)) {   // one query per sequence: stream K and V, nothing for a 128-row MMA to do
+        attentionDecode(a, stream);
+        return;
+    }
     if (attentionUsesTensorCores(a)) {
         attentionTensorCore(a, stream);
         return;

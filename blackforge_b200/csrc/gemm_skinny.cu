@@ -2,9 +2,10 @@
 //
 // With a handful of rows the work is streaming W once, so the kernel is laid out for HBM bandwidth, not for the
 // tensor pipe: the WEIGHT rows take the MMA's M side (128 per CTA) and the activation rows its N side (M padded
-// to 16, 32, 64 or 128), and K is split across CTAs until about one CTA per SM streams its own slice of W:
+// to 16, 32, 64 or 128), and K is split across CTAs until about two CTAs per SM stream their own slices of W:
 //   grid = ceil(N / 128) x splits, CTA (tile, split) computes W[tile*128 .. +128, k-slice] * A[:, k-slice]^T
-//   warp 0      TMA producer: W slice (128 x 128 B, 128-byte swizzle) + A slice (mPad x 128 B) per stage, 6 stages
+//   warp 0      TMA producer: W slice (128 x 128 B, 128-byte swizzle) + A slice (mPad x 128 B) per stage, 3-6 stages
+//               (about 100 KB, so that two CTAs share an SM)
 //   warp 1      MMA issuer + TMEM owner: tcgen05.mma 128 x mPad x 16 (x32 for e4m3), fp32 accumulator in TMEM
 //   warps 2-5   drain: tcgen05.ld the accumulator (lane = weight row = output column) and store the fp32 partial
 //               products to a workspace [split][m][N]; for one activation row the 32 lanes write 32 consecutive floats
@@ -27,7 +28,8 @@ namespace {
 
 constexpr int kTileN = 128;                 // weight rows (output columns) per CTA
 constexpr int kRowBytesS = 128;             // one swizzle atom of K per stage
-constexpr int kStagesS = 6;
+constexpr int kMaxStagesS = 6;              // fewer for wider A slices: two CTAs share an SM's shared memory
+constexpr int kSmemBudgetS = 110 * 1024;
 constexpr int kWBytes = kTileN * kRowBytesS;   // 16 KiB
 constexpr int kThreadsS = 192;
 constexpr int kDrainWarps = 4;
@@ -35,9 +37,9 @@ constexpr int kDrainWarps = 4;
 __host__ __device__ constexpr int skinnyStageBytes(int mPad) { return kWBytes + mPad * kRowBytesS; }
 
 template <int kElemBytes>
-__global__ void __launch_bounds__(kThreadsS, 1)
+__global__ void __launch_bounds__(kThreadsS, 2)
 gemmSkinnyKernel(const __grid_constant__ CUtensorMap tmapW, const __grid_constant__ CUtensorMap tmapA, float* ws, int m,
-                 int n, int mPad, int tilesN, int numK, int blocksPerSplit, int* status) {
+                 int n, int mPad, int tilesN, int numK, int blocksPerSplit, int stages, int* status) {
     constexpr int kBlockK = kRowBytesS / kElemBytes;
     constexpr int kUmmaK = 32 / kElemBytes;
     constexpr int kMmaPerStage = kBlockK / kUmmaK;  // 4
@@ -45,10 +47,10 @@ gemmSkinnyKernel(const __grid_constant__ CUtensorMap tmapW, const __grid_constan
     extern __shared__ uint8_t smemRaw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
     const int stageBytes = skinnyStageBytes(mPad);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStagesS * stageBytes);
-    uint64_t* fullBar = bars;                 // [kStagesS]
-    uint64_t* emptyBar = bars + kStagesS;     // [kStagesS]
-    uint64_t* accFullBar = bars + 2 * kStagesS;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + stages * stageBytes);
+    uint64_t* fullBar = bars;                 // [stages]
+    uint64_t* emptyBar = bars + kMaxStagesS;  // [stages]
+    uint64_t* accFullBar = bars + 2 * kMaxStagesS;
     uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(accFullBar + 1);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
@@ -61,7 +63,7 @@ gemmSkinnyKernel(const __grid_constant__ CUtensorMap tmapW, const __grid_constan
     const uint32_t tmemCols = mPad < 32 ? 32u : static_cast<uint32_t>(mPad);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStagesS; ++s) {
+        for (int s = 0; s < stages; ++s) {
             mbar_init(&fullBar[s], 1);
             mbar_init(&emptyBar[s], 1);
         }
@@ -83,8 +85,8 @@ gemmSkinnyKernel(const __grid_constant__ CUtensorMap tmapW, const __grid_constan
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         for (int kb = kbBegin, it = 0; kb < kbEnd; ++kb, ++it) {
-            const int s = it % kStagesS;
-            const uint32_t use = static_cast<uint32_t>(it / kStagesS);
+            const int s = it % stages;
+            const uint32_t use = static_cast<uint32_t>(it / stages);
             if (!warp_all(mbar_wait(&emptyBar[s], (use & 1u) ^ 1u, abortFlag, status, kDevTimeoutStageEmpty))) break;
             if (lane == 0) {
                 uint8_t* dst = smem + s * stageBytes;
@@ -99,8 +101,8 @@ gemmSkinnyKernel(const __grid_constant__ CUtensorMap tmapW, const __grid_constan
         const uint32_t idesc = make_idesc(kTileN, static_cast<uint32_t>(mPad), kElemBytes == 2 ? 1u : 0u, 0u);
         bool alive = true;
         for (int kb = kbBegin, it = 0; kb < kbEnd; ++kb, ++it) {
-            const int s = it % kStagesS;
-            const uint32_t use = static_cast<uint32_t>(it / kStagesS);
+            const int s = it % stages;
+            const uint32_t use = static_cast<uint32_t>(it / stages);
             if (!warp_all(mbar_wait(&fullBar[s], use & 1u, abortFlag, status, kDevTimeoutTmaFull))) {
                 alive = false;
                 break;
@@ -257,7 +259,7 @@ skinnyFinishKernel(FinishParams p, int m, int n, int parts) {
 int padRows(int64_t m) { return m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : 128)); }
 
 struct SkinnyPlan {
-    int mPad, tilesN, numK, splits, blocksPerSplit;
+    int mPad, tilesN, numK, splits, blocksPerSplit, stages;
 };
 
 SkinnyPlan planSkinny(const GemmArgs& g) {
@@ -267,8 +269,10 @@ SkinnyPlan planSkinny(const GemmArgs& g) {
     p.mPad = padRows(g.m);
     p.tilesN = static_cast<int>((g.n + kTileN - 1) / kTileN);
     p.numK = static_cast<int>((g.k + blockK - 1) / blockK);
-    // about one CTA per SM; the split depends on N and K only, so a row gives the same bits whatever rows sit beside it
-    int splits = std::max(1, std::min({(smCount() + p.tilesN - 1) / p.tilesN, p.numK, 16}));
+    // two CTAs fit on an SM: as many splits as keep all CTAs resident at once (one wave). The split depends on N and
+    // K only, so a row gives the same bits whatever rows sit beside it
+    p.stages = std::max(2, std::min(kMaxStagesS, kSmemBudgetS / skinnyStageBytes(p.mPad)));
+    int splits = std::max(1, std::min({2 * smCount() / p.tilesN, p.numK, 16}));
     p.blocksPerSplit = (p.numK + splits - 1) / splits;
     p.splits = (p.numK + p.blocksPerSplit - 1) / p.blocksPerSplit;
     return p;
@@ -290,12 +294,12 @@ void launchSkinny(const GemmArgs& g, const SkinnyPlan& p, float* ws, cudaStream_
         uint32_t box[2] = {static_cast<uint32_t>(kBlockK), static_cast<uint32_t>(p.mPad)};
         encodeTensorMap(&ta, g.a, kElemBytes, 2, dims, strides, box);
     }
-    const int smemBytes = kStagesS * skinnyStageBytes(p.mPad) + 1024 + 256;
+    const int smemBytes = p.stages * skinnyStageBytes(p.mPad) + 1024 + 256;
     auto kernel = gemmSkinnyKernel<kElemBytes>;
     BFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smemBytes));
     kernel<<<static_cast<unsigned>(p.tilesN * p.splits), kThreadsS, smemBytes, stream>>>(
         *reinterpret_cast<CUtensorMap*>(tw.bytes), *reinterpret_cast<CUtensorMap*>(ta.bytes), ws, static_cast<int>(g.m),
-        static_cast<int>(g.n), p.mPad, p.tilesN, p.numK, p.blocksPerSplit, g.dStatus);
+        static_cast<int>(g.n), p.mPad, p.tilesN, p.numK, p.blocksPerSplit, p.stages, g.dStatus);
     BFB_LAUNCH_CHECK();
     noteLaunch();
 }

@@ -107,6 +107,10 @@ struct AttentionArgs {
     int causal = 1;
     int* dStatus = nullptr;
 };
+// One query per sequence and head against cached keys and values (a generation step): a bandwidth-oriented CUDA-core
+// kernel, see attention_decode.cu.
+bool attentionDecodeEligible(const AttentionArgs& args);
+void attentionDecode(const AttentionArgs& args, cudaStream_t stream);
 void attentionForward(const AttentionArgs& args, cudaStream_t stream);
 bool attentionUsesTensorCores(const AttentionArgs& args);
 

@@ -90,3 +90,21 @@ def test_interleaved_qkv_strides(gpu):
     got = gpu.download(out, gpu.BF16, (B, S, dim))
     q, k, v = packed[..., :dim], packed[..., dim:2 * dim], packed[..., 2 * dim:]
     assert np.max(np.abs(got - O.attention_core(q, k, v, H, exact_order=False))) <= TOL
+
+
+@pytest.mark.parametrize("B,H,total", [(3, 2, 700), (1, 1, 5000), (2, 16, 1), (5, 3, 263)])
+def test_one_query_against_a_cache(gpu, B, H, total):
+    """A generation step: one new query per sequence and head against `total` cached keys (the bandwidth-oriented
+    kernel, with the keys split over several CTAs when they are many), against the oracle."""
+    rng = np.random.default_rng(B * 100 + H * 10 + total)
+    q, k, v = qkv(rng, B, 1, total, H)
+    out, m, l = attention(gpu, q, k, v, H, gpu.BF16, old_len=total - 1)
+    want = O.attention_core(q, k, v, H, old_len=total - 1, exact_order=False)
+    assert np.max(np.abs(out - want)) <= TOL
+    D = 128
+    sc = np.einsum("bqhd,bkhd->bhqk", q.reshape(B, 1, H, D), k.reshape(B, total, H, D)).astype(np.float64) / np.sqrt(D)
+    assert np.allclose(m, sc.max(-1), atol=2e-3)
+    assert np.allclose(l, np.exp(sc - sc.max(-1, keepdims=True)).sum(-1), rtol=2e-3)
+    # bidirectional with one query is the same computation
+    out2, _, _ = attention(gpu, q, k, v, H, gpu.BF16, causal=0)
+    assert np.array_equal(out, out2)
