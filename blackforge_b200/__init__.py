@@ -85,7 +85,7 @@ SIGNATURES = {
     "bfb_weight_prepare": (_I32, [_P, _P, _I32, _I64, _I64, _F, _P, _P]),
     "bfb_gemm": (_I32, [_P, _P, _P, _I64, _I64, _I64, _I32, _I32, _I32, _I32, _P, _P, _F, _P, _I32, _P, _P]),
     "bfb_row_sum_squares": (_I32, [_P, _I32, _P, _I64, _I64, _P]),
-    "bfb_gemm_rmsnorm": (_I32, [_P, _P, _P, _I64, _I64, _I64, _I32, _I32, _I32, _P, _P, _P, _I32, _F, _P, _P, _P]),
+    "bfb_gemm_rmsnorm": (_I32, [_P, _P, _P, _I64, _I64, _I64, _I32, _I32, _I32, _P, _P, _P, _I32, _F, _P, _P, _P, _P]),
     "bfb_gemm_few_rows": (_I32, [_P, _P, _P, _I64, _I64, _I64, _I32, _I32, _I32, _P, _P, _F, _P, _I32, _F, _P, _P, _P]),
     "bfb_matmul_transpose_b": (_I32, [_P, _P, _P, _I64, _I64, _I64, _P]),
     "bfb_attention_fwd": (_I32, [_P, _P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64,

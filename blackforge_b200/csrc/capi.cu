@@ -257,7 +257,7 @@ bfb_status bfb_row_sum_squares(const void* d_x, int32_t dtype, float* d_out, int
 bfb_status bfb_gemm_rmsnorm(const void* d_a, const void* d_w, void* d_c, int64_t m, int64_t n, int64_t k,
                             int32_t ab_dtype, int32_t c_dtype, int32_t epilogue, const float* d_bias,
                             const void* d_residual, const float* d_row_sum_sq, int32_t row_sum_sq_parts, float eps,
-                            float* d_out_sum_sq, int32_t* d_status, void* stream) {
+                            float* d_out_sum_sq, float* d_out_max_abs, int32_t* d_status, void* stream) {
     return guarded([&] {
         bfb::GemmArgs g;
         g.a = d_a;
@@ -277,6 +277,7 @@ bfb_status bfb_gemm_rmsnorm(const void* d_a, const void* d_w, void* d_c, int64_t
         g.rowInvDim = k > 0 ? 1.0f / static_cast<float>(k) : 0.0f;
         g.rowEps = eps;
         g.outSumSq = d_out_sum_sq;
+        g.outMaxAbs = d_out_max_abs;
         g.dStatus = d_status;
         bfb::gemm(g, asStream(stream));
     });

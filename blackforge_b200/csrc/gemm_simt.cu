@@ -144,11 +144,11 @@ void gemm(const GemmArgs& g, cudaStream_t stream) {
     if (needsBias) require(g.bias != nullptr, "gemm: bias missing");
     if (needsRes) require(g.residual != nullptr, "gemm: residual missing");
 
-    if (g.preferSkinny != 0 && gemmSkinnyEligible(g)) {
+    if (g.preferSkinny != 0 && g.outMaxAbs == nullptr && gemmSkinnyEligible(g)) {
         gemmSkinny(g, stream);
         return;
     }
-    if ((g.rowSumSq != nullptr || g.outSumSq != nullptr) && !gemmSupportsRowStats(g)) {
+    if ((g.rowSumSq != nullptr || g.outSumSq != nullptr || g.outMaxAbs != nullptr) && !gemmSupportsRowStats(g)) {
         fail(BFB_UNSUPPORTED, "gemm: row statistics need the CTA-pair tensor-core kernel (bf16 or e4m3 operands, [N,K] weights, 16-byte aligned rows)");
     }
     if (gemmUsesTensorCores(g)) {

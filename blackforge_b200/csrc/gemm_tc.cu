@@ -416,7 +416,7 @@ void gemmTensorCore(const GemmArgs& g, cudaStream_t stream) {
     // CTA pairs share 256-row tiles: worth it once there is more than one 128-row tile of work
     // ... or when row statistics are asked for, which only that kernel has (whatever the number of rows, so that
     // a sequence gives the same bits alone and inside a batch)
-    const bool stats = g.rowSumSq != nullptr || g.outSumSq != nullptr;
+    const bool stats = g.rowSumSq != nullptr || g.outSumSq != nullptr || g.outMaxAbs != nullptr;
     if (g.bLayout == BFB_B_NK && (g.m > 128 || stats) && pairKernelEnabled()) {
         gemmTensorCorePair(g, stream);
         return;

@@ -80,6 +80,7 @@ struct PairEpilogue {
     float rowInvDim;         // row scale = 1 / sqrt(sum * rowInvDim + rowEps)
     float rowEps;
     float* outSumSq;         // [ceil(n / 128)][m]: sums of squares of the stored values per 128-column part, or null
+    float* outMaxAbs;        // same layout: largest magnitude of the stored values, or null
 };
 
 __device__ __forceinline__ float siluFast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
@@ -248,11 +249,14 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
             }
             // Sums of squares of what this thread stores, one per 128-column part of the row, each written by
             // exactly one thread: no atomics, so the figures do not depend on timing or on the tile width.
-            float sumSq = 0.0f;
+            float sumSq = 0.0f, maxAbs = 0.0f;
             int part = -1;
             auto flushPart = [&]() {
-                if (ep.outSumSq != nullptr && rowOk && part >= 0)
-                    ep.outSumSq[static_cast<size_t>(part) * static_cast<size_t>(m) + row] = sumSq;
+                if (rowOk && part >= 0) {
+                    const size_t at = static_cast<size_t>(part) * static_cast<size_t>(m) + row;
+                    if (ep.outSumSq != nullptr) ep.outSumSq[at] = sumSq;
+                    if (ep.outMaxAbs != nullptr) ep.outMaxAbs[at] = maxAbs;
+                }
             };
             const uint32_t tBase = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>(buf * kAccN + colHalf * kColsPerWarp);
@@ -264,6 +268,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
                     flushPart();
                     part = col0 >> 7;
                     sumSq = 0.0f;
+                    maxAbs = 0.0f;
                 }
                 uint32_t raw[32];
                 tmem_ld_32x32(tBase + static_cast<uint32_t>(chunk * 32), raw);
@@ -305,6 +310,10 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
 #pragma unroll
                                 for (int j = 0; j < 8; ++j) sumSq = fmaf(v[j], v[j], sumSq);
                             }
+                            if (ep.outMaxAbs != nullptr) {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) maxAbs = fmaxf(maxAbs, fabsf(v[j]));
+                            }
                         } else {
                             if (hasRes) {
                                 const uint4 rr = *reinterpret_cast<const uint4*>(res + rowOff + col);
@@ -322,9 +331,10 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
                             for (int j = 0; j < 4; ++j) {
                                 __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
                                 pw[j] = *reinterpret_cast<uint32_t*>(&h);
-                                if (ep.outSumSq != nullptr) {
+                                if (ep.outSumSq != nullptr || ep.outMaxAbs != nullptr) {
                                     const float2 f = __bfloat1622float2(h);   // the values as stored
                                     sumSq = fmaf(f.x, f.x, fmaf(f.y, f.y, sumSq));
+                                    maxAbs = fmaxf(maxAbs, fmaxf(fabsf(f.x), fabsf(f.y)));
                                 }
                             }
                             *reinterpret_cast<uint4*>(cOut + rowOff + col) = packed;
@@ -387,7 +397,7 @@ void launchPair(const GemmArgs& g, cudaStream_t stream) {
     const int groupN = (tilesN + groups - 1) / groups;
     const int clusters = std::max(1, std::min(tilesM * tilesN, smCount() / 2));
     PairEpilogue ep{g.c, g.bias, g.residual, g.alpha, g.dAlpha, g.epilogue, g.roundCBf16,
-                    g.rowSumSq, g.rowSumSqParts, g.rowInvDim, g.rowEps, g.outSumSq};
+                    g.rowSumSq, g.rowSumSqParts, g.rowInvDim, g.rowEps, g.outSumSq, g.outMaxAbs};
     auto kernel = gemmPairKernel<kElemBytes, TC, kAccN>;
     BFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     ProfileScope prof(kProfGemmTc, stream, 2.0 * static_cast<double>(g.m) * static_cast<double>(g.n) * static_cast<double>(g.k));

@@ -555,7 +555,8 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
     };
     auto runGemm = [&](const void* a, const void* w, void* c, std::size_t m, std::size_t n, std::size_t k, int cDtype,
                        int epilogue, const float* bias, const void* residual, const float* dAlpha, int roundC,
-                       const float* rowSumSq = nullptr, int rowSumSqParts = 1, float* outSumSq = nullptr) {
+                       const float* rowSumSq = nullptr, int rowSumSqParts = 1, float* outSumSq = nullptr,
+                       float* outMaxAbs = nullptr) {
         bfb::GemmArgs g;
         g.a = a;
         g.b = w;
@@ -577,6 +578,7 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
         g.rowInvDim = k > 0 ? 1.0f / static_cast<float>(k) : 0.0f;
         g.rowEps = 1e-6f;
         g.outSumSq = outSumSq;
+        g.outMaxAbs = outMaxAbs;
         // a generation step has a handful of rows: stream the weights through every SM instead of tiling C
         g.preferSkinny = incremental && m <= 128 ? 1 : 0;
         bfb::gemm(g, stream);
@@ -734,6 +736,7 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                 const float* sc = static_cast<const float*>(l.scales.ptr);
                 const float* dAlpha = nullptr;
                 void* hidden = buf("hidden", tokens * fl * 2);
+                float* hiddenMaxima = nullptr;
                 const bool fuse = fusedNormOk(tokens, fl, d, l.w0.ptr);
                 if (fuse) {
                     const float* sums = needSumSq(tokens, d);
@@ -741,8 +744,23 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                             nullptr, nullptr, 0, sums, ssParts, nullptr);
                 } else if (fp8 && S == BFB_BF16) {
                     const void* a1 = normedFp8Input(tokens, d, sc, &dAlpha);
+                    // the epilogue that writes `hidden` also reports its largest magnitudes (one per row and 128
+                    // columns): the quantisation below then needs no pass over `hidden` to find its scale
+                    bfb::GemmArgs probe;
+                    probe.a = a1;
+                    probe.b = l.w0.ptr;
+                    probe.c = hidden;
+                    probe.m = static_cast<int64_t>(tokens);
+                    probe.n = static_cast<int64_t>(fl);
+                    probe.k = static_cast<int64_t>(d);
+                    probe.abDtype = ab;
+                    probe.bLayout = BFB_B_NK;
+                    probe.cDtype = BFB_BF16;
+                    if (!incremental && bfb::gemmSupportsRowStats(probe)) {
+                        hiddenMaxima = static_cast<float*>(buf("hidden_maxima", ((fl + 127) / 128) * tokens * sizeof(float)));
+                    }
                     runGemm(a1, l.w0.ptr, hidden, tokens, fl, d, BFB_BF16, BFB_EPI_BIAS_SILU, params[l.p[1]].value.data(),
-                            nullptr, dAlpha, 0);
+                            nullptr, dAlpha, 0, nullptr, 1, nullptr, hiddenMaxima);
                 } else {
                     void* normed = buf("normed", tokens * d * 2);
                     bfb::rmsnorm(x, S, normed, BFB_BF16, static_cast<int64_t>(tokens), static_cast<int64_t>(d), 1e-6f, stream);
@@ -750,7 +768,20 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                     runGemm(a1, l.w0.ptr, hidden, tokens, fl, d, BFB_BF16, BFB_EPI_BIAS_SILU, params[l.p[1]].value.data(),
                             nullptr, dAlpha, 0);
                 }
-                const void* a2 = gemmInput(hidden, tokens * fl, "act8_f", sc + 2, &dAlpha);
+                const void* a2 = nullptr;
+                if (hiddenMaxima != nullptr) {
+                    float* st = static_cast<float*>(fp8Stats.ptr) + 4 * (fp8Slot++);
+                    void* a8 = buf("act8_f", tokens * fl);
+                    const int64_t count = static_cast<int64_t>(((fl + 127) / 128) * tokens);
+                    float* scratch = static_cast<float*>(
+                        buf("partial_maxima", static_cast<std::size_t>(bfb::quantizeScratchFloats(count)) * sizeof(float)));
+                    bfb::quantizeE4m3FromMaxima(hidden, BFB_BF16, static_cast<int64_t>(tokens * fl), a8, st, sc + 3, hiddenMaxima,
+                                                count, scratch, stream);
+                    dAlpha = st + 2;
+                    a2 = a8;
+                } else {
+                    a2 = gemmInput(hidden, tokens * fl, "act8_f", sc + 2, &dAlpha);
+                }
                 const bool lead = tpWorld == 1 || tpRank == 0;
                 float* produced = fuse && fusedNormOk(tokens, d, fl, l.w1.ptr) ? nextSumSq(tokens, d) : nullptr;
                 runGemm(a2, l.w1.ptr, x, tokens, d, fl, S, lead ? BFB_EPI_BIAS_RESIDUAL : BFB_EPI_NONE,

@@ -40,6 +40,11 @@ void quantizeE4m3(const void* in, int inDtype, int64_t n, void* out, float* dSca
 // rmsnorm (no weights) of bf16 rows followed by per-tensor e4m3 quantisation, without storing the normalised rows:
 // out = e4m3(bf16(x * r_row) * scale), scale = 448 / max|bf16(x * r_row)|; dScales as for quantizeE4m3. `scratch`
 // holds rmsnormQuantizeScratchFloats(rows) floats.
+// Per-tensor e4m3 quantisation of `in` whose maximum magnitude is the maximum of `maxima` (count floats, e.g. a
+// GEMM's outMaxAbs): the maximum pass reads that small array instead of `in`. `scratch` holds
+// quantizeScratchFloats(count) floats.
+void quantizeE4m3FromMaxima(const void* in, int inDtype, int64_t n, void* out, float* dScales, const float* dWeightInverse,
+                            const float* maxima, int64_t count, float* scratch, cudaStream_t stream);
 int64_t rmsnormQuantizeScratchFloats(int64_t rows);
 void rmsnormQuantizeE4m3(const void* x, int64_t rows, int64_t dim, float eps, void* out, float* dScales,
                          const float* dWeightInverse, float* scratch, cudaStream_t stream);
@@ -73,6 +78,10 @@ struct GemmArgs {
     float rowInvDim = 0.0f;
     float rowEps = 0.0f;
     float* outSumSq = nullptr;
+    // Same layout and the same kernel as outSumSq: the largest magnitude of each stored row per 128-column part,
+    // outMaxAbs[p * m + i]. The per-tensor maximum an e4m3 quantisation of C needs is then the maximum of a small
+    // array instead of another pass over C.
+    float* outMaxAbs = nullptr;
     // Few rows (a generation step): stream the weights through as many SMs as possible instead of tiling C (see
     // gemm_skinny.cu). Takes effect for 1..128 rows with [N,K] weights in a tensor-core format; has the row
     // statistics. `workspace` (gemmSkinnyWorkspaceBytes) is optional: without it the pool lends the memory.

@@ -267,6 +267,27 @@ void quantizeE4m3(const void* in, int inDtype, int64_t n, void* out, float* dSca
     if (n > 0) castScaled(in, inDtype, out, BFB_FP8_E4M3, n, 1.0f, dScales, stream);
 }
 
+void quantizeE4m3FromMaxima(const void* in, int inDtype, int64_t n, void* out, float* dScales, const float* dWeightInverse,
+                            const float* maxima, int64_t count, float* scratch, cudaStream_t stream) {
+    require(n >= 0 && count >= 0, "quantize_e4m3: negative size");
+    require(inDtype == BFB_F32 || inDtype == BFB_BF16, "quantize_e4m3: input must be f32 or bf16");
+    require(dScales != nullptr && scratch != nullptr, "quantize_e4m3: null scale or scratch pointer");
+    if (n > 0) require(in != nullptr && out != nullptr && maxima != nullptr && count > 0, "quantize_e4m3: null pointer");
+    const int64_t blocks = quantizeScratchFloats(count);
+    require(blocks <= 0x7FFFFFFF, "quantize_e4m3: too many maxima for one launch");
+    if (n > 0) {
+        // the maxima are magnitudes already; the kernel's fabs changes nothing
+        partialAmaxKernel<float><<<static_cast<unsigned>(blocks), kChunkThreads, 0, stream>>>(
+            maxima, count, scratch, reinterpret_cast<uintptr_t>(maxima) % 16 == 0 ? 1 : 0);
+        BFB_LAUNCH_CHECK();
+        noteLaunch();
+    }
+    finalizeScaleKernel<<<1, 1024, 0, stream>>>(scratch, n > 0 ? blocks : 0, dScales, dWeightInverse);
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+    if (n > 0) castScaled(in, inDtype, out, BFB_FP8_E4M3, n, 1.0f, dScales, stream);
+}
+
 }  // namespace bfb
 
 // ---- allocation-free variant ---------------------------------------------------------------------------

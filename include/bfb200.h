@@ -227,13 +227,15 @@ bfb_status bfb_gemm(const void* d_a, const void* d_b, void* d_c, int64_t m, int6
  * sum over p < row_sum_sq_parts of d_row_sum_sq[p * m + i]. bfb_row_sum_squares computes s (one part); a
  * producing GEMM can also deliver it: with d_out_sum_sq set, the sums of squares of every stored row of C are
  * written there per 128-column part, d_out_sum_sq[p * m + i] for p < ceil(n / 128) (no atomics: the same bits on
- * every run). d_row_sum_sq and d_out_sum_sq may be NULL. Weights are [n,k] (BFB_B_NK); needs the tensor-core
+ * every run); d_out_max_abs, same layout, receives the largest magnitude of each part instead (the per-tensor
+ * maximum an e4m3 quantisation of C needs, without another pass over C). d_row_sum_sq, d_out_sum_sq and
+ * d_out_max_abs may be NULL. Weights are [n,k] (BFB_B_NK); needs the tensor-core
  * formats and 16-byte aligned rows, else BFB_UNSUPPORTED. */
 bfb_status bfb_row_sum_squares(const void* d_x, int32_t dtype, float* d_out, int64_t rows, int64_t dim, void* stream);
 bfb_status bfb_gemm_rmsnorm(const void* d_a, const void* d_w, void* d_c, int64_t m, int64_t n, int64_t k,
                             int32_t ab_dtype, int32_t c_dtype, int32_t epilogue, const float* d_bias,
                             const void* d_residual, const float* d_row_sum_sq, int32_t row_sum_sq_parts, float eps,
-                            float* d_out_sum_sq, int32_t* d_status, void* stream);
+                            float* d_out_sum_sq, float* d_out_max_abs, int32_t* d_status, void* stream);
 /* The linear of a generation step (few rows, all of W): C[m,n] = epilogue(alpha * A[m,k] W^T [* row scale]) for
  * 1 <= m <= 128, W [n,k], bf16 or e4m3 operands. It stands for the same reference calls as bfb_gemm
  * (matmulBf16 / linearBf16, ops_tensorcore.cu:308-387) in the shape Model::forwardIncremental produces. The weight

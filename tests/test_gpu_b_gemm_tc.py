@@ -188,12 +188,13 @@ def test_rmsnorm_folded_into_the_gemm(gpu, m, n, k, epilogue, wide):
     d_c = gpu.DeviceBuffer(m * n * 2)
     parts = (n + 127) // 128
     d_out_ss = gpu.DeviceBuffer(parts * m * 4)
+    d_out_mx = gpu.DeviceBuffer(parts * m * 4)
     status = gpu.DeviceBuffer.zeros(4)
     epi = gpu.EPI[epilogue]
     gpu.check(gpu.lib().bfb_gemm_rmsnorm(d_a.ptr, d_w.ptr, d_c.ptr, m, n, k, gpu.BF16, gpu.BF16, epi,
                                          d_bias.ptr if epilogue != "none" else None,
                                          d_res.ptr if epilogue == "bias_residual" else None,
-                                         d_ss.ptr, 1, 1e-6, d_out_ss.ptr, status.ptr, None))
+                                         d_ss.ptr, 1, 1e-6, d_out_ss.ptr, d_out_mx.ptr, status.ptr, None))
     got = gpu.download(d_c, gpu.BF16, (m, n))
     assert status.to_numpy(np.int32, (1,))[0] == 0
     normed = a.astype(np.float64) / np.sqrt(want_ss / k + 1e-6)[:, None]
@@ -211,16 +212,20 @@ def test_rmsnorm_folded_into_the_gemm(gpu, m, n, k, epilogue, wide):
     padded[:, :n] = got.astype(np.float64) ** 2
     stored = padded.reshape(m, parts, 128).sum(axis=2).T          # [parts][m], one figure per 128 columns
     assert np.max(np.abs(out_ss - stored) / (stored + 1e-30)) <= 1e-5
+    out_mx = d_out_mx.to_numpy(np.float32, (parts, m))
+    padded_abs = np.zeros((m, parts * 128), np.float32)
+    padded_abs[:, :n] = np.abs(got)
+    assert np.array_equal(out_mx, padded_abs.reshape(m, parts, 128).max(axis=2).T)     # exact: maxima of stored values
     # those parts drive the next GEMM exactly like the one-part sums of a separate pass over C
     d_c2, d_c3 = gpu.DeviceBuffer(m * 64 * 2), gpu.DeviceBuffer(m * 64 * 2)
     w2 = O.round_bf16(rng.standard_normal((64, n)).astype(np.float32) * 0.1)
     d_w2 = gpu.upload(w2, gpu.BF16)
     gpu.check(gpu.lib().bfb_gemm_rmsnorm(d_c.ptr, d_w2.ptr, d_c2.ptr, m, 64, n, gpu.BF16, gpu.BF16, gpu.EPI["none"], None,
-                                         None, d_out_ss.ptr, parts, 1e-6, None, status.ptr, None))
+                                         None, d_out_ss.ptr, parts, 1e-6, None, None, status.ptr, None))
     d_one = gpu.DeviceBuffer(m * 4)
     gpu.check(gpu.lib().bfb_row_sum_squares(d_c.ptr, gpu.BF16, d_one.ptr, m, n, None))
     gpu.check(gpu.lib().bfb_gemm_rmsnorm(d_c.ptr, d_w2.ptr, d_c3.ptr, m, 64, n, gpu.BF16, gpu.BF16, gpu.EPI["none"], None,
-                                         None, d_one.ptr, 1, 1e-6, None, status.ptr, None))
+                                         None, d_one.ptr, 1, 1e-6, None, None, status.ptr, None))
     got2, got3 = gpu.download(d_c2, gpu.BF16, (m, 64)), gpu.download(d_c3, gpu.BF16, (m, 64))
     assert np.max(np.abs(got2 - got3) / (np.abs(got3) + 0.05)) <= 2.0 ** -7
 
@@ -231,7 +236,7 @@ def test_row_statistics_need_the_tensor_core_kernel(gpu):
     d_a, d_w, d_c = gpu.upload(a, gpu.BF16), gpu.upload(a, gpu.BF16), gpu.DeviceBuffer(64 * 64 * 2)
     d_ss = gpu.DeviceBuffer.zeros(64 * 4)
     rc = gpu.lib().bfb_gemm_rmsnorm(d_a.ptr, d_w.ptr, d_c.ptr, 64, 64, 60, gpu.BF16, gpu.BF16, gpu.EPI["none"], None, None,
-                                    d_ss.ptr, 1, 1e-6, None, None, None)
+                                    d_ss.ptr, 1, 1e-6, None, None, None, None)
     assert rc == gpu.UNSUPPORTED
 
 
@@ -249,7 +254,7 @@ def test_folded_rmsnorm_gives_the_same_bits_for_any_number_of_rows(gpu):
         d_out = gpu.DeviceBuffer(4 * rows * 4)
         gpu.check(gpu.lib().bfb_row_sum_squares(d_a.ptr, gpu.BF16, d_ss.ptr, rows, k, None))
         gpu.check(gpu.lib().bfb_gemm_rmsnorm(d_a.ptr, d_w.ptr, d_c.ptr, rows, n, k, gpu.BF16, gpu.BF16, gpu.EPI["none"],
-                                             None, None, d_ss.ptr, 1, 1e-6, d_out.ptr, None, None))
+                                             None, None, d_ss.ptr, 1, 1e-6, d_out.ptr, None, None, None))
         return gpu.download(d_c, gpu.BF16, (rows, n)), d_out.to_numpy(np.float32, (4, rows))
 
     whole, whole_ss = run(m)
