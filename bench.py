@@ -503,6 +503,30 @@ def main():
                "result_bytes_per_step": out_elems * 4, "steps": e2e_steps,
                "api": "bfb_model_forward_host (fromHost -> Model::forward -> toHost), pinned host buffers"}
         del h_out
+        # the same pipeline handing the logits to the host as bf16 (bfb_model_forward_host_bf16): not the reference's
+        # fp32 contract, reported beside it because it is what keeps several GPUs from saturating one host's memory
+        if (precision or {}).get("storage") == "bf16":
+            h_out16 = torch.empty(out_elems, dtype=torch.int16).pin_memory()
+
+            def step_host16():
+                bfb.check(bfb.lib().bfb_model_forward_host_bf16(model._h, h_ids.data_ptr(), shape_arr, 2, h_out16.data_ptr(),
+                                                                oshape, C.byref(orank)))
+
+            step_host16()
+            launch.barrier()
+            torch.cuda.synchronize()
+            s3, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s3.record()
+            for _ in range(e2e_steps):
+                step_host16()
+            e3.record()
+            torch.cuda.synchronize()
+            launch.barrier()
+            ms16 = launch.max_over_ranks(s3.elapsed_time(e3), dev if world > 1 else None) / e2e_steps
+            e2e["bf16_result"] = {"value": replicas * tokens_per_step / (ms16 / 1e3), "unit": "tokens/s", "ms_per_step": ms16,
+                                  "d2h_bytes_per_step": bfb.host_transfer_bytes()[1],
+                                  "api": "bfb_model_forward_host_bf16 (logits stay bf16 on the host)"}
+            del h_out16
 
     if world > 1:
         launch.barrier()

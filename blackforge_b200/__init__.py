@@ -111,6 +111,7 @@ SIGNATURES = {
     "bfb_model_forward": (_I32, [_P, _P, C.POINTER(_I64), _I32, _I32, C.POINTER(_P), C.POINTER(_I64),
                                  C.POINTER(_I32), _P]),
     "bfb_model_forward_host": (_I32, [_P, _P, C.POINTER(_I64), _I32, _P, C.POINTER(_I64), C.POINTER(_I32)]),
+    "bfb_model_forward_host_bf16": (_I32, [_P, _P, C.POINTER(_I64), _I32, _P, C.POINTER(_I64), C.POINTER(_I32)]),
     "bfb_host_transfer_bytes": (_I32, [C.POINTER(_I64), C.POINTER(_I64)]),
     "bfb_host_widen_bf16": (_I32, [_P, _P, _I64, _I32]),
     "bfb_launch_count": (_I64, [_I32]),
@@ -339,6 +340,19 @@ class Model:
         out = np.empty([out_shape[i] for i in range(out_rank.value)], dtype=np.float32)
         check(lib().bfb_model_forward_host(self._h, x.ctypes.data, shape, x.ndim, out.ctypes.data, out_shape,
                                            C.byref(out_rank)))
+        return out
+
+    def forward_host_bf16(self, x) -> np.ndarray:
+        """Host ids in, host logits out as bf16 bit patterns (uint16); needs storage bf16."""
+        a = np.ascontiguousarray(x, dtype=np.float32)
+        s = (_I64 * a.ndim)(*a.shape)
+        out_shape = (_I64 * 8)()
+        out_rank = _I32(0)
+        check(lib().bfb_model_forward_host_bf16(self._h, a.ctypes.data, s, a.ndim, None, out_shape, C.byref(out_rank)))
+        oshape = tuple(out_shape[i] for i in range(out_rank.value))
+        out = np.empty(oshape, dtype=np.uint16)
+        check(lib().bfb_model_forward_host_bf16(self._h, a.ctypes.data, s, a.ndim, out.ctypes.data, out_shape,
+                                                C.byref(out_rank)))
         return out
 
     def forward_device(self, d_input: int, shape: Sequence[int], trusted: bool = False, stream=None):

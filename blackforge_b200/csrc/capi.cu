@@ -741,6 +741,62 @@ bfb_status bfb_host_transfer_bytes(int64_t* h2d_bytes, int64_t* d2h_bytes) {
     });
 }
 
+// The same pipeline with the result left as it crossed the link: bf16. No host thread touches the data.
+bfb_status bfb_model_forward_host_bf16(bfb_model* model, const float* h_input, const int64_t* shape, int32_t rank,
+                                       uint16_t* h_out16, int64_t* out_shape, int32_t* out_rank) {
+    return guarded([&] {
+        require(model != nullptr && h_input != nullptr && shape != nullptr && out_shape != nullptr && out_rank != nullptr,
+                "model_forward_host_bf16: null argument");
+        require(rank >= 1 && rank <= 8, "model_forward_host_bf16: bad rank");
+        std::vector<std::size_t> dims(shape, shape + rank);
+        std::vector<std::size_t> outDims = model->model->outputShape(dims);
+        *out_rank = static_cast<int32_t>(outDims.size());
+        for (std::size_t i = 0; i < outDims.size(); ++i) out_shape[i] = static_cast<int64_t>(outDims[i]);
+        if (h_out16 == nullptr) return;  // shape query only
+        if (!model->model->resultIsBf16Exact()) {
+            bfb::fail(BFB_UNSUPPORTED, "model_forward_host_bf16: needs storage bf16 and a pipeline from an embedding to a linear");
+        }
+        requireDevice();
+        std::size_t count = 1;
+        for (std::size_t d : dims) count *= d;
+        const std::size_t batch = dims[0];
+        if (count == 0 || batch == 0) return;
+        bfb200::DeviceTensor in(dims);
+        BFB_CUDA(cudaMemcpy(in.data(), h_input, count * sizeof(float), cudaMemcpyHostToDevice));
+        hostTransfer().h2d = static_cast<int64_t>(count * sizeof(float));
+        hostTransfer().d2h = 0;
+        HostPathStreams& st = hostPathStreams();
+        const std::size_t perSeqIn = count / batch;
+        std::size_t outCount = 1;
+        for (std::size_t d : outDims) outCount *= d;
+        const std::size_t perSeqOut = outCount / batch;
+        const std::size_t seqs = batch >= 16 ? std::max<std::size_t>(1, batch / 8) : step4(batch);
+        st.ensureStaging(seqs * perSeqOut * 2);   // only the device slots of the ring are used here
+        std::size_t slice = 0;
+        for (std::size_t b0 = 0; b0 < batch; b0 += seqs, ++slice) {
+            const std::size_t nb = std::min(seqs, batch - b0);
+            const int k = static_cast<int>(slice % HostPathStreams::kSlots);
+            // the copy that last read this device slot (four slices ago) must have finished
+            if (slice >= HostPathStreams::kSlots) BFB_CUDA(cudaEventSynchronize(st.copied[k]));
+            std::vector<std::size_t> sliceDims = dims;
+            sliceDims[0] = nb;
+            bfb200::DeviceTensor view = bfb200::DeviceTensor::borrow(in.data() + b0 * perSeqIn, sliceDims);
+            try {
+                model->model->forwardBf16(view, st.dev16[k], false, st.compute);
+            } catch (...) {
+                view.releaseOwnership();
+                cudaStreamSynchronize(st.copy);
+                throw;
+            }
+            view.releaseOwnership();
+            BFB_CUDA(cudaMemcpyAsync(h_out16 + b0 * perSeqOut, st.dev16[k], nb * perSeqOut * 2, cudaMemcpyDeviceToHost, st.copy));
+            BFB_CUDA(cudaEventRecord(st.copied[k], st.copy));
+            hostTransfer().d2h += static_cast<int64_t>(nb * perSeqOut * 2);
+        }
+        BFB_CUDA(cudaStreamSynchronize(st.copy));
+    });
+}
+
 int64_t bfb_launch_count(int32_t reset) {
     int64_t v = bfb::launchCounter();
     if (reset != 0) bfb::launchCounter() = 0;

@@ -333,6 +333,13 @@ bfb_status bfb_model_generation_position(bfb_model* model, int64_t* position);
  * h_out must hold product(out_shape) floats; call once with h_out == NULL to learn the shape. */
 bfb_status bfb_model_forward_host(bfb_model* model, const float* h_input, const int64_t* shape, int32_t rank,
                                   float* h_out, int64_t* out_shape, int32_t* out_rank);
+/* The same call for a host that takes the logits as bf16 (no reference counterpart: its tensors are fp32). Needs
+ * `storage bf16` and a pipeline from an embedding to a final linear, where every logit IS a bf16 number, so
+ * h_out16[i] holds the upper 16 bits of the fp32 word bfb_model_forward_host would deliver. Half the bytes over the
+ * link and into host memory, and no host thread touches them: what to use when several GPUs return logits to one
+ * host, whose memory bandwidth is then the limit. BFB_UNSUPPORTED for other models. */
+bfb_status bfb_model_forward_host_bf16(bfb_model* model, const float* h_input, const int64_t* shape, int32_t rank,
+                                       uint16_t* h_out16, int64_t* out_shape, int32_t* out_rank);
 /* Bytes the calling thread's most recent bfb_model_forward_host moved over the host link: ids host to device,
  * result device to host. Under `storage bf16` part of the result travels as 2-byte bf16 and is widened to the
  * caller's fp32 words by host threads, so d2h can be below 4 * product(out_shape).

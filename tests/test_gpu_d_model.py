@@ -319,3 +319,18 @@ def test_operator_level_incremental_attention(gpu):
     want = O.model_forward(ops, params, ids, exact_order=False)
     got = np.concatenate([m.forward_incremental(ids[:, a:b]) for a, b in ((0, 10), (10, 11), (11, 20), (20, 24))], axis=1)
     assert np.max(np.abs(got - want)) <= 1e-4
+
+
+def test_bf16_host_result_is_the_upper_half_of_the_fp32_result(gpu):
+    ops = O.lm_ops(**TC)
+    m = gpu.Model(ops, precision={"storage": "bf16", "compute": "bf16"}, seed=11)
+    for batch in (3, 19):          # one slice per call; ten slices through the four device slots
+        ids = O.synth_token_ids(batch, 96, TC["vocab"], seed=6)
+        want = m.forward_host(ids)
+        got = m.forward_host_bf16(ids)
+        assert got.dtype == np.uint16 and got.shape == want.shape
+        assert np.array_equal(got.astype(np.uint32) << 16, want.view(np.uint32))
+        assert gpu.host_transfer_bytes()[1] == want.size * 2
+    m32 = gpu.Model(ops, precision={"storage": "fp32", "compute": "bf16"}, seed=11)
+    with pytest.raises(gpu.BfbError):
+        m32.forward_host_bf16(ids)
