@@ -364,6 +364,10 @@ def main():
                     help="tokens of the single-thread cpu_baseline sample of the default arm (about 11 s)")
     ap.add_argument("--cpu-workers", type=int, default=32)
     ap.add_argument("--seed", type=int, default=1234)
+    ap.add_argument("--tp-groups", type=int, default=2,
+                    help="tensor-parallel workloads: sequence groups whose all-reduces overlap the next group's GEMMs (1: none)")
+    ap.add_argument("--tp-reserved-sms", type=int, default=0,
+                    help="SMs the persistent kernels leave to the overlapped collective")
     ap.add_argument("--decode", action="store_true",
                     help="measure key/value-cache generation instead of prefill: a prompt of --context tokens per "
                          "sequence (untimed), then --steps single-token steps for the whole batch")
@@ -411,6 +415,7 @@ def main():
         ident = launch.broadcast_bytes(bfb.tp_unique_id() if rank == 0 else b"", 128, 0, dev)
         bfb.tp_init(ident, rank, world)
         model.set_tensor_parallel(rank, world)
+        model.set_tensor_parallel_overlap(args.tp_groups, args.tp_reserved_sms if args.tp_groups > 1 else 0)
         # weights drawn on the device (N(0, 0.01), the same full matrices whatever the split); the fp32 copies of
         # the GEMM weights are dropped once the first forward has converted them
         for i, _name in enumerate(model.param_names()):
@@ -577,6 +582,8 @@ def main():
                    "precision": precision,
                    "parallelism": (f"tensor-parallel x{world}: heads, feed-forward columns and logits columns sharded, "
                                    "NCCL all-reduce after the out-projection and the feed-forward down-projection"
+                                   + (f", {args.tp_groups} sequence groups: one group's all-reduce runs beside the next "
+                                      f"group's kernels, whose GEMMs draw their tiles dynamically ({args.tp_reserved_sms} SMs left free)" if args.tp_groups > 1 else "")
                                    if tensor_parallel else f"batch-sharded x{world}, no data-path collective"),
                    "l2": "per-step working set (weights and activations, GBs) far exceeds the 126 MB L2; no flush needed",
                    "flops_per_token": g_flops + a_flops},

@@ -94,6 +94,8 @@ SIGNATURES = {
     "bfb_model_create_uninitialised": (_I32, [C.POINTER(OpDesc), _I32, _I64, C.POINTER(Precision), C.POINTER(_P)]),
     "bfb_model_destroy": (None, [_P]),
     "bfb_model_set_tensor_parallel": (_I32, [_P, _I32, _I32]),
+    "bfb_model_set_tensor_parallel_overlap": (_I32, [_P, _I32, _I32]),
+    "bfb_set_shared_sm_mode": (_I32, [_I32, _I32]),
     "bfb_model_param_count": (_I32, [_P]),
     "bfb_model_param_name": (C.c_char_p, [_P, _I32]),
     "bfb_model_param_rank": (_I32, [_P, _I32]),
@@ -294,6 +296,9 @@ class Model:
     def set_tensor_parallel(self, rank: int, world: int):
         check(lib().bfb_model_set_tensor_parallel(self._h, rank, world))
 
+    def set_tensor_parallel_overlap(self, groups: int, reserved_sms: int):
+        check(lib().bfb_model_set_tensor_parallel_overlap(self._h, groups, reserved_sms))
+
     def param_names(self) -> List[str]:
         return [lib().bfb_model_param_name(self._h, i).decode() for i in range(lib().bfb_model_param_count(self._h))]
 
@@ -425,6 +430,10 @@ def tp_unique_id() -> bytes:
     buf = C.create_string_buffer(128)
     check(lib().bfb_tp_unique_id(buf))
     return buf.raw
+
+
+def set_shared_sm_mode(dynamic_tiles: bool, reserved_sms: int = 0):
+    check(lib().bfb_set_shared_sm_mode(1 if dynamic_tiles else 0, reserved_sms))
 
 
 def tp_init(unique_id: bytes, rank: int, world: int):

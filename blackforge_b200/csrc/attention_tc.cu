@@ -562,7 +562,7 @@ void attentionTensorCore(const AttentionArgs& a, cudaStream_t stream) {
     const int64_t items = static_cast<int64_t>(p.numQBlocks) * a.batch * a.numHeads;
     require(items <= 0x7FFFFFFF, "attention: too many query blocks for one launch");
     p.totalItems = static_cast<int>(items);
-    const int grid = static_cast<int>(std::min<int64_t>(items, smCount()));
+    const int grid = static_cast<int>(std::min<int64_t>(items, persistentSms()));
     // visible (query, key) pairs per (batch, head): causal rows see old_len + i + 1 keys
     const double nl = static_cast<double>(a.newLen), tl = static_cast<double>(a.totalLen);
     const double pairs = a.causal ? nl * static_cast<double>(a.oldLen) + nl * (nl + 1.0) / 2.0 : nl * tl;

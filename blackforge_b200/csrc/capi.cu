@@ -385,6 +385,21 @@ bfb_status bfb_model_set_tensor_parallel(bfb_model* model, int32_t rank, int32_t
     });
 }
 
+bfb_status bfb_set_shared_sm_mode(int32_t dynamic_tiles, int32_t reserved_sms) {
+    return guarded([&] {
+        require(reserved_sms >= 0, "shared_sm_mode: reserved_sms must not be negative");
+        bfb::setDynamicTiles(dynamic_tiles != 0);
+        bfb::setReservedSms(reserved_sms);
+    });
+}
+
+bfb_status bfb_model_set_tensor_parallel_overlap(bfb_model* model, int32_t groups, int32_t reserved_sms) {
+    return guarded([&] {
+        require(model != nullptr, "model: null handle");
+        model->model->setTensorParallelOverlap(groups, reserved_sms);
+    });
+}
+
 // Parameter metadata comes from the structure alone: no device memory is touched, so these work
 // without a GPU.
 int32_t bfb_model_param_count(const bfb_model* model) {

@@ -80,6 +80,18 @@ inline size_t dtypeBytes(int32_t dtype) {
 
 // Number of SMs of the current device (cached per device).
 int smCount();
+// SMs the persistent kernels (tcgen05 GEMMs, flash attention) size their grids for: all of them, minus the ones a
+// caller set aside for kernels of another stream that must run beside them (a collective that overlaps the GEMMs:
+// a persistent grid over every SM would make it wait for a whole GEMM). Even, at least 2.
+int persistentSms();
+void setReservedSms(int count);
+int reservedSms();
+// Dynamic tile order for the CTA-pair GEMM (tiles drawn from a device counter instead of the static round-robin):
+// for GEMMs that share the SMs with a kernel of another stream. nextTileCounter() lends one of a small rotating set
+// of device counters of the current device; the caller zeroes it on its stream before the launch.
+void setDynamicTiles(bool on);
+bool dynamicTiles();
+int* nextTileCounter();
 
 // ---- per-kernel device timing (off by default) -----------------------------------------------------
 // When enabled on the calling thread, a ProfileScope brackets one kernel launch with CUDA events on

@@ -346,7 +346,7 @@ void launchTc(const GemmArgs& g, cudaStream_t stream) {
     int tilesN = static_cast<int>((g.n + kBlockN - 1) / kBlockN);
     int groups = (tilesN + 15) / 16;
     int groupN = (tilesN + groups - 1) / groups;
-    int grid = std::min(tilesM * tilesN, smCount());
+    int grid = std::min(tilesM * tilesN, persistentSms());
     EpilogueParams ep{g.c, g.bias, g.residual, g.alpha, g.dAlpha, g.epilogue, g.roundCBf16};
     auto kernel = gemmTcKernel<kElemBytes, kBMnMajor, TC>;
     // per device, so set on every launch (the process may have switched devices)

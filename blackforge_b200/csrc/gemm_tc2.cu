@@ -15,6 +15,14 @@
 //   empty[s]     one per CTA; the leader's tcgen05.commit arrives on both
 //   accFull[b]   one per CTA; same commit form, tells both epilogues the accumulator is complete
 //   accEmpty[b]  lives in the leader; the epilogue threads of both CTAs arrive on it
+//   tileFull[r]  one per CTA; the scheduler warp (leader) arrives after writing the tile index into both CTAs' rings
+//   tileFree[r]  lives in the leader; every role warp of both CTAs arrives once it has read slot r
+//
+// Tile order: static round-robin (tile = pair + i * pairs), every role computing it for itself. With a device
+// counter (setDynamicTiles) a scheduler warp in the leader CTA draws tiles with atomicAdd and hands them to the
+// roles of both CTAs through a small ring of tile indices: pairs that start late, because SMs are held by a kernel
+// of another stream (a collective that runs beside the GEMM), find the work done by the others instead of leaving
+// a tail. The ring costs 2-4 % of an undisturbed GEMM, so it is only used when asked for.
 // Operands: A [M,K] and B^T [N,K], K contiguous (bf16 or e4m3); C f32 or bf16 with the fused epilogues.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -35,6 +43,9 @@ constexpr int kRowBytes2 = 128;
 constexpr int kABytes2 = 128 * kRowBytes2;  // 16 KiB
 constexpr int kThreads2 = 384;              // producer, MMA, TMEM, spare + 8 epilogue warps
 constexpr int kEpilogueThreads2 = 256;
+constexpr int kTileRing = 4;                // tile indices in flight between the scheduler warp and the roles
+// arrivals that free a ring slot: two producers, the MMA warp, the epilogue warps of both CTAs
+constexpr int kTileReaders = 2 + 1 + 2 * (kEpilogueThreads2 / 32);
 
 template <int kAccN>
 struct PairCfg {
@@ -88,7 +99,7 @@ __device__ __forceinline__ float siluFast(float x) { return __fdividef(x, 1.0f +
 template <int kElemBytes, typename TC, int kAccN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
 gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, PairEpilogue ep,
-               int m, int n, int k, int tilesM, int tilesN, int groupN, int* status) {
+               int m, int n, int k, int tilesM, int tilesN, int groupN, int* status, int* tileCounter) {
     using Cfg = PairCfg<kAccN>;
     constexpr int kBlockK = kRowBytes2 / kElemBytes;
     constexpr int kMmaPerStage = 4;
@@ -105,8 +116,11 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
     uint64_t* emptyBar = bars + kStages;
     uint64_t* accFullBar = bars + 2 * kStages;
     uint64_t* accEmptyBar = accFullBar + 2;
-    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(accEmptyBar + 2);
+    uint64_t* tileFullBar = accEmptyBar + 2;
+    uint64_t* tileFreeBar = tileFullBar + kTileRing;
+    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(tileFreeBar + kTileRing);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
+    volatile int* tileRing = reinterpret_cast<volatile int*>(tmemSlot + 2);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -126,6 +140,10 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
             mbar_init(&accFullBar[b], 1);
             mbar_init(&accEmptyBar[b], 2 * (kEpilogueThreads2 / 32));  // one arrival per epilogue warp of both CTAs
         }
+        for (int r = 0; r < kTileRing; ++r) {
+            mbar_init(&tileFullBar[r], 1);
+            mbar_init(&tileFreeBar[r], kTileReaders);
+        }
         *abortFlag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmapA);
@@ -141,12 +159,57 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
     tc_fence_after();
     const uint32_t tmemBase = *tmemSlot;
 
-    if (warp == 0) {
+    // next tile index for this warp (warp-uniform), -1 when there is none or the wait was abandoned
+    int ringSlot = 0;
+    uint32_t ringPhase = 0;
+    int staticNext = clusterId;
+    auto nextTile = [&]() -> int {
+        if (tileCounter == nullptr) {   // static round-robin: no scheduler warp, no ring
+            const int t = staticNext;
+            staticNext += numClusters;
+            return t < totalTiles ? t : -1;
+        }
+        if (!warp_all(mbar_wait_cluster(&tileFullBar[ringSlot], ringPhase, abortFlag, status, kDevTimeoutTile))) return -1;
+        const int t = tileRing[ringSlot];
+        __syncwarp();  // every lane has read the slot before it is handed back
+        if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&tileFreeBar[ringSlot]), 0));
+        if (++ringSlot == kTileRing) {
+            ringSlot = 0;
+            ringPhase ^= 1u;
+        }
+        return t;
+    };
+
+    if (warp == 3 && leader && tileCounter != nullptr) {
+        // ---------------- tile scheduler (leader CTA, dynamic order only) ----------------
+        const uint32_t peerRing = mapa_cluster(smem_u32(const_cast<int*>(tileRing)), 1);
+        const uint32_t peerFull = mapa_cluster(smem_u32(tileFullBar), 1);
+        int slot = 0;
+        uint32_t phase = 0;
+        while (true) {
+            if (!warp_all(mbar_wait(&tileFreeBar[slot], phase ^ 1u, abortFlag, status, kDevTimeoutTile))) break;
+            int t = 0;
+            if (lane == 0) {
+                t = atomicAdd(tileCounter, 1);
+                if (t >= totalTiles) t = -1;
+                tileRing[slot] = t;
+                st_shared_cluster_u32(peerRing + static_cast<uint32_t>(slot) * 4u, static_cast<uint32_t>(t));
+                mbar_arrive(&tileFullBar[slot]);
+                mbar_arrive_cluster(peerFull + static_cast<uint32_t>(slot) * 8u);
+            }
+            t = __shfl_sync(0xFFFFFFFFu, t, 0);
+            if (t < 0) break;   // the roles have been told; nothing more to hand out
+            if (++slot == kTileRing) {
+                slot = 0;
+                phase ^= 1u;
+            }
+        }
+    } else if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
         int stage = 0;
         uint32_t phase = 0;
         bool alive = true;
-        for (int t = clusterId; t < totalTiles && alive; t += numClusters) {
+        for (int t = nextTile(); t >= 0 && alive; t = nextTile()) {
             PairTile tc = pairTileCoord(t, tilesM, tilesN, groupN);
             const int rowA = tc.m * kPairM + static_cast<int>(rank) * 128;
             for (int kb = 0; kb < numK; ++kb) {
@@ -180,7 +243,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
         uint32_t phase = 0;
         int local = 0;
         bool alive = true;
-        for (int t = clusterId; t < totalTiles && alive; t += numClusters, ++local) {
+        for (int t = nextTile(); t >= 0 && alive; t = nextTile(), ++local) {
             const int buf = local % kBufs;
             const uint32_t accPhase = static_cast<uint32_t>(local / kBufs) & 1u;
             if (!warp_all(mbar_wait(&accEmptyBar[buf], accPhase ^ 1u, abortFlag, status, kDevTimeoutAccEmpty))) break;
@@ -231,7 +294,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
         TC* cOut = static_cast<TC*>(ep.c);
         const TC* res = static_cast<const TC*>(ep.residual);
         int local = 0;
-        for (int t = clusterId; t < totalTiles; t += numClusters, ++local) {
+        for (int t = nextTile(); t >= 0; t = nextTile(), ++local) {
             PairTile tc = pairTileCoord(t, tilesM, tilesN, groupN);
             const int buf = local % kBufs;
             const uint32_t accPhase = static_cast<uint32_t>(local / kBufs) & 1u;
@@ -395,16 +458,21 @@ void launchPair(const GemmArgs& g, cudaStream_t stream) {
     const int maxGroup = 4096 / kAccN;
     const int groups = (tilesN + maxGroup - 1) / maxGroup;
     const int groupN = (tilesN + groups - 1) / groups;
-    const int clusters = std::max(1, std::min(tilesM * tilesN, smCount() / 2));
+    const int clusters = std::max(1, std::min(tilesM * tilesN, persistentSms() / 2));
     PairEpilogue ep{g.c, g.bias, g.residual, g.alpha, g.dAlpha, g.epilogue, g.roundCBf16,
                     g.rowSumSq, g.rowSumSqParts, g.rowInvDim, g.rowEps, g.outSumSq, g.outMaxAbs};
     auto kernel = gemmPairKernel<kElemBytes, TC, kAccN>;
     BFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    int* tileCounter = nullptr;
+    if (dynamicTiles() && tilesM * tilesN > clusters) {
+        tileCounter = nextTileCounter();
+        BFB_CUDA(cudaMemsetAsync(tileCounter, 0, sizeof(int), stream));
+    }
     ProfileScope prof(kProfGemmTc, stream, 2.0 * static_cast<double>(g.m) * static_cast<double>(g.n) * static_cast<double>(g.k));
     kernel<<<2 * clusters, kThreads2, Cfg::kSmemBytes, stream>>>(*reinterpret_cast<CUtensorMap*>(ta.bytes),
                                                                  *reinterpret_cast<CUtensorMap*>(tb.bytes), ep,
                                                                  static_cast<int>(g.m), static_cast<int>(g.n),
-                                                                 static_cast<int>(g.k), tilesM, tilesN, groupN, g.dStatus);
+                                                                 static_cast<int>(g.k), tilesM, tilesN, groupN, g.dStatus, tileCounter);
     BFB_LAUNCH_CHECK();
     noteLaunch();
 }

@@ -152,6 +152,11 @@ public:
     // Heads, feed-forward columns and logits columns sharded over `world` ranks; call before any
     // parameter is set. Outputs of a final linear are this rank's column slice.
     void setTensorParallel(int rank, int world);
+    // How a tensor-parallel prompt pass hides its all-reduces: the batch is cut into `groups` groups of sequences
+    // (1 = no overlap; fewer when the batch does not divide), and while one group's rows are summed over the ranks
+    // on a second stream the next group computes; its GEMMs draw their tiles from a device counter (pairs the
+    // collective's CTAs keep waiting then leave no tail) and its persistent kernels can leave `reservedSms` SMs free. Defaults: 2 and 0 (environment BFB_TP_CHUNKS, BFB_TP_RESERVE_SMS). Results do not depend on it.
+    void setTensorParallelOverlap(int groups, int reservedSms);
 
     DeviceTensor forward(const DeviceTensor& input, bool inputRangeTrusted = false, void* stream = nullptr);
     // Under `storage bf16` every value of forward()'s result is a bf16 number held in an fp32 word. When the

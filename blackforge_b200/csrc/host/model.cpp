@@ -18,6 +18,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <fstream>
 #include <map>
@@ -148,8 +149,37 @@ struct Model::Impl {
     std::size_t genBatch = 0;      // batch size the caches were opened with
     DevBuf fp8Stats;  // per GEMM input: [amax, scale, inverse, alpha]
     DevBuf status;    // device status word for bounded waits + id range counter
+    // Tensor-parallel prompt passes run the layers over `tpChunks` groups of sequences, the all-reduce of one group on
+    // `commStream` beside the next group's GEMMs, which leave `tpReserveSms` SMs to it.
+    int tpChunks = 2;
+    int tpReserveSms = 0;
+    cudaStream_t commStream = nullptr;
+    std::vector<cudaEvent_t> computed, reduced;
+
+    Impl() {
+        if (const char* e = std::getenv("BFB_TP_CHUNKS")) tpChunks = std::max(1, std::atoi(e));
+        if (const char* e = std::getenv("BFB_TP_RESERVE_SMS")) tpReserveSms = std::max(0, std::atoi(e));
+    }
+
+    void ensureOverlapStreams(std::size_t chunks) {
+        if (commStream == nullptr) {
+            int least = 0, greatest = 0;
+            BFB_CUDA(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+            BFB_CUDA(cudaStreamCreateWithPriority(&commStream, cudaStreamNonBlocking, greatest));
+        }
+        while (computed.size() < chunks) {
+            cudaEvent_t a = nullptr, b = nullptr;
+            BFB_CUDA(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+            BFB_CUDA(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+            computed.push_back(a);
+            reduced.push_back(b);
+        }
+    }
 
     ~Impl() {
+        for (cudaEvent_t e : computed) cudaEventDestroy(e);
+        for (cudaEvent_t e : reduced) cudaEventDestroy(e);
+        if (commStream != nullptr) cudaStreamDestroy(commStream);
         for (auto& l : layers) {
             l.w0.reset();
             l.w1.reset();
@@ -634,9 +664,65 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
     bool haveResult = false;
     const std::size_t w = static_cast<std::size_t>(tpWorld);
 
+    // Tensor parallelism, prompt pass: sequences are independent, so an attention or feed-forward layer runs over
+    // one group of sequences after the other, and the all-reduce that completes a group's rows of x runs on a second
+    // stream while the next group (then the next layer of the first group) computes. All groups share the scratch
+    // buffers (the compute stream is in order); only their rows of x differ.
+    std::size_t groups = 1;
+    std::vector<char> inFlight;   // group g's rows of x are being reduced on the second stream
+    auto planGroups = [&](std::size_t batch) {
+        std::size_t want = (tpWorld > 1 && !incremental) ? static_cast<std::size_t>(tpChunks) : 1;
+        while (want > 1 && (batch % want != 0)) --want;
+        if (want != groups) {
+            require(std::find(inFlight.begin(), inFlight.end(), 1) == inFlight.end(), "Model: group count changed mid-flight");
+            groups = want;
+        }
+        if (groups > 1) ensureOverlapStreams(groups);
+        inFlight.resize(groups, 0);
+    };
+    auto awaitGroup = [&](std::size_t g) {
+        if (g < inFlight.size() && inFlight[g]) {
+            BFB_CUDA(cudaStreamWaitEvent(stream, reduced[g], 0));
+            inFlight[g] = 0;
+        }
+    };
+    auto awaitAllGroups = [&]() {
+        for (std::size_t g = 0; g < inFlight.size(); ++g) awaitGroup(g);
+    };
+    // the sum over ranks of `count` values at `rows`, which group g's GEMM has just written on `stream`
+    auto reduceGroup = [&](std::size_t g, void* rows, std::size_t count) {
+        if (tpWorld == 1) return;
+        if (groups == 1) {
+            tpAllReduceSum(rows, static_cast<int64_t>(count), S, stream);
+            return;
+        }
+        BFB_CUDA(cudaEventRecord(computed[g], stream));
+        BFB_CUDA(cudaStreamWaitEvent(commStream, computed[g], 0));
+        tpAllReduceSum(rows, static_cast<int64_t>(count), S, commStream);
+        BFB_CUDA(cudaEventRecord(reduced[g], commStream));
+        inFlight[g] = 1;
+    };
+    // while a collective may hold some SMs, the GEMMs draw their tiles dynamically (and may leave SMs free)
+    struct SharedSmGuard {
+        int reservedBefore;
+        bool dynamicBefore;
+        SharedSmGuard(bool on, int reserve) : reservedBefore(bfb::reservedSms()), dynamicBefore(bfb::dynamicTiles()) {
+            if (on) {
+                bfb::setReservedSms(reserve);
+                bfb::setDynamicTiles(true);
+            }
+        }
+        ~SharedSmGuard() {
+            bfb::setReservedSms(reservedBefore);
+            bfb::setDynamicTiles(dynamicBefore);
+        }
+    };
+    SharedSmGuard sharedSms(tpWorld > 1 && !incremental && tpChunks > 1, tpReserveSms);
+
     for (std::size_t i = 0; i < layers.size(); ++i) {
         Layer& l = layers[i];
-        const std::size_t tokens = tokensOf();
+        const std::size_t allTokens = tokensOf();
+        std::size_t tokens = allTokens;
         switch (l.kind) {
             case BFB_OP_EMBEDDING: {
                 require(i == 0, "Model: embedding must be the first operation of the planned route");
@@ -668,8 +754,16 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
             case BFB_OP_ATTENTION: {
                 require(x != nullptr, "Model: the planned route must start with an embedding");
                 if (shape.size() != 3) throw std::invalid_argument("selfAttention: input [batch, seq, dim] required");
-                const std::size_t batch = shape[0], seq = shape[1], d = feat, dl = d / w, hl = l.heads / w;
+                const std::size_t seq = shape[1], d = feat, dl = d / w, hl = l.heads / w;
                 const std::size_t hd = d / l.heads;
+                planGroups(shape[0]);
+                const std::size_t batch = shape[0] / groups;
+                tokens = batch * seq;
+                void* const xAll = x;
+                for (std::size_t g = 0; g < groups; ++g) {
+                x = static_cast<char*>(xAll) + g * tokens * d * sb;
+                awaitGroup(g);
+                if (groups > 1) ssParts = 0;
                 const float* sc = static_cast<const float*>(l.scales.ptr);
                 const float* dAlpha = nullptr;
                 void* qkv = buf("qkv", tokens * 3 * dl * 2);
@@ -727,12 +821,21 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                 float* produced = fuse && fusedNormOk(tokens, d, dl, l.w1.ptr) ? nextSumSq(tokens, d) : nullptr;
                 runGemm(aOut, l.w1.ptr, x, tokens, d, dl, S, epi, nullptr, x, dAlpha, 0, nullptr, 1, produced);
                 producedSumSq(produced, d);
-                if (tpWorld > 1) tpAllReduceSum(x, static_cast<int64_t>(tokens * d), S, stream);
+                reduceGroup(g, x, tokens * d);
+                }
+                x = xAll;
                 break;
             }
             case BFB_OP_FEEDFORWARD: {
                 require(x != nullptr, "Model: the planned route must start with an embedding");
                 const std::size_t d = feat, fl = l.hidden / w;
+                planGroups(shape.size() == 3 ? shape[0] : 1);
+                tokens = allTokens / groups;
+                void* const xAll = x;
+                for (std::size_t g = 0; g < groups; ++g) {
+                x = static_cast<char*>(xAll) + g * tokens * d * sb;
+                awaitGroup(g);
+                if (groups > 1) ssParts = 0;
                 const float* sc = static_cast<const float*>(l.scales.ptr);
                 const float* dAlpha = nullptr;
                 void* hidden = buf("hidden", tokens * fl * 2);
@@ -787,11 +890,14 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                 runGemm(a2, l.w1.ptr, x, tokens, d, fl, S, lead ? BFB_EPI_BIAS_RESIDUAL : BFB_EPI_NONE,
                         lead ? params[l.p[3]].value.data() : nullptr, lead ? x : nullptr, dAlpha, 0, nullptr, 1, produced);
                 producedSumSq(produced, d);
-                if (tpWorld > 1) tpAllReduceSum(x, static_cast<int64_t>(tokens * d), S, stream);
+                reduceGroup(g, x, tokens * d);
+                }
+                x = xAll;
                 break;
             }
             case BFB_OP_LINEAR: {
                 require(x != nullptr, "Model: the planned route must start with an embedding");
+                awaitAllGroups();
                 const std::size_t d = feat, outL = l.shardedLinear ? l.outFeat / w : l.outFeat;
                 const void* a16 = x;
                 if (S == BFB_F32) {
@@ -830,6 +936,7 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
             default: {
                 // elementwise / norm / softmax / standalone positions: run on an fp32 copy
                 require(x != nullptr, "Model: the planned route must start with an embedding");
+                awaitAllGroups();
                 const std::size_t count = tokens * feat;
                 DeviceTensor tmp(shape);
                 bfb::castScaled(x, S, tmp.data(), BFB_F32, static_cast<int64_t>(count), 1.0f, nullptr, stream);
@@ -851,6 +958,7 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
             }
         }
     }
+    awaitAllGroups();
     if (!haveResult) {
         require(x != nullptr, "Model: empty pipeline");
         result = DeviceTensor(shape);
@@ -882,6 +990,12 @@ Model::Model(const std::vector<OpDesc>& ops, std::int64_t inputLastDim, unsigned
 }
 
 Model::~Model() = default;
+
+void Model::setTensorParallelOverlap(int groups, int reservedSms) {
+    if (groups < 1 || reservedSms < 0) throw std::invalid_argument("Model: bad tensor-parallel overlap setting");
+    impl_->tpChunks = groups;
+    impl_->tpReserveSms = reservedSms;
+}
 
 void Model::setTensorParallel(int rank, int world) {
     if (world < 1 || rank < 0 || rank >= world) throw std::invalid_argument("Model: bad tensor-parallel rank/size");

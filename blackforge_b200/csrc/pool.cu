@@ -3,6 +3,7 @@
 // The pool keeps the reference's contract (exact-size free lists per device, memory is reused and
 // never handed back to the driver on release, release must not throw) and adds a mutex, statistics
 // and an explicit trim.
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -34,6 +35,37 @@ int smCount() {
     BFB_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
     cache[dev] = n;
     return n;
+}
+
+namespace {
+std::atomic<int> gReservedSms{0};
+}
+
+namespace {
+std::atomic<bool> gDynamicTiles{false};
+constexpr int kTileCounters = 256;
+}
+
+void setDynamicTiles(bool on) { gDynamicTiles.store(on); }
+bool dynamicTiles() { return gDynamicTiles.load(); }
+int* nextTileCounter() {
+    static std::mutex mu;
+    static std::unordered_map<int, int*> perDevice;
+    static std::unordered_map<int, unsigned> next;
+    int dev = 0;
+    BFB_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    int*& base = perDevice[dev];
+    if (base == nullptr) BFB_CUDA(cudaMalloc(&base, kTileCounters * sizeof(int)));
+    return base + (next[dev]++ % kTileCounters);
+}
+
+void setReservedSms(int count) { gReservedSms.store(count < 0 ? 0 : count); }
+int reservedSms() { return gReservedSms.load(); }
+int persistentSms() {
+    const int all = smCount();
+    const int left = (all - gReservedSms.load()) & ~1;
+    return left < 2 ? (all < 2 ? all : 2) : left;
 }
 
 // ---- per-kernel timing -----------------------------------------------------------------------------

@@ -19,6 +19,7 @@ enum : int {
     kDevTimeoutAccEmpty = 4,
     kDevTimeoutSoftmax = 5,
     kDevTimeoutOther = 6,
+    kDevTimeoutTile = 7,   // a role of the CTA-pair GEMM waiting for its next tile index (or the scheduler for a free slot)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -71,6 +72,39 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 255u) == 0u) {
+            if (*abort_flag != 0) return false;
+            if (global_timer_ns() - start > kWaitLimitNs) {
+                *abort_flag = 1;
+                if (status != nullptr) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+// The same wait with acquire semantics at cluster scope: for data another CTA of the cluster wrote to this CTA's
+// shared memory (st.shared::cluster) before its releasing arrive (mbar_arrive_cluster).
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                  int code) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    uint64_t start = global_timer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
         if ((++spins & 255u) == 0u) {
             if (*abort_flag != 0) return false;
             if (global_timer_ns() - start > kWaitLimitNs) {
@@ -211,6 +245,9 @@ __device__ __forceinline__ uint32_t mapa_cluster(uint32_t local_smem_addr, uint3
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t value) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(value) : "memory");
 }
 // TMA tile load whose completion bytes are booked on an mbarrier that may live in the peer CTA of the pair.
 __device__ __forceinline__ void tma_load_2d_pair(void* dst, const void* tmap, uint32_t mbar_cluster_addr, int c0, int c1) {

@@ -36,6 +36,9 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--dynamic-tiles", action="store_true",
+                    help="gemm: tiles drawn from a device counter (the mode for GEMMs that share the SMs)")
+    ap.add_argument("--reserved-sms", type=int, default=0, help="size the persistent grids for this many fewer SMs")
     args = ap.parse_args()
 
     import torch
@@ -44,6 +47,8 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("kernel_bench needs a CUDA device")
     lib = bfb.lib()
+    if args.dynamic_tiles or args.reserved_sms:
+        bfb.set_shared_sm_mode(args.dynamic_tiles, args.reserved_sms)
     rng = np.random.default_rng(0)
     flush = None if args.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 

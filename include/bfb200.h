@@ -287,6 +287,20 @@ bfb_status bfb_model_create_uninitialised(const bfb_op_desc* ops, int32_t n_ops,
  * sharded); the all-reduce is done by the communicator installed with bfb_tp_init. world == 1 is
  * the default. Must be called before parameters are set. */
 bfb_status bfb_model_set_tensor_parallel(bfb_model* model, int32_t rank, int32_t world);
+/* Overlap of the all-reduces with compute in a tensor-parallel prompt pass (the reference has no tensor
+ * parallelism; its data-parallel runner averages on the host, multi_gpu_train_runner.cu:275-297): the batch is
+ * cut into `groups` groups of sequences, and while one group's rows are summed over the ranks on a second stream
+ * the next group computes. The CTA-pair GEMMs of such a pass draw their tiles from a device counter, so that pairs
+ * kept waiting by the collective's CTAs leave no tail; the persistent kernels can also leave `reserved_sms` SMs
+ * free altogether. groups == 1 runs everything on the caller's stream. Defaults 2 and 0 (environment BFB_TP_CHUNKS,
+ * BFB_TP_RESERVE_SMS). May be changed between forward calls; results do not depend on it. */
+bfb_status bfb_model_set_tensor_parallel_overlap(bfb_model* model, int32_t groups, int32_t reserved_sms);
+
+/* Process-wide mode of the persistent tensor-core kernels for callers that run a kernel of their own beside them
+ * on another stream: dynamic_tiles != 0 makes the CTA-pair GEMM draw tiles from a device counter instead of the
+ * static round-robin (same tiles, same values); reserved_sms sizes the persistent grids for that many fewer SMs.
+ * Both default to 0. A tensor-parallel model sets and restores them around its own passes. */
+bfb_status bfb_set_shared_sm_mode(int32_t dynamic_tiles, int32_t reserved_sms);
 
 int32_t bfb_model_param_count(const bfb_model* model);
 const char* bfb_model_param_name(const bfb_model* model, int32_t index);

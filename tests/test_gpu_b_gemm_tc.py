@@ -263,6 +263,38 @@ def test_folded_rmsnorm_gives_the_same_bits_for_any_number_of_rows(gpu):
         assert np.array_equal(part, whole[:rows]) and np.array_equal(part_ss, whole_ss[:, :rows])
 
 
+@pytest.mark.parametrize("m,n,k", [(4133, 3080, 512), (9000, 1024, 256), (300, 512, 128)])
+def test_tiles_drawn_from_a_counter_give_the_same_bits(gpu, m, n, k):
+    """The CTA-pair GEMM with its tiles handed out by atomicAdd (the mode for GEMMs that share the SMs with another
+    stream's kernel), also on a grid sized for fewer SMs: same tiles, so every value and statistic is identical."""
+    rng = np.random.default_rng(m + n + k)
+    a = O.round_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    w = O.round_bf16(rng.standard_normal((n, k)).astype(np.float32) * 0.1)
+    d_a, d_w = gpu.upload(a, gpu.BF16), gpu.upload(w, gpu.BF16)
+    parts = (n + 127) // 128
+
+    def run():
+        d_ss, d_c = gpu.DeviceBuffer(m * 4), gpu.DeviceBuffer(m * n * 2)
+        d_out = gpu.DeviceBuffer(parts * m * 4)
+        gpu.check(gpu.lib().bfb_row_sum_squares(d_a.ptr, gpu.BF16, d_ss.ptr, m, k, None))
+        gpu.check(gpu.lib().bfb_gemm_rmsnorm(d_a.ptr, d_w.ptr, d_c.ptr, m, n, k, gpu.BF16, gpu.BF16, gpu.EPI["none"],
+                                             None, None, d_ss.ptr, 1, 1e-6, d_out.ptr, None, None, None))
+        return gpu.download(d_c, gpu.BF16, (m, n)), d_out.to_numpy(np.float32, (parts, m))
+
+    want, want_ss = run()
+    try:
+        for reserved in (0, 40, 146):
+            gpu.set_shared_sm_mode(True, reserved)
+            for _ in range(2):
+                got, got_ss = run()
+                assert np.array_equal(got, want) and np.array_equal(got_ss, want_ss), reserved
+    finally:
+        gpu.set_shared_sm_mode(False, 0)
+    ref = a.astype(np.float64) @ w.astype(np.float64).T
+    ref /= np.sqrt(np.mean(a.astype(np.float64) ** 2, axis=1, keepdims=True) + 1e-6)
+    assert np.max(np.abs(want - ref)) <= 2e-2 * np.max(np.abs(ref))
+
+
 @pytest.mark.parametrize("m,n,k,epilogue,c_dtype", [
     (1, 264, 136, "none", "bf16"),              # one row, N tail of 8 columns, K tail
     (7, 2048, 2048, "residual", "bf16"),        # 16 column tiles x 8 K-splits

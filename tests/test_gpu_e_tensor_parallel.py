@@ -46,6 +46,23 @@ m.set_tensor_parallel(rank, world)
 m.set_params(params)
 out = m.forward_host(ids)
 np.save(os.path.join(work, f"logits_{rank}.npy"), out)
+# the same pass with the all-reduces on the caller's stream (no sequence groups), and with other settings: the
+# groups are independent sequences and a two-rank sum has one order, so every value is the same
+for groups, reserved in ((1, 0), (2, 0), (2, 32)):
+    m.set_tensor_parallel_overlap(groups, reserved)
+    again = m.forward_host(ids)
+    assert np.array_equal(again, out), (groups, reserved, float(np.max(np.abs(again - out))))
+# bf16 residual stream (rmsnorm folded into the GEMMs, statistics per group)
+m16 = bfb.Model(ops, precision={"storage": "bf16", "compute": "bf16"}, random_init=False)
+m16.set_tensor_parallel(rank, world)
+m16.set_params(params)
+ids4 = O.synth_token_ids(4, 160, cfg["vocab"], seed=23)
+m16.set_tensor_parallel_overlap(1, 0)
+plain = m16.forward_host(ids4)
+m16.set_tensor_parallel_overlap(2, 16)
+grouped = m16.forward_host(ids4)
+assert np.array_equal(plain, grouped), float(np.max(np.abs(plain - grouped)))
+np.save(os.path.join(work, f"logits16_{rank}.npy"), grouped)
 bfb.tp_destroy()
 print("rank", rank, "ok", out.shape)
 """
@@ -74,3 +91,9 @@ def test_two_gpu_tensor_parallel_matches_single_gpu(gpu, tmp_path):
     want = single.forward_host(ids)
     # same arithmetic, different summation order across the two partial products
     assert np.max(np.abs(sharded - want)) / np.max(np.abs(want)) <= 5e-3
+    # bf16 residual stream, four sequences in two groups
+    sharded16 = np.concatenate([np.load(tmp_path / f"logits16_{r}.npy") for r in range(2)], axis=-1)
+    single16 = gpu.Model(ops, precision={"storage": "bf16", "compute": "bf16"}, random_init=False)
+    single16.set_params(params)
+    want16 = single16.forward_host(O.synth_token_ids(4, 160, CFG["vocab"], seed=23))
+    assert np.sqrt(np.sum((sharded16 - want16) ** 2) / np.sum(want16 ** 2)) <= 2e-2
