@@ -106,6 +106,10 @@ SIGNATURES = {
     "bfb_model_release_master_weights": (_I32, [_P]),
     "bfb_model_load_checkpoint": (_I32, [_P, C.c_char_p]),
     "bfb_model_save_checkpoint": (_I32, [_P, C.c_char_p]),
+    "bfb_model_benchmark": (_I32, [_P, _P, C.POINTER(_I64), _I32, _I64, _I64, _P, _P, _I32, _P]),
+    "bfb_model_load_checkpoint_streaming": (_I32, [_P, C.c_char_p, C.c_uint64, _P]),
+    "bfb_checkpoint_index": (_I32, [C.c_char_p, _I32, C.c_char_p, _I32, C.POINTER(_I32), C.POINTER(_I64),
+                                    C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(_I32)]),
     "bfb_model_forward_incremental": (_I32, [_P, _P, C.POINTER(_I64), _I32, _I32, C.POINTER(_P), C.POINTER(_I64),
                                               C.POINTER(_I32), _P]),
     "bfb_model_reset_generation": (_I32, [_P]),
@@ -332,6 +336,12 @@ class Model:
     def load_checkpoint(self, path: str):
         check(lib().bfb_model_load_checkpoint(self._h, path.encode()))
 
+    def load_checkpoint_streaming(self, path: str, chunk_bytes: int = 0) -> dict:
+        """load_checkpoint with its figures: tensors, file / read / uploaded bytes, seconds."""
+        stats = CheckpointLoadStats()
+        check(lib().bfb_model_load_checkpoint_streaming(self._h, path.encode(), chunk_bytes, C.byref(stats)))
+        return {name: getattr(stats, name) for name, _ in CheckpointLoadStats._fields_}
+
     def save_checkpoint(self, path: str):
         check(lib().bfb_model_save_checkpoint(self._h, path.encode()))
 
@@ -346,6 +356,22 @@ class Model:
         check(lib().bfb_model_forward_host(self._h, x.ctypes.data, shape, x.ndim, out.ctypes.data, out_shape,
                                            C.byref(out_rank)))
         return out
+
+    def benchmark(self, x, warmup: int = 1, measured: int = 5) -> dict:
+        """Device-timed passes over the host array `x` (uploaded once): mean ms, samples/s, the reference's memory
+        estimate and the mean device time of every pipeline operation inside the pass."""
+        a = np.ascontiguousarray(x, dtype=np.float32)
+        d_in = DeviceBuffer.from_numpy(a)
+        shape = (_I64 * a.ndim)(*a.shape)
+        res = BenchmarkResult()
+        count = max(1, len(self._ops))
+        per_op = (OpBenchmark * count)()
+        check(lib().bfb_model_benchmark(self._h, d_in.ptr, shape, a.ndim, warmup, measured, C.byref(res), per_op, count, None))
+        return {"mean_ms": res.mean_ms, "samples_per_second": res.samples_per_second,
+                "estimated_memory_bytes": res.estimated_memory_bytes, "warmup": res.warmup_iterations,
+                "measured": res.measured_iterations,
+                "per_operation": [(per_op[i].name.decode(), per_op[i].index, per_op[i].mean_ms)
+                                  for i in range(min(count, res.op_count))]}
 
     def forward_host_bf16(self, x) -> np.ndarray:
         """Host ids in, host logits out as bf16 bit patterns (uint16); needs storage bf16."""
@@ -430,6 +456,34 @@ def tp_unique_id() -> bytes:
     buf = C.create_string_buffer(128)
     check(lib().bfb_tp_unique_id(buf))
     return buf.raw
+
+
+class OpBenchmark(C.Structure):
+    _fields_ = [("name", C.c_char * 32), ("index", C.c_int32), ("mean_ms", C.c_double)]
+
+
+class BenchmarkResult(C.Structure):
+    _fields_ = [("warmup_iterations", C.c_int64), ("measured_iterations", C.c_int64), ("mean_ms", C.c_double),
+                ("samples_per_second", C.c_double), ("estimated_memory_bytes", C.c_uint64), ("op_count", C.c_int32)]
+
+
+class CheckpointLoadStats(C.Structure):
+    _fields_ = [("tensors", C.c_int64), ("file_bytes", C.c_uint64), ("read_bytes", C.c_uint64),
+                ("uploaded_bytes", C.c_uint64), ("seconds", C.c_double)]
+
+
+def checkpoint_index(path: str) -> list:
+    """Header pass over a BFCKPT1 file (no device): [(name, shape, data_offset, data_bytes), ...]."""
+    count = C.c_int32(0)
+    check(lib().bfb_checkpoint_index(path.encode(), -1, None, 0, None, None, None, None, C.byref(count)))
+    out = []
+    for i in range(count.value):
+        name = C.create_string_buffer(1024)
+        rank, dims = C.c_int32(0), (C.c_int64 * 8)()
+        off, size = C.c_uint64(0), C.c_uint64(0)
+        check(lib().bfb_checkpoint_index(path.encode(), i, name, 1024, C.byref(rank), dims, C.byref(off), C.byref(size), None))
+        out.append((name.value.decode(), tuple(dims[d] for d in range(rank.value)), off.value, size.value))
+    return out
 
 
 def set_shared_sm_mode(dynamic_tiles: bool, reserved_sms: int = 0):

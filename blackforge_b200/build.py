@@ -35,6 +35,7 @@ SOURCES = [
     "host/model.cpp",
     "host/tp.cpp",
     "host/widen.cpp",
+    "host/checkpoint.cpp",
 ]
 
 NVCC_FLAGS = [

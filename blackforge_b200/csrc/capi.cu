@@ -465,6 +465,44 @@ bfb_status bfb_model_load_checkpoint(bfb_model* model, const char* path) {
     });
 }
 
+bfb_status bfb_model_load_checkpoint_streaming(bfb_model* model, const char* path, uint64_t chunk_bytes,
+                                               bfb_checkpoint_load_stats* stats) {
+    return guarded([&] {
+        require(model != nullptr && path != nullptr, "model: null argument");
+        const bfb200::CheckpointLoadStats s = bfb200::loadCheckpoint(*model->model, path, static_cast<std::size_t>(chunk_bytes));
+        if (stats != nullptr) {
+            stats->tensors = static_cast<int64_t>(s.tensors);
+            stats->file_bytes = s.fileBytes;
+            stats->read_bytes = s.readBytes;
+            stats->uploaded_bytes = s.uploadedBytes;
+            stats->seconds = s.seconds;
+        }
+    });
+}
+
+bfb_status bfb_checkpoint_index(const char* path, int32_t index, char* name_buf, int32_t name_capacity, int32_t* rank,
+                                int64_t* dims8, uint64_t* data_offset, uint64_t* data_bytes, int32_t* count) {
+    return guarded([&] {
+        require(path != nullptr, "checkpoint_index: null path");
+        const std::vector<bfb200::CheckpointEntry> entries = bfb200::indexCheckpoint(path);
+        if (count != nullptr) *count = static_cast<int32_t>(entries.size());
+        if (index < 0) return;
+        require(static_cast<std::size_t>(index) < entries.size(), "checkpoint_index: no such entry");
+        const bfb200::CheckpointEntry& e = entries[static_cast<std::size_t>(index)];
+        if (name_buf != nullptr && name_capacity > 0) {
+            const std::size_t n = std::min<std::size_t>(e.name.size(), static_cast<std::size_t>(name_capacity) - 1);
+            std::memcpy(name_buf, e.name.data(), n);
+            name_buf[n] = '\0';
+        }
+        if (rank != nullptr) *rank = static_cast<int32_t>(e.shape.size());
+        if (dims8 != nullptr) {
+            for (std::size_t d = 0; d < e.shape.size() && d < 8; ++d) dims8[d] = static_cast<int64_t>(e.shape[d]);
+        }
+        if (data_offset != nullptr) *data_offset = e.dataOffset;
+        if (data_bytes != nullptr) *data_bytes = e.dataBytes;
+    });
+}
+
 bfb_status bfb_model_save_checkpoint(bfb_model* model, const char* path) {
     return guarded([&] {
         require(model != nullptr && path != nullptr, "model: null argument");
@@ -495,6 +533,40 @@ bfb_status bfb_model_forward(bfb_model* model, const float* d_input, const int64
         *out_rank = static_cast<int32_t>(result.rank());
         for (std::size_t i = 0; i < result.rank(); ++i) out_shape[i] = static_cast<int64_t>(result.dim(i));
         *d_out = result.releaseOwnership();
+    });
+}
+
+bfb_status bfb_model_benchmark(bfb_model* model, const float* d_input, const int64_t* shape, int32_t rank, int64_t warmup,
+                               int64_t measured, bfb_benchmark_result* out, bfb_op_benchmark* per_op,
+                               int32_t per_op_capacity, void* stream) {
+    return guarded([&] {
+        require(model != nullptr && shape != nullptr && out != nullptr, "model_benchmark: null argument");
+        require(rank >= 1 && rank <= 8, "model_benchmark: bad rank");
+        require(warmup >= 0 && measured >= 0, "model_benchmark: negative iteration count");
+        if (measured == 0) throw std::invalid_argument("runBenchmark: measuredIterations must be positive");
+        requireDevice();
+        std::vector<std::size_t> dims(shape, shape + rank);
+        bfb200::DeviceTensor borrowed = bfb200::DeviceTensor::borrow(const_cast<float*>(d_input), dims);
+        bfb200::BenchmarkResult r;
+        try {
+            r = model->model->benchmark(borrowed, static_cast<std::size_t>(warmup), static_cast<std::size_t>(measured), stream);
+        } catch (...) {
+            borrowed.releaseOwnership();
+            throw;
+        }
+        borrowed.releaseOwnership();
+        out->warmup_iterations = static_cast<int64_t>(r.warmupIterations);
+        out->measured_iterations = static_cast<int64_t>(r.measuredIterations);
+        out->mean_ms = r.meanMilliseconds;
+        out->samples_per_second = r.throughputSamplesPerSecond;
+        out->estimated_memory_bytes = r.estimatedMemoryBytes;
+        out->op_count = static_cast<int32_t>(r.perOperation.size());
+        for (std::size_t i = 0; per_op != nullptr && i < r.perOperation.size() && i < static_cast<std::size_t>(std::max(0, per_op_capacity)); ++i) {
+            std::memset(per_op[i].name, 0, sizeof(per_op[i].name));
+            std::strncpy(per_op[i].name, r.perOperation[i].operationName.c_str(), sizeof(per_op[i].name) - 1);
+            per_op[i].index = static_cast<int32_t>(r.perOperation[i].operationIndex);
+            per_op[i].mean_ms = r.perOperation[i].meanMilliseconds;
+        }
     });
 }
 

@@ -140,6 +140,22 @@ struct Parameter {  // include/blackforge/backend/cuda/model.hpp:15-19 (gradient
 };
 
 // include/blackforge/backend/cuda/model.hpp:57-113 (forward side).
+// include/blackforge/backend/cpu/benchmark.hpp:14-45
+struct OperationBenchmark {
+    std::string operationName;   // "linear", "attention", ... (ir::opKindName)
+    std::size_t operationIndex;  // position in the pipeline
+    double meanMilliseconds;
+};
+struct BenchmarkResult {
+    std::vector<std::size_t> inputShape;
+    std::size_t warmupIterations = 0;
+    std::size_t measuredIterations = 0;
+    double meanMilliseconds = 0.0;
+    double throughputSamplesPerSecond = 0.0;
+    std::size_t estimatedMemoryBytes = 0;   // elements x 4 bytes of input, operation outputs and parameters
+    std::vector<OperationBenchmark> perOperation;
+};
+
 class Model {
 public:
     Model(const std::vector<OpDesc>& ops, std::int64_t inputLastDim, unsigned int seed = 42,
@@ -193,6 +209,28 @@ public:
     void invalidatePreparedWeights();
     [[nodiscard]] std::optional<std::size_t> firstLayerEmbeddingVocabSize() const;
 
+    // include/blackforge/backend/cpu/benchmark.hpp:48-62 (runBenchmark), on the device and on the caller's input:
+    // `warmupIterations` discarded passes, then `measuredIterations` timed ones. Times are device times between CUDA
+    // events recorded on the forward's stream at the start of every pipeline operation: the per-operation figures
+    // the reference's header says its CUDA side lacks (benchmark.hpp:34-43), taken inside the full pass instead of
+    // operation by operation. An operation fused into its predecessor (positions into the embedding) reports 0.
+    // Throws std::invalid_argument for an empty pipeline or measuredIterations == 0, as the reference does.
+    BenchmarkResult benchmark(const DeviceTensor& input, std::size_t warmupIterations, std::size_t measuredIterations,
+                              void* stream = nullptr);
+
+    // A parameter seen as rows of the full (unsharded) tensor, and the rows this tensor-parallel rank holds a part
+    // of: all of them, except for row-sharded matrices and sharded vectors (one element per row).
+    struct RowView {
+        std::size_t rows = 0, rowElems = 0;
+        std::size_t firstNeededRow = 0, neededRows = 0;
+    };
+    RowView parameterRowView(std::size_t index) const;
+    // Asynchronous upload of `rowCount` full-width rows (host memory, pinned for a truly asynchronous copy) starting
+    // at row `firstRow` of the full tensor; this rank's columns are taken out of them where the parameter is
+    // column-sharded. Returns the bytes sent to the device.
+    std::size_t uploadParameterRows(std::size_t index, std::size_t firstRow, std::size_t rowCount, const float* hostRows,
+                                    void* stream);
+
     struct Impl;
 
 private:
@@ -200,9 +238,24 @@ private:
     std::string name_;
 };
 
-// include/blackforge/backend/cuda/checkpoint.hpp:24-27 — BFCKPT1 files.
+// include/blackforge/backend/cuda/checkpoint.hpp:24-27 — BFCKPT1 files. The loader streams: headers first, then
+// whole rows through pinned buffers while earlier rows upload; a tensor-parallel rank reads only the rows it holds
+// of row-sharded tensors. chunkBytes == 0 picks 4 MiB.
+struct CheckpointEntry {
+    std::string name;
+    std::vector<std::size_t> shape;
+    std::uint64_t dataOffset = 0, dataBytes = 0;
+};
+struct CheckpointLoadStats {
+    std::size_t tensors = 0;
+    std::uint64_t fileBytes = 0;      // fp32 payload of the file
+    std::uint64_t readBytes = 0;      // read from the file by this rank
+    std::uint64_t uploadedBytes = 0;  // sent to the device
+    double seconds = 0.0;
+};
+std::vector<CheckpointEntry> indexCheckpoint(const std::string& path);
 void saveCheckpoint(Model& model, const std::string& path);
-void loadCheckpoint(Model& model, const std::string& path);
+CheckpointLoadStats loadCheckpoint(Model& model, const std::string& path, std::size_t chunkBytes = 0);
 
 // include/blackforge/backend/cuda/executor.hpp:20-33 — weights regenerated from the seed on every run.
 class Executor {

@@ -151,6 +151,27 @@ struct Model::Impl {
     DevBuf status;    // device status word for bounded waits + id range counter
     // Tensor-parallel prompt passes run the layers over `tpChunks` groups of sequences, the all-reduce of one group on
     // `commStream` beside the next group's GEMMs, which leave `tpReserveSms` SMs to it.
+    // benchmark(): when set, the forward records a timing event on its stream before each pipeline operation it
+    // starts (an operation fused into its predecessor records none) and one after the last
+    struct OpMarks {
+        std::vector<cudaEvent_t> events;
+        std::vector<std::size_t> opIndex;   // pipeline position of the operation that starts at events[i]
+        std::size_t used = 0;
+        void mark(std::size_t op, cudaStream_t stream) {
+            if (used == events.size()) {
+                cudaEvent_t e = nullptr;
+                BFB_CUDA(cudaEventCreate(&e));
+                events.push_back(e);
+                opIndex.push_back(0);
+            }
+            opIndex[used] = op;
+            BFB_CUDA(cudaEventRecord(events[used++], stream));
+        }
+        ~OpMarks() {
+            for (cudaEvent_t e : events) cudaEventDestroy(e);
+        }
+    };
+    OpMarks* marks = nullptr;
     int tpChunks = 2;
     int tpReserveSms = 0;
     cudaStream_t commStream = nullptr;
@@ -488,6 +509,7 @@ DeviceTensor Model::Impl::forwardFp32(const DeviceTensor& input, bool trusted, b
     };
     for (std::size_t i = 0; i < layers.size(); ++i) {
         Layer& l = layers[i];
+        if (marks != nullptr) marks->mark(i, nullptr);
         switch (l.kind) {
             case BFB_OP_LINEAR: current = linear(current, params[l.p[0]].value, params[l.p[1]].value); break;
             case BFB_OP_SILU: current = silu(current); break;
@@ -517,6 +539,7 @@ DeviceTensor Model::Impl::forwardFp32(const DeviceTensor& input, bool trusted, b
         }
         roundStorage(current);
     }
+    if (marks != nullptr) marks->mark(layers.size(), nullptr);
     if (incremental) genPosition += input.rank() >= 2 ? input.dim(1) : 0;
     return current;
 }
@@ -723,6 +746,7 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
         Layer& l = layers[i];
         const std::size_t allTokens = tokensOf();
         std::size_t tokens = allTokens;
+        if (marks != nullptr) marks->mark(i, stream);
         switch (l.kind) {
             case BFB_OP_EMBEDDING: {
                 require(i == 0, "Model: embedding must be the first operation of the planned route");
@@ -964,6 +988,7 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
         result = DeviceTensor(shape);
         bfb::castScaled(x, S, result.data(), BFB_F32, static_cast<int64_t>(tokensOf() * feat), 1.0f, nullptr, stream);
     }
+    if (marks != nullptr) marks->mark(layers.size(), stream);
     checkStatus(stream, idsChecked, vocabForCheck);
     if (incremental) genPosition += shape.size() >= 2 ? shape[1] : 0;
     return result;
@@ -1041,6 +1066,86 @@ DeviceTensor Model::forwardIncremental(const DeviceTensor& newTokenIds, bool inp
     return impl_->forwardPlanned(newTokenIds, inputRangeTrusted, static_cast<cudaStream_t>(stream), nullptr, true);
 }
 
+namespace {
+const char* opKindName(int kind) {   // src/ir/operation.cpp:36-50
+    switch (kind) {
+        case BFB_OP_LINEAR: return "linear";
+        case BFB_OP_SILU: return "silu";
+        case BFB_OP_RELU: return "relu";
+        case BFB_OP_GELU: return "gelu";
+        case BFB_OP_RMSNORM: return "rmsnorm";
+        case BFB_OP_SOFTMAX: return "softmax";
+        case BFB_OP_EMBEDDING: return "embedding";
+        case BFB_OP_POSITIONAL_EMBEDDING: return "positional_embedding";
+        case BFB_OP_ATTENTION: return "attention";
+        case BFB_OP_FEEDFORWARD: return "feedforward";
+        case BFB_OP_BIDIRECTIONAL_ATTENTION: return "bidirectional_attention";
+        default: return "?";
+    }
+}
+}  // namespace
+
+BenchmarkResult Model::benchmark(const DeviceTensor& input, std::size_t warmupIterations, std::size_t measuredIterations,
+                                 void* stream) {
+    if (impl_->layers.empty()) throw std::invalid_argument("runBenchmark: the model '" + name_ + "' has no pipeline to run");
+    if (measuredIterations == 0) throw std::invalid_argument("runBenchmark: measuredIterations must be positive");
+    BenchmarkResult r;
+    r.inputShape = input.shape();
+    r.warmupIterations = warmupIterations;
+    r.measuredIterations = measuredIterations;
+    for (std::size_t i = 0; i < warmupIterations; ++i) (void)forward(input, false, stream);
+
+    const std::size_t nOps = impl_->layers.size();
+    std::vector<double> perOp(nOps, 0.0);
+    double total = 0.0;
+    Impl::OpMarks marks;
+    struct Unset {
+        Impl* impl;
+        ~Unset() { impl->marks = nullptr; }
+    } unset{impl_.get()};
+    std::size_t outElements = 0;
+    for (std::size_t it = 0; it < measuredIterations; ++it) {
+        marks.used = 0;
+        impl_->marks = &marks;
+        DeviceTensor out = forward(input, false, stream);
+        impl_->marks = nullptr;
+        outElements = out.elementCount();
+        BFB_CUDA(cudaEventSynchronize(marks.events[marks.used - 1]));
+        for (std::size_t m = 0; m + 1 < marks.used; ++m) {
+            float ms = 0.0f;
+            BFB_CUDA(cudaEventElapsedTime(&ms, marks.events[m], marks.events[m + 1]));
+            if (marks.opIndex[m] < nOps) perOp[marks.opIndex[m]] += static_cast<double>(ms);
+            total += static_cast<double>(ms);
+        }
+    }
+    const double n = static_cast<double>(measuredIterations);
+    r.meanMilliseconds = total / n;
+    const double batch = input.rank() >= 1 ? static_cast<double>(input.dim(0)) : 1.0;
+    r.throughputSamplesPerSecond = r.meanMilliseconds > 0.0 ? batch * 1000.0 / r.meanMilliseconds : 0.0;
+    for (std::size_t i = 0; i < nOps; ++i) {
+        r.perOperation.push_back(OperationBenchmark{opKindName(impl_->layers[i].kind), i, perOp[i] / n});
+    }
+    // the reference's estimate (elements x 4 bytes of the input, every operation's output and the parameters;
+    // src/backend/cpu/benchmark.cpp:117-137), with every parameter counted, not only those of `linear`
+    std::size_t elements = input.elementCount();
+    std::vector<std::size_t> shape = input.shape();
+    for (const Layer& l : impl_->layers) {
+        if (l.kind == BFB_OP_EMBEDDING) shape.push_back(l.outFeat);
+        else if (l.kind == BFB_OP_LINEAR && !shape.empty()) shape.back() = l.outFeat;
+        std::size_t count = 1;
+        for (std::size_t d : shape) count *= d;
+        elements += count;
+    }
+    for (const Parameter& p : impl_->params) {
+        std::size_t count = 1;
+        for (std::size_t d : p.fullShape) count *= d;
+        elements += count;
+    }
+    (void)outElements;
+    r.estimatedMemoryBytes = elements * sizeof(float);
+    return r;
+}
+
 void Model::resetGenerationState() { impl_->resetGeneration(); }
 std::size_t Model::generationPosition() const { return impl_->genPosition; }
 
@@ -1115,6 +1220,64 @@ void Model::releaseMasterWeights() {
     bfb::poolTrim();
 }
 
+// A parameter as rows of the full (unsharded) tensor: [rows, cols] for rank 2, one element per row for vectors (so
+// that a vector's slice is a row range), one row otherwise.
+Model::RowView Model::parameterRowView(std::size_t index) const {
+    require(index < impl_->params.size(), "Model: parameter index out of range");
+    const std::vector<std::size_t>& full = impl_->params[index].fullShape;
+    RowView v;
+    if (full.size() == 2) {
+        v.rows = full[0];
+        v.rowElems = full[1];
+    } else if (full.size() == 1) {
+        v.rows = full[0];
+        v.rowElems = 1;
+    } else {
+        v.rows = 1;
+        v.rowElems = 1;
+        for (std::size_t d : full) v.rowElems *= d;
+    }
+    v.firstNeededRow = 0;
+    v.neededRows = v.rows;
+    const Shard s = impl_->tpWorld > 1 ? impl_->meta[index].shard : Shard::None;
+    if (s == Shard::Rows || s == Shard::Vec) {
+        v.neededRows = v.rows / static_cast<std::size_t>(impl_->tpWorld);
+        v.firstNeededRow = static_cast<std::size_t>(impl_->tpRank) * v.neededRows;
+    }
+    return v;
+}
+
+std::size_t Model::uploadParameterRows(std::size_t index, std::size_t firstRow, std::size_t rowCount,
+                                       const float* hostRows, void* stream) {
+    impl_->allocateParams();
+    require(index < impl_->params.size(), "Model: parameter index out of range");
+    require(hostRows != nullptr, "Model: null parameter data");
+    Parameter& prm = impl_->params[index];
+    if (impl_->mastersReleased && prm.value.data() == nullptr) {
+        fail(BFB_UNSUPPORTED, "Model: the fp32 copy of '" + prm.name + "' was released; it can no longer be set");
+    }
+    const RowView v = parameterRowView(index);
+    if (firstRow < v.firstNeededRow || firstRow + rowCount > v.firstNeededRow + v.neededRows) {
+        fail(BFB_INVALID_ARGUMENT, "Model: rows outside this rank's part of '" + prm.name + "'");
+    }
+    const Shard s = impl_->tpWorld > 1 ? impl_->meta[index].shard : Shard::None;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    std::size_t bytes = 0;
+    if (s == Shard::Cols) {   // this rank's columns out of full rows
+        const std::size_t nLoc = v.rowElems / static_cast<std::size_t>(impl_->tpWorld);
+        bytes = rowCount * nLoc * sizeof(float);
+        BFB_CUDA(cudaMemcpy2DAsync(prm.value.data() + firstRow * nLoc, nLoc * sizeof(float),
+                                   hostRows + static_cast<std::size_t>(impl_->tpRank) * nLoc, v.rowElems * sizeof(float),
+                                   nLoc * sizeof(float), rowCount, cudaMemcpyHostToDevice, st));
+    } else {
+        bytes = rowCount * v.rowElems * sizeof(float);
+        BFB_CUDA(cudaMemcpyAsync(prm.value.data() + (firstRow - v.firstNeededRow) * v.rowElems, hostRows, bytes,
+                                 cudaMemcpyHostToDevice, st));
+    }
+    if (!impl_->mastersReleased) impl_->prepared = false;
+    return bytes;
+}
+
 void Model::setParameter(std::size_t index, const float* hostFullValues) { impl_->setParam(index, hostFullValues); }
 void Model::getParameter(std::size_t index, float* hostFullValues) { impl_->getParam(index, hostFullValues); }
 void Model::invalidatePreparedWeights() { impl_->prepared = false; }
@@ -1122,87 +1285,6 @@ void Model::invalidatePreparedWeights() { impl_->prepared = false; }
 std::optional<std::size_t> Model::firstLayerEmbeddingVocabSize() const {
     if (impl_->layers.empty() || impl_->layers.front().kind != BFB_OP_EMBEDDING) return std::nullopt;
     return impl_->layers.front().vocab;
-}
-
-// ---- checkpoints (BFCKPT1) --------------------------------------------------------------------------------
-
-namespace {
-constexpr char kMagic[8] = {'B', 'F', 'C', 'K', 'P', 'T', '1', '\0'};
-[[noreturn]] void ioFail(const std::string& text) { fail(BFB_IO_ERROR, text); }
-}  // namespace
-
-void saveCheckpoint(Model& model, const std::string& path) {
-    std::vector<Parameter*> params = model.parameters();
-    std::ofstream out(path, std::ios::binary | std::ios::trunc);
-    if (!out) ioFail("saveCheckpoint: cannot write '" + path + "'");
-    out.write(kMagic, sizeof(kMagic));
-    auto u32 = [&](std::uint32_t v) { out.write(reinterpret_cast<const char*>(&v), sizeof(v)); };
-    auto u64 = [&](std::uint64_t v) { out.write(reinterpret_cast<const char*>(&v), sizeof(v)); };
-    u32(static_cast<std::uint32_t>(params.size()));
-    std::vector<float> host;
-    for (std::size_t i = 0; i < params.size(); ++i) {
-        const Parameter& p = *params[i];
-        u32(static_cast<std::uint32_t>(p.name.size()));
-        out.write(p.name.data(), static_cast<std::streamsize>(p.name.size()));
-        u32(static_cast<std::uint32_t>(p.fullShape.size()));
-        std::size_t count = 1;
-        for (std::size_t d : p.fullShape) {
-            u64(static_cast<std::uint64_t>(d));
-            count *= d;
-        }
-        host.resize(count);
-        model.getParameter(i, host.data());
-        out.write(reinterpret_cast<const char*>(host.data()), static_cast<std::streamsize>(count * sizeof(float)));
-    }
-    if (!out) ioFail("saveCheckpoint: write to '" + path + "' failed");
-}
-
-void loadCheckpoint(Model& model, const std::string& path) {
-    std::ifstream in(path, std::ios::binary);
-    if (!in) ioFail("loadCheckpoint: cannot open '" + path + "'");
-    char magic[8];
-    in.read(magic, sizeof(magic));
-    if (!in || std::memcmp(magic, kMagic, sizeof(kMagic)) != 0) {
-        ioFail("loadCheckpoint: '" + path + "' is not a BlackForge checkpoint");
-    }
-    std::vector<Parameter*> params = model.parameters();
-    std::map<std::string, std::size_t> byName;
-    for (std::size_t i = 0; i < params.size(); ++i) byName[params[i]->name] = i;
-    auto u32 = [&]() {
-        std::uint32_t v = 0;
-        in.read(reinterpret_cast<char*>(&v), sizeof(v));
-        return v;
-    };
-    auto u64 = [&]() {
-        std::uint64_t v = 0;
-        in.read(reinterpret_cast<char*>(&v), sizeof(v));
-        return v;
-    };
-    std::uint32_t count = u32();
-    if (!in) ioFail("loadCheckpoint: '" + path + "' is truncated");
-    std::vector<float> data;
-    for (std::uint32_t i = 0; i < count; ++i) {
-        std::uint32_t nameLen = u32();
-        if (!in || nameLen > (1u << 20)) ioFail("loadCheckpoint: '" + path + "' is truncated or corrupt");
-        std::string name(nameLen, '\0');
-        in.read(name.data(), nameLen);
-        std::uint32_t rank = u32();
-        if (!in || rank > 8) ioFail("loadCheckpoint: '" + path + "' is truncated or corrupt");
-        std::vector<std::size_t> shape(rank);
-        std::size_t elements = 1;
-        for (std::uint32_t d = 0; d < rank; ++d) {
-            shape[d] = static_cast<std::size_t>(u64());
-            elements *= shape[d];
-        }
-        if (!in) ioFail("loadCheckpoint: '" + path + "' is truncated or corrupt");
-        auto it = byName.find(name);
-        if (it == byName.end()) ioFail("loadCheckpoint: the model has no parameter named '" + name + "'");
-        if (params[it->second]->fullShape != shape) ioFail("loadCheckpoint: shape mismatch for '" + name + "'");
-        data.resize(elements);
-        in.read(reinterpret_cast<char*>(data.data()), static_cast<std::streamsize>(elements * sizeof(float)));
-        if (!in) ioFail("loadCheckpoint: '" + path + "' is truncated or corrupt");
-        model.setParameter(it->second, data.data());
-    }
 }
 
 // ---- Executor -----------------------------------------------------------------------------------------------

@@ -6,6 +6,10 @@ run, on small cases.
     python -m blackforge_b200.kernel_bench attention --batch 16 --heads 16 --seq 2048
     python -m blackforge_b200.kernel_bench rmsnorm --rows 65536 --dim 2048
     python -m blackforge_b200.kernel_bench embed --batch 32 --seq 2048 --vocab 32000 --dim 2048
+
+and the checkpoint loader (host I/O + uploads, wall clock; the file is written first, so it comes from the page cache):
+
+    python -m blackforge_b200.kernel_bench checkpoint --layers 16 [--dim 2048 --hidden 5632 --vocab 32000] [--path FILE]
 """
 from __future__ import annotations
 
@@ -18,7 +22,11 @@ import numpy as np
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attention", "rmsnorm", "embed"])
+    ap.add_argument("kernel", choices=["gemm", "attention", "rmsnorm", "embed", "checkpoint"])
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--hidden", type=int, default=5632)
+    ap.add_argument("--chunk-mib", type=int, default=0, help="checkpoint: staging buffer size (0: the loader's default)")
+    ap.add_argument("--path", default="", help="checkpoint: where to write the file (default: a temporary directory)")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=2048)
     ap.add_argument("--k", type=int, default=2048)
@@ -47,6 +55,8 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("kernel_bench needs a CUDA device")
     lib = bfb.lib()
+    if args.kernel == "checkpoint":
+        return checkpoint_io(args, bfb)
     if args.dynamic_tiles or args.reserved_sms:
         bfb.set_shared_sm_mode(args.dynamic_tiles, args.reserved_sms)
     rng = np.random.default_rng(0)
@@ -130,6 +140,54 @@ def main():
     print(json.dumps({"kernel": args.kernel, "case": desc, "ms_median": ms, "ms_min": float(min(times)), "rate": rate,
                       "unit": unit, "iters": args.iters, "l2_flushed": flush is not None, "device_status": st}))
     return 0 if st == 0 else 1
+
+
+def checkpoint_io(args, bfb):
+    """Writes a BFCKPT1 file of a decoder of the given shape (weights drawn on the device), then times the streaming
+    loader into a fresh model, and the reference's way of loading (each tensor whole into pageable host memory, one
+    synchronous upload per tensor) beside it."""
+    import tempfile
+    import time
+
+    ops, vid = [], 0
+    for kind, kw in ([("embedding", dict(vocab=args.vocab, emb_dim=args.dim)), ("positional_embedding", dict(max_seq=args.seq))]
+                     + [("attention", dict(heads=args.dim // 128)), ("feedforward", dict(hidden=args.hidden))] * args.layers
+                     + [("linear", dict(linear_out=args.vocab))]):
+        ops.append(dict(kind=kind, input=vid, output=vid + 1, **kw))
+        vid += 1
+    src = bfb.Model(ops, random_init=False)
+    for i, _ in enumerate(src.param_names()):
+        src.fill_param_normal(i, 1000 + i, 0.02)
+    with tempfile.TemporaryDirectory() as tmp:
+        path = args.path or f"{tmp}/weights.bfckpt"
+        t0 = time.perf_counter()
+        src.save_checkpoint(path)
+        save_s = time.perf_counter() - t0
+        src.close()
+        index = bfb.checkpoint_index(path)
+        runs = []
+        for _ in range(max(1, args.iters // 5)):
+            dst = bfb.Model(ops, random_init=False)
+            runs.append(dst.load_checkpoint_streaming(path, args.chunk_mib << 20))
+            dst.close()
+        best = min(runs, key=lambda r: r["seconds"])
+        # the reference's order of work: read a tensor whole, upload it synchronously, next tensor
+        dst = bfb.Model(ops, random_init=False)
+        names = dst.param_names()
+        t0 = time.perf_counter()
+        with open(path, "rb") as f:
+            for name, shape, offset, size in index:
+                f.seek(offset)
+                dst.set_param(names.index(name), np.frombuffer(f.read(size), np.float32).reshape(shape))
+        whole_s = time.perf_counter() - t0
+        dst.close()
+    print(json.dumps({"kernel": "checkpoint_load", "case": {"layers": args.layers, "dim": args.dim, "hidden": args.hidden,
+                                                            "vocab": args.vocab, "tensors": len(index)},
+                      "file_gb": best["file_bytes"] / 1e9, "seconds": best["seconds"],
+                      "rate": best["file_bytes"] / 1e9 / best["seconds"], "unit": "GB/s",
+                      "whole_tensor_sync_seconds": whole_s, "whole_tensor_sync_rate": best["file_bytes"] / 1e9 / whole_s,
+                      "save_seconds": save_s, "file": "page cache (written just before)"}))
+    return 0
 
 
 if __name__ == "__main__":

@@ -324,6 +324,51 @@ bfb_status bfb_model_release_master_weights(bfb_model* model);
 bfb_status bfb_model_load_checkpoint(bfb_model* model, const char* path);
 bfb_status bfb_model_save_checkpoint(bfb_model* model, const char* path);
 
+/* cpu::runBenchmark (include/blackforge/backend/cpu/benchmark.hpp:14-62) on the device, on the caller's input:
+ * `warmup` discarded passes, `measured` timed ones (0 gives BFB_INVALID_ARGUMENT, as the reference throws). mean_ms is
+ * device time between CUDA events on the forward's stream; per_op[i] is the mean device time of pipeline operation
+ * i inside the full pass, the per-operation breakdown the reference's header says its CUDA side lacks
+ * (benchmark.hpp:34-43). An operation fused into its predecessor reports 0. estimated_memory_bytes is the
+ * reference's estimate: 4 bytes per element of the input, every operation's output and every parameter. At most
+ * per_op_capacity entries are written; op_count is the pipeline's length. */
+typedef struct bfb_op_benchmark {
+    char name[32];
+    int32_t index;
+    double mean_ms;
+} bfb_op_benchmark;
+typedef struct bfb_benchmark_result {
+    int64_t warmup_iterations;
+    int64_t measured_iterations;
+    double mean_ms;
+    double samples_per_second;
+    uint64_t estimated_memory_bytes;
+    int32_t op_count;
+} bfb_benchmark_result;
+bfb_status bfb_model_benchmark(bfb_model* model, const float* d_input, const int64_t* shape, int32_t rank, int64_t warmup,
+                               int64_t measured, bfb_benchmark_result* out, bfb_op_benchmark* per_op,
+                               int32_t per_op_capacity, void* stream);
+
+/* The same load with its figures. The reference (src/backend/cuda/checkpoint.cu:82-130) reads each tensor whole
+ * into a host vector and uploads it synchronously; this loader reads the headers first, checks every name and
+ * shape, then streams whole rows through a few pinned buffers of about chunk_bytes (0: 4 MiB), filled by up to four
+ * reader threads, while earlier rows upload, and a tensor-parallel rank reads only the rows it holds of row-sharded tensors (column-sharded ones are
+ * read in full rows and sliced by the copy). bfb_model_load_checkpoint is this call without the figures. */
+typedef struct bfb_checkpoint_load_stats {
+    int64_t tensors;
+    uint64_t file_bytes;     /* fp32 payload of the file */
+    uint64_t read_bytes;     /* read from the file by this rank */
+    uint64_t uploaded_bytes; /* sent to the device */
+    double seconds;
+} bfb_checkpoint_load_stats;
+bfb_status bfb_model_load_checkpoint_streaming(bfb_model* model, const char* path, uint64_t chunk_bytes,
+                                               bfb_checkpoint_load_stats* stats);
+
+/* Header pass over a BFCKPT1 file, no device needed: entry `index` (name copied into name_buf, up to 8 dims, the
+ * byte offset and size of its fp32 data) and the number of entries. index == -1 only counts. The whole file's
+ * extent is checked: a truncated or corrupt file gives BFB_IO_ERROR. */
+bfb_status bfb_checkpoint_index(const char* path, int32_t index, char* name_buf, int32_t name_capacity, int32_t* rank,
+                                int64_t* dims8, uint64_t* data_offset, uint64_t* data_bytes, int32_t* count);
+
 /* forward on device buffers: d_input f32 with `rank` dims (token ids as float for a model that starts
  * with an embedding). The result is acquired from the pool (f32); release it with bfb_pool_release
  * (bytes = 4 * product(out_shape)). input_range_trusted != 0 skips the id range check

@@ -120,3 +120,31 @@ def test_host_widening_is_exact(count, threads, offset):
     assert np.array_equal(dst.view(np.uint32), src.astype(np.uint32) << 16)
     assert backing[:offset].tolist() == [0.0] * offset and backing[-1] == 0.0
     assert bfb.lib().bfb_host_widen_bf16(src.ctypes.data, dst.ctypes.data, count, 0) == bfb.INVALID_ARGUMENT
+
+
+def test_checkpoint_index_reads_headers_only(bfb, tmp_path):
+    """The header pass of the streaming loader (no device): names, shapes and data offsets of a file written in the
+    reference's format, and the whole file's extent checked before anything would be loaded."""
+    rng = np.random.default_rng(5)
+    tensors = [("embedding1.table", rng.standard_normal((8, 6)).astype(np.float32)),
+               ("feedforward4.b1", rng.standard_normal(16).astype(np.float32)),
+               ("empty", np.zeros((0, 4), np.float32)),
+               ("linear5.weight", rng.standard_normal((6, 8)).astype(np.float32))]
+    path = str(tmp_path / "x.bfckpt")
+    O.save_checkpoint(path, tensors)
+    raw = open(path, "rb").read()
+    index = bfb.checkpoint_index(path)
+    assert [(n, s) for n, s, _, _ in index] == [(n, a.shape) for n, a in tensors]
+    for (name, shape, offset, size), (_, want) in zip(index, tensors):
+        assert size == want.nbytes
+        assert np.array_equal(np.frombuffer(raw[offset:offset + size], np.float32).reshape(shape), want)
+    for label, blob in (("magic", b"XXXXXXXX" + raw[8:]), ("cut_data", raw[:-3]), ("cut_header", raw[:14]),
+                        ("cut_mid", raw[:index[1][2] + 2])):
+        bad = str(tmp_path / label)
+        open(bad, "wb").write(blob)
+        with pytest.raises(bfb.RuntimeFailure) as e:
+            bfb.checkpoint_index(bad)
+        assert e.value.status == bfb.IO_ERROR, label
+    with pytest.raises(bfb.RuntimeFailure) as e:
+        bfb.checkpoint_index(str(tmp_path / "missing"))
+    assert e.value.status == bfb.IO_ERROR

@@ -51,6 +51,56 @@ def test_checkpoint_route_matches_reference(gpu, golden_c1_normal, tmp_path):
     assert open(back, "rb").read() == open(path, "rb").read()
 
 
+@pytest.mark.parametrize("precision", [None, {"storage": "bf16", "compute": "bf16"}])
+def test_benchmark_reports_every_operation(gpu, precision):
+    """The device counterpart of runBenchmark: device-timed passes and a per-operation breakdown whose parts add up to
+    the whole (they are intervals between events of one stream), with the reference's names, its memory estimate and
+    its refusal of zero measured iterations."""
+    cfg = dict(vocab=512, dim=256, layers=2, heads=2, hidden=512, max_seq=128)
+    ops = O.lm_ops(**cfg)
+    m = gpu.Model(ops, precision=precision)
+    ids = O.synth_token_ids(4, 128, cfg["vocab"], seed=9)
+    r = m.benchmark(ids, warmup=2, measured=4)
+    assert r["warmup"] == 2 and r["measured"] == 4
+    assert [n for n, _, _ in r["per_operation"]] == [op["kind"] for op in ops]
+    assert [i for _, i, _ in r["per_operation"]] == list(range(len(ops)))
+    times = [t for _, _, t in r["per_operation"]]
+    assert all(t >= 0.0 for t in times) and r["mean_ms"] > 0.0
+    assert abs(sum(times) - r["mean_ms"]) <= 1e-3 * r["mean_ms"] + 1e-6
+    assert times[2] > 0.0 and times[3] > 0.0 and times[-1] > 0.0          # attention, feedforward, logits
+    assert abs(r["samples_per_second"] - 4 * 1000.0 / r["mean_ms"]) <= 1e-6 * r["samples_per_second"]
+    elements = ids.size + sum(4 * 128 * (cfg["vocab"] if op["kind"] == "linear" else cfg["dim"]) for op in ops)
+    elements += sum(int(np.prod(shape)) for _, shape in O.param_layout(ops))
+    assert r["estimated_memory_bytes"] == 4 * elements
+    with pytest.raises(gpu.InvalidArgument):
+        m.benchmark(ids, warmup=0, measured=0)
+    # the marks are gone afterwards: a plain forward still works and agrees with itself
+    assert np.array_equal(m.forward_host(ids), m.forward_host(ids))
+
+
+@pytest.mark.parametrize("chunk", [64, 4096, 0])
+def test_streaming_load_in_small_pieces(gpu, tmp_path, chunk):
+    """The loader's pipeline (reader thread, three pinned buffers, asynchronous uploads) with pieces far smaller than
+    the tensors: every parameter arrives intact, and the figures add up."""
+    ops = O.lm_ops(vocab=96, dim=64, layers=2, heads=4, hidden=160, max_seq=24)
+    params = O.synth_params(ops, None, seed=3, sigma=0.05, bias_sigma=0.05)
+    path = str(tmp_path / "m.bfckpt")
+    O.save_checkpoint(path, [(n, params[n]) for n, _ in O.param_layout(ops)])
+    m = gpu.Model(ops, random_init=False)
+    stats = m.load_checkpoint_streaming(path, chunk)
+    names = m.param_names()
+    assert stats["tensors"] == len(names)
+    payload = sum(params[n].nbytes for n in names)
+    assert stats["file_bytes"] == stats["read_bytes"] == stats["uploaded_bytes"] == payload
+    for i, n in enumerate(names):
+        assert np.array_equal(m.get_param(i), params[n]), n
+    # loading twice, or into a model that has already run, replaces the weights
+    ids = O.synth_token_ids(2, 24, 96, seed=4)
+    first = m.forward_host(ids)
+    m.load_checkpoint_streaming(path, chunk)
+    assert np.array_equal(m.forward_host(ids), first)
+
+
 def test_checkpoint_errors(gpu, tmp_path):
     ops = O.lm_ops(vocab=8, dim=8, layers=1, heads=2, hidden=16, max_seq=6)
     m = gpu.Model(ops)

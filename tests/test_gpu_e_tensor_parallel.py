@@ -52,6 +52,16 @@ for groups, reserved in ((1, 0), (2, 0), (2, 32)):
     m.set_tensor_parallel_overlap(groups, reserved)
     again = m.forward_host(ids)
     assert np.array_equal(again, out), (groups, reserved, float(np.max(np.abs(again - out))))
+# the same weights from a checkpoint file: each rank streams its own slices (row ranges read directly, column
+# slices cut out of full rows by the upload)
+ckpt = os.path.join(work, f"weights_{rank}.bfckpt")
+O.save_checkpoint(ckpt, [(n, params[n]) for n, _ in O.param_layout(ops)])
+mc = bfb.Model(ops, precision={"storage": "fp32", "compute": "bf16"}, random_init=False)
+mc.set_tensor_parallel(rank, world)
+stats = mc.load_checkpoint_streaming(ckpt, 8192)
+assert stats["read_bytes"] < stats["file_bytes"] and stats["uploaded_bytes"] < stats["read_bytes"], stats
+assert np.array_equal(mc.forward_host(ids), out)
+mc.close()
 # bf16 residual stream (rmsnorm folded into the GEMMs, statistics per group)
 m16 = bfb.Model(ops, precision={"storage": "bf16", "compute": "bf16"}, random_init=False)
 m16.set_tensor_parallel(rank, world)
