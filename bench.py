@@ -269,25 +269,29 @@ def run_decode(args, bfb, launch, torch, model, cfg, batch, ids, precision, labe
     prompt = bfb.DeviceBuffer.from_numpy(np.ascontiguousarray(ids[:, :context]))
     step_ids = [bfb.DeviceBuffer.from_numpy(np.ascontiguousarray(ids[:, context + i:context + i + 1]))
                 for i in range(max(args.warmup, 1) + args.steps)]
-    model.reset_generation()
-    out, _ = model.forward_incremental_device(prompt.ptr, (batch, context), trusted=True)
-    out.free()
-    sampler = ClockSampler(local) if rank == 0 else None
-    for i in range(max(args.warmup, 1)):
-        out, _ = model.forward_incremental_device(step_ids[i].ptr, (batch, 1), trusted=True)
+    def prime():
+        model.reset_generation()
+        out, _ = model.forward_incremental_device(prompt.ptr, (batch, context), trusted=True)
         out.free()
-    torch.cuda.synchronize()
-    bfb.lib().bfb_profile_reset()
-    bfb.lib().bfb_profile_enable(1)
+        for i in range(max(args.warmup, 1)):
+            out, _ = model.forward_incremental_device(step_ids[i].ptr, (batch, 1), trusted=True)
+            out.free()
+        torch.cuda.synchronize()
+
+    def steps():
+        for i in range(args.steps):
+            out, _ = model.forward_incremental_device(step_ids[max(args.warmup, 1) + i].ptr, (batch, 1), trusted=True)
+            out.free()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    prime()
     bfb.lib().bfb_launch_count(1)
     launch.barrier()
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     wall_begin = time.time()
     start.record()
-    for i in range(args.steps):
-        out, _ = model.forward_incremental_device(step_ids[max(args.warmup, 1) + i].ptr, (batch, 1), trusted=True)
-        out.free()
+    steps()
     stop.record()
     torch.cuda.synchronize()
     wall_end = time.time()
@@ -295,12 +299,20 @@ def run_decode(args, bfb, launch, torch, model, cfg, batch, ids, precision, labe
     elapsed_ms = launch.max_over_ranks(start.elapsed_time(stop), dev if world > 1 else None)
     clocks = sampler.stop(wall_begin, wall_end) if sampler else None
     launches = bfb.lib().bfb_launch_count(0)
+    # per-kernel times from a second pass over the same positions: the events around every launch would otherwise sit
+    # between the kernels of the timed steps (a step is some 180 short launches) and keep them from overlapping
+    prime()
+    bfb.lib().bfb_profile_reset()
+    bfb.lib().bfb_profile_enable(1)
+    steps()
+    torch.cuda.synchronize()
     bfb.lib().bfb_profile_enable(0)
     kernels = {}
     for name, kind in (("gemm_tcgen05", 0), ("attention_tcgen05", 1), ("rmsnorm", 2), ("embed_pos", 3), ("cast", 4)):
         ms, n, work = profile_read(bfb, kind)
         if n:
-            kernels[name] = {"ms_total": ms, "launches": n, "share_of_step": ms / elapsed_ms}
+            kernels[name] = {"ms_total": ms, "launches": n, "ms_per_step": ms / args.steps,
+                             "measured": "separate pass with events around each launch"}
     if world > 1:
         launch.barrier()
         torch.distributed.destroy_process_group()

@@ -14,6 +14,7 @@
 
 #include "common.cuh"
 #include "kernels.hpp"
+#include "ptx_sm100.cuh"
 #include "pool.hpp"
 
 namespace bfb {
@@ -54,6 +55,8 @@ struct DecodeParams {
 
 __global__ void __launch_bounds__(kDecodeThreads, 6)
 attentionDecodeKernel(DecodeParams p) {
+    if (threadIdx.x == 0) pdl_launch_dependents();
+    pdl_wait();   // the query and the newest keys and values come from the kernels before
     __shared__ float merge[kDecodeWarps][kPartialFloats];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -175,6 +178,8 @@ attentionDecodeKernel(DecodeParams p) {
 __global__ void attentionDecodeMergeKernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
                                            float* __restrict__ mOut, float* __restrict__ lOut, int pairs, int splits,
                                            int numHeads, int64_t ldO) {
+    if (threadIdx.x == 0) pdl_launch_dependents();
+    pdl_wait();   // the partial results come from the kernel before
     const int lane = threadIdx.x & 31;
     const int bh = static_cast<int>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (bh >= pairs) return;
@@ -245,12 +250,12 @@ void attentionDecode(const AttentionArgs& a, cudaStream_t stream) {
     try {
         // the work figure of this kernel is the bytes of K and V it streams; the FLOP figure keeps the shared counter's unit
         ProfileScope prof(kProfAttnTc, stream, 4.0 * kDecodeDim * static_cast<double>(a.totalLen) * pairs);
-        attentionDecodeKernel<<<static_cast<unsigned>(pairs * splits), kDecodeThreads, 0, stream>>>(p);
+        launchDependent(attentionDecodeKernel, dim3(static_cast<unsigned>(pairs * splits)), dim3(kDecodeThreads), 0, stream, p);
         BFB_LAUNCH_CHECK();
         noteLaunch();
         if (splits > 1) {
-            attentionDecodeMergeKernel<<<(pairs + 7) / 8, 256, 0, stream>>>(p.partial, p.out, p.mOut, p.lOut, pairs, splits,
-                                                                            p.numHeads, p.ldO);
+            launchDependent(attentionDecodeMergeKernel, dim3(static_cast<unsigned>((pairs + 7) / 8)), dim3(256), 0, stream,
+                            p.partial, p.out, p.mOut, p.lOut, pairs, splits, p.numHeads, p.ldO);
             BFB_LAUNCH_CHECK();
             noteLaunch();
         }

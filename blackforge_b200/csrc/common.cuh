@@ -78,6 +78,26 @@ inline size_t dtypeBytes(int32_t dtype) {
     }
 }
 
+// Launch with programmatic stream serialisation: the kernel may begin (up to its griddepcontrol.wait) before the
+// previous kernel on `stream` has finished. Only for kernels that call pdl_wait() before they touch global memory
+// the previous kernel writes or reads. For chains of short kernels (a generation step), where launch latency and
+// each kernel's prologue are a large part of the time.
+template <typename... KArgs, typename... Args>
+inline void launchDependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smemBytes, cudaStream_t stream,
+                            Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    BFB_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
+
 // Number of SMs of the current device (cached per device).
 int smCount();
 // SMs the persistent kernels (tcgen05 GEMMs, flash attention) size their grids for: all of them, minus the ones a

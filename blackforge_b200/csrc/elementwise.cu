@@ -9,6 +9,7 @@
 
 #include "common.cuh"
 #include "kernels.hpp"
+#include "ptx_sm100.cuh"
 
 namespace bfb {
 
@@ -720,6 +721,8 @@ template <typename V>
 __global__ void appendKvKernel(const V* __restrict__ src, int64_t ldV, int64_t kOffV, int64_t vOffV, V* __restrict__ kCache,
                                V* __restrict__ vCache, int64_t batch, int64_t newLen, int64_t widthV, int64_t capRows,
                                int64_t oldLen) {
+    if (threadIdx.x == 0) pdl_launch_dependents();
+    pdl_wait();   // the new keys and values come from the kernel before; the caches may still be read by it
     const int64_t total = batch * newLen * widthV * 2;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -748,10 +751,9 @@ void appendKv(const void* src, int dtype, int64_t ld, int64_t kOffset, int64_t v
     const int64_t total = batch * newLen * (width / per) * 2;
     const int grid = static_cast<int>(std::min<int64_t>((total + kThreads - 1) / kThreads, static_cast<int64_t>(smCount()) * 8));
     if (vec) {
-        appendKvKernel<uint4><<<grid, kThreads, 0, stream>>>(static_cast<const uint4*>(src), ld / per, kOffset / per,
-                                                             vOffset / per, static_cast<uint4*>(kCache),
-                                                             static_cast<uint4*>(vCache), batch, newLen, width / per,
-                                                             capRows, oldLen);
+        launchDependent(appendKvKernel<uint4>, dim3(static_cast<unsigned>(grid)), dim3(kThreads), 0, stream,
+                        static_cast<const uint4*>(src), ld / per, kOffset / per, vOffset / per, static_cast<uint4*>(kCache),
+                        static_cast<uint4*>(vCache), batch, newLen, width / per, capRows, oldLen);
     } else if (dtype == BFB_F32) {
         appendKvKernel<float><<<grid, kThreads, 0, stream>>>(static_cast<const float*>(src), ld, kOffset, vOffset,
                                                              static_cast<float*>(kCache), static_cast<float*>(vCache),

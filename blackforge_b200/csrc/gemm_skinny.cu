@@ -63,6 +63,7 @@ gemmSkinnyKernel(const __grid_constant__ CUtensorMap tmapW, const __grid_constan
     const uint32_t tmemCols = mPad < 32 ? 32u : static_cast<uint32_t>(mPad);
 
     if (threadIdx.x == 0) {
+        pdl_launch_dependents();   // the finish kernel may get ready; it waits for this grid before it reads
         for (int s = 0; s < stages; ++s) {
             mbar_init(&fullBar[s], 1);
             mbar_init(&emptyBar[s], 1);
@@ -84,7 +85,24 @@ gemmSkinnyKernel(const __grid_constant__ CUtensorMap tmapW, const __grid_constan
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        for (int kb = kbBegin, it = 0; kb < kbEnd; ++kb, ++it) {
+        // The weights do not change during a pass, so their tiles of the first ring lap are requested while the
+        // kernel before this one may still be running; the activation tiles (its output) follow once it is done.
+        // Everything this kernel writes depends on those, so it also writes only after that.
+        const int early = min(kbEnd - kbBegin, stages);
+        if (lane == 0) {
+            for (int it = 0; it < early; ++it) {
+                mbar_arrive_expect_tx(&fullBar[it], static_cast<uint32_t>(stageBytes));
+                tma_load_2d(smem + it * stageBytes, &tmapW, &fullBar[it], (kbBegin + it) * kBlockK, tile * kTileN);
+            }
+        }
+        pdl_wait();
+        if (lane == 0) {
+            for (int it = 0; it < early; ++it) {
+                tma_load_2d(smem + it * stageBytes + kWBytes, &tmapA, &fullBar[it], (kbBegin + it) * kBlockK, 0);
+            }
+        }
+        __syncwarp();
+        for (int kb = kbBegin + early, it = early; kb < kbEnd; ++kb, ++it) {
             const int s = it % stages;
             const uint32_t use = static_cast<uint32_t>(it / stages);
             if (!warp_all(mbar_wait(&emptyBar[s], (use & 1u) ^ 1u, abortFlag, status, kDevTimeoutStageEmpty))) break;
@@ -186,6 +204,8 @@ __device__ __forceinline__ float siluSkinny(float x) { return __fdividef(x, 1.0f
 template <typename TC>
 __global__ void __launch_bounds__(256)
 skinnyFinishKernel(FinishParams p, int m, int n, int parts) {
+    if (threadIdx.x == 0) pdl_launch_dependents();
+    pdl_wait();   // the partial products come from the kernel before
     const int lane = threadIdx.x & 31;
     const int unit = static_cast<int>(blockIdx.x) * 8 + (threadIdx.x >> 5);
     if (unit >= m * parts) return;
@@ -297,9 +317,10 @@ void launchSkinny(const GemmArgs& g, const SkinnyPlan& p, float* ws, cudaStream_
     const int smemBytes = p.stages * skinnyStageBytes(p.mPad) + 1024 + 256;
     auto kernel = gemmSkinnyKernel<kElemBytes>;
     BFB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smemBytes));
-    kernel<<<static_cast<unsigned>(p.tilesN * p.splits), kThreadsS, smemBytes, stream>>>(
-        *reinterpret_cast<CUtensorMap*>(tw.bytes), *reinterpret_cast<CUtensorMap*>(ta.bytes), ws, static_cast<int>(g.m),
-        static_cast<int>(g.n), p.mPad, p.tilesN, p.numK, p.blocksPerSplit, p.stages, g.dStatus);
+    launchDependent(kernel, dim3(static_cast<unsigned>(p.tilesN * p.splits)), dim3(kThreadsS), static_cast<size_t>(smemBytes),
+                    stream, *reinterpret_cast<CUtensorMap*>(tw.bytes), *reinterpret_cast<CUtensorMap*>(ta.bytes), ws,
+                    static_cast<int>(g.m), static_cast<int>(g.n), p.mPad, p.tilesN, p.numK, p.blocksPerSplit, p.stages,
+                    g.dStatus);
     BFB_LAUNCH_CHECK();
     noteLaunch();
 }
@@ -335,8 +356,13 @@ void gemmSkinny(const GemmArgs& g, cudaStream_t stream) {
         const int parts = static_cast<int>((g.n + 127) / 128);
         const int units = static_cast<int>(g.m) * parts;
         const int grid = (units + 7) / 8;
-        if (g.cDtype == BFB_F32) skinnyFinishKernel<float><<<grid, 256, 0, stream>>>(f, static_cast<int>(g.m), static_cast<int>(g.n), parts);
-        else skinnyFinishKernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(f, static_cast<int>(g.m), static_cast<int>(g.n), parts);
+        if (g.cDtype == BFB_F32) {
+            launchDependent(skinnyFinishKernel<float>, dim3(grid), dim3(256), 0, stream, f, static_cast<int>(g.m),
+                            static_cast<int>(g.n), parts);
+        } else {
+            launchDependent(skinnyFinishKernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, f, static_cast<int>(g.m),
+                            static_cast<int>(g.n), parts);
+        }
         BFB_LAUNCH_CHECK();
         noteLaunch();
     } catch (...) {

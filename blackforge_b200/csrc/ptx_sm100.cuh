@@ -228,6 +228,14 @@ __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- programmatic dependent launch --------------------------------------------------------------
+// A kernel launched with launchDependent() (common.cuh) may start while the kernel before it on the stream is still
+// running. pdl_wait() returns once that kernel has completed and its writes are visible: nothing the predecessor
+// wrote (or still reads) may be touched before it. pdl_launch_dependents() lets the NEXT kernel on the stream start
+// its own prologue early. Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- CTA pairs (cluster of two CTAs driving one tcgen05.mma.cta_group::2) ------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
