@@ -24,7 +24,9 @@ namespace {
 constexpr int kDecodeDim = 128;
 constexpr int kDecodeWarps = 8;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
+constexpr int kDecodeGroups = kDecodeWarps * 2;   // half-warps: 16 lanes x 8 dims cover one key row
 constexpr int kKeysInFlight = 4;
+constexpr int kDecodeCtasPerSm = 4;
 constexpr int kPartialFloats = kDecodeDim + 2;   // m, l, acc[128]
 
 __device__ __forceinline__ float ex2Decode(float x) {
@@ -33,11 +35,14 @@ __device__ __forceinline__ float ex2Decode(float x) {
     return y;
 }
 
-__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {   // the query row
-    const uint2 raw = *reinterpret_cast<const uint2*>(p);
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
 }
 
 struct DecodeParams {
@@ -53,98 +58,104 @@ struct DecodeParams {
     float scaleLog2;
 };
 
-__global__ void __launch_bounds__(kDecodeThreads, 6)
+__global__ void __launch_bounds__(kDecodeThreads, kDecodeCtasPerSm)
 attentionDecodeKernel(DecodeParams p) {
     if (threadIdx.x == 0) pdl_launch_dependents();
     pdl_wait();   // the query and the newest keys and values come from the kernels before
-    __shared__ float merge[kDecodeWarps][kPartialFloats];
+    __shared__ float merge[kDecodeGroups][kPartialFloats];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
+    const int sub = lane & 15;                       // this lane's 8 dims: sub * 8 ...
+    const int group = warp * 2 + (lane >> 4);        // the half-warp, which has its own keys and softmax state
     const int bh = static_cast<int>(blockIdx.x) / p.splits;
     const int split = static_cast<int>(blockIdx.x) - bh * p.splits;
     const int b = bh / p.numHeads, h = bh - b * p.numHeads;
-    // this CTA's keys: a contiguous range, multiples of the warp count so the ranges differ by at most 8 keys
-    const int perSplit = ((p.totalLen + p.splits - 1) / p.splits + kDecodeWarps - 1) / kDecodeWarps * kDecodeWarps;
+    // this CTA's keys: a contiguous range, multiples of the group count so the ranges differ by at most 16 keys
+    const int perSplit = ((p.totalLen + p.splits - 1) / p.splits + kDecodeGroups - 1) / kDecodeGroups * kDecodeGroups;
     const int k0 = split * perSplit;
     const int k1 = min(p.totalLen, k0 + perSplit);
 
-    float q[4];
-    load4(p.q + static_cast<int64_t>(b) * p.ldQ + h * kDecodeDim + lane * 4, q);
+    float q[8];
+    unpack8(*reinterpret_cast<const uint4*>(p.q + static_cast<int64_t>(b) * p.ldQ + h * kDecodeDim + sub * 8), q);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) q[i] *= p.scaleLog2;
+    for (int i = 0; i < 8; ++i) q[i] *= p.scaleLog2;
 
-    const __nv_bfloat16* kBase = p.k + (static_cast<int64_t>(b) * p.kvBatchRows) * p.ldK + h * kDecodeDim + lane * 4;
-    const __nv_bfloat16* vBase = p.v + (static_cast<int64_t>(b) * p.kvBatchRows) * p.ldV + h * kDecodeDim + lane * 4;
+    const __nv_bfloat16* kBase = p.k + (static_cast<int64_t>(b) * p.kvBatchRows) * p.ldK + h * kDecodeDim + sub * 8;
+    const __nv_bfloat16* vBase = p.v + (static_cast<int64_t>(b) * p.kvBatchRows) * p.ldV + h * kDecodeDim + sub * 8;
     float m = -INFINITY, l = 0.0f;
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
 
-    // Keys of this warp: k0 + warp, + 8, + 16, ... in batches of kKeysInFlight whose rows are requested together
-    // and whose shuffle reductions run side by side. Latency is hidden by occupancy: the kernel needs 40 registers,
-    // so 48 warps fit on an SM, and the host asks for enough key splits to have that many.
-    for (int j0 = k0 + warp; j0 < k1; j0 += kDecodeWarps * kKeysInFlight) {
-        uint2 kr[kKeysInFlight], vr[kKeysInFlight];
+    // Keys of this half-warp: k0 + group, + 16, + 32, ... in batches of kKeysInFlight whose rows are requested
+    // together (16 bytes per lane and row) and whose shuffle reductions run side by side. A warp instruction thus
+    // serves two keys, which matters: with one key per warp the kernel was bound by instruction issue (two thirds of
+    // the issue slots busy at 56 % of the DRAM rate), not by memory. The loop trip count is the same for both halves
+    // of a warp (keys past the end re-read the last one and count for nothing), so the shuffles stay convergent.
+    for (int j0 = k0 + group; j0 - (lane >> 4) < k1; j0 += kDecodeGroups * kKeysInFlight) {
+        uint4 kr[kKeysInFlight], vr[kKeysInFlight];
 #pragma unroll
         for (int u = 0; u < kKeysInFlight; ++u) {
-            const int j = min(j0 + u * kDecodeWarps, k1 - 1);   // a key past the end re-reads the last one, unused
-            kr[u] = *reinterpret_cast<const uint2*>(kBase + static_cast<int64_t>(j) * p.ldK);
-            vr[u] = *reinterpret_cast<const uint2*>(vBase + static_cast<int64_t>(j) * p.ldV);
+            const int j = max(k0, min(j0 + u * kDecodeGroups, k1 - 1));
+            kr[u] = *reinterpret_cast<const uint4*>(kBase + static_cast<int64_t>(j) * p.ldK);
+            vr[u] = *reinterpret_cast<const uint4*>(vBase + static_cast<int64_t>(j) * p.ldV);
         }
         float s[kKeysInFlight];
 #pragma unroll
         for (int u = 0; u < kKeysInFlight; ++u) {
-            const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr[u].x));
-            const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr[u].y));
-            s[u] = fmaf(q[3], c.y, fmaf(q[2], c.x, fmaf(q[1], a.y, q[0] * a.x)));
+            float kf[8];
+            unpack8(kr[u], kf);
+            float d = q[0] * kf[0];
+#pragma unroll
+            for (int i = 1; i < 8; ++i) d = fmaf(q[i], kf[i], d);
+            s[u] = d;
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
+        for (int o = 8; o > 0; o >>= 1) {
 #pragma unroll
             for (int u = 0; u < kKeysInFlight; ++u) s[u] += __shfl_xor_sync(0xFFFFFFFFu, s[u], o);
         }
-        // the batch's maximum first: one rescale per batch instead of one per key
+        // the batch's maximum first: one rescale per batch instead of one per key (branch-free: the two halves of
+        // the warp decide differently)
         float mNew = m;
 #pragma unroll
         for (int u = 0; u < kKeysInFlight; ++u) {
-            if (j0 + u * kDecodeWarps < k1) mNew = fmaxf(mNew, s[u]);
+            if (j0 + u * kDecodeGroups < k1) mNew = fmaxf(mNew, s[u]);
         }
-        if (mNew > m) {   // the same decision in every lane: the sums are complete everywhere
-            const float alpha = ex2Decode(m - mNew);
-            l *= alpha;
+        const float alpha = mNew == -INFINITY ? 1.0f : ex2Decode(m - mNew);
+        l *= alpha;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[i] *= alpha;
-            m = mNew;
-        }
+        for (int i = 0; i < 8; ++i) acc[i] *= alpha;
+        m = mNew;
 #pragma unroll
         for (int u = 0; u < kKeysInFlight; ++u) {
-            const float pr = (j0 + u * kDecodeWarps < k1) ? ex2Decode(s[u] - m) : 0.0f;
+            const float pr = (j0 + u * kDecodeGroups < k1) ? ex2Decode(s[u] - m) : 0.0f;
             l += pr;
-            const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr[u].x));
-            const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr[u].y));
-            acc[0] = fmaf(pr, a.x, acc[0]);
-            acc[1] = fmaf(pr, a.y, acc[1]);
-            acc[2] = fmaf(pr, c.x, acc[2]);
-            acc[3] = fmaf(pr, c.y, acc[3]);
+            float vf[8];
+            unpack8(vr[u], vf);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(pr, vf[i], acc[i]);
         }
     }
 
-    // merge the 8 warps: common maximum, rescaled sums
-    if (lane == 0) {
-        merge[warp][0] = m;
-        merge[warp][1] = l;
+    // merge the 16 half-warps: common maximum, rescaled sums
+    if (sub == 0) {
+        merge[group][0] = m;
+        merge[group][1] = l;
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) merge[warp][2 + lane * 4 + i] = acc[i];
+    for (int i = 0; i < 8; ++i) merge[group][2 + sub * 8 + i] = acc[i];
     __syncthreads();
     if (warp != 0) return;
     float mAll = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kDecodeWarps; ++w) mAll = fmaxf(mAll, merge[w][0]);
+    for (int w = 0; w < kDecodeGroups; ++w) mAll = fmaxf(mAll, merge[w][0]);
     float lAll = 0.0f;
     float total[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-    for (int w = 0; w < kDecodeWarps; ++w) {
+    for (int w = 0; w < kDecodeGroups; ++w) {
         const float mw = merge[w][0];
-        const float f = mw == -INFINITY ? 0.0f : ex2Decode(mw - mAll);   // a warp without keys contributes nothing
+        const float f = mw == -INFINITY ? 0.0f : ex2Decode(mw - mAll);   // a half-warp without keys contributes nothing
         lAll = fmaf(merge[w][1], f, lAll);
 #pragma unroll
         for (int i = 0; i < 4; ++i) total[i] = fmaf(merge[w][2 + lane * 4 + i], f, total[i]);
@@ -214,9 +225,9 @@ __global__ void attentionDecodeMergeKernel(const float* __restrict__ partial, __
 
 bool attentionDecodeEligible(const AttentionArgs& a) {
     if (a.dtype != BFB_BF16 || a.headDim != kDecodeDim || a.newLen != 1 || a.totalLen < 1) return false;
-    if (a.ldQ % 4 || a.ldK % 4 || a.ldV % 4 || a.ldO % 4) return false;
-    auto aligned8 = [](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 8 == 0; };
-    if (!aligned8(a.q) || !aligned8(a.k) || !aligned8(a.v) || !aligned8(a.out)) return false;
+    if (a.ldQ % 8 || a.ldK % 8 || a.ldV % 8 || a.ldO % 4) return false;   // 16-byte loads of q, k, v; 8-byte stores
+    auto aligned = [](const void* ptr, uintptr_t to) { return reinterpret_cast<uintptr_t>(ptr) % to == 0; };
+    if (!aligned(a.q, 16) || !aligned(a.k, 16) || !aligned(a.v, 16) || !aligned(a.out, 8)) return false;
     // the one query sees every key whether or not the mask is on: old_len + 1 == total_len
     if (a.causal && a.oldLen + 1 != a.totalLen) return false;
     return a.batch * a.numHeads <= 0x7FFFFF && a.totalLen <= 0x3FFFFFFF;
@@ -225,9 +236,9 @@ bool attentionDecodeEligible(const AttentionArgs& a) {
 void attentionDecode(const AttentionArgs& a, cudaStream_t stream) {
     require(attentionDecodeEligible(a), "attention: the one-query kernel needs new_len 1, head_dim 128 and bf16 data");
     const int pairs = static_cast<int>(a.batch * a.numHeads);
-    // Six CTAs (48 warps) fit on an SM. The keys are split until the grid is several times that, so that the last,
+    // Four CTAs (32 warps, 64 registers a thread) fit on an SM. The keys are split until the grid is several times that, so that the last,
     // partly filled round of CTAs costs little; a split is worth at least 128 keys.
-    const int wanted = (smCount() * 6 * 8 + pairs - 1) / pairs;
+    const int wanted = (smCount() * kDecodeCtasPerSm * 8 + pairs - 1) / pairs;
     const int splits = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(std::min(wanted, 32), a.totalLen / 128)));
     DecodeParams p;
     p.q = static_cast<const __nv_bfloat16*>(a.q);

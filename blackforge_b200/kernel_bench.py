@@ -44,6 +44,8 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--decode-context", type=int, default=0,
+                    help="attention: one new query per sequence against this many cached keys (a generation step)")
     ap.add_argument("--dynamic-tiles", action="store_true",
                     help="gemm: tiles drawn from a device counter (the mode for GEMMs that share the SMs)")
     ap.add_argument("--reserved-sms", type=int, default=0, help="size the persistent grids for this many fewer SMs")
@@ -88,6 +90,18 @@ def main():
         work, unit = 2.0 * args.m * args.n * args.k, "TFLOP/s"
         desc = {"m": args.m, "n": args.n, "k": args.k, "operands": args.dtype, "c": args.cdtype, "epilogue": args.epilogue,
                 "b_layout": args.layout}
+    elif args.kernel == "attention" and args.decode_context > 0:
+        dim, ctx = args.heads * 128, args.decode_context
+        q = rand_dev(args.batch * dim, bfb.BF16)
+        k, v = (rand_dev(args.batch * ctx * dim, bfb.BF16) for _ in range(2))
+        out = bfb.DeviceBuffer(args.batch * dim * 2)
+
+        def run():
+            bfb.check(lib.bfb_attention_fwd(q.ptr, k.ptr, v.ptr, out.ptr, None, None, bfb.BF16, args.batch, 1, ctx,
+                                            args.heads, 128, dim, dim, dim, dim, float(128 ** -0.5), ctx - 1, 1,
+                                            status.ptr, None))
+        work, unit = float(2 * args.batch * ctx * dim * 2), "GB/s"
+        desc = {"batch": args.batch, "heads": args.heads, "context": ctx, "head_dim": 128, "bytes": "keys + values, bf16"}
     elif args.kernel == "attention":
         dim = args.heads * 128
         q, k, v = (rand_dev(args.batch * args.seq * dim, bfb.BF16) for _ in range(3))
