@@ -1103,13 +1103,11 @@ BenchmarkResult Model::benchmark(const DeviceTensor& input, std::size_t warmupIt
         Impl* impl;
         ~Unset() { impl->marks = nullptr; }
     } unset{impl_.get()};
-    std::size_t outElements = 0;
     for (std::size_t it = 0; it < measuredIterations; ++it) {
         marks.used = 0;
         impl_->marks = &marks;
         DeviceTensor out = forward(input, false, stream);
         impl_->marks = nullptr;
-        outElements = out.elementCount();
         BFB_CUDA(cudaEventSynchronize(marks.events[marks.used - 1]));
         for (std::size_t m = 0; m + 1 < marks.used; ++m) {
             float ms = 0.0f;
@@ -1141,7 +1139,6 @@ BenchmarkResult Model::benchmark(const DeviceTensor& input, std::size_t warmupIt
         for (std::size_t d : p.fullShape) count *= d;
         elements += count;
     }
-    (void)outElements;
     r.estimatedMemoryBytes = elements * sizeof(float);
     return r;
 }
