@@ -2,12 +2,15 @@
 // values in the caches. Per query and key the arithmetic is 256 FMAs against 512 bytes of K and V, so the kernel is
 // laid out for HBM bandwidth and runs on CUDA cores:
 //   grid = (batch * heads) x splits; a CTA of 8 warps takes a contiguous range of keys of one (batch, head);
-//   a warp takes one key at a time: its 32 lanes read the key's 128 dims as one coalesced 256-byte row (4 dims per
-//   lane), the dot product with q is a 5-step shuffle reduction, the probability is the same in every lane, and
-//   each lane accumulates its 4 output dims from the value row (again one coalesced row). Keys go in batches of 4
-//   per warp; 48 warps per SM hide the latency. Online softmax per warp in log2 units; the 8 warps are merged through shared memory.
+//   a half-warp takes one key at a time: its 16 lanes read the key's 128 dims as one coalesced 256-byte row (8 dims =
+//   16 bytes per lane), the dot product with q is a 4-step shuffle reduction, the probability is the same in every
+//   lane of the half, and each lane accumulates its 8 output dims from the value row (again one coalesced row). Keys
+//   go in batches of 4 per half-warp; 32 warps per SM hide the latency. Online softmax per half-warp in log2 units;
+//   the 16 half-warps are merged through shared memory.
 // With one split the CTA writes the bf16 output row (and the row statistics); with several, fp32 partial results
-// {m, l, acc[128]} go to a workspace and attentionDecodeMergeKernel combines them in split order.
+// {m, l, acc[128]} go to a workspace and attentionDecodeMergeKernel combines them in split order. (Letting the CTA
+// that finishes a (batch, head) last do that merge, behind a fence and a counter, saves the launch but no time: as
+// a programmatic dependent the merge launch already overlaps the kernel's tail.)
 #include <cuda_bf16.h>
 
 #include <algorithm>
