@@ -108,6 +108,7 @@ SIGNATURES = {
     "bfb_model_save_checkpoint": (_I32, [_P, C.c_char_p]),
     "bfb_model_benchmark": (_I32, [_P, _P, C.POINTER(_I64), _I32, _I64, _I64, _P, _P, _I32, _P]),
     "bfb_model_load_checkpoint_streaming": (_I32, [_P, C.c_char_p, C.c_uint64, _P]),
+    "bfb_model_load_checkpoint_cached": (_I32, [_P, C.c_char_p, C.c_uint64, _P]),
     "bfb_checkpoint_index": (_I32, [C.c_char_p, _I32, C.c_char_p, _I32, C.POINTER(_I32), C.POINTER(_I64),
                                     C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(_I32)]),
     "bfb_model_forward_incremental": (_I32, [_P, _P, C.POINTER(_I64), _I32, _I32, C.POINTER(_P), C.POINTER(_I64),
@@ -342,6 +343,12 @@ class Model:
         check(lib().bfb_model_load_checkpoint_streaming(self._h, path.encode(), chunk_bytes, C.byref(stats)))
         return {name: getattr(stats, name) for name, _ in CheckpointLoadStats._fields_}
 
+    def load_checkpoint_cached(self, path: str, chunk_bytes: int = 0) -> dict:
+        """Streaming load that keeps / uses a cache of the converted GEMM weights beside the file."""
+        stats = CheckpointLoadStats()
+        check(lib().bfb_model_load_checkpoint_cached(self._h, path.encode(), chunk_bytes, C.byref(stats)))
+        return {name: getattr(stats, name) for name, _ in CheckpointLoadStats._fields_}
+
     def save_checkpoint(self, path: str):
         check(lib().bfb_model_save_checkpoint(self._h, path.encode()))
 
@@ -469,7 +476,8 @@ class BenchmarkResult(C.Structure):
 
 class CheckpointLoadStats(C.Structure):
     _fields_ = [("tensors", C.c_int64), ("file_bytes", C.c_uint64), ("read_bytes", C.c_uint64),
-                ("uploaded_bytes", C.c_uint64), ("seconds", C.c_double)]
+                ("uploaded_bytes", C.c_uint64), ("seconds", C.c_double), ("cache_hit", C.c_int32),
+                ("cache_bytes", C.c_uint64)]
 
 
 def checkpoint_index(path: str) -> list:

@@ -465,18 +465,32 @@ bfb_status bfb_model_load_checkpoint(bfb_model* model, const char* path) {
     });
 }
 
+namespace {
+void copyLoadStats(const bfb200::CheckpointLoadStats& s, bfb_checkpoint_load_stats* stats) {
+    if (stats == nullptr) return;
+    stats->tensors = static_cast<int64_t>(s.tensors);
+    stats->file_bytes = s.fileBytes;
+    stats->read_bytes = s.readBytes;
+    stats->uploaded_bytes = s.uploadedBytes;
+    stats->seconds = s.seconds;
+    stats->cache_hit = s.cacheHit ? 1 : 0;
+    stats->cache_bytes = s.cacheBytes;
+}
+}  // namespace
+
 bfb_status bfb_model_load_checkpoint_streaming(bfb_model* model, const char* path, uint64_t chunk_bytes,
                                                bfb_checkpoint_load_stats* stats) {
     return guarded([&] {
         require(model != nullptr && path != nullptr, "model: null argument");
-        const bfb200::CheckpointLoadStats s = bfb200::loadCheckpoint(*model->model, path, static_cast<std::size_t>(chunk_bytes));
-        if (stats != nullptr) {
-            stats->tensors = static_cast<int64_t>(s.tensors);
-            stats->file_bytes = s.fileBytes;
-            stats->read_bytes = s.readBytes;
-            stats->uploaded_bytes = s.uploadedBytes;
-            stats->seconds = s.seconds;
-        }
+        copyLoadStats(bfb200::loadCheckpoint(*model->model, path, static_cast<std::size_t>(chunk_bytes)), stats);
+    });
+}
+
+bfb_status bfb_model_load_checkpoint_cached(bfb_model* model, const char* path, uint64_t chunk_bytes,
+                                            bfb_checkpoint_load_stats* stats) {
+    return guarded([&] {
+        require(model != nullptr && path != nullptr, "model: null argument");
+        copyLoadStats(bfb200::loadCheckpointCached(*model->model, path, static_cast<std::size_t>(chunk_bytes)), stats);
     });
 }
 

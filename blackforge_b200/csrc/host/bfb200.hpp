@@ -218,6 +218,20 @@ public:
     BenchmarkResult benchmark(const DeviceTensor& input, std::size_t warmupIterations, std::size_t measuredIterations,
                               void* stream = nullptr);
 
+    // Converted GEMM weights (bf16 or e4m3, transposed, with their scales) as the tensor-core route holds them: for a
+    // cache file beside a checkpoint (loadCheckpointCached). The tag names compute format and tensor-parallel split
+    // (empty for an fp32-compute model, which has no converted weights); the fingerprint covers the tag and every
+    // parameter's name and shape. After adoptPreparedWeights() the fp32 copies of the GEMM weights do not exist.
+    struct PreparedPiece {
+        void* data;
+        std::size_t bytes;
+    };
+    std::string preparedWeightsTag() const;
+    std::uint64_t structureFingerprint() const;
+    std::vector<PreparedPiece> preparedWeightPieces(bool allocate);
+    void adoptPreparedWeights();
+    bool parameterIsGemmWeight(std::size_t index) const;
+
     // A parameter seen as rows of the full (unsharded) tensor, and the rows this tensor-parallel rank holds a part
     // of: all of them, except for row-sharded matrices and sharded vectors (one element per row).
     struct RowView {
@@ -252,10 +266,18 @@ struct CheckpointLoadStats {
     std::uint64_t readBytes = 0;      // read from the file by this rank
     std::uint64_t uploadedBytes = 0;  // sent to the device
     double seconds = 0.0;
+    bool cacheHit = false;            // loadCheckpointCached: the converted weights came from the cache file
+    std::uint64_t cacheBytes = 0;     // read from (hit) or written to (miss) the cache file
 };
 std::vector<CheckpointEntry> indexCheckpoint(const std::string& path);
 void saveCheckpoint(Model& model, const std::string& path);
 CheckpointLoadStats loadCheckpoint(Model& model, const std::string& path, std::size_t chunkBytes = 0);
+// The same, with a cache of the CONVERTED GEMM weights beside the file (`<path>.bfb200cache.<format>.tp<r>of<w>`):
+// written after the first load, and read instead of the fp32 GEMM weights on the next ones as long as the
+// checkpoint's size and modification time and the model's structure are unchanged. A hit reads half (bf16) or a
+// quarter (e4m3) of the bytes, skips the conversion pass and never creates the fp32 copies of the GEMM weights
+// (they can then not be read back, set or saved). An fp32-compute model loads as loadCheckpoint does.
+CheckpointLoadStats loadCheckpointCached(Model& model, const std::string& path, std::size_t chunkBytes = 0);
 
 // include/blackforge/backend/cuda/executor.hpp:20-33 — weights regenerated from the seed on every run.
 class Executor {

@@ -23,6 +23,7 @@
 #include <cstring>
 #include <deque>
 #include <fstream>
+#include <functional>
 #include <map>
 #include <mutex>
 #include <thread>
@@ -69,6 +70,7 @@ struct Segment {
     std::size_t firstRow = 0, rows = 0;
     std::uint64_t offset = 0;
     std::size_t bytes = 0;
+    void* deviceDst = nullptr;   // pieces of a converted-weights file go straight to this address
 };
 
 // Pinned staging buffers that travel between the reader thread and the uploading thread.
@@ -160,6 +162,76 @@ private:
     std::string error_;
 };
 
+// Reads the pieces with a few threads into pinned buffers while the calling thread hands each filled buffer to `upload`
+// (which issues asynchronous copies on the given stream and returns the bytes it sent). Returns their sum.
+using UploadFn = std::function<std::size_t(const Segment&, const void*, cudaStream_t)>;
+std::size_t streamSegments(const std::string& path, const std::vector<Segment>& segments, std::size_t largest,
+                           const UploadFn& upload) {
+    std::size_t uploadedBytes = 0;
+    Fd file(path);
+    if (file.fd < 0) ioFail("loadCheckpoint: cannot open '" + path + "'");
+    // a few readers (pread is thread-safe and the pieces are independent); two more buffers than readers, so that
+    // uploads are in flight while every reader holds one
+    const int readers = static_cast<int>(std::max<std::size_t>(
+        1, std::min<std::size_t>({4, segments.size(), std::max(1u, std::thread::hardware_concurrency() / 2)})));
+    const int kBuffers = readers + 2;
+    Ring ring(kBuffers, largest);
+    ring.setReaders(readers);
+    cudaStream_t stream = nullptr;
+    BFB_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    std::vector<cudaEvent_t> uploaded(static_cast<std::size_t>(kBuffers), nullptr);
+    for (auto& e : uploaded) BFB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+
+    std::atomic<std::size_t> nextSegment{0};
+    std::vector<std::thread> readerThreads;
+    for (int t = 0; t < readers; ++t) {
+        readerThreads.emplace_back([&] {
+            std::string error;
+            while (true) {
+                const std::size_t i = nextSegment.fetch_add(1);
+                if (i >= segments.size()) break;
+                const Segment& s = segments[i];
+                const int b = ring.takeFree();
+                if (b < 0) break;
+                if (readAt(file.fd, ring.data(b), s.bytes, s.offset) != s.bytes) {
+                    error = "loadCheckpoint: '" + path + "' is truncated or corrupt";
+                    break;
+                }
+                ring.giveFilled(b, s);
+            }
+            ring.readerFinished(error);
+        });
+    }
+
+    std::string failure;
+    try {
+        std::deque<int> inFlight;
+        int b = 0;
+        Segment s;
+        while (ring.takeFilled(&b, &s)) {
+            uploadedBytes += upload(s, ring.data(b), stream);
+            BFB_CUDA(cudaEventRecord(uploaded[b], stream));
+            inFlight.push_back(b);
+            while (inFlight.size() >= 2) {   // the other buffers stay with the readers
+                BFB_CUDA(cudaEventSynchronize(uploaded[inFlight.front()]));
+                ring.giveFree(inFlight.front());
+                inFlight.pop_front();
+            }
+        }
+        BFB_CUDA(cudaStreamSynchronize(stream));
+    } catch (const std::exception& e) {
+        failure = e.what();
+    }
+    ring.abandon();
+    for (std::thread& t : readerThreads) t.join();
+    (void)cudaStreamSynchronize(stream);
+    for (auto& e : uploaded) cudaEventDestroy(e);
+    cudaStreamDestroy(stream);
+    if (!failure.empty()) fail(BFB_CUDA_ERROR, failure);
+    if (!ring.error().empty()) ioFail(ring.error());
+    return uploadedBytes;
+}
+
 }  // namespace
 
 std::vector<CheckpointEntry> indexCheckpoint(const std::string& path) {
@@ -213,7 +285,8 @@ std::vector<CheckpointEntry> indexCheckpoint(const std::string& path) {
     return entries;
 }
 
-CheckpointLoadStats loadCheckpoint(Model& model, const std::string& path, std::size_t chunkBytes) {
+namespace {
+CheckpointLoadStats loadTensors(Model& model, const std::string& path, std::size_t chunkBytes, bool skipGemmWeights) {
     const auto t0 = std::chrono::steady_clock::now();
     const std::vector<CheckpointEntry> entries = indexCheckpoint(path);
 
@@ -240,6 +313,7 @@ CheckpointLoadStats loadCheckpoint(Model& model, const std::string& path, std::s
         const Model::RowView view = model.parameterRowView(target[i]);
         stats.fileBytes += entries[i].dataBytes;
         if (view.rows == 0 || view.rowElems == 0) continue;
+        if (skipGemmWeights && model.parameterIsGemmWeight(target[i])) continue;   // their converted form is in place
         const std::size_t rowBytes = view.rowElems * sizeof(float);
         const std::size_t perChunk = std::max<std::size_t>(1, chunkBytes / rowBytes);
         for (std::size_t r = 0; r < view.neededRows; r += perChunk) {
@@ -256,69 +330,142 @@ CheckpointLoadStats loadCheckpoint(Model& model, const std::string& path, std::s
     }
     if (segments.empty()) return stats;
 
-    Fd file(path);
-    if (file.fd < 0) ioFail("loadCheckpoint: cannot open '" + path + "'");
-    // a few readers (pread is thread-safe and the pieces are independent); two more buffers than readers, so that
-    // uploads are in flight while every reader holds one
-    const int readers = static_cast<int>(std::max<std::size_t>(
-        1, std::min<std::size_t>({4, segments.size(), std::max(1u, std::thread::hardware_concurrency() / 2)})));
-    const int kBuffers = readers + 2;
-    Ring ring(kBuffers, largest);
-    ring.setReaders(readers);
-    cudaStream_t stream = nullptr;
-    BFB_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
-    std::vector<cudaEvent_t> uploaded(static_cast<std::size_t>(kBuffers), nullptr);
-    for (auto& e : uploaded) BFB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-
-    std::atomic<std::size_t> nextSegment{0};
-    std::vector<std::thread> readerThreads;
-    for (int t = 0; t < readers; ++t) {
-        readerThreads.emplace_back([&] {
-            std::string error;
-            while (true) {
-                const std::size_t i = nextSegment.fetch_add(1);
-                if (i >= segments.size()) break;
-                const Segment& s = segments[i];
-                const int b = ring.takeFree();
-                if (b < 0) break;
-                if (readAt(file.fd, ring.data(b), s.bytes, s.offset) != s.bytes) {
-                    error = "loadCheckpoint: '" + path + "' is truncated or corrupt";
-                    break;
-                }
-                ring.giveFilled(b, s);
-            }
-            ring.readerFinished(error);
-        });
-    }
-
-    std::string failure;
-    try {
-        std::deque<int> inFlight;
-        int b = 0;
-        Segment s;
-        while (ring.takeFilled(&b, &s)) {
-            stats.uploadedBytes += model.uploadParameterRows(s.param, s.firstRow, s.rows,
-                                                             static_cast<const float*>(ring.data(b)), stream);
-            BFB_CUDA(cudaEventRecord(uploaded[b], stream));
-            inFlight.push_back(b);
-            while (inFlight.size() >= 2) {   // the other buffers stay with the readers
-                BFB_CUDA(cudaEventSynchronize(uploaded[inFlight.front()]));
-                ring.giveFree(inFlight.front());
-                inFlight.pop_front();
-            }
-        }
-        BFB_CUDA(cudaStreamSynchronize(stream));
-    } catch (const std::exception& e) {
-        failure = e.what();
-    }
-    ring.abandon();
-    for (std::thread& t : readerThreads) t.join();
-    (void)cudaStreamSynchronize(stream);
-    for (auto& e : uploaded) cudaEventDestroy(e);
-    cudaStreamDestroy(stream);
+    stats.uploadedBytes += streamSegments(path, segments, largest, [&](const Segment& seg, const void* host, cudaStream_t stream) {
+        return model.uploadParameterRows(seg.param, seg.firstRow, seg.rows, static_cast<const float*>(host), stream);
+    });
     model.invalidatePreparedWeights();
-    if (!failure.empty()) fail(BFB_CUDA_ERROR, failure);
-    if (!ring.error().empty()) ioFail(ring.error());
+    stats.seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    return stats;
+}
+
+}  // namespace
+
+CheckpointLoadStats loadCheckpoint(Model& model, const std::string& path, std::size_t chunkBytes) {
+    return loadTensors(model, path, chunkBytes, false);
+}
+
+// ---- cache of converted weights beside the checkpoint ------------------------------------------------------
+namespace {
+
+constexpr char kCacheMagic[8] = {'B', 'F', 'B', '2', 'P', 'R', 'E', 'P'};
+struct CacheHeader {
+    char magic[8];
+    std::uint32_t version;
+    std::uint32_t pieces;
+    std::uint64_t fingerprint;
+    std::uint64_t sourceBytes;
+    std::int64_t sourceMtimeNs;
+};   // followed by `pieces` u64 sizes, then the pieces' bytes back to back
+
+bool sourceIdentity(const std::string& path, std::uint64_t* bytes, std::int64_t* mtimeNs) {
+    struct stat st {};
+    if (::stat(path.c_str(), &st) != 0) return false;
+    *bytes = static_cast<std::uint64_t>(st.st_size);
+    *mtimeNs = static_cast<std::int64_t>(st.st_mtim.tv_sec) * 1000000000ll + st.st_mtim.tv_nsec;
+    return true;
+}
+
+// The cache's data offset when the file is a valid cache of this checkpoint for this model, else 0.
+std::uint64_t validCache(const std::string& cachePath, const CacheHeader& want, const std::vector<std::uint64_t>& sizes) {
+    Fd file(cachePath);
+    if (file.fd < 0) return 0;
+    CacheHeader have{};
+    if (readAt(file.fd, &have, sizeof(have), 0) != sizeof(have)) return 0;
+    if (std::memcmp(have.magic, want.magic, sizeof(have.magic)) != 0 || have.version != want.version ||
+        have.pieces != want.pieces || have.fingerprint != want.fingerprint || have.sourceBytes != want.sourceBytes ||
+        have.sourceMtimeNs != want.sourceMtimeNs) {
+        return 0;
+    }
+    std::vector<std::uint64_t> stored(sizes.size());
+    const std::size_t tableBytes = sizes.size() * sizeof(std::uint64_t);
+    if (readAt(file.fd, stored.data(), tableBytes, sizeof(have)) != tableBytes || stored != sizes) return 0;
+    std::uint64_t total = sizeof(have) + tableBytes;
+    for (std::uint64_t b : sizes) total += b;
+    struct stat st {};
+    if (::fstat(file.fd, &st) != 0 || static_cast<std::uint64_t>(st.st_size) != total) return 0;
+    return sizeof(have) + tableBytes;
+}
+
+}  // namespace
+
+CheckpointLoadStats loadCheckpointCached(Model& model, const std::string& path, std::size_t chunkBytes) {
+    const auto t0 = std::chrono::steady_clock::now();
+    const std::string tag = model.preparedWeightsTag();
+    if (tag.empty()) return loadCheckpoint(model, path, chunkBytes);   // fp32 compute: nothing to cache
+    (void)indexCheckpoint(path);   // a missing or damaged checkpoint fails here, cache or not
+    if (chunkBytes == 0) chunkBytes = std::size_t(4) << 20;
+    const std::string cachePath = path + ".bfb200cache." + tag;
+    CacheHeader want{};
+    std::memcpy(want.magic, kCacheMagic, sizeof(kCacheMagic));
+    want.version = 1;
+    want.fingerprint = model.structureFingerprint();
+    if (!sourceIdentity(path, &want.sourceBytes, &want.sourceMtimeNs)) ioFail("loadCheckpoint: cannot stat '" + path + "'");
+
+    std::vector<Model::PreparedPiece> pieces = model.preparedWeightPieces(true);
+    std::vector<std::uint64_t> sizes;
+    for (const Model::PreparedPiece& p : pieces) sizes.push_back(p.bytes);
+    want.pieces = static_cast<std::uint32_t>(pieces.size());
+
+    const std::uint64_t dataAt = validCache(cachePath, want, sizes);
+    if (dataAt != 0) {
+        std::vector<Segment> segments;
+        std::size_t largest = 0;
+        std::uint64_t at = dataAt, cacheBytes = 0;
+        for (const Model::PreparedPiece& p : pieces) {
+            for (std::size_t done = 0; done < p.bytes; done += chunkBytes) {
+                Segment s;
+                s.offset = at + done;
+                s.bytes = std::min(chunkBytes, p.bytes - done);
+                s.deviceDst = static_cast<char*>(p.data) + done;
+                largest = std::max(largest, s.bytes);
+                segments.push_back(s);
+            }
+            at += p.bytes;
+            cacheBytes += p.bytes;
+        }
+        const std::size_t sent = streamSegments(cachePath, segments, largest, [](const Segment& seg, const void* host, cudaStream_t stream) {
+            BFB_CUDA(cudaMemcpyAsync(seg.deviceDst, host, seg.bytes, cudaMemcpyHostToDevice, stream));
+            return seg.bytes;
+        });
+        model.adoptPreparedWeights();
+        CheckpointLoadStats stats = loadTensors(model, path, chunkBytes, true);   // tables, biases
+        stats.cacheHit = true;
+        stats.cacheBytes = cacheBytes;
+        stats.readBytes += cacheBytes;
+        stats.uploadedBytes += sent;
+        stats.seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+        return stats;
+    }
+
+    // miss: the ordinary load, one conversion, and the cache for next time (written beside, renamed into place)
+    CheckpointLoadStats stats = loadCheckpoint(model, path, chunkBytes);
+    pieces = model.preparedWeightPieces(false);
+    const std::string tmpPath = cachePath + ".tmp" + std::to_string(static_cast<long long>(::getpid()));
+    {
+        std::ofstream out(tmpPath, std::ios::binary | std::ios::trunc);
+        if (!out) return stats;   // a read-only directory: no cache, no error
+        out.write(reinterpret_cast<const char*>(&want), sizeof(want));
+        out.write(reinterpret_cast<const char*>(sizes.data()), static_cast<std::streamsize>(sizes.size() * sizeof(std::uint64_t)));
+        std::vector<char> host(std::min<std::size_t>(std::size_t(64) << 20, std::max<std::size_t>(chunkBytes, 1)));
+        for (const Model::PreparedPiece& p : pieces) {
+            for (std::size_t done = 0; done < p.bytes; done += host.size()) {
+                const std::size_t n = std::min(host.size(), p.bytes - done);
+                BFB_CUDA(cudaMemcpy(host.data(), static_cast<const char*>(p.data) + done, n, cudaMemcpyDeviceToHost));
+                out.write(host.data(), static_cast<std::streamsize>(n));
+            }
+            stats.cacheBytes += p.bytes;
+        }
+        if (!out) {
+            out.close();
+            ::unlink(tmpPath.c_str());
+            stats.cacheBytes = 0;
+            return stats;
+        }
+    }
+    if (::rename(tmpPath.c_str(), cachePath.c_str()) != 0) {
+        ::unlink(tmpPath.c_str());
+        stats.cacheBytes = 0;
+    }
     stats.seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
     return stats;
 }

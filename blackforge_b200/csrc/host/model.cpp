@@ -240,6 +240,7 @@ struct Model::Impl {
 
     void buildStructure();
     void allocateParams();
+    std::vector<char> gemmWeightMask() const;
     void setParam(std::size_t index, const float* hostFull);
     void getParam(std::size_t index, float* hostFull);
     void prepare(cudaStream_t stream);
@@ -351,14 +352,32 @@ void Model::Impl::buildStructure() {
     }
 }
 
+// GEMM weights (attention wq/wk/wv/wout, feed-forward w1/w2, linear weight) by parameter index
+std::vector<char> Model::Impl::gemmWeightMask() const {
+    std::vector<char> mask(params.size(), 0);
+    for (const Layer& l : layers) {
+        if (l.kind != BFB_OP_ATTENTION && l.kind != BFB_OP_FEEDFORWARD && l.kind != BFB_OP_LINEAR) continue;
+        const int weightSlots[3][4] = {{0, 1, 2, 3}, {0, 2, -1, -1}, {0, -1, -1, -1}};
+        const int* slots = l.kind == BFB_OP_ATTENTION ? weightSlots[0] : l.kind == BFB_OP_FEEDFORWARD ? weightSlots[1] : weightSlots[2];
+        for (int i = 0; i < 4; ++i) {
+            if (slots[i] >= 0) mask[l.p[slots[i]]] = 1;
+        }
+    }
+    return mask;
+}
+
 void Model::Impl::allocateParams() {
     if (built) return;
+    // converted weights adopted from a cache file: the fp32 copies of the GEMM weights never exist
+    const std::vector<char> skip = mastersReleased ? gemmWeightMask() : std::vector<char>(params.size(), 0);
     for (std::size_t i = 0; i < params.size(); ++i) {
+        if (skip[i]) continue;
         params[i].value = DeviceTensor::zeros(localShape(params[i].fullShape, meta[i].shard));
     }
     built = true;
     if (randomInit) {
         for (std::size_t i = 0; i < params.size(); ++i) {
+            if (skip[i]) continue;
             HostTensor t = randomTensor(params[i].fullShape, seedFor(seed, meta[i].valueId, meta[i].salt));
             setParam(i, t.data.data());
         }
@@ -1217,6 +1236,92 @@ void Model::releaseMasterWeights() {
     bfb::poolTrim();
 }
 
+bool Model::parameterIsGemmWeight(std::size_t index) const {
+    require(index < impl_->params.size(), "Model: parameter index out of range");
+    return impl_->mode != Mode::Fp32 && impl_->gemmWeightMask()[index] != 0;
+}
+
+std::string Model::preparedWeightsTag() const {
+    if (impl_->mode == Mode::Fp32) return "";
+    return std::string(impl_->mode == Mode::Bf16 ? "bf16" : "e4m3") + ".tp" + std::to_string(impl_->tpRank) + "of" +
+           std::to_string(impl_->tpWorld);
+}
+
+// FNV-1a over the compute format, the tensor-parallel split and every parameter's name and full shape
+std::uint64_t Model::structureFingerprint() const {
+    std::uint64_t h = 1469598103934665603ull;
+    auto mix = [&](const void* data, std::size_t bytes) {
+        const unsigned char* p = static_cast<const unsigned char*>(data);
+        for (std::size_t i = 0; i < bytes; ++i) {
+            h ^= p[i];
+            h *= 1099511628211ull;
+        }
+    };
+    const std::string tag = preparedWeightsTag();
+    mix(tag.data(), tag.size());
+    for (const Parameter& p : impl_->params) {
+        mix(p.name.data(), p.name.size());
+        for (std::size_t d : p.fullShape) {
+            const std::uint64_t v = d;
+            mix(&v, sizeof(v));
+        }
+    }
+    return h;
+}
+
+// The converted weights of the planned route, layer by layer: w0, w1 (when the layer has one) and the four scale
+// floats. allocate == false: after a conversion, for saving. allocate == true: buffers of the right sizes are created
+// to be filled from a file; adoptPreparedWeights() then makes them the model's weights.
+std::vector<Model::PreparedPiece> Model::preparedWeightPieces(bool allocate) {
+    std::vector<PreparedPiece> pieces;
+    if (impl_->mode == Mode::Fp32) return pieces;
+    if (!allocate) {
+        impl_->prepare(nullptr);
+        BFB_CUDA(cudaStreamSynchronize(nullptr));
+    }
+    const std::size_t eb = impl_->mode == Mode::Bf16 ? 2 : 1;
+    auto elems = [&](int paramIndex) {
+        std::size_t n = 1;
+        for (std::size_t d : impl_->localShape(impl_->params[paramIndex].fullShape, impl_->meta[paramIndex].shard)) n *= d;
+        return n;
+    };
+    for (Layer& l : impl_->layers) {
+        if (l.kind != BFB_OP_ATTENTION && l.kind != BFB_OP_FEEDFORWARD && l.kind != BFB_OP_LINEAR) continue;
+        std::size_t b0 = 0, b1 = 0;
+        if (l.kind == BFB_OP_ATTENTION) {
+            b0 = (elems(l.p[0]) + elems(l.p[1]) + elems(l.p[2])) * eb;
+            b1 = elems(l.p[3]) * eb;
+        } else if (l.kind == BFB_OP_FEEDFORWARD) {
+            b0 = elems(l.p[0]) * eb;
+            b1 = elems(l.p[2]) * eb;
+        } else {
+            b0 = elems(l.p[0]) * eb;
+        }
+        if (allocate) {
+            l.w0.ensure(b0);
+            if (b1 > 0) l.w1.ensure(b1);
+            l.scales.ensure(4 * sizeof(float));
+        }
+        pieces.push_back({l.w0.ptr, b0});
+        if (b1 > 0) pieces.push_back({l.w1.ptr, b1});
+        pieces.push_back({l.scales.ptr, 4 * sizeof(float)});
+    }
+    return pieces;
+}
+
+void Model::adoptPreparedWeights() {
+    if (impl_->mode == Mode::Fp32) return;
+    if (impl_->built) {   // fp32 copies exist already: drop those of the GEMM weights
+        const std::vector<char> mask = impl_->gemmWeightMask();
+        for (std::size_t i = 0; i < impl_->params.size(); ++i) {
+            if (mask[i]) impl_->params[i].value = DeviceTensor();
+        }
+        bfb::poolTrim();
+    }
+    impl_->mastersReleased = true;
+    impl_->prepared = true;
+}
+
 // A parameter as rows of the full (unsharded) tensor: [rows, cols] for rank 2, one element per row for vectors (so
 // that a vector's slice is a row range), one row otherwise.
 Model::RowView Model::parameterRowView(std::size_t index) const {
@@ -1277,7 +1382,9 @@ std::size_t Model::uploadParameterRows(std::size_t index, std::size_t firstRow, 
 
 void Model::setParameter(std::size_t index, const float* hostFullValues) { impl_->setParam(index, hostFullValues); }
 void Model::getParameter(std::size_t index, float* hostFullValues) { impl_->getParam(index, hostFullValues); }
-void Model::invalidatePreparedWeights() { impl_->prepared = false; }
+void Model::invalidatePreparedWeights() {
+    if (!impl_->mastersReleased) impl_->prepared = false;   // without fp32 copies there is nothing to convert again
+}
 
 std::optional<std::size_t> Model::firstLayerEmbeddingVocabSize() const {
     if (impl_->layers.empty() || impl_->layers.front().kind != BFB_OP_EMBEDDING) return std::nullopt;

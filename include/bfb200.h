@@ -359,9 +359,20 @@ typedef struct bfb_checkpoint_load_stats {
     uint64_t read_bytes;     /* read from the file by this rank */
     uint64_t uploaded_bytes; /* sent to the device */
     double seconds;
+    int32_t cache_hit;       /* bfb_model_load_checkpoint_cached: the converted weights came from the cache file */
+    uint64_t cache_bytes;    /* read from (hit) or written to (miss) the cache file */
 } bfb_checkpoint_load_stats;
 bfb_status bfb_model_load_checkpoint_streaming(bfb_model* model, const char* path, uint64_t chunk_bytes,
                                                bfb_checkpoint_load_stats* stats);
+
+/* The streaming load with a cache of the CONVERTED GEMM weights (bf16 or e4m3, transposed, with their scales) beside
+ * the checkpoint, `<path>.bfb200cache.<format>.tp<rank>of<world>`: written after the first load and read instead of
+ * the fp32 GEMM weights on later ones while the checkpoint's size and modification time and the model's structure are
+ * unchanged. A hit reads half (bf16) or a quarter (e4m3) of the bytes, skips the conversion pass and never creates the
+ * fp32 copies of the GEMM weights (as after bfb_model_release_master_weights they can then not be read, set or
+ * saved). A cache that cannot be written is not an error. An fp32-compute model loads as bfb_model_load_checkpoint. */
+bfb_status bfb_model_load_checkpoint_cached(bfb_model* model, const char* path, uint64_t chunk_bytes,
+                                            bfb_checkpoint_load_stats* stats);
 
 /* Header pass over a BFCKPT1 file, no device needed: entry `index` (name copied into name_buf, up to 8 dims, the
  * byte offset and size of its fp32 data) and the number of entries. index == -1 only counts. The whole file's

@@ -101,6 +101,59 @@ def test_streaming_load_in_small_pieces(gpu, tmp_path, chunk):
     assert np.array_equal(m.forward_host(ids), first)
 
 
+@pytest.mark.parametrize("compute", ["bf16", "fp8.e4m3"])
+def test_cache_of_converted_weights_beside_the_checkpoint(gpu, tmp_path, compute):
+    """First load: ordinary, and the converted GEMM weights are written beside the file. Later loads read those instead
+    of the fp32 GEMM weights: fewer bytes, the same logits bit for bit, no fp32 copies of the GEMM weights. A changed
+    checkpoint or another model structure does not use the stale cache."""
+    cfg = dict(vocab=256, dim=256, layers=2, heads=2, hidden=512, max_seq=64)
+    ops = O.lm_ops(**cfg)
+    prec = {"storage": "bf16", "compute": compute}
+    params = O.synth_params(ops, None, seed=5, sigma=0.05, bias_sigma=0.05)
+    path = str(tmp_path / "w.bfckpt")
+    O.save_checkpoint(path, [(n, params[n]) for n, _ in O.param_layout(ops)])
+    ids = O.synth_token_ids(2, 64, cfg["vocab"], seed=6)
+
+    plain = gpu.Model(ops, precision=prec, random_init=False)
+    plain.load_checkpoint(path)
+    want = plain.forward_host(ids)
+
+    first = gpu.Model(ops, precision=prec, random_init=False)
+    s1 = first.load_checkpoint_cached(path, 4096)
+    assert s1["cache_hit"] == 0 and s1["cache_bytes"] > 0
+    caches = [f for f in os.listdir(tmp_path) if ".bfb200cache." in f]
+    assert len(caches) == 1 and caches[0].endswith(".tp0of1")
+    assert np.array_equal(first.forward_host(ids), want)
+
+    second = gpu.Model(ops, precision=prec, random_init=False)
+    s2 = second.load_checkpoint_cached(path, 4096)
+    assert s2["cache_hit"] == 1 and s2["cache_bytes"] == s1["cache_bytes"]
+    assert s2["read_bytes"] < s1["read_bytes"]
+    assert np.array_equal(second.forward_host(ids), want)
+    names = second.param_names()
+    assert np.array_equal(second.get_param(names.index("embedding1.table")), params["embedding1.table"])
+    with pytest.raises(gpu.BfbError):                      # the fp32 copy of a GEMM weight was never made
+        second.get_param(names.index("attention3.wq"))
+
+    # another structure (one more layer) ignores this cache: different file name content, fingerprint mismatch
+    other_ops = O.lm_ops(**dict(cfg, hidden=768))
+    other_params = O.synth_params(other_ops, None, seed=5, sigma=0.05, bias_sigma=0.05)
+    O.save_checkpoint(path, [(n, other_params[n]) for n, _ in O.param_layout(other_ops)])   # same path, new content
+    third = gpu.Model(other_ops, precision=prec, random_init=False)
+    s3 = third.load_checkpoint_cached(path, 4096)
+    assert s3["cache_hit"] == 0
+    ref = gpu.Model(other_ops, precision=prec, random_init=False)
+    ref.load_checkpoint(path)
+    assert np.array_equal(third.forward_host(ids), ref.forward_host(ids))
+    # a damaged cache file is not trusted
+    cache = os.path.join(tmp_path, [f for f in os.listdir(tmp_path) if ".bfb200cache." in f][0])
+    blob = open(cache, "rb").read()
+    open(cache, "wb").write(blob[:-5])
+    fourth = gpu.Model(other_ops, precision=prec, random_init=False)
+    assert fourth.load_checkpoint_cached(path, 4096)["cache_hit"] == 0
+    assert np.array_equal(fourth.forward_host(ids), ref.forward_host(ids))
+
+
 def test_checkpoint_errors(gpu, tmp_path):
     ops = O.lm_ops(vocab=8, dim=8, layers=1, heads=2, hidden=16, max_seq=6)
     m = gpu.Model(ops)
