@@ -642,7 +642,9 @@ HostTransfer& hostTransfer() {
 // Measured with 2 G logits per call: one process on a 16-core host with a PCIe 5 x16 link, all slices narrow
 // 127-138 ms, three quarters 148 ms, half 158 ms, none 168-182 ms (bound by the link); four processes on a 32-core
 // host, half narrow 487 ms per step, because they share the host's memory bandwidth, which is then the limit and
-// which the plain copies load least. So: everything when this process has the host to itself and 12 or more
+// which the plain copies load least. (One host of the same kind took 176 ms with all slices narrow and 147 ms with
+// seven of eight; there seven of eight cost 143 against 138 ms on a host that keeps up. The default stays with the
+// common case.) So: everything when this process has the host to itself and 12 or more
 // threads, half with 6 or more, none below or when a launcher reports several processes on the host
 // (LOCAL_WORLD_SIZE > 1). BFB_HOST_NARROW_PCT overrides (0..100).
 int narrowSharePercent() {
