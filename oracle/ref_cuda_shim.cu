@@ -1,0 +1,152 @@
+// TEST INFRASTRUCTURE — not part of the product path.
+//
+// A C-ABI window onto the UNMODIFIED BlackForge CUDA backend (blackforge::backend::cuda::Model with its cuBLASLt
+// bf16 path, fusedAttentionForward), compiled from the reference's own sources where they lie (oracle/Makefile,
+// target cuda). It lets the GPU parity tests compare this repository's kernels with the reference's own device
+// results on the same inputs. Nothing here re-implements reference behaviour: every entry point forwards to a
+// reference function and copies the result out. Handles of compiled programs come from refCompile (ref_shim.cpp).
+//
+// Conventions as in ref_shim.cpp: 0 on success, 1 for std::invalid_argument, 2 for any other std::exception
+// (message in refCudaLastError()); tensor results are left in a per-thread slot (refCudaResult*).
+
+#include <cstdint>
+#include <exception>
+#include <optional>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "blackforge/backend/cuda/device_query.hpp"
+#include "blackforge/backend/cuda/device_tensor.hpp"
+#include "blackforge/backend/cuda/fused_attention.hpp"
+#include "blackforge/backend/cuda/model.hpp"
+#include "blackforge/ir/module.hpp"
+
+namespace bf = blackforge;
+namespace cuda = blackforge::backend::cuda;
+using bf::runtime::Tensor;
+
+extern "C" const void* refCompiledModelIR(void* handle);   // ref_shim.cpp
+
+namespace {
+
+thread_local std::string gError;
+thread_local Tensor gOut;
+
+template <typename Fn>
+int guarded(Fn&& fn) {
+    try {
+        fn();
+        return 0;
+    } catch (const std::invalid_argument& e) {
+        gError = e.what();
+        return 1;
+    } catch (const std::exception& e) {
+        gError = e.what();
+        return 2;
+    }
+}
+
+Tensor hostTensor(const float* data, const int64_t* shape, int rank) {
+    std::vector<std::size_t> dims(static_cast<std::size_t>(rank));
+    std::size_t count = 1;
+    for (int i = 0; i < rank; ++i) {
+        dims[static_cast<std::size_t>(i)] = static_cast<std::size_t>(shape[i]);
+        count *= dims[static_cast<std::size_t>(i)];
+    }
+    return Tensor(std::move(dims), std::vector<float>(data, data + count));
+}
+
+bf::sema::DType dtypeFromCode(int code) {   // the codes of ref_shim.cpp
+    switch (code) {
+        case 0: return bf::sema::DType::FP8_E4M3;
+        case 1: return bf::sema::DType::FP8_E5M2;
+        case 2: return bf::sema::DType::FP16;
+        case 3: return bf::sema::DType::BF16;
+        case 4: return bf::sema::DType::TF32;
+        default: return bf::sema::DType::FP32;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* refCudaLastError() { return gError.c_str(); }
+int refCudaResultRank() { return static_cast<int>(gOut.rank()); }
+void refCudaResultShape(int64_t* out) {
+    for (std::size_t i = 0; i < gOut.rank(); ++i) out[i] = static_cast<int64_t>(gOut.shape()[i]);
+}
+int64_t refCudaResultCount() { return static_cast<int64_t>(gOut.elementCount()); }
+void refCudaResultCopy(float* out) {
+    for (std::size_t i = 0; i < gOut.elementCount(); ++i) out[i] = gOut.at(i);
+}
+
+int refCudaDeviceCount() {
+    try {
+        return static_cast<int>(cuda::enumerateDevices().size());
+    } catch (...) {
+        return 0;
+    }
+}
+
+int refCudaSetDevice(int index) {
+    return guarded([&] { cuda::setActiveDevice(index); });
+}
+
+// cuda::Model of a compiled program's first model; compute < 0 means no precision policy (fp32 path).
+int refCudaModelNew(void* compiled, unsigned int seed, int storage, int compute, int accumulate, void** outModel) {
+    return guarded([&] {
+        const auto* ir = static_cast<const bf::ir::ModelIR*>(refCompiledModelIR(compiled));
+        std::optional<bf::ir::PrecisionPolicy> policy;
+        if (compute >= 0) {
+            bf::ir::PrecisionPolicy p;
+            p.storage = dtypeFromCode(storage);
+            p.compute = dtypeFromCode(compute);
+            p.accumulate = dtypeFromCode(accumulate);
+            policy = p;
+        }
+        *outModel = new cuda::Model(*ir, seed, policy);
+    });
+}
+
+void refCudaModelFree(void* model) { delete static_cast<cuda::Model*>(model); }
+
+int refCudaModelParamCount(void* model) {
+    return static_cast<int>(static_cast<cuda::Model*>(model)->parameters().size());
+}
+
+const char* refCudaModelParamName(void* model, int index) {
+    return static_cast<cuda::Model*>(model)->parameters().at(static_cast<std::size_t>(index))->name.c_str();
+}
+
+int refCudaModelParamSet(void* model, int index, const float* data, const int64_t* shape, int rank) {
+    return guarded([&] {
+        cuda::Parameter* p = static_cast<cuda::Model*>(model)->parameters().at(static_cast<std::size_t>(index));
+        Tensor t = hostTensor(data, shape, rank);
+        if (t.shape() != p->value.shape()) throw std::invalid_argument("refCudaModelParamSet: shape mismatch");
+        p->value = cuda::DeviceTensor::fromHost(t);
+    });
+}
+
+int refCudaModelForward(void* model, const float* data, const int64_t* shape, int rank) {
+    return guarded([&] {
+        cuda::DeviceTensor in = cuda::DeviceTensor::fromHost(hostTensor(data, shape, rank));
+        gOut = static_cast<cuda::Model*>(model)->forward(in).toHost();
+    });
+}
+
+// fusedAttentionForward on fp32 q [batch, newLen, dim], k / v [batch, totalLen, dim]; the output lands in the result slot.
+int refCudaFusedAttention(const float* q, const int64_t* qShape, const float* k, const int64_t* kShape, const float* v,
+                          int64_t numHeads, float scale, int64_t oldLen) {
+    return guarded([&] {
+        cuda::DeviceTensor dq = cuda::DeviceTensor::fromHost(hostTensor(q, qShape, 3));
+        cuda::DeviceTensor dk = cuda::DeviceTensor::fromHost(hostTensor(k, kShape, 3));
+        cuda::DeviceTensor dv = cuda::DeviceTensor::fromHost(hostTensor(v, kShape, 3));
+        cuda::FusedAttentionForwardResult r = cuda::fusedAttentionForward(dq, dk, dv, static_cast<std::size_t>(numHeads),
+                                                                          scale, static_cast<std::size_t>(oldLen));
+        gOut = r.output.toHost();
+    });
+}
+
+}  // extern "C"

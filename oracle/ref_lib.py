@@ -218,3 +218,96 @@ class Model:
     def set_param(self, index: int, value):
         a, packed = _t(value)
         _check(lib().refModelParamSet(self._m, index, *packed))
+
+
+# ---- the reference's CUDA backend (oracle/_ref/libbf_ref_cuda.so, `make -C oracle cuda`) ------------------------
+# A second library that holds the reference's front end, CPU backend AND its unmodified CUDA backend (cuBLAS /
+# cuBLASLt), so that the GPU parity tests can compare this repository's kernels with the reference's own device
+# results. Programs are compiled through this library's own front end: handles do not cross libraries.
+
+CUDA_LIB_PATH = os.path.join(_HERE, "_ref", "libbf_ref_cuda.so")
+_cuda_lib = None
+
+
+def cuda_available() -> bool:
+    return os.path.exists(CUDA_LIB_PATH)
+
+
+def cuda_lib():
+    global _cuda_lib
+    if _cuda_lib is None:
+        if not cuda_available():
+            raise FileNotFoundError(f"{CUDA_LIB_PATH} missing: run `make -C oracle cuda` where the reference sources exist")
+        _cuda_lib = C.CDLL(CUDA_LIB_PATH)
+        _cuda_lib.refLastError.restype = C.c_char_p
+        _cuda_lib.refCudaLastError.restype = C.c_char_p
+        _cuda_lib.refCudaResultCount.restype = C.c_int64
+        _cuda_lib.refCudaModelParamName.restype = C.c_char_p
+    return _cuda_lib
+
+
+def _cuda_check(code: int, front_end: bool = False):
+    if code != 0:
+        l = cuda_lib()
+        raise RefError(code, (l.refLastError() if front_end else l.refCudaLastError()).decode("utf-8", "replace"))
+
+
+def _cuda_result() -> np.ndarray:
+    l = cuda_lib()
+    rank = l.refCudaResultRank()
+    shape = (C.c_int64 * max(rank, 1))()
+    l.refCudaResultShape(shape)
+    out = np.empty([shape[i] for i in range(rank)], dtype=np.float32)
+    if out.size:
+        l.refCudaResultCopy(out.ctypes.data_as(C.c_void_p))
+    return out
+
+
+class CudaModel:
+    """blackforge::backend::cuda::Model (the reference's own device path) built from program text."""
+
+    def __init__(self, source: str, seed: int = 42, precision: Optional[dict] = None):
+        l = cuda_lib()
+        self._c = C.c_void_p()
+        self._m = C.c_void_p()
+        _cuda_check(l.refCompile(source.encode(), C.byref(self._c)), front_end=True)
+        if precision is None:
+            codes = (5, -1, 5)
+        else:
+            codes = (DTYPE_CODES[precision["storage"]], DTYPE_CODES[precision["compute"]],
+                     DTYPE_CODES[precision.get("accumulate", "fp32")])
+        _cuda_check(l.refCudaModelNew(self._c, C.c_uint(seed), *codes, C.byref(self._m)))
+
+    def close(self):
+        if getattr(self, "_m", None) and _cuda_lib is not None:
+            _cuda_lib.refCudaModelFree(self._m)
+            self._m = None
+        if getattr(self, "_c", None) and _cuda_lib is not None:
+            _cuda_lib.refCompiledFree(self._c)
+            self._c = None
+
+    def __del__(self):
+        self.close()
+
+    def param_names(self) -> list:
+        l = cuda_lib()
+        return [l.refCudaModelParamName(self._m, i).decode() for i in range(l.refCudaModelParamCount(self._m))]
+
+    def set_param(self, index: int, value):
+        a, packed = _t(value)
+        _cuda_check(cuda_lib().refCudaModelParamSet(self._m, index, *packed))
+
+    def forward(self, x) -> np.ndarray:
+        a, packed = _t(x)
+        _cuda_check(cuda_lib().refCudaModelForward(self._m, *packed))
+        return _cuda_result()
+
+
+def cuda_fused_attention(q, k, v, num_heads: int, scale: float, old_len: int = 0) -> np.ndarray:
+    """fusedAttentionForward of the reference on fp32 q [batch, newLen, dim], k / v [batch, totalLen, dim]."""
+    qa, ka, va = (np.ascontiguousarray(t, dtype=np.float32) for t in (q, k, v))
+    qs, ks = (C.c_int64 * 3)(*qa.shape), (C.c_int64 * 3)(*ka.shape)
+    _cuda_check(cuda_lib().refCudaFusedAttention(qa.ctypes.data_as(C.c_void_p), qs, ka.ctypes.data_as(C.c_void_p), ks,
+                                                 va.ctypes.data_as(C.c_void_p), C.c_int64(num_heads), C.c_float(scale),
+                                                 C.c_int64(old_len)))
+    return _cuda_result()

@@ -141,6 +141,9 @@ int refCompile(const char* source, void** outHandle) {
 
 void refCompiledFree(void* handle) { delete static_cast<Compiled*>(handle); }
 
+// The first model's IR of a compiled program, for ref_cuda_shim.cu (which builds the reference's cuda::Model from it).
+const void* refCompiledModelIR(void* handle) { return &static_cast<Compiled*>(handle)->module.models.front(); }
+
 // precision block: returns 1 if present and fills storage/compute/accumulate dtype codes.
 int refCompiledPrecision(void* handle, int* storage, int* compute, int* accumulate) {
     auto* c = static_cast<Compiled*>(handle);
