@@ -9,6 +9,8 @@
 // Conventions as in ref_shim.cpp: 0 on success, 1 for std::invalid_argument, 2 for any other std::exception
 // (message in refCudaLastError()); tensor results are left in a per-thread slot (refCudaResult*).
 
+#include <cuda_runtime.h>
+
 #include <cstdint>
 #include <exception>
 #include <optional>
@@ -133,6 +135,29 @@ int refCudaModelForward(void* model, const float* data, const int64_t* shape, in
     return guarded([&] {
         cuda::DeviceTensor in = cuda::DeviceTensor::fromHost(hostTensor(data, shape, rank));
         gOut = static_cast<cuda::Model*>(model)->forward(in).toHost();
+    });
+}
+
+// Device time of `iters` forward passes (CUDA events around them, input uploaded once, results dropped on the
+// device), after `warmup` untimed ones: the reference's own GPU path as a timing baseline.
+int refCudaModelForwardTimed(void* model, const float* data, const int64_t* shape, int rank, int warmup, int iters,
+                             double* msPerPass) {
+    return guarded([&] {
+        cuda::DeviceTensor in = cuda::DeviceTensor::fromHost(hostTensor(data, shape, rank));
+        auto* m = static_cast<cuda::Model*>(model);
+        for (int i = 0; i < warmup; ++i) (void)m->forward(in);
+        cudaEvent_t a = nullptr, b = nullptr;
+        if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) throw std::runtime_error("cudaEventCreate failed");
+        cudaDeviceSynchronize();
+        cudaEventRecord(a, nullptr);
+        for (int i = 0; i < iters; ++i) (void)m->forward(in);
+        cudaEventRecord(b, nullptr);
+        if (cudaEventSynchronize(b) != cudaSuccess) throw std::runtime_error("the reference's forward failed on the device");
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, a, b);
+        cudaEventDestroy(a);
+        cudaEventDestroy(b);
+        *msPerPass = static_cast<double>(ms) / (iters > 0 ? iters : 1);
     });
 }
 

@@ -302,6 +302,13 @@ class CudaModel:
         _cuda_check(cuda_lib().refCudaModelForward(self._m, *packed))
         return _cuda_result()
 
+    def forward_timed(self, x, warmup: int = 1, iters: int = 3) -> float:
+        """Device milliseconds per forward pass (CUDA events; input uploaded once, results left on the device)."""
+        a, packed = _t(x)
+        ms = C.c_double(0.0)
+        _cuda_check(cuda_lib().refCudaModelForwardTimed(self._m, *packed, C.c_int(warmup), C.c_int(iters), C.byref(ms)))
+        return ms.value
+
 
 def cuda_fused_attention(q, k, v, num_heads: int, scale: float, old_len: int = 0) -> np.ndarray:
     """fusedAttentionForward of the reference on fp32 q [batch, newLen, dim], k / v [batch, totalLen, dim]."""
