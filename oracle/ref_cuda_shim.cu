@@ -138,6 +138,18 @@ int refCudaModelForward(void* model, const float* data, const int64_t* shape, in
     });
 }
 
+// Generation with the reference's key/value caches: `data` holds only the new token ids.
+int refCudaModelForwardIncremental(void* model, const float* data, const int64_t* shape, int rank) {
+    return guarded([&] {
+        cuda::DeviceTensor in = cuda::DeviceTensor::fromHost(hostTensor(data, shape, rank));
+        gOut = static_cast<cuda::Model*>(model)->forwardIncremental(in).toHost();
+    });
+}
+
+int refCudaModelResetGeneration(void* model) {
+    return guarded([&] { static_cast<cuda::Model*>(model)->resetGenerationState(); });
+}
+
 // Device time of `iters` forward passes (CUDA events around them, input uploaded once, results dropped on the
 // device), after `warmup` untimed ones: the reference's own GPU path as a timing baseline.
 int refCudaModelForwardTimed(void* model, const float* data, const int64_t* shape, int rank, int warmup, int iters,

@@ -302,6 +302,14 @@ class CudaModel:
         _cuda_check(cuda_lib().refCudaModelForward(self._m, *packed))
         return _cuda_result()
 
+    def forward_incremental(self, new_ids) -> np.ndarray:
+        a, packed = _t(new_ids)
+        _cuda_check(cuda_lib().refCudaModelForwardIncremental(self._m, *packed))
+        return _cuda_result()
+
+    def reset_generation(self):
+        _cuda_check(cuda_lib().refCudaModelResetGeneration(self._m))
+
     def forward_timed(self, x, warmup: int = 1, iters: int = 3) -> float:
         """Device milliseconds per forward pass (CUDA events; input uploaded once, results left on the device)."""
         a, packed = _t(x)

@@ -89,3 +89,30 @@ def test_attention_against_the_reference_fused_kernel(gpu, refcuda, old_len):
     assert int(d_status.to_numpy(np.int32, (1,))[0]) == 0
     print("attention vs reference fused kernel: max abs diff", float(np.max(np.abs(got - want))))
     assert float(np.max(np.abs(got - want))) <= 1.2e-2
+
+
+@pytest.mark.parametrize("precision", [None, {"storage": "fp32", "compute": "bf16", "accumulate": "fp32"}])
+def test_generation_steps_against_the_reference_key_value_cache(gpu, refcuda, precision):
+    """Model::forwardIncremental here (in-place caches, one-query attention, few-rows GEMMs on the bf16 route) against
+    the reference's own cuda::Model::forwardIncremental: a prompt, then single-token steps, same weights and ids."""
+    cfg = dict(vocab=512, dim=256, layers=2, heads=2, hidden=512, max_seq=96)
+    ops = O.lm_ops(**cfg)
+    params = O.synth_params(ops, None, seed=51, sigma=0.05, bias_sigma=0.05)
+    ids = O.synth_token_ids(3, 70, cfg["vocab"], seed=52)
+    theirs = refcuda.CudaModel(O.lm_source(seq=96, **cfg), seed=1, precision=precision)
+    for i, n in enumerate(theirs.param_names()):
+        theirs.set_param(i, params[n])
+    ours = gpu.Model(ops, precision=None if precision is None else {"storage": "fp32", "compute": "bf16"}, random_init=False)
+    ours.set_params(params)
+    theirs.reset_generation()
+    ours.reset_generation()
+    bar = 1e-3 if precision is None else 2e-2
+    worst = 0.0
+    for lo, hi in ((0, 64), (64, 65), (65, 66), (66, 70)):
+        want = theirs.forward_incremental(ids[:, lo:hi])
+        got = ours.forward_incremental(ids[:, lo:hi])
+        assert got.shape == want.shape
+        worst = max(worst, float(np.max(np.abs(got - want))) / float(np.max(np.abs(want))))
+    print("generation vs reference key/value cache: worst max abs diff / max abs =", worst)
+    assert worst <= bar
+    theirs.close()
