@@ -173,6 +173,37 @@ int refCudaModelForwardTimed(void* model, const float* data, const int64_t* shap
     });
 }
 
+// Device time per generation step: the caches are reset, the prompt [batch, context] goes through forwardIncremental
+// untimed, then `steps` single-token calls (columns of `stepIds` [batch, steps]) are timed with CUDA events.
+int refCudaModelGenerationTimed(void* model, const float* prompt, int64_t batch, int64_t context, const float* stepIds,
+                                int64_t steps, double* msPerStep) {
+    return guarded([&] {
+        auto* m = static_cast<cuda::Model*>(model);
+        m->resetGenerationState();
+        const int64_t promptShape[2] = {batch, context};
+        (void)m->forwardIncremental(cuda::DeviceTensor::fromHost(hostTensor(prompt, promptShape, 2)));
+        std::vector<cuda::DeviceTensor> columns;
+        for (int64_t s = 0; s < steps; ++s) {
+            std::vector<float> col(static_cast<std::size_t>(batch));
+            for (int64_t b = 0; b < batch; ++b) col[static_cast<std::size_t>(b)] = stepIds[b * steps + s];
+            const int64_t shape[2] = {batch, 1};
+            columns.push_back(cuda::DeviceTensor::fromHost(hostTensor(col.data(), shape, 2)));
+        }
+        cudaEvent_t a = nullptr, b = nullptr;
+        if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) throw std::runtime_error("cudaEventCreate failed");
+        cudaDeviceSynchronize();
+        cudaEventRecord(a, nullptr);
+        for (int64_t s = 0; s < steps; ++s) (void)m->forwardIncremental(columns[static_cast<std::size_t>(s)]);
+        cudaEventRecord(b, nullptr);
+        if (cudaEventSynchronize(b) != cudaSuccess) throw std::runtime_error("the reference's generation step failed on the device");
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, a, b);
+        cudaEventDestroy(a);
+        cudaEventDestroy(b);
+        *msPerStep = static_cast<double>(ms) / static_cast<double>(steps > 0 ? steps : 1);
+    });
+}
+
 // fusedAttentionForward on fp32 q [batch, newLen, dim], k / v [batch, totalLen, dim]; the output lands in the result slot.
 int refCudaFusedAttention(const float* q, const int64_t* qShape, const float* k, const int64_t* kShape, const float* v,
                           int64_t numHeads, float scale, int64_t oldLen) {

@@ -310,6 +310,16 @@ class CudaModel:
     def reset_generation(self):
         _cuda_check(cuda_lib().refCudaModelResetGeneration(self._m))
 
+    def generation_timed(self, prompt, step_ids) -> float:
+        """Device milliseconds per single-token step after the prompt (CUDA events)."""
+        p = np.ascontiguousarray(prompt, dtype=np.float32)
+        s = np.ascontiguousarray(step_ids, dtype=np.float32)
+        ms = C.c_double(0.0)
+        _cuda_check(cuda_lib().refCudaModelGenerationTimed(
+            self._m, p.ctypes.data_as(C.c_void_p), C.c_int64(p.shape[0]), C.c_int64(p.shape[1]),
+            s.ctypes.data_as(C.c_void_p), C.c_int64(s.shape[1]), C.byref(ms)))
+        return ms.value
+
     def forward_timed(self, x, warmup: int = 1, iters: int = 3) -> float:
         """Device milliseconds per forward pass (CUDA events; input uploaded once, results left on the device)."""
         a, packed = _t(x)
