@@ -217,4 +217,30 @@ int refCudaFusedAttention(const float* q, const int64_t* qShape, const float* k,
     });
 }
 
+// The same call timed on the device (CUDA events, operands uploaded once, `iters` calls after one warm-up); the last
+// output lands in the result slot.
+int refCudaFusedAttentionTimed(const float* q, const int64_t* qShape, const float* k, const int64_t* kShape,
+                               const float* v, int64_t numHeads, float scale, int64_t oldLen, int iters, double* msPerCall) {
+    return guarded([&] {
+        cuda::DeviceTensor dq = cuda::DeviceTensor::fromHost(hostTensor(q, qShape, 3));
+        cuda::DeviceTensor dk = cuda::DeviceTensor::fromHost(hostTensor(k, kShape, 3));
+        cuda::DeviceTensor dv = cuda::DeviceTensor::fromHost(hostTensor(v, kShape, 3));
+        const std::size_t heads = static_cast<std::size_t>(numHeads), old = static_cast<std::size_t>(oldLen);
+        cuda::FusedAttentionForwardResult r = cuda::fusedAttentionForward(dq, dk, dv, heads, scale, old);
+        cudaEvent_t a = nullptr, b = nullptr;
+        if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) throw std::runtime_error("cudaEventCreate failed");
+        cudaDeviceSynchronize();
+        cudaEventRecord(a, nullptr);
+        for (int i = 0; i < iters; ++i) r = cuda::fusedAttentionForward(dq, dk, dv, heads, scale, old);
+        cudaEventRecord(b, nullptr);
+        if (cudaEventSynchronize(b) != cudaSuccess) throw std::runtime_error("the reference's attention kernel failed on the device");
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, a, b);
+        cudaEventDestroy(a);
+        cudaEventDestroy(b);
+        *msPerCall = static_cast<double>(ms) / (iters > 0 ? iters : 1);
+        gOut = r.output.toHost();
+    });
+}
+
 }  // extern "C"

@@ -336,3 +336,14 @@ def cuda_fused_attention(q, k, v, num_heads: int, scale: float, old_len: int = 0
                                                  va.ctypes.data_as(C.c_void_p), C.c_int64(num_heads), C.c_float(scale),
                                                  C.c_int64(old_len)))
     return _cuda_result()
+
+
+def cuda_fused_attention_timed(q, k, v, num_heads: int, scale: float, old_len: int = 0, iters: int = 3):
+    """(output, device milliseconds per call) of the reference's fusedAttentionForward."""
+    qa, ka, va = (np.ascontiguousarray(t, dtype=np.float32) for t in (q, k, v))
+    qs, ks = (C.c_int64 * 3)(*qa.shape), (C.c_int64 * 3)(*ka.shape)
+    ms = C.c_double(0.0)
+    _cuda_check(cuda_lib().refCudaFusedAttentionTimed(
+        qa.ctypes.data_as(C.c_void_p), qs, ka.ctypes.data_as(C.c_void_p), ks, va.ctypes.data_as(C.c_void_p),
+        C.c_int64(num_heads), C.c_float(scale), C.c_int64(old_len), C.c_int(iters), C.byref(ms)))
+    return _cuda_result(), ms.value

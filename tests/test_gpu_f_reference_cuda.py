@@ -116,3 +116,38 @@ def test_generation_steps_against_the_reference_key_value_cache(gpu, refcuda, pr
     print("generation vs reference key/value cache: worst max abs diff / max abs =", worst)
     assert worst <= bar
     theirs.close()
+
+
+def test_attention_configuration_2_in_full_against_the_reference_kernel(gpu, refcuda):
+    """Configuration 2 at its full size (batch 16, 16 heads of 128, sequence 2048, causal): every output element of
+    the tcgen05 kernel against the reference's fused kernel on the same bf16-valued inputs, and both device times."""
+    rng = np.random.default_rng(2)
+    batch, heads, seq = 16, 16, 2048
+    dim = heads * 128
+    q, k, v = (O.round_bf16(rng.standard_normal((batch, seq, dim), dtype=np.float32)) for _ in range(3))
+    scale = float(128 ** -0.5)
+    want, ref_ms = refcuda.cuda_fused_attention_timed(q, k, v, heads, scale, 0, iters=2)
+    d_q, d_k, d_v = (gpu.upload(t, gpu.BF16) for t in (q, k, v))
+    d_o = gpu.DeviceBuffer(batch * seq * dim * 2)
+    d_status = gpu.DeviceBuffer.zeros(4)
+
+    def run():
+        gpu.check(gpu.lib().bfb_attention_fwd(d_q.ptr, d_k.ptr, d_v.ptr, d_o.ptr, None, None, gpu.BF16, batch, seq, seq, heads,
+                                              128, dim, dim, dim, dim, scale, 0, 1, d_status.ptr, None))
+    import torch
+    run()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(5):
+        run()
+    b.record()
+    torch.cuda.synchronize()
+    our_ms = a.elapsed_time(b) / 5
+    got = gpu.download(d_o, gpu.BF16, (batch, seq, dim))
+    assert int(d_status.to_numpy(np.int32, (1,))[0]) == 0
+    err = float(np.max(np.abs(got - want)))
+    flops = 4.0 * 128 * batch * heads * seq * (seq + 1) / 2.0
+    print(f"configuration 2 vs reference fused kernel: max abs diff {err:.3e}; reference {ref_ms:.2f} ms "
+          f"({flops / ref_ms / 1e9:.1f} TFLOP/s causal), this kernel {our_ms:.3f} ms ({flops / our_ms / 1e9:.1f} TFLOP/s)")
+    assert err <= 1.2e-2
