@@ -26,10 +26,15 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <type_traits>
 
 #include "common.cuh"
 #include "kernels.hpp"
 #include "ptx_sm100.cuh"
+
+#ifndef BFB_ATT_V
+#define BFB_ATT_V 0
+#endif
 
 namespace bfb {
 
@@ -41,14 +46,22 @@ constexpr int kBN = 128;                    // keys per tile
 constexpr int kItemRows = 2 * kBM;
 constexpr int kHalfBytes = 128 * 128;       // one 64-wide half of a 128-row tile
 constexpr int kTileBytes = 2 * kHalfBytes;  // 32 KiB
-constexpr int kKvSlots = 3;
-constexpr int kQOff = 0;                    // [2 buffers][2 sides] Q tiles
-constexpr int kKvOff = 4 * kTileBytes;
-constexpr int kBarOff = kKvOff + kKvSlots * kTileBytes;
+constexpr int kKvSlots = 4;
+constexpr int kQOff = 0;                    // [2 sides] Q tiles of the current item
+constexpr int kKvOff = 2 * kTileBytes;
+constexpr int kStageBytes = 32 * 128;            // one softmax warp's 32 rows x 64 output values (bf16), swizzled
+constexpr int kStageOff = kKvOff + kKvSlots * kTileBytes;   // [8 softmax warps]
+constexpr int kBarOff = kStageOff + 8 * kStageBytes;
 constexpr int kSmemBytes = kBarOff + 256;
-constexpr int kSoftmaxWarps = 8;
+#if (BFB_ATT_V & 16)
+constexpr int kFirstSoftmaxWarp = 4;        // warps 0-3: MMA issuer, TMA producer, two idle; warps 4-11 softmax
+constexpr int kProducerWarp = 1;
+constexpr int kMmaWarp = 0;
+#else
+constexpr int kFirstSoftmaxWarp = 0;
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
+#endif
 constexpr int kThreads = 384;
 constexpr int kSoftmaxRegs = 232;           // 384 threads start with 168 registers each; the last warpgroup gives
 constexpr int kOtherRegs = 40;              // 128 * (168 - 40), the two softmax warpgroups take 2 * 128 * (232 - 168)
@@ -61,6 +74,76 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+
+// experiment switches
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_x(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+#if (BFB_ATT_V & 2)
+    if (mbar_try_wait_hint(bar, parity, 2000)) return true;
+    uint64_t start = global_timer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait_hint(bar, parity, 2000)) return true;
+        if ((++spins & 15u) == 0u) {
+            if (*abort_flag != 0) return false;
+            if (global_timer_ns() - start > kWaitLimitNs) {
+                *abort_flag = 1;
+                if (status != nullptr) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+#else
+    return mbar_wait(bar, parity, abort_flag, status, code);
+#endif
+}
+// wait executed by the whole warp (default) or by one lane whose result is broadcast
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+#if (BFB_ATT_V & 1)
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait_x(bar, parity, abort_flag, status, code);
+    return __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
+#else
+    return warp_all(mbar_wait_x(bar, parity, abort_flag, status, code));
+#endif
+}
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+#if (BFB_ATT_V & 4)
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+#else
+    return fmaxf(fmaxf(a, b), c);
+#endif
+}
+
+// A role runs either on a whole (converged) warp that elects a lane for each single-thread instruction, or on one
+// elected thread for the entire role.
+#if (BFB_ATT_V & 32)
+#define ROLE_OPEN if (elect_one()) {
+#define ROLE_CLOSE } __syncwarp();
+#define ROLE_WAIT mbar_wait_x
+#define ROLE_ELECT true
+#define ROLE_SYNCWARP() do {} while (0)
+#else
+#define ROLE_OPEN {
+#define ROLE_CLOSE }
+#define ROLE_WAIT warp_wait
+#define ROLE_ELECT elect_one()
+#define ROLE_SYNCWARP() __syncwarp()
+#endif
 
 struct AttnParams {
     __nv_bfloat16* out;
@@ -124,18 +207,19 @@ __device__ __forceinline__ int itemAt(uint32_t k) {
 
 __global__ void __launch_bounds__(kThreads, 1)
 attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_constant__ CUtensorMap tmapK,
-                  const __grid_constant__ CUtensorMap tmapV, AttnParams p, int* status) {
+                  const __grid_constant__ CUtensorMap tmapV, const __grid_constant__ CUtensorMap tmapO, AttnParams p,
+                  int* status) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOff);
-    uint64_t* qFull = bars;            // [2 buffers]
-    uint64_t* qEmpty = bars + 2;       // [2]
-    uint64_t* kvFull = bars + 4;       // [3 slots]
-    uint64_t* kvEmpty = bars + 7;      // [3]
-    uint64_t* sFull = bars + 10;       // [2 sides]
-    uint64_t* pFull = bars + 12;       // [2]
-    uint64_t* oFull = bars + 14;       // [2]
-    uint64_t* oFree = bars + 16;       // [2]
-    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 18);
+    uint64_t* qFull = bars;            // [1]
+    uint64_t* qEmpty = bars + 1;       // [1]
+    uint64_t* kvFull = bars + 2;       // [kKvSlots]
+    uint64_t* kvEmpty = bars + 2 + kKvSlots;
+    uint64_t* sFull = bars + 2 + 2 * kKvSlots;   // [2 sides]
+    uint64_t* pFull = sFull + 2;       // [2]
+    uint64_t* oFull = sFull + 4;       // [2]
+    uint64_t* oFree = sFull + 6;       // [2]
+    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(sFull + 8);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
     // The swizzled tiles need a 1024-byte aligned base; refuse to run otherwise (uniform across the CTA).
@@ -148,9 +232,9 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
     const int lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
+        mbar_init(&qFull[0], 1);
+        mbar_init(&qEmpty[0], 1);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&qFull[i], 1);
-            mbar_init(&qEmpty[i], 1);
             mbar_init(&sFull[i], 1);
             mbar_init(&pFull[i], 4);   // one arrival per softmax warp of the side
             mbar_init(&oFull[i], 1);
@@ -165,6 +249,7 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
         tma_prefetch_desc(&tmapQ);
         tma_prefetch_desc(&tmapK);
         tma_prefetch_desc(&tmapV);
+        tma_prefetch_desc(&tmapO);
     }
     if (warp == kMmaWarp) {
         tmem_alloc(tmemSlot, 512);
@@ -178,31 +263,33 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
     if (warp == kProducerWarp) {
         // ---------------- TMA producer: runs ahead across items ----------------
         setmaxnreg_dec<kOtherRegs>();
+        ROLE_OPEN
         uint32_t it = 0;     // items taken by this CTA so far
         uint32_t idx = 0;    // K/V tiles loaded so far (K of an item's key tile j, then its V)
         bool alive = true;
         for (int item = itemAt(0); item < p.totalItems && alive; item = itemAt(++it)) {
             const Item w = decodeItem(p, item);
-            const int qb = it & 1u;
-            if (!warp_all(mbar_wait(&qEmpty[qb], ((it >> 1) & 1u) ^ 1u, abortFlag, status, kDevTimeoutStageEmpty))) break;
-            if (lane == 0) {
-                uint8_t* dst = smem + kQOff + qb * 2 * kTileBytes;
+            // Q of the item: its buffer is free once the previous item's last scores have been computed, which is a
+            // whole key tile before this item's first scores are issued
+            if (!(ROLE_WAIT(&qEmpty[0], (it & 1u) ^ 1u, abortFlag, status, kDevTimeoutStageEmpty))) break;
+            if (ROLE_ELECT) {
+                uint8_t* dst = smem + kQOff;
                 const int sides = w.nKv[1] > 0 ? 2 : 1;
-                mbar_arrive_expect_tx(&qFull[qb], sides * kTileBytes);
+                mbar_arrive_expect_tx(&qFull[0], sides * kTileBytes);
                 for (int s = 0; s < sides; ++s) {
-                    tma_load_3d(dst + s * kTileBytes, &tmapQ, &qFull[qb], w.h * kD, w.q0 + s * kBM, w.b);
-                    tma_load_3d(dst + s * kTileBytes + kHalfBytes, &tmapQ, &qFull[qb], w.h * kD + 64, w.q0 + s * kBM, w.b);
+                    tma_load_3d(dst + s * kTileBytes, &tmapQ, &qFull[0], w.h * kD, w.q0 + s * kBM, w.b);
+                    tma_load_3d(dst + s * kTileBytes + kHalfBytes, &tmapQ, &qFull[0], w.h * kD + 64, w.q0 + s * kBM, w.b);
                 }
             }
-            __syncwarp();
+            ROLE_SYNCWARP();
             for (int t = 0; t < 2 * w.n; ++t, ++idx) {
                 const int slot = idx % kKvSlots;
                 const uint32_t use = idx / kKvSlots;
-                if (!warp_all(mbar_wait(&kvEmpty[slot], (use & 1u) ^ 1u, abortFlag, status, kDevTimeoutStageEmpty))) {
+                if (!(ROLE_WAIT(&kvEmpty[slot], (use & 1u) ^ 1u, abortFlag, status, kDevTimeoutStageEmpty))) {
                     alive = false;
                     break;
                 }
-                if (lane == 0) {
+                if (ROLE_ELECT) {
                     const int j = t >> 1;
                     const CUtensorMap* map = (t & 1) ? &tmapV : &tmapK;
                     uint8_t* dst = smem + kKvOff + slot * kTileBytes;
@@ -210,70 +297,79 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                     tma_load_3d(dst, map, &kvFull[slot], w.h * kD, j * kBN, w.b);
                     tma_load_3d(dst + kHalfBytes, map, &kvFull[slot], w.h * kD + 64, j * kBN, w.b);
                 }
-                __syncwarp();
+                ROLE_SYNCWARP();
             }
         }
+        ROLE_CLOSE
     } else if (warp == kMmaWarp) {
-        // ---------------- MMA issuer ----------------
+        // ---------------- MMA issuer (one elected thread) ----------------
+        // A thread can run about six tcgen05.mma ahead of the tensor pipe, no further: whatever it does between
+        // two batches beyond that is time the pipe stands still. So everything that is normally long complete (the
+        // K/V tiles, the next item's Q) is checked BEFORE the wait for the probabilities, which is the one wait that
+        // really takes time, and a batch of P V is followed by the next scores of the same side without a wait in
+        // between. Completion is signalled once per side and key tile (sFull, after the scores, which also covers
+        // the P V before them); oFull only after an item's last P V.
         setmaxnreg_dec<kOtherRegs>();
-        const uint32_t kvAddr = smem_u32(smem + kKvOff);
-        uint32_t tilesDone[2] = {0u, 0u};   // P V products issued per side (phase of pFull / oFull)
+        ROLE_OPEN
+        const uint32_t kvLoBase = smem_desc_lo(smem_u32(smem + kKvOff), 0);
+        const uint32_t qLoBase = smem_desc_lo(smem_u32(smem + kQOff), 0);
+        constexpr uint32_t kHi = smem_desc_hi_sw128(1024);
+        uint32_t tilesDone[2] = {0u, 0u};   // P V products issued per side (phase of pFull)
         uint32_t itemsDone[2] = {0u, 0u};   // items whose output the side's softmax warps have taken (phase of oFree)
 
         auto waitKv = [&](uint32_t idx) -> bool {
-            return warp_all(mbar_wait(&kvFull[idx % kKvSlots], (idx / kKvSlots) & 1u, abortFlag, status, kDevTimeoutTmaFull));
+            return (ROLE_WAIT(&kvFull[idx % kKvSlots], (idx / kKvSlots) & 1u, abortFlag, status, kDevTimeoutTmaFull));
         };
         // S_side = Q_side K^T for the key tile in ring entry kIdx
-        auto issueQK = [&](int side, uint32_t itemNo, uint32_t kIdx) {
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t qAddr = smem_u32(smem + kQOff + ((itemNo & 1u) * 2 + side) * kTileBytes);
-                const uint32_t kAddr = kvAddr + (kIdx % kKvSlots) * kTileBytes;
+        auto issueQK = [&](int side, uint32_t kIdx) {
+            if (ROLE_ELECT) {
+                const uint32_t qLo = qLoBase + side * (kTileBytes >> 4);
+                const uint32_t kLo = kvLoBase + (kIdx % kKvSlots) * (kTileBytes >> 4);
                 const uint32_t dS = tmemBase + static_cast<uint32_t>(side * kBN);
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-                    umma_f16(dS, make_smem_desc_sw128(qAddr + off, 0, 1024), make_smem_desc_sw128(kAddr + off, 0, 1024),
-                             kIdescQK, kk > 0 ? 1u : 0u);
+                    const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
+                    umma_f16_words(dS, qLo + off, kHi, kLo + off, kHi, kIdescQK, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(&sFull[side]);
             }
-            __syncwarp();
+            ROLE_SYNCWARP();
         };
-        // O_side (+)= P_side V for the key tile whose V is ring entry vIdx; `first` starts a new item's sum
-        auto issuePV = [&](int side, uint32_t vIdx, bool first) -> bool {
-            if (!warp_all(mbar_wait(&pFull[side], tilesDone[side] & 1u, abortFlag, status, kDevTimeoutSoftmax))) return false;
+        // O_side (+)= P_side V for the key tile whose V is ring entry vIdx; `first` starts a new item's sum, `last`
+        // ends it
+        auto issuePV = [&](int side, uint32_t vIdx, bool first, bool last) -> bool {
+            if (!(ROLE_WAIT(&pFull[side], tilesDone[side] & 1u, abortFlag, status, kDevTimeoutSoftmax))) return false;
             if (first) {
                 // the previous item's output must have left tensor memory
-                if (!warp_all(mbar_wait(&oFree[side], (itemsDone[side] & 1u) ^ 1u, abortFlag, status, kDevTimeoutAccEmpty)))
+                if (!(ROLE_WAIT(&oFree[side], (itemsDone[side] & 1u) ^ 1u, abortFlag, status, kDevTimeoutAccEmpty)))
                     return false;
                 ++itemsDone[side];
             }
             tc_fence_after();
-            if (lane == 0) {
-                const uint32_t vAddr = kvAddr + (vIdx % kKvSlots) * kTileBytes;
-                const uint32_t pTmem = tmemBase + static_cast<uint32_t>(side * kBN);  // P sits where S was
+            if (ROLE_ELECT) {
+                // P from tensor memory (it sits where S was): 16 keys = 8 packed columns per step. V: keys are rows
+                // (MN-major B): 8-key groups 1024 B apart, the two 64-wide halves of head_dim one half-tile apart.
+                const uint32_t pTmem = tmemBase + static_cast<uint32_t>(side * kBN);
                 const uint32_t dO = tmemBase + 256u + static_cast<uint32_t>(side * kD);
+                const uint32_t vLo = kvLoBase + (vIdx % kKvSlots) * (kTileBytes >> 4) + ((kHalfBytes >> 4) << 16);
+                const uint32_t accFirst = first ? 0u : 1u;
 #pragma unroll
                 for (int kk = 0; kk < kBN / 16; ++kk) {
-                    // P from tensor memory: 16 keys = 8 packed columns per step. V: keys are rows (MN-major B):
-                    // 8-key groups 1024 B apart, the two 64-wide halves of head_dim one half-tile apart.
-                    umma_f16_ts(dO, pTmem + static_cast<uint32_t>(kk * 8),
-                                make_smem_desc_sw128(vAddr + kk * 2048, kHalfBytes, 1024), kIdescPV,
-                                (kk > 0 || !first) ? 1u : 0u);
+                    umma_f16_ts_words(dO, pTmem + static_cast<uint32_t>(kk * 8), vLo + kk * (2048 >> 4), kHi, kIdescPV,
+                                      kk > 0 ? 1u : accFirst);
                 }
-                umma_commit(&oFull[side]);
+                if (last) umma_commit(&oFull[side]);
             }
-            __syncwarp();
+            ROLE_SYNCWARP();
             ++tilesDone[side];
             return true;
         };
         auto waitQ = [&](uint32_t itemNo) -> bool {
-            return warp_all(mbar_wait(&qFull[itemNo & 1u], (itemNo >> 1) & 1u, abortFlag, status, kDevTimeoutTmaFull));
+            return (ROLE_WAIT(&qFull[0], itemNo & 1u, abortFlag, status, kDevTimeoutTmaFull));
         };
         auto commitTo = [&](uint64_t* bar) {
-            if (lane == 0) umma_commit(bar);
-            __syncwarp();
+            if (ROLE_ELECT) umma_commit(bar);
+            ROLE_SYNCWARP();
         };
 
         int item = itemAt(0);
@@ -283,8 +379,9 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
             Item w = decodeItem(p, item);
             bool alive = waitQ(0) && waitKv(0);
             if (alive) {
-                issueQK(0, 0, 0);
-                if (w.nKv[1] > 0) issueQK(1, 0, 0);
+                tc_fence_after();
+                issueQK(0, 0);
+                if (w.nKv[1] > 0) issueQK(1, 0);
                 commitTo(&kvEmpty[0]);
                 if (w.n == 1) commitTo(&qEmpty[0]);
             }
@@ -305,26 +402,21 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                     const uint32_t kItemNo = inItem ? it : it + 1;
                     const Item& kw = inItem ? w : nw;
                     const int kj = inItem ? j + 1 : 0;
-                    bool kReady = false;
+                    // operands first: V of this key tile, K (and Q) of the next scores
                     if (!waitKv(vIdx)) { alive = false; break; }
+                    if (haveNext && ((!inItem && !waitQ(kItemNo)) || !waitKv(kIdx))) { alive = false; break; }
 #pragma unroll
                     for (int side = 0; side < 2; ++side) {
                         if (j < w.nKv[side]) {
-                            if (!issuePV(side, vIdx, j == 0)) { alive = false; break; }
+                            if (!issuePV(side, vIdx, j == 0, j == w.nKv[side] - 1)) { alive = false; break; }
                         }
-                        if (haveNext && kj < kw.nKv[side]) {
-                            if (!kReady) {
-                                if ((!inItem && !waitQ(kItemNo)) || !waitKv(kIdx)) { alive = false; break; }
-                                kReady = true;
-                            }
-                            issueQK(side, kItemNo, kIdx);
-                        }
+                        if (haveNext && kj < kw.nKv[side]) issueQK(side, kIdx);
                     }
                     if (!alive) break;
                     commitTo(&kvEmpty[vIdx % kKvSlots]);
                     if (haveNext) {
                         commitTo(&kvEmpty[kIdx % kKvSlots]);
-                        if (kj == kw.n - 1) commitTo(&qEmpty[kItemNo & 1u]);   // those were the item's last scores
+                        if (kj == kw.n - 1) commitTo(&qEmpty[0]);   // those were the item's last scores
                     }
                 }
                 if (!alive || !haveNextItem) break;
@@ -334,15 +426,17 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                 ++it;
             }
         }
-    } else if (warp < kSoftmaxWarps) {
+        ROLE_CLOSE
+    } else if (warp >= kFirstSoftmaxWarp && warp < kFirstSoftmaxWarp + 8) {
         // ---------------- softmax: one thread per query row ----------------
         setmaxnreg_inc<kSoftmaxRegs>();
-        const int side = warp >> 2;
+        const int side = (warp - kFirstSoftmaxWarp) >> 2;
         const int r = (warp & 3) * 32 + lane;       // query row inside the side's tile
         const uint32_t laneBase = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t sAddr = tmemBase + laneBase + static_cast<uint32_t>(side * kBN);
         const uint32_t oAddr = tmemBase + laneBase + 256u + static_cast<uint32_t>(side * kD);
-        uint32_t tiles = 0;                         // key tiles this side has processed (phase of sFull / oFull)
+        uint32_t tiles = 0;                         // key tiles this side has processed (phase of sFull)
+        uint32_t sideItems = 0;                     // items this side has finished (phase of oFull)
         bool alive = true;
 
         for (uint32_t it = 0; alive; ++it) {
@@ -360,7 +454,7 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
             float lRun = 0.0f;         // row sum relative to mRef
 
             for (int j = 0; j < nKv; ++j, ++tiles) {
-                if (!warp_all(mbar_wait(&sFull[side], tiles & 1u, abortFlag, status, kDevTimeoutAccFull))) {
+                if (!(warp_wait(&sFull[side], tiles & 1u, abortFlag, status, kDevTimeoutAccFull))) {
                     alive = false;
                     break;
                 }
@@ -377,32 +471,73 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                         for (int i = 0; i < 32; ++i)
                             if (j * kBN + c * 32 + i > keyLimit) s[c][i] = 0xFF800000u;  // -inf
                 }
-                // four independent chains instead of one long dependency
+                // Exponentials of the tile against the reference `ref` (log2 units), written over S as bf16 pairs (two
+                // keys per 32-bit column: the 32 keys of chunk c take 16 columns, the tile the first 64 columns of the S
+                // region); returns the row sum. With kTrackMax it also takes the maximum of the raw scores on the way,
+                // which costs nothing next to the exponentials (other pipe). Packed fp32 pairs: one FMA / ADD instruction
+                // serves two scores. Masked entries hold -inf: ex2(-inf) = 0.
                 float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+                auto expPass = [&](float ref, auto trackMax) -> float {
+                    constexpr bool kTrackMax = decltype(trackMax)::value;
+                    const uint64_t scale2 = pack_f32x2(p.scaleLog2, p.scaleLog2);
+                    const uint64_t negRef2 = pack_f32x2(-ref, -ref);
+                    uint64_t sumA = pack_f32x2(0.0f, 0.0f), sumB = sumA;
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t packed[16];
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        m0 = fmaxf(m0, __uint_as_float(s[c][i]));
-                        m1 = fmaxf(m1, __uint_as_float(s[c][i + 1]));
-                        m2 = fmaxf(m2, __uint_as_float(s[c][i + 2]));
-                        m3 = fmaxf(m3, __uint_as_float(s[c][i + 3]));
+                        for (int i = 0; i < 32; i += 2) {
+                            const float s0 = __uint_as_float(s[c][i]), s1 = __uint_as_float(s[c][i + 1]);
+                            if (kTrackMax) {
+                                if ((i & 6) == 0) m0 = max3f(m0, s0, s1);
+                                else if ((i & 6) == 2) m1 = max3f(m1, s0, s1);
+                                else if ((i & 6) == 4) m2 = max3f(m2, s0, s1);
+                                else m3 = max3f(m3, s0, s1);
+                            }
+                            const uint64_t arg = fma_f32x2(pack_f32x2(s0, s1), scale2, negRef2);
+                            float a0, a1;
+                            unpack_f32x2(arg, a0, a1);
+                            const float p0 = ex2(a0);
+                            const float p1 = ex2(a1);
+                            if ((i & 2) == 0) sumA = add_f32x2(sumA, pack_f32x2(p0, p1));
+                            else sumB = add_f32x2(sumB, pack_f32x2(p0, p1));
+                            __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+                            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+                        }
+                        tmem_st_32x16(sAddr + static_cast<uint32_t>(c * 16), packed);
                     }
-                const float mTile = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * p.scaleLog2;
-                mTrue = fmaxf(mTrue, mTile);
-
+                    float sumLo, sumHi;
+                    unpack_f32x2(add_f32x2(sumA, sumB), sumLo, sumHi);
+                    return sumLo + sumHi;
+                };
+                float tileSum;
                 if (j == 0) {
-                    mRef = mTile;
+                    // first key tile of the item: the reference is the tile's own maximum (four independent chains)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            m0 = max3f(m0, __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+                            m1 = max3f(m1, __uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3]));
+                            m2 = max3f(m2, __uint_as_float(s[c][i + 4]), __uint_as_float(s[c][i + 5]));
+                            m3 = max3f(m3, __uint_as_float(s[c][i + 6]), __uint_as_float(s[c][i + 7]));
+                        }
+                    mRef = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * p.scaleLog2;
+                    mTrue = mRef;
+                    // a row with no visible key yet keeps everything at zero instead of producing NaN
+                    tileSum = expPass((mRef == -INFINITY) ? 0.0f : mRef, std::false_type{});
                 } else {
+                    // Later tiles exponentiate against the reference they inherit and find their maximum on the way.
+                    // The reference may trail the true maximum by kRescaleSlack, so the probabilities stay below
+                    // 2^kRescaleSlack; only when a row's maximum has grown by more than that is the tile done again.
+                    tileSum = expPass((mRef == -INFINITY) ? 0.0f : mRef, std::true_type{});
+                    const float mTile = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * p.scaleLog2;
+                    mTrue = fmaxf(mTrue, mTile);
                     const bool moved = mTile > mRef + kRescaleSlack;
                     if (__any_sync(0xFFFFFFFFu, moved)) {
-                        // Rare: bring O and the row sum to the new reference. The previous tile's P V must have
-                        // finished; the next one is issued only after this warp reports P below.
-                        if (!warp_all(mbar_wait(&oFull[side], (tiles - 1u) & 1u, abortFlag, status, kDevTimeoutAccFull))) {
-                            alive = false;
-                            break;
-                        }
-                        tc_fence_after();
+                        // Rare: bring O and the row sum to the new reference. The previous tile's P V has finished:
+                        // these scores were issued after it by the same thread, and sFull reports everything that
+                        // thread had issued. The next P V is issued only after this warp reports P below.
                         const float alpha = moved ? ex2(mRef - mTile) : 1.0f;   // 0 when there was no visible key yet
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
@@ -418,77 +553,63 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                             tmem_st_32x16(oAddr + static_cast<uint32_t>(c * 32), lo);
                             tmem_st_32x16(oAddr + static_cast<uint32_t>(c * 32 + 16), hi);
                         }
-                        tmem_st_wait();
                         lRun *= alpha;
                         if (moved) mRef = mTile;
+                        // every lane takes part (the stores to tensor memory are warp-wide); a row that has not
+                        // moved gets the values it had
+                        tileSum = expPass((mRef == -INFINITY) ? 0.0f : mRef, std::false_type{});
                     }
                 }
-                // a row with no visible key yet keeps everything at zero instead of producing NaN
-                const float mUse = (mRef == -INFINITY) ? 0.0f : mRef;
-
-                // packed fp32 pairs: one FMA / ADD instruction serves two scores
-                const uint64_t scale2 = pack_f32x2(p.scaleLog2, p.scaleLog2);
-                const uint64_t negRef2 = pack_f32x2(-mUse, -mUse);
-                uint64_t sumA = pack_f32x2(0.0f, 0.0f), sumB = sumA;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t packed[16];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        // masked entries hold -inf: ex2(-inf) = 0
-                        const uint64_t arg = fma_f32x2(
-                            pack_f32x2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), scale2, negRef2);
-                        float a0, a1;
-                        unpack_f32x2(arg, a0, a1);
-                        const float p0 = ex2(a0);
-                        const float p1 = ex2(a1);
-                        if ((i & 2) == 0) sumA = add_f32x2(sumA, pack_f32x2(p0, p1));
-                        else sumB = add_f32x2(sumB, pack_f32x2(p0, p1));
-                        __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-                        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
-                    }
-                    // P replaces S in tensor memory: two bf16 keys per 32-bit column, so the 32 keys of chunk c take
-                    // 16 columns and the whole tile the first 64 columns of the S region
-                    tmem_st_32x16(sAddr + static_cast<uint32_t>(c * 16), packed);
-                }
+                lRun += tileSum;
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();               // one arrival per warp: per-thread arrivals on one word serialise
                 if (lane == 0) mbar_arrive(&pFull[side]);
-                float sumLo, sumHi;
-                unpack_f32x2(add_f32x2(sumA, sumB), sumLo, sumHi);
-                lRun += sumLo + sumHi;
             }
             if (!alive) break;
 
-            // the item's output: wait for the last P V, normalise, store, hand the O region back
-            if (!warp_all(mbar_wait(&oFull[side], (tiles - 1u) & 1u, abortFlag, status, kDevTimeoutAccFull))) break;
+            // The item's output: wait for the last P V, normalise, hand the O region back. Each warp turns its 32
+            // rows into bf16 in two halves of 64 values, lays a half out in its own staging tile (128-byte rows, the
+            // 16-byte pieces of a row XOR-swizzled by the row so that the stores do not collide on banks: the layout
+            // the tensor map expects) and lets the TMA engine write it: whole 128-byte lines, no store instruction
+            // per row piece, and rows past the end of the sequence are clipped by the tensor map.
+            if (!(warp_wait(&oFull[side], sideItems & 1u, abortFlag, status, kDevTimeoutAccFull))) break;
+            ++sideItems;
             tc_fence_after();
             const float inv = lRun > 0.0f ? 1.0f / lRun : 0.0f;
             const bool store = row < p.newLen;
-            __nv_bfloat16* dst = p.out + (static_cast<int64_t>(w.b) * p.newLen + row) * p.ldO + static_cast<int64_t>(w.h) * kD;
+            uint8_t* stage = smem + kStageOff + (warp - kFirstSoftmaxWarp) * kStageBytes;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t o[32];
-                tmem_ld_32x32(oAddr + static_cast<uint32_t>(c * 32), o);
+            for (int h = 0; h < 2; ++h) {
+                uint32_t o[2][32];
+                tmem_ld_32x32(oAddr + static_cast<uint32_t>(h * 64), o[0]);
+                tmem_ld_32x32(oAddr + static_cast<uint32_t>(h * 64 + 32), o[1]);
                 tmem_ld_wait();
-                if (c == 3) {
+                if (h == 1) {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&oFree[side]);
                 }
-                if (store) {
+                // the store issued from this tile before must have read it
+                if (lane == 0) tma_store_wait_read();
+                __syncwarp();
 #pragma unroll
-                    for (int gq = 0; gq < 4; ++gq) {
-                        uint32_t wd[4];
+                for (int g = 0; g < 8; ++g) {
+                    uint32_t wd[4];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int e = gq * 8 + 2 * i;
-                            __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
-                            wd[i] = *reinterpret_cast<uint32_t*>(&hh);
-                        }
-                        *reinterpret_cast<uint4*>(dst + c * 32 + gq * 8) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+                    for (int i = 0; i < 4; ++i) {
+                        const int e = (g & 3) * 8 + 2 * i;
+                        __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(o[g >> 2][e]) * inv,
+                                                                  __uint_as_float(o[g >> 2][e + 1]) * inv);
+                        wd[i] = *reinterpret_cast<uint32_t*>(&hh);
                     }
+                    *reinterpret_cast<uint4*>(stage + lane * 128 + ((g ^ (lane & 7)) << 4)) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_3d(&tmapO, stage, w.h * kD + h * 64, w.q0 + side * kBM + (warp & 3) * 32, w.b);
+                    tma_store_commit();
                 }
             }
             if (store) {
@@ -498,6 +619,7 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                 if (p.lOut != nullptr) p.lOut[statIdx] = (mTrue == -INFINITY) ? 0.0f : lRun * ex2(mRef - mTrue);
             }
         }
+        if (lane == 0) tma_store_wait_all();
     } else {
         setmaxnreg_dec<kOtherRegs>();  // idle warps of the last warpgroup
     }
@@ -517,10 +639,10 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
 
 // `batchRows`: rows from one batch entry to the next (the length itself when densely packed, the capacity for a cache)
 void makeMap(TensorMapStorage* out, const void* base, int64_t dim, int64_t len, int64_t batch, int64_t ld,
-             int64_t batchRows) {
+             int64_t batchRows, uint32_t boxRows = 128u) {
     uint64_t dims[3] = {static_cast<uint64_t>(dim), static_cast<uint64_t>(len), static_cast<uint64_t>(batch)};
     uint64_t strides[2] = {static_cast<uint64_t>(ld) * 2, static_cast<uint64_t>(ld) * 2 * static_cast<uint64_t>(batchRows)};
-    uint32_t box[3] = {64u, 128u, 1u};
+    uint32_t box[3] = {64u, boxRows, 1u};
     encodeTensorMap(out, base, 2, 3, dims, strides, box);
 }
 
@@ -538,11 +660,12 @@ bool attentionUsesTensorCores(const AttentionArgs& a) {
 
 void attentionTensorCore(const AttentionArgs& a, cudaStream_t stream) {
     const int64_t dim = a.numHeads * a.headDim;
-    TensorMapStorage tq, tk, tv;
+    TensorMapStorage tq, tk, tv, to;
     const int64_t kvRows = a.kvBatchRows > 0 ? a.kvBatchRows : a.totalLen;
     makeMap(&tq, a.q, dim, a.newLen, a.batch, a.ldQ, a.newLen);
     makeMap(&tk, a.k, dim, a.totalLen, a.batch, a.ldK, kvRows);
     makeMap(&tv, a.v, dim, a.totalLen, a.batch, a.ldV, kvRows);
+    makeMap(&to, a.out, dim, a.newLen, a.batch, a.ldO, a.newLen, 32u);
     AttnParams p;
     p.out = static_cast<__nv_bfloat16*>(a.out);
     p.mOut = a.m;
@@ -570,7 +693,7 @@ void attentionTensorCore(const AttentionArgs& a, cudaStream_t stream) {
     BFB_CUDA(cudaFuncSetAttribute(attentionTcKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     attentionTcKernel<<<static_cast<unsigned>(grid), kThreads, kSmemBytes, stream>>>(
         *reinterpret_cast<const CUtensorMap*>(tq.bytes), *reinterpret_cast<const CUtensorMap*>(tk.bytes),
-        *reinterpret_cast<const CUtensorMap*>(tv.bytes), p, a.dStatus);
+        *reinterpret_cast<const CUtensorMap*>(tv.bytes), *reinterpret_cast<const CUtensorMap*>(to.bytes), p, a.dStatus);
     BFB_LAUNCH_CHECK();
     noteLaunch();
 }
