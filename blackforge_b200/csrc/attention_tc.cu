@@ -4,20 +4,23 @@
 // Persistent CTAs (one per SM) walk a list of work items; an item is a block of 256 query rows of one
 // (batch, head), handled as two 128-row tiles, side A and side B, that share every K and V tile. Roles:
 //   warps 0-3   softmax of side A, warps 4-7 softmax of side B: ONE thread per query row and no exchange between
-//               threads. A thread reads its row of S (128 scores) from tensor memory, takes the maximum,
-//               exponentiates, and writes the probabilities back as bf16 INTO TENSOR MEMORY over the scores (two
-//               keys per 32-bit column). The two sides are independent, so while one waits for its next scores
-//               the other has the scheduler's exp unit to itself.
-//   warp 8      TMA producer: Q of each item (both sides) into one of two Q buffers, K and V tiles (128 keys x
-//               128 dims, two 64-wide swizzled halves each) through a 3-slot ring. It runs ahead into the next
-//               item, so the pipeline does not drain between items.
-//   warp 9      MMA issuer + TMEM owner. Per key tile and side: O += P V (P from tensor memory, V from shared
-//               memory), then S = Q K^T of that side's NEXT key tile. Tensor-core operations of one thread run in
-//               issue order, so the next scores overwrite P only after P V has read it.
+//               threads. A thread reads its row of S (128 scores) from tensor memory, exponentiates against the
+//               reference it carries over from the tile before (taking the tile's maximum on the way, on another
+//               pipe), and writes the probabilities back as bf16 INTO TENSOR MEMORY over the scores (two keys per
+//               32-bit column). The two sides are independent, so while one waits for its next scores the other
+//               has the scheduler's exp unit to itself. At the end of an item a warp passes its 32 output rows
+//               through a small swizzled staging tile in shared memory and a TMA store writes whole lines.
+//   warp 8      TMA producer (one elected thread): Q of each item (both sides), K and V tiles (128 keys x 128 dims,
+//               two 64-wide swizzled halves each) through a 4-slot ring. It runs ahead into the next item, so the
+//               pipeline does not drain between items.
+//   warp 9      MMA issuer (one elected thread) + TMEM owner. Per key tile and side: O += P V (P from tensor
+//               memory, V from shared memory), then S = Q K^T of that side's NEXT key tile. Tensor-core operations
+//               of one thread run in issue order, so the next scores overwrite P only after P V has read it.
 //   warps 10-11 idle (they complete the warpgroup whose registers are handed to the softmax warps).
 // O stays in tensor memory for the whole item and accumulates across key tiles. The exponent reference of a
-// row follows the running maximum lazily: it moves (and O and the row sum are rescaled) only when the maximum
-// has grown by more than 8 in log2 units, so probabilities stay below 2^8 and almost no tile pays for a rescale.
+// row follows the running maximum lazily: it moves (and O and the row sum are rescaled, and the tile is
+// exponentiated again) only when the maximum has grown by more than 8 in log2 units, so probabilities stay below
+// 2^8 and almost no tile pays for it.
 // TMEM columns: S_A [0,128) S_B [128,256) O_A [256,384) O_B [384,512); P of a tile occupies the first 64
 // columns of its S region. Key tiles above the causal diagonal are never visited; only tiles that straddle it
 // are masked. All mbarrier waits are bounded.
@@ -31,10 +34,6 @@
 #include "common.cuh"
 #include "kernels.hpp"
 #include "ptx_sm100.cuh"
-
-#ifndef BFB_ATT_V
-#define BFB_ATT_V 0
-#endif
 
 namespace bfb {
 
@@ -53,15 +52,9 @@ constexpr int kStageBytes = 32 * 128;            // one softmax warp's 32 rows x
 constexpr int kStageOff = kKvOff + kKvSlots * kTileBytes;   // [8 softmax warps]
 constexpr int kBarOff = kStageOff + 8 * kStageBytes;
 constexpr int kSmemBytes = kBarOff + 256;
-#if (BFB_ATT_V & 16)
-constexpr int kFirstSoftmaxWarp = 4;        // warps 0-3: MMA issuer, TMA producer, two idle; warps 4-11 softmax
-constexpr int kProducerWarp = 1;
-constexpr int kMmaWarp = 0;
-#else
 constexpr int kFirstSoftmaxWarp = 0;
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
-#endif
 constexpr int kThreads = 384;
 constexpr int kSoftmaxRegs = 232;           // 384 threads start with 168 registers each; the last warpgroup gives
 constexpr int kOtherRegs = 40;              // 128 * (168 - 40), the two softmax warpgroups take 2 * 128 * (232 - 168)
@@ -75,75 +68,12 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// experiment switches
-__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_x(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-#if (BFB_ATT_V & 2)
-    if (mbar_try_wait_hint(bar, parity, 2000)) return true;
-    uint64_t start = global_timer_ns();
-    uint32_t spins = 0;
-    while (true) {
-        if (mbar_try_wait_hint(bar, parity, 2000)) return true;
-        if ((++spins & 15u) == 0u) {
-            if (*abort_flag != 0) return false;
-            if (global_timer_ns() - start > kWaitLimitNs) {
-                *abort_flag = 1;
-                if (status != nullptr) atomicCAS(status, 0, code);
-                return false;
-            }
-        }
-    }
-#else
-    return mbar_wait(bar, parity, abort_flag, status, code);
-#endif
-}
-// wait executed by the whole warp (default) or by one lane whose result is broadcast
-__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-#if (BFB_ATT_V & 1)
-    bool ok = true;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait_x(bar, parity, abort_flag, status, code);
-    return __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
-#else
-    return warp_all(mbar_wait_x(bar, parity, abort_flag, status, code));
-#endif
-}
-__device__ __forceinline__ float max3f(float a, float b, float c) {
-#if (BFB_ATT_V & 4)
-    float d;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
-#else
-    return fmaxf(fmaxf(a, b), c);
-#endif
-}
+__device__ __forceinline__ float max3f(float a, float b, float c) { return fmaxf(fmaxf(a, b), c); }
 
-// A role runs either on a whole (converged) warp that elects a lane for each single-thread instruction, or on one
-// elected thread for the entire role.
-#if (BFB_ATT_V & 32)
-#define ROLE_OPEN if (elect_one()) {
-#define ROLE_CLOSE } __syncwarp();
-#define ROLE_WAIT mbar_wait_x
-#define ROLE_ELECT true
-#define ROLE_SYNCWARP() do {} while (0)
-#else
-#define ROLE_OPEN {
-#define ROLE_CLOSE }
-#define ROLE_WAIT warp_wait
-#define ROLE_ELECT elect_one()
-#define ROLE_SYNCWARP() __syncwarp()
-#endif
+// A wait by every lane of a converged warp, with a warp-uniform outcome.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    return warp_all(mbar_wait(bar, parity, abort_flag, status, code));
+}
 
 struct AttnParams {
     __nv_bfloat16* out;
@@ -261,35 +191,34 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
     const uint32_t tmemBase = *tmemSlot;
 
     if (warp == kProducerWarp) {
-        // ---------------- TMA producer: runs ahead across items ----------------
+        // ---------------- TMA producer (one elected thread): runs ahead across items ----------------
         setmaxnreg_dec<kOtherRegs>();
-        ROLE_OPEN
-        uint32_t it = 0;     // items taken by this CTA so far
-        uint32_t idx = 0;    // K/V tiles loaded so far (K of an item's key tile j, then its V)
-        bool alive = true;
-        for (int item = itemAt(0); item < p.totalItems && alive; item = itemAt(++it)) {
-            const Item w = decodeItem(p, item);
-            // Q of the item: its buffer is free once the previous item's last scores have been computed, which is a
-            // whole key tile before this item's first scores are issued
-            if (!(ROLE_WAIT(&qEmpty[0], (it & 1u) ^ 1u, abortFlag, status, kDevTimeoutStageEmpty))) break;
-            if (ROLE_ELECT) {
-                uint8_t* dst = smem + kQOff;
-                const int sides = w.nKv[1] > 0 ? 2 : 1;
-                mbar_arrive_expect_tx(&qFull[0], sides * kTileBytes);
-                for (int s = 0; s < sides; ++s) {
-                    tma_load_3d(dst + s * kTileBytes, &tmapQ, &qFull[0], w.h * kD, w.q0 + s * kBM, w.b);
-                    tma_load_3d(dst + s * kTileBytes + kHalfBytes, &tmapQ, &qFull[0], w.h * kD + 64, w.q0 + s * kBM, w.b);
+        if (elect_one()) {
+            uint32_t it = 0;     // items taken by this CTA so far
+            uint32_t idx = 0;    // K/V tiles loaded so far (K of an item's key tile j, then its V)
+            bool alive = true;
+            for (int item = itemAt(0); item < p.totalItems && alive; item = itemAt(++it)) {
+                const Item w = decodeItem(p, item);
+                // Q of the item: its buffer is free once the previous item's last scores have been computed, which
+                // is a whole key tile before this item's first scores are issued
+                if (!mbar_wait(&qEmpty[0], (it & 1u) ^ 1u, abortFlag, status, kDevTimeoutStageEmpty)) break;
+                {
+                    uint8_t* dst = smem + kQOff;
+                    const int sides = w.nKv[1] > 0 ? 2 : 1;
+                    mbar_arrive_expect_tx(&qFull[0], sides * kTileBytes);
+                    for (int s = 0; s < sides; ++s) {
+                        tma_load_3d(dst + s * kTileBytes, &tmapQ, &qFull[0], w.h * kD, w.q0 + s * kBM, w.b);
+                        tma_load_3d(dst + s * kTileBytes + kHalfBytes, &tmapQ, &qFull[0], w.h * kD + 64, w.q0 + s * kBM,
+                                    w.b);
+                    }
                 }
-            }
-            ROLE_SYNCWARP();
-            for (int t = 0; t < 2 * w.n; ++t, ++idx) {
-                const int slot = idx % kKvSlots;
-                const uint32_t use = idx / kKvSlots;
-                if (!(ROLE_WAIT(&kvEmpty[slot], (use & 1u) ^ 1u, abortFlag, status, kDevTimeoutStageEmpty))) {
-                    alive = false;
-                    break;
-                }
-                if (ROLE_ELECT) {
+                for (int t = 0; t < 2 * w.n; ++t, ++idx) {
+                    const int slot = idx % kKvSlots;
+                    const uint32_t use = idx / kKvSlots;
+                    if (!mbar_wait(&kvEmpty[slot], (use & 1u) ^ 1u, abortFlag, status, kDevTimeoutStageEmpty)) {
+                        alive = false;
+                        break;
+                    }
                     const int j = t >> 1;
                     const CUtensorMap* map = (t & 1) ? &tmapV : &tmapK;
                     uint8_t* dst = smem + kKvOff + slot * kTileBytes;
@@ -297,32 +226,34 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                     tma_load_3d(dst, map, &kvFull[slot], w.h * kD, j * kBN, w.b);
                     tma_load_3d(dst + kHalfBytes, map, &kvFull[slot], w.h * kD + 64, j * kBN, w.b);
                 }
-                ROLE_SYNCWARP();
             }
         }
-        ROLE_CLOSE
+        __syncwarp();
     } else if (warp == kMmaWarp) {
         // ---------------- MMA issuer (one elected thread) ----------------
-        // A thread can run about six tcgen05.mma ahead of the tensor pipe, no further: whatever it does between
-        // two batches beyond that is time the pipe stands still. So everything that is normally long complete (the
-        // K/V tiles, the next item's Q) is checked BEFORE the wait for the probabilities, which is the one wait that
-        // really takes time, and a batch of P V is followed by the next scores of the same side without a wait in
-        // between. Completion is signalled once per side and key tile (sFull, after the scores, which also covers
-        // the P V before them); oFull only after an item's last P V.
+        // The role runs on ONE thread chosen by elect.sync (the compiler then keeps the descriptors in uniform
+        // registers; a test on the lane index made every instruction of the region several times slower). That
+        // thread can run about six tcgen05.mma ahead of the tensor pipe, no further: whatever it does between two
+        // batches beyond that is time the pipe stands still, and it shares its scheduler with two softmax warps, so
+        // each of its instructions waits for an issue slot. Hence: descriptors are stepped with one integer add per
+        // operand; everything that is normally long complete (the K/V tiles, the next item's Q) is checked BEFORE
+        // the wait for the probabilities, the one wait that really takes time; a batch of P V is followed by the
+        // next scores of the same side without a wait in between; completion is signalled once per side and key
+        // tile (sFull, after the scores, which also covers the P V before them) and oFull only after an item's last
+        // P V.
         setmaxnreg_dec<kOtherRegs>();
-        ROLE_OPEN
-        const uint32_t kvLoBase = smem_desc_lo(smem_u32(smem + kKvOff), 0);
-        const uint32_t qLoBase = smem_desc_lo(smem_u32(smem + kQOff), 0);
-        constexpr uint32_t kHi = smem_desc_hi_sw128(1024);
-        uint32_t tilesDone[2] = {0u, 0u};   // P V products issued per side (phase of pFull)
-        uint32_t itemsDone[2] = {0u, 0u};   // items whose output the side's softmax warps have taken (phase of oFree)
+        if (elect_one()) {
+            const uint32_t kvLoBase = smem_desc_lo(smem_u32(smem + kKvOff), 0);
+            const uint32_t qLoBase = smem_desc_lo(smem_u32(smem + kQOff), 0);
+            constexpr uint32_t kHi = smem_desc_hi_sw128(1024);
+            uint32_t tilesDone[2] = {0u, 0u};   // P V products issued per side (phase of pFull)
+            uint32_t itemsDone[2] = {0u, 0u};   // items whose output the side's softmax warps have taken (phase of oFree)
 
-        auto waitKv = [&](uint32_t idx) -> bool {
-            return (ROLE_WAIT(&kvFull[idx % kKvSlots], (idx / kKvSlots) & 1u, abortFlag, status, kDevTimeoutTmaFull));
-        };
-        // S_side = Q_side K^T for the key tile in ring entry kIdx
-        auto issueQK = [&](int side, uint32_t kIdx) {
-            if (ROLE_ELECT) {
+            auto waitKv = [&](uint32_t idx) -> bool {
+                return mbar_wait(&kvFull[idx % kKvSlots], (idx / kKvSlots) & 1u, abortFlag, status, kDevTimeoutTmaFull);
+            };
+            // S_side = Q_side K^T for the key tile in ring entry kIdx
+            auto issueQK = [&](int side, uint32_t kIdx) {
                 const uint32_t qLo = qLoBase + side * (kTileBytes >> 4);
                 const uint32_t kLo = kvLoBase + (kIdx % kKvSlots) * (kTileBytes >> 4);
                 const uint32_t dS = tmemBase + static_cast<uint32_t>(side * kBN);
@@ -332,21 +263,18 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                     umma_f16_words(dS, qLo + off, kHi, kLo + off, kHi, kIdescQK, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(&sFull[side]);
-            }
-            ROLE_SYNCWARP();
-        };
-        // O_side (+)= P_side V for the key tile whose V is ring entry vIdx; `first` starts a new item's sum, `last`
-        // ends it
-        auto issuePV = [&](int side, uint32_t vIdx, bool first, bool last) -> bool {
-            if (!(ROLE_WAIT(&pFull[side], tilesDone[side] & 1u, abortFlag, status, kDevTimeoutSoftmax))) return false;
-            if (first) {
-                // the previous item's output must have left tensor memory
-                if (!(ROLE_WAIT(&oFree[side], (itemsDone[side] & 1u) ^ 1u, abortFlag, status, kDevTimeoutAccEmpty)))
-                    return false;
-                ++itemsDone[side];
-            }
-            tc_fence_after();
-            if (ROLE_ELECT) {
+            };
+            // O_side (+)= P_side V for the key tile whose V is ring entry vIdx; `first` starts a new item's sum,
+            // `last` ends it
+            auto issuePV = [&](int side, uint32_t vIdx, bool first, bool last) -> bool {
+                if (!mbar_wait(&pFull[side], tilesDone[side] & 1u, abortFlag, status, kDevTimeoutSoftmax)) return false;
+                if (first) {
+                    // the previous item's output must have left tensor memory
+                    if (!mbar_wait(&oFree[side], (itemsDone[side] & 1u) ^ 1u, abortFlag, status, kDevTimeoutAccEmpty))
+                        return false;
+                    ++itemsDone[side];
+                }
+                tc_fence_after();
                 // P from tensor memory (it sits where S was): 16 keys = 8 packed columns per step. V: keys are rows
                 // (MN-major B): 8-key groups 1024 B apart, the two 64-wide halves of head_dim one half-tile apart.
                 const uint32_t pTmem = tmemBase + static_cast<uint32_t>(side * kBN);
@@ -359,74 +287,68 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                                       kk > 0 ? 1u : accFirst);
                 }
                 if (last) umma_commit(&oFull[side]);
-            }
-            ROLE_SYNCWARP();
-            ++tilesDone[side];
-            return true;
-        };
-        auto waitQ = [&](uint32_t itemNo) -> bool {
-            return (ROLE_WAIT(&qFull[0], itemNo & 1u, abortFlag, status, kDevTimeoutTmaFull));
-        };
-        auto commitTo = [&](uint64_t* bar) {
-            if (ROLE_ELECT) umma_commit(bar);
-            ROLE_SYNCWARP();
-        };
+                ++tilesDone[side];
+                return true;
+            };
+            auto waitQ = [&](uint32_t itemNo) -> bool {
+                return mbar_wait(&qFull[0], itemNo & 1u, abortFlag, status, kDevTimeoutTmaFull);
+            };
 
-        int item = itemAt(0);
-        if (item < p.totalItems) {
-            uint32_t it = 0;
-            uint32_t base = 0;   // ring entry of this item's K(0); K(j) is base + 2j, V(j) is base + 2j + 1
-            Item w = decodeItem(p, item);
-            bool alive = waitQ(0) && waitKv(0);
-            if (alive) {
-                tc_fence_after();
-                issueQK(0, 0);
-                if (w.nKv[1] > 0) issueQK(1, 0);
-                commitTo(&kvEmpty[0]);
-                if (w.n == 1) commitTo(&qEmpty[0]);
-            }
-            while (alive) {
-                // the item that follows, if any: its first scores are issued under this item's last key tile
-                const int nextItem = itemAt(it + 1);
-                const bool haveNextItem = nextItem < p.totalItems;
-                Item nw = w;
-                if (haveNextItem) nw = decodeItem(p, nextItem);
-                const uint32_t nextBase = base + 2u * static_cast<uint32_t>(w.n);
-
-                for (int j = 0; j < w.n && alive; ++j) {
-                    const uint32_t vIdx = base + 2u * j + 1u;
-                    // the key tile whose scores are issued in this round
-                    const bool inItem = j + 1 < w.n;
-                    const bool haveNext = inItem || haveNextItem;
-                    const uint32_t kIdx = inItem ? base + 2u * (j + 1) : nextBase;
-                    const uint32_t kItemNo = inItem ? it : it + 1;
-                    const Item& kw = inItem ? w : nw;
-                    const int kj = inItem ? j + 1 : 0;
-                    // operands first: V of this key tile, K (and Q) of the next scores
-                    if (!waitKv(vIdx)) { alive = false; break; }
-                    if (haveNext && ((!inItem && !waitQ(kItemNo)) || !waitKv(kIdx))) { alive = false; break; }
-#pragma unroll
-                    for (int side = 0; side < 2; ++side) {
-                        if (j < w.nKv[side]) {
-                            if (!issuePV(side, vIdx, j == 0, j == w.nKv[side] - 1)) { alive = false; break; }
-                        }
-                        if (haveNext && kj < kw.nKv[side]) issueQK(side, kIdx);
-                    }
-                    if (!alive) break;
-                    commitTo(&kvEmpty[vIdx % kKvSlots]);
-                    if (haveNext) {
-                        commitTo(&kvEmpty[kIdx % kKvSlots]);
-                        if (kj == kw.n - 1) commitTo(&qEmpty[0]);   // those were the item's last scores
-                    }
+            int item = itemAt(0);
+            if (item < p.totalItems) {
+                uint32_t it = 0;
+                uint32_t base = 0;   // ring entry of this item's K(0); K(j) is base + 2j, V(j) is base + 2j + 1
+                Item w = decodeItem(p, item);
+                bool alive = waitQ(0) && waitKv(0);
+                if (alive) {
+                    tc_fence_after();
+                    issueQK(0, 0);
+                    if (w.nKv[1] > 0) issueQK(1, 0);
+                    umma_commit(&kvEmpty[0]);
+                    if (w.n == 1) umma_commit(&qEmpty[0]);
                 }
-                if (!alive || !haveNextItem) break;
-                item = nextItem;
-                w = nw;
-                base = nextBase;
-                ++it;
+                while (alive) {
+                    // the item that follows, if any: its first scores are issued under this item's last key tile
+                    const int nextItem = itemAt(it + 1);
+                    const bool haveNextItem = nextItem < p.totalItems;
+                    Item nw = w;
+                    if (haveNextItem) nw = decodeItem(p, nextItem);
+                    const uint32_t nextBase = base + 2u * static_cast<uint32_t>(w.n);
+
+                    for (int j = 0; j < w.n && alive; ++j) {
+                        const uint32_t vIdx = base + 2u * j + 1u;
+                        // the key tile whose scores are issued in this round
+                        const bool inItem = j + 1 < w.n;
+                        const bool haveNext = inItem || haveNextItem;
+                        const uint32_t kIdx = inItem ? base + 2u * (j + 1) : nextBase;
+                        const Item& kw = inItem ? w : nw;
+                        const int kj = inItem ? j + 1 : 0;
+                        // operands first: V of this key tile, K (and Q) of the next scores
+                        if (!waitKv(vIdx)) { alive = false; break; }
+                        if (haveNext && ((!inItem && !waitQ(it + 1)) || !waitKv(kIdx))) { alive = false; break; }
+#pragma unroll
+                        for (int side = 0; side < 2; ++side) {
+                            if (j < w.nKv[side]) {
+                                if (!issuePV(side, vIdx, j == 0, j == w.nKv[side] - 1)) { alive = false; break; }
+                            }
+                            if (haveNext && kj < kw.nKv[side]) issueQK(side, kIdx);
+                        }
+                        if (!alive) break;
+                        umma_commit(&kvEmpty[vIdx % kKvSlots]);
+                        if (haveNext) {
+                            umma_commit(&kvEmpty[kIdx % kKvSlots]);
+                            if (kj == kw.n - 1) umma_commit(&qEmpty[0]);   // those were the item's last scores
+                        }
+                    }
+                    if (!alive || !haveNextItem) break;
+                    item = nextItem;
+                    w = nw;
+                    base = nextBase;
+                    ++it;
+                }
             }
         }
-        ROLE_CLOSE
+        __syncwarp();
     } else if (warp >= kFirstSoftmaxWarp && warp < kFirstSoftmaxWarp + 8) {
         // ---------------- softmax: one thread per query row ----------------
         setmaxnreg_inc<kSoftmaxRegs>();
