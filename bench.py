@@ -7,8 +7,9 @@ One step = one forward of one batch of synthetic token ids through Model::forwar
 `blackforge run --device cuda --from-checkpoint`). Default workload: the 2B-class decoder (vocab 32000,
 d_model 2048, 16 layers, 16 heads x 128, feed-forward 5632, learned positions), precision {storage bf16,
 compute bf16, accumulate fp32}, 32 sequences x 2048 tokens per GPU; weights N(0, 0.02) from a seeded
-generator, ids uniform. With N GPUs every rank (one process per GPU, launched by torchrun) runs its own
-32 sequences: sequences are independent, so there is no data-path collective (weak scaling).
+generator, ids uniform. With N GPUs (one process per GPU, launched by torchrun) the 32 sequences are split over the
+ranks, 32/N each (strong scaling; `--scaling weak` gives every rank all 32): sequences are independent, so there
+is no data-path collective.
 
 Prints ONE JSON line on rank 0:
   value     tokens/s over all GPUs, ids already in HBM, device-timed (CUDA events, max over ranks)
@@ -16,6 +17,9 @@ Prints ONE JSON line on rank 0:
             the timed region every step
   roofline  the tcgen05 GEMM (dominant kernel): algorithmic FLOPs / event-timed duration inside the timed region
   cpu_baseline  the reference's own CPU backend (oracle/_ref) timed here on a bounded sample (N = 1 only)
+Extra keys of the default workload: at 1 GPU `attention_c2` (stand-alone causal attention at its benchmark shape) and
+`fp8` (the same model with compute fp8.e4m3); at 2 or more GPUs `weak` (every rank runs the whole batch) and `tp_c5`
+(the 24B-class model, tensor parallel); `e2e.ceiling` puts the end-to-end figure beside what the host's links allow.
 `--impl reference` times that CPU backend alone, on all host cores it can use, and prints the same line shape.
 """
 from __future__ import annotations
@@ -54,9 +58,9 @@ WORKLOADS = {
 TENSOR_PARALLEL = {"c5"}
 
 # DRAM bytes per launch of the dominant kernel from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum),
-# keyed by workload; None until a capture of that kernel has been summarised under profiles/.
+# keyed by workload; None where no capture of that kernel has been summarised.
 # c3: capture of M=32768, N=K=2048 (239.2 MB for 0.275 TFLOP, equal to A+B+C) scaled by FLOPs to the step's average
-# GEMM launch (1.418 TFLOP); see profiles/gemm_pair_bf16_m32768_n2048_k2048.md.
+# GEMM launch (1.418 TFLOP).
 NCU_TRAFFIC_BYTES_PER_LAUNCH = {"c3": 1.233e9, "c4": None, "c1": None, "c5": None}
 
 
@@ -250,7 +254,9 @@ def run_reference_arm(args, cfg, seq, label, precision):
     line = {
         "impl": "reference", "metric": "prefill tokens/s", "value": tokens_per_s, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "higher_is_better": True,
+        "scaling": "strong" if (args.gpus > 1 and args.scaling != "weak") or args.workload in TENSOR_PARALLEL else "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": label, "seq_len": seq, "precision": precision or "fp32 (no precision block)"},
         "cpu_baseline": {"value": tokens_per_s, "unit": "tokens/s", "cores": workers, "kind": kind, "sample": sample,
                          "host_cores": cores, "gflops": workers * flops / per_step / 1e9},
@@ -357,6 +363,278 @@ def cpu_baseline_inline(cfg, seq, sample_seq):
 
 
 # ---------------------------------------------------------------------------------------------------------
+# measurement pieces of the default arm
+# ---------------------------------------------------------------------------------------------------------
+
+KERNEL_KINDS = (("gemm_tcgen05", 0), ("attention_tcgen05", 1), ("rmsnorm", 2), ("embed_pos", 3), ("cast", 4))
+
+
+class Ctx:
+    """What every measurement needs: the binding, rank plumbing and the current device."""
+
+    def __init__(self, bfb, launch, torch, rank, world, local):
+        self.bfb, self.launch, self.torch = bfb, launch, torch
+        self.rank, self.world, self.local = rank, world, local
+        self.dev = torch.device("cuda", local)
+
+    def max_ms(self, ms):
+        return self.launch.max_over_ranks(ms, self.dev if self.world > 1 else None)
+
+
+def build_model(ctx, cfg, precision, tensor_parallel, seed, tp_groups=2, tp_reserved_sms=0):
+    bfb = ctx.bfb
+    model = bfb.Model(lm_ops(**cfg), precision=precision, random_init=False)
+    if tensor_parallel:
+        model.set_tensor_parallel(ctx.rank, ctx.world)
+        model.set_tensor_parallel_overlap(tp_groups, tp_reserved_sms if tp_groups > 1 else 0)
+        # weights drawn on the device (N(0, 0.01), the same full matrices whatever the split); the fp32 copies of
+        # the GEMM weights are dropped once the first forward has converted them
+        for i, _name in enumerate(model.param_names()):
+            model.fill_param_normal(i, seed * 1000003 + i, 0.01)
+    else:
+        synth_weights(bfb, model, seed, 0.02)
+    return model
+
+
+def draw_ids(cfg, batch, seq, seed, stream_id):
+    rng = np.random.Generator(np.random.PCG64([seed, 7919 + stream_id]))
+    return rng.integers(0, cfg["vocab"], size=(batch, seq)).astype(np.float32)
+
+
+def time_device_steps(ctx, model, d_ids, shape, steps, warmup, release_masters=False, sample_clocks=False):
+    """W warm-up and K timed forwards with the ids resident in HBM: CUDA events on the launching stream, barrier and
+    synchronize on both sides, max over ranks; per-kernel device times from the library's own events."""
+    bfb, torch = ctx.bfb, ctx.torch
+
+    def step():
+        out, oshape = model.forward_device(d_ids.ptr, shape, trusted=True)
+        out.free()   # back to the pool: the next step reuses the same memory
+        return oshape
+
+    sampler = ClockSampler(ctx.local) if (sample_clocks and ctx.rank == 0) else None
+    out_shape = None
+    for i in range(max(warmup, 1)):
+        out_shape = step()
+        if i == 0 and release_masters:
+            torch.cuda.synchronize()
+            model.release_master_weights()
+    torch.cuda.synchronize()
+    bfb.lib().bfb_profile_reset()
+    bfb.lib().bfb_profile_enable(1)
+    bfb.lib().bfb_launch_count(1)
+    ctx.launch.barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wall_begin = time.time()
+    start.record()
+    for _ in range(steps):
+        step()
+    stop.record()
+    torch.cuda.synchronize()
+    wall_end = time.time()
+    ctx.launch.barrier()
+    elapsed_ms = ctx.max_ms(start.elapsed_time(stop))
+    clocks = sampler.stop(wall_begin, wall_end) if sampler else None
+    launches = bfb.lib().bfb_launch_count(0)
+    bfb.lib().bfb_profile_enable(0)
+    kernels = {}
+    for name, kind in KERNEL_KINDS:
+        ms, n, work = profile_read(bfb, kind)
+        if n:
+            secs = ms / 1e3
+            k = {"ms_total": ms, "launches": n, "work": work, "share_of_step": ms / elapsed_ms}
+            if name in ("gemm_tcgen05", "attention_tcgen05"):
+                k["tflops"] = work / secs / 1e12
+            else:
+                k["gbs"] = work / secs / 1e9
+            kernels[name] = k
+    bfb.lib().bfb_profile_reset()
+    return {"ms_per_step": elapsed_ms / steps, "elapsed_ms": elapsed_ms, "kernels": kernels, "launches": int(launches),
+            "clocks": clocks, "out_shape": out_shape}
+
+
+def time_e2e(ctx, model, ids, out_shape, steps, precision, tokens_global):
+    """The same forward through the host-buffer API: pinned host ids in, pinned host logits out, both copies inside
+    the timed region of every step."""
+    bfb, torch = ctx.bfb, ctx.torch
+    out_elems = int(np.prod(out_shape))
+    h_ids = torch.from_numpy(ids).pin_memory()
+    h_out = torch.empty(out_elems, dtype=torch.float32).pin_memory()
+    shape_arr = (C.c_int64 * 2)(*ids.shape)
+    oshape, orank = (C.c_int64 * 8)(), C.c_int32()
+
+    def timed(fn):
+        fn()
+        ctx.launch.barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(steps):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        ctx.launch.barrier()
+        return ctx.max_ms(s.elapsed_time(e)) / steps
+
+    ms = timed(lambda: bfb.check(bfb.lib().bfb_model_forward_host(model._h, h_ids.data_ptr(), shape_arr, 2,
+                                                                   h_out.data_ptr(), oshape, C.byref(orank))))
+    # bytes the call itself booked for its copies: under storage bf16 part of the logits may cross the link as
+    # 2-byte bf16 and be widened to the caller's fp32 buffer by host threads
+    h2d_bytes, d2h_bytes = bfb.host_transfer_bytes()
+    e2e = {"value": tokens_global / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms,
+           "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+           "result_bytes_per_step": out_elems * 4, "steps": steps,
+           "api": "bfb_model_forward_host (fromHost -> Model::forward -> toHost), pinned host buffers"}
+    del h_out
+    # the same pipeline handing the logits to the host as bf16 (bfb_model_forward_host_bf16): not the reference's
+    # fp32 contract, reported beside it because it is what keeps several GPUs from saturating one host
+    if (precision or {}).get("storage") == "bf16":
+        h_out16 = torch.empty(out_elems, dtype=torch.int16).pin_memory()
+        ms16 = timed(lambda: bfb.check(bfb.lib().bfb_model_forward_host_bf16(
+            model._h, h_ids.data_ptr(), shape_arr, 2, h_out16.data_ptr(), oshape, C.byref(orank))))
+        e2e["bf16_result"] = {"value": tokens_global / (ms16 / 1e3), "unit": "tokens/s", "ms_per_step": ms16,
+                              "d2h_bytes_per_step": bfb.host_transfer_bytes()[1],
+                              "api": "bfb_model_forward_host_bf16 (logits stay bf16 on the host)"}
+        del h_out16
+    return e2e
+
+
+def d2h_probe(ctx, nbytes=1 << 30, repeats=3):
+    """Device-to-pinned-host copies of `nbytes` issued by every rank at the same time: what this host takes in from
+    its GPUs together (GB/s over all ranks, max-over-ranks time), the ceiling of any end-to-end figure."""
+    torch = ctx.torch
+    src = torch.empty(nbytes, dtype=torch.uint8, device=ctx.dev)
+    dst = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    dst.copy_(src, non_blocking=True)
+    torch.cuda.synchronize()
+    ctx.launch.barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(repeats):
+        dst.copy_(src, non_blocking=True)
+    e.record()
+    torch.cuda.synchronize()
+    ctx.launch.barrier()
+    ms = ctx.max_ms(s.elapsed_time(e)) / repeats
+    return {"aggregate_gbs": ctx.world * nbytes / (ms / 1e3) / 1e9, "per_rank_gbs": nbytes / (ms / 1e3) / 1e9,
+            "bytes_per_rank": nbytes, "ranks": ctx.world}
+
+
+def attention_config2(ctx, peaks, iters=20, warmup=3):
+    """BASELINE config 2: stand-alone causal attention, Q/K/V bf16 [16, 16 heads, 2048, 128] i.i.d. N(0,1), scale
+    1/sqrt(128); CUDA events, L2 flushed between iterations (the operands are 4 x 134 MB, about the size of L2)."""
+    bfb, torch = ctx.bfb, ctx.torch
+    lib = bfb.lib()
+    batch, heads, seq, hd = 16, 16, 2048, 128
+    dim = heads * hd
+    n = batch * seq * dim
+
+    def rand_bf16(seed):
+        g = torch.Generator(device=ctx.dev)
+        g.manual_seed(seed)
+        t = torch.randn(n, device=ctx.dev, dtype=torch.float32, generator=g)
+        buf = bfb.DeviceBuffer(n * 2)
+        bfb.check(lib.bfb_cast(t.data_ptr(), bfb.F32, buf.ptr, bfb.BF16, n, 1.0, None, None))
+        torch.cuda.synchronize()
+        return buf
+
+    q, k, v = rand_bf16(11), rand_bf16(12), rand_bf16(13)
+    out = bfb.DeviceBuffer(n * 2)
+    status = bfb.DeviceBuffer.zeros(4)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=ctx.dev)
+
+    def run():
+        bfb.check(lib.bfb_attention_fwd(q.ptr, k.ptr, v.ptr, out.ptr, None, None, bfb.BF16, batch, seq, seq, heads, hd,
+                                        dim, dim, dim, dim, float(hd ** -0.5), 0, 1, status.ptr, None))
+
+    for _ in range(warmup):
+        run()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        run()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    code = int(status.to_numpy(np.int32, (1,))[0])
+    for b in (q, k, v, out, status):
+        b.free()
+    ms = statistics.median(times)
+    flops = 4.0 * hd * batch * heads * seq * (seq + 1) / 2.0
+    tflops = flops / (ms / 1e3) / 1e12
+    return {"workload": "causal attention forward, bf16 [16, 16, 2048, 128], fp32 online softmax (BASELINE config 2)",
+            "kernel": "attentionTcKernel (tcgen05, S/P/O in tensor memory, TMA-fed)", "ms": ms, "ms_min": min(times),
+            "tflops": tflops, "flops": "causal: 4*D per visible (query, key) pair", "iters": iters,
+            "frac_of_burst": tflops / peaks["tflops_burst"], "frac_of_sustained": tflops / peaks["tflops_sustained"],
+            "frac_of_nominal_2250": tflops / 2250.0, "peak_source": "of " + peaks["source"] + " (cuBLAS bf16)",
+            "l2": "256 MiB written between iterations", "device_status": code}
+
+
+NOMINAL_FP8_TFLOPS = 4500.0
+
+
+def fp8_config4(ctx, args, peaks, bf16_ms):
+    """BASELINE config 4 beside the headline: the same model with compute fp8.e4m3, a few steps."""
+    cfg, batch, seq, precision, label = WORKLOADS["c4"]
+    model = build_model(ctx, dict(cfg), precision, False, args.seed)
+    ids = draw_ids(cfg, batch, seq, args.seed, ctx.rank)
+    d_ids = ctx.bfb.DeviceBuffer.from_numpy(ids)
+    m = time_device_steps(ctx, model, d_ids, ids.shape, steps=max(3, min(args.steps, 5)), warmup=3)
+    d_ids.free()
+    model.close()
+    ctx.bfb.check(ctx.bfb.lib().bfb_pool_trim())
+    g, a = flops_per_token(cfg, seq)
+    tokens = batch * seq
+    res = {"workload": label, "tokens_per_s": tokens / (m["ms_per_step"] / 1e3), "ms_per_step": m["ms_per_step"],
+           "speedup_vs_bf16_step": bf16_ms / m["ms_per_step"] if bf16_ms else None,
+           "model_tflops": (g + a) * tokens / (m["ms_per_step"] / 1e3) / 1e12, "gpu_launches": m["launches"],
+           "kernels": m["kernels"], "parity": "unpinned (the reference has no fp8 implementation)"}
+    k = m["kernels"].get("gemm_tcgen05")
+    if k:
+        res["gemm_tflops"] = k["tflops"]
+        res["gemm_frac_of_nominal_4500"] = k["tflops"] / NOMINAL_FP8_TFLOPS
+        res["peak_note"] = ("no fp8 peak was measured on this pool: the fraction is of the NOMINAL dense fp8 figure "
+                            f"({NOMINAL_FP8_TFLOPS:.0f} TFLOP/s); the measured bf16 cuBLAS peaks are "
+                            f"{peaks['tflops_burst']:.0f} burst / {peaks['tflops_sustained']:.0f} sustained")
+    return res
+
+
+def tensor_parallel_config5(ctx, args, steps=3, warmup=2):
+    """BASELINE config 5 on this many GPUs: the 24B-class model, heads / feed-forward columns / logits columns
+    sharded, NCCL all-reduces hidden behind the next sequence group's kernels. Every rank runs the same 8 x 4096
+    tokens."""
+    bfb, launch = ctx.bfb, ctx.launch
+    cfg, batch, seq, precision, label = WORKLOADS["c5"]
+    ident = launch.broadcast_bytes(bfb.tp_unique_id() if ctx.rank == 0 else b"", 128, 0, ctx.dev)
+    bfb.tp_init(ident, ctx.rank, ctx.world)
+    model = build_model(ctx, dict(cfg), precision, True, args.seed, args.tp_groups, args.tp_reserved_sms)
+    ids = draw_ids(cfg, batch, seq, args.seed, 0)    # the same sequences on every rank
+    d_ids = bfb.DeviceBuffer.from_numpy(ids)
+    m = time_device_steps(ctx, model, d_ids, ids.shape, steps=steps, warmup=warmup, release_masters=True)
+    d_ids.free()
+    model.close()
+    bfb.tp_destroy()
+    bfb.check(bfb.lib().bfb_pool_trim())
+    g, a = flops_per_token(cfg, seq)
+    tokens = batch * seq
+    kern = m["kernels"]
+    busy = sum(k["ms_total"] for k in kern.values()) / steps
+    res = {"workload": label, "tokens_per_s": tokens / (m["ms_per_step"] / 1e3), "ms_per_step": m["ms_per_step"],
+           "model_tflops_per_gpu": (g + a) * tokens / (m["ms_per_step"] / 1e3) / 1e12 / ctx.world,
+           "gemm_tflops": kern.get("gemm_tcgen05", {}).get("tflops"),
+           "attention_tflops": kern.get("attention_tcgen05", {}).get("tflops"),
+           # what the step takes beyond its own kernels back to back on the compute stream: all-reduce time that
+           # is NOT hidden, plus launch gaps
+           "allreduce_exposed_ms": max(0.0, m["ms_per_step"] - busy), "kernel_ms_per_step": busy,
+           "allreduces_per_step": 2 * cfg["layers"] * max(args.tp_groups, 1),
+           "allreduce_bytes_per_step": 2 * cfg["layers"] * tokens * cfg["dim"] * 2,
+           "sequence_groups": args.tp_groups, "steps": steps, "warmup": warmup, "gpu_launches": m["launches"],
+           "scaling": "strong (the same batch on 2, 4 or 8 GPUs)"}
+    return res
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -365,11 +643,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--scaling", default="auto", choices=["auto", "strong", "weak"],
+                    help="batch-sharded workloads on N GPUs: strong = the workload's batch split over the ranks "
+                         "(32 -> 32/N sequences per GPU; the default), weak = the whole batch on every rank")
     ap.add_argument("--batch", type=int, default=0, help="sequences per GPU (default: the workload's)")
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (invalid as a headline number)")
     ap.add_argument("--e2e-steps", type=int, default=-1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the extra keys (attention_c2 and fp8 at 1 GPU; weak and tp_c5 at 2 or more)")
     ap.add_argument("--cpu-sample-seq", type=int, default=32,
                     help="tokens per worker and step of the reference arm's bounded sample")
     ap.add_argument("--cpu-baseline-seq", type=int, default=192,
@@ -415,166 +698,111 @@ def main():
     bfb.check(bfb.lib().bfb_set_device(local))
     if world > 1:
         launch.init_process_group("nccl")
-    dev = torch.device("cuda", local)
+    ctx = Ctx(bfb, launch, torch, rank, world, local)
+    dev = ctx.dev
+
+    tensor_parallel = args.workload in TENSOR_PARALLEL
+    if tensor_parallel and world < 2:
+        raise SystemExit(f"workload {args.workload} is tensor parallel: launch it on 2, 4 or 8 GPUs")
+    # batch-sharded workloads: strong scaling splits the workload's batch over the ranks, weak gives every rank all of it
+    scaling = "strong" if tensor_parallel else (args.scaling if args.scaling != "auto" else ("strong" if world > 1 else "weak"))
+    global_batch = batch
+    if tensor_parallel:
+        batch_per_gpu = batch
+    elif scaling == "strong" and world > 1:
+        if batch % world:
+            raise SystemExit(f"strong scaling needs the batch ({batch}) to divide by --gpus ({world})")
+        batch_per_gpu = batch // world
+    else:
+        batch_per_gpu, global_batch = batch, batch * world
 
     # ---- model and inputs --------------------------------------------------------------------------------
-    ops = lm_ops(**cfg)
-    model = bfb.Model(ops, precision=precision, random_init=False)
-    tensor_parallel = args.workload in TENSOR_PARALLEL
     if tensor_parallel:
-        if world < 2:
-            raise SystemExit(f"workload {args.workload} is tensor parallel: launch it on 2, 4 or 8 GPUs")
         ident = launch.broadcast_bytes(bfb.tp_unique_id() if rank == 0 else b"", 128, 0, dev)
         bfb.tp_init(ident, rank, world)
-        model.set_tensor_parallel(rank, world)
-        model.set_tensor_parallel_overlap(args.tp_groups, args.tp_reserved_sms if args.tp_groups > 1 else 0)
-        # weights drawn on the device (N(0, 0.01), the same full matrices whatever the split); the fp32 copies of
-        # the GEMM weights are dropped once the first forward has converted them
-        for i, _name in enumerate(model.param_names()):
-            model.fill_param_normal(i, args.seed * 1000003 + i, 0.01)
-    else:
-        synth_weights(bfb, model, args.seed, 0.02)
+    model = build_model(ctx, cfg, precision, tensor_parallel, args.seed, args.tp_groups, args.tp_reserved_sms)
     # batch-sharded ranks draw their own sequences; tensor-parallel ranks must all see the same ones
-    rng = np.random.Generator(np.random.PCG64([args.seed, 7919 + (0 if tensor_parallel else rank)]))
-    ids = rng.integers(0, cfg["vocab"], size=(batch, seq)).astype(np.float32)
+    ids = draw_ids(cfg, batch_per_gpu, seq, args.seed, 0 if tensor_parallel else rank)
     d_ids = bfb.DeviceBuffer.from_numpy(ids)
-    tokens_per_step = batch * seq
+    tokens_global = global_batch * seq
     if args.decode:
-        run_decode(args, bfb, launch, torch, model, cfg, batch, ids, precision, label, rank, world, local, dev)
+        run_decode(args, bfb, launch, torch, model, cfg, batch_per_gpu, ids, precision, label, rank, world, local, dev)
         return
 
-    def step_device():
-        out, shape = model.forward_device(d_ids.ptr, ids.shape, trusted=True)
-        out.free()   # back to the pool: the next step reuses the same memory
-        return shape
-
-    # ---- warm-up (first call converts the weights) -------------------------------------------------------
-    sampler = ClockSampler(local) if rank == 0 else None
-    out_shape = None
-    for i in range(max(args.warmup, 1)):
-        out_shape = step_device()
-        if i == 0 and tensor_parallel:
-            torch.cuda.synchronize()
-            model.release_master_weights()
-    torch.cuda.synchronize()
-
-    # ---- timed region: K steps, CUDA events on the launching (default) stream ------------------------------
-    bfb.lib().bfb_profile_reset()
-    bfb.lib().bfb_profile_enable(1)
-    bfb.lib().bfb_launch_count(1)
-    launch.barrier()
-    torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    wall_begin = time.time()
-    start.record()
-    for _ in range(args.steps):
-        step_device()
-    stop.record()
-    torch.cuda.synchronize()
-    wall_end = time.time()
-    launch.barrier()
-    elapsed_ms = launch.max_over_ranks(start.elapsed_time(stop), dev if world > 1 else None)
-    clocks = sampler.stop(wall_begin, wall_end) if sampler else None
-    launches = bfb.lib().bfb_launch_count(0)
-    bfb.lib().bfb_profile_enable(0)
-    kernels = {}
-    for name, kind in (("gemm_tcgen05", 0), ("attention_tcgen05", 1), ("rmsnorm", 2), ("embed_pos", 3), ("cast", 4)):
-        ms, n, work = profile_read(bfb, kind)
-        if n:
-            kernels[name] = {"ms_total": ms, "launches": n, "work": work}
-    bfb.lib().bfb_profile_reset()
-    ms_per_step = elapsed_ms / args.steps
-    replicas = 1 if tensor_parallel else world   # tensor-parallel ranks share one batch
-    value = replicas * tokens_per_step / (ms_per_step / 1e3)
+    # ---- timed region: ids in HBM, CUDA events on the launching stream ---------------------------------------
+    m = time_device_steps(ctx, model, d_ids, ids.shape, args.steps, args.warmup, release_masters=tensor_parallel,
+                          sample_clocks=True)
+    ms_per_step, kernels, elapsed_ms = m["ms_per_step"], m["kernels"], m["elapsed_ms"]
+    value = tokens_global / (ms_per_step / 1e3)
 
     # ---- end to end through the host-buffer API: ids H2D + logits D2H inside the timed region ---------------
     e2e = None
     e2e_steps = args.steps if args.e2e_steps < 0 else args.e2e_steps
     if e2e_steps > 0:
-        out_elems = int(np.prod(out_shape))
-        h_ids = torch.from_numpy(ids).pin_memory()
-        h_out = torch.empty(out_elems, dtype=torch.float32).pin_memory()
-        shape_arr = (C.c_int64 * 2)(*ids.shape)
-        oshape, orank = (C.c_int64 * 8)(), C.c_int32()
+        e2e = time_e2e(ctx, model, ids, m["out_shape"], e2e_steps, precision, tokens_global)
+        probe = d2h_probe(ctx)
+        bytes_per_token = e2e["d2h_bytes_per_step"] * (1 if tensor_parallel else world) / tokens_global
+        link_rate = probe["aggregate_gbs"] * 1e9 / bytes_per_token
+        e2e["ceiling"] = {"value": min(value, link_rate), "unit": "tokens/s",
+                          "formula": "min(device-timed tokens/s, aggregate pinned D2H GB/s of this host / result bytes per token)",
+                          "device_tokens_per_s": value, "d2h_aggregate_gbs": probe["aggregate_gbs"],
+                          "d2h_per_rank_gbs": probe["per_rank_gbs"], "d2h_bytes_per_token": bytes_per_token,
+                          "link_tokens_per_s": link_rate, "e2e_over_ceiling": e2e["value"] / min(value, link_rate),
+                          "probe": f"{probe['bytes_per_rank'] >> 20} MiB device -> pinned host on all {world} rank(s) at once"}
 
-        def step_host():
-            bfb.check(bfb.lib().bfb_model_forward_host(model._h, h_ids.data_ptr(), shape_arr, 2, h_out.data_ptr(), oshape,
-                                                       C.byref(orank)))
-
-        step_host()
-        launch.barrier()
-        torch.cuda.synchronize()
-        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s2.record()
-        for _ in range(e2e_steps):
-            step_host()
-        e2.record()
-        torch.cuda.synchronize()
-        launch.barrier()
-        e2e_ms = launch.max_over_ranks(s2.elapsed_time(e2), dev if world > 1 else None) / e2e_steps
-        # bytes the call itself booked for its copies: under storage bf16 part of the logits crosses the link as
-        # 2-byte bf16 and is widened to the caller's fp32 buffer by host threads
-        h2d_bytes, d2h_bytes = bfb.host_transfer_bytes()
-        e2e = {"value": replicas * tokens_per_step / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
-               "result_bytes_per_step": out_elems * 4, "steps": e2e_steps,
-               "api": "bfb_model_forward_host (fromHost -> Model::forward -> toHost), pinned host buffers"}
-        del h_out
-        # the same pipeline handing the logits to the host as bf16 (bfb_model_forward_host_bf16): not the reference's
-        # fp32 contract, reported beside it because it is what keeps several GPUs from saturating one host's memory
-        if (precision or {}).get("storage") == "bf16":
-            h_out16 = torch.empty(out_elems, dtype=torch.int16).pin_memory()
-
-            def step_host16():
-                bfb.check(bfb.lib().bfb_model_forward_host_bf16(model._h, h_ids.data_ptr(), shape_arr, 2, h_out16.data_ptr(),
-                                                                oshape, C.byref(orank)))
-
-            step_host16()
-            launch.barrier()
-            torch.cuda.synchronize()
-            s3, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s3.record()
-            for _ in range(e2e_steps):
-                step_host16()
-            e3.record()
-            torch.cuda.synchronize()
-            launch.barrier()
-            ms16 = launch.max_over_ranks(s3.elapsed_time(e3), dev if world > 1 else None) / e2e_steps
-            e2e["bf16_result"] = {"value": replicas * tokens_per_step / (ms16 / 1e3), "unit": "tokens/s", "ms_per_step": ms16,
-                                  "d2h_bytes_per_step": bfb.host_transfer_bytes()[1],
-                                  "api": "bfb_model_forward_host_bf16 (logits stay bf16 on the host)"}
-            del h_out16
+    # ---- extra keys: the other halves of the headline metric --------------------------------------------------
+    peaks = measured_peaks()
+    extras = {}
+    headline = args.workload == "c3" and not reduced and not args.no_extras
+    if headline and world > 1 and scaling == "strong":
+        # the weak-scaling figure beside it: every rank runs the whole 32 x 2048 batch
+        w_ids = draw_ids(cfg, batch, seq, args.seed, rank)
+        w_d = bfb.DeviceBuffer.from_numpy(w_ids)
+        wm = time_device_steps(ctx, model, w_d, w_ids.shape, steps=3, warmup=2)
+        w_d.free()
+        extras["weak"] = {"value": world * batch * seq / (wm["ms_per_step"] / 1e3), "unit": "tokens/s",
+                          "ms_per_step": wm["ms_per_step"], "batch_per_gpu": batch, "global_batch": batch * world,
+                          "steps": 3, "warmup": 2, "scaling": "weak"}
+    d_ids.free()
+    model.close()
+    bfb.check(bfb.lib().bfb_pool_trim())
+    if tensor_parallel:
+        bfb.tp_destroy()
+    if headline and world == 1:
+        for key, fn in (("attention_c2", lambda: attention_config2(ctx, peaks)),
+                        ("fp8", lambda: fp8_config4(ctx, args, peaks, ms_per_step))):
+            try:
+                extras[key] = fn()
+            except Exception as exc:   # an extra key must not cost the headline line
+                extras[key] = {"error": repr(exc)}
+    if headline and world > 1:
+        try:
+            extras["tp_c5"] = tensor_parallel_config5(ctx, args)
+        except Exception as exc:
+            extras["tp_c5"] = {"error": repr(exc)}
 
     if world > 1:
         launch.barrier()
-        if tensor_parallel:
-            bfb.tp_destroy()
         torch.distributed.destroy_process_group()
     if rank != 0:
         return
 
     # ---- roofline of the dominant kernel ---------------------------------------------------------------------
-    peaks = measured_peaks()
     g_flops, a_flops = flops_per_token(cfg, seq)
     roofline = None
     if "gemm_tcgen05" in kernels:
         k = kernels["gemm_tcgen05"]
-        achieved = k["work"] / (k["ms_total"] / 1e3) / 1e12
-        roofline = {"kernel": "gemmPairKernel (tcgen05 cta_group::2, 256x256 tiles per CTA pair, TMA-fed, TMEM accumulators)", "bound": "tensor",
-                    "achieved": achieved, "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
-                    "frac": achieved / peaks["tflops_sustained"], "peak_source": f"of {peaks['source']} (sustained cuBLAS bf16)",
+        fp8 = (precision or {}).get("compute") == "fp8.e4m3"
+        peak = NOMINAL_FP8_TFLOPS if fp8 else peaks["tflops_sustained"]
+        roofline = {"kernel": "gemmPairKernel (tcgen05 cta_group::2, 256x256 tiles per CTA pair, TMA-fed, TMEM accumulators)",
+                    "bound": "tensor", "achieved": k["tflops"], "peak": peak, "unit": "TFLOP/s", "frac": k["tflops"] / peak,
+                    "peak_source": ("of NOMINAL dense fp8 (no fp8 peak was measured on this pool)" if fp8 else
+                                    f"of {peaks['source']} (sustained cuBLAS bf16)"),
                     "launches": k["launches"], "avg_launch_ms": k["ms_total"] / k["launches"],
                     "share_of_step": k["ms_total"] / elapsed_ms,
                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.workload)}
-    for name, k in kernels.items():
-        secs = k["ms_total"] / 1e3
-        if name in ("gemm_tcgen05", "attention_tcgen05"):
-            k["tflops"] = k["work"] / secs / 1e12
-        else:
-            k["gbs"] = k["work"] / secs / 1e9
-        k["share_of_step"] = k["ms_total"] / elapsed_ms
     # per GPU: a tensor-parallel rank does 1/world of the batch's arithmetic
-    model_tflops = (g_flops + a_flops) * tokens_per_step / (ms_per_step / 1e3) / 1e12 / (world if tensor_parallel else 1)
+    model_tflops = (g_flops + a_flops) * tokens_global / (ms_per_step / 1e3) / 1e12 / world
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
@@ -586,25 +814,27 @@ def main():
     line = {
         "metric": "prefill tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 1), "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "strong" if tensor_parallel else "weak",
+        "scaling": scaling,
         "vs_baseline": None, "dtype": "bf16" if (precision or {}).get("compute") == "bf16" else
         ("fp8.e4m3" if (precision or {}).get("compute") == "fp8.e4m3" else "f32"),
         "data": f"synthetic (seeded uniform token ids, N(0,{'0.01' if tensor_parallel else '0.02'}) weights)",
-        "config": {"workload": label, "global_batch": batch * replicas, "batch_per_gpu": batch, "seq_len": seq,
+        "config": {"workload": label, "global_batch": global_batch, "batch_per_gpu": batch_per_gpu, "seq_len": seq,
                    "precision": precision,
                    "parallelism": (f"tensor-parallel x{world}: heads, feed-forward columns and logits columns sharded, "
                                    "NCCL all-reduce after the out-projection and the feed-forward down-projection"
                                    + (f", {args.tp_groups} sequence groups: one group's all-reduce runs beside the next "
                                       f"group's kernels, whose GEMMs draw their tiles dynamically ({args.tp_reserved_sms} SMs left free)" if args.tp_groups > 1 else "")
-                                   if tensor_parallel else f"batch-sharded x{world}, no data-path collective"),
+                                   if tensor_parallel else
+                                   f"batch-sharded x{world} ({batch_per_gpu} sequences per GPU), no data-path collective"),
                    "l2": "per-step working set (weights and activations, GBs) far exceeds the 126 MB L2; no flush needed",
                    "flops_per_token": g_flops + a_flops},
         "model_tflops": model_tflops,
         "model_frac_of_peak": {"measured_sustained": model_tflops / peaks["tflops_sustained"],
                                "nominal_2250": model_tflops / 2250.0},
-        "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
-        "clocks": clocks, "peaks": peaks,
+        "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": m["launches"],
+        "clocks": m["clocks"], "peaks": peaks,
     }
+    line.update(extras)
     print(json.dumps(line))
 
 

@@ -126,6 +126,9 @@ SIGNATURES = {
     "bfb_profile_reset": (_I32, []),
     "bfb_profile_read": (_I32, [_I32, C.POINTER(C.c_double), C.POINTER(_I64), C.POINTER(C.c_double)]),
     "bfb_synthetic_input": (_I32, [C.POINTER(OpDesc), _I32, C.POINTER(_I64), _I32, _I64, C.c_uint32, _P]),
+    "bfb_selftest_bounded_wait": (_I32, [C.c_uint64, C.POINTER(_I32), _P]),
+    "bfb_pool_fail_after": (_I32, [_I64]),
+    "bfb_selftest_collective_watchdog": (_I32, [_I32, _I32, _I64, C.POINTER(_I32), C.POINTER(_I32)]),
     "bfb_tp_unique_id": (_I32, [_P]),
     "bfb_tp_init": (_I32, [_P, _I32, _I32]),
     "bfb_tp_allreduce_sum": (_I32, [_P, _I64, _I32, _P]),

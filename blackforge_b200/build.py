@@ -30,11 +30,13 @@ SOURCES = [
     "attention_simt.cu",
     "attention_tc.cu",
     "attention_decode.cu",
+    "selftest.cu",
     "capi.cu",
     "host/ops.cpp",
     "host/model.cpp",
     "host/tp.cpp",
     "host/widen.cpp",
+    "host/watchdog.cpp",
     "host/checkpoint.cpp",
 ]
 

@@ -11,6 +11,7 @@
 #include "common.cuh"
 #include "host/bfb200.hpp"
 #include "host/tp.hpp"
+#include "host/watchdog.hpp"
 #include "host/widen.hpp"
 #include "kernels.hpp"
 #include "pool.hpp"
@@ -934,6 +935,32 @@ bfb_status bfb_synthetic_input(const bfb_op_desc* ops, int32_t n_ops, const int6
 }
 
 // ---- tensor parallel ------------------------------------------------------------------------------------
+
+bfb_status bfb_selftest_bounded_wait(uint64_t limit_ns, int32_t* h_observed, void* stream) {
+    return guarded([&] {
+        int observed[3] = {0, 0, 0};
+        const int code = bfb::selfTestBoundedWait(limit_ns, observed, asStream(stream));
+        if (h_observed != nullptr) {
+            for (int i = 0; i < 3; ++i) h_observed[i] = observed[i];
+        }
+        bfb::failOnDeviceStatus(code);
+    });
+}
+
+bfb_status bfb_pool_fail_after(int64_t nth) {
+    return guarded([&] { bfb::poolFailAfter(nth); });
+}
+
+bfb_status bfb_selftest_collective_watchdog(int32_t ranks, int32_t skip_rank, int64_t timeout_ms, int32_t* timed_out,
+                                            int32_t* sum_ok) {
+    return guarded([&] {
+        require(ranks >= 1 && ranks <= 16 && skip_rank < ranks && timeout_ms >= 0, "selftest_collective_watchdog: bad arguments");
+        bool ok = false;
+        const int n = bfb200::watchdogSelfTest(ranks, skip_rank, timeout_ms, &ok);
+        if (timed_out != nullptr) *timed_out = n;
+        if (sum_ok != nullptr) *sum_ok = ok ? 1 : 0;
+    });
+}
 
 bfb_status bfb_tp_unique_id(void* h_id_128) {
     return guarded([&] { bfb200::tpUniqueId(h_id_128); });

@@ -67,6 +67,13 @@ bfb_status guarded(Fn&& fn) noexcept {
     }
 }
 
+// The status word a tensor-core kernel leaves behind (0 = ok): anything else means one of its bounded waits ran out.
+inline void failOnDeviceStatus(int code) {
+    if (code != 0) {
+        fail(BFB_TIMEOUT, "a bounded wait inside a tensor-core kernel ran out (device code " + std::to_string(code) + ")");
+    }
+}
+
 inline cudaStream_t asStream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
 inline size_t dtypeBytes(int32_t dtype) {

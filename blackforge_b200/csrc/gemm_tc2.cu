@@ -239,6 +239,54 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
         }
     } else if (warp == 1 && leader) {
         // ---------------- MMA issuer (leader CTA only) ----------------
+#ifdef BFB_GEMM_ELECT
+        // One elected thread runs the role (the compiler then keeps descriptors in uniform registers), and the
+        // descriptors of a stage are its base words plus constants: one integer add per operand and MMA.
+        if (tileCounter == nullptr && elect_one()) {
+            constexpr uint32_t kHi = smem_desc_hi_sw128(1024);
+            const uint32_t stage0Lo = smem_desc_lo(smem_u32(smem), 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool alive = true;
+            for (int t = staticNext; t < totalTiles && alive; t += numClusters, ++local) {
+                const int buf = local % kBufs;
+                const uint32_t accPhase = static_cast<uint32_t>(local / kBufs) & 1u;
+                if (!mbar_wait(&accEmptyBar[buf], accPhase ^ 1u, abortFlag, status, kDevTimeoutAccEmpty)) break;
+                tc_fence_after();
+                const uint32_t dTmem = tmemBase + static_cast<uint32_t>(buf * kAccN);
+                for (int kb = 0; kb < numK; ++kb) {
+                    if (!mbar_wait(&fullBar[stage], phase, abortFlag, status, kDevTimeoutTmaFull)) {
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t aLo = stage0Lo + static_cast<uint32_t>(stage) * (kStageBytes >> 4);
+                    const uint32_t bLo = aLo + (kABytes2 >> 4);
+#pragma unroll
+                    for (int kk = 0; kk < kMmaPerStage; ++kk) {
+                        const uint32_t step = static_cast<uint32_t>((kk * 32) >> 4);
+                        const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
+#pragma unroll
+                        for (int h = 0; h < kHalves; ++h) {
+                            const uint32_t bh = bLo + static_cast<uint32_t>(h * ((128 * kRowBytes2) >> 4)) + step;
+                            const uint32_t d = dTmem + static_cast<uint32_t>(h * 256);
+                            if constexpr (kElemBytes == 2) umma_f16_pair_words(d, aLo + step, kHi, bh, kHi, kIdesc, acc);
+                            else umma_f8_pair_words(d, aLo + step, kHi, bh, kHi, kIdesc, acc);
+                        }
+                    }
+                    umma_commit_pair(&emptyBar[stage]);
+                    if (kb == numK - 1) umma_commit_pair(&accFullBar[buf]);
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (tileCounter != nullptr) {
+#endif
         int stage = 0;
         uint32_t phase = 0;
         int local = 0;
@@ -281,6 +329,9 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
                 }
             }
         }
+#ifdef BFB_GEMM_ELECT
+        }
+#endif
     } else if (warp >= 4) {
         // ---------------- epilogue (both CTAs, 8 warps: lane quarter x column half) ----------------
         constexpr int kColsPerWarp = kAccN / 2;

@@ -473,14 +473,13 @@ void Model::Impl::prepare(cudaStream_t stream) {
 void Model::Impl::checkStatus(cudaStream_t stream, bool checkIds, std::size_t vocab) {
     int host[2] = {0, 0};
     BFB_CUDA(cudaMemcpyAsync(host, status.ptr, sizeof(host), cudaMemcpyDeviceToHost, stream));
-    BFB_CUDA(cudaStreamSynchronize(stream));
+    if (tpWorld > 1) tpSynchronize(stream);   // with a deadline: a collective may wait for a rank that never comes
+    else BFB_CUDA(cudaStreamSynchronize(stream));
     if (checkIds && host[1] != 0) {
         throw std::invalid_argument("embeddingLookup: " + std::to_string(host[1]) +
                                     " token id(s) outside the vocabulary [0, " + std::to_string(vocab) + ")");
     }
-    if (host[0] != 0) {
-        fail(BFB_TIMEOUT, "a bounded wait inside a tensor-core kernel ran out (device code " + std::to_string(host[0]) + ")");
-    }
+    bfb::failOnDeviceStatus(host[0]);
 }
 
 // ---- exactness route: op by op on fp32 tensors ----------------------------------------------------------
@@ -589,11 +588,21 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
     std::size_t vocabForCheck = 0;
     const std::size_t oldLen = incremental ? genPosition : 0;   // positions already cached
     std::size_t cacheHint = 0;                                 // the positional table's length, when there is one
+    // e4m3 operands: one block of four floats [amax/scale, inverse, alpha, -] per quantised GEMM input. An attention
+    // or feed-forward layer quantises two inputs per group of sequences, any other layer at most one; the group count
+    // is at most tpChunks (and 1 outside tensor-parallel prompt passes).
     int fp8Slot = 0;
+    int fp8SlotLimit = 0;
     if (fp8) {
-        fp8Stats.ensure(layers.size() * 4 * 4 * sizeof(float));
+        const std::size_t maxGroups = (tpWorld > 1 && !incremental) ? static_cast<std::size_t>(std::max(tpChunks, 1)) : 1;
+        fp8SlotLimit = static_cast<int>((layers.size() * 2 + 1) * maxGroups);
+        fp8Stats.ensure(static_cast<std::size_t>(fp8SlotLimit) * 4 * sizeof(float));
         BFB_CUDA(cudaMemsetAsync(fp8Stats.ptr, 0, fp8Stats.bytes, stream));
     }
+    auto nextFp8Stats = [&]() -> float* {
+        require(fp8Slot < fp8SlotLimit, "Model: more quantised GEMM inputs than scale slots");
+        return static_cast<float*>(fp8Stats.ptr) + 4 * (fp8Slot++);
+    };
 
     // A-operand of a GEMM from a bf16 activation: the buffer itself (bf16) or an e4m3 copy with a fresh
     // per-tensor scale; returns the device alpha pointer for fp8 (1 / (scale_a * scale_w)).
@@ -603,7 +612,7 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
             *dAlpha = nullptr;
             return act16;
         }
-        float* st = static_cast<float*>(fp8Stats.ptr) + 4 * (fp8Slot++);  // [0]=scale [1]=inverse [2]=alpha
+        float* st = nextFp8Stats();  // [0]=scale [1]=inverse [2]=alpha
         void* a8 = buf(name, count);
         const int64_t n = static_cast<int64_t>(count);
         float* scratch = static_cast<float*>(
@@ -615,7 +624,7 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
     // e4m3 A-operand of the GEMM that follows an rmsnorm, straight from the bf16 residual stream: the norm and
     // the quantisation in two passes over x, without a normalised copy in between
     auto normedFp8Input = [&](std::size_t tokens, std::size_t d, const float* wScales, const float** dAlpha) -> const void* {
-        float* st = static_cast<float*>(fp8Stats.ptr) + 4 * (fp8Slot++);
+        float* st = nextFp8Stats();
         void* a8 = buf("act8_d", tokens * d);
         float* scratch = static_cast<float*>(
             buf("norm_quant", static_cast<std::size_t>(bfb::rmsnormQuantizeScratchFloats(static_cast<int64_t>(tokens))) *
@@ -916,7 +925,7 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                 }
                 const void* a2 = nullptr;
                 if (hiddenMaxima != nullptr) {
-                    float* st = static_cast<float*>(fp8Stats.ptr) + 4 * (fp8Slot++);
+                    float* st = nextFp8Stats();
                     void* a8 = buf("act8_f", tokens * fl);
                     const int64_t count = static_cast<int64_t>(((fl + 127) / 128) * tokens);
                     float* scratch = static_cast<float*>(
@@ -991,7 +1000,12 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                     case BFB_OP_GELU: out = gelu(tmp); break;
                     case BFB_OP_RMSNORM: out = rmsnorm(tmp); break;
                     case BFB_OP_SOFTMAX: out = softmax(tmp); break;
-                    case BFB_OP_POSITIONAL_EMBEDDING: out = addPositionalEmbedding(tmp, params[l.p[0]].value); break;
+                    case BFB_OP_POSITIONAL_EMBEDDING:
+                        // positions continue after the cached ones (the reference's forwardIncremental uses
+                        // addPositionalEmbeddingAt with its generation position); the call checks the table's length
+                        out = addPositionalEmbeddingAt(tmp, params[l.p[0]].value, oldLen);
+                        cacheHint = params[l.p[0]].value.dim(0);
+                        break;
                     default: fail(BFB_UNSUPPORTED, "Model: operation not available on the device");
                 }
                 BFB_CUDA(cudaStreamSynchronize(nullptr));

@@ -3,10 +3,12 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
 #include "../common.cuh"
+#include "watchdog.hpp"
 
 namespace bfb200 {
 
@@ -18,6 +20,8 @@ struct NcclApi {
     ncclResult_t (*commInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*allReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*commDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*commAbort)(ncclComm_t) = nullptr;
+    ncclResult_t (*commGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
     const char* (*getErrorString)(ncclResult_t) = nullptr;
 };
 
@@ -36,6 +40,8 @@ NcclApi& api() {
     a.commInitRank = reinterpret_cast<decltype(a.commInitRank)>(sym("ncclCommInitRank"));
     a.allReduce = reinterpret_cast<decltype(a.allReduce)>(sym("ncclAllReduce"));
     a.commDestroy = reinterpret_cast<decltype(a.commDestroy)>(sym("ncclCommDestroy"));
+    a.commAbort = reinterpret_cast<decltype(a.commAbort)>(sym("ncclCommAbort"));
+    a.commGetAsyncError = reinterpret_cast<decltype(a.commGetAsyncError)>(sym("ncclCommGetAsyncError"));
     a.getErrorString = reinterpret_cast<decltype(a.getErrorString)>(sym("ncclGetErrorString"));
     return a;
 }
@@ -87,5 +93,52 @@ void tpDestroy() {
 }
 
 bool tpReady() { return gComm != nullptr; }
+
+std::int64_t tpTimeoutMs() {
+    if (const char* e = std::getenv("BFB_TP_TIMEOUT_MS")) {
+        const long long v = std::atoll(e);
+        if (v > 0) return static_cast<std::int64_t>(v);
+    }
+    return 120000;
+}
+
+void tpSynchronize(void* stream) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (gComm == nullptr) {
+        BFB_CUDA(cudaStreamSynchronize(s));
+        return;
+    }
+    WatchdogHooks hooks;
+    cudaError_t queryError = cudaSuccess;
+    hooks.query = [&] {
+        const cudaError_t e = cudaStreamQuery(s);
+        if (e == cudaSuccess) return 0;
+        if (e == cudaErrorNotReady) return 1;
+        queryError = e;
+        return 2;
+    };
+    hooks.asyncError = [&] {
+        ncclResult_t state = ncclSuccess;
+        if (api().commGetAsyncError(gComm, &state) != ncclSuccess) return 1;
+        return (state == ncclSuccess || state == ncclInProgress) ? 0 : 1;
+    };
+    hooks.abort = [&] {
+        // frees the communicator and makes its kernels on the device give up; the process group is gone afterwards
+        api().commAbort(gComm);
+        gComm = nullptr;
+        gWorld = 1;
+    };
+    const std::int64_t limit = tpTimeoutMs();
+    switch (waitWithDeadline(hooks, limit)) {
+        case WatchdogOutcome::Completed: return;
+        case WatchdogOutcome::TimedOut:
+            bfb::fail(BFB_TIMEOUT, "tensor parallelism: the step did not finish within " + std::to_string(limit) +
+                                       " ms (a rank is missing from a collective?); the communicator was aborted");
+        case WatchdogOutcome::AsyncError:
+            bfb::fail(BFB_CUDA_ERROR, "tensor parallelism: the communicator reported an asynchronous error and was aborted");
+        case WatchdogOutcome::QueryError:
+            bfb::fail(BFB_CUDA_ERROR, std::string("tensor parallelism: stream query failed: ") + cudaGetErrorString(queryError));
+    }
+}
 
 }  // namespace bfb200

@@ -13,5 +13,10 @@ void tpInit(const void* hostId128, int rank, int world);
 void tpAllReduceSum(void* deviceBuffer, std::int64_t count, int dtype, void* stream);
 void tpDestroy();
 bool tpReady();
+// Waits for `stream` like cudaStreamSynchronize, but with a deadline (BFB_TP_TIMEOUT_MS, default 120 s) while a
+// communicator exists: polls the stream and the communicator's asynchronous error state and aborts the communicator
+// when the deadline passes or it reports an error (BFB_TIMEOUT / BFB_CUDA_ERROR), so that a rank that is missing
+// from a collective cannot block the others for ever. Without a communicator it is a plain synchronize.
+void tpSynchronize(void* stream);
 
 }  // namespace bfb200

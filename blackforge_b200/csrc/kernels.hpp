@@ -129,6 +129,9 @@ void gemmTensorCore(const GemmArgs& args, cudaStream_t stream);
 void gemmTensorCorePair(const GemmArgs& args, cudaStream_t stream);
 void attentionTensorCore(const AttentionArgs& args, cudaStream_t stream);
 
+// Bounded-wait self-test (selftest.cu): device status code of a wait that was made to run out after `limitNs`.
+int selfTestBoundedWait(unsigned long long limitNs, int* observedHost, cudaStream_t stream);
+
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda dependency).
 // dims/strides innermost first; strides in bytes for dims 1..rank-1; elemBytes 1 or 2.
 struct TensorMapStorage {

@@ -159,8 +159,18 @@ int currentDevice() {
 
 }  // namespace
 
+namespace {
+std::atomic<long long> gFailCountdown{0};
+}
+
+void poolFailAfter(long long nth) { gFailCountdown.store(nth > 0 ? nth : 0); }
+
 void* poolAcquire(size_t bytes) {
     if (bytes == 0) return nullptr;
+    if (gFailCountdown.load(std::memory_order_relaxed) > 0 && gFailCountdown.fetch_sub(1) == 1) {
+        fail(BFB_CUDA_ERROR, "device pool: allocation of " + std::to_string(bytes) +
+                                 " bytes failed (failure injected by bfb_pool_fail_after)");
+    }
     int dev = currentDevice();
     {
         std::lock_guard<std::mutex> lock(gPoolMutex);

@@ -11,4 +11,7 @@ void poolRelease(void* ptr, size_t bytes) noexcept;  // same `bytes` as the acqu
 void poolTrim();
 void poolStats(size_t* cachedBytes, size_t* liveBytes);
 
+// Fault injection for tests, on the host only: the `nth` acquisition from now on (1 = the next one), on any thread,
+// fails as an exhausted device would (BFB_CUDA_ERROR) without touching the device; 0 disarms. One shot.
+void poolFailAfter(long long nth);
 }  // namespace bfb

@@ -64,9 +64,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr uint64_t kWaitLimitNs = 1500ull * 1000ull * 1000ull;
 
 // Bounded wait. `abort_flag` lives in shared memory and is set by whichever thread times out first,
-// so the other roles stop waiting promptly. Returns false when the wait was abandoned.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int code) {
+// so the other roles stop waiting promptly. Returns false when the wait was abandoned. `limit_ns` is the longest
+// time this one wait may take; kernels use kWaitLimitNs, the self-test of this mechanism a much shorter one.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                int code, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t start = global_timer_ns();
     uint32_t spins = 0;
@@ -74,13 +75,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 255u) == 0u) {
             if (*abort_flag != 0) return false;
-            if (global_timer_ns() - start > kWaitLimitNs) {
+            if (global_timer_ns() - start > limit_ns) {
                 *abort_flag = 1;
                 if (status != nullptr) atomicCAS(status, 0, code);
                 return false;
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          int code) {
+    return mbar_wait_limit(bar, parity, abort_flag, status, code, kWaitLimitNs);
 }
 
 // The same wait with acquire semantics at cluster scope: for data another CTA of the cluster wrote to this CTA's
@@ -372,6 +377,34 @@ __device__ __forceinline__ void umma_f16_ts_words(uint32_t d_tmem, uint32_t a_tm
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
         "}\n" ::"r"(d_tmem),
         "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair_words(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                    uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        ".reg .b64 da, db;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f8_pair_words(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                   uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        ".reg .b64 da, db;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], da, db, %5, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // 32 lanes x 16 columns of 32-bit: thread t of the warp writes lane (base lane + t), 16 consecutive columns.

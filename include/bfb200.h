@@ -188,8 +188,12 @@ bfb_status bfb_rmsnorm_quantize_e4m3(const void* d_x, int64_t rows, int64_t dim,
  * process exits. Limits and rules:
  *  - n <= 536 870 912 elements (65 536 partial maxima of 8192 elements each); larger n is refused with
  *    BFB_INVALID_ARGUMENT and nothing is launched.
- *  - The first call on each device looks up the array's device address (once, with that device current);
- *    make that first call before starting any stream capture.
+ *  - The first call on each device looks up the array's device address (once, with that device current), and if
+ *    the CUDA runtime loads modules lazily it is also the call that loads this library's kernels onto the device,
+ *    which the driver may back with memory of its own. So make one warm-up call per device at start-up, before the
+ *    phase in which nothing may allocate and before starting any stream capture.
+ *  - The looked-up address is kept for the life of the process: after cudaDeviceReset() on a device this entry
+ *    point must not be used on it again.
  *  - All calls on a device share the one array. It keeps the previous call's values, which is harmless because
  *    each call overwrites every slot it later reads; but two calls whose kernels overlap on the GPU (different
  *    streams) race on it. Keep calls to this entry point on one stream, or order them yourself. */
@@ -433,6 +437,29 @@ bfb_status bfb_profile_read(int32_t kind, double* milliseconds, int64_t* launche
 /* Executor::makeSyntheticInput (executor.cu:26-42): seeded ids/values, host side. */
 bfb_status bfb_synthetic_input(const bfb_op_desc* ops, int32_t n_ops, const int64_t* input_shape, int32_t rank,
                                int64_t batch, uint32_t seed, float* h_out);
+
+/* ---- failure paths, exercised without harming a device --------------------------------------------
+ * The reference turns every failed CUDA / cuBLAS call into std::runtime_error
+ * (include/blackforge/backend/cuda/cuda_check.hpp:14-53) and has no waits that can time out. This library's
+ * tensor-core kernels wait on barriers with a time limit and report through a status word, its device pool can
+ * run out, and its collectives can lose a rank; these entry points let a test take each of those paths on purpose.
+ *
+ * bfb_selftest_bounded_wait: launches a one-CTA kernel in which one role waits on a barrier nobody arrives on,
+ * through the same bounded wait the kernels use but with `limit_ns` (1 us .. 1 s) as its limit; it gives up, flags
+ * the other role (which then leaves long before its own, ordinary limit), the CTA frees its tensor memory and
+ * returns. Nothing traps and the context stays usable. Returns BFB_TIMEOUT, as Model::forward does for a kernel
+ * whose wait ran out (BFB_OK would mean the wait did not expire). h_observed (3 ints, may be null) receives
+ * {first wait succeeded, second wait succeeded, microseconds the second role waited}.
+ * bfb_pool_fail_after: host-only fault injection; the nth bfb_pool_acquire / internal pool acquisition from now on
+ * (1 = the next) fails with BFB_CUDA_ERROR as an exhausted device would; 0 disarms. One shot.
+ * bfb_selftest_collective_watchdog: host only, no device. `ranks` threads run a stand-in all-reduce of host values
+ * guarded by the watchdog that also guards the tensor-parallel step (poll, look for an asynchronous error, abort at
+ * the deadline); rank `skip_rank` never joins (-1: all join). *timed_out = ranks that gave up and aborted,
+ * *sum_ok = 1 when every rank that completed saw the right sum. */
+bfb_status bfb_selftest_bounded_wait(uint64_t limit_ns, int32_t* h_observed, void* stream);
+bfb_status bfb_pool_fail_after(int64_t nth);
+bfb_status bfb_selftest_collective_watchdog(int32_t ranks, int32_t skip_rank, int64_t timeout_ms, int32_t* timed_out,
+                                            int32_t* sum_ok);
 
 /* ---- tensor-parallel communicator (NCCL over NVLink) -------------------------------------------
  * No counterpart in the reference (its only multi-GPU code is host-staged gradient averaging,

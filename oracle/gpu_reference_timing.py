@@ -4,6 +4,13 @@ beside this repository's forward on the same GPU, the same model and the same to
 
     python -m oracle.gpu_reference_timing [--batch 4] [--seq 2048] [--layers 16]
     python -m oracle.gpu_reference_timing --decode [--batch 32] [--context 1920] [--steps 4]
+    python -m oracle.gpu_reference_timing --gemm [--rows 65536] [--seconds 1.0]
+
+The first form also reports how far the two sets of logits are apart (largest difference over the largest logit, raw
+top-1 agreement, agreement on the positions the reference decides by more than 2e-2 of the largest logit). `--gemm`
+times the library call the reference's bf16Gemm makes (cublasLtMatmul with its settings, ops_tensorcore.cu:156-304)
+beside this repository's tcgen05 GEMM on the five GEMM shapes of the 2B-class step, each for about a second of
+back-to-back launches (so both run at the clocks the power cap allows), alternating, with the SM clock sampled.
 
 The reference keeps the activations of every layer for its backward pass and an fp32 gradient beside every weight, so
 it holds a slice of the headline batch (4 of the 32 sequences by default), not all of it. Both sides use their seeded
@@ -29,9 +36,14 @@ def main():
     ap.add_argument("--decode", action="store_true", help="time single-token generation steps after a prompt instead")
     ap.add_argument("--context", type=int, default=1920)
     ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--gemm", action="store_true", help="cublasLtMatmul as the reference calls it against the tcgen05 GEMM")
+    ap.add_argument("--rows", type=int, default=65536, help="--gemm: rows of A (tokens of a step)")
+    ap.add_argument("--seconds", type=float, default=1.0, help="--gemm: length of each timed run")
     args = ap.parse_args()
     if args.decode:
         return decode(args)
+    if args.gemm:
+        return gemm_ab(args)
 
     import torch
     import blackforge_b200 as bfb
@@ -44,6 +56,7 @@ def main():
 
     ref = ref_lib.CudaModel(O.lm_source(seq=args.seq, **cfg), seed=42, precision=policy)
     ref_ms = ref.forward_timed(ids, warmup=1, iters=args.iters)
+    ref_logits = ref.forward(ids)
     ref.close()
 
     ours = bfb.Model(O.lm_ops(**cfg), seed=42, precision={"storage": "bf16", "compute": "bf16"})
@@ -61,9 +74,113 @@ def main():
     torch.cuda.synchronize()
     our_ms = a.elapsed_time(b) / args.iters
     tokens = args.batch * args.seq
+    got = ours.forward_host(ids)
+    scale = float(np.max(np.abs(ref_logits)))
+    top2 = np.sort(ref_logits, axis=-1)[..., -2:]
+    decided = (top2[..., 1] - top2[..., 0]) > 2e-2 * scale
+    agree = np.argmax(got, axis=-1) == np.argmax(ref_logits, axis=-1)
+    diff = {"max_abs_over_max": float(np.max(np.abs(got - ref_logits))) / scale, "top1_raw": float(agree.mean()),
+            "decided_fraction": float(decided.mean()),
+            "top1_decided": float(agree[decided].mean()) if decided.any() else None}
     print(json.dumps({"model": cfg, "batch": args.batch, "seq": args.seq,
                       "reference_cuda_ms": ref_ms, "reference_cuda_tokens_per_s": tokens / (ref_ms / 1e3),
-                      "this_ms": our_ms, "this_tokens_per_s": tokens / (our_ms / 1e3), "ratio": ref_ms / our_ms}))
+                      "this_ms": our_ms, "this_tokens_per_s": tokens / (our_ms / 1e3), "ratio": ref_ms / our_ms,
+                      "logits_vs_reference": diff}))
+
+
+def gemm_ab(args):
+    import subprocess
+    import torch
+    import blackforge_b200 as bfb
+    from oracle import ref_lib
+
+    lib = bfb.lib()
+    m = args.rows
+    # (name, n, k, C format of the step's launch)
+    shapes = [("out-projection", 2048, 2048, "bf16"), ("QKV", 6144, 2048, "bf16"), ("feed-forward up", 5632, 2048, "bf16"),
+              ("feed-forward down", 2048, 5632, "bf16"), ("logits", 32000, 2048, "f32")]
+
+    def rand_bf16(count, scale):
+        t = torch.randn(count, device="cuda", dtype=torch.float32) * scale
+        buf = bfb.DeviceBuffer(count * 2)
+        bfb.check(lib.bfb_cast(t.data_ptr(), bfb.F32, buf.ptr, bfb.BF16, count, 1.0, None, None))
+        torch.cuda.synchronize()
+        return buf
+
+    # SM clock samples every 100 ms for the whole run, read by a thread; a timed run takes the median of its window
+    import statistics
+    import threading
+    import time
+    samples = []
+    try:
+        smi = subprocess.Popen(["nvidia-smi", "-i", "0", "--query-gpu=clocks.sm", "--format=csv,noheader,nounits", "-lms", "100"],
+                               stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+
+        def reader():
+            for line in smi.stdout:
+                try:
+                    samples.append((time.time(), float(line.strip())))
+                except ValueError:
+                    pass
+        threading.Thread(target=reader, daemon=True).start()
+    except OSError:
+        smi = None
+
+    def clocked(fn):
+        t0 = time.time()
+        ms = fn()
+        t1 = time.time()
+        time.sleep(0.12)
+        inside = [v for (t, v) in samples if t0 + 0.2 <= t <= t1]
+        return ms, (statistics.median(inside) if inside else None)
+
+    status = bfb.DeviceBuffer.zeros(4)
+    rows = []
+    for name, n, k, cfmt in shapes:
+        a = rand_bf16(m * k, 1.0)
+        w_nk = rand_bf16(n * k, 0.02)      # this repository's layout: W^T [n, k]
+        w_kn = rand_bf16(k * n, 0.02)      # the reference's layout: W [k, n]
+        c = bfb.DeviceBuffer(m * n * 4)         # large enough for either result format
+        cd = bfb.BF16 if cfmt == "bf16" else bfb.F32
+        flops = 2.0 * m * n * k
+
+        def ours(iters):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(iters):
+                bfb.check(lib.bfb_gemm(a.ptr, w_nk.ptr, c.ptr, m, n, k, bfb.BF16, bfb.B_NK, cd, bfb.EPI["none"], None, None,
+                                       1.0, None, 0, status.ptr, None))
+            e.record()
+            torch.cuda.synchronize()
+            return s.elapsed_time(e) / iters
+
+        def theirs(iters, c_bf16):
+            return ref_lib.cuda_lt_gemm_timed(a.ptr, w_kn.ptr, c.ptr, m, n, k, c_bf16, 0, iters)
+
+        est = max(ours(3), 1e-3)
+        iters = max(3, int(args.seconds * 1e3 / est))
+        entry = {"gemm": name, "m": m, "n": n, "k": k, "c": cfmt, "iters": iters}
+        # alternate so that neither side always runs on the warmer chip; the clock is read right after each run
+        for rep in range(2):
+            t, mhz = clocked(lambda: ours(iters))
+            entry.setdefault("this_tflops", []).append(flops / (t / 1e3) / 1e12)
+            entry.setdefault("this_sm_mhz", []).append(mhz)
+            t, mhz = clocked(lambda: theirs(iters, cfmt == "bf16"))
+            entry.setdefault("cublaslt_tflops", []).append(flops / (t / 1e3) / 1e12)
+            entry.setdefault("cublaslt_sm_mhz", []).append(mhz)
+        if cfmt == "bf16":
+            t, mhz = clocked(lambda: theirs(iters, False))
+            entry["cublaslt_f32_result_tflops"] = flops / (t / 1e3) / 1e12   # the reference's own result format
+        entry["ratio"] = max(entry["this_tflops"]) / max(entry["cublaslt_tflops"])
+        rows.append(entry)
+        for buf in (a, w_nk, w_kn, c):
+            buf.free()
+        bfb.check(lib.bfb_pool_trim())
+    if smi is not None:
+        smi.terminate()
+    print(json.dumps({"rows_of_a": m, "seconds_per_run": args.seconds, "gemms": rows,
+                      "note": "cublasLtMatmul with the reference's settings (row-major bf16 A [m,k] and B [k,n], fp32 "
+                              "compute, heuristic top-1, 4 MiB workspace); this repository's kernel reads W^T [n,k]"}))
 
 
 def decode(args):

@@ -9,6 +9,8 @@
 // Conventions as in ref_shim.cpp: 0 on success, 1 for std::invalid_argument, 2 for any other std::exception
 // (message in refCudaLastError()); tensor results are left in a per-thread slot (refCudaResult*).
 
+#include <cublasLt.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -240,6 +242,75 @@ int refCudaFusedAttentionTimed(const float* q, const int64_t* qShape, const floa
         cudaEventDestroy(b);
         *msPerCall = static_cast<double>(ms) / (iters > 0 ? iters : 1);
         gOut = r.output.toHost();
+    });
+}
+
+// cublasLtMatmul configured the way the reference's bf16Gemm configures it (src/backend/cuda/ops_tensorcore.cu:
+// 156-304: row-major layouts, A [m, k] and B [k, n] in bf16, fp32 compute, the top result of the heuristic search with
+// at most 4 MiB of workspace, alpha 1, beta 0) and timed on the device. bf16Gemm itself sits in an unnamed namespace
+// of the reference, so the library call it makes is made here with its settings; `cIsBf16` = 0 gives the fp32 result
+// the reference writes, 1 a bf16 result (what a bf16 activation stream wants). Operands are the caller's device
+// buffers. The calls run back to back for `iters` launches after `warmup`, so a long run settles at the clocks the
+// power cap allows, like a kernel inside a long step.
+int refCudaLtGemmTimed(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int cIsBf16, int warmup,
+                       int iters, double* msPerCall) {
+    return guarded([&] {
+        auto ok = [](cublasStatus_t st, const char* what) {
+            if (st != CUBLAS_STATUS_SUCCESS) throw std::runtime_error(std::string("cuBLASLt ") + what + " failed");
+        };
+        cublasLtHandle_t handle = nullptr;
+        ok(cublasLtCreate(&handle), "create");
+        cublasLtMatmulDesc_t op = nullptr;
+        ok(cublasLtMatmulDescCreate(&op, CUBLAS_COMPUTE_32F, CUDA_R_32F), "desc");
+        cublasOperation_t none = CUBLAS_OP_N;
+        ok(cublasLtMatmulDescSetAttribute(op, CUBLASLT_MATMUL_DESC_TRANSA, &none, sizeof(none)), "transa");
+        ok(cublasLtMatmulDescSetAttribute(op, CUBLASLT_MATMUL_DESC_TRANSB, &none, sizeof(none)), "transb");
+        cublasLtOrder_t row = CUBLASLT_ORDER_ROW;
+        cublasLtMatrixLayout_t la = nullptr, lb = nullptr, lc = nullptr;
+        ok(cublasLtMatrixLayoutCreate(&la, CUDA_R_16BF, static_cast<uint64_t>(m), static_cast<uint64_t>(k), k), "layout a");
+        ok(cublasLtMatrixLayoutCreate(&lb, CUDA_R_16BF, static_cast<uint64_t>(k), static_cast<uint64_t>(n), n), "layout b");
+        ok(cublasLtMatrixLayoutCreate(&lc, cIsBf16 ? CUDA_R_16BF : CUDA_R_32F, static_cast<uint64_t>(m),
+                                      static_cast<uint64_t>(n), n), "layout c");
+        for (cublasLtMatrixLayout_t l : {la, lb, lc})
+            ok(cublasLtMatrixLayoutSetAttribute(l, CUBLASLT_MATRIX_LAYOUT_ORDER, &row, sizeof(row)), "order");
+        cublasLtMatmulPreference_t pref = nullptr;
+        ok(cublasLtMatmulPreferenceCreate(&pref), "preference");
+        std::size_t maxWorkspace = 4 * 1024 * 1024;
+        ok(cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &maxWorkspace,
+                                                sizeof(maxWorkspace)), "workspace preference");
+        cublasLtMatmulHeuristicResult_t heur = {};
+        int found = 0;
+        ok(cublasLtMatmulAlgoGetHeuristic(handle, op, la, lb, lc, lc, pref, 1, &heur, &found), "heuristic");
+        if (found == 0) throw std::runtime_error("cuBLASLt: no algorithm for this shape");
+        void* workspace = nullptr;
+        if (heur.workspaceSize > 0 && cudaMalloc(&workspace, heur.workspaceSize) != cudaSuccess)
+            throw std::runtime_error("workspace allocation failed");
+        const float alpha = 1.0f, beta = 0.0f;
+        auto launch = [&] {
+            ok(cublasLtMatmul(handle, op, &alpha, a, la, b, lb, &beta, c, lc, c, lc, &heur.algo, workspace,
+                              heur.workspaceSize, nullptr), "matmul");
+        };
+        for (int i = 0; i < warmup; ++i) launch();
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        cudaEventCreate(&e0);
+        cudaEventCreate(&e1);
+        cudaDeviceSynchronize();
+        cudaEventRecord(e0, nullptr);
+        for (int i = 0; i < iters; ++i) launch();
+        cudaEventRecord(e1, nullptr);
+        if (cudaEventSynchronize(e1) != cudaSuccess) throw std::runtime_error("cublasLtMatmul failed on the device");
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        *msPerCall = static_cast<double>(ms) / (iters > 0 ? iters : 1);
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        if (workspace != nullptr) cudaFree(workspace);
+        cublasLtMatmulPreferenceDestroy(pref);
+        cublasLtMatrixLayoutDestroy(la);
+        cublasLtMatrixLayoutDestroy(lb);
+        cublasLtMatrixLayoutDestroy(lc);
+        cublasLtMatmulDescDestroy(op);
+        cublasLtDestroy(handle);
     });
 }
 

@@ -347,3 +347,14 @@ def cuda_fused_attention_timed(q, k, v, num_heads: int, scale: float, old_len: i
         qa.ctypes.data_as(C.c_void_p), qs, ka.ctypes.data_as(C.c_void_p), ks, va.ctypes.data_as(C.c_void_p),
         C.c_int64(num_heads), C.c_float(scale), C.c_int64(old_len), C.c_int(iters), C.byref(ms)))
     return _cuda_result(), ms.value
+
+
+def cuda_lt_gemm_timed(a_ptr: int, b_ptr: int, c_ptr: int, m: int, n: int, k: int, c_is_bf16: bool, warmup: int,
+                       iters: int) -> float:
+    """Device milliseconds per cublasLtMatmul call configured as the reference's bf16Gemm configures it, on the
+    caller's device buffers: A [m, k] bf16, B [k, n] bf16, C [m, n] fp32 (the reference's) or bf16, all row-major."""
+    ms = C.c_double(0.0)
+    _cuda_check(cuda_lib().refCudaLtGemmTimed(C.c_void_p(a_ptr), C.c_void_p(b_ptr), C.c_void_p(c_ptr), C.c_int64(m),
+                                              C.c_int64(n), C.c_int64(k), C.c_int(1 if c_is_bf16 else 0),
+                                              C.c_int(warmup), C.c_int(iters), C.byref(ms)))
+    return ms.value

@@ -411,6 +411,29 @@ def test_incremental_forward_matches_full_forward(gpu, precision, tol):
         m.forward_incremental(long_ids[:, :1])
 
 
+def test_incremental_positions_when_the_table_does_not_follow_the_embedding(gpu):
+    """embedding -> rmsnorm -> positional embedding -> attention -> ...: the positions of a generation step continue
+    after the cached ones on the tensor-core route too (the reference's forwardIncremental always adds them at its
+    generation position, model.cu:401-403), and the table's length still bounds the sequence."""
+    cfg = dict(vocab=256, dim=256, heads=2, hidden=512, max_seq=64)
+    ops, vid = [], 0
+    for kind, kw in (("embedding", dict(vocab=cfg["vocab"], emb_dim=cfg["dim"])), ("rmsnorm", {}),
+                     ("positional_embedding", dict(max_seq=cfg["max_seq"])), ("attention", dict(heads=cfg["heads"])),
+                     ("feedforward", dict(hidden=cfg["hidden"])), ("linear", dict(linear_out=cfg["vocab"]))):
+        ops.append(dict(kind=kind, input=vid, output=vid + 1, **kw))
+        vid += 1
+    m = gpu.Model(ops, precision={"storage": "bf16", "compute": "bf16"}, seed=17)
+    ids = O.synth_token_ids(2, 40, cfg["vocab"], seed=18)
+    full = m.forward_host(ids)
+    got = np.concatenate([m.forward_incremental(ids[:, a:b]) for a, b in ((0, 30), (30, 31), (31, 40))], axis=1)
+    assert np.max(np.abs(got - full)) / np.max(np.abs(full)) <= 2e-2
+    assert top1_agreement(got, full)[1] >= 0.995
+    m.reset_generation()
+    m.forward_incremental(O.synth_token_ids(2, cfg["max_seq"], cfg["vocab"], seed=19))
+    with pytest.raises(gpu.InvalidArgument):
+        m.forward_incremental(ids[:, :1])
+
+
 def test_operator_level_incremental_attention(gpu):
     """selfAttentionIncremental at the operator level is reached through the fp32 model route; the caches grow by
     concatenation as in the reference (ops_transformer.cu:133-180). Checked against the oracle's full attention."""

@@ -73,6 +73,13 @@ m16.set_tensor_parallel_overlap(2, 16)
 grouped = m16.forward_host(ids4)
 assert np.array_equal(plain, grouped), float(np.max(np.abs(plain - grouped)))
 np.save(os.path.join(work, f"logits16_{rank}.npy"), grouped)
+# e4m3 operands with four sequence groups: every group quantises its own GEMM inputs, so the pass needs a block of
+# scales per group and layer (per-tensor scales follow the group, so the values differ a little from one group)
+m8 = bfb.Model(ops, precision={"storage": "bf16", "compute": "fp8.e4m3"}, random_init=False)
+m8.set_tensor_parallel(rank, world)
+m8.set_params(params)
+m8.set_tensor_parallel_overlap(4, 0)
+np.save(os.path.join(work, f"logits8_{rank}.npy"), m8.forward_host(ids4))
 bfb.tp_destroy()
 print("rank", rank, "ok", out.shape)
 """
@@ -101,9 +108,16 @@ def test_two_gpu_tensor_parallel_matches_single_gpu(gpu, tmp_path):
     want = single.forward_host(ids)
     # same arithmetic, different summation order across the two partial products
     assert np.max(np.abs(sharded - want)) / np.max(np.abs(want)) <= 5e-3
+    # and against the oracle's statement of the reference's bf16 device path (bf16 GEMM operands, fp32 elsewhere)
+    oracle = O.model_forward(ops, params, ids, cuda_policy={"compute": "bf16"}, exact_order=False)
+    assert np.max(np.abs(sharded - oracle)) / np.max(np.abs(oracle)) <= 2e-2
     # bf16 residual stream, four sequences in two groups
     sharded16 = np.concatenate([np.load(tmp_path / f"logits16_{r}.npy") for r in range(2)], axis=-1)
     single16 = gpu.Model(ops, precision={"storage": "bf16", "compute": "bf16"}, random_init=False)
     single16.set_params(params)
     want16 = single16.forward_host(O.synth_token_ids(4, 160, CFG["vocab"], seed=23))
     assert np.sqrt(np.sum((sharded16 - want16) ** 2) / np.sum(want16 ** 2)) <= 2e-2
+    # e4m3 operands, four groups: finite and within the e4m3 tolerance of the bf16 result
+    sharded8 = np.concatenate([np.load(tmp_path / f"logits8_{r}.npy") for r in range(2)], axis=-1)
+    assert np.isfinite(sharded8).all()
+    assert np.sqrt(np.sum((sharded8 - want16) ** 2) / np.sum(want16 ** 2)) <= 0.15

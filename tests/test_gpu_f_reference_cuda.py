@@ -56,6 +56,100 @@ def test_bf16_model_against_the_reference_cublaslt_path(gpu, refcuda, cfg, batch
     assert decided.mean() > 0.2 and agree[decided].mean() >= 0.995
 
 
+def logit_differences(got, want):
+    """The figures the bf16 criterion is stated in, all of them: the largest difference relative to the largest logit,
+    RAW top-1 agreement over every position, and agreement on the positions the reference decides by more than the
+    2e-2 bar (with the share of positions that is)."""
+    scale = float(np.max(np.abs(want)))
+    top2 = np.sort(want, axis=-1)[..., -2:]
+    decided = (top2[..., 1] - top2[..., 0]) > 2e-2 * scale
+    agree = np.argmax(got, axis=-1) == np.argmax(want, axis=-1)
+    return {"max_abs_over_max": float(np.max(np.abs(got - want))) / scale,
+            "rel_l2": float(np.sqrt(np.sum((got - want) ** 2) / np.sum(want ** 2))),
+            "top1_raw": float(agree.mean()), "decided_fraction": float(decided.mean()),
+            "top1_decided": float(agree[decided].mean()) if decided.any() else float("nan")}
+
+
+def _set_all(model, params, names):
+    for i, n in enumerate(names):
+        model.set_param(i, params[n])
+
+
+def test_benchmarked_route_at_full_depth_against_the_reference_cublaslt_path(gpu, refcuda):
+    """The route the benchmark times, {storage bf16, compute bf16} (bf16 residual stream, rmsnorm folded into the GEMM
+    epilogues), on the 2B-class model at its full depth: 16 layers, d 2048, 16 heads of 128, ffn 5632, vocabulary
+    32000, weights N(0, 0.02) as the benchmark configuration states, two whole sequences of 2048 tokens, against the
+    reference's own device path with `compute bf16` (its cuBLASLt GEMMs on fp32 activations, model.cu:252-306,
+    ops_tensorcore.cu:293-327). The rounding of the residual stream grows with depth, so this is the case that
+    decides whether the timed route meets the 2e-2 bar; the fp32-stream route is measured beside it. How much bf16
+    rounding moves THIS model at all is measured too: the reference's bf16 path against the reference's own fp32
+    path (cublasSgemm). All figures are printed: they are quoted in BASELINE.md."""
+    cfg = dict(vocab=32000, dim=2048, layers=16, heads=16, hidden=5632, max_seq=2048)
+    batch, seq = 2, 2048
+    ops = O.lm_ops(**cfg)
+    params = O.synth_params(ops, None, seed=41, sigma=0.02, bias_sigma=0.02)
+    ids = O.synth_token_ids(batch, seq, cfg["vocab"], seed=7)
+    source = O.lm_source(seq=seq, **cfg)
+
+    def reference(precision):
+        ref = refcuda.CudaModel(source, seed=1, precision=precision)
+        _set_all(ref, params, ref.param_names())
+        out = ref.forward(ids)
+        ref.close()
+        return out
+
+    want = reference({"storage": "fp32", "compute": "bf16", "accumulate": "fp32"})
+    results = {"reference fp32 path vs its bf16 path": logit_differences(reference(None), want)}
+    for storage in ("bf16", "fp32"):
+        ours = gpu.Model(ops, precision={"storage": storage, "compute": "bf16"}, random_init=False)
+        ours.set_params(params)
+        got = ours.forward_host(ids)
+        ours.close()
+        gpu.check(gpu.lib().bfb_pool_trim())
+        assert got.shape == want.shape == (batch, seq, cfg["vocab"])
+        results[storage] = logit_differences(got, want)
+    for name, r in results.items():
+        print(f"16 layers, 2 x 2048 tokens, N(0, 0.02) weights, {name}:", r)
+    for storage in ("bf16", "fp32"):
+        r = results[storage]
+        assert r["max_abs_over_max"] <= 2e-2, (storage, r)
+        assert r["top1_decided"] >= 0.995, (storage, r)
+    # raw agreement: random-weight logits have many near ties (the two best logits closer than the bf16 noise), which
+    # no bf16 implementation decides the same way; the figure is recorded, and must not fall far below the bar
+    assert results["bf16"]["top1_raw"] >= 0.97, results["bf16"]
+
+
+def test_seeded_default_weights_at_full_depth_are_ill_conditioned_for_everyone(gpu, refcuda):
+    """The same comparison on the reference's seeded default weights (uniform(-0.1, 0.1), seed 42: the values both
+    sides draw when no checkpoint is given). At d 2048 every projection then multiplies the norm by about 2.6 and the
+    attention scores have a spread of several units, so after 16 layers bf16 rounding anywhere moves the logits by a
+    tenth of their range: the reference's own bf16 path is that far from the reference's own fp32 path. No bar can be
+    asserted against such a target beyond "no further from the reference's bf16 path than its own fp32 path is";
+    the figures are printed for BASELINE.md."""
+    cfg = dict(vocab=32000, dim=2048, layers=16, heads=16, hidden=5632, max_seq=2048)
+    batch, seq = 2, 2048
+    ids = O.synth_token_ids(batch, seq, cfg["vocab"], seed=7)
+    source = O.lm_source(seq=seq, **cfg)
+
+    def reference(precision):
+        ref = refcuda.CudaModel(source, seed=42, precision=precision)
+        out = ref.forward(ids)
+        ref.close()
+        return out
+
+    want = reference({"storage": "fp32", "compute": "bf16", "accumulate": "fp32"})
+    own = logit_differences(reference(None), want)
+    print("16 layers, default uniform(-0.1, 0.1) weights, reference fp32 path vs its bf16 path:", own)
+    for storage in ("bf16", "fp32"):
+        ours = gpu.Model(O.lm_ops(**cfg), seed=42, precision={"storage": storage, "compute": "bf16"})
+        got = ours.forward_host(ids)
+        ours.close()
+        gpu.check(gpu.lib().bfb_pool_trim())
+        r = logit_differences(got, want)
+        print(f"16 layers, default uniform(-0.1, 0.1) weights, storage {storage} vs reference cuBLASLt path:", r)
+        assert r["rel_l2"] <= 2.0 * own["rel_l2"] + 2e-2, (storage, r, own)
+
+
 def test_fp32_model_against_the_reference_device_path(gpu, refcuda):
     cfg = dict(vocab=256, dim=64, layers=2, heads=4, hidden=256, max_seq=32)
     ops = O.lm_ops(**cfg)

@@ -32,6 +32,38 @@ def test_static_scratch_variant_matches_pool_variant_twice_in_a_row(gpu):
         assert np.array_equal(got_q, want_q)
 
 
+def test_static_scratch_variant_takes_no_device_memory(gpu):
+    """The property the entry point exists for: after one warm-up call (address lookup, module load) a call takes
+    nothing from the library's device pool and leaves the device's free memory where it was. The pool variant,
+    measured the same way, does take its scratch from the pool."""
+    import ctypes as C
+    import torch
+
+    lib = gpu.lib()
+    x = (np.random.default_rng(7).standard_normal(8192 * 64) * 3).astype(np.float32)
+    src = gpu.upload(x, gpu.BF16)
+    out = gpu.DeviceBuffer(x.size)
+    scales = gpu.DeviceBuffer.zeros(12)
+
+    def pool():
+        cached, live = C.c_size_t(0), C.c_size_t(0)
+        gpu.check(lib.bfb_pool_stats(C.byref(cached), C.byref(live)))
+        return cached.value, live.value
+
+    gpu.check(lib.bfb_quantize_e4m3_static(src.ptr, gpu.BF16, x.size, out.ptr, scales.ptr, None, None))   # warm-up
+    gpu.sync()
+    gpu.check(lib.bfb_pool_trim())          # nothing cached: an acquisition would have to show up as new memory
+    before_pool, before_free = pool(), torch.cuda.mem_get_info()[0]
+    gpu.check(lib.bfb_quantize_e4m3_static(src.ptr, gpu.BF16, x.size, out.ptr, scales.ptr, None, None))
+    gpu.sync()
+    assert pool() == before_pool
+    assert torch.cuda.mem_get_info()[0] == before_free
+    # the same measurement sees the pool variant's scratch (kept cached by the pool after the call)
+    gpu.check(lib.bfb_quantize_e4m3(src.ptr, gpu.BF16, x.size, out.ptr, scales.ptr, None, None))
+    gpu.sync()
+    assert pool()[0] > before_pool[0]
+
+
 def test_static_scratch_variant_refuses_oversized_tensors(gpu):
     lib = gpu.lib()
     tiny = gpu.DeviceBuffer.zeros(64)
