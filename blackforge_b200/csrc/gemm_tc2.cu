@@ -54,7 +54,7 @@ struct PairCfg {
     static constexpr int kStageBytes = kABytes2 + kBBytes;      // 32 or 48 KiB
     static constexpr int kStages = kAccN == 256 ? 6 : 4;
     static constexpr int kBufs = 512 / kAccN;                   // accumulator buffers in the 512 TMEM columns
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + 8 * 4096;   // + one 4 KiB staging tile per epilogue warp
 };
 
 struct PairTile {
@@ -217,7 +217,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
                     alive = false;
                     break;
                 }
-                if (lane == 0) {
+                if (elect_one()) {
                     uint8_t* sa = smem + stage * kStageBytes;
                     uint8_t* sb = sa + kABytes2;
                     if (leader) mbar_arrive_expect_tx(&fullBar[stage], 2 * kStageBytes);
@@ -239,8 +239,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
         }
     } else if (warp == 1 && leader) {
         // ---------------- MMA issuer (leader CTA only) ----------------
-#ifdef BFB_GEMM_ELECT
-        // One elected thread runs the role (the compiler then keeps descriptors in uniform registers), and the
+        // Static tile order: one elected thread runs the role (the compiler then keeps descriptors in uniform registers), and the
         // descriptors of a stage are its base words plus constants: one integer add per operand and MMA.
         if (tileCounter == nullptr && elect_one()) {
             constexpr uint32_t kHi = smem_desc_hi_sw128(1024);
@@ -285,8 +284,8 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
             }
         }
         __syncwarp();
+        // dynamic tile order: the tile index arrives through the ring, read by the whole warp
         if (tileCounter != nullptr) {
-#endif
         int stage = 0;
         uint32_t phase = 0;
         int local = 0;
@@ -329,9 +328,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
                 }
             }
         }
-#ifdef BFB_GEMM_ELECT
         }
-#endif
     } else if (warp >= 4) {
         // ---------------- epilogue (both CTAs, 8 warps: lane quarter x column half) ----------------
         constexpr int kColsPerWarp = kAccN / 2;
@@ -344,6 +341,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
         const bool hasRes = ep.epilogue == BFB_EPI_BIAS_RESIDUAL || ep.epilogue == BFB_EPI_RESIDUAL;
         TC* cOut = static_cast<TC*>(ep.c);
         const TC* res = static_cast<const TC*>(ep.residual);
+        uint8_t* stageTile = smem + kStages * kStageBytes + 256 + (warp - 4) * 4096;
         int local = 0;
         for (int t = nextTile(); t >= 0; t = nextTile(), ++local) {
             PairTile tc = pairTileCoord(t, tilesM, tilesN, groupN);
@@ -374,9 +372,17 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
             };
             const uint32_t tBase = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>(buf * kAccN + colHalf * kColsPerWarp);
+            // The warp's 32 rows x 128 columns go out in rounds of 128 bytes per row (32 fp32 or 64 bf16 columns): a lane
+            // finishes ITS row's values in registers (scale, bias, silu, residual, rounding, row statistics), lays them
+            // into the warp's staging tile (16-byte pieces XOR-swizzled by the row: no bank conflicts either way), and the
+            // warp writes the tile out four rows at a time, so that one store instruction covers four whole 128-byte
+            // lines of C instead of 32 pieces of 32 different lines.
+            constexpr int kRoundCols = 128 / static_cast<int>(sizeof(TC));      // columns per round
+            constexpr int kPieceCols = 16 / static_cast<int>(sizeof(TC));       // columns per 16-byte piece
+            const int row0 = tc.m * kPairM + static_cast<int>(rank) * 128 + quarter * 32;
 #pragma unroll 1
-            for (int chunk = 0; chunk < kColsPerWarp / 32; ++chunk) {
-                const int col0 = tc.n * kAccN + colHalf * kColsPerWarp + chunk * 32;
+            for (int round = 0; round < kColsPerWarp / kRoundCols; ++round) {
+                const int col0 = tc.n * kAccN + colHalf * kColsPerWarp + round * kRoundCols;
                 if (col0 >= n) break;
                 if ((col0 >> 7) != part) {
                     flushPart();
@@ -384,19 +390,20 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
                     sumSq = 0.0f;
                     maxAbs = 0.0f;
                 }
-                uint32_t raw[32];
-                tmem_ld_32x32(tBase + static_cast<uint32_t>(chunk * 32), raw);
-                tmem_ld_wait();
-                if (rowOk) {
+#pragma unroll
+                for (int sub = 0; sub < kRoundCols / 32; ++sub) {
+                    uint32_t raw[32];
+                    tmem_ld_32x32(tBase + static_cast<uint32_t>(round * kRoundCols + sub * 32), raw);
+                    tmem_ld_wait();
                     const size_t rowOff = static_cast<size_t>(row) * static_cast<size_t>(n);
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
-                        const int col = col0 + g * 8;
-                        if (col + 8 > n) break;
+                        const int col = col0 + sub * 32 + g * 8;
+                        const bool live = rowOk && col + 8 <= n;
                         float v[8];
 #pragma unroll
                         for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(raw[g * 8 + j]) * rowScale;
-                        if (hasBias) {
+                        if (hasBias && live) {
                             const float4 b0 = __ldg(reinterpret_cast<const float4*>(ep.bias + col));
                             const float4 b1 = __ldg(reinterpret_cast<const float4*>(ep.bias + col + 4));
                             v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
@@ -407,7 +414,7 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
                             for (int j = 0; j < 8; ++j) v[j] = siluFast(v[j]);
                         }
                         if constexpr (sizeof(TC) == 4) {
-                            if (hasRes) {
+                            if (hasRes && live) {
                                 const float4 r0 = *reinterpret_cast<const float4*>(res + rowOff + col);
                                 const float4 r1 = *reinterpret_cast<const float4*>(res + rowOff + col + 4);
                                 v[0] += r0.x; v[1] += r0.y; v[2] += r0.z; v[3] += r0.w;
@@ -417,19 +424,23 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
 #pragma unroll
                                 for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
                             }
-                            float4* dst = reinterpret_cast<float4*>(cOut + rowOff + col);
-                            dst[0] = make_float4(v[0], v[1], v[2], v[3]);
-                            dst[1] = make_float4(v[4], v[5], v[6], v[7]);
-                            if (ep.outSumSq != nullptr) {
+                            // pieces 2g and 2g + 1 of the row's 8 (one sub-block per round for fp32)
+                            *reinterpret_cast<float4*>(stageTile + lane * 128 + (((2 * g) ^ (lane & 7)) << 4)) =
+                                make_float4(v[0], v[1], v[2], v[3]);
+                            *reinterpret_cast<float4*>(stageTile + lane * 128 + (((2 * g + 1) ^ (lane & 7)) << 4)) =
+                                make_float4(v[4], v[5], v[6], v[7]);
+                            if (live) {
+                                if (ep.outSumSq != nullptr) {
 #pragma unroll
-                                for (int j = 0; j < 8; ++j) sumSq = fmaf(v[j], v[j], sumSq);
-                            }
-                            if (ep.outMaxAbs != nullptr) {
+                                    for (int j = 0; j < 8; ++j) sumSq = fmaf(v[j], v[j], sumSq);
+                                }
+                                if (ep.outMaxAbs != nullptr) {
 #pragma unroll
-                                for (int j = 0; j < 8; ++j) maxAbs = fmaxf(maxAbs, fabsf(v[j]));
+                                    for (int j = 0; j < 8; ++j) maxAbs = fmaxf(maxAbs, fabsf(v[j]));
+                                }
                             }
                         } else {
-                            if (hasRes) {
+                            if (hasRes && live) {
                                 const uint4 rr = *reinterpret_cast<const uint4*>(res + rowOff + col);
                                 const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rr);
 #pragma unroll
@@ -445,16 +456,29 @@ gemmPairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant_
                             for (int j = 0; j < 4; ++j) {
                                 __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
                                 pw[j] = *reinterpret_cast<uint32_t*>(&h);
-                                if (ep.outSumSq != nullptr || ep.outMaxAbs != nullptr) {
+                                if (live && (ep.outSumSq != nullptr || ep.outMaxAbs != nullptr)) {
                                     const float2 f = __bfloat1622float2(h);   // the values as stored
                                     sumSq = fmaf(f.x, f.x, fmaf(f.y, f.y, sumSq));
                                     maxAbs = fmaxf(maxAbs, fmaxf(fabsf(f.x), fabsf(f.y)));
                                 }
                             }
-                            *reinterpret_cast<uint4*>(cOut + rowOff + col) = packed;
+                            // piece sub * 4 + g of the row's 8 (two sub-blocks per round for bf16)
+                            *reinterpret_cast<uint4*>(stageTile + lane * 128 + (((sub * 4 + g) ^ (lane & 7)) << 4)) = packed;
                         }
                     }
                 }
+                __syncwarp();
+                const int piece = lane & 7;
+                const int colOut = col0 + piece * kPieceCols;
+#pragma unroll
+                for (int q4 = 0; q4 < 8; ++q4) {
+                    const int rr = q4 * 4 + (lane >> 3);
+                    const uint4 val = *reinterpret_cast<const uint4*>(stageTile + rr * 128 + ((piece ^ (rr & 7)) << 4));
+                    if (row0 + rr < m && colOut + kPieceCols <= n) {
+                        *reinterpret_cast<uint4*>(cOut + static_cast<size_t>(row0 + rr) * static_cast<size_t>(n) + colOut) = val;
+                    }
+                }
+                __syncwarp();
             }
             tc_fence_before();
             __syncwarp();  // one (remote) arrival per warp instead of one per thread
