@@ -29,10 +29,16 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <map>
+#include <mutex>
+#include <queue>
+#include <tuple>
 #include <type_traits>
+#include <vector>
 
 #include "common.cuh"
 #include "kernels.hpp"
+#include "pool.hpp"
 #include "ptx_sm100.cuh"
 
 namespace bfb {
@@ -83,8 +89,9 @@ struct AttnParams {
     int64_t ldO;
     float scaleLog2;
     int oldLen, causal, numQBlocks;
-    int headsPerGroup;  // (batch, head) pairs whose K + V are kept in L2 together
     int totalItems;
+    const int* schedule;   // [rounds][grid]: the item CTA c takes in round k, or -1
+    int rounds;
 };
 
 struct Item {
@@ -100,23 +107,10 @@ __device__ __forceinline__ int keyTiles(const AttnParams& p, int firstRow) {
     return lastKey / kBN + 1;
 }
 
-// Item order: (batch, head) pairs are taken in groups whose K and V fit in L2 together; inside a group the
-// heaviest query blocks (most key tiles) come first. All query blocks of a head therefore run close in time and
-// K/V come from DRAM once.
+// An item is (batch * heads + head) * numQBlocks + query block.
 __device__ __forceinline__ Item decodeItem(const AttnParams& p, int item) {
-    const int bhCount = p.batch * p.numHeads;
-    const int perGroup = p.headsPerGroup * p.numQBlocks;
-    const int fullGroups = bhCount / p.headsPerGroup;
-    int group = item / perGroup;
-    int rem = item - group * perGroup;
-    int width = p.headsPerGroup;
-    if (group >= fullGroups) {
-        group = fullGroups;
-        rem = item - fullGroups * perGroup;
-        width = bhCount - fullGroups * p.headsPerGroup;
-    }
-    const int qb = p.numQBlocks - 1 - rem / width;
-    const int bh = group * p.headsPerGroup + rem % width;
+    const int bh = item / p.numQBlocks;
+    const int qb = item - bh * p.numQBlocks;
     Item it;
     it.b = bh / p.numHeads;
     it.h = bh % p.numHeads;
@@ -127,13 +121,14 @@ __device__ __forceinline__ Item decodeItem(const AttnParams& p, int item) {
     return it;
 }
 
-// The k-th item of this CTA, or a value >= totalItems when it has none left. Rounds alternate direction
-// (CTA c takes position c in even rounds and grid-1-c in odd ones): with items sorted heaviest first, a CTA
-// that got a heavier item in one round gets a lighter one in the next.
-__device__ __forceinline__ int itemAt(uint32_t k) {
-    const int pos = (k & 1u) ? static_cast<int>(gridDim.x - 1u - blockIdx.x) : static_cast<int>(blockIdx.x);
-    return static_cast<int>(k * gridDim.x) + pos;
+// The k-th item of this CTA, or a value >= totalItems when it has none left: read from the schedule the host made
+// for this shape (attentionSchedule below), which balances the CTAs' total work.
+__device__ __forceinline__ int itemAtOf(const AttnParams& p, uint32_t k) {
+    if (k >= static_cast<uint32_t>(p.rounds)) return p.totalItems;
+    const int item = __ldg(p.schedule + static_cast<size_t>(k) * gridDim.x + blockIdx.x);
+    return item < 0 ? p.totalItems : item;
 }
+#define itemAt(k) itemAtOf(p, (k))
 
 __global__ void __launch_bounds__(kThreads, 1)
 attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_constant__ CUtensorMap tmapK,
@@ -559,6 +554,99 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
     }
 }
 
+// ---- which CTA takes which item, in what order ------------------------------------------------------------------
+// Items differ in weight by up to the number of key tiles (a causal query block sees 2 to 2 * blocks key tiles), and
+// a launch may hold only a few items per CTA, so a fixed round-robin can leave CTAs idle for a fifth of the kernel
+// (measured: 790 to 1015 TFLOP/s on one shape depending on nothing but the order). The order is therefore planned on
+// the host, once per shape and grid, and kept on the device:
+//   * (batch, head) pairs are taken in groups whose K and V together fit an L2 budget (default 16 MB; the two halves
+//     of the 126 MB L2 mirror lines that both dies read): a group's query blocks run close together in time, so K
+//     and V come from DRAM about once;
+//   * inside a group the heaviest query blocks come first, and every item goes to the CTA with the least work so far
+//     (list scheduling: no CTA ends more than one item after the average), each CTA working through its list in order.
+// Cost of an item: its key-tile rounds plus a fixed share for Q load, first scores and output (kItemOverhead).
+struct ScheduleKey {
+    int device, grid, batch, heads, newLen, totalLen, oldLen, causal;
+    long long groupBytes;
+    bool operator<(const ScheduleKey& o) const {
+        return std::tie(device, grid, batch, heads, newLen, totalLen, oldLen, causal, groupBytes) <
+               std::tie(o.device, o.grid, o.batch, o.heads, o.newLen, o.totalLen, o.oldLen, o.causal, o.groupBytes);
+    }
+};
+struct ScheduleEntry {
+    int* dev = nullptr;
+    int rounds = 0;
+    std::vector<int> host;   // kept: the asynchronous upload reads it
+};
+constexpr double kItemOverhead = 1.5;
+
+int hostKeyTiles(const AttentionArgs& a, int64_t firstRow) {
+    if (firstRow >= a.newLen) return 0;
+    int64_t lastKey = a.totalLen - 1;
+    if (a.causal) lastKey = std::min<int64_t>(lastKey, a.oldLen + firstRow + kBM - 1);
+    return static_cast<int>(lastKey / kBN + 1);
+}
+
+const ScheduleEntry& attentionSchedule(const AttentionArgs& a, int grid, int numQBlocks, cudaStream_t stream) {
+    static std::mutex mu;
+    static std::map<ScheduleKey, ScheduleEntry> cache;
+    static const long long groupBytes = [] {
+        const char* e = std::getenv("BFB_ATTN_L2_MB");
+        const long long mb = e != nullptr ? std::atoll(e) : 16;
+        return std::max<long long>(1, mb) << 20;
+    }();
+    int device = 0;
+    BFB_CUDA(cudaGetDevice(&device));
+    const ScheduleKey key{device, grid, static_cast<int>(a.batch), static_cast<int>(a.numHeads), static_cast<int>(a.newLen),
+                          static_cast<int>(a.totalLen), static_cast<int>(a.oldLen), a.causal, groupBytes};
+    std::lock_guard<std::mutex> lock(mu);
+    auto found = cache.find(key);
+    if (found != cache.end()) return found->second;
+    if (cache.size() >= 512) {
+        // many different shapes (a server with free-form prompt lengths): start over; the buffers may still be in use
+        BFB_CUDA(cudaDeviceSynchronize());
+        for (auto& kv : cache) poolRelease(kv.second.dev, kv.second.host.size() * sizeof(int));
+        cache.clear();
+    }
+    const int bhCount = static_cast<int>(a.batch * a.numHeads);
+    std::vector<double> blockCost(static_cast<size_t>(numQBlocks));
+    for (int qb = 0; qb < numQBlocks; ++qb) {
+        const int64_t q0 = static_cast<int64_t>(qb) * kItemRows;
+        blockCost[static_cast<size_t>(qb)] = std::max(hostKeyTiles(a, q0), hostKeyTiles(a, q0 + kBM)) + kItemOverhead;
+    }
+    std::vector<int> byWeight(static_cast<size_t>(numQBlocks));
+    for (int qb = 0; qb < numQBlocks; ++qb) byWeight[static_cast<size_t>(qb)] = qb;
+    std::stable_sort(byWeight.begin(), byWeight.end(), [&](int x, int y) { return blockCost[x] > blockCost[y]; });
+    const long long kvBytes = 2ll * a.totalLen * kD * 2;
+    const int perGroup = static_cast<int>(std::max<long long>(1, std::min<long long>(bhCount, groupBytes / std::max<long long>(kvBytes, 1))));
+    // least-loaded CTA first; ties go to the lower index
+    using Load = std::pair<double, int>;
+    std::priority_queue<Load, std::vector<Load>, std::greater<Load>> loads;
+    for (int c = 0; c < grid; ++c) loads.push({0.0, c});
+    std::vector<std::vector<int>> lists(static_cast<size_t>(grid));
+    for (int g0 = 0; g0 < bhCount; g0 += perGroup) {
+        const int g1 = std::min(bhCount, g0 + perGroup);
+        for (int qb : byWeight) {
+            for (int bh = g0; bh < g1; ++bh) {
+                Load l = loads.top();
+                loads.pop();
+                lists[static_cast<size_t>(l.second)].push_back(bh * numQBlocks + qb);
+                l.first += blockCost[static_cast<size_t>(qb)];
+                loads.push(l);
+            }
+        }
+    }
+    ScheduleEntry e;
+    for (const auto& l : lists) e.rounds = std::max<int>(e.rounds, static_cast<int>(l.size()));
+    e.host.assign(static_cast<size_t>(e.rounds) * grid, -1);
+    for (int c = 0; c < grid; ++c)
+        for (size_t k = 0; k < lists[static_cast<size_t>(c)].size(); ++k) e.host[k * grid + c] = lists[static_cast<size_t>(c)][k];
+    e.dev = static_cast<int*>(poolAcquire(e.host.size() * sizeof(int)));
+    ScheduleEntry& kept = cache[key] = std::move(e);
+    BFB_CUDA(cudaMemcpyAsync(kept.dev, kept.host.data(), kept.host.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
+    return kept;
+}
+
 // `batchRows`: rows from one batch entry to the next (the length itself when densely packed, the capacity for a cache)
 void makeMap(TensorMapStorage* out, const void* base, int64_t dim, int64_t len, int64_t batch, int64_t ld,
              int64_t batchRows, uint32_t boxRows = 128u) {
@@ -601,13 +689,13 @@ void attentionTensorCore(const AttentionArgs& a, cudaStream_t stream) {
     p.oldLen = static_cast<int>(a.oldLen);
     p.causal = a.causal;
     p.numQBlocks = static_cast<int>((a.newLen + kItemRows - 1) / kItemRows);
-    // K + V of one (batch, head): 2 * total_len * 128 * 2 bytes; keep about 64 MB of them live in the 126 MB L2
-    const int64_t kvBytes = 2 * a.totalLen * kD * 2;
-    p.headsPerGroup = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(a.batch * a.numHeads, (64ll << 20) / kvBytes)));
     const int64_t items = static_cast<int64_t>(p.numQBlocks) * a.batch * a.numHeads;
     require(items <= 0x7FFFFFFF, "attention: too many query blocks for one launch");
     p.totalItems = static_cast<int>(items);
     const int grid = static_cast<int>(std::min<int64_t>(items, persistentSms()));
+    const ScheduleEntry& sched = attentionSchedule(a, grid, p.numQBlocks, stream);
+    p.schedule = sched.dev;
+    p.rounds = sched.rounds;
     // visible (query, key) pairs per (batch, head): causal rows see old_len + i + 1 keys
     const double nl = static_cast<double>(a.newLen), tl = static_cast<double>(a.totalLen);
     const double pairs = a.causal ? nl * static_cast<double>(a.oldLen) + nl * (nl + 1.0) / 2.0 : nl * tl;

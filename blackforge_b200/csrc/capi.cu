@@ -686,6 +686,15 @@ struct HostPathStreams {
         sliceBytes = bytes;
     }
 };
+// One host-buffer forward at a time per device: the calls of several host threads share the two streams and the
+// staging ring above, so the second caller waits for the first (held for the whole sliced pass).
+std::mutex& hostPathMutex() {
+    static std::mutex perDevice[64];
+    int dev = 0;
+    BFB_CUDA(cudaGetDevice(&dev));
+    return perDevice[dev & 63];
+}
+
 HostPathStreams& hostPathStreams() {
     static std::mutex mu;
     static std::map<int, HostPathStreams> perDevice;
@@ -733,6 +742,7 @@ bfb_status bfb_model_forward_host(bfb_model* model, const float* h_input, const 
             }
             return;
         }
+        std::lock_guard<std::mutex> hostPathLock(hostPathMutex());
         HostPathStreams& st = hostPathStreams();
         const std::size_t perSeqIn = count / batch;
         std::size_t outCount = 1;
@@ -869,6 +879,7 @@ bfb_status bfb_model_forward_host_bf16(bfb_model* model, const float* h_input, c
         BFB_CUDA(cudaMemcpy(in.data(), h_input, count * sizeof(float), cudaMemcpyHostToDevice));
         hostTransfer().h2d = static_cast<int64_t>(count * sizeof(float));
         hostTransfer().d2h = 0;
+        std::lock_guard<std::mutex> hostPathLock(hostPathMutex());
         HostPathStreams& st = hostPathStreams();
         const std::size_t perSeqIn = count / batch;
         std::size_t outCount = 1;

@@ -392,7 +392,25 @@ CheckpointLoadStats loadCheckpointCached(Model& model, const std::string& path, 
     const auto t0 = std::chrono::steady_clock::now();
     const std::string tag = model.preparedWeightsTag();
     if (tag.empty()) return loadCheckpoint(model, path, chunkBytes);   // fp32 compute: nothing to cache
-    (void)indexCheckpoint(path);   // a missing or damaged checkpoint fails here, cache or not
+    const std::vector<CheckpointEntry> entries = indexCheckpoint(path);   // a missing or damaged checkpoint fails here, cache or not
+    // A checkpoint may hold only some of the tensors (the loader keeps the model's own values for the rest, as the
+    // reference does). The cache holds converted GEMM weights without saying where they came from, so it is written
+    // and read only when every GEMM weight comes from the file: otherwise a weight the file lacks would be taken from
+    // whichever model wrote the cache.
+    {
+        std::size_t covered = 0, wanted = 0;
+        for (std::size_t i = 0; i < model.parameterCount(); ++i) {
+            if (!model.parameterIsGemmWeight(i)) continue;
+            ++wanted;
+            for (const CheckpointEntry& e : entries) {
+                if (e.name == model.parameterName(i)) {
+                    ++covered;
+                    break;
+                }
+            }
+        }
+        if (covered != wanted) return loadCheckpoint(model, path, chunkBytes);
+    }
     if (chunkBytes == 0) chunkBytes = std::size_t(4) << 20;
     const std::string cachePath = path + ".bfb200cache." + tag;
     CacheHeader want{};

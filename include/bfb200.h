@@ -404,7 +404,9 @@ bfb_status bfb_model_forward_incremental(bfb_model* model, const float* d_new_id
 bfb_status bfb_model_reset_generation(bfb_model* model);
 bfb_status bfb_model_generation_position(bfb_model* model, int64_t* position);
 /* The `blackforge run` path (src/main.cpp:356-388): host ids in, host logits out, synchronous.
- * h_out must hold product(out_shape) floats; call once with h_out == NULL to learn the shape. */
+ * h_out must hold product(out_shape) floats; call once with h_out == NULL to learn the shape.
+ * Host threads may call the host-buffer entry points on one device concurrently: the calls are serialised per
+ * device (they share the library's copy streams and staging buffers). */
 bfb_status bfb_model_forward_host(bfb_model* model, const float* h_input, const int64_t* shape, int32_t rank,
                                   float* h_out, int64_t* out_shape, int32_t* out_rank);
 /* The same call for a host that takes the logits as bf16 (no reference counterpart: its tensors are fp32). Needs

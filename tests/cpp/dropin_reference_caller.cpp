@@ -4,6 +4,8 @@
 // blackforge_b200/dropin/blackforge_backend_cuda.cpp + libbfb200.so instead of the reference's CUDA sources, and
 // against the reference's own front end and CPU backend (compiled in place by oracle/Makefile) for the values to
 // compare with. It shows that such caller code compiles and runs unchanged. Exit code 0 = every check passed.
+#include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -188,6 +190,40 @@ int main(int argc, char** argv) {
         Tensor in = cpuExec.makeSyntheticInput(module.models.front(), 3);
         expectNear(in, cudaExec.makeSyntheticInput(module.models.front(), 3), 0.0F, "makeSyntheticInput");
         expectNear(cpuExec.run(module.models.front(), in), cudaExec.run(module.models.front(), in), 1e-3F, "Executor::run");
+    }
+    // src/main.cpp:803-849 — the `benchmark` command's device part as the reference wrote it: warm-up and measured
+    // Executor::run calls timed on the host clock, then the speed-up and the largest difference against the CPU
+    // executor's result for the same seed (same input, same initial weights)
+    {
+        ir::Module module = buildModule(kTinyLm);
+        const ir::ModelIR& model = module.models.front();
+        const std::size_t batchSize = 4, warmupIterations = 2, measuredIterations = 5;
+        cpu::Executor cpuExecutor;
+        Tensor cpuInput = cpuExecutor.makeSyntheticInput(model, batchSize);
+        auto cpuStart = std::chrono::steady_clock::now();
+        Tensor cpuOutput = cpuExecutor.run(model, cpuInput);
+        const double cpuMillis = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - cpuStart).count();
+        std::string gpuName = "unknown GPU";
+        for (const auto& d : cuda::enumerateDevices()) {
+            if (d.index == 0) gpuName = d.name;
+        }
+        cuda::Executor cudaExecutor;
+        Tensor cudaInput = cudaExecutor.makeSyntheticInput(model, batchSize);
+        for (std::size_t i = 0; i < warmupIterations; ++i) (void)cudaExecutor.run(model, cudaInput);
+        Tensor gpuOutput;
+        auto start = std::chrono::steady_clock::now();
+        for (std::size_t i = 0; i < measuredIterations; ++i) gpuOutput = cudaExecutor.run(model, cudaInput);
+        const double gpuMeanMillis = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - start).count() /
+                                     static_cast<double>(measuredIterations);
+        float maxAbsDiff = 0.0F;
+        for (std::size_t i = 0; i < cpuOutput.elementCount() && i < gpuOutput.elementCount(); ++i) {
+            maxAbsDiff = std::max(maxAbsDiff, std::fabs(cpuOutput.at(i) - gpuOutput.at(i)));
+        }
+        std::printf("benchmark report: %s, mean GPU time %.3f ms, throughput %.1f samples/s, speed-up vs CPU %.2fx, "
+                    "largest difference vs CPU (reference) %.3g\n",
+                    gpuName.c_str(), gpuMeanMillis, gpuMeanMillis > 0.0 ? batchSize * 1000.0 / gpuMeanMillis : 0.0,
+                    cpuMillis / gpuMeanMillis, maxAbsDiff);
+        expect(gpuOutput.shape() == cpuOutput.shape() && maxAbsDiff <= 1e-3F, "benchmark report: CPU and GPU agree for the same seed");
     }
     // ops.hpp — operator level against the CPU backend's operators (ops_tests.cu compares the same pairs)
     {

@@ -154,6 +154,30 @@ def test_cache_of_converted_weights_beside_the_checkpoint(gpu, tmp_path, compute
     assert np.array_equal(fourth.forward_host(ids), ref.forward_host(ids))
 
 
+def test_partial_checkpoint_does_not_use_or_write_the_cache(gpu, tmp_path):
+    """A checkpoint that lacks a GEMM weight leaves that weight to the model (its seeded values, as in the reference's
+    loader). The cache of converted weights does not record where a weight came from, so such a checkpoint is loaded
+    the plain way: two models with different seeds keep their own values for the missing weight."""
+    cfg = dict(vocab=256, dim=256, layers=1, heads=2, hidden=512, max_seq=64)
+    ops = O.lm_ops(**cfg)
+    prec = {"storage": "bf16", "compute": "bf16"}
+    params = O.synth_params(ops, None, seed=5, sigma=0.05, bias_sigma=0.05)
+    path = str(tmp_path / "partial.bfckpt")
+    O.save_checkpoint(path, [(n, params[n]) for n, _ in O.param_layout(ops) if n != "attention3.wout"])
+    ids = O.synth_token_ids(2, 64, cfg["vocab"], seed=6)
+    outs = []
+    for seed in (1, 2):
+        m = gpu.Model(ops, precision=prec, seed=seed)
+        stats = m.load_checkpoint_cached(path, 4096)
+        assert stats["cache_hit"] == 0 and stats["cache_bytes"] == 0
+        plain = gpu.Model(ops, precision=prec, seed=seed)
+        plain.load_checkpoint(path)
+        outs.append(m.forward_host(ids))
+        assert np.array_equal(outs[-1], plain.forward_host(ids))
+    assert not [f for f in os.listdir(tmp_path) if ".bfb200cache." in f]
+    assert not np.array_equal(outs[0], outs[1])     # each kept its own out-projection
+
+
 def test_checkpoint_errors(gpu, tmp_path):
     ops = O.lm_ops(vocab=8, dim=8, layers=1, heads=2, hidden=16, max_seq=6)
     m = gpu.Model(ops)
