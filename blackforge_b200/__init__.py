@@ -88,8 +88,11 @@ SIGNATURES = {
     "bfb_gemm_rmsnorm": (_I32, [_P, _P, _P, _I64, _I64, _I64, _I32, _I32, _I32, _P, _P, _P, _I32, _F, _P, _P, _P, _P]),
     "bfb_gemm_few_rows": (_I32, [_P, _P, _P, _I64, _I64, _I64, _I32, _I32, _I32, _P, _P, _F, _P, _I32, _F, _P, _P, _P]),
     "bfb_matmul_transpose_b": (_I32, [_P, _P, _P, _I64, _I64, _I64, _P]),
+    "bfb_matmul_bf16_backward": (_I32, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _P]),
     "bfb_attention_fwd": (_I32, [_P, _P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64,
                                  _F, _I64, _I32, _P, _P]),
+    "bfb_attention_bwd": (_I32, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _I64, _I64, _I64,
+                                 _I64, _I64, _I64, _F, _I64, _I32, _P, _P]),
     "bfb_model_create": (_I32, [C.POINTER(OpDesc), _I32, _I64, C.c_uint32, C.POINTER(Precision), C.POINTER(_P)]),
     "bfb_model_create_uninitialised": (_I32, [C.POINTER(OpDesc), _I32, _I64, C.POINTER(Precision), C.POINTER(_P)]),
     "bfb_model_destroy": (None, [_P]),
@@ -132,6 +135,7 @@ SIGNATURES = {
     "bfb_tp_unique_id": (_I32, [_P]),
     "bfb_tp_init": (_I32, [_P, _I32, _I32]),
     "bfb_tp_allreduce_sum": (_I32, [_P, _I64, _I32, _P]),
+    "bfb_gradients_average": (_I32, [_P, _P, _I32, _P]),
     "bfb_tp_destroy": (_I32, []),
 }
 

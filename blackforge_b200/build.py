@@ -29,6 +29,7 @@ SOURCES = [
     "gemm_skinny.cu",
     "attention_simt.cu",
     "attention_tc.cu",
+    "attention_bwd.cu",
     "attention_decode.cu",
     "selftest.cu",
     "capi.cu",

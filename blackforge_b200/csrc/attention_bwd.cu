@@ -1,0 +1,556 @@
+// Backward of the causal attention core (fusedAttentionBackward, src/backend/cuda/fused_attention.cu:158-303,343-380
+// in the reference): from dO, Q, K, V, O and the forward's row statistics (m, l) to dQ, dK, dV.
+//
+//   D_i  = sum_d O[i,d] dO[i,d]                      (attentionBackwardPrepKernel; also lse_i = m_i + ln l_i)
+//   P    = exp(scale * Q K^T - lse)                   dP = dO V^T
+//   dS   = scale * P o (dP - D)
+//   dV   = P^T dO        dK = dS^T Q        dQ = dS K
+//
+// Two kernels:
+//  * attentionBackwardTcKernel: tcgen05, head_dim 128, bf16 operands, fp32 accumulation. One CTA per (batch, head,
+//    block of 128 keys); it walks the query blocks that see those keys. Everything is computed TRANSPOSED, with the
+//    keys on the tensor-memory lanes: S^T = K Q^T and dP^T = V dO^T are ordinary shared-memory MMAs; a thread owns one
+//    key row of both, so P^T and dS^T are written back as bf16 over them in tensor memory and are the TMEM operand of
+//    dV += P^T dO and dK += dS^T Q, whose accumulators stay in tensor memory for the whole CTA. Only dS^T also goes
+//    through shared memory, as the B operand of dQ^T = K^T dS^T (K^T is the K tile itself, read MN-major); dQ^T comes
+//    back with head_dim on the lanes, so a warp's atomic adds into dQ are 128 contiguous bytes.
+//    TMEM columns: S^T / P^T / dQ^T [0,128)  dP^T / dS^T [128,256)  dV [256,384)  dK [384,512).
+//    dK and dV are written with plain stores (a CTA owns its keys); dQ is accumulated with fp32 atomics over the key
+//    blocks (zeroed by the host first), as the reference accumulates dK and dV.
+//  * attentionBackwardSimtKernel: any head_dim <= 256, fp32 or bf16 storage, one warp per query row; the shape-general
+//    path, with the reference's own order of work.
+// All mbarrier waits are bounded.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <algorithm>
+#include <cmath>
+
+#include "common.cuh"
+#include "kernels.hpp"
+#include "ptx_sm100.cuh"
+
+namespace bfb {
+
+namespace {
+
+constexpr int kD = 128;
+constexpr int kBlk = 128;                    // keys per CTA, query rows per step
+constexpr int kHalfBytes = 128 * 128;        // one 64-wide half of a 128-row bf16 tile
+constexpr int kTileBytes = 2 * kHalfBytes;   // 32 KiB
+constexpr int kKOff = 0;
+constexpr int kVOff = kTileBytes;
+constexpr int kRingOff = 2 * kTileBytes;     // [2 stages][Q, dO]
+constexpr int kDsOff = kRingOff + 4 * kTileBytes;
+constexpr int kRowOff = kDsOff + kTileBytes; // [2 steps in flight][lse2, D][128] floats
+constexpr int kBarOff = kRowOff + 2 * 2 * 128 * 4;
+constexpr int kSmemBytes = kBarOff + 256;
+constexpr int kSoftmaxWarps = 4;
+constexpr int kProducerWarp = 4;
+constexpr int kMmaWarp = 5;
+constexpr int kThreads = 192;
+// A and B formats bf16, fp32 accumulate; bit 15 = A is MN-major, bit 16 = B is MN-major
+constexpr uint32_t kIdescKK = make_idesc(128, 128, 1u, 0u);                  // both K-major
+constexpr uint32_t kIdescKM = make_idesc(128, 128, 1u, 1u);                  // B MN-major (A from TMEM or K-major)
+constexpr uint32_t kIdescMM = make_idesc(128, 128, 1u, 1u) | (1u << 15);     // A and B MN-major
+
+__device__ __forceinline__ float ex2f(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+struct BwdParams {
+    float* dQ;
+    float* dK;
+    float* dV;
+    const float* lse2;   // [batch, heads, newLen]: (m + ln l) * log2(e)
+    const float* dTerm;  // [batch, heads, newLen]: sum_d O dO
+    int batch, newLen, totalLen, numHeads;
+    int64_t ldDq, ldDk, ldDv;
+    float scale, scaleLog2;
+    int oldLen, causal, numKvBlocks;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_constant__ CUtensorMap tmapK,
+                          const __grid_constant__ CUtensorMap tmapV, const __grid_constant__ CUtensorMap tmapDo,
+                          BwdParams p, int* status) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOff);
+    uint64_t* kvFull = bars;          // [1]
+    uint64_t* qFull = bars + 1;       // [2]
+    uint64_t* qEmpty = bars + 3;      // [2]
+    uint64_t* sFull = bars + 5;       // S^T and dP^T complete
+    uint64_t* pFull = bars + 6;       // P^T written (4 warps)
+    uint64_t* dsFull = bars + 7;      // dS^T written (4 warps)
+    uint64_t* dqFull = bars + 8;      // dQ^T complete (and everything issued before it)
+    uint64_t* dqFree = bars + 9;      // dQ^T read (4 warps): the S^T columns are free
+    uint64_t* accFull = bars + 10;    // dV and dK complete
+    uint64_t* rowFull = bars + 11;    // [2] row statistics of a step written (4 warps)
+    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 13);
+    volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
+
+    if ((smem_u32(smem) & 1023u) != 0u) {
+        if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, kDevTimeoutOther);
+        return;
+    }
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // work: blocks are ordered heaviest first (key block 0 is seen by every query block)
+    const int kvBlock = static_cast<int>(blockIdx.x % static_cast<unsigned>(p.numKvBlocks));
+    const int bh = static_cast<int>(blockIdx.x / static_cast<unsigned>(p.numKvBlocks));
+    const int b = bh / p.numHeads, h = bh % p.numHeads;
+    const int k0 = kvBlock * kBlk;
+    const int numQBlocks = (p.newLen + kBlk - 1) / kBlk;
+    // first query block with a row that sees key k0: old_len + i >= k0
+    const int firstQ = p.causal ? max(0, k0 - p.oldLen) / kBlk : 0;
+    const int steps = max(0, numQBlocks - firstQ);
+
+    if (threadIdx.x == 0) {
+        mbar_init(kvFull, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&qFull[i], 1);
+            mbar_init(&qEmpty[i], 1);
+        }
+        mbar_init(sFull, 1);
+        mbar_init(pFull, kSoftmaxWarps);
+        mbar_init(dsFull, kSoftmaxWarps);
+        mbar_init(dqFull, 1);
+        mbar_init(dqFree, kSoftmaxWarps);
+        mbar_init(accFull, 1);
+        mbar_init(&rowFull[0], kSoftmaxWarps);
+        mbar_init(&rowFull[1], kSoftmaxWarps);
+        *abortFlag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmapQ);
+        tma_prefetch_desc(&tmapK);
+        tma_prefetch_desc(&tmapV);
+        tma_prefetch_desc(&tmapDo);
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(tmemSlot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmemBase = *tmemSlot;
+
+    if (warp == kProducerWarp) {
+        // ---------------- TMA producer (one elected thread) ----------------
+        if (elect_one() && steps > 0) {
+            mbar_arrive_expect_tx(kvFull, 2 * kTileBytes);
+            tma_load_3d(smem + kKOff, &tmapK, kvFull, h * kD, k0, b);
+            tma_load_3d(smem + kKOff + kHalfBytes, &tmapK, kvFull, h * kD + 64, k0, b);
+            tma_load_3d(smem + kVOff, &tmapV, kvFull, h * kD, k0, b);
+            tma_load_3d(smem + kVOff + kHalfBytes, &tmapV, kvFull, h * kD + 64, k0, b);
+            for (int it = 0; it < steps; ++it) {
+                const int stage = it & 1;
+                if (!mbar_wait(&qEmpty[stage], ((it >> 1) & 1) ^ 1, abortFlag, status, kDevTimeoutStageEmpty)) break;
+                uint8_t* dst = smem + kRingOff + stage * 2 * kTileBytes;
+                const int q0 = (firstQ + it) * kBlk;
+                mbar_arrive_expect_tx(&qFull[stage], 2 * kTileBytes);
+                tma_load_3d(dst, &tmapQ, &qFull[stage], h * kD, q0, b);
+                tma_load_3d(dst + kHalfBytes, &tmapQ, &qFull[stage], h * kD + 64, q0, b);
+                tma_load_3d(dst + kTileBytes, &tmapDo, &qFull[stage], h * kD, q0, b);
+                tma_load_3d(dst + kTileBytes + kHalfBytes, &tmapDo, &qFull[stage], h * kD + 64, q0, b);
+            }
+        }
+        __syncwarp();
+    } else if (warp == kMmaWarp) {
+        // ---------------- MMA issuer (one elected thread) ----------------
+        if (elect_one() && steps > 0) {
+            constexpr uint32_t kHi = smem_desc_hi_sw128(1024);
+            const uint32_t kLo = smem_desc_lo(smem_u32(smem + kKOff), 0);
+            const uint32_t vLo = smem_desc_lo(smem_u32(smem + kVOff), 0);
+            const uint32_t dsLoMn = smem_desc_lo(smem_u32(smem + kDsOff), kHalfBytes);
+            const uint32_t kLoMn = smem_desc_lo(smem_u32(smem + kKOff), kHalfBytes);
+            const uint32_t tS = tmemBase, tDp = tmemBase + 128u, tDv = tmemBase + 256u, tDk = tmemBase + 384u;
+            bool alive = mbar_wait(kvFull, 0, abortFlag, status, kDevTimeoutTmaFull);
+            for (int it = 0; it < steps && alive; ++it) {
+                const int stage = it & 1;
+                const uint32_t par = static_cast<uint32_t>(it) & 1u;
+                const uint32_t qLo = smem_desc_lo(smem_u32(smem + kRingOff + stage * 2 * kTileBytes), 0);
+                const uint32_t doLo = qLo + (kTileBytes >> 4);
+                const uint32_t qLoMn = qLo + ((kHalfBytes >> 4) << 16);
+                const uint32_t doLoMn = doLo + ((kHalfBytes >> 4) << 16);
+                if (!mbar_wait(&qFull[stage], (it >> 1) & 1, abortFlag, status, kDevTimeoutTmaFull)) { alive = false; break; }
+                // the S^T columns also receive dQ^T: the previous step's dQ^T must have been read
+                if (it > 0 && !mbar_wait(dqFree, par ^ 1u, abortFlag, status, kDevTimeoutAccEmpty)) { alive = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kD / 16; ++kk) {      // S^T = K Q^T (reduction over head_dim)
+                    const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
+                    umma_f16_words(tS, kLo + off, kHi, qLo + off, kHi, kIdescKK, kk > 0 ? 1u : 0u);
+                }
+#pragma unroll
+                for (int kk = 0; kk < kD / 16; ++kk) {      // dP^T = V dO^T
+                    const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
+                    umma_f16_words(tDp, vLo + off, kHi, doLo + off, kHi, kIdescKK, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(sFull);
+                if (!mbar_wait(pFull, par, abortFlag, status, kDevTimeoutSoftmax)) { alive = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kBlk / 16; ++kk) {    // dV += P^T dO (reduction over the query rows)
+                    umma_f16_ts_words(tDv, tS + static_cast<uint32_t>(kk * 8), doLoMn + kk * (2048 >> 4), kHi, kIdescKM,
+                                      (it > 0 || kk > 0) ? 1u : 0u);
+                }
+                if (!mbar_wait(dsFull, par, abortFlag, status, kDevTimeoutSoftmax)) { alive = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kBlk / 16; ++kk) {    // dK += dS^T Q
+                    umma_f16_ts_words(tDk, tDp + static_cast<uint32_t>(kk * 8), qLoMn + kk * (2048 >> 4), kHi, kIdescKM,
+                                      (it > 0 || kk > 0) ? 1u : 0u);
+                }
+#pragma unroll
+                for (int kk = 0; kk < kBlk / 16; ++kk) {    // dQ^T = K^T dS^T (reduction over the keys), over S^T / P^T
+                    umma_f16_words(tS, kLoMn + kk * (2048 >> 4), kHi, dsLoMn + kk * (2048 >> 4), kHi, kIdescMM,
+                                   kk > 0 ? 1u : 0u);
+                }
+                umma_commit(dqFull);
+                umma_commit(&qEmpty[stage]);
+            }
+            if (alive) umma_commit(accFull);
+        }
+        __syncwarp();
+    } else {
+        // ---------------- softmax / gradient warps: one thread per key row ----------------
+        const int keyRow = warp * 32 + lane;               // key inside the block, also head_dim index for dQ^T
+        const int keyPos = k0 + keyRow;
+        const bool keyValid = keyPos < p.totalLen;
+        const uint32_t laneBase = static_cast<uint32_t>(warp * 32) << 16;
+        const uint32_t tS = tmemBase + laneBase, tDp = tS + 128u, tDv = tS + 256u, tDk = tS + 384u;
+        uint8_t* dsTile = smem + kDsOff;
+        bool alive = true;
+        for (int it = 0; it < steps && alive; ++it) {
+            const uint32_t par = static_cast<uint32_t>(it) & 1u;
+            const int q0 = (firstQ + it) * kBlk;
+            // statistics of this step's 128 query rows: thread c writes row c (a row past the end gets +inf, which makes
+            // its probabilities zero). The buffer of two steps ago is free: every warp arrived on the barrier of the
+            // step in between only after its last read.
+            const int stage = it & 1;
+            float* lseS = reinterpret_cast<float*>(smem + kRowOff) + stage * 256;
+            float* dS = lseS + 128;
+            {
+                const int qi = q0 + keyRow;
+                const bool ok = qi < p.newLen;
+                const size_t at = (static_cast<size_t>(b) * p.numHeads + h) * p.newLen + (ok ? qi : 0);
+                lseS[keyRow] = ok ? p.lse2[at] : INFINITY;
+                dS[keyRow] = ok ? p.dTerm[at] : 0.0f;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&rowFull[stage]);
+            if (!warp_all(mbar_wait(&rowFull[stage], (it >> 1) & 1, abortFlag, status, kDevTimeoutOther))) {
+                alive = false;
+                break;
+            }
+            if (!warp_all(mbar_wait(sFull, par, abortFlag, status, kDevTimeoutAccFull))) {
+                alive = false;
+                break;
+            }
+            tc_fence_after();
+            // ---- P^T = exp2(S^T * scale_log2 - lse2[c]); masked: key beyond the row's causal limit or past the end
+            // row c sees this key iff keyPos <= old_len + q0 + c: columns below firstVisible are masked
+            const int firstVisible = p.causal ? keyPos - p.oldLen - q0 : -1;
+            uint32_t pk[4][16];   // P^T as bf16 pairs, kept for dS^T (chunk c reads columns [32c, 32c+32) and writes
+                                  // [16c, 16c+16), which earlier chunks have already read)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t sc[32];
+                tmem_ld_32x32(tS + static_cast<uint32_t>(c * 32), sc);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const int col = c * 32 + i;
+                    float p0 = ex2f(fmaf(__uint_as_float(sc[i]), p.scaleLog2, -lseS[col]));
+                    float p1 = ex2f(fmaf(__uint_as_float(sc[i + 1]), p.scaleLog2, -lseS[col + 1]));
+                    if (!keyValid || col < firstVisible) p0 = 0.0f;
+                    if (!keyValid || col + 1 < firstVisible) p1 = 0.0f;
+                    __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+                    pk[c][i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+                }
+                tmem_st_32x16(tS + static_cast<uint32_t>(c * 16), pk[c]);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(pFull);
+            // ---- dS^T = scale * P^T o (dP^T - D[c]); written over dP^T (TMEM operand of dK) and to shared memory
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t dp[32];
+                tmem_ld_32x32(tDp + static_cast<uint32_t>(c * 32), dp);
+                tmem_ld_wait();
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const int col = c * 32 + i;
+                    const float2 pr = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[c][i >> 1]));
+                    const float d0 = pr.x * (__uint_as_float(dp[i]) - dS[col]) * p.scale;
+                    const float d1 = pr.y * (__uint_as_float(dp[i + 1]) - dS[col + 1]) * p.scale;
+                    __nv_bfloat162 hh = __floats2bfloat162_rn(d0, d1);
+                    packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+                }
+                tmem_st_32x16(tDp + static_cast<uint32_t>(c * 16), packed);
+                // shared-memory copy: row = key, 64 query rows per 128-byte half-row, 16-byte pieces swizzled by the row
+                uint8_t* half = dsTile + (c >> 1) * kHalfBytes + keyRow * 128;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const int piece = (c & 1) * 4 + g;
+                    *reinterpret_cast<uint4*>(half + ((piece ^ (keyRow & 7)) << 4)) =
+                        make_uint4(packed[g * 4], packed[g * 4 + 1], packed[g * 4 + 2], packed[g * 4 + 3]);
+                }
+            }
+            tmem_st_wait();
+            fence_proxy_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(dsFull);
+            // ---- dQ^T: lane = head_dim index, column = query row; added into dQ (fp32 atomics, a warp = 128 bytes)
+            if (!warp_all(mbar_wait(dqFull, par, abortFlag, status, kDevTimeoutAccFull))) {
+                alive = false;
+                break;
+            }
+            tc_fence_after();
+            float* dqBase = p.dQ + (static_cast<size_t>(b) * p.newLen + q0) * p.ldDq + static_cast<size_t>(h) * kD + keyRow;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t dq[32];
+                tmem_ld_32x32(tS + static_cast<uint32_t>(c * 32), dq);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int col = c * 32 + i;
+                    if (q0 + col < p.newLen) atomicAdd(dqBase + static_cast<size_t>(col) * p.ldDq, __uint_as_float(dq[i]));
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(dqFree);
+        }
+        // ---- dV and dK of this CTA's keys
+        if (alive && steps > 0 && warp_all(mbar_wait(accFull, 0, abortFlag, status, kDevTimeoutAccFull))) {
+            tc_fence_after();
+#pragma unroll 1
+            for (int which = 0; which < 2; ++which) {
+                float* dst = (which == 0 ? p.dV : p.dK) +
+                             (static_cast<size_t>(b) * p.totalLen + keyPos) * (which == 0 ? p.ldDv : p.ldDk) +
+                             static_cast<size_t>(h) * kD;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t acc[32];
+                    tmem_ld_32x32((which == 0 ? tDv : tDk) + static_cast<uint32_t>(c * 32), acc);
+                    tmem_ld_wait();
+                    if (keyValid) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            *reinterpret_cast<float4*>(dst + c * 32 + i) =
+                                make_float4(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]), __uint_as_float(acc[i + 2]),
+                                            __uint_as_float(acc[i + 3]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        if (*abortFlag != 0) {
+            uint64_t t0 = global_timer_ns();
+            while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
+        tc_fence_after();
+        tmem_dealloc(tmemBase, 512);
+    }
+}
+
+// D_i = sum_d O dO and lse2_i = (m_i + ln l_i) * log2(e), one warp per (batch, head, query row)
+template <typename T>
+__global__ void attentionBackwardPrepKernel(const T* out, const T* dOut, const float* m, const float* l, float* lse2,
+                                            float* dTerm, int64_t rows, int numHeads, int64_t newLen, int headDim,
+                                            int64_t ldO, int64_t ldDo) {
+    const int64_t warpId = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warpId >= rows) return;
+    const int64_t i = warpId % newLen;
+    const int64_t bh = warpId / newLen;
+    const int64_t h = bh % numHeads, b = bh / numHeads;
+    const T* o = out + (b * newLen + i) * ldO + h * headDim;
+    const T* g = dOut + (b * newLen + i) * ldDo + h * headDim;
+    float acc = 0.0f;
+    for (int d = lane; d < headDim; d += 32) acc += static_cast<float>(o[d]) * static_cast<float>(g[d]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
+    if (lane == 0) {
+        dTerm[warpId] = acc;
+        const float lv = l[warpId];
+        // a row with no visible key (l == 0) never contributes: +inf makes every probability zero
+        lse2[warpId] = lv > 0.0f ? (m[warpId] + logf(lv)) * 1.4426950408889634f : INFINITY;
+    }
+}
+
+// Shape-general path: one warp per query row, the reference's order of work (fused_attention.cu:183-303): scores and
+// dP by warp reductions, dQ in registers, dK / dV by atomics. T is the storage type of q, k, v, dO.
+template <typename T>
+__global__ void attentionBackwardSimtKernel(const T* q, const T* k, const T* v, const T* dOut, const float* lse2,
+                                            const float* dTerm, float* dQ, float* dK, float* dV, int64_t rows, int numHeads,
+                                            int64_t newLen, int64_t totalLen, int headDim, int64_t ldQ, int64_t ldK,
+                                            int64_t ldV, int64_t ldDo, int64_t ldDq, int64_t ldDk, int64_t ldDv,
+                                            float scale, int64_t oldLen, int causal) {
+    constexpr int kMaxPerLane = 8;   // head_dim <= 256
+    const int64_t warpId = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warpId >= rows) return;
+    const int64_t i = warpId % newLen;
+    const int64_t bh = warpId / newLen;
+    const int64_t h = bh % numHeads, b = bh / numHeads;
+    float qReg[kMaxPerLane], gReg[kMaxPerLane], dqAcc[kMaxPerLane];
+#pragma unroll
+    for (int e = 0; e < kMaxPerLane; ++e) {
+        const int d = lane + e * 32;
+        const bool ok = d < headDim;
+        qReg[e] = ok ? static_cast<float>(q[(b * newLen + i) * ldQ + h * headDim + d]) : 0.0f;
+        gReg[e] = ok ? static_cast<float>(dOut[(b * newLen + i) * ldDo + h * headDim + d]) : 0.0f;
+        dqAcc[e] = 0.0f;
+    }
+    const float lseRow = lse2[warpId] * 0.6931471805599453f;   // back to natural-log units
+    const float dRow = dTerm[warpId];
+    const int64_t last = causal ? min(totalLen - 1, oldLen + i) : totalLen - 1;
+    for (int64_t kp = 0; kp <= last; ++kp) {
+        const T* kRow = k + (b * totalLen + kp) * ldK + h * headDim;
+        const T* vRow = v + (b * totalLen + kp) * ldV + h * headDim;
+        float sc = 0.0f, dp = 0.0f;
+#pragma unroll
+        for (int e = 0; e < kMaxPerLane; ++e) {
+            const int d = lane + e * 32;
+            if (d < headDim) {
+                sc = fmaf(qReg[e], static_cast<float>(kRow[d]), sc);
+                dp = fmaf(gReg[e], static_cast<float>(vRow[d]), dp);
+            }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            sc += __shfl_xor_sync(0xFFFFFFFFu, sc, off);
+            dp += __shfl_xor_sync(0xFFFFFFFFu, dp, off);
+        }
+        const float pr = expf(sc * scale - lseRow);
+        const float ds = pr * (dp - dRow) * scale;
+#pragma unroll
+        for (int e = 0; e < kMaxPerLane; ++e) {
+            const int d = lane + e * 32;
+            if (d < headDim) {
+                dqAcc[e] = fmaf(ds, static_cast<float>(kRow[d]), dqAcc[e]);
+                atomicAdd(dK + (b * totalLen + kp) * ldDk + h * headDim + d, ds * qReg[e]);
+                atomicAdd(dV + (b * totalLen + kp) * ldDv + h * headDim + d, pr * gReg[e]);
+            }
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < kMaxPerLane; ++e) {
+        const int d = lane + e * 32;
+        if (d < headDim) dQ[(b * newLen + i) * ldDq + h * headDim + d] = dqAcc[e];
+    }
+}
+
+void makeMap3(TensorMapStorage* out, const void* base, int64_t dim, int64_t len, int64_t batch, int64_t ld) {
+    uint64_t dims[3] = {static_cast<uint64_t>(dim), static_cast<uint64_t>(len), static_cast<uint64_t>(batch)};
+    uint64_t strides[2] = {static_cast<uint64_t>(ld) * 2, static_cast<uint64_t>(ld) * 2 * static_cast<uint64_t>(len)};
+    uint32_t box[3] = {64u, 128u, 1u};
+    encodeTensorMap(out, base, 2, 3, dims, strides, box);
+}
+
+}  // namespace
+
+bool attentionBackwardUsesTensorCores(const AttentionBackwardArgs& a) {
+    if (a.dtype != BFB_BF16 || a.headDim != kD) return false;
+    if (a.ldQ % 8 || a.ldK % 8 || a.ldV % 8 || a.ldDo % 8 || a.ldDk % 4 || a.ldDv % 4) return false;
+    auto aligned16 = [](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
+    if (!aligned16(a.q) || !aligned16(a.k) || !aligned16(a.v) || !aligned16(a.dOut) || !aligned16(a.dK) || !aligned16(a.dV))
+        return false;
+    if (a.batch * a.numHeads > 0x3FFFFF || a.totalLen > 0x3FFFFFFF || a.newLen > 0x3FFFFFFF) return false;
+    return true;
+}
+
+void attentionBackward(const AttentionBackwardArgs& a, cudaStream_t stream) {
+    require(a.batch >= 0 && a.newLen >= 0 && a.totalLen >= 0 && a.numHeads > 0 && a.headDim > 0, "attention_bwd: bad sizes");
+    require(a.headDim <= 256, "attention_bwd: head_dim up to 256");
+    require(a.totalLen >= a.oldLen + a.newLen || !a.causal, "attention_bwd: total_len must cover old_len + new_len");
+    require(a.dtype == BFB_F32 || a.dtype == BFB_BF16, "attention_bwd: q, k, v, out and d_out are f32 or bf16");
+    const int64_t rows = a.batch * a.numHeads * a.newLen;
+    const size_t kvElems = static_cast<size_t>(a.batch) * a.totalLen;
+    // dK and dV start from zero (rows no query sees keep it); dQ too on the tensor-core path, which accumulates into it
+    if (kvElems > 0) {
+        BFB_CUDA(cudaMemset2DAsync(a.dK, static_cast<size_t>(a.ldDk) * 4, 0, static_cast<size_t>(a.numHeads * a.headDim) * 4, kvElems, stream));
+        BFB_CUDA(cudaMemset2DAsync(a.dV, static_cast<size_t>(a.ldDv) * 4, 0, static_cast<size_t>(a.numHeads * a.headDim) * 4, kvElems, stream));
+    }
+    if (rows == 0) return;
+    const int threads = 256;
+    const unsigned prepBlocks = static_cast<unsigned>((rows * 32 + threads - 1) / threads);
+    if (a.dtype == BFB_F32) {
+        attentionBackwardPrepKernel<float><<<prepBlocks, threads, 0, stream>>>(
+            static_cast<const float*>(a.out), static_cast<const float*>(a.dOut), a.m, a.l, a.lse2Scratch, a.dTermScratch, rows,
+            static_cast<int>(a.numHeads), a.newLen, static_cast<int>(a.headDim), a.ldO, a.ldDo);
+    } else {
+        attentionBackwardPrepKernel<__nv_bfloat16><<<prepBlocks, threads, 0, stream>>>(
+            static_cast<const __nv_bfloat16*>(a.out), static_cast<const __nv_bfloat16*>(a.dOut), a.m, a.l, a.lse2Scratch,
+            a.dTermScratch, rows, static_cast<int>(a.numHeads), a.newLen, static_cast<int>(a.headDim), a.ldO, a.ldDo);
+    }
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+    if (attentionBackwardUsesTensorCores(a)) {
+        BFB_CUDA(cudaMemset2DAsync(a.dQ, static_cast<size_t>(a.ldDq) * 4, 0, static_cast<size_t>(a.numHeads * a.headDim) * 4,
+                                   static_cast<size_t>(a.batch) * a.newLen, stream));
+        const int64_t dim = a.numHeads * a.headDim;
+        TensorMapStorage tq, tk, tv, tg;
+        makeMap3(&tq, a.q, dim, a.newLen, a.batch, a.ldQ);
+        makeMap3(&tk, a.k, dim, a.totalLen, a.batch, a.ldK);
+        makeMap3(&tv, a.v, dim, a.totalLen, a.batch, a.ldV);
+        makeMap3(&tg, a.dOut, dim, a.newLen, a.batch, a.ldDo);
+        BwdParams p;
+        p.dQ = a.dQ;
+        p.dK = a.dK;
+        p.dV = a.dV;
+        p.lse2 = a.lse2Scratch;
+        p.dTerm = a.dTermScratch;
+        p.batch = static_cast<int>(a.batch);
+        p.newLen = static_cast<int>(a.newLen);
+        p.totalLen = static_cast<int>(a.totalLen);
+        p.numHeads = static_cast<int>(a.numHeads);
+        p.ldDq = a.ldDq;
+        p.ldDk = a.ldDk;
+        p.ldDv = a.ldDv;
+        p.scale = a.scale;
+        p.scaleLog2 = a.scale * 1.4426950408889634f;
+        p.oldLen = static_cast<int>(a.oldLen);
+        p.causal = a.causal;
+        p.numKvBlocks = static_cast<int>((a.totalLen + kBlk - 1) / kBlk);
+        const int64_t blocks = static_cast<int64_t>(p.numKvBlocks) * a.batch * a.numHeads;
+        require(blocks <= 0x7FFFFFFF, "attention_bwd: too many key blocks for one launch");
+        BFB_CUDA(cudaFuncSetAttribute(attentionBackwardTcKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        attentionBackwardTcKernel<<<static_cast<unsigned>(blocks), kThreads, kSmemBytes, stream>>>(
+            *reinterpret_cast<const CUtensorMap*>(tq.bytes), *reinterpret_cast<const CUtensorMap*>(tk.bytes),
+            *reinterpret_cast<const CUtensorMap*>(tv.bytes), *reinterpret_cast<const CUtensorMap*>(tg.bytes), p, a.dStatus);
+        BFB_LAUNCH_CHECK();
+        noteLaunch();
+        return;
+    }
+    const unsigned blocks = static_cast<unsigned>((rows * 32 + threads - 1) / threads);
+    auto launch = [&](auto tag) {
+        using T = decltype(tag);
+        attentionBackwardSimtKernel<T><<<blocks, threads, 0, stream>>>(
+            static_cast<const T*>(a.q), static_cast<const T*>(a.k), static_cast<const T*>(a.v), static_cast<const T*>(a.dOut),
+            a.lse2Scratch, a.dTermScratch, a.dQ, a.dK, a.dV, rows, static_cast<int>(a.numHeads), a.newLen, a.totalLen,
+            static_cast<int>(a.headDim), a.ldQ, a.ldK, a.ldV, a.ldDo, a.ldDq, a.ldDk, a.ldDv, a.scale, a.oldLen, a.causal);
+    };
+    if (a.dtype == BFB_F32) launch(float{}); else launch(__nv_bfloat16{});
+    BFB_LAUNCH_CHECK();
+    noteLaunch();
+}
+
+}  // namespace bfb

@@ -321,6 +321,11 @@ bfb_status bfb_matmul_transpose_b(const float* d_a, const float* d_b, float* d_c
     return guarded([&] { bfb::matmulTransposeB(d_a, d_b, d_c, m, n, k, asStream(stream)); });
 }
 
+bfb_status bfb_matmul_bf16_backward(const float* d_a, const float* d_b, const float* d_grad, float* d_da, float* d_db,
+                                    int64_t m, int64_t k, int64_t n, void* stream) {
+    return guarded([&] { bfb::matmulBf16Backward(d_a, d_b, d_grad, d_da, d_db, m, k, n, nullptr, asStream(stream)); });
+}
+
 bfb_status bfb_attention_fwd(const void* d_q, const void* d_k, const void* d_v, void* d_out, float* d_m, float* d_l,
                              int32_t dtype, int64_t batch, int64_t new_len, int64_t total_len, int64_t num_heads,
                              int64_t head_dim, int64_t ld_q, int64_t ld_k, int64_t ld_v, int64_t ld_o, float scale,
@@ -348,6 +353,45 @@ bfb_status bfb_attention_fwd(const void* d_q, const void* d_k, const void* d_v, 
         a.causal = causal;
         a.dStatus = d_status;
         bfb::attentionForward(a, asStream(stream));
+    });
+}
+
+bfb_status bfb_attention_bwd(const void* d_dout, const void* d_q, const void* d_k, const void* d_v, const void* d_out,
+                             const float* d_m, const float* d_l, float* d_dq, float* d_dk, float* d_dv, float* d_scratch,
+                             int32_t dtype, int64_t batch, int64_t new_len, int64_t total_len, int64_t num_heads,
+                             int64_t head_dim, int64_t ld_in, int64_t ld_kv, int64_t ld_grad_q, int64_t ld_grad_kv,
+                             float scale, int64_t old_len, int32_t causal, int32_t* d_status, void* stream) {
+    return guarded([&] {
+        bfb::AttentionBackwardArgs a;
+        a.dOut = d_dout;
+        a.q = d_q;
+        a.k = d_k;
+        a.v = d_v;
+        a.out = d_out;
+        a.m = d_m;
+        a.l = d_l;
+        a.dQ = d_dq;
+        a.dK = d_dk;
+        a.dV = d_dv;
+        require(batch >= 0 && new_len >= 0 && num_heads > 0, "attention_bwd: bad sizes");
+        require(d_scratch != nullptr || batch * new_len == 0, "attention_bwd: scratch of 2 * batch * heads * new_len floats required");
+        a.lse2Scratch = d_scratch;
+        a.dTermScratch = d_scratch == nullptr ? nullptr : d_scratch + batch * num_heads * new_len;
+        a.dtype = dtype;
+        a.batch = batch;
+        a.newLen = new_len;
+        a.totalLen = total_len;
+        a.numHeads = num_heads;
+        a.headDim = head_dim;
+        a.ldQ = a.ldO = a.ldDo = ld_in;
+        a.ldK = a.ldV = ld_kv;
+        a.ldDq = ld_grad_q;
+        a.ldDk = a.ldDv = ld_grad_kv;
+        a.scale = scale;
+        a.oldLen = old_len;
+        a.causal = causal;
+        a.dStatus = d_status;
+        bfb::attentionBackward(a, asStream(stream));
     });
 }
 
@@ -986,6 +1030,10 @@ bfb_status bfb_tp_init(const void* h_id_128, int32_t rank, int32_t world) {
 
 bfb_status bfb_tp_allreduce_sum(void* d_buf, int64_t count, int32_t dtype, void* stream) {
     return guarded([&] { bfb200::tpAllReduceSum(d_buf, count, dtype, stream); });
+}
+
+bfb_status bfb_gradients_average(void* const* d_grads, const int64_t* counts, int32_t n_tensors, void* stream) {
+    return guarded([&] { bfb200::tpAverageGradients(d_grads, counts, n_tensors, stream); });
 }
 
 bfb_status bfb_tp_destroy(void) {

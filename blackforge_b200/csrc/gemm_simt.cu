@@ -6,6 +6,7 @@
 
 #include "common.cuh"
 #include "kernels.hpp"
+#include "pool.hpp"
 
 namespace bfb {
 
@@ -165,6 +166,63 @@ void gemm(const GemmArgs& g, cudaStream_t stream) {
     } else {
         if (cf32) launchSimt<f8, float>(g, stream); else launchSimt<f8, bf>(g, stream);
     }
+}
+
+namespace {
+struct PoolScratch {
+    void* ptr;
+    size_t bytes;
+    explicit PoolScratch(size_t b) : ptr(poolAcquire(b)), bytes(b) {}
+    ~PoolScratch() { poolRelease(ptr, bytes); }
+    PoolScratch(const PoolScratch&) = delete;
+    PoolScratch& operator=(const PoolScratch&) = delete;
+};
+}  // namespace
+
+// Both products run on the CTA-pair kernel, which wants its second operand as [N, K] with the reduction contiguous:
+//   dA = G (m x n) times b16 read as [N' = k][K' = n]  — b's own layout, no transpose;
+//   dB = A^T (k x m) times G^T read as [N' = n][K' = m] — a and grad go through the transposing cast, which costs the
+//        same pass over them as the plain cast the reference makes (toBf16, ops_tensorcore.cu:401-403).
+void matmulBf16Backward(const float* a, const float* b, const float* grad, float* dA, float* dB, int64_t m, int64_t k,
+                        int64_t n, const void* bNatural16, cudaStream_t stream) {
+    require(m >= 0 && k >= 0 && n >= 0, "matmul_bf16_backward: negative size");
+    if (m == 0 || k == 0 || n == 0) {
+        // the reference's zero fill of both results (ops_tensorcore.cu:412-415)
+        if (m * k > 0) BFB_CUDA(cudaMemsetAsync(dA, 0, static_cast<size_t>(m * k) * 4, stream));
+        if (k * n > 0) BFB_CUDA(cudaMemsetAsync(dB, 0, static_cast<size_t>(k * n) * 4, stream));
+        return;
+    }
+    require(a != nullptr && b != nullptr && grad != nullptr && dA != nullptr && dB != nullptr,
+            "matmul_bf16_backward: null pointer");
+    PoolScratch g16(static_cast<size_t>(m * n) * 2), gT16(static_cast<size_t>(m * n) * 2), aT16(static_cast<size_t>(m * k) * 2);
+    castScaled(grad, BFB_F32, g16.ptr, BFB_BF16, m * n, 1.0f, nullptr, stream);
+    weightPrepare(grad, gT16.ptr, BFB_BF16, m, n, 1.0f, nullptr, stream);   // [m,n] -> [n,m]
+    weightPrepare(a, aT16.ptr, BFB_BF16, m, k, 1.0f, nullptr, stream);      // [m,k] -> [k,m]
+    GemmArgs g;
+    g.abDtype = BFB_BF16;
+    g.cDtype = BFB_F32;
+    g.bLayout = BFB_B_NK;
+    g.a = g16.ptr;
+    g.c = dA;
+    g.m = m;
+    g.n = k;
+    g.k = n;
+    if (bNatural16 != nullptr) {
+        g.b = bNatural16;
+        gemm(g, stream);
+    } else {
+        PoolScratch b16(static_cast<size_t>(k * n) * 2);
+        castScaled(b, BFB_F32, b16.ptr, BFB_BF16, k * n, 1.0f, nullptr, stream);
+        g.b = b16.ptr;
+        gemm(g, stream);
+    }
+    g.a = aT16.ptr;
+    g.b = gT16.ptr;
+    g.c = dB;
+    g.m = k;
+    g.n = n;
+    g.k = m;
+    gemm(g, stream);
 }
 
 void matmulTransposeB(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, cudaStream_t stream) {

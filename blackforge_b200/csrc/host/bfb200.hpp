@@ -73,6 +73,15 @@ DeviceTensor matmulTransposeB(const DeviceTensor& a, const DeviceTensor& b);
 DeviceTensor matmulBf16(const DeviceTensor& a, const DeviceTensor& b);
 DeviceTensor matmulBf16CachedWeight(const DeviceTensor& a, const DeviceTensor& b);
 void invalidateBf16WeightCache();
+// include/blackforge/backend/cuda/autodiff.hpp:18-37: gradients of C = A B on the bf16 tensor-core route
+// (dA = gradOutput B^T, dB = A^T gradOutput; fp32 tensors in and out). The CachedWeight form keeps a bf16 copy of B
+// until invalidateBf16WeightCache().
+struct MatmulGrad {
+    DeviceTensor dA;
+    DeviceTensor dB;
+};
+MatmulGrad matmulBf16Backward(const DeviceTensor& a, const DeviceTensor& b, const DeviceTensor& gradOutput);
+MatmulGrad matmulBf16BackwardCachedWeight(const DeviceTensor& a, const DeviceTensor& b, const DeviceTensor& gradOutput);
 // New: e4m3 operands with per-tensor amax scales, fp32 accumulate (the declared `compute fp8.e4m3`).
 DeviceTensor matmulFp8(const DeviceTensor& a, const DeviceTensor& b);
 DeviceTensor silu(const DeviceTensor& input);
@@ -123,6 +132,24 @@ FusedAttentionForwardResult fusedAttentionForward(const DeviceTensor& q, const D
 FusedAttentionForwardResult fusedAttentionForwardBf16(const DeviceTensor& q, const DeviceTensor& k,
                                                       const DeviceTensor& v, std::size_t numHeads, float scaleFactor,
                                                       std::size_t oldLen);
+
+// include/blackforge/backend/cuda/fused_attention.hpp:59-76: gradients of the attention core from the forward's
+// operands, output and row statistics. dQ [batch, new_len, dim]; dK, dV [batch, total_len, dim].
+struct FusedAttentionGrad {
+    DeviceTensor dQ;
+    DeviceTensor dK;
+    DeviceTensor dV;
+};
+FusedAttentionGrad fusedAttentionBackward(const DeviceTensor& dOutput, const DeviceTensor& q, const DeviceTensor& k,
+                                          const DeviceTensor& v, const DeviceTensor& output, const DeviceTensor& m,
+                                          const DeviceTensor& l, std::size_t numHeads, float scaleFactor,
+                                          std::size_t oldLen);
+// Same contract; operands are rounded to bf16 and run through the tensor-core kernel when head_dim is 128
+// (gradients stay fp32).
+FusedAttentionGrad fusedAttentionBackwardBf16(const DeviceTensor& dOutput, const DeviceTensor& q, const DeviceTensor& k,
+                                              const DeviceTensor& v, const DeviceTensor& output, const DeviceTensor& m,
+                                              const DeviceTensor& l, std::size_t numHeads, float scaleFactor,
+                                              std::size_t oldLen);
 
 // ---- model ------------------------------------------------------------------------------------------
 using OpDesc = bfb_op_desc;

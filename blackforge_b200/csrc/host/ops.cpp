@@ -278,6 +278,77 @@ FusedAttentionForwardResult attentionImpl(const DeviceTensor& q, const DeviceTen
     return r;
 }
 
+FusedAttentionGrad attentionBackwardImpl(const DeviceTensor& dOutput, const DeviceTensor& q, const DeviceTensor& k,
+                                         const DeviceTensor& v, const DeviceTensor& output, const DeviceTensor& m,
+                                         const DeviceTensor& l, std::size_t numHeads, float scaleFactor,
+                                         std::size_t oldLen, bool bf16) {
+    if (q.rank() != 3 || k.rank() != 3 || v.rank() != 3) {
+        throw std::invalid_argument("fusedAttentionBackward: q, k, v must be [batch, len, dim]");
+    }
+    std::size_t batch = q.dim(0), newLen = q.dim(1), dim = q.dim(2), totalLen = k.dim(1);
+    if (k.dim(0) != batch || v.dim(0) != batch || k.dim(2) != dim || v.dim(2) != dim || v.dim(1) != totalLen ||
+        dOutput.shape() != q.shape() || output.shape() != q.shape()) {
+        throw std::invalid_argument("fusedAttentionBackward: operand shapes disagree");
+    }
+    if (numHeads == 0 || dim % numHeads != 0) {
+        throw std::invalid_argument("fusedAttentionBackward: numHeads must divide dim");
+    }
+    std::size_t headDim = dim / numHeads;
+    if (headDim > 256) throw std::invalid_argument("fusedAttentionBackward: head_dim above 256 is not supported");
+    if (oldLen + newLen != totalLen) {
+        throw std::invalid_argument("fusedAttentionBackward: old_len + new_len must equal total_len");
+    }
+    std::size_t statCount = batch * numHeads * newLen;
+    if (m.elementCount() != statCount || l.elementCount() != statCount) {
+        throw std::invalid_argument("fusedAttentionBackward: m and l must be [batch, heads, new_len]");
+    }
+    FusedAttentionGrad g{DeviceTensor({batch, newLen, dim}), DeviceTensor({batch, totalLen, dim}),
+                         DeviceTensor({batch, totalLen, dim})};
+    Scratch stats(std::max<std::size_t>(statCount, 1) * 2 * sizeof(float));
+    bfb::AttentionBackwardArgs a;
+    a.batch = static_cast<int64_t>(batch);
+    a.newLen = static_cast<int64_t>(newLen);
+    a.totalLen = static_cast<int64_t>(totalLen);
+    a.numHeads = static_cast<int64_t>(numHeads);
+    a.headDim = static_cast<int64_t>(headDim);
+    a.ldQ = a.ldK = a.ldV = a.ldO = a.ldDo = a.ldDq = a.ldDk = a.ldDv = static_cast<int64_t>(dim);
+    a.scale = scaleFactor;
+    a.oldLen = static_cast<int64_t>(oldLen);
+    a.causal = 1;
+    a.m = m.data();
+    a.l = l.data();
+    a.dQ = g.dQ.data();
+    a.dK = g.dK.data();
+    a.dV = g.dV.data();
+    a.lse2Scratch = stats.as<float>();
+    a.dTermScratch = stats.as<float>() + statCount;
+    if (!bf16) {
+        a.dtype = BFB_F32;
+        a.dOut = dOutput.data();
+        a.q = q.data();
+        a.k = k.data();
+        a.v = v.data();
+        a.out = output.data();
+        bfb::attentionBackward(a, nullptr);
+        return g;
+    }
+    std::size_t nq = q.elementCount(), nk = k.elementCount();
+    Scratch q16(nq * 2), k16(nk * 2), v16(nk * 2), o16(nq * 2), g16(nq * 2);
+    bfb::castScaled(q.data(), BFB_F32, q16.ptr, BFB_BF16, static_cast<int64_t>(nq), 1.0f, nullptr, nullptr);
+    bfb::castScaled(k.data(), BFB_F32, k16.ptr, BFB_BF16, static_cast<int64_t>(nk), 1.0f, nullptr, nullptr);
+    bfb::castScaled(v.data(), BFB_F32, v16.ptr, BFB_BF16, static_cast<int64_t>(nk), 1.0f, nullptr, nullptr);
+    bfb::castScaled(output.data(), BFB_F32, o16.ptr, BFB_BF16, static_cast<int64_t>(nq), 1.0f, nullptr, nullptr);
+    bfb::castScaled(dOutput.data(), BFB_F32, g16.ptr, BFB_BF16, static_cast<int64_t>(nq), 1.0f, nullptr, nullptr);
+    a.dtype = BFB_BF16;
+    a.dOut = g16.ptr;
+    a.q = q16.ptr;
+    a.k = k16.ptr;
+    a.v = v16.ptr;
+    a.out = o16.ptr;
+    bfb::attentionBackward(a, nullptr);
+    return g;
+}
+
 DeviceTensor selfAttentionImpl(const DeviceTensor& input, const DeviceTensor& wq, const DeviceTensor& wk,
                                const DeviceTensor& wv, const DeviceTensor& wout, std::size_t numHeads, bool bf16,
                                const char* name) {
@@ -454,6 +525,11 @@ struct CachedWeight {
     std::size_t bytes;
     std::size_t k, n;
 };
+// bf16 copies in the weight's own [K,N] layout, which the backward's dA = G B^T reads as its [N,K] operand
+std::unordered_map<const float*, CachedWeight>& naturalWeightCache() {
+    static std::unordered_map<const float*, CachedWeight> cache;
+    return cache;
+}
 std::unordered_map<const float*, CachedWeight>& weightCache() {
     static std::unordered_map<const float*, CachedWeight> cache;
     return cache;
@@ -463,6 +539,46 @@ std::unordered_map<const float*, CachedWeight>& weightCache() {
 void invalidateBf16WeightCache() {
     for (auto& kv : weightCache()) bfb::poolRelease(kv.second.ptr, kv.second.bytes);
     weightCache().clear();
+    for (auto& kv : naturalWeightCache()) bfb::poolRelease(kv.second.ptr, kv.second.bytes);
+    naturalWeightCache().clear();
+}
+
+namespace {
+MatmulGrad matmulBackwardImpl(const DeviceTensor& a, const DeviceTensor& b, const DeviceTensor& gradOutput, bool cached,
+                              const char* name) {
+    if (a.rank() != 2 || b.rank() != 2 || gradOutput.rank() != 2 || a.dim(1) != b.dim(0) ||
+        gradOutput.dim(0) != a.dim(0) || gradOutput.dim(1) != b.dim(1)) {
+        throw std::invalid_argument(std::string(name) + ": incompatible shapes");
+    }
+    std::size_t m = a.dim(0), k = a.dim(1), n = b.dim(1);
+    const void* natural = nullptr;
+    if (cached && k * n > 0) {
+        auto& cache = naturalWeightCache();
+        auto it = cache.find(b.data());
+        if (it == cache.end() || it->second.k != k || it->second.n != n) {
+            if (it != cache.end()) {
+                bfb::poolRelease(it->second.ptr, it->second.bytes);
+                cache.erase(it);
+            }
+            CachedWeight cw{bfb::poolAcquire(k * n * 2), k * n * 2, k, n};
+            bfb::castScaled(b.data(), BFB_F32, cw.ptr, BFB_BF16, static_cast<int64_t>(k * n), 1.0f, nullptr, nullptr);
+            it = cache.emplace(b.data(), cw).first;
+        }
+        natural = it->second.ptr;
+    }
+    MatmulGrad g{DeviceTensor({m, k}), DeviceTensor({k, n})};
+    bfb::matmulBf16Backward(a.data(), b.data(), gradOutput.data(), g.dA.data(), g.dB.data(), static_cast<int64_t>(m),
+                            static_cast<int64_t>(k), static_cast<int64_t>(n), natural, nullptr);
+    return g;
+}
+}  // namespace
+
+MatmulGrad matmulBf16Backward(const DeviceTensor& a, const DeviceTensor& b, const DeviceTensor& gradOutput) {
+    return matmulBackwardImpl(a, b, gradOutput, false, "matmulBf16Backward");
+}
+
+MatmulGrad matmulBf16BackwardCachedWeight(const DeviceTensor& a, const DeviceTensor& b, const DeviceTensor& gradOutput) {
+    return matmulBackwardImpl(a, b, gradOutput, true, "matmulBf16BackwardCachedWeight");
 }
 
 DeviceTensor matmulBf16CachedWeight(const DeviceTensor& a, const DeviceTensor& b) {
@@ -626,6 +742,20 @@ FusedAttentionForwardResult fusedAttentionForwardBf16(const DeviceTensor& q, con
                                                       const DeviceTensor& v, std::size_t numHeads, float scaleFactor,
                                                       std::size_t oldLen) {
     return attentionImpl(q, k, v, numHeads, scaleFactor, oldLen, true);
+}
+
+FusedAttentionGrad fusedAttentionBackward(const DeviceTensor& dOutput, const DeviceTensor& q, const DeviceTensor& k,
+                                          const DeviceTensor& v, const DeviceTensor& output, const DeviceTensor& m,
+                                          const DeviceTensor& l, std::size_t numHeads, float scaleFactor,
+                                          std::size_t oldLen) {
+    return attentionBackwardImpl(dOutput, q, k, v, output, m, l, numHeads, scaleFactor, oldLen, false);
+}
+
+FusedAttentionGrad fusedAttentionBackwardBf16(const DeviceTensor& dOutput, const DeviceTensor& q, const DeviceTensor& k,
+                                              const DeviceTensor& v, const DeviceTensor& output, const DeviceTensor& m,
+                                              const DeviceTensor& l, std::size_t numHeads, float scaleFactor,
+                                              std::size_t oldLen) {
+    return attentionBackwardImpl(dOutput, q, k, v, output, m, l, numHeads, scaleFactor, oldLen, true);
 }
 
 }  // namespace bfb200

@@ -19,6 +19,8 @@ struct NcclApi {
     ncclResult_t (*getUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*commInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*allReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*groupStart)() = nullptr;
+    ncclResult_t (*groupEnd)() = nullptr;
     ncclResult_t (*commDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*commAbort)(ncclComm_t) = nullptr;
     ncclResult_t (*commGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
@@ -39,6 +41,8 @@ NcclApi& api() {
     a.getUniqueId = reinterpret_cast<decltype(a.getUniqueId)>(sym("ncclGetUniqueId"));
     a.commInitRank = reinterpret_cast<decltype(a.commInitRank)>(sym("ncclCommInitRank"));
     a.allReduce = reinterpret_cast<decltype(a.allReduce)>(sym("ncclAllReduce"));
+    a.groupStart = reinterpret_cast<decltype(a.groupStart)>(sym("ncclGroupStart"));
+    a.groupEnd = reinterpret_cast<decltype(a.groupEnd)>(sym("ncclGroupEnd"));
     a.commDestroy = reinterpret_cast<decltype(a.commDestroy)>(sym("ncclCommDestroy"));
     a.commAbort = reinterpret_cast<decltype(a.commAbort)>(sym("ncclCommAbort"));
     a.commGetAsyncError = reinterpret_cast<decltype(a.commGetAsyncError)>(sym("ncclCommGetAsyncError"));
@@ -82,6 +86,28 @@ void tpAllReduceSum(void* deviceBuffer, std::int64_t count, int dtype, void* str
     check(api().allReduce(deviceBuffer, deviceBuffer, static_cast<size_t>(count), dtype == BFB_F32 ? ncclFloat32 : ncclBfloat16,
                           ncclSum, gComm, static_cast<cudaStream_t>(stream)),
           "allReduce");
+}
+
+void tpAverageGradients(void* const* deviceBuffers, const std::int64_t* counts, int tensors, void* stream) {
+    if (gComm == nullptr) bfb::fail(BFB_INVALID_ARGUMENT, "gradient average: communicator not initialised (bfb_tp_init)");
+    bfb::require(tensors >= 0, "gradient average: negative tensor count");
+    bfb::require(tensors == 0 || (deviceBuffers != nullptr && counts != nullptr), "gradient average: null table");
+    for (int i = 0; i < tensors; ++i) {
+        bfb::require(counts[i] >= 0, "gradient average: negative element count");
+        bfb::require(counts[i] == 0 || deviceBuffers[i] != nullptr, "gradient average: null gradient buffer");
+    }
+    // one group: the library fuses the per-parameter reductions into as few launches as it can, so that the many small
+    // tensors (biases, norms) cost no launch each
+    check(api().groupStart(), "groupStart");
+    ncclResult_t first = ncclSuccess;
+    for (int i = 0; i < tensors && first == ncclSuccess; ++i) {
+        if (counts[i] == 0) continue;
+        first = api().allReduce(deviceBuffers[i], deviceBuffers[i], static_cast<size_t>(counts[i]), ncclFloat32, ncclAvg, gComm,
+                                static_cast<cudaStream_t>(stream));
+    }
+    const ncclResult_t end = api().groupEnd();
+    check(first, "allReduce (average)");
+    check(end, "groupEnd");
 }
 
 void tpDestroy() {

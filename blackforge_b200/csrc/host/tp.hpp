@@ -11,6 +11,10 @@ void tpUniqueId(void* hostId128);
 void tpInit(const void* hostId128, int rank, int world);
 // In-place sum over all ranks on `stream`; dtype is BFB_F32 or BFB_BF16.
 void tpAllReduceSum(void* deviceBuffer, std::int64_t count, int dtype, void* stream);
+// In-place average over all ranks of `tensors` fp32 gradient buffers, issued as one group on `stream`: replaces the
+// reference's host-staged average (download every replica's gradient, add and scale on the host, upload to every
+// replica; src/backend/cuda/multi_gpu_train_runner.cu:275-297).
+void tpAverageGradients(void* const* deviceBuffers, const std::int64_t* counts, int tensors, void* stream);
 void tpDestroy();
 bool tpReady();
 // Waits for `stream` like cudaStreamSynchronize, but with a deadline (BFB_TP_TIMEOUT_MS, default 120 s) while a

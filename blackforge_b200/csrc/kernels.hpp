@@ -97,6 +97,11 @@ void gemmSkinny(const GemmArgs& args, cudaStream_t stream);
 // True when the tcgen05 kernel takes this problem (otherwise the CUDA-core kernel runs).
 bool gemmUsesTensorCores(const GemmArgs& args);
 void matmulTransposeB(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, cudaStream_t stream);
+// Gradients of C = A B on the bf16 tensor-core route (matmulBf16Backward, src/backend/cuda/ops_tensorcore.cu:389-417):
+// dA[m,k] = G[m,n] B^T and dB[k,n] = A^T G from fp32 a [m,k], b [k,n], grad [m,n]; operands rounded to bf16, fp32
+// accumulation and results. `bNatural16` (may be null) is a ready bf16 copy of b in its own [k,n] layout.
+void matmulBf16Backward(const float* a, const float* b, const float* grad, float* dA, float* dB, int64_t m, int64_t k,
+                        int64_t n, const void* bNatural16, cudaStream_t stream);
 
 struct AttentionArgs {
     const void* q = nullptr;
@@ -122,6 +127,33 @@ bool attentionDecodeEligible(const AttentionArgs& args);
 void attentionDecode(const AttentionArgs& args, cudaStream_t stream);
 void attentionForward(const AttentionArgs& args, cudaStream_t stream);
 bool attentionUsesTensorCores(const AttentionArgs& args);
+
+// Backward of the attention core (attention_bwd.cu): dQ, dK, dV in fp32 from dOut, q, k, v, out (f32 or bf16, one
+// type for all five) and the forward's row statistics m, l [batch, heads, new_len]. lse2Scratch and dTermScratch are
+// caller-provided [batch * heads * new_len] floats. head_dim 128 in bf16 runs on the tensor cores.
+struct AttentionBackwardArgs {
+    const void* dOut = nullptr;
+    const void* q = nullptr;
+    const void* k = nullptr;
+    const void* v = nullptr;
+    const void* out = nullptr;
+    const float* m = nullptr;
+    const float* l = nullptr;
+    float* dQ = nullptr;
+    float* dK = nullptr;
+    float* dV = nullptr;
+    float* lse2Scratch = nullptr;
+    float* dTermScratch = nullptr;
+    int dtype = 0;
+    int64_t batch = 0, newLen = 0, totalLen = 0, numHeads = 0, headDim = 0;
+    int64_t ldQ = 0, ldK = 0, ldV = 0, ldO = 0, ldDo = 0, ldDq = 0, ldDk = 0, ldDv = 0;
+    float scale = 1.0f;
+    int64_t oldLen = 0;
+    int causal = 1;
+    int* dStatus = nullptr;
+};
+void attentionBackward(const AttentionBackwardArgs& args, cudaStream_t stream);
+bool attentionBackwardUsesTensorCores(const AttentionBackwardArgs& args);
 
 // Tensor-core kernels (gemm_tc.cu / attention_tc.cu); callers have checked eligibility.
 void gemmTensorCore(const GemmArgs& args, cudaStream_t stream);

@@ -9,7 +9,8 @@
 // It needs the reference's headers to compile (-I<blackforge>/include) and nothing else from it. Same error
 // behaviour as the reference: std::invalid_argument for shape / rank / range problems, std::runtime_error for
 // everything else (cuda_check.hpp:14-53). Training (Model::backward, zeroGrad, the *ForwardCached and *Backward
-// functions, train runners) is outside this backend: those members throw, the free functions are not defined here.
+// functions, train runners) is outside this backend: those members throw, the free functions are not defined here,
+// except fusedAttentionBackward (the gradient of the attention core), which is.
 //
 // How the reference's private layout is served without touching its headers:
 //  * DeviceTensor has no way to adopt memory; a result that arrives from the C ABI as a pool pointer is taken over
@@ -580,6 +581,35 @@ FusedAttentionForwardResult fusedAttentionForward(const DeviceTensor& q, const D
     r.l = DeviceTensor({q.dim(0), numHeads, q.dim(1)});
     r.output = attentionCore(q, k, v, numHeads, scaleFactor, oldLen, false, &r.m, &r.l);
     return r;
+}
+
+// ---- fused_attention.hpp:59-76 ---------------------------------------------------------------------------------
+// The one piece of the training side that is served: the gradient of the attention core, in the reference's fp32
+// arithmetic (the tensor-core route of the library is reached through bfb_attention_bwd with bf16 operands).
+FusedAttentionGrad fusedAttentionBackward(const DeviceTensor& dOutput, const DeviceTensor& q, const DeviceTensor& k,
+                                          const DeviceTensor& v, const DeviceTensor& output, const DeviceTensor& m,
+                                          const DeviceTensor& l, std::size_t numHeads, float scaleFactor,
+                                          std::size_t oldLen) {
+    if (q.rank() != 3 || k.rank() != 3 || v.rank() != 3 || k.shape() != v.shape() || q.dim(0) != k.dim(0) ||
+        q.dim(2) != k.dim(2) || numHeads == 0 || q.dim(2) % numHeads != 0 || k.dim(1) != oldLen + q.dim(1) ||
+        dOutput.shape() != q.shape() || output.shape() != q.shape() ||
+        m.elementCount() != q.dim(0) * numHeads * q.dim(1) || l.elementCount() != m.elementCount()) {
+        throw std::invalid_argument("fusedAttentionBackward: incompatible shapes");
+    }
+    const std::size_t batch = q.dim(0), newLen = q.dim(1), totalLen = k.dim(1), dim = q.dim(2), hd = dim / numHeads;
+    FusedAttentionGrad g;
+    g.dQ = DeviceTensor(q.shape());
+    g.dK = DeviceTensor(k.shape());
+    g.dV = DeviceTensor(k.shape());
+    DeviceTensor scratch({2, batch, numHeads, newLen});
+    const int64_t ld = static_cast<int64_t>(dim);
+    check(bfb_attention_bwd(dOutput.data(), q.data(), k.data(), v.data(), output.data(), m.data(), l.data(), g.dQ.data(),
+                            g.dK.data(), g.dV.data(), scratch.data(), BFB_F32, static_cast<int64_t>(batch),
+                            static_cast<int64_t>(newLen), static_cast<int64_t>(totalLen), static_cast<int64_t>(numHeads),
+                            static_cast<int64_t>(hd), ld, ld, ld, ld, scaleFactor, static_cast<int64_t>(oldLen), 1, nullptr,
+                            nullptr));
+    check(bfb_stream_synchronize(nullptr));   // the scratch tensor goes back to the pool on return
+    return g;
 }
 
 // ---- model.hpp:57-113 -------------------------------------------------------------------------------------------

@@ -254,6 +254,12 @@ bfb_status bfb_gemm_few_rows(const void* d_a, const void* d_w, void* d_c, int64_
 bfb_status bfb_matmul_transpose_b(const float* d_a, const float* d_b, float* d_c, int64_t m, int64_t n, int64_t k,
                                   void* stream);
 
+/* Gradients of C = A B with bf16 operands (matmulBf16Backward, src/backend/cuda/ops_tensorcore.cu:389-417):
+ * d_da[M,K] = grad[M,N] * b^T and d_db[K,N] = a^T * grad from fp32 a [M,K], b [K,N], grad [M,N]; operands are
+ * rounded to bf16, accumulation and results are fp32. A zero dimension zero-fills both results, as there. */
+bfb_status bfb_matmul_bf16_backward(const float* d_a, const float* d_b, const float* d_grad, float* d_da, float* d_db,
+                                    int64_t m, int64_t k, int64_t n, void* stream);
+
 /* ---- causal attention core ---------------------------------------------------------------------
  * Replaces fusedAttentionForward (src/backend/cuda/fused_attention.cu:315-341, kernel :60-157).
  * q [batch, new_len, H*D] with row stride ld_q elements; k, v [batch, total_len, H*D] with strides
@@ -269,6 +275,20 @@ bfb_status bfb_attention_fwd(const void* d_q, const void* d_k, const void* d_v, 
                              int32_t dtype, int64_t batch, int64_t new_len, int64_t total_len, int64_t num_heads,
                              int64_t head_dim, int64_t ld_q, int64_t ld_k, int64_t ld_v, int64_t ld_o, float scale,
                              int64_t old_len, int32_t causal, int32_t* d_status, void* stream);
+
+/* Backward of the attention core. Replaces cuda::fusedAttentionBackward
+ * (src/backend/cuda/fused_attention.cu:343-380; kernels computeDKernel :166-190 and
+ * tiledFusedAttentionBackwardKernel :200-303). d_dout, d_q, d_out are [batch, new_len, ld_in] and d_k, d_v
+ * [batch, total_len, ld_kv], all of `dtype` (BFB_F32 or BFB_BF16); d_m, d_l are the forward's row statistics
+ * [batch, num_heads, new_len]. Results are fp32: d_dq [batch, new_len, ld_grad_q], d_dk and d_dv
+ * [batch, total_len, ld_grad_kv] (every element written: keys no query sees get zero). d_scratch holds
+ * 2 * batch * num_heads * new_len floats. head_dim 128 in bf16 runs on the tensor cores (operands rounded to
+ * bf16, fp32 accumulation); other shapes on a CUDA-core kernel that keeps the reference's arithmetic. */
+bfb_status bfb_attention_bwd(const void* d_dout, const void* d_q, const void* d_k, const void* d_v, const void* d_out,
+                             const float* d_m, const float* d_l, float* d_dq, float* d_dk, float* d_dv, float* d_scratch,
+                             int32_t dtype, int64_t batch, int64_t new_len, int64_t total_len, int64_t num_heads,
+                             int64_t head_dim, int64_t ld_in, int64_t ld_kv, int64_t ld_grad_q, int64_t ld_grad_kv,
+                             float scale, int64_t old_len, int32_t causal, int32_t* d_status, void* stream);
 
 /* ---- model: the IR executor's device side ------------------------------------------------------
  * Replaces cuda::Model (src/backend/cuda/model.cu:139-306: constructor, forward, parameters),
@@ -470,6 +490,11 @@ bfb_status bfb_selftest_collective_watchdog(int32_t ranks, int32_t skip_rank, in
 bfb_status bfb_tp_unique_id(void* h_id_128);
 bfb_status bfb_tp_init(const void* h_id_128, int32_t rank, int32_t world);
 bfb_status bfb_tp_allreduce_sum(void* d_buf, int64_t count, int32_t dtype, void* stream);
+/* In-place average over all ranks of n_tensors fp32 gradient buffers (d_grads[i] holds counts[i] elements; both
+ * tables are host arrays), one grouped NCCL all-reduce on `stream`. Replaces the host-staged gradient average of the
+ * data-parallel train runner (src/backend/cuda/multi_gpu_train_runner.cu:275-297: every replica's gradient copied to
+ * the host, added, scaled by 1/replicas and copied back to every replica). */
+bfb_status bfb_gradients_average(void* const* d_grads, const int64_t* counts, int32_t n_tensors, void* stream);
 bfb_status bfb_tp_destroy(void);
 
 #ifdef __cplusplus

@@ -213,6 +213,65 @@ def attention_core(q, k, v, num_heads: int, causal: bool = True, old_len: int = 
     return out
 
 
+def attention_forward_stats(q, k, v, num_heads: int, scale_factor: float, old_len: int = 0):
+    """(output, m, l) of the fused forward: m the row maximum of the scaled, masked scores and l the sum of
+    exp(score - m), per (batch, head, query row) — the statistics the backward needs
+    (src/backend/cuda/fused_attention.cu:56-156; the mask j <= oldLen + i of :96-99)."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    B, new_len, dim = q.shape
+    total_len = k.shape[1]
+    hd = dim // num_heads
+    out = np.zeros_like(q)
+    m = np.zeros((B, num_heads, new_len), F32)
+    l = np.zeros((B, num_heads, new_len), F32)
+    i = np.arange(new_len)[:, None]
+    j = np.arange(total_len)[None, :]
+    for b in range(B):
+        for h in range(num_heads):
+            sl = slice(h * hd, (h + 1) * hd)
+            s = (q[b, :, sl].astype(np.float64) @ k[b, :, sl].astype(np.float64).T) * float(scale_factor)
+            s = np.where(j > old_len + i, -np.inf, s)
+            mx = s.max(axis=1)
+            e = np.exp(s - mx[:, None])
+            lsum = e.sum(axis=1)
+            out[b, :, sl] = ((e / lsum[:, None]) @ v[b, :, sl].astype(np.float64)).astype(F32)
+            m[b, h], l[b, h] = mx.astype(F32), lsum.astype(F32)
+    return out, m, l
+
+
+def attention_backward(d_out, q, k, v, out, m, l, num_heads: int, scale_factor: float, old_len: int = 0):
+    """(dQ, dK, dV) of the fused attention core, the arithmetic of fusedAttentionBackward
+    (src/backend/cuda/fused_attention.cu:158-303): D_i = dot(out_i, dOut_i) (:166-190); per visible key j
+    p = exp(score - m_i) / l_i, dP = dot(dOut_i, v_j), dScore = p (dP - D_i), dQ_i += dScore scale k_j,
+    dK_j += dScore scale q_i, dV_j += p dOut_i (:255-296); keys no query row sees keep zero (:366-367).
+    Accumulated in float64, so that it is the exact value both the reference's fp32 atomics and a tensor-core
+    kernel approximate."""
+    g, q, k, v, out = (np.asarray(t, dtype=np.float64) for t in (d_out, q, k, v, out))
+    m, l = np.asarray(m, dtype=np.float64), np.asarray(l, dtype=np.float64)
+    B, new_len, dim = q.shape
+    total_len = k.shape[1]
+    hd = dim // num_heads
+    dq = np.zeros((B, new_len, dim), np.float64)
+    dk = np.zeros((B, total_len, dim), np.float64)
+    dv = np.zeros((B, total_len, dim), np.float64)
+    i = np.arange(new_len)[:, None]
+    j = np.arange(total_len)[None, :]
+    visible = j <= old_len + i
+    for b in range(B):
+        for h in range(num_heads):
+            sl = slice(h * hd, (h + 1) * hd)
+            d_term = (out[b, :, sl] * g[b, :, sl]).sum(axis=1)
+            s = (q[b, :, sl] @ k[b, :, sl].T) * float(scale_factor)
+            with np.errstate(over="ignore"):
+                p = np.where(visible, np.exp(np.where(visible, s, 0.0) - m[b, h][:, None]) / l[b, h][:, None], 0.0)
+            dp = g[b, :, sl] @ v[b, :, sl].T
+            ds = p * (dp - d_term[:, None]) * float(scale_factor)
+            dq[b, :, sl] = ds @ k[b, :, sl]
+            dk[b, :, sl] = ds.T @ q[b, :, sl]
+            dv[b, :, sl] = p.T @ g[b, :, sl]
+    return dq.astype(F32), dk.astype(F32), dv.astype(F32)
+
+
 def self_attention(x, wq, wk, wv, wout, num_heads: int, causal: bool = True, gemm=None, exact_order: bool = True):
     x = _f32(x)
     if x.ndim != 3:

@@ -20,6 +20,7 @@
 #include <string>
 #include <vector>
 
+#include "blackforge/backend/cuda/autodiff.hpp"
 #include "blackforge/backend/cuda/device_query.hpp"
 #include "blackforge/backend/cuda/device_tensor.hpp"
 #include "blackforge/backend/cuda/fused_attention.hpp"
@@ -242,6 +243,66 @@ int refCudaFusedAttentionTimed(const float* q, const int64_t* qShape, const floa
         cudaEventDestroy(b);
         *msPerCall = static_cast<double>(ms) / (iters > 0 ? iters : 1);
         gOut = r.output.toHost();
+    });
+}
+
+// fusedAttentionForward followed by fusedAttentionBackward of the reference (src/backend/cuda/fused_attention.cu:
+// 305-380) on fp32 host operands; every result is copied to the caller's host buffers: out [batch, newLen, dim],
+// m and l [batch, heads, newLen], dQ [batch, newLen, dim], dK and dV [batch, totalLen, dim]. `iters` > 0 also times
+// the backward call alone on the device.
+int refCudaFusedAttentionBackward(const float* dOut, const float* q, const int64_t* qShape, const float* k,
+                                  const int64_t* kShape, const float* v, int64_t numHeads, float scale, int64_t oldLen,
+                                  float* out, float* m, float* l, float* dQ, float* dK, float* dV, int iters,
+                                  double* msPerCall) {
+    return guarded([&] {
+        cuda::DeviceTensor dq = cuda::DeviceTensor::fromHost(hostTensor(q, qShape, 3));
+        cuda::DeviceTensor dk = cuda::DeviceTensor::fromHost(hostTensor(k, kShape, 3));
+        cuda::DeviceTensor dv = cuda::DeviceTensor::fromHost(hostTensor(v, kShape, 3));
+        cuda::DeviceTensor dg = cuda::DeviceTensor::fromHost(hostTensor(dOut, qShape, 3));
+        const std::size_t heads = static_cast<std::size_t>(numHeads), old = static_cast<std::size_t>(oldLen);
+        cuda::FusedAttentionForwardResult f = cuda::fusedAttentionForward(dq, dk, dv, heads, scale, old);
+        cuda::FusedAttentionGrad g = cuda::fusedAttentionBackward(dg, dq, dk, dv, f.output, f.m, f.l, heads, scale, old);
+        if (iters > 0 && msPerCall != nullptr) {
+            cudaEvent_t a = nullptr, b = nullptr;
+            if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) throw std::runtime_error("cudaEventCreate failed");
+            cudaDeviceSynchronize();
+            cudaEventRecord(a, nullptr);
+            for (int i = 0; i < iters; ++i) g = cuda::fusedAttentionBackward(dg, dq, dk, dv, f.output, f.m, f.l, heads, scale, old);
+            cudaEventRecord(b, nullptr);
+            if (cudaEventSynchronize(b) != cudaSuccess) throw std::runtime_error("the reference's attention backward failed on the device");
+            float ms = 0.0f;
+            cudaEventElapsedTime(&ms, a, b);
+            cudaEventDestroy(a);
+            cudaEventDestroy(b);
+            *msPerCall = static_cast<double>(ms) / iters;
+        }
+        auto copyOut = [](const cuda::DeviceTensor& t, float* dst) {
+            if (dst == nullptr) return;
+            Tensor h = t.toHost();
+            std::copy(h.data().begin(), h.data().end(), dst);
+        };
+        copyOut(f.output, out);
+        copyOut(f.m, m);
+        copyOut(f.l, l);
+        copyOut(g.dQ, dQ);
+        copyOut(g.dK, dK);
+        copyOut(g.dV, dV);
+    });
+}
+
+// matmulBf16Backward of the reference (src/backend/cuda/ops_tensorcore.cu:389-417) on fp32 host operands a [m,k],
+// b [k,n], grad [m,n]; dA [m,k] and dB [k,n] are copied to the caller's host buffers.
+int refCudaMatmulBf16Backward(const float* a, const float* b, const float* grad, int64_t m, int64_t k, int64_t n, float* dA,
+                              float* dB) {
+    return guarded([&] {
+        const int64_t sa[2] = {m, k}, sb[2] = {k, n}, sg[2] = {m, n};
+        cuda::DeviceTensor da = cuda::DeviceTensor::fromHost(hostTensor(a, sa, 2));
+        cuda::DeviceTensor db = cuda::DeviceTensor::fromHost(hostTensor(b, sb, 2));
+        cuda::DeviceTensor dg = cuda::DeviceTensor::fromHost(hostTensor(grad, sg, 2));
+        cuda::MatmulGrad r = cuda::matmulBf16Backward(da, db, dg);
+        Tensor ha = r.dA.toHost(), hb = r.dB.toHost();
+        std::copy(ha.data().begin(), ha.data().end(), dA);
+        std::copy(hb.data().begin(), hb.data().end(), dB);
     });
 }
 

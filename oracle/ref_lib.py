@@ -349,6 +349,38 @@ def cuda_fused_attention_timed(q, k, v, num_heads: int, scale: float, old_len: i
     return _cuda_result(), ms.value
 
 
+def cuda_fused_attention_backward(d_out, q, k, v, num_heads: int, scale: float, old_len: int = 0, iters: int = 0):
+    """The reference's fusedAttentionForward + fusedAttentionBackward on fp32 operands: a dict with out, m, l, dq, dk,
+    dv (and ms, the device time of one backward call, when iters > 0)."""
+    ga, qa, ka, va = (np.ascontiguousarray(t, dtype=np.float32) for t in (d_out, q, k, v))
+    qs, ks = (C.c_int64 * 3)(*qa.shape), (C.c_int64 * 3)(*ka.shape)
+    batch, new_len, _ = qa.shape
+    res = {"out": np.empty_like(qa), "m": np.empty((batch, num_heads, new_len), np.float32),
+           "l": np.empty((batch, num_heads, new_len), np.float32), "dq": np.empty_like(qa), "dk": np.empty_like(ka),
+           "dv": np.empty_like(ka)}
+    ms = C.c_double(0.0)
+    ptr = lambda a: a.ctypes.data_as(C.c_void_p)
+    _cuda_check(cuda_lib().refCudaFusedAttentionBackward(
+        ptr(ga), ptr(qa), qs, ptr(ka), ks, ptr(va), C.c_int64(num_heads), C.c_float(scale), C.c_int64(old_len),
+        ptr(res["out"]), ptr(res["m"]), ptr(res["l"]), ptr(res["dq"]), ptr(res["dk"]), ptr(res["dv"]), C.c_int(iters),
+        C.byref(ms)))
+    if iters > 0:
+        res["ms"] = ms.value
+    return res
+
+
+def cuda_matmul_bf16_backward(a, b, grad):
+    """(dA, dB) of the reference's matmulBf16Backward (cuBLASLt, bf16 operands, fp32 results) for fp32 a [m,k], b [k,n],
+    grad [m,n]."""
+    aa, ba, ga = (np.ascontiguousarray(t, dtype=np.float32) for t in (a, b, grad))
+    (m, k), n = aa.shape, ba.shape[1]
+    d_a, d_b = np.empty((m, k), np.float32), np.empty((k, n), np.float32)
+    ptr = lambda t: t.ctypes.data_as(C.c_void_p)
+    _cuda_check(cuda_lib().refCudaMatmulBf16Backward(ptr(aa), ptr(ba), ptr(ga), C.c_int64(m), C.c_int64(k), C.c_int64(n),
+                                                     ptr(d_a), ptr(d_b)))
+    return d_a, d_b
+
+
 def cuda_lt_gemm_timed(a_ptr: int, b_ptr: int, c_ptr: int, m: int, n: int, k: int, c_is_bf16: bool, warmup: int,
                        iters: int) -> float:
     """Device milliseconds per cublasLtMatmul call configured as the reference's bf16Gemm configures it, on the

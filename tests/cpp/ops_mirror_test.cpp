@@ -124,6 +124,54 @@ std::vector<double> attentionRef(const std::vector<double>& q, const std::vector
     return out;
 }
 
+// gradients of sum(g * attention(q, k, v)) in double, straight from the definition: p = softmax row, dS = p (dP - D)
+struct GradRef {
+    std::vector<double> dq, dk, dv;
+};
+GradRef attentionBackwardRef(const std::vector<double>& g, const std::vector<double>& q, const std::vector<double>& k,
+                             const std::vector<double>& v, std::size_t batch, std::size_t newLen, std::size_t totalLen,
+                             std::size_t dim, std::size_t heads) {
+    const std::size_t hd = dim / heads, old = totalLen - newLen;
+    const double scale = 1.0 / std::sqrt(static_cast<double>(hd));
+    GradRef r{std::vector<double>(q.size(), 0.0), std::vector<double>(k.size(), 0.0), std::vector<double>(v.size(), 0.0)};
+    for (std::size_t b = 0; b < batch; ++b)
+        for (std::size_t h = 0; h < heads; ++h)
+            for (std::size_t i = 0; i < newLen; ++i) {
+                const std::size_t visible = old + i + 1, qi = (b * newLen + i) * dim + h * hd;
+                std::vector<double> p(visible), dp(visible);
+                double m = -1e300, l = 0.0, dTerm = 0.0;
+                for (std::size_t j = 0; j < visible; ++j) {
+                    const std::size_t kj = (b * totalLen + j) * dim + h * hd;
+                    double dot = 0.0, dpv = 0.0;
+                    for (std::size_t d = 0; d < hd; ++d) {
+                        dot += q[qi + d] * k[kj + d];
+                        dpv += g[qi + d] * v[kj + d];
+                    }
+                    p[j] = dot * scale;
+                    dp[j] = dpv;
+                    m = std::fmax(m, p[j]);
+                }
+                for (std::size_t j = 0; j < visible; ++j) {
+                    p[j] = std::exp(p[j] - m);
+                    l += p[j];
+                }
+                for (std::size_t j = 0; j < visible; ++j) {
+                    p[j] /= l;
+                    dTerm += p[j] * dp[j];
+                }
+                for (std::size_t j = 0; j < visible; ++j) {
+                    const std::size_t kj = (b * totalLen + j) * dim + h * hd;
+                    const double ds = p[j] * (dp[j] - dTerm) * scale;
+                    for (std::size_t d = 0; d < hd; ++d) {
+                        r.dq[qi + d] += ds * k[kj + d];
+                        r.dk[kj + d] += ds * q[qi + d];
+                        r.dv[kj + d] += p[j] * g[qi + d];
+                    }
+                }
+            }
+    return r;
+}
+
 }  // namespace
 
 int main() {
@@ -249,6 +297,63 @@ int main() {
         bool sane = lo.shape == std::vector<std::size_t>({batch, heads, newLen});
         for (float v : lo.data) sane = sane && v >= 1.0f - 1e-3f && std::isfinite(v);
         expect(sane, "row sums are [batch, heads, new_len] and at least 1");
+    }
+    {
+        // gradient of the attention core from the forward's own output and statistics: the fp32 route and the bf16
+        // tensor-core route (fused_attention.hpp:59-76), 150 new rows after 40 cached ones
+        const std::size_t newLen = 150, old = 40;
+        HostTensor hq = ramp({batch, newLen, d}, 1.0f, -0.5f), hk = ramp({batch, newLen + old, d}, 0.9f, -0.45f),
+                   hv = ramp({batch, newLen + old, d}, 0.8f, -0.4f), hg = ramp({batch, newLen, d}, 0.7f, -0.3f);
+        const float scale = 1.0f / std::sqrt(128.0f);
+        const GradRef want = attentionBackwardRef(toDouble(hg), toDouble(hq), toDouble(hk), toDouble(hv), batch, newLen,
+                                                  newLen + old, d, heads);
+        DeviceTensor dq = dev(hq), dk = dev(hk), dv = dev(hv), dg = dev(hg);
+        FusedAttentionForwardResult f = fusedAttentionForward(dq, dk, dv, heads, scale, old);
+        FusedAttentionGrad g32 = fusedAttentionBackward(dg, dq, dk, dv, f.output, f.m, f.l, heads, scale, old);
+        near(want.dq, g32.dQ.toHost(), 2e-4, "fusedAttentionBackward dQ");
+        near(want.dk, g32.dK.toHost(), 2e-4, "fusedAttentionBackward dK");
+        near(want.dv, g32.dV.toHost(), 2e-4, "fusedAttentionBackward dV");
+        FusedAttentionGrad g16 = fusedAttentionBackwardBf16(dg, dq, dk, dv, f.output, f.m, f.l, heads, scale, old);
+        near(want.dq, g16.dQ.toHost(), 1e-2, "fusedAttentionBackwardBf16 dQ");
+        near(want.dk, g16.dK.toHost(), 1e-2, "fusedAttentionBackwardBf16 dK");
+        near(want.dv, g16.dV.toHost(), 1e-2, "fusedAttentionBackwardBf16 dV");
+        bool threw = false;
+        try {
+            fusedAttentionBackward(dg, dq, dk, dv, f.output, f.m, f.l, heads, scale, old + 1);
+        } catch (const std::invalid_argument&) {
+            threw = true;
+        }
+        expect(threw, "fusedAttentionBackward rejects old_len + new_len != total_len");
+    }
+    {
+        // gradients of C = A B on the bf16 route (autodiff.hpp:18-37), plain and with the cached weight copy
+        const std::size_t m = 192, k = 256, n = 128;
+        HostTensor ha = ramp({m, k}, 1.0f, -0.5f), hb = ramp({k, n}, 0.9f, -0.45f), hg = ramp({m, n}, 0.8f, -0.4f);
+        std::vector<double> wantA(m * k, 0.0), wantB(k * n, 0.0);
+        for (std::size_t i = 0; i < m; ++i)
+            for (std::size_t j = 0; j < n; ++j) {
+                const double gv = hg.data[i * n + j];
+                for (std::size_t p = 0; p < k; ++p) {
+                    wantA[i * k + p] += gv * hb.data[p * n + j];
+                    wantB[p * n + j] += gv * ha.data[i * k + p];
+                }
+            }
+        DeviceTensor da = dev(ha), db = dev(hb), dg = dev(hg);
+        MatmulGrad g1 = matmulBf16Backward(da, db, dg);
+        near(wantA, g1.dA.toHost(), 2e-5, "matmulBf16Backward dA");
+        near(wantB, g1.dB.toHost(), 2e-5, "matmulBf16Backward dB");
+        MatmulGrad g2 = matmulBf16BackwardCachedWeight(da, db, dg);
+        MatmulGrad g3 = matmulBf16BackwardCachedWeight(da, db, dg);   // second call: the cached copy
+        near(wantA, g2.dA.toHost(), 2e-5, "matmulBf16BackwardCachedWeight dA");
+        near(wantB, g3.dB.toHost(), 2e-5, "matmulBf16BackwardCachedWeight dB (cache hit)");
+        invalidateBf16WeightCache();
+        bool threw = false;
+        try {
+            matmulBf16Backward(da, db, da);
+        } catch (const std::invalid_argument&) {
+            threw = true;
+        }
+        expect(threw, "matmulBf16Backward rejects a gradient of the wrong shape");
     }
     std::printf(failures == 0 ? "ops mirror: all checks passed\n" : "ops mirror: %d check(s) FAILED\n", failures);
     return failures == 0 ? 0 : 1;

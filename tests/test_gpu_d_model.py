@@ -294,20 +294,35 @@ def test_bf16_compute_bf16_storage(gpu):
 
 
 def test_fp8_compute_tracks_bf16(gpu):
-    bf, _, (m, ops, params, ids) = planned_case(gpu, {"storage": "bf16", "compute": "bf16"}, {"compute": "bf16"})
+    """`compute fp8.e4m3` has no reference implementation (parity unpinned); what can be pinned is that the distance
+    between the e4m3 run and the bf16 run is the distance the DEFINITION gives, not something the kernels add: the
+    oracle's emulation of the same arithmetic (per-tensor amax scales, e4m3 operands rounded to nearest even, fp32
+    accumulate) is run through the whole model on the CPU, and its distance from the oracle's bf16 forward is compared
+    with the distance between the two GPU runs."""
+    bf, bf_oracle, (m, ops, params, ids) = planned_case(gpu, {"storage": "bf16", "compute": "bf16"}, {"compute": "bf16"})
     m8 = gpu.Model(ops, precision={"storage": "bf16", "compute": "fp8.e4m3", "accumulate": "fp32"}, random_init=False)
     m8.set_params(params)
     got = m8.forward_host(ids)
-    # The oracle's statement of the same arithmetic (per-tensor amax scales, e4m3 operands, fp32 accumulate).
-    # On identical GEMM inputs the kernel matches it to 1e-5 (test_fp8_scaled_gemm_definition); through a whole
-    # model the two drift apart by the e4m3 noise itself, because a last-bit difference upstream (bf16 vs fp32
-    # activations) moves values across e4m3 rounding boundaries, each flip worth a 6 % step.
     want8 = O.model_forward(ops, params, ids, cuda_policy={"compute": "fp8.e4m3"}, exact_order=False)
-    assert np.linalg.norm(got - want8) / np.linalg.norm(want8) <= 0.15
-    # stated tolerance of the fp8 path against the bf16 run of the same weights: e4m3 keeps 3 mantissa bits, so
-    # every GEMM output carries a few percent of rounding noise on Gaussian data
-    rel_l2 = np.linalg.norm(got - bf) / np.linalg.norm(bf)
-    assert rel_l2 <= 0.15 and top1_agreement(got, bf)[0] >= 0.85
+
+    def rel_l2(a, b):
+        return float(np.linalg.norm(a - b) / np.linalg.norm(b))
+
+    gpu_gap, oracle_gap = rel_l2(got, bf), rel_l2(want8, bf_oracle)
+    gpu_top1, oracle_top1 = top1_agreement(got, bf)[0], top1_agreement(want8, bf_oracle)[0]
+    print(f"e4m3 vs bf16, relative L2: GPU {gpu_gap:.4f}, CPU emulation of the definition {oracle_gap:.4f}; "
+          f"top-1 agreement: GPU {gpu_top1:.4f}, CPU emulation {oracle_top1:.4f}; "
+          f"GPU e4m3 vs emulated e4m3 {rel_l2(got, want8):.4f}")
+    # the e4m3 noise is a property of the format (3 mantissa bits: a few percent per GEMM on Gaussian data): the
+    # kernels add nothing to what the emulation shows
+    assert gpu_gap <= 1.25 * oracle_gap + 5e-3
+    assert gpu_top1 >= oracle_top1 - 0.03
+    # On identical GEMM inputs the kernel matches the emulation to 1e-5 (test_fp8_scaled_gemm_definition); through a
+    # whole model the two runs are two samples of that same noise (a last-bit difference upstream moves values
+    # across e4m3 rounding boundaries, each flip worth a 6 % step), so they are about sqrt(2) gaps apart
+    assert rel_l2(got, want8) <= 1.6 * oracle_gap + 5e-3
+    # stated tolerance of the fp8 path against the bf16 run of the same weights
+    assert gpu_gap <= 0.15 and gpu_top1 >= 0.85
 
 
 def test_planned_route_is_causal_and_batch_independent(gpu):

@@ -121,3 +121,72 @@ def test_two_gpu_tensor_parallel_matches_single_gpu(gpu, tmp_path):
     sharded8 = np.concatenate([np.load(tmp_path / f"logits8_{r}.npy") for r in range(2)], axis=-1)
     assert np.isfinite(sharded8).all()
     assert np.sqrt(np.sum((sharded8 - want16) ** 2) / np.sum(want16 ** 2)) <= 0.15
+
+
+GRAD_WORKER = r"""
+import ctypes as C
+import os, sys, time
+import numpy as np
+sys.path.insert(0, os.environ["BFB_ROOT"])
+import blackforge_b200 as bfb
+rank, world, work = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+bfb.check(bfb.lib().bfb_set_device(rank))
+id_path = os.path.join(work, "nccl_id_grad")
+if rank == 0:
+    ident = bfb.tp_unique_id()
+    with open(id_path + ".tmp", "wb") as f:
+        f.write(ident)
+    os.replace(id_path + ".tmp", id_path)
+else:
+    deadline = time.time() + 120
+    while not os.path.exists(id_path):
+        if time.time() > deadline:
+            raise SystemExit("no communicator id from rank 0")
+        time.sleep(0.05)
+    ident = open(id_path, "rb").read()
+bfb.tp_init(ident, rank, world)
+# every replica's own gradients: a large matrix, ragged small tensors and an empty one, seeded by the rank
+shapes = [(1024, 1536), (1536,), (7,), (0,), (3, 5)]
+rng = np.random.default_rng(100 + rank)
+grads = [rng.standard_normal(s).astype(np.float32) for s in shapes]
+bufs = [bfb.upload(g, bfb.F32) for g in grads]
+table = (C.c_void_p * len(bufs))(*[b.ptr or None for b in bufs])
+counts = (C.c_int64 * len(bufs))(*[g.size for g in grads])
+bfb.check(bfb.lib().bfb_gradients_average(table, counts, len(bufs), None))
+bfb.sync()
+for i, (b, s) in enumerate(zip(bufs, shapes)):
+    np.save(os.path.join(work, f"avg_{rank}_{i}.npy"), bfb.download(b, bfb.F32, s))
+bfb.tp_destroy()
+print("rank", rank, "ok")
+"""
+
+
+def test_two_gpu_gradient_average_matches_the_host_staged_average(gpu, tmp_path):
+    """The grouped NCCL average against the reference's rule (multi_gpu_train_runner.cu:275-297): the replicas'
+    gradients added in replica order and scaled by 1 / replicas; with two replicas both give the same bits, and
+    every replica ends with the same values."""
+    n = C.c_int32(0)
+    gpu.check(gpu.lib().bfb_device_count(C.byref(n)))
+    if n.value < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "grad_worker.py"
+    script.write_text(GRAD_WORKER)
+    env = dict(os.environ, BFB_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, str(script), str(r), "2", str(tmp_path)], env=env, stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    shapes = [(1024, 1536), (1536,), (7,), (0,), (3, 5)]
+    rngs = [np.random.default_rng(100 + r) for r in range(2)]
+    per_rank = [[rng.standard_normal(s).astype(np.float32) for s in shapes] for rng in rngs]
+    for i, s in enumerate(shapes):
+        want = O.scale(O.add(per_rank[0][i], per_rank[1][i]), np.float32(0.5)) if np.prod(s) else np.zeros(s, np.float32)
+        got = [np.load(tmp_path / f"avg_{r}_{i}.npy") for r in range(2)]
+        assert np.array_equal(got[0], got[1]) and np.array_equal(got[0], want), i
+
+
+def test_gradient_average_without_a_communicator_is_refused(gpu):
+    buf = gpu.DeviceBuffer.zeros(16)
+    table = (C.c_void_p * 1)(buf.ptr)
+    counts = (C.c_int64 * 1)(4)
+    assert gpu.lib().bfb_gradients_average(table, counts, 1, None) == gpu.INVALID_ARGUMENT

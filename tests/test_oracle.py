@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 
 from oracle import bf_oracle as O
+from tests.conftest import GOLDEN
 
 C1 = dict(vocab=256, dim=64, layers=2, heads=4, hidden=256, max_seq=32)
 
@@ -221,3 +222,65 @@ def test_live_reference_precision_block_parses(ref):
     src = O.lm_source(seq=8, vocab=16, dim=8, layers=1, heads=2, hidden=16, max_seq=8,
                       precision={"storage": "bf16", "compute": "fp8.e4m3", "accumulate": "fp32"})
     assert ref.Compiled(src).precision() == {"storage": "bf16", "compute": "fp8.e4m3", "accumulate": "fp32"}
+
+
+# ---- attention backward (src/backend/cuda/fused_attention.cu:158-380) ------------------------------------------
+
+def _attention_loss64(q, k, v, g, heads, scale, old_len):
+    """sum(dOut * attention(q, k, v)) in float64, written independently of the oracle's backward."""
+    B, new_len, dim = q.shape
+    total, hd = k.shape[1], dim // heads
+    loss = 0.0
+    i = np.arange(new_len)[:, None]
+    j = np.arange(total)[None, :]
+    for b in range(B):
+        for h in range(heads):
+            sl = slice(h * hd, (h + 1) * hd)
+            s = (q[b, :, sl] @ k[b, :, sl].T) * scale
+            s = np.where(j > old_len + i, -np.inf, s)
+            p = np.exp(s - s.max(axis=1, keepdims=True))
+            p /= p.sum(axis=1, keepdims=True)
+            loss += float(((p @ v[b, :, sl]) * g[b, :, sl]).sum())
+    return loss
+
+
+def test_attention_backward_matches_finite_differences():
+    rng = np.random.default_rng(77)
+    B, H, D, old, new = 1, 2, 4, 2, 5
+    q, g = (rng.standard_normal((B, new, H * D)) for _ in range(2))
+    k, v = (rng.standard_normal((B, old + new, H * D)) for _ in range(2))
+    scale = 0.5
+    out, m, l = O.attention_forward_stats(q, k, v, H, scale, old)
+    dq, dk, dv = O.attention_backward(g, q, k, v, out, m, l, H, scale, old)
+    eps = 1e-5
+    for name, x, grad in (("q", q, dq), ("k", k, dk), ("v", v, dv)):
+        num = np.zeros_like(x)
+        for idx in np.ndindex(*x.shape):
+            keep = x[idx]
+            x[idx] = keep + eps
+            up = _attention_loss64(q, k, v, g, H, scale, old)
+            x[idx] = keep - eps
+            down = _attention_loss64(q, k, v, g, H, scale, old)
+            x[idx] = keep
+            num[idx] = (up - down) / (2 * eps)
+        # the oracle takes fp32 operands and fp32 (out, m, l): 1e-5 relative
+        assert np.max(np.abs(num - grad)) <= 2e-5 * max(1.0, np.max(np.abs(num))), name
+
+
+def test_attention_backward_matches_the_reference_kernel_outputs():
+    """Outputs of the reference's own fusedAttentionForward + fusedAttentionBackward, produced on a B200 by
+    tests/golden/make_attention_backward_golden.py: the oracle's forward statistics and its gradients agree with them
+    to fp32 rounding."""
+    gold = dict(np.load(os.path.join(GOLDEN, "attention_backward.npz")))
+    for tag in ("small", "hd128"):
+        heads, old = int(gold[f"{tag}_heads"]), int(gold[f"{tag}_old_len"])
+        g, q, k, v = (gold[f"{tag}_{n}"] for n in ("d_out", "q", "k", "v"))
+        scale = float(1.0 / np.sqrt(np.float32(q.shape[2] // heads)))
+        out, m, l = O.attention_forward_stats(q, k, v, heads, scale, old)
+        assert np.max(np.abs(out - gold[f"{tag}_out"])) <= 1e-5
+        # the reference keeps a running maximum: m is the final maximum either way, l the matching sum
+        assert np.allclose(m, gold[f"{tag}_m"], atol=1e-5) and np.allclose(l, gold[f"{tag}_l"], rtol=1e-5)
+        got = O.attention_backward(g, q, k, v, gold[f"{tag}_out"], gold[f"{tag}_m"], gold[f"{tag}_l"], heads, scale, old)
+        for name, a in zip(("dq", "dk", "dv"), got):
+            want = gold[f"{tag}_{name}"]
+            assert np.max(np.abs(a - want)) <= 2e-5 * max(1.0, float(np.max(np.abs(want)))), (tag, name)
