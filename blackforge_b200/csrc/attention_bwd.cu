@@ -45,10 +45,10 @@ constexpr int kDsOff = kRingOff + 4 * kTileBytes;
 constexpr int kRowOff = kDsOff + kTileBytes; // [2 steps in flight][lse2, D][128] floats
 constexpr int kBarOff = kRowOff + 2 * 2 * 128 * 4;
 constexpr int kSmemBytes = kBarOff + 256;
-constexpr int kSoftmaxWarps = 4;
-constexpr int kProducerWarp = 4;
-constexpr int kMmaWarp = 5;
-constexpr int kThreads = 192;
+constexpr int kSoftmaxWarps = 8;   // two per lane quadrant of tensor memory; each takes 64 of a step's 128 query columns
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kThreads = 320;
 // A and B formats bf16, fp32 accumulate; bit 15 = A is MN-major, bit 16 = B is MN-major
 constexpr uint32_t kIdescKK = make_idesc(128, 128, 1u, 0u);                  // both K-major
 constexpr uint32_t kIdescKM = make_idesc(128, 128, 1u, 1u);                  // B MN-major (A from TMEM or K-major)
@@ -169,68 +169,89 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
             const uint32_t kLoMn = smem_desc_lo(smem_u32(smem + kKOff), kHalfBytes);
             const uint32_t tS = tmemBase, tDp = tmemBase + 128u, tDv = tmemBase + 256u, tDk = tmemBase + 384u;
             bool alive = mbar_wait(kvFull, 0, abortFlag, status, kDevTimeoutTmaFull);
-            for (int it = 0; it < steps && alive; ++it) {
-                const int stage = it & 1;
-                const uint32_t par = static_cast<uint32_t>(it) & 1u;
-                const uint32_t qLo = smem_desc_lo(smem_u32(smem + kRingOff + stage * 2 * kTileBytes), 0);
-                const uint32_t doLo = qLo + (kTileBytes >> 4);
-                const uint32_t qLoMn = qLo + ((kHalfBytes >> 4) << 16);
-                const uint32_t doLoMn = doLo + ((kHalfBytes >> 4) << 16);
-                if (!mbar_wait(&qFull[stage], (it >> 1) & 1, abortFlag, status, kDevTimeoutTmaFull)) { alive = false; break; }
-                // the S^T columns also receive dQ^T: the previous step's dQ^T must have been read
-                if (it > 0 && !mbar_wait(dqFree, par ^ 1u, abortFlag, status, kDevTimeoutAccEmpty)) { alive = false; break; }
-                tc_fence_after();
+            auto ringLo = [&](int it) { return smem_desc_lo(smem_u32(smem + kRingOff + (it & 1) * 2 * kTileBytes), 0); };
+            auto issueDp = [&](int it) {                    // dP^T = V dO^T (reduction over head_dim)
+                const uint32_t doLo = ringLo(it) + (kTileBytes >> 4);
 #pragma unroll
-                for (int kk = 0; kk < kD / 16; ++kk) {      // S^T = K Q^T (reduction over head_dim)
-                    const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
-                    umma_f16_words(tS, kLo + off, kHi, qLo + off, kHi, kIdescKK, kk > 0 ? 1u : 0u);
-                }
-#pragma unroll
-                for (int kk = 0; kk < kD / 16; ++kk) {      // dP^T = V dO^T
+                for (int kk = 0; kk < kD / 16; ++kk) {
                     const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
                     umma_f16_words(tDp, vLo + off, kHi, doLo + off, kHi, kIdescKK, kk > 0 ? 1u : 0u);
                 }
+            };
+            auto issueS = [&](int it) {                     // S^T = K Q^T
+                const uint32_t qLo = ringLo(it);
+#pragma unroll
+                for (int kk = 0; kk < kD / 16; ++kk) {
+                    const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
+                    umma_f16_words(tS, kLo + off, kHi, qLo + off, kHi, kIdescKK, kk > 0 ? 1u : 0u);
+                }
+            };
+            // the bf16 operand a pair of warps leaves in tensor memory: query rows 0..63 over the first half of the
+            // fp32 region, rows 64..127 over its second half (each warp writes only over columns it alone reads)
+            auto aCol = [](int kk) { return static_cast<uint32_t>((kk >> 2) * 64 + (kk & 3) * 8); };
+            if (alive && mbar_wait(&qFull[0], 0, abortFlag, status, kDevTimeoutTmaFull)) {
+                tc_fence_after();
+                issueS(0);
+                issueDp(0);
                 umma_commit(sFull);
+            } else {
+                alive = false;
+            }
+            for (int it = 0; it < steps && alive; ++it) {
+                const int stage = it & 1;
+                const uint32_t par = static_cast<uint32_t>(it) & 1u;
+                const uint32_t qLoMn = ringLo(it) + ((kHalfBytes >> 4) << 16);
+                const uint32_t doLoMn = qLoMn + (kTileBytes >> 4);
                 if (!mbar_wait(pFull, par, abortFlag, status, kDevTimeoutSoftmax)) { alive = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < kBlk / 16; ++kk) {    // dV += P^T dO (reduction over the query rows)
-                    umma_f16_ts_words(tDv, tS + static_cast<uint32_t>(kk * 8), doLoMn + kk * (2048 >> 4), kHi, kIdescKM,
-                                      (it > 0 || kk > 0) ? 1u : 0u);
+                    umma_f16_ts_words(tDv, tS + aCol(kk), doLoMn + kk * (2048 >> 4), kHi, kIdescKM, (it > 0 || kk > 0) ? 1u : 0u);
                 }
                 if (!mbar_wait(dsFull, par, abortFlag, status, kDevTimeoutSoftmax)) { alive = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < kBlk / 16; ++kk) {    // dK += dS^T Q
-                    umma_f16_ts_words(tDk, tDp + static_cast<uint32_t>(kk * 8), qLoMn + kk * (2048 >> 4), kHi, kIdescKM,
-                                      (it > 0 || kk > 0) ? 1u : 0u);
+                    umma_f16_ts_words(tDk, tDp + aCol(kk), qLoMn + kk * (2048 >> 4), kHi, kIdescKM, (it > 0 || kk > 0) ? 1u : 0u);
                 }
 #pragma unroll
                 for (int kk = 0; kk < kBlk / 16; ++kk) {    // dQ^T = K^T dS^T (reduction over the keys), over S^T / P^T
-                    umma_f16_words(tS, kLoMn + kk * (2048 >> 4), kHi, dsLoMn + kk * (2048 >> 4), kHi, kIdescMM,
-                                   kk > 0 ? 1u : 0u);
+                    umma_f16_words(tS, kLoMn + kk * (2048 >> 4), kHi, dsLoMn + kk * (2048 >> 4), kHi, kIdescMM, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(dqFull);
                 umma_commit(&qEmpty[stage]);
+                if (it + 1 < steps) {
+                    // the next step's dP^T can follow at once (the pipe runs in order, dK has read dS^T by then); its
+                    // S^T shares columns with dQ^T and waits until the gradient warps have read that
+                    if (!mbar_wait(&qFull[stage ^ 1], ((it + 1) >> 1) & 1, abortFlag, status, kDevTimeoutTmaFull)) { alive = false; break; }
+                    tc_fence_after();
+                    issueDp(it + 1);
+                    if (!mbar_wait(dqFree, par, abortFlag, status, kDevTimeoutAccEmpty)) { alive = false; break; }
+                    tc_fence_after();
+                    issueS(it + 1);
+                    umma_commit(sFull);
+                }
             }
             if (alive) umma_commit(accFull);
         }
         __syncwarp();
     } else {
-        // ---------------- softmax / gradient warps: one thread per key row ----------------
-        const int keyRow = warp * 32 + lane;               // key inside the block, also head_dim index for dQ^T
+        // ---------------- gradient warps: a thread owns one key row and 64 of the step's 128 query columns ----------------
+        const int quad = warp & 3, half = warp >> 2;
+        const int keyRow = quad * 32 + lane;               // key inside the block; the head_dim index when reading dQ^T
         const int keyPos = k0 + keyRow;
         const bool keyValid = keyPos < p.totalLen;
-        const uint32_t laneBase = static_cast<uint32_t>(warp * 32) << 16;
-        const uint32_t tS = tmemBase + laneBase, tDp = tS + 128u, tDv = tS + 256u, tDk = tS + 384u;
-        uint8_t* dsTile = smem + kDsOff;
+        const uint32_t laneBase = static_cast<uint32_t>(quad * 32) << 16;
+        const uint32_t tS = tmemBase + laneBase + static_cast<uint32_t>(half * 64), tDp = tS + 128u;
+        uint8_t* dsRow = smem + kDsOff + half * kHalfBytes + keyRow * 128;
+        const bool raggedKeys = k0 + kBlk > p.totalLen;
         bool alive = true;
         for (int it = 0; it < steps && alive; ++it) {
             const uint32_t par = static_cast<uint32_t>(it) & 1u;
             const int q0 = (firstQ + it) * kBlk;
-            // statistics of this step's 128 query rows: thread c writes row c (a row past the end gets +inf, which makes
-            // its probabilities zero). The buffer of two steps ago is free: every warp arrived on the barrier of the
-            // step in between only after its last read.
+            // statistics of this step's 128 query rows: the first four warps bring lse2, the others D (a row past the
+            // end gets +inf, which makes its probabilities zero). The buffer of two steps ago is free: every warp
+            // arrived on the barrier of the step in between only after its last read.
             const int stage = it & 1;
             float* lseS = reinterpret_cast<float*>(smem + kRowOff) + stage * 256;
             float* dS = lseS + 128;
@@ -238,8 +259,8 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
                 const int qi = q0 + keyRow;
                 const bool ok = qi < p.newLen;
                 const size_t at = (static_cast<size_t>(b) * p.numHeads + h) * p.newLen + (ok ? qi : 0);
-                lseS[keyRow] = ok ? p.lse2[at] : INFINITY;
-                dS[keyRow] = ok ? p.dTerm[at] : 0.0f;
+                if (half == 0) lseS[keyRow] = ok ? p.lse2[at] : INFINITY;
+                else dS[keyRow] = ok ? p.dTerm[at] : 0.0f;
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&rowFull[stage]);
@@ -252,25 +273,36 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
                 break;
             }
             tc_fence_after();
-            // ---- P^T = exp2(S^T * scale_log2 - lse2[c]); masked: key beyond the row's causal limit or past the end
-            // row c sees this key iff keyPos <= old_len + q0 + c: columns below firstVisible are masked
+            // ---- P^T = exp2(S^T * scale_log2 - lse2[c]). Row c sees this key iff keyPos <= old_len + q0 + c: columns
+            // below firstVisible are masked, which only the steps on the diagonal (or a ragged last key block) need.
             const int firstVisible = p.causal ? keyPos - p.oldLen - q0 : -1;
-            uint32_t pk[4][16];   // P^T as bf16 pairs, kept for dS^T (chunk c reads columns [32c, 32c+32) and writes
-                                  // [16c, 16c+16), which earlier chunks have already read)
+            const bool maskStep = raggedKeys || (p.causal && k0 + kBlk - 1 - p.oldLen - q0 > 0);
+            const float* lseH = lseS + half * 64;
+            const float* dH = dS + half * 64;
+            uint32_t pk[2][16];   // P^T as bf16 pairs, kept for dS^T (chunk c reads columns [32c, 32c+32) of this warp's
+                                  // half and writes [16c, 16c+16), which it has already read)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t sc[32];
                 tmem_ld_32x32(tS + static_cast<uint32_t>(c * 32), sc);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const int col = c * 32 + i;
-                    float p0 = ex2f(fmaf(__uint_as_float(sc[i]), p.scaleLog2, -lseS[col]));
-                    float p1 = ex2f(fmaf(__uint_as_float(sc[i + 1]), p.scaleLog2, -lseS[col + 1]));
-                    if (!keyValid || col < firstVisible) p0 = 0.0f;
-                    if (!keyValid || col + 1 < firstVisible) p1 = 0.0f;
-                    __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-                    pk[c][i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+                for (int i = 0; i < 32; i += 4) {
+                    const float4 ls = *reinterpret_cast<const float4*>(lseH + c * 32 + i);
+                    float pv[4];
+                    pv[0] = ex2f(fmaf(__uint_as_float(sc[i]), p.scaleLog2, -ls.x));
+                    pv[1] = ex2f(fmaf(__uint_as_float(sc[i + 1]), p.scaleLog2, -ls.y));
+                    pv[2] = ex2f(fmaf(__uint_as_float(sc[i + 2]), p.scaleLog2, -ls.z));
+                    pv[3] = ex2f(fmaf(__uint_as_float(sc[i + 3]), p.scaleLog2, -ls.w));
+                    if (maskStep) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            if (!keyValid || half * 64 + c * 32 + i + e < firstVisible) pv[e] = 0.0f;
+                        }
+                    }
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(pv[0], pv[1]), h1 = __floats2bfloat162_rn(pv[2], pv[3]);
+                    pk[c][i >> 1] = *reinterpret_cast<uint32_t*>(&h0);
+                    pk[c][(i >> 1) + 1] = *reinterpret_cast<uint32_t*>(&h1);
                 }
                 tmem_st_32x16(tS + static_cast<uint32_t>(c * 16), pk[c]);
             }
@@ -278,29 +310,34 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(pFull);
-            // ---- dS^T = scale * P^T o (dP^T - D[c]); written over dP^T (TMEM operand of dK) and to shared memory
+            // ---- dS^T = P^T o (scale dP^T - scale D[c]) (the statistics kernel stores D already scaled); written over
+            // dP^T as the tensor-memory operand of dK, and to shared memory as the operand of dQ^T
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t dp[32];
                 tmem_ld_32x32(tDp + static_cast<uint32_t>(c * 32), dp);
                 tmem_ld_wait();
                 uint32_t packed[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const int col = c * 32 + i;
-                    const float2 pr = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[c][i >> 1]));
-                    const float d0 = pr.x * (__uint_as_float(dp[i]) - dS[col]) * p.scale;
-                    const float d1 = pr.y * (__uint_as_float(dp[i + 1]) - dS[col + 1]) * p.scale;
-                    __nv_bfloat162 hh = __floats2bfloat162_rn(d0, d1);
-                    packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+                for (int i = 0; i < 32; i += 4) {
+                    const float4 dt = *reinterpret_cast<const float4*>(dH + c * 32 + i);
+                    const float2 pa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[c][i >> 1]));
+                    const float2 pb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[c][(i >> 1) + 1]));
+                    const float d0 = pa.x * fmaf(__uint_as_float(dp[i]), p.scale, -dt.x);
+                    const float d1 = pa.y * fmaf(__uint_as_float(dp[i + 1]), p.scale, -dt.y);
+                    const float d2 = pb.x * fmaf(__uint_as_float(dp[i + 2]), p.scale, -dt.z);
+                    const float d3 = pb.y * fmaf(__uint_as_float(dp[i + 3]), p.scale, -dt.w);
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(d0, d1), h1 = __floats2bfloat162_rn(d2, d3);
+                    packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h0);
+                    packed[(i >> 1) + 1] = *reinterpret_cast<uint32_t*>(&h1);
                 }
                 tmem_st_32x16(tDp + static_cast<uint32_t>(c * 16), packed);
-                // shared-memory copy: row = key, 64 query rows per 128-byte half-row, 16-byte pieces swizzled by the row
-                uint8_t* half = dsTile + (c >> 1) * kHalfBytes + keyRow * 128;
+                // shared-memory copy: row = key, this warp's 64 query rows are one 128-byte row of its half tile, 16-byte
+                // pieces swizzled by the row
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
-                    const int piece = (c & 1) * 4 + g;
-                    *reinterpret_cast<uint4*>(half + ((piece ^ (keyRow & 7)) << 4)) =
+                    const int piece = c * 4 + g;
+                    *reinterpret_cast<uint4*>(dsRow + ((piece ^ (keyRow & 7)) << 4)) =
                         make_uint4(packed[g * 4], packed[g * 4 + 1], packed[g * 4 + 2], packed[g * 4 + 3]);
                 }
             }
@@ -309,48 +346,55 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(dsFull);
-            // ---- dQ^T: lane = head_dim index, column = query row; added into dQ (fp32 atomics, a warp = 128 bytes)
+            // ---- dQ^T: lane = head_dim index, column = query row; added into dQ (fp32 reductions, a warp = 128 bytes)
             if (!warp_all(mbar_wait(dqFull, par, abortFlag, status, kDevTimeoutAccFull))) {
                 alive = false;
                 break;
             }
             tc_fence_after();
-            float* dqBase = p.dQ + (static_cast<size_t>(b) * p.newLen + q0) * p.ldDq + static_cast<size_t>(h) * kD + keyRow;
+            const int qFirst = q0 + half * 64;
+            float* dqPtr = p.dQ + (static_cast<size_t>(b) * p.newLen + qFirst) * p.ldDq + static_cast<size_t>(h) * kD + keyRow;
+            const int rowsLeft = p.newLen - qFirst;     // rows of this warp's half that exist
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t dq[32];
                 tmem_ld_32x32(tS + static_cast<uint32_t>(c * 32), dq);
                 tmem_ld_wait();
+                if (rowsLeft >= c * 32 + 32) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int col = c * 32 + i;
-                    if (q0 + col < p.newLen) atomicAdd(dqBase + static_cast<size_t>(col) * p.ldDq, __uint_as_float(dq[i]));
+                    for (int i = 0; i < 32; ++i) {
+                        atomicAdd(dqPtr, __uint_as_float(dq[i]));
+                        dqPtr += p.ldDq;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (c * 32 + i < rowsLeft) atomicAdd(dqPtr, __uint_as_float(dq[i]));
+                        dqPtr += p.ldDq;
+                    }
                 }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(dqFree);
         }
-        // ---- dV and dK of this CTA's keys
+        // ---- dV (first four warps) and dK (the others) of this CTA's keys
         if (alive && steps > 0 && warp_all(mbar_wait(accFull, 0, abortFlag, status, kDevTimeoutAccFull))) {
             tc_fence_after();
+            const uint32_t tAcc = tmemBase + laneBase + (half == 0 ? 256u : 384u);
+            float* dst = (half == 0 ? p.dV : p.dK) +
+                         (static_cast<size_t>(b) * p.totalLen + keyPos) * (half == 0 ? p.ldDv : p.ldDk) + static_cast<size_t>(h) * kD;
 #pragma unroll 1
-            for (int which = 0; which < 2; ++which) {
-                float* dst = (which == 0 ? p.dV : p.dK) +
-                             (static_cast<size_t>(b) * p.totalLen + keyPos) * (which == 0 ? p.ldDv : p.ldDk) +
-                             static_cast<size_t>(h) * kD;
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t acc[32];
-                    tmem_ld_32x32((which == 0 ? tDv : tDk) + static_cast<uint32_t>(c * 32), acc);
-                    tmem_ld_wait();
-                    if (keyValid) {
+            for (int c = 0; c < 4; ++c) {
+                uint32_t acc[32];
+                tmem_ld_32x32(tAcc + static_cast<uint32_t>(c * 32), acc);
+                tmem_ld_wait();
+                if (keyValid) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            *reinterpret_cast<float4*>(dst + c * 32 + i) =
-                                make_float4(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]), __uint_as_float(acc[i + 2]),
-                                            __uint_as_float(acc[i + 3]));
-                        }
+                    for (int i = 0; i < 32; i += 4) {
+                        *reinterpret_cast<float4*>(dst + c * 32 + i) =
+                            make_float4(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]), __uint_as_float(acc[i + 2]),
+                                        __uint_as_float(acc[i + 3]));
                     }
                 }
             }
@@ -370,11 +414,11 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
     }
 }
 
-// D_i = sum_d O dO and lse2_i = (m_i + ln l_i) * log2(e), one warp per (batch, head, query row)
+// D_i = dScale * sum_d O dO and lse2_i = (m_i + ln l_i) * log2(e), one warp per (batch, head, query row)
 template <typename T>
 __global__ void attentionBackwardPrepKernel(const T* out, const T* dOut, const float* m, const float* l, float* lse2,
                                             float* dTerm, int64_t rows, int numHeads, int64_t newLen, int headDim,
-                                            int64_t ldO, int64_t ldDo) {
+                                            int64_t ldO, int64_t ldDo, float dScale) {
     const int64_t warpId = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (warpId >= rows) return;
@@ -388,7 +432,7 @@ __global__ void attentionBackwardPrepKernel(const T* out, const T* dOut, const f
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
     if (lane == 0) {
-        dTerm[warpId] = acc;
+        dTerm[warpId] = acc * dScale;
         const float lv = l[warpId];
         // a row with no visible key (l == 0) never contributes: +inf makes every probability zero
         lse2[warpId] = lv > 0.0f ? (m[warpId] + logf(lv)) * 1.4426950408889634f : INFINITY;
@@ -491,15 +535,17 @@ void attentionBackward(const AttentionBackwardArgs& a, cudaStream_t stream) {
     }
     if (rows == 0) return;
     const int threads = 256;
+    // the tensor-core kernel wants D already multiplied by the score scale
+    const float dScale = attentionBackwardUsesTensorCores(a) ? a.scale : 1.0f;
     const unsigned prepBlocks = static_cast<unsigned>((rows * 32 + threads - 1) / threads);
     if (a.dtype == BFB_F32) {
         attentionBackwardPrepKernel<float><<<prepBlocks, threads, 0, stream>>>(
             static_cast<const float*>(a.out), static_cast<const float*>(a.dOut), a.m, a.l, a.lse2Scratch, a.dTermScratch, rows,
-            static_cast<int>(a.numHeads), a.newLen, static_cast<int>(a.headDim), a.ldO, a.ldDo);
+            static_cast<int>(a.numHeads), a.newLen, static_cast<int>(a.headDim), a.ldO, a.ldDo, dScale);
     } else {
         attentionBackwardPrepKernel<__nv_bfloat16><<<prepBlocks, threads, 0, stream>>>(
             static_cast<const __nv_bfloat16*>(a.out), static_cast<const __nv_bfloat16*>(a.dOut), a.m, a.l, a.lse2Scratch,
-            a.dTermScratch, rows, static_cast<int>(a.numHeads), a.newLen, static_cast<int>(a.headDim), a.ldO, a.ldDo);
+            a.dTermScratch, rows, static_cast<int>(a.numHeads), a.newLen, static_cast<int>(a.headDim), a.ldO, a.ldDo, dScale);
     }
     BFB_LAUNCH_CHECK();
     noteLaunch();

@@ -4,6 +4,7 @@ run, on small cases.
 
     python -m blackforge_b200.kernel_bench gemm --m 65536 --n 2048 --k 2048 [--dtype bf16|fp8] [--epilogue none]
     python -m blackforge_b200.kernel_bench attention --batch 16 --heads 16 --seq 2048
+    python -m blackforge_b200.kernel_bench attention-bwd --batch 8 --heads 16 --seq 2048
     python -m blackforge_b200.kernel_bench rmsnorm --rows 65536 --dim 2048
     python -m blackforge_b200.kernel_bench embed --batch 32 --seq 2048 --vocab 32000 --dim 2048
 
@@ -22,7 +23,7 @@ import numpy as np
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attention", "rmsnorm", "embed", "checkpoint"])
+    ap.add_argument("kernel", choices=["gemm", "attention", "attention-bwd", "rmsnorm", "embed", "checkpoint"])
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--hidden", type=int, default=5632)
     ap.add_argument("--chunk-mib", type=int, default=0, help="checkpoint: staging buffer size (0: the loader's default)")
@@ -113,6 +114,25 @@ def main():
                                             status.ptr, None))
         work, unit = 4.0 * 128 * args.batch * args.heads * args.seq * (args.seq + 1) / 2.0, "TFLOP/s"
         desc = {"batch": args.batch, "heads": args.heads, "seq": args.seq, "head_dim": 128, "flops": "causal"}
+    elif args.kernel == "attention-bwd":
+        # the forward first (its output and row statistics are the backward's operands), then the backward alone is timed:
+        # the statistics kernel, the zero fill of the three gradients and the tensor-core kernel
+        dim = args.heads * 128
+        q, k, v, g = (rand_dev(args.batch * args.seq * dim, bfb.BF16) for _ in range(4))
+        out = bfb.DeviceBuffer(args.batch * args.seq * dim * 2)
+        rows = args.batch * args.heads * args.seq
+        m_, l_, scratch = bfb.DeviceBuffer(rows * 4), bfb.DeviceBuffer(rows * 4), bfb.DeviceBuffer(rows * 8)
+        dq, dk, dv = (bfb.DeviceBuffer(args.batch * args.seq * dim * 4) for _ in range(3))
+        bfb.check(lib.bfb_attention_fwd(q.ptr, k.ptr, v.ptr, out.ptr, m_.ptr, l_.ptr, bfb.BF16, args.batch, args.seq, args.seq,
+                                        args.heads, 128, dim, dim, dim, dim, float(128 ** -0.5), 0, 1, status.ptr, None))
+
+        def run():
+            bfb.check(lib.bfb_attention_bwd(g.ptr, q.ptr, k.ptr, v.ptr, out.ptr, m_.ptr, l_.ptr, dq.ptr, dk.ptr, dv.ptr,
+                                            scratch.ptr, bfb.BF16, args.batch, args.seq, args.seq, args.heads, 128, dim, dim,
+                                            dim, dim, float(128 ** -0.5), 0, 1, status.ptr, None))
+        # five products of 2 * 128 flops per visible (query, key) pair
+        work, unit = 10.0 * 128 * args.batch * args.heads * args.seq * (args.seq + 1) / 2.0, "TFLOP/s"
+        desc = {"batch": args.batch, "heads": args.heads, "seq": args.seq, "head_dim": 128, "flops": "causal, 5 products"}
     elif args.kernel == "rmsnorm":
         sd = bfb.BF16 if args.stream_dtype == "bf16" else bfb.F32
         x = rand_dev(args.rows * args.dim, sd)
