@@ -12,11 +12,13 @@
 //    keys on the tensor-memory lanes: S^T = K Q^T and dP^T = V dO^T are ordinary shared-memory MMAs; a thread owns one
 //    key row of both, so P^T and dS^T are written back as bf16 over them in tensor memory and are the TMEM operand of
 //    dV += P^T dO and dK += dS^T Q, whose accumulators stay in tensor memory for the whole CTA. Only dS^T also goes
-//    through shared memory, as the B operand of dQ^T = K^T dS^T (K^T is the K tile itself, read MN-major); dQ^T comes
-//    back with head_dim on the lanes, so a warp's atomic adds into dQ are 128 contiguous bytes.
-//    TMEM columns: S^T / P^T / dQ^T [0,128)  dP^T / dS^T [128,256)  dV [256,384)  dK [384,512).
-//    dK and dV are written with plain stores (a CTA owns its keys); dQ is accumulated with fp32 atomics over the key
-//    blocks (zeroed by the host first), as the reference accumulates dK and dV.
+//    through shared memory, as the A operand of dQ = dS K (both tiles read MN-major: the dS^T tile with its query rows
+//    and the K tile with head_dim contiguous). The dQ tile of a step is staged in the shared-memory slot that held the
+//    step's Q and dO and ADDED to global memory by the TMA unit (cp.reduce.async.bulk.tensor), four instructions per
+//    step; per-element atomics took a third of the step.
+//    TMEM columns: S^T / P^T / dQ [0,128)  dP^T / dS^T [128,256)  dV [256,384)  dK [384,512).
+//    dK and dV are written with plain stores (a CTA owns its keys); dQ is accumulated over the key blocks (zeroed by the
+//    host first), as the reference accumulates dK and dV with atomics.
 //  * attentionBackwardSimtKernel: any head_dim <= 256, fp32 or bf16 storage, one warp per query row; the shape-general
 //    path, with the reference's own order of work.
 // All mbarrier waits are bounded.
@@ -75,12 +77,12 @@ struct BwdParams {
 __global__ void __launch_bounds__(kThreads, 1)
 attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_constant__ CUtensorMap tmapK,
                           const __grid_constant__ CUtensorMap tmapV, const __grid_constant__ CUtensorMap tmapDo,
-                          BwdParams p, int* status) {
+                          const __grid_constant__ CUtensorMap tmapDq, BwdParams p, int* status) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOff);
     uint64_t* kvFull = bars;          // [1]
     uint64_t* qFull = bars + 1;       // [2]
-    uint64_t* qEmpty = bars + 3;      // [2]
+    uint64_t* dqStaged = bars + 3;    // [2] the step's dQ tile is in the slot its Q and dO came from (8 warps)
     uint64_t* sFull = bars + 5;       // S^T and dP^T complete
     uint64_t* pFull = bars + 6;       // P^T written (4 warps)
     uint64_t* dsFull = bars + 7;      // dS^T written (4 warps)
@@ -112,7 +114,7 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
         mbar_init(kvFull, 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&qFull[i], 1);
-            mbar_init(&qEmpty[i], 1);
+            mbar_init(&dqStaged[i], kSoftmaxWarps);
         }
         mbar_init(sFull, 1);
         mbar_init(pFull, kSoftmaxWarps);
@@ -128,6 +130,7 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
         tma_prefetch_desc(&tmapK);
         tma_prefetch_desc(&tmapV);
         tma_prefetch_desc(&tmapDo);
+        tma_prefetch_desc(&tmapDq);
     }
     if (warp == kMmaWarp) {
         tmem_alloc(tmemSlot, 512);
@@ -146,17 +149,31 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
             tma_load_3d(smem + kKOff + kHalfBytes, &tmapK, kvFull, h * kD + 64, k0, b);
             tma_load_3d(smem + kVOff, &tmapV, kvFull, h * kD, k0, b);
             tma_load_3d(smem + kVOff + kHalfBytes, &tmapV, kvFull, h * kD + 64, k0, b);
-            for (int it = 0; it < steps; ++it) {
+            // Slot (it & 1) receives the Q and dO tiles of step it. Before that, the dQ tile the gradient warps staged
+            // there for step it - 2 is added to global memory; the slot is free again when that tile has been read.
+            for (int it = 0; it < steps + 2; ++it) {
                 const int stage = it & 1;
-                if (!mbar_wait(&qEmpty[stage], ((it >> 1) & 1) ^ 1, abortFlag, status, kDevTimeoutStageEmpty)) break;
-                uint8_t* dst = smem + kRingOff + stage * 2 * kTileBytes;
-                const int q0 = (firstQ + it) * kBlk;
-                mbar_arrive_expect_tx(&qFull[stage], 2 * kTileBytes);
-                tma_load_3d(dst, &tmapQ, &qFull[stage], h * kD, q0, b);
-                tma_load_3d(dst + kHalfBytes, &tmapQ, &qFull[stage], h * kD + 64, q0, b);
-                tma_load_3d(dst + kTileBytes, &tmapDo, &qFull[stage], h * kD, q0, b);
-                tma_load_3d(dst + kTileBytes + kHalfBytes, &tmapDo, &qFull[stage], h * kD + 64, q0, b);
+                uint8_t* slot = smem + kRingOff + stage * 2 * kTileBytes;
+                if (it >= 2) {
+                    if (!mbar_wait(&dqStaged[stage], ((it - 2) >> 1) & 1, abortFlag, status, kDevTimeoutStageEmpty)) break;
+                    const int qPrev = (firstQ + it - 2) * kBlk;
+#pragma unroll
+                    for (int box = 0; box < 4; ++box) {
+                        tma_reduce_add_3d(&tmapDq, slot + box * (kBlk * 128), h * kD + box * 32, qPrev, b);
+                    }
+                    tma_store_commit();
+                    tma_store_wait_read();
+                }
+                if (it < steps) {
+                    const int q0 = (firstQ + it) * kBlk;
+                    mbar_arrive_expect_tx(&qFull[stage], 2 * kTileBytes);
+                    tma_load_3d(slot, &tmapQ, &qFull[stage], h * kD, q0, b);
+                    tma_load_3d(slot + kHalfBytes, &tmapQ, &qFull[stage], h * kD + 64, q0, b);
+                    tma_load_3d(slot + kTileBytes, &tmapDo, &qFull[stage], h * kD, q0, b);
+                    tma_load_3d(slot + kTileBytes + kHalfBytes, &tmapDo, &qFull[stage], h * kD + 64, q0, b);
+                }
             }
+            tma_store_wait_all();
         }
         __syncwarp();
     } else if (warp == kMmaWarp) {
@@ -215,11 +232,10 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
                     umma_f16_ts_words(tDk, tDp + aCol(kk), qLoMn + kk * (2048 >> 4), kHi, kIdescKM, (it > 0 || kk > 0) ? 1u : 0u);
                 }
 #pragma unroll
-                for (int kk = 0; kk < kBlk / 16; ++kk) {    // dQ^T = K^T dS^T (reduction over the keys), over S^T / P^T
-                    umma_f16_words(tS, kLoMn + kk * (2048 >> 4), kHi, dsLoMn + kk * (2048 >> 4), kHi, kIdescMM, kk > 0 ? 1u : 0u);
+                for (int kk = 0; kk < kBlk / 16; ++kk) {    // dQ = dS K (reduction over the keys), over S^T / P^T
+                    umma_f16_words(tS, dsLoMn + kk * (2048 >> 4), kHi, kLoMn + kk * (2048 >> 4), kHi, kIdescMM, kk > 0 ? 1u : 0u);
                 }
-                umma_commit(dqFull);
-                umma_commit(&qEmpty[stage]);
+                umma_commit(dqFull);     // dK has finished too: the slot of this step's Q and dO is free for the dQ tile
                 if (it + 1 < steps) {
                     // the next step's dP^T can follow at once (the pipe runs in order, dK has read dS^T by then); its
                     // S^T shares columns with dQ^T and waits until the gradient warps have read that
@@ -238,7 +254,7 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
     } else {
         // ---------------- gradient warps: a thread owns one key row and 64 of the step's 128 query columns ----------------
         const int quad = warp & 3, half = warp >> 2;
-        const int keyRow = quad * 32 + lane;               // key inside the block; the head_dim index when reading dQ^T
+        const int keyRow = quad * 32 + lane;               // key inside the block; the query row when reading dQ
         const int keyPos = k0 + keyRow;
         const bool keyValid = keyPos < p.totalLen;
         const uint32_t laneBase = static_cast<uint32_t>(quad * 32) << 16;
@@ -346,37 +362,33 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(dsFull);
-            // ---- dQ^T: lane = head_dim index, column = query row; added into dQ (fp32 reductions, a warp = 128 bytes)
+            // ---- dQ: lane = query row, columns = head_dim. The tile goes to the slot this step's Q and dO came from, as
+            // four boxes of 32 floats x 128 rows in the 128-byte swizzle; the producer thread hands it to the TMA unit.
             if (!warp_all(mbar_wait(dqFull, par, abortFlag, status, kDevTimeoutAccFull))) {
                 alive = false;
                 break;
             }
             tc_fence_after();
-            const int qFirst = q0 + half * 64;
-            float* dqPtr = p.dQ + (static_cast<size_t>(b) * p.newLen + qFirst) * p.ldDq + static_cast<size_t>(h) * kD + keyRow;
-            const int rowsLeft = p.newLen - qFirst;     // rows of this warp's half that exist
-#pragma unroll 1
+            uint8_t* slot = smem + kRingOff + stage * 2 * kTileBytes;
+#pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t dq[32];
                 tmem_ld_32x32(tS + static_cast<uint32_t>(c * 32), dq);
                 tmem_ld_wait();
-                if (rowsLeft >= c * 32 + 32) {
+                uint8_t* row = slot + (half * 2 + c) * (kBlk * 128) + keyRow * 128;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        atomicAdd(dqPtr, __uint_as_float(dq[i]));
-                        dqPtr += p.ldDq;
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (c * 32 + i < rowsLeft) atomicAdd(dqPtr, __uint_as_float(dq[i]));
-                        dqPtr += p.ldDq;
-                    }
+                for (int j = 0; j < 8; ++j) {
+                    *reinterpret_cast<uint4*>(row + ((j ^ (keyRow & 7)) << 4)) =
+                        make_uint4(dq[j * 4], dq[j * 4 + 1], dq[j * 4 + 2], dq[j * 4 + 3]);
                 }
             }
+            fence_proxy_async_smem();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(dqFree);
+            if (lane == 0) {
+                mbar_arrive(dqFree);
+                mbar_arrive(&dqStaged[stage]);
+            }
         }
         // ---- dV (first four warps) and dK (the others) of this CTA's keys
         if (alive && steps > 0 && warp_all(mbar_wait(accFull, 0, abortFlag, status, kDevTimeoutAccFull))) {
@@ -513,9 +525,9 @@ void makeMap3(TensorMapStorage* out, const void* base, int64_t dim, int64_t len,
 
 bool attentionBackwardUsesTensorCores(const AttentionBackwardArgs& a) {
     if (a.dtype != BFB_BF16 || a.headDim != kD) return false;
-    if (a.ldQ % 8 || a.ldK % 8 || a.ldV % 8 || a.ldDo % 8 || a.ldDk % 4 || a.ldDv % 4) return false;
+    if (a.ldQ % 8 || a.ldK % 8 || a.ldV % 8 || a.ldDo % 8 || a.ldDq % 4 || a.ldDk % 4 || a.ldDv % 4) return false;
     auto aligned16 = [](const void* ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
-    if (!aligned16(a.q) || !aligned16(a.k) || !aligned16(a.v) || !aligned16(a.dOut) || !aligned16(a.dK) || !aligned16(a.dV))
+    if (!aligned16(a.q) || !aligned16(a.k) || !aligned16(a.v) || !aligned16(a.dOut) || !aligned16(a.dQ) || !aligned16(a.dK) || !aligned16(a.dV))
         return false;
     if (a.batch * a.numHeads > 0x3FFFFF || a.totalLen > 0x3FFFFFFF || a.newLen > 0x3FFFFFFF) return false;
     return true;
@@ -553,7 +565,13 @@ void attentionBackward(const AttentionBackwardArgs& a, cudaStream_t stream) {
         BFB_CUDA(cudaMemset2DAsync(a.dQ, static_cast<size_t>(a.ldDq) * 4, 0, static_cast<size_t>(a.numHeads * a.headDim) * 4,
                                    static_cast<size_t>(a.batch) * a.newLen, stream));
         const int64_t dim = a.numHeads * a.headDim;
-        TensorMapStorage tq, tk, tv, tg;
+        TensorMapStorage tq, tk, tv, tg, tdq;
+        {
+            uint64_t dims[3] = {static_cast<uint64_t>(dim), static_cast<uint64_t>(a.newLen), static_cast<uint64_t>(a.batch)};
+            uint64_t strides[2] = {static_cast<uint64_t>(a.ldDq) * 4, static_cast<uint64_t>(a.ldDq) * 4 * static_cast<uint64_t>(a.newLen)};
+            uint32_t box[3] = {32u, 128u, 1u};
+            encodeTensorMap(&tdq, a.dQ, 4, 3, dims, strides, box);
+        }
         makeMap3(&tq, a.q, dim, a.newLen, a.batch, a.ldQ);
         makeMap3(&tk, a.k, dim, a.totalLen, a.batch, a.ldK);
         makeMap3(&tv, a.v, dim, a.totalLen, a.batch, a.ldV);
@@ -581,7 +599,8 @@ void attentionBackward(const AttentionBackwardArgs& a, cudaStream_t stream) {
         BFB_CUDA(cudaFuncSetAttribute(attentionBackwardTcKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         attentionBackwardTcKernel<<<static_cast<unsigned>(blocks), kThreads, kSmemBytes, stream>>>(
             *reinterpret_cast<const CUtensorMap*>(tq.bytes), *reinterpret_cast<const CUtensorMap*>(tk.bytes),
-            *reinterpret_cast<const CUtensorMap*>(tv.bytes), *reinterpret_cast<const CUtensorMap*>(tg.bytes), p, a.dStatus);
+            *reinterpret_cast<const CUtensorMap*>(tv.bytes), *reinterpret_cast<const CUtensorMap*>(tg.bytes),
+            *reinterpret_cast<const CUtensorMap*>(tdq.bytes), p, a.dStatus);
         BFB_LAUNCH_CHECK();
         noteLaunch();
         return;

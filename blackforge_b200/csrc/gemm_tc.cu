@@ -374,7 +374,9 @@ void encodeTensorMap(TensorMapStorage* out, const void* base, int elemBytes, int
         estr[i] = 1;
         if (i > 0) gstrides[i - 1] = stridesBytes[i - 1];
     }
-    CUtensorMapDataType dt = elemBytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    CUtensorMapDataType dt = elemBytes == 4   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                             : elemBytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                              : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     CUresult r = encodeFn()(reinterpret_cast<CUtensorMap*>(out->bytes), dt, static_cast<cuuint32_t>(rank),
                             const_cast<void*>(base), gdims, gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

@@ -165,7 +165,7 @@ void attentionTensorCore(const AttentionArgs& args, cudaStream_t stream);
 int selfTestBoundedWait(unsigned long long limitNs, int* observedHost, cudaStream_t stream);
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda dependency).
-// dims/strides innermost first; strides in bytes for dims 1..rank-1; elemBytes 1 or 2.
+// dims/strides innermost first; strides in bytes for dims 1..rank-1; elemBytes 1, 2 (bf16) or 4 (fp32).
 struct TensorMapStorage {
     alignas(64) unsigned char bytes[128];
 };
