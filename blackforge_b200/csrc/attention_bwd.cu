@@ -89,8 +89,9 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
     uint64_t* dqFull = bars + 8;      // dQ^T complete (and everything issued before it)
     uint64_t* dqFree = bars + 9;      // dQ^T read (4 warps): the S^T columns are free
     uint64_t* accFull = bars + 10;    // dV and dK complete
-    uint64_t* rowFull = bars + 11;    // [2] row statistics of a step written (4 warps)
-    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 13);
+    uint64_t* rowFull = bars + 11;    // [2] row statistics of a step written (8 warps)
+    uint64_t* slotFree = bars + 13;   // every product that reads the step's Q and dO tiles is complete
+    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 14);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
     if ((smem_u32(smem) & 1023u) != 0u) {
@@ -122,6 +123,7 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
         mbar_init(dqFull, 1);
         mbar_init(dqFree, kSoftmaxWarps);
         mbar_init(accFull, 1);
+        mbar_init(slotFree, 1);
         mbar_init(&rowFull[0], kSoftmaxWarps);
         mbar_init(&rowFull[1], kSoftmaxWarps);
         *abortFlag = 0;
@@ -228,14 +230,15 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
                 if (!mbar_wait(dsFull, par, abortFlag, status, kDevTimeoutSoftmax)) { alive = false; break; }
                 tc_fence_after();
 #pragma unroll
-                for (int kk = 0; kk < kBlk / 16; ++kk) {    // dK += dS^T Q
-                    umma_f16_ts_words(tDk, tDp + aCol(kk), qLoMn + kk * (2048 >> 4), kHi, kIdescKM, (it > 0 || kk > 0) ? 1u : 0u);
-                }
-#pragma unroll
                 for (int kk = 0; kk < kBlk / 16; ++kk) {    // dQ = dS K (reduction over the keys), over S^T / P^T
                     umma_f16_words(tS, dsLoMn + kk * (2048 >> 4), kHi, kLoMn + kk * (2048 >> 4), kHi, kIdescMM, kk > 0 ? 1u : 0u);
                 }
-                umma_commit(dqFull);     // dK has finished too: the slot of this step's Q and dO is free for the dQ tile
+                umma_commit(dqFull);
+#pragma unroll
+                for (int kk = 0; kk < kBlk / 16; ++kk) {    // dK += dS^T Q
+                    umma_f16_ts_words(tDk, tDp + aCol(kk), qLoMn + kk * (2048 >> 4), kHi, kIdescKM, (it > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(slotFree);   // dV and dK have read this step's dO and Q: their slot may take the dQ tile
                 if (it + 1 < steps) {
                     // the next step's dP^T can follow at once (the pipe runs in order, dK has read dS^T by then); its
                     // S^T shares columns with dQ^T and waits until the gradient warps have read that
@@ -262,24 +265,28 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
         uint8_t* dsRow = smem + kDsOff + half * kHalfBytes + keyRow * 128;
         const bool raggedKeys = k0 + kBlk > p.totalLen;
         bool alive = true;
+        auto fetchStat = [&](int qBase) -> float {
+            const int qi = qBase + keyRow;
+            const bool ok = qi < p.newLen;
+            const size_t at = (static_cast<size_t>(b) * p.numHeads + h) * p.newLen + (ok ? qi : 0);
+            if (half == 0) return ok ? p.lse2[at] : INFINITY;
+            return ok ? p.dTerm[at] : 0.0f;
+        };
+        if (steps > 0) {
+            reinterpret_cast<float*>(smem + kRowOff)[half * 128 + keyRow] = fetchStat(firstQ * kBlk);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&rowFull[0]);
+        }
         for (int it = 0; it < steps && alive; ++it) {
             const uint32_t par = static_cast<uint32_t>(it) & 1u;
             const int q0 = (firstQ + it) * kBlk;
-            // statistics of this step's 128 query rows: the first four warps bring lse2, the others D (a row past the
-            // end gets +inf, which makes its probabilities zero). The buffer of two steps ago is free: every warp
-            // arrived on the barrier of the step in between only after its last read.
+            // statistics of the step's 128 query rows (lse2 from the first four warps, D from the others; a row past the
+            // end gets +inf, which makes its probabilities zero): this step's are in shared memory already, the next
+            // step's are fetched now and stored at the end of the step, so that no step waits for global memory
             const int stage = it & 1;
             float* lseS = reinterpret_cast<float*>(smem + kRowOff) + stage * 256;
             float* dS = lseS + 128;
-            {
-                const int qi = q0 + keyRow;
-                const bool ok = qi < p.newLen;
-                const size_t at = (static_cast<size_t>(b) * p.numHeads + h) * p.newLen + (ok ? qi : 0);
-                if (half == 0) lseS[keyRow] = ok ? p.lse2[at] : INFINITY;
-                else dS[keyRow] = ok ? p.dTerm[at] : 0.0f;
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&rowFull[stage]);
+            const float nextStat = it + 1 < steps ? fetchStat(q0 + kBlk) : 0.0f;
             if (!warp_all(mbar_wait(&rowFull[stage], (it >> 1) & 1, abortFlag, status, kDevTimeoutOther))) {
                 alive = false;
                 break;
@@ -369,25 +376,37 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
                 break;
             }
             tc_fence_after();
+            uint32_t dq[2][32];
+            tmem_ld_32x32(tS, dq[0]);
+            tmem_ld_32x32(tS + 32u, dq[1]);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(dqFree);       // the columns may take the next step's S^T
+            if (!warp_all(mbar_wait(slotFree, par, abortFlag, status, kDevTimeoutAccFull))) {
+                alive = false;
+                break;
+            }
             uint8_t* slot = smem + kRingOff + stage * 2 * kTileBytes;
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                uint32_t dq[32];
-                tmem_ld_32x32(tS + static_cast<uint32_t>(c * 32), dq);
-                tmem_ld_wait();
                 uint8_t* row = slot + (half * 2 + c) * (kBlk * 128) + keyRow * 128;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     *reinterpret_cast<uint4*>(row + ((j ^ (keyRow & 7)) << 4)) =
-                        make_uint4(dq[j * 4], dq[j * 4 + 1], dq[j * 4 + 2], dq[j * 4 + 3]);
+                        make_uint4(dq[c][j * 4], dq[c][j * 4 + 1], dq[c][j * 4 + 2], dq[c][j * 4 + 3]);
                 }
             }
             fence_proxy_async_smem();
-            tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(dqFree);
-                mbar_arrive(&dqStaged[stage]);
+            if (lane == 0) mbar_arrive(&dqStaged[stage]);
+            // the statistics of the next step, fetched at the top of this one, go to the other buffer: every warp
+            // has left the step that read it (this step's S^T needed all of them to finish the one before)
+            if (it + 1 < steps) {
+                float* nextRows = reinterpret_cast<float*>(smem + kRowOff) + (stage ^ 1) * 256 + half * 128;
+                nextRows[keyRow] = nextStat;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&rowFull[stage ^ 1]);
             }
         }
         // ---- dV (first four warps) and dK (the others) of this CTA's keys
