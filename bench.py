@@ -560,12 +560,48 @@ def attention_config2(ctx, peaks, iters=20, warmup=3):
         torch.cuda.synchronize()
         times.append(s.elapsed_time(e))
     code = int(status.to_numpy(np.int32, (1,))[0])
-    for b in (q, k, v, out, status):
-        b.free()
     ms = statistics.median(times)
     flops = 4.0 * hd * batch * heads * seq * (seq + 1) / 2.0
     tflops = flops / (ms / 1e3) / 1e12
+    # the backward of the same problem (the training-side kernel): statistics kernel, zero fill of dQ and the tcgen05
+    # kernel, from the forward's output and row statistics
+    backward = None
+    try:
+        rows = batch * heads * seq
+        g = rand_bf16(14)
+        m_, l_, scratch = bfb.DeviceBuffer(rows * 4), bfb.DeviceBuffer(rows * 4), bfb.DeviceBuffer(rows * 8)
+        grads = [bfb.DeviceBuffer(n * 4) for _ in range(3)]
+        bfb.check(lib.bfb_attention_fwd(q.ptr, k.ptr, v.ptr, out.ptr, m_.ptr, l_.ptr, bfb.BF16, batch, seq, seq, heads, hd,
+                                        dim, dim, dim, dim, float(hd ** -0.5), 0, 1, status.ptr, None))
+
+        def run_bwd():
+            bfb.check(lib.bfb_attention_bwd(g.ptr, q.ptr, k.ptr, v.ptr, out.ptr, m_.ptr, l_.ptr, grads[0].ptr, grads[1].ptr,
+                                            grads[2].ptr, scratch.ptr, bfb.BF16, batch, seq, seq, heads, hd, dim, dim, dim,
+                                            dim, float(hd ** -0.5), 0, 1, status.ptr, None))
+        for _ in range(warmup):
+            run_bwd()
+        torch.cuda.synchronize()
+        btimes = []
+        for _ in range(max(5, iters // 2)):
+            flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            run_bwd()
+            e.record()
+            torch.cuda.synchronize()
+            btimes.append(s.elapsed_time(e))
+        bms = statistics.median(btimes)
+        backward = {"kernel": "attentionBackwardTcKernel (tcgen05, keys on the tensor-memory lanes, dQ added by TMA)",
+                    "ms": bms, "tflops": 2.5 * flops / (bms / 1e3) / 1e12, "flops": "causal: five products of 2*D per visible pair",
+                    "device_status": int(status.to_numpy(np.int32, (1,))[0])}
+        for b in [g, m_, l_, scratch] + grads:
+            b.free()
+    except Exception as exc:   # the forward figure stands without it
+        backward = {"error": repr(exc)}
+    for b in (q, k, v, out, status):
+        b.free()
     return {"workload": "causal attention forward, bf16 [16, 16, 2048, 128], fp32 online softmax (BASELINE config 2)",
+            "backward": backward,
             "kernel": "attentionTcKernel (tcgen05, S/P/O in tensor memory, TMA-fed)", "ms": ms, "ms_min": min(times),
             "tflops": tflops, "flops": "causal: 4*D per visible (query, key) pair", "iters": iters,
             "frac_of_burst": tflops / peaks["tflops_burst"], "frac_of_sustained": tflops / peaks["tflops_sustained"],

@@ -409,7 +409,13 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
                 if (lane == 0) mbar_arrive(&rowFull[stage ^ 1]);
             }
         }
-        // ---- dV (first four warps) and dK (the others) of this CTA's keys
+        // ---- dV (first four warps) and dK (the others) of this CTA's keys; keys that no query row sees get zeros
+        if (steps == 0 && keyValid) {
+            float* dst = (half == 0 ? p.dV : p.dK) +
+                         (static_cast<size_t>(b) * p.totalLen + keyPos) * (half == 0 ? p.ldDv : p.ldDk) + static_cast<size_t>(h) * kD;
+#pragma unroll 4
+            for (int i = 0; i < kD; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
         if (alive && steps > 0 && warp_all(mbar_wait(accFull, 0, abortFlag, status, kDevTimeoutAccFull))) {
             tc_fence_after();
             const uint32_t tAcc = tmemBase + laneBase + (half == 0 ? 256u : 384u);
@@ -559,15 +565,17 @@ void attentionBackward(const AttentionBackwardArgs& a, cudaStream_t stream) {
     require(a.dtype == BFB_F32 || a.dtype == BFB_BF16, "attention_bwd: q, k, v, out and d_out are f32 or bf16");
     const int64_t rows = a.batch * a.numHeads * a.newLen;
     const size_t kvElems = static_cast<size_t>(a.batch) * a.totalLen;
-    // dK and dV start from zero (rows no query sees keep it); dQ too on the tensor-core path, which accumulates into it
-    if (kvElems > 0) {
+    const bool tensorCores = rows > 0 && attentionBackwardUsesTensorCores(a);
+    // The CUDA-core kernel accumulates dK and dV with atomics: they start from zero. The tensor-core kernel writes every
+    // element of both itself (a CTA owns its keys) and accumulates dQ, which then starts from zero.
+    if (kvElems > 0 && !tensorCores) {
         BFB_CUDA(cudaMemset2DAsync(a.dK, static_cast<size_t>(a.ldDk) * 4, 0, static_cast<size_t>(a.numHeads * a.headDim) * 4, kvElems, stream));
         BFB_CUDA(cudaMemset2DAsync(a.dV, static_cast<size_t>(a.ldDv) * 4, 0, static_cast<size_t>(a.numHeads * a.headDim) * 4, kvElems, stream));
     }
     if (rows == 0) return;
     const int threads = 256;
     // the tensor-core kernel wants D already multiplied by the score scale
-    const float dScale = attentionBackwardUsesTensorCores(a) ? a.scale : 1.0f;
+    const float dScale = tensorCores ? a.scale : 1.0f;
     const unsigned prepBlocks = static_cast<unsigned>((rows * 32 + threads - 1) / threads);
     if (a.dtype == BFB_F32) {
         attentionBackwardPrepKernel<float><<<prepBlocks, threads, 0, stream>>>(
@@ -580,7 +588,7 @@ void attentionBackward(const AttentionBackwardArgs& a, cudaStream_t stream) {
     }
     BFB_LAUNCH_CHECK();
     noteLaunch();
-    if (attentionBackwardUsesTensorCores(a)) {
+    if (tensorCores) {
         BFB_CUDA(cudaMemset2DAsync(a.dQ, static_cast<size_t>(a.ldDq) * 4, 0, static_cast<size_t>(a.numHeads * a.headDim) * 4,
                                    static_cast<size_t>(a.batch) * a.newLen, stream));
         const int64_t dim = a.numHeads * a.headDim;
