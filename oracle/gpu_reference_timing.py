@@ -5,6 +5,7 @@ beside this repository's forward on the same GPU, the same model and the same to
     python -m oracle.gpu_reference_timing [--batch 4] [--seq 2048] [--layers 16]
     python -m oracle.gpu_reference_timing --decode [--batch 32] [--context 1920] [--steps 4]
     python -m oracle.gpu_reference_timing --gemm [--rows 65536] [--seconds 1.0]
+    python -m oracle.gpu_reference_timing --attention-bwd [--batch 1] [--heads 2] [--seq 2048]
 
 The first form also reports how far the two sets of logits are apart (largest difference over the largest logit, raw
 top-1 agreement, agreement on the positions the reference decides by more than 2e-2 of the largest logit). `--gemm`
@@ -14,7 +15,9 @@ back-to-back launches (so both run at the clocks the power cap allows), alternat
 
 The reference keeps the activations of every layer for its backward pass and an fp32 gradient beside every weight, so
 it holds a slice of the headline batch (4 of the 32 sequences by default), not all of it. Both sides use their seeded
-default initialisation (the same values). Prints one JSON line."""
+default initialisation (the same values). `--attention-bwd` times the reference's fusedAttentionBackward (fp32, CUDA
+cores) beside this repository's tensor-core backward on the same bf16-valued operands and reports how far the gradients
+are apart. Prints one JSON line."""
 from __future__ import annotations
 
 import argparse
@@ -39,7 +42,11 @@ def main():
     ap.add_argument("--gemm", action="store_true", help="cublasLtMatmul as the reference calls it against the tcgen05 GEMM")
     ap.add_argument("--rows", type=int, default=65536, help="--gemm: rows of A (tokens of a step)")
     ap.add_argument("--seconds", type=float, default=1.0, help="--gemm: length of each timed run")
+    ap.add_argument("--attention-bwd", action="store_true", help="the reference's fusedAttentionBackward against the tcgen05 backward")
+    ap.add_argument("--heads", type=int, default=2, help="--attention-bwd: heads of 128")
     args = ap.parse_args()
+    if args.attention_bwd:
+        return attention_backward(args)
     if args.decode:
         return decode(args)
     if args.gemm:
@@ -86,6 +93,52 @@ def main():
                       "reference_cuda_ms": ref_ms, "reference_cuda_tokens_per_s": tokens / (ref_ms / 1e3),
                       "this_ms": our_ms, "this_tokens_per_s": tokens / (our_ms / 1e3), "ratio": ref_ms / our_ms,
                       "logits_vs_reference": diff}))
+
+
+def attention_backward(args):
+    import blackforge_b200 as bfb
+    from oracle import bf_oracle as O
+    from oracle import ref_lib
+
+    batch = args.batch if args.batch != 4 else 1
+    heads, seq, hd = args.heads, args.seq, 128
+    dim = heads * hd
+    rng = np.random.default_rng(5)
+    q, k, v, g = (O.round_bf16(rng.standard_normal((batch, seq, dim)).astype(np.float32)) for _ in range(4))
+    scale = float(hd ** -0.5)
+    ref = ref_lib.cuda_fused_attention_backward(g, q, k, v, heads, scale, 0, iters=args.iters)
+    lib = bfb.lib()
+    dev = {n: bfb.upload(t, bfb.BF16) for n, t in (("g", g), ("q", q), ("k", k), ("v", v), ("o", O.round_bf16(ref["out"])))}
+    d_m, d_l = bfb.upload(ref["m"], bfb.F32), bfb.upload(ref["l"], bfb.F32)
+    grads = [bfb.DeviceBuffer(q.size * 4) for _ in range(3)]
+    scratch = bfb.DeviceBuffer(batch * heads * seq * 8)
+    status = bfb.DeviceBuffer.zeros(4)
+
+    def run():
+        bfb.check(lib.bfb_attention_bwd(dev["g"].ptr, dev["q"].ptr, dev["k"].ptr, dev["v"].ptr, dev["o"].ptr, d_m.ptr, d_l.ptr,
+                                        grads[0].ptr, grads[1].ptr, grads[2].ptr, scratch.ptr, bfb.BF16, batch, seq, seq,
+                                        heads, hd, dim, dim, dim, dim, scale, 0, 1, status.ptr, None))
+    import torch
+    for _ in range(2):
+        run()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(args.iters):
+        run()
+    e.record()
+    torch.cuda.synchronize()
+    ours_ms = s.elapsed_time(e) / args.iters
+    flops = 10.0 * hd * batch * heads * seq * (seq + 1) / 2.0
+    diffs = {}
+    for name, buf in zip(("dq", "dk", "dv"), grads):
+        got = bfb.download(buf, bfb.F32, q.shape)
+        diffs[name] = float(np.max(np.abs(got - ref[name])) / np.max(np.abs(ref[name])))
+    print(json.dumps({"what": "attention backward, causal, bf16-valued operands", "batch": batch, "heads": heads, "seq": seq,
+                      "reference_ms": ref["ms"], "reference_tflops": flops / (ref["ms"] * 1e-3) / 1e12, "ours_ms": ours_ms,
+                      "ours_tflops": flops / (ours_ms * 1e-3) / 1e12, "speedup": ref["ms"] / ours_ms,
+                      "max_abs_diff_over_max_abs": diffs, "device_status": int(status.to_numpy(np.int32, (1,))[0])}))
+    return 0
 
 
 def gemm_ab(args):
