@@ -83,7 +83,7 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
     uint64_t* kvFull = bars;          // [1]
     uint64_t* qFull = bars + 1;       // [2]
     uint64_t* dqStaged = bars + 3;    // [2] the step's dQ tile is in the slot its Q and dO came from (8 warps)
-    uint64_t* sFull = bars + 5;       // S^T and dP^T complete
+    uint64_t* sFull = bars + 5;       // S^T complete
     uint64_t* pFull = bars + 6;       // P^T written (4 warps)
     uint64_t* dsFull = bars + 7;      // dS^T written (4 warps)
     uint64_t* dqFull = bars + 8;      // dQ^T complete (and everything issued before it)
@@ -91,7 +91,8 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
     uint64_t* accFull = bars + 10;    // dV and dK complete
     uint64_t* rowFull = bars + 11;    // [2] row statistics of a step written (8 warps)
     uint64_t* slotFree = bars + 13;   // every product that reads the step's Q and dO tiles is complete
-    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 14);
+    uint64_t* dpFull = bars + 14;     // dP^T complete
+    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 15);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
     if ((smem_u32(smem) & 1023u) != 0u) {
@@ -124,6 +125,7 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
         mbar_init(dqFree, kSoftmaxWarps);
         mbar_init(accFull, 1);
         mbar_init(slotFree, 1);
+        mbar_init(dpFull, 1);
         mbar_init(&rowFull[0], kSoftmaxWarps);
         mbar_init(&rowFull[1], kSoftmaxWarps);
         *abortFlag = 0;
@@ -186,7 +188,12 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
             const uint32_t vLo = smem_desc_lo(smem_u32(smem + kVOff), 0);
             const uint32_t dsLoMn = smem_desc_lo(smem_u32(smem + kDsOff), kHalfBytes);
             const uint32_t kLoMn = smem_desc_lo(smem_u32(smem + kKOff), kHalfBytes);
-            const uint32_t tS = tmemBase, tDp = tmemBase + 128u, tDv = tmemBase + 256u, tDk = tmemBase + 384u;
+            // The two 128-column regions swap roles every step: S^T of step it + 1 goes where dP^T / dS^T of step it was
+            // (free as soon as dK of step it is issued: the pipe runs in order), dP^T of step it + 1 where S^T / P^T / dQ
+            // of step it was (free when the gradient warps have read dQ). So the next S^T never waits for them.
+            const uint32_t tDv = tmemBase + 256u, tDk = tmemBase + 384u;
+            auto regionS = [&](int it) { return tmemBase + static_cast<uint32_t>((it & 1) * 128); };
+            auto regionDp = [&](int it) { return tmemBase + static_cast<uint32_t>(((it & 1) ^ 1) * 128); };
             bool alive = mbar_wait(kvFull, 0, abortFlag, status, kDevTimeoutTmaFull);
             auto ringLo = [&](int it) { return smem_desc_lo(smem_u32(smem + kRingOff + (it & 1) * 2 * kTileBytes), 0); };
             auto issueDp = [&](int it) {                    // dP^T = V dO^T (reduction over head_dim)
@@ -194,7 +201,7 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; ++kk) {
                     const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
-                    umma_f16_words(tDp, vLo + off, kHi, doLo + off, kHi, kIdescKK, kk > 0 ? 1u : 0u);
+                    umma_f16_words(regionDp(it), vLo + off, kHi, doLo + off, kHi, kIdescKK, kk > 0 ? 1u : 0u);
                 }
             };
             auto issueS = [&](int it) {                     // S^T = K Q^T
@@ -202,7 +209,7 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; ++kk) {
                     const uint32_t off = ((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4;
-                    umma_f16_words(tS, kLo + off, kHi, qLo + off, kHi, kIdescKK, kk > 0 ? 1u : 0u);
+                    umma_f16_words(regionS(it), kLo + off, kHi, qLo + off, kHi, kIdescKK, kk > 0 ? 1u : 0u);
                 }
             };
             // the bf16 operand a pair of warps leaves in tensor memory: query rows 0..63 over the first half of the
@@ -211,8 +218,9 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
             if (alive && mbar_wait(&qFull[0], 0, abortFlag, status, kDevTimeoutTmaFull)) {
                 tc_fence_after();
                 issueS(0);
-                issueDp(0);
                 umma_commit(sFull);
+                issueDp(0);
+                umma_commit(dpFull);
             } else {
                 alive = false;
             }
@@ -221,6 +229,7 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
                 const uint32_t par = static_cast<uint32_t>(it) & 1u;
                 const uint32_t qLoMn = ringLo(it) + ((kHalfBytes >> 4) << 16);
                 const uint32_t doLoMn = qLoMn + (kTileBytes >> 4);
+                const uint32_t tS = regionS(it), tDp = regionDp(it);
                 if (!mbar_wait(pFull, par, abortFlag, status, kDevTimeoutSoftmax)) { alive = false; break; }
                 tc_fence_after();
 #pragma unroll
@@ -240,15 +249,14 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
                 }
                 umma_commit(slotFree);   // dV and dK have read this step's dO and Q: their slot may take the dQ tile
                 if (it + 1 < steps) {
-                    // the next step's dP^T can follow at once (the pipe runs in order, dK has read dS^T by then); its
-                    // S^T shares columns with dQ^T and waits until the gradient warps have read that
                     if (!mbar_wait(&qFull[stage ^ 1], ((it + 1) >> 1) & 1, abortFlag, status, kDevTimeoutTmaFull)) { alive = false; break; }
-                    tc_fence_after();
-                    issueDp(it + 1);
-                    if (!mbar_wait(dqFree, par, abortFlag, status, kDevTimeoutAccEmpty)) { alive = false; break; }
                     tc_fence_after();
                     issueS(it + 1);
                     umma_commit(sFull);
+                    if (!mbar_wait(dqFree, par, abortFlag, status, kDevTimeoutAccEmpty)) { alive = false; break; }
+                    tc_fence_after();
+                    issueDp(it + 1);
+                    umma_commit(dpFull);
                 }
             }
             if (alive) umma_commit(accFull);
@@ -261,7 +269,7 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
         const int keyPos = k0 + keyRow;
         const bool keyValid = keyPos < p.totalLen;
         const uint32_t laneBase = static_cast<uint32_t>(quad * 32) << 16;
-        const uint32_t tS = tmemBase + laneBase + static_cast<uint32_t>(half * 64), tDp = tS + 128u;
+        const uint32_t tHalf = tmemBase + laneBase + static_cast<uint32_t>(half * 64);   // + 128 for the other region
         uint8_t* dsRow = smem + kDsOff + half * kHalfBytes + keyRow * 128;
         const bool raggedKeys = k0 + kBlk > p.totalLen;
         bool alive = true;
@@ -280,6 +288,7 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
         for (int it = 0; it < steps && alive; ++it) {
             const uint32_t par = static_cast<uint32_t>(it) & 1u;
             const int q0 = (firstQ + it) * kBlk;
+            const uint32_t tS = tHalf + par * 128u, tDp = tHalf + (par ^ 1u) * 128u;   // the regions swap roles every step
             // statistics of the step's 128 query rows (lse2 from the first four warps, D from the others; a row past the
             // end gets +inf, which makes its probabilities zero): this step's are in shared memory already, the next
             // step's are fetched now and stored at the end of the step, so that no step waits for global memory
@@ -333,6 +342,11 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(pFull);
+            if (!warp_all(mbar_wait(dpFull, par, abortFlag, status, kDevTimeoutAccFull))) {
+                alive = false;
+                break;
+            }
+            tc_fence_after();
             // ---- dS^T = P^T o (scale dP^T - scale D[c]) (the statistics kernel stores D already scaled); written over
             // dP^T as the tensor-memory operand of dK, and to shared memory as the operand of dQ^T
 #pragma unroll
