@@ -256,7 +256,10 @@ bfb_status bfb_matmul_transpose_b(const float* d_a, const float* d_b, float* d_c
 
 /* Gradients of C = A B with bf16 operands (matmulBf16Backward, src/backend/cuda/ops_tensorcore.cu:389-417):
  * d_da[M,K] = grad[M,N] * b^T and d_db[K,N] = a^T * grad from fp32 a [M,K], b [K,N], grad [M,N]; operands are
- * rounded to bf16, accumulation and results are fp32. A zero dimension zero-fills both results, as there. */
+ * rounded to bf16, accumulation and results are fp32. A zero dimension zero-fills both results, as there.
+ * The bf16 copies live in pool buffers that go back to the pool when the call returns, while the kernels may
+ * still be running on `stream`: as with the reference's pool (which knows no streams either), a buffer handed
+ * out again is safe for work queued on the SAME stream; a caller that uses several streams synchronises first. */
 bfb_status bfb_matmul_bf16_backward(const float* d_a, const float* d_b, const float* d_grad, float* d_da, float* d_db,
                                     int64_t m, int64_t k, int64_t n, void* stream);
 
