@@ -80,6 +80,7 @@ SIGNATURES = {
     "bfb_amax": (_I32, [_P, _I32, _I64, _P, _P]),
     "bfb_fp8_scale_from_amax": (_I32, [_P, _P, _P]),
     "bfb_rmsnorm_quantize_e4m3": (_I32, [_P, _I64, _I64, _F, _P, _P, _P, _P]),
+    "bfb_rmsnorm_quantize_e4m3_from_stats": (_I32, [_P, _I64, _I64, _F, _P, _P, _P, _P, _P, _I32, _P]),
     "bfb_quantize_e4m3": (_I32, [_P, _I32, _I64, _P, _P, _P, _P]),
     "bfb_quantize_e4m3_static": (_I32, [_P, _I32, _I64, _P, _P, _P, _P]),
     "bfb_weight_prepare": (_I32, [_P, _P, _I32, _I64, _I64, _F, _P, _P]),
@@ -91,6 +92,8 @@ SIGNATURES = {
     "bfb_matmul_bf16_backward": (_I32, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _P]),
     "bfb_attention_fwd": (_I32, [_P, _P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64,
                                  _F, _I64, _I32, _P, _P]),
+    "bfb_attention_fwd_maxima": (_I32, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _F, _I64,
+                                        _P, _P]),
     "bfb_attention_bwd": (_I32, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _I64, _I64, _I64,
                                  _I64, _I64, _I64, _F, _I64, _I32, _P, _P]),
     "bfb_model_create": (_I32, [C.POINTER(OpDesc), _I32, _I64, C.c_uint32, C.POINTER(Precision), C.POINTER(_P)]),

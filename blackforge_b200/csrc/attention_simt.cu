@@ -109,6 +109,10 @@ void attentionForward(const AttentionArgs& a, cudaStream_t stream) {
     const int64_t kvRows = a.kvBatchRows > 0 ? a.kvBatchRows : a.totalLen;
     require(a.q != nullptr && a.k != nullptr && a.v != nullptr && a.out != nullptr, "attention: null pointer");
 
+    const bool tensorCores = !attentionDecodeEligible(a) && attentionUsesTensorCores(a);
+    if (a.outMaxima != nullptr && !tensorCores) {
+        fail(BFB_UNSUPPORTED, "attention: output maxima come from the tensor-core kernel only (bf16, head_dim 128, more than one query)");
+    }
     if (attentionDecodeEligible(a)) {   // one query per sequence: stream K and V, nothing for a 128-row MMA to do
         attentionDecode(a, stream);
         return;

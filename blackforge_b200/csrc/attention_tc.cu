@@ -92,6 +92,7 @@ struct AttnParams {
     int totalItems;
     const int* schedule;   // [rounds][grid]: the item CTA c takes in round k, or -1
     int rounds;
+    float* outMaxima;      // [batch][heads][ceil(newLen / 128)][4]: largest stored magnitude per 32 output rows, or null
 };
 
 struct Item {
@@ -495,6 +496,7 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
             tc_fence_after();
             const float inv = lRun > 0.0f ? 1.0f / lRun : 0.0f;
             const bool store = row < p.newLen;
+            float rowMax = 0.0f;   // largest |o| of this thread's row (an e4m3 quantisation of the output wants the maximum)
             uint8_t* stage = smem + kStageOff + (warp - kFirstSoftmaxWarp) * kStageBytes;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -516,9 +518,10 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const int e = (g & 3) * 8 + 2 * i;
-                        __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(o[g >> 2][e]) * inv,
-                                                                  __uint_as_float(o[g >> 2][e + 1]) * inv);
+                        const float v0 = __uint_as_float(o[g >> 2][e]) * inv, v1 = __uint_as_float(o[g >> 2][e + 1]) * inv;
+                        __nv_bfloat162 hh = __floats2bfloat162_rn(v0, v1);
                         wd[i] = *reinterpret_cast<uint32_t*>(&hh);
+                        if (p.outMaxima != nullptr) rowMax = fmaxf(rowMax, fmaxf(fabsf(v0), fabsf(v1)));
                     }
                     *reinterpret_cast<uint4*>(stage + lane * 128 + ((g ^ (lane & 7)) << 4)) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
                 }
@@ -528,6 +531,15 @@ attentionTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_consta
                     tma_store_3d(&tmapO, stage, w.h * kD + h * 64, w.q0 + side * kBM + (warp & 3) * 32, w.b);
                     tma_store_commit();
                 }
+            }
+            if (p.outMaxima != nullptr) {
+                // rounding to bf16 is monotonic: the largest stored magnitude is the rounded largest value
+                float v = store ? __bfloat162float(__float2bfloat16_rn(rowMax)) : 0.0f;
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
+                const int rowBlocks = (p.newLen + kBM - 1) / kBM;
+                const int64_t slot = ((static_cast<int64_t>(w.b) * p.numHeads + w.h) * rowBlocks + (w.q0 / kBM + side)) * 4 + (warp & 3);
+                if (lane == 0 && w.q0 + side * kBM < p.newLen) p.outMaxima[slot] = v;
             }
             if (store) {
                 const int64_t statIdx = (static_cast<int64_t>(w.b) * p.numHeads + w.h) * p.newLen + row;
@@ -668,6 +680,10 @@ bool attentionUsesTensorCores(const AttentionArgs& a) {
     return true;
 }
 
+int64_t attentionMaximaCount(const AttentionArgs& a) {
+    return a.batch * a.numHeads * ((a.newLen + kBM - 1) / kBM) * 4;
+}
+
 void attentionTensorCore(const AttentionArgs& a, cudaStream_t stream) {
     const int64_t dim = a.numHeads * a.headDim;
     TensorMapStorage tq, tk, tv, to;
@@ -680,6 +696,7 @@ void attentionTensorCore(const AttentionArgs& a, cudaStream_t stream) {
     p.out = static_cast<__nv_bfloat16*>(a.out);
     p.mOut = a.m;
     p.lOut = a.l;
+    p.outMaxima = a.outMaxima;
     p.batch = static_cast<int>(a.batch);
     p.newLen = static_cast<int>(a.newLen);
     p.totalLen = static_cast<int>(a.totalLen);

@@ -221,6 +221,27 @@ bfb_status bfb_rmsnorm_quantize_e4m3(const void* d_x, int64_t rows, int64_t dim,
     });
 }
 
+bfb_status bfb_rmsnorm_quantize_e4m3_from_stats(const void* d_x, int64_t rows, int64_t dim, float eps, void* d_out,
+                                                float* d_scales, const float* d_weight_inverse, const float* d_sum_sq_parts,
+                                                const float* d_max_parts, int32_t parts, void* stream) {
+    return guarded([&] {
+        require(rows >= 0, "rmsnorm_quantize_e4m3_from_stats: negative size");
+        require(parts >= 1 && d_sum_sq_parts != nullptr && d_max_parts != nullptr,
+                "rmsnorm_quantize_e4m3_from_stats: the row statistics are missing");
+        requireDevice();
+        const size_t bytes = static_cast<size_t>(bfb::rmsnormQuantizeScratchFloats(rows)) * sizeof(float);
+        float* scratch = static_cast<float*>(bfb::poolAcquire(bytes));
+        try {
+            bfb::rmsnormQuantizeE4m3(d_x, rows, dim, eps, d_out, d_scales, d_weight_inverse, scratch, asStream(stream),
+                                     d_sum_sq_parts, d_max_parts, parts);
+        } catch (...) {
+            bfb::poolRelease(scratch, bytes);
+            throw;
+        }
+        bfb::poolRelease(scratch, bytes);
+    });
+}
+
 bfb_status bfb_weight_prepare(const float* d_w, void* d_out, int32_t out_dtype, int64_t k, int64_t n, float scale,
                               const float* d_scale, void* stream) {
     return guarded([&] { bfb::weightPrepare(d_w, d_out, out_dtype, k, n, scale, d_scale, asStream(stream)); });
@@ -352,6 +373,37 @@ bfb_status bfb_attention_fwd(const void* d_q, const void* d_k, const void* d_v, 
         a.oldLen = old_len;
         a.causal = causal;
         a.dStatus = d_status;
+        bfb::attentionForward(a, asStream(stream));
+    });
+}
+
+bfb_status bfb_attention_fwd_maxima(const void* d_q, const void* d_k, const void* d_v, void* d_out, float* d_maxima,
+                                    int64_t maxima_count, int64_t batch, int64_t new_len, int64_t total_len, int64_t num_heads,
+                                    int64_t ld_q, int64_t ld_k, int64_t ld_v, int64_t ld_o, float scale, int64_t old_len,
+                                    int32_t* d_status, void* stream) {
+    return guarded([&] {
+        bfb::AttentionArgs a;
+        a.q = d_q;
+        a.k = d_k;
+        a.v = d_v;
+        a.out = d_out;
+        a.dtype = BFB_BF16;
+        a.batch = batch;
+        a.newLen = new_len;
+        a.totalLen = total_len;
+        a.numHeads = num_heads;
+        a.headDim = 128;
+        a.ldQ = ld_q;
+        a.ldK = ld_k;
+        a.ldV = ld_v;
+        a.ldO = ld_o;
+        a.scale = scale;
+        a.oldLen = old_len;
+        a.causal = 1;
+        a.dStatus = d_status;
+        a.outMaxima = d_maxima;
+        require(d_maxima != nullptr, "attention_fwd_maxima: null maxima pointer");
+        require(maxima_count == bfb::attentionMaximaCount(a), "attention_fwd_maxima: maxima_count must be batch * heads * ceil(new_len / 128) * 4");
         bfb::attentionForward(a, asStream(stream));
     });
 }

@@ -599,6 +599,11 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
         fp8Stats.ensure(static_cast<std::size_t>(fp8SlotLimit) * 4 * sizeof(float));
         BFB_CUDA(cudaMemsetAsync(fp8Stats.ptr, 0, fp8Stats.bytes, stream));
     }
+    // Row statistics of the current x from the epilogue of the GEMM that wrote it: sums of squares (`ss`) and, on the
+    // e4m3 route, largest magnitudes (`mx`), as [parts][tokens]; ssParts == 0 means they do not describe the current x.
+    float* ss = nullptr;
+    float* mx = nullptr;
+    int ssParts = 0;
     auto nextFp8Stats = [&]() -> float* {
         require(fp8Slot < fp8SlotLimit, "Model: more quantised GEMM inputs than scale slots");
         return static_cast<float*>(fp8Stats.ptr) + 4 * (fp8Slot++);
@@ -629,8 +634,11 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
         float* scratch = static_cast<float*>(
             buf("norm_quant", static_cast<std::size_t>(bfb::rmsnormQuantizeScratchFloats(static_cast<int64_t>(tokens))) *
                                   sizeof(float)));
+        // with the producer's row statistics the first pass (1 / rms per row, the tensor's maximum) reads those
+        // instead of x
+        const bool fromStats = ssParts > 0 && mx != nullptr;
         bfb::rmsnormQuantizeE4m3(x, static_cast<int64_t>(tokens), static_cast<int64_t>(d), 1e-6f, a8, st, wScales + 1,
-                                 scratch, stream);
+                                 scratch, stream, fromStats ? ss : nullptr, fromStats ? mx : nullptr, fromStats ? ssParts : 0);
         *dAlpha = st + 2;
         return a8;
     };
@@ -688,8 +696,6 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
     // Sums of squares of the rows of x as [parts][tokens]: one part from the read-only pass, one per 128 columns
     // from the epilogue of the GEMM that wrote x. One buffer is enough: by the time a GEMM writes the sums of the
     // next x, the GEMM that read the previous ones has finished (same stream).
-    float* ss = nullptr;
-    int ssParts = 0;         // 0: ss does not describe the current x
     auto sumSqBuffer = [&](std::size_t tokens, std::size_t d) {
         return static_cast<float*>(buf("row_sumsq", ((d + 127) / 128) * tokens * sizeof(float)));
     };
@@ -706,9 +712,29 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
         if (tpWorld > 1) return nullptr;   // x is completed by an all-reduce: the epilogue only sees a partial sum
         return sumSqBuffer(tokens, d);
     };
-    auto producedSumSq = [&](float* produced, std::size_t d) {
+    auto producedSumSq = [&](float* produced, std::size_t d, float* producedMax = nullptr) {
         ss = produced;
+        mx = produced != nullptr ? producedMax : nullptr;
         ssParts = produced != nullptr ? static_cast<int>((d + 127) / 128) : 0;
+    };
+    // e4m3 route: can the GEMM that writes the next x (tokens x d from a reduction over k) leave the row statistics
+    // the next norm + quantisation needs?
+    auto fp8StatsOk = [&](const void* a, std::size_t tokens, std::size_t d, std::size_t k, const void* wt) {
+        if (!fp8 || S != BFB_BF16 || incremental || tpWorld > 1) return false;
+        bfb::GemmArgs probe;
+        probe.a = a;
+        probe.b = wt;
+        probe.c = x;
+        probe.m = static_cast<int64_t>(tokens);
+        probe.n = static_cast<int64_t>(d);
+        probe.k = static_cast<int64_t>(k);
+        probe.abDtype = ab;
+        probe.bLayout = BFB_B_NK;
+        probe.cDtype = BFB_BF16;
+        return bfb::gemmSupportsRowStats(probe);
+    };
+    auto maxBuffer = [&](std::size_t tokens, std::size_t d) {
+        return static_cast<float*>(buf("row_max", ((d + 127) / 128) * tokens * sizeof(float)));
     };
 
     DeviceTensor result;
@@ -866,13 +892,37 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                 a.oldLen = static_cast<int64_t>(oldLen);
                 a.causal = 1;
                 a.dStatus = dStatus;
+                // e4m3 route: the attention epilogue also reports the largest magnitudes of what it stores, so the
+                // quantisation of its output needs no pass of its own to find the scale
+                int64_t ctxMaximaCount = 0;
+                if (fp8 && !incremental && bfb::attentionUsesTensorCores(a)) {
+                    ctxMaximaCount = bfb::attentionMaximaCount(a);
+                    a.outMaxima = static_cast<float*>(buf("ctx_maxima", static_cast<std::size_t>(ctxMaximaCount) * sizeof(float)));
+                }
                 bfb::attentionForward(a, stream);
-                const void* aOut = gemmInput(ctx, tokens * dl, "act8_dl", sc + 2, &dAlpha);
+                const void* aOut = nullptr;
+                if (a.outMaxima != nullptr) {
+                    float* st = nextFp8Stats();
+                    void* a8 = buf("act8_dl", tokens * dl);
+                    float* scratch = static_cast<float*>(
+                        buf("partial_ctx_maxima", static_cast<std::size_t>(bfb::quantizeScratchFloats(ctxMaximaCount)) * sizeof(float)));
+                    bfb::quantizeE4m3FromMaxima(ctx, BFB_BF16, static_cast<int64_t>(tokens * dl), a8, st, sc + 3, a.outMaxima,
+                                                ctxMaximaCount, scratch, stream);
+                    dAlpha = st + 2;
+                    aOut = a8;
+                } else {
+                    aOut = gemmInput(ctx, tokens * dl, "act8_dl", sc + 2, &dAlpha);
+                }
                 // x = x + ctx * Wout (in place); under tensor parallelism rank 0 carries the residual
                 const int epi = (tpWorld == 1 || tpRank == 0) ? BFB_EPI_RESIDUAL : BFB_EPI_NONE;
                 float* produced = fuse && fusedNormOk(tokens, d, dl, l.w1.ptr) ? nextSumSq(tokens, d) : nullptr;
-                runGemm(aOut, l.w1.ptr, x, tokens, d, dl, S, epi, nullptr, x, dAlpha, 0, nullptr, 1, produced);
-                producedSumSq(produced, d);
+                float* producedMax = nullptr;
+                if (fp8StatsOk(aOut, tokens, d, dl, l.w1.ptr)) {
+                    produced = nextSumSq(tokens, d);
+                    producedMax = maxBuffer(tokens, d);
+                }
+                runGemm(aOut, l.w1.ptr, x, tokens, d, dl, S, epi, nullptr, x, dAlpha, 0, nullptr, 1, produced, producedMax);
+                producedSumSq(produced, d, producedMax);
                 reduceGroup(g, x, tokens * d);
                 }
                 x = xAll;
@@ -939,9 +989,15 @@ DeviceTensor Model::Impl::forwardPlanned(const DeviceTensor& input, bool trusted
                 }
                 const bool lead = tpWorld == 1 || tpRank == 0;
                 float* produced = fuse && fusedNormOk(tokens, d, fl, l.w1.ptr) ? nextSumSq(tokens, d) : nullptr;
+                float* producedMax = nullptr;
+                if (fp8StatsOk(a2, tokens, d, fl, l.w1.ptr)) {
+                    produced = nextSumSq(tokens, d);
+                    producedMax = maxBuffer(tokens, d);
+                }
                 runGemm(a2, l.w1.ptr, x, tokens, d, fl, S, lead ? BFB_EPI_BIAS_RESIDUAL : BFB_EPI_NONE,
-                        lead ? params[l.p[3]].value.data() : nullptr, lead ? x : nullptr, dAlpha, 0, nullptr, 1, produced);
-                producedSumSq(produced, d);
+                        lead ? params[l.p[3]].value.data() : nullptr, lead ? x : nullptr, dAlpha, 0, nullptr, 1, produced,
+                        producedMax);
+                producedSumSq(produced, d, producedMax);
                 reduceGroup(g, x, tokens * d);
                 }
                 x = xAll;

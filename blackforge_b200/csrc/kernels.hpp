@@ -46,8 +46,12 @@ void quantizeE4m3(const void* in, int inDtype, int64_t n, void* out, float* dSca
 void quantizeE4m3FromMaxima(const void* in, int inDtype, int64_t n, void* out, float* dScales, const float* dWeightInverse,
                             const float* maxima, int64_t count, float* scratch, cudaStream_t stream);
 int64_t rmsnormQuantizeScratchFloats(int64_t rows);
+// `sumSqParts` / `maxParts` ([parts][rows], may be null): sums of squares and largest magnitudes of x per row and part,
+// as the epilogue of the GEMM that wrote x leaves them (GemmArgs::outSumSq, outMaxAbs); with them the first pass reads
+// those figures instead of x.
 void rmsnormQuantizeE4m3(const void* x, int64_t rows, int64_t dim, float eps, void* out, float* dScales,
-                         const float* dWeightInverse, float* scratch, cudaStream_t stream);
+                         const float* dWeightInverse, float* scratch, cudaStream_t stream,
+                         const float* sumSqParts = nullptr, const float* maxParts = nullptr, int parts = 0);
 // Seeded N(0, sigma) values for the [rows, colsLocal] block at (rowOffset, colOffset) of a tensor with colsFull
 // columns; a value depends only on the seed and its position in the full tensor.
 void fillNormal(float* out, int64_t rows, int64_t colsLocal, int64_t colsFull, int64_t rowOffset, int64_t colOffset,
@@ -120,7 +124,12 @@ struct AttentionArgs {
     int64_t oldLen = 0;
     int causal = 1;
     int* dStatus = nullptr;
+    // Tensor-core kernel only (attentionUsesTensorCores): the largest magnitude of the stored output per 32 rows of a
+    // (batch, head), attentionMaximaCount(args) floats, every one written: what a per-tensor e4m3 quantisation of the
+    // output needs, without another pass over it. Null: not wanted.
+    float* outMaxima = nullptr;
 };
+int64_t attentionMaximaCount(const AttentionArgs& args);
 // One query per sequence and head against cached keys and values (a generation step): a bandwidth-oriented CUDA-core
 // kernel, see attention_decode.cu.
 bool attentionDecodeEligible(const AttentionArgs& args);

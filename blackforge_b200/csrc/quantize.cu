@@ -189,6 +189,40 @@ __global__ void normQuantizeScalarKernel(const __nv_bfloat16* __restrict__ x, __
     }
 }
 
+// Pass 1 without reading x: the GEMM that wrote x left, per row and 128-column part, the sum of squares and the largest
+// magnitude of the values it stored. One thread per row adds and maximises the parts (in index order, so the same
+// bits on every run): r = 1 / sqrt(mean(x^2) + eps) to rowInv[row], the block's maximum of bf16(max|x| * r) to
+// partial[block] — the figures normAmaxKernel would have found by reading x.
+__global__ void __launch_bounds__(kNormThreads)
+rowStatsAmaxKernel(const float* __restrict__ sumSqParts, const float* __restrict__ maxParts, int parts, int64_t rows,
+                   int64_t dim, float eps, float* __restrict__ rowInv, float* __restrict__ partial) {
+    __shared__ float warpMax[kNormThreads / 32];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kNormThreads;
+    float best = 0.0f;
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * kNormThreads + threadIdx.x; row < rows; row += stride) {
+        float ss = 0.0f, mx = 0.0f;
+        for (int p = 0; p < parts; ++p) {
+            ss += sumSqParts[static_cast<int64_t>(p) * rows + row];
+            mx = fmaxf(mx, maxParts[static_cast<int64_t>(p) * rows + row]);
+        }
+        const float inv = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps);
+        rowInv[row] = inv;
+        best = fmaxf(best, bf16Rounded(mx * inv));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(0xFFFFFFFFu, best, o));
+    if (lane == 0) warpMax[warp] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = warpMax[0];
+#pragma unroll
+        for (int w = 1; w < kNormThreads / 32; ++w) t = fmaxf(t, warpMax[w]);
+        partial[blockIdx.x] = t;
+    }
+}
+
 int normAmaxBlocks(int64_t rows) {
     return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>((rows + kNormThreads / 32 - 1) / (kNormThreads / 32),
                                                                  static_cast<int64_t>(smCount()) * 8)));
@@ -199,16 +233,24 @@ int normAmaxBlocks(int64_t rows) {
 int64_t rmsnormQuantizeScratchFloats(int64_t rows) { return rows + normAmaxBlocks(rows); }
 
 void rmsnormQuantizeE4m3(const void* x, int64_t rows, int64_t dim, float eps, void* out, float* dScales,
-                         const float* dWeightInverse, float* scratch, cudaStream_t stream) {
+                         const float* dWeightInverse, float* scratch, cudaStream_t stream, const float* sumSqParts,
+                         const float* maxParts, int parts) {
     require(rows >= 0 && dim > 0, "rmsnorm_quantize_e4m3: bad sizes");
     require(dScales != nullptr && scratch != nullptr, "rmsnorm_quantize_e4m3: null scale or scratch pointer");
     if (rows > 0) require(x != nullptr && out != nullptr, "rmsnorm_quantize_e4m3: null pointer");
+    const bool fromStats = sumSqParts != nullptr && maxParts != nullptr && parts > 0;
     float* rowInv = scratch;
     float* partial = scratch + rows;
-    const int blocks = normAmaxBlocks(rows);
+    int blocks = normAmaxBlocks(rows);
     const bool vec = dim % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0;
     const double elems = static_cast<double>(rows) * static_cast<double>(dim);
-    if (rows > 0) {
+    if (rows > 0 && fromStats) {
+        blocks = static_cast<int>(std::min<int64_t>((rows + kNormThreads - 1) / kNormThreads, blocks));
+        ProfileScope prof(kProfRmsnorm, stream, static_cast<double>(rows) * parts * 8.0);
+        rowStatsAmaxKernel<<<blocks, kNormThreads, 0, stream>>>(sumSqParts, maxParts, parts, rows, dim, eps, rowInv, partial);
+        BFB_LAUNCH_CHECK();
+        noteLaunch();
+    } else if (rows > 0) {
         ProfileScope prof(kProfRmsnorm, stream, elems * 2.0);
         normAmaxKernel<<<blocks, kNormThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, dim, eps, rowInv,
                                                             partial, vec ? 1 : 0);

@@ -180,6 +180,13 @@ bfb_status bfb_quantize_e4m3(const void* d_in, int32_t in_dtype, int64_t n, void
  * (one float per row and per block) comes from the device pool for the duration of the call. */
 bfb_status bfb_rmsnorm_quantize_e4m3(const void* d_x, int64_t rows, int64_t dim, float eps, void* d_out, float* d_scales,
                                      const float* d_weight_inverse, void* stream);
+/* The same result when the GEMM that wrote x also left its row statistics (d_out_sum_sq and d_out_max_abs of
+ * bfb_gemm_rmsnorm, both [parts][rows] with parts = ceil(dim / 128)): the first pass (1 / rms per row, the largest
+ * normalised magnitude) reads those figures instead of x, so x is read once. The sums are added in part order, so a
+ * row's 1 / rms may differ in its last bit from the plain call's. No reference counterpart. */
+bfb_status bfb_rmsnorm_quantize_e4m3_from_stats(const void* d_x, int64_t rows, int64_t dim, float eps, void* d_out,
+                                                float* d_scales, const float* d_weight_inverse, const float* d_sum_sq_parts,
+                                                const float* d_max_parts, int32_t parts, void* stream);
 /* Same operation and results as bfb_quantize_e4m3, for callers that must not allocate device memory while
  * they run: a host engine that gave the whole GPU to its own arena at start-up, or a latency-critical
  * serving loop where a trip into the device allocator can stall every stream. This entry point has no
@@ -278,6 +285,16 @@ bfb_status bfb_attention_fwd(const void* d_q, const void* d_k, const void* d_v, 
                              int32_t dtype, int64_t batch, int64_t new_len, int64_t total_len, int64_t num_heads,
                              int64_t head_dim, int64_t ld_q, int64_t ld_k, int64_t ld_v, int64_t ld_o, float scale,
                              int64_t old_len, int32_t causal, int32_t* d_status, void* stream);
+
+/* The causal attention core on bf16 data with head_dim 128 (the tensor-core kernel), which also reports the largest
+ * magnitude of the output it stores per 32 rows of a (batch, head): d_maxima[((b * heads + h) * ceil(new_len / 128)
+ * + row / 128) * 4 + (row % 128) / 32], maxima_count floats, all written. A per-tensor e4m3 quantisation of the
+ * output then needs no pass of its own to find its scale. BFB_UNSUPPORTED where the tensor-core kernel does not
+ * apply (one query row, unaligned strides). No reference counterpart (fp8 is declared only). */
+bfb_status bfb_attention_fwd_maxima(const void* d_q, const void* d_k, const void* d_v, void* d_out, float* d_maxima,
+                                    int64_t maxima_count, int64_t batch, int64_t new_len, int64_t total_len, int64_t num_heads,
+                                    int64_t ld_q, int64_t ld_k, int64_t ld_v, int64_t ld_o, float scale, int64_t old_len,
+                                    int32_t* d_status, void* stream);
 
 /* Backward of the attention core. Replaces cuda::fusedAttentionBackward
  * (src/backend/cuda/fused_attention.cu:343-380; kernels computeDKernel :166-190 and

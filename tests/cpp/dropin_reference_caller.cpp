@@ -325,6 +325,34 @@ int main(int argc, char** argv) {
             }
         std::printf("%-58s max abs diff %.3g (output) %.3g (m, l)\n", "fusedAttentionForward vs direct evaluation", worstO, worstM);
         expect(worstO <= 1e-5F && worstM <= 1e-5F, "fusedAttentionForward");
+
+        // fusedAttentionBackward (fused_attention.hpp:59-76) against central differences of the forward above:
+        // loss = sum(g * output), one element of q, k or v moved by +-0.01 at a time
+        Tensor g = ramp({1, 4, 8}, 0.6f, -0.2f);
+        cuda::FusedAttentionGrad grad = cuda::fusedAttentionBackward(dev(g), dev(q), dev(k), dev(v), fr.output, fr.m, fr.l, 2, 0.5f, 0);
+        Tensor gq = grad.dQ.toHost(), gk = grad.dK.toHost(), gv = grad.dV.toHost();
+        auto loss = [&](const Tensor& qq, const Tensor& kk, const Tensor& vv) {
+            Tensor o = cuda::fusedAttentionForward(dev(qq), dev(kk), dev(vv), 2, 0.5f, 0).output.toHost();
+            double acc = 0.0;
+            for (std::size_t i = 0; i < 32; ++i) acc += static_cast<double>(o.at(i)) * g.at(i);
+            return acc;
+        };
+        float worstG = 0.0f;
+        for (int which = 0; which < 3; ++which) {
+            const Tensor& analytic = which == 0 ? gq : (which == 1 ? gk : gv);
+            for (std::size_t i = 0; i < 32; ++i) {
+                std::vector<float> up = (which == 0 ? q : (which == 1 ? k : v)).data(), down = up;
+                up[i] += 0.01f;
+                down[i] -= 0.01f;
+                Tensor tu({1, 4, 8}, up), td({1, 4, 8}, down);
+                const double numeric = which == 0   ? (loss(tu, k, v) - loss(td, k, v)) / 0.02
+                                       : which == 1 ? (loss(q, tu, v) - loss(q, td, v)) / 0.02
+                                                    : (loss(q, k, tu) - loss(q, k, td)) / 0.02;
+                worstG = std::fmax(worstG, std::fabs(static_cast<float>(numeric) - analytic.at(i)));
+            }
+        }
+        std::printf("%-58s max abs diff %.3g\n", "fusedAttentionBackward vs differences of the forward", worstG);
+        expect(worstG <= 2e-3F, "fusedAttentionBackward");
     }
     std::printf(failures == 0 ? "dropin: all checks passed\n" : "dropin: %d check(s) FAILED\n", failures);
     return failures == 0 ? 0 : 1;

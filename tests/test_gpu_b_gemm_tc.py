@@ -228,6 +228,19 @@ def test_rmsnorm_folded_into_the_gemm(gpu, m, n, k, epilogue, wide):
                                          None, d_one.ptr, 1, 1e-6, None, None, status.ptr, None))
     got2, got3 = gpu.download(d_c2, gpu.BF16, (m, 64)), gpu.download(d_c3, gpu.BF16, (m, 64))
     assert np.max(np.abs(got2 - got3) / (np.abs(got3) + 0.05)) <= 2.0 ** -7
+    # and the e4m3 quantisation of rmsnorm(C): from the epilogue's statistics (C read once) as from two passes over C
+    winv = gpu.DeviceBuffer.from_numpy(np.array([0.5], np.float32))
+    q_plain, s_plain = gpu.DeviceBuffer(m * n), gpu.DeviceBuffer.zeros(12)
+    q_stats, s_stats = gpu.DeviceBuffer(m * n), gpu.DeviceBuffer.zeros(12)
+    gpu.check(gpu.lib().bfb_rmsnorm_quantize_e4m3(d_c.ptr, m, n, 1e-6, q_plain.ptr, s_plain.ptr, winv.ptr, None))
+    gpu.check(gpu.lib().bfb_rmsnorm_quantize_e4m3_from_stats(d_c.ptr, m, n, 1e-6, q_stats.ptr, s_stats.ptr, winv.ptr,
+                                                             d_out_ss.ptr, d_out_mx.ptr, parts, None))
+    sp, st = s_plain.to_numpy(np.float32, (3,)), s_stats.to_numpy(np.float32, (3,))
+    assert np.max(np.abs(sp - st) / sp) <= 2.0 ** -7            # the maximum may sit one bf16 step apart
+    qa, qb = gpu.download(q_plain, gpu.FP8_E4M3, (m, n)), gpu.download(q_stats, gpu.FP8_E4M3, (m, n))
+    if np.array_equal(sp, st):
+        # a last-bit difference in a row's 1 / rms may move single values across a rounding boundary
+        assert np.mean(qa != qb) <= 2e-3 and np.max(np.abs(qa - qb) / (np.abs(qa) + 2.0 ** -6)) <= 0.13
 
 
 def test_row_statistics_need_the_tensor_core_kernel(gpu):

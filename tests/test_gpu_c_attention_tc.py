@@ -108,3 +108,33 @@ def test_one_query_against_a_cache(gpu, B, H, total):
     # bidirectional with one query is the same computation
     out2, _, _ = attention(gpu, q, k, v, H, gpu.BF16, causal=0)
     assert np.array_equal(out, out2)
+
+
+@pytest.mark.parametrize("B,new,old,H", [(2, 256, 0, 2), (1, 200, 72, 3), (1, 1000, 0, 1)])
+def test_output_maxima_for_an_e4m3_quantisation(gpu, B, new, old, H):
+    """The epilogue's per-32-row maxima are exactly the maxima of the bf16 output it stores (ragged last blocks and
+    cached keys included), and the output itself is what the plain call gives."""
+    rng = np.random.default_rng(B + new + old + H)
+    q, k, v = qkv(rng, B, new, old + new, H)
+    dim = H * 128
+    d_q, d_k, d_v = (gpu.upload(t, gpu.BF16) for t in (q, k, v))
+    out = gpu.DeviceBuffer(q.size * 2)
+    blocks = (new + 127) // 128
+    count = B * H * blocks * 4
+    maxima = gpu.upload(np.full(count, np.nan, np.float32), gpu.F32)
+    status = gpu.DeviceBuffer.zeros(4)
+    gpu.check(gpu.lib().bfb_attention_fwd_maxima(d_q.ptr, d_k.ptr, d_v.ptr, out.ptr, maxima.ptr, count, B, new, old + new, H,
+                                                 dim, dim, dim, dim, float(1 / np.sqrt(128.0)), old, status.ptr, None))
+    gpu.sync()
+    assert int(status.to_numpy(np.int32, (1,))[0]) == 0
+    got = gpu.download(out, gpu.BF16, q.shape)
+    plain, _, _ = attention(gpu, q, k, v, H, gpu.BF16, old_len=old)
+    assert np.array_equal(got, plain)
+    padded = np.zeros((B, blocks * 128, H, 128), np.float32)
+    padded[:, :new] = np.abs(got).reshape(B, new, H, 128)
+    want = padded.reshape(B, blocks, 4, 32, H, 128).max(axis=(3, 5)).transpose(0, 3, 1, 2)      # [B, H, blocks, 4]
+    assert np.array_equal(gpu.download(maxima, gpu.F32, (B, H, blocks, 4)), want)
+    # one query row has no tensor-core route: refused, not silently without maxima
+    code = gpu.lib().bfb_attention_fwd_maxima(d_q.ptr, d_k.ptr, d_v.ptr, out.ptr, maxima.ptr, B * H * 4, B, 1, old + new, H,
+                                              dim, dim, dim, dim, 0.1, old + new - 1, status.ptr, None)
+    assert code == gpu.UNSUPPORTED
