@@ -83,7 +83,7 @@ def test_benchmarked_route_at_full_depth_against_the_reference_cublaslt_path(gpu
     ops_tensorcore.cu:293-327). The rounding of the residual stream grows with depth, so this is the case that
     decides whether the timed route meets the 2e-2 bar; the fp32-stream route is measured beside it. How much bf16
     rounding moves THIS model at all is measured too: the reference's bf16 path against the reference's own fp32
-    path (cublasSgemm). All figures are printed: they are quoted in BASELINE.md."""
+    path (cublasSgemm). All figures are printed."""
     cfg = dict(vocab=32000, dim=2048, layers=16, heads=16, hidden=5632, max_seq=2048)
     batch, seq = 2, 2048
     ops = O.lm_ops(**cfg)
@@ -125,7 +125,7 @@ def test_seeded_default_weights_at_full_depth_are_ill_conditioned_for_everyone(g
     attention scores have a spread of several units, so after 16 layers bf16 rounding anywhere moves the logits by a
     tenth of their range: the reference's own bf16 path is that far from the reference's own fp32 path. No bar can be
     asserted against such a target beyond "no further from the reference's bf16 path than its own fp32 path is";
-    the figures are printed for BASELINE.md."""
+    the figures are printed."""
     cfg = dict(vocab=32000, dim=2048, layers=16, heads=16, hidden=5632, max_seq=2048)
     batch, seq = 2, 2048
     ids = O.synth_token_ids(batch, seq, cfg["vocab"], seed=7)
