@@ -628,9 +628,76 @@ __global__ void transposeCastKernel(const float* __restrict__ w, void* __restric
     }
 }
 
+// in [rows, cols] f32 -> bf16 copies in one pass over `in`: plain [rows, cols] (optional) and transposed [cols, rows].
+// 64 x 64 tiles through shared memory; 16-byte reads, 8-byte plain and 16-byte transposed writes, so every access is
+// whole sectors. rows % 8 == 0 and cols % 4 == 0 (the caller falls back to the scalar kernels otherwise).
+constexpr int kPairTile = 64;
+__global__ void __launch_bounds__(256)
+castPairKernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ plain, __nv_bfloat16* __restrict__ transposed,
+               int64_t rows, int64_t cols) {
+    __shared__ __nv_bfloat16 tile[kPairTile][kPairTile + 2];
+    const int64_t tilesC = (cols + kPairTile - 1) / kPairTile;
+    const int64_t tilesR = (rows + kPairTile - 1) / kPairTile;
+    for (int64_t t = blockIdx.x; t < tilesR * tilesC; t += gridDim.x) {
+        const int64_t r0 = (t / tilesC) * kPairTile, c0 = (t % tilesC) * kPairTile;
+        __syncthreads();
+        // 64 rows x 16 float4: thread -> (row = i / 16, four columns at (i % 16) * 4)
+#pragma unroll
+        for (int i = threadIdx.x; i < kPairTile * 16; i += 256) {
+            const int r = i >> 4, c = (i & 15) * 4;
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (r0 + r < rows && c0 + c < cols) v = *reinterpret_cast<const float4*>(in + (r0 + r) * cols + c0 + c);
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+            *reinterpret_cast<__nv_bfloat162*>(&tile[r][c]) = lo;
+            *reinterpret_cast<__nv_bfloat162*>(&tile[r][c + 2]) = hi;
+            if (plain != nullptr && r0 + r < rows && c0 + c < cols) {
+                uint2 packed;
+                packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(plain + (r0 + r) * cols + c0 + c) = packed;
+            }
+        }
+        __syncthreads();
+        // 64 output rows (input columns) x 8 pieces of 8 input rows: thread -> (column = i / 8, rows (i % 8) * 8 ..)
+#pragma unroll
+        for (int i = threadIdx.x; i < kPairTile * 8; i += 256) {
+            const int c = i >> 3, r = (i & 7) * 8;
+            if (c0 + c < cols && r0 + r < rows) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const __nv_bfloat162 pair = __halves2bfloat162(tile[r + 2 * j][c], tile[r + 2 * j + 1][c]);
+                    w[j] = *reinterpret_cast<const uint32_t*>(&pair);
+                }
+                *reinterpret_cast<uint4*>(transposed + (c0 + c) * rows + r0 + r) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    }
+}
+
 }  // namespace
 
 // ---- host entry points ------------------------------------------------------------------------
+
+void castPairBf16(const float* in, void* plain, void* transposed, int64_t rows, int64_t cols, cudaStream_t stream) {
+    require(rows >= 0 && cols >= 0, "cast_pair: negative size");
+    if (rows == 0 || cols == 0) return;
+    require(in != nullptr && transposed != nullptr, "cast_pair: null pointer");
+    auto aligned = [](const void* p, uintptr_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; };
+    if (rows % 8 == 0 && cols % 4 == 0 && aligned(in, 16) && aligned(transposed, 16) && (plain == nullptr || aligned(plain, 8))) {
+        const int64_t tiles = ((rows + kPairTile - 1) / kPairTile) * ((cols + kPairTile - 1) / kPairTile);
+        const int grid = static_cast<int>(std::min<int64_t>(tiles, static_cast<int64_t>(smCount()) * 16));
+        ProfileScope prof(kProfCast, stream, static_cast<double>(rows) * static_cast<double>(cols) * (plain != nullptr ? 8.0 : 6.0));
+        castPairKernel<<<grid, 256, 0, stream>>>(in, static_cast<__nv_bfloat16*>(plain), static_cast<__nv_bfloat16*>(transposed),
+                                                 rows, cols);
+        BFB_LAUNCH_CHECK();
+        noteLaunch();
+        return;
+    }
+    if (plain != nullptr) castScaled(in, BFB_F32, plain, BFB_BF16, rows * cols, 1.0f, nullptr, stream);
+    weightPrepare(in, transposed, BFB_BF16, rows, cols, 1.0f, nullptr, stream);
+}
+
 
 void embedPos(const float* ids, const float* table, const float* pos, void* out, int outDtype, int64_t batch,
               int64_t seq, int64_t vocab, int64_t dim, int64_t maxSeq, int64_t posOffset, int* oobCount,

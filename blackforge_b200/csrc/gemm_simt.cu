@@ -181,8 +181,9 @@ struct PoolScratch {
 
 // Both products run on the CTA-pair kernel, which wants its second operand as [N, K] with the reduction contiguous:
 //   dA = G (m x n) times b16 read as [N' = k][K' = n]  — b's own layout, no transpose;
-//   dB = A^T (k x m) times G^T read as [N' = n][K' = m] — a and grad go through the transposing cast, which costs the
-//        same pass over them as the plain cast the reference makes (toBf16, ops_tensorcore.cu:401-403).
+//   dB = A^T (k x m) times G^T read as [N' = n][K' = m] — a and grad go through a transposing cast (grad's plain and
+//        transposed copies come from one pass over it), where the reference makes plain casts (toBf16,
+//        ops_tensorcore.cu:401-403).
 void matmulBf16Backward(const float* a, const float* b, const float* grad, float* dA, float* dB, int64_t m, int64_t k,
                         int64_t n, const void* bNatural16, cudaStream_t stream) {
     require(m >= 0 && k >= 0 && n >= 0, "matmul_bf16_backward: negative size");
@@ -195,9 +196,8 @@ void matmulBf16Backward(const float* a, const float* b, const float* grad, float
     require(a != nullptr && b != nullptr && grad != nullptr && dA != nullptr && dB != nullptr,
             "matmul_bf16_backward: null pointer");
     PoolScratch g16(static_cast<size_t>(m * n) * 2), gT16(static_cast<size_t>(m * n) * 2), aT16(static_cast<size_t>(m * k) * 2);
-    castScaled(grad, BFB_F32, g16.ptr, BFB_BF16, m * n, 1.0f, nullptr, stream);
-    weightPrepare(grad, gT16.ptr, BFB_BF16, m, n, 1.0f, nullptr, stream);   // [m,n] -> [n,m]
-    weightPrepare(a, aT16.ptr, BFB_BF16, m, k, 1.0f, nullptr, stream);      // [m,k] -> [k,m]
+    castPairBf16(grad, g16.ptr, gT16.ptr, m, n, stream);      // [m,n] and [n,m] in one pass over grad
+    castPairBf16(a, nullptr, aT16.ptr, m, k, stream);         // [k,m]
     GemmArgs g;
     g.abDtype = BFB_BF16;
     g.cDtype = BFB_F32;

@@ -32,6 +32,9 @@ void fp8ScaleFromAmax(const float* dAmax, float* dScales, cudaStream_t stream);
 void fp8ActScale(const float* dAmax, float* out, const float* dWeightInverse, cudaStream_t stream);
 void weightPrepare(const float* w, void* out, int outDtype, int64_t k, int64_t n, float scale, const float* dScale,
                    cudaStream_t stream);
+// bf16 copies of in [rows, cols] (f32) in one pass over it: `plain` [rows, cols] (may be null) and `transposed`
+// [cols, rows].
+void castPairBf16(const float* in, void* plain, void* transposed, int64_t rows, int64_t cols, cudaStream_t stream);
 // Per-tensor e4m3 quantisation: dScales[0] = 448 / max|in|, [1] = its inverse, [2] = inverse * *dWeightInverse
 // (1 when null); out = e4m3(in * dScales[0]). `scratch` holds quantizeScratchFloats(n) floats of partial maxima.
 int64_t quantizeScratchFloats(int64_t n);

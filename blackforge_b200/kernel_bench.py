@@ -5,6 +5,7 @@ run, on small cases.
     python -m blackforge_b200.kernel_bench gemm --m 65536 --n 2048 --k 2048 [--dtype bf16|fp8] [--epilogue none]
     python -m blackforge_b200.kernel_bench attention --batch 16 --heads 16 --seq 2048
     python -m blackforge_b200.kernel_bench attention-bwd --batch 8 --heads 16 --seq 2048
+    python -m blackforge_b200.kernel_bench matmul-bwd --m 65536 --k 2048 --n 5632
     python -m blackforge_b200.kernel_bench rmsnorm --rows 65536 --dim 2048
     python -m blackforge_b200.kernel_bench embed --batch 32 --seq 2048 --vocab 32000 --dim 2048
 
@@ -23,7 +24,7 @@ import numpy as np
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attention", "attention-bwd", "rmsnorm", "embed", "checkpoint"])
+    ap.add_argument("kernel", choices=["gemm", "attention", "attention-bwd", "matmul-bwd", "rmsnorm", "embed", "checkpoint"])
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--hidden", type=int, default=5632)
     ap.add_argument("--chunk-mib", type=int, default=0, help="checkpoint: staging buffer size (0: the loader's default)")
@@ -133,6 +134,18 @@ def main():
         # five products of 2 * 128 flops per visible (query, key) pair
         work, unit = 10.0 * 128 * args.batch * args.heads * args.seq * (args.seq + 1) / 2.0, "TFLOP/s"
         desc = {"batch": args.batch, "heads": args.heads, "seq": args.seq, "head_dim": 128, "flops": "causal, 5 products"}
+    elif args.kernel == "matmul-bwd":
+        # both gradients of C = A B from fp32 tensors, as the reference's matmulBf16Backward takes them: three casts to
+        # bf16 (two of them transposing) and two tensor-core GEMMs
+        a = rand_dev(args.m * args.k, bfb.F32)
+        b = rand_dev(args.k * args.n, bfb.F32, 0.05)
+        g = rand_dev(args.m * args.n, bfb.F32)
+        d_a, d_b = bfb.DeviceBuffer(args.m * args.k * 4), bfb.DeviceBuffer(args.k * args.n * 4)
+
+        def run():
+            bfb.check(lib.bfb_matmul_bf16_backward(a.ptr, b.ptr, g.ptr, d_a.ptr, d_b.ptr, args.m, args.k, args.n, None))
+        work, unit = 4.0 * args.m * args.k * args.n, "TFLOP/s"
+        desc = {"m": args.m, "k": args.k, "n": args.n, "operands": "fp32 in, bf16 products, fp32 out", "flops": "dA and dB"}
     elif args.kernel == "rmsnorm":
         sd = bfb.BF16 if args.stream_dtype == "bf16" else bfb.F32
         x = rand_dev(args.rows * args.dim, sd)
