@@ -222,3 +222,43 @@ def test_matmul_bf16_backward_against_the_reference_cublaslt_path(gpu, refcuda):
     got_a, got_b = matmul_bf16_backward(gpu, a, b, g)
     print("matmul bf16 backward vs reference: dA", float(np.max(np.abs(got_a - want_a))), "dB", float(np.max(np.abs(got_b - want_b))))
     assert close(got_a, want_a, 2e-5) and close(got_b, want_b, 2e-5)
+
+
+def test_backward_configuration_2_in_full_against_the_reference_kernel(gpu, refcuda):
+    """The attention benchmark's full size (batch 16, 16 heads of 128, sequence 2048, causal): every element of dQ, dK
+    and dV from the tensor-core kernel against the reference's fusedAttentionBackward on the same bf16-valued inputs
+    (operands: the reference's own forward output and row statistics), and both device times."""
+    rng = np.random.default_rng(3)
+    B, H, D, S = 16, 16, 128, 2048
+    q, k, v, g = (O.round_bf16(rng.standard_normal((B, S, H * D), dtype=np.float32)) for _ in range(4))
+    scale = float(D ** -0.5)
+    want = refcuda.cuda_fused_attention_backward(g, q, k, v, H, scale, 0, iters=1)
+    dim = H * D
+    dev = [gpu.upload(t, gpu.BF16) for t in (g, q, k, v, O.round_bf16(want["out"]))]
+    d_m, d_l = gpu.upload(want["m"], gpu.F32), gpu.upload(want["l"], gpu.F32)
+    grads = [gpu.DeviceBuffer(q.size * 4) for _ in range(3)]
+    scratch, status = gpu.DeviceBuffer(B * H * S * 8), gpu.DeviceBuffer.zeros(4)
+
+    def run():
+        gpu.check(gpu.lib().bfb_attention_bwd(dev[0].ptr, dev[1].ptr, dev[2].ptr, dev[3].ptr, dev[4].ptr, d_m.ptr, d_l.ptr,
+                                              grads[0].ptr, grads[1].ptr, grads[2].ptr, scratch.ptr, gpu.BF16, B, S, S, H, D,
+                                              dim, dim, dim, dim, scale, 0, 1, status.ptr, None))
+    import torch
+    run()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(3):
+        run()
+    b.record()
+    torch.cuda.synchronize()
+    ours_ms = a.elapsed_time(b) / 3
+    assert int(status.to_numpy(np.int32, (1,))[0]) == 0
+    flops = 10.0 * D * B * H * S * (S + 1) / 2.0
+    print(f"configuration 2 backward: reference {want['ms']:.1f} ms ({flops / want['ms'] / 1e9:.2f} TFLOP/s causal), "
+          f"this kernel {ours_ms:.3f} ms ({flops / ours_ms / 1e9:.1f} TFLOP/s)")
+    for name, buf in zip(("dq", "dk", "dv"), grads):
+        got = gpu.download(buf, gpu.F32, q.shape)
+        err, top = float(np.max(np.abs(got - want[name]))), float(np.max(np.abs(want[name])))
+        print(f"  {name}: max abs diff {err:.3e} of {top:.3f}")
+        assert np.isfinite(got).all() and err <= TOL_BF16 * max(1.0, top), name
