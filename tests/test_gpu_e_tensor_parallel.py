@@ -190,3 +190,39 @@ def test_gradient_average_without_a_communicator_is_refused(gpu):
     table = (C.c_void_p * 1)(buf.ptr)
     counts = (C.c_int64 * 1)(4)
     assert gpu.lib().bfb_gradients_average(table, counts, 1, None) == gpu.INVALID_ARGUMENT
+
+
+ONE_RANK_WORKER = r"""
+import ctypes as C
+import os, sys
+import numpy as np
+sys.path.insert(0, os.environ["BFB_ROOT"])
+import blackforge_b200 as bfb
+bfb.check(bfb.lib().bfb_set_device(0))
+bfb.tp_init(bfb.tp_unique_id(), 0, 1)
+rng = np.random.default_rng(9)
+grads = [rng.standard_normal(s).astype(np.float32) for s in ((257, 33), (5,), (0,))]
+bufs = [bfb.upload(g, bfb.F32) for g in grads]
+table = (C.c_void_p * len(bufs))(*[b.ptr or None for b in bufs])
+counts = (C.c_int64 * len(bufs))(*[g.size for g in grads])
+bfb.check(bfb.lib().bfb_gradients_average(table, counts, len(bufs), None))
+bfb.sync()
+for b, g in zip(bufs, grads):
+    assert np.array_equal(bfb.download(b, bfb.F32, g.shape), g)
+# a negative count is refused before anything is issued
+bad = (C.c_int64 * 1)(-1)
+assert bfb.lib().bfb_gradients_average(table, bad, 1, None) == bfb.INVALID_ARGUMENT
+bfb.tp_destroy()
+print("one rank ok")
+"""
+
+
+def test_gradient_average_over_one_replica_is_the_identity(gpu, tmp_path):
+    """The grouped average on a one-rank communicator (what a single-GPU box can run): every gradient comes back
+    unchanged, an empty tensor is skipped, a bad table is refused."""
+    script = tmp_path / "one_rank_worker.py"
+    script.write_text(ONE_RANK_WORKER)
+    env = dict(os.environ, BFB_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    proc = subprocess.run([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                          timeout=300)
+    assert proc.returncode == 0 and "one rank ok" in proc.stdout, proc.stdout
