@@ -262,3 +262,36 @@ def test_backward_configuration_2_in_full_against_the_reference_kernel(gpu, refc
         err, top = float(np.max(np.abs(got - want[name]))), float(np.max(np.abs(want[name])))
         print(f"  {name}: max abs diff {err:.3e} of {top:.3f}")
         assert np.isfinite(got).all() and err <= TOL_BF16 * max(1.0, top), name
+
+
+@pytest.mark.parametrize("B,H,old,new,causal", [
+    (1, 1, 130, 1, 1),      # one new row after a cache: a single step on every key block
+    (1, 3, 0, 129, 1),      # one row into the second query block
+    (2, 1, 5, 640, 1),      # five and six steps per key block: both parities of every barrier several times over
+    (1, 2, 257, 255, 1),    # cache and rows both off the tile grid
+    (1, 1, 0, 300, 0),      # bidirectional: every key block walks every query block
+    (1, 2, 64, 64, 0),
+])
+def test_tensor_core_backward_shapes_off_the_tile_grid(gpu, B, H, old, new, causal):
+    rng = np.random.default_rng(B + 10 * H + old + 3 * new + causal)
+    D = 128
+    r = O.round_bf16
+    q = r(rng.standard_normal((B, new, H * D)).astype(np.float32))
+    k = r(rng.standard_normal((B, old + new, H * D)).astype(np.float32))
+    v = r(rng.standard_normal((B, old + new, H * D)).astype(np.float32))
+    g = r(rng.standard_normal((B, new, H * D)).astype(np.float32))
+    scale = float(D ** -0.5)
+    if causal:
+        out, m, l = O.attention_forward_stats(q, k, v, H, scale, old)
+        want = O.attention_backward(g, q, k, v, out, m, l, H, scale, old)
+    else:
+        # every key visible: the oracle's mask j <= old_len + i with old_len = total_len lets everything through
+        out, m, l = O.attention_forward_stats(q, k, v, H, scale, old + new)
+        want = O.attention_backward(g, q, k, v, out, m, l, H, scale, old + new)
+    got = attention_backward(gpu, g, q, k, v, r(out), m, l, H, gpu.BF16, old_len=old, causal=causal)
+    for name, a, b in zip(("dQ", "dK", "dV"), got, want):
+        assert close(a, b, TOL_BF16), name
+    # the fp32 route on the same problem
+    got32 = attention_backward(gpu, g, q, k, v, out, m, l, H, gpu.F32, old_len=old, causal=causal)
+    for name, a, b in zip(("dQ", "dK", "dV"), got32, want):
+        assert close(a, b, TOL_F32), name
