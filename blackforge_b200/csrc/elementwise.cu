@@ -658,18 +658,23 @@ castPairKernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ plain, 
             }
         }
         __syncthreads();
-        // 64 output rows (input columns) x 8 pieces of 8 input rows: thread -> (column = i / 8, rows (i % 8) * 8 ..)
-#pragma unroll
-        for (int i = threadIdx.x; i < kPairTile * 8; i += 256) {
-            const int c = i >> 3, r = (i & 7) * 8;
+        // 32 pairs of output rows (input columns c, c + 1) x 8 pieces of 8 input rows: one 32-bit read serves both rows
+        {
+            const int i = threadIdx.x;
+            const int c = (i >> 3) * 2, r = (i & 7) * 8;
             if (c0 + c < cols && r0 + r < rows) {
-                uint32_t w[4];
+                uint32_t lo[4], hi[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const __nv_bfloat162 pair = __halves2bfloat162(tile[r + 2 * j][c], tile[r + 2 * j + 1][c]);
-                    w[j] = *reinterpret_cast<const uint32_t*>(&pair);
+                    const uint32_t a = *reinterpret_cast<const uint32_t*>(&tile[r + 2 * j][c]);       // (c, c + 1) of row r + 2j
+                    const uint32_t b = *reinterpret_cast<const uint32_t*>(&tile[r + 2 * j + 1][c]);
+                    lo[j] = __byte_perm(a, b, 0x5410);   // column c of both rows
+                    hi[j] = __byte_perm(a, b, 0x7632);   // column c + 1
                 }
-                *reinterpret_cast<uint4*>(transposed + (c0 + c) * rows + r0 + r) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(transposed + (c0 + c) * rows + r0 + r) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                if (c0 + c + 1 < cols) {
+                    *reinterpret_cast<uint4*>(transposed + (c0 + c + 1) * rows + r0 + r) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                }
             }
         }
     }
