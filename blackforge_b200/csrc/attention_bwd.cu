@@ -102,9 +102,17 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    // work: blocks are ordered heaviest first (key block 0 is seen by every query block)
-    const int kvBlock = static_cast<int>(blockIdx.x % static_cast<unsigned>(p.numKvBlocks));
-    const int bh = static_cast<int>(blockIdx.x / static_cast<unsigned>(p.numKvBlocks));
+    // work: key block 0 is seen by every query block, the last one by one: blocks differ in weight by the number of key blocks
+    // (batch, head) pairs in groups of kGroup (their Q, K, V and dO together stay in L2: 2 MB a pair at 2048 rows); inside
+    // a group the heaviest key blocks of all its pairs come first, so that the light ones fill the SMs at its end
+    constexpr int kGroup = 8;
+    const int numBh = p.batch * p.numHeads;
+    const int perGroup = kGroup * p.numKvBlocks;
+    const int group = static_cast<int>(blockIdx.x) / perGroup;
+    const int inGroup = static_cast<int>(blockIdx.x) - group * perGroup;
+    const int groupSize = min(kGroup, numBh - group * kGroup);
+    const int kvBlock = inGroup / groupSize;
+    const int bh = group * kGroup + inGroup % groupSize;
     const int b = bh / p.numHeads, h = bh % p.numHeads;
     const int k0 = kvBlock * kBlk;
     const int numQBlocks = (p.newLen + kBlk - 1) / kBlk;
