@@ -587,6 +587,18 @@ void attentionBackward(const AttentionBackwardArgs& a, cudaStream_t stream) {
     require(a.dtype == BFB_F32 || a.dtype == BFB_BF16, "attention_bwd: q, k, v, out and d_out are f32 or bf16");
     const int64_t rows = a.batch * a.numHeads * a.newLen;
     const size_t kvElems = static_cast<size_t>(a.batch) * a.totalLen;
+    const int64_t dimAll = a.numHeads * a.headDim;
+    require(a.ldQ >= dimAll && a.ldK >= dimAll && a.ldV >= dimAll && a.ldO >= dimAll && a.ldDo >= dimAll &&
+                a.ldDq >= dimAll && a.ldDk >= dimAll && a.ldDv >= dimAll,
+            "attention_bwd: row stride below heads*head_dim");
+    if (kvElems > 0) require(a.dK != nullptr && a.dV != nullptr, "attention_bwd: null gradient pointer");
+    if (rows > 0) {
+        require(a.totalLen > 0, "attention_bwd: no keys");
+        require(a.dOut != nullptr && a.q != nullptr && a.k != nullptr && a.v != nullptr && a.out != nullptr && a.m != nullptr &&
+                    a.l != nullptr && a.dQ != nullptr,
+                "attention_bwd: null pointer");
+        require(a.lse2Scratch != nullptr && a.dTermScratch != nullptr, "attention_bwd: null scratch pointer");
+    }
     const bool tensorCores = rows > 0 && attentionBackwardUsesTensorCores(a);
     // The CUDA-core kernel accumulates dK and dV with atomics: they start from zero. The tensor-core kernel writes every
     // element of both itself (a CTA owns its keys) and accumulates dQ, which then starts from zero.

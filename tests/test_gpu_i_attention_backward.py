@@ -112,6 +112,15 @@ def test_backward_empty_and_rejected_inputs(gpu):
     code = gpu.lib().bfb_attention_bwd(None, None, None, None, None, None, None, None, None, None, None, gpu.F32, 1, 2, 2,
                                        1, 300, 300, 300, 300, 300, 1.0, 0, 1, None, None)
     assert code == gpu.INVALID_ARGUMENT
+    # valid sizes with a missing operand: refused on the host, nothing is launched
+    buf = gpu.DeviceBuffer.zeros(2 * 2 * 16 * 4)
+    code = gpu.lib().bfb_attention_bwd(buf.ptr, buf.ptr, buf.ptr, buf.ptr, buf.ptr, buf.ptr, None, buf.ptr, buf.ptr, buf.ptr,
+                                       buf.ptr, gpu.F32, 1, 2, 2, 1, 16, 16, 16, 16, 16, 1.0, 0, 1, None, None)
+    assert code == gpu.INVALID_ARGUMENT and b"null" in gpu.lib().bfb_last_error()
+    # a row stride below heads * head_dim
+    code = gpu.lib().bfb_attention_bwd(buf.ptr, buf.ptr, buf.ptr, buf.ptr, buf.ptr, buf.ptr, buf.ptr, buf.ptr, buf.ptr, buf.ptr,
+                                       buf.ptr, gpu.F32, 1, 2, 2, 1, 16, 8, 16, 16, 16, 1.0, 0, 1, None, None)
+    assert code == gpu.INVALID_ARGUMENT
 
 
 def test_backward_against_committed_reference_outputs(gpu):
