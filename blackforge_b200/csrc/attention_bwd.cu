@@ -17,8 +17,9 @@
 //    step's Q and dO and ADDED to global memory by the TMA unit (cp.reduce.async.bulk.tensor), four instructions per
 //    step; per-element atomics took a third of the step.
 //    TMEM columns: S^T / P^T / dQ [0,128)  dP^T / dS^T [128,256)  dV [256,384)  dK [384,512).
-//    dK and dV are written with plain stores (a CTA owns its keys); dQ is accumulated over the key blocks (zeroed by the
-//    host first), as the reference accumulates dK and dV with atomics.
+//    dK and dV are written once (a CTA owns its keys), staged in the K and V tiles' shared memory and stored by the TMA
+//    unit; dQ is accumulated over the key blocks (zeroed by the host first), as the reference accumulates dK and dV
+//    with atomics.
 //  * attentionBackwardSimtKernel: any head_dim <= 256, fp32 or bf16 storage, one warp per query row; the shape-general
 //    path, with the reference's own order of work.
 // All mbarrier waits are bounded.
@@ -77,7 +78,8 @@ struct BwdParams {
 __global__ void __launch_bounds__(kThreads, 1)
 attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_constant__ CUtensorMap tmapK,
                           const __grid_constant__ CUtensorMap tmapV, const __grid_constant__ CUtensorMap tmapDo,
-                          const __grid_constant__ CUtensorMap tmapDq, BwdParams p, int* status) {
+                          const __grid_constant__ CUtensorMap tmapDq, const __grid_constant__ CUtensorMap tmapDk,
+                          const __grid_constant__ CUtensorMap tmapDv, BwdParams p, int* status) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOff);
     uint64_t* kvFull = bars;          // [1]
@@ -92,7 +94,9 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
     uint64_t* rowFull = bars + 11;    // [2] row statistics of a step written (8 warps)
     uint64_t* slotFree = bars + 13;   // every product that reads the step's Q and dO tiles is complete
     uint64_t* dpFull = bars + 14;     // dP^T complete
-    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 15);
+    uint64_t* epiStaged = bars + 15;  // a gradient tile of the keys is in shared memory (8 warps)
+    uint64_t* epiFree = bars + 16;    // ... and has been read out of it
+    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 17);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
     if ((smem_u32(smem) & 1023u) != 0u) {
@@ -134,6 +138,8 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
         mbar_init(accFull, 1);
         mbar_init(slotFree, 1);
         mbar_init(dpFull, 1);
+        mbar_init(epiStaged, kSoftmaxWarps);
+        mbar_init(epiFree, 1);
         mbar_init(&rowFull[0], kSoftmaxWarps);
         mbar_init(&rowFull[1], kSoftmaxWarps);
         *abortFlag = 0;
@@ -143,6 +149,8 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
         tma_prefetch_desc(&tmapV);
         tma_prefetch_desc(&tmapDo);
         tma_prefetch_desc(&tmapDq);
+        tma_prefetch_desc(&tmapDk);
+        tma_prefetch_desc(&tmapDv);
     }
     if (warp == kMmaWarp) {
         tmem_alloc(tmemSlot, 512);
@@ -439,23 +447,48 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
             for (int i = 0; i < kD; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
         if (alive && steps > 0 && warp_all(mbar_wait(accFull, 0, abortFlag, status, kDevTimeoutAccFull))) {
+            // dV, then dK: a thread owns a key row, so the 64 KB tile is laid into the K and V tiles' shared memory (no
+            // product reads them any more) as four boxes of 32 floats x 128 rows in the 128-byte swizzle, and the TMA
+            // unit writes it: whole lines, and rows past the last key are clipped by the tensor map.
             tc_fence_after();
-            const uint32_t tAcc = tmemBase + laneBase + (half == 0 ? 256u : 384u);
-            float* dst = (half == 0 ? p.dV : p.dK) +
-                         (static_cast<size_t>(b) * p.totalLen + keyPos) * (half == 0 ? p.ldDv : p.ldDk) + static_cast<size_t>(h) * kD;
+            uint8_t* stageBase = smem + kKOff;
+            bool ok = true;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t acc[32];
-                tmem_ld_32x32(tAcc + static_cast<uint32_t>(c * 32), acc);
-                tmem_ld_wait();
-                if (keyValid) {
+            for (int which = 0; which < 2 && ok; ++which) {
+                if (which == 1 && !warp_all(mbar_wait(epiFree, 0, abortFlag, status, kDevTimeoutStageEmpty))) break;
+                const uint32_t tAcc = tmemBase + laneBase + (which == 0 ? 256u : 384u) + static_cast<uint32_t>(half * 64);
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        *reinterpret_cast<float4*>(dst + c * 32 + i) =
-                            make_float4(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]), __uint_as_float(acc[i + 2]),
-                                        __uint_as_float(acc[i + 3]));
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t acc[32];
+                    tmem_ld_32x32(tAcc + static_cast<uint32_t>(c * 32), acc);
+                    tmem_ld_wait();
+                    uint8_t* row = stageBase + (half * 2 + c) * (kBlk * 128) + keyRow * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        *reinterpret_cast<uint4*>(row + ((j ^ (keyRow & 7)) << 4)) =
+                            make_uint4(acc[j * 4], acc[j * 4 + 1], acc[j * 4 + 2], acc[j * 4 + 3]);
                     }
                 }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(epiStaged);
+                if (warp == 0 && lane == 0) {
+                    if (mbar_wait(epiStaged, static_cast<uint32_t>(which), abortFlag, status, kDevTimeoutOther)) {
+                        const CUtensorMap* map = which == 0 ? &tmapDv : &tmapDk;
+#pragma unroll
+                        for (int box = 0; box < 4; ++box) {
+                            tma_store_3d(map, stageBase + box * (kBlk * 128), h * kD + box * 32, k0, b);
+                        }
+                        tma_store_commit();
+                        if (which == 0) {
+                            tma_store_wait_read();
+                            mbar_arrive(epiFree);
+                        } else {
+                            tma_store_wait_all();
+                        }
+                    }
+                }
+                __syncwarp();
             }
         }
     }
@@ -633,6 +666,15 @@ void attentionBackward(const AttentionBackwardArgs& a, cudaStream_t stream) {
             uint32_t box[3] = {32u, 128u, 1u};
             encodeTensorMap(&tdq, a.dQ, 4, 3, dims, strides, box);
         }
+        TensorMapStorage tdk, tdv;
+        {
+            uint64_t dims[3] = {static_cast<uint64_t>(dim), static_cast<uint64_t>(a.totalLen), static_cast<uint64_t>(a.batch)};
+            uint32_t box[3] = {32u, 128u, 1u};
+            uint64_t sk[2] = {static_cast<uint64_t>(a.ldDk) * 4, static_cast<uint64_t>(a.ldDk) * 4 * static_cast<uint64_t>(a.totalLen)};
+            uint64_t sv[2] = {static_cast<uint64_t>(a.ldDv) * 4, static_cast<uint64_t>(a.ldDv) * 4 * static_cast<uint64_t>(a.totalLen)};
+            encodeTensorMap(&tdk, a.dK, 4, 3, dims, sk, box);
+            encodeTensorMap(&tdv, a.dV, 4, 3, dims, sv, box);
+        }
         makeMap3(&tq, a.q, dim, a.newLen, a.batch, a.ldQ);
         makeMap3(&tk, a.k, dim, a.totalLen, a.batch, a.ldK);
         makeMap3(&tv, a.v, dim, a.totalLen, a.batch, a.ldV);
@@ -661,7 +703,8 @@ void attentionBackward(const AttentionBackwardArgs& a, cudaStream_t stream) {
         attentionBackwardTcKernel<<<static_cast<unsigned>(blocks), kThreads, kSmemBytes, stream>>>(
             *reinterpret_cast<const CUtensorMap*>(tq.bytes), *reinterpret_cast<const CUtensorMap*>(tk.bytes),
             *reinterpret_cast<const CUtensorMap*>(tv.bytes), *reinterpret_cast<const CUtensorMap*>(tg.bytes),
-            *reinterpret_cast<const CUtensorMap*>(tdq.bytes), p, a.dStatus);
+            *reinterpret_cast<const CUtensorMap*>(tdq.bytes), *reinterpret_cast<const CUtensorMap*>(tdk.bytes),
+            *reinterpret_cast<const CUtensorMap*>(tdv.bytes), p, a.dStatus);
         BFB_LAUNCH_CHECK();
         noteLaunch();
         return;
