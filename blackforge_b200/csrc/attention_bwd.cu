@@ -17,8 +17,8 @@
 //    step's Q and dO and ADDED to global memory by the TMA unit (cp.reduce.async.bulk.tensor), four instructions per
 //    step; per-element atomics took a third of the step.
 //    TMEM columns: S^T / P^T / dQ [0,128)  dP^T / dS^T [128,256)  dV [256,384)  dK [384,512).
-//    dK and dV are written once (a CTA owns its keys), staged in the K and V tiles' shared memory and stored by the TMA
-//    unit; dQ is accumulated over the key blocks (zeroed by the host first), as the reference accumulates dK and dV
+//    dK and dV are written once (a CTA owns its keys), staged in the K and V tiles' shared memory and stored from there
+//    a whole row per warp instruction; dQ is accumulated over the key blocks (zeroed by the host first), as the reference accumulates dK and dV
 //    with atomics.
 //  * attentionBackwardSimtKernel: any head_dim <= 256, fp32 or bf16 storage, one warp per query row; the shape-general
 //    path, with the reference's own order of work.
@@ -78,8 +78,7 @@ struct BwdParams {
 __global__ void __launch_bounds__(kThreads, 1)
 attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __grid_constant__ CUtensorMap tmapK,
                           const __grid_constant__ CUtensorMap tmapV, const __grid_constant__ CUtensorMap tmapDo,
-                          const __grid_constant__ CUtensorMap tmapDq, const __grid_constant__ CUtensorMap tmapDk,
-                          const __grid_constant__ CUtensorMap tmapDv, BwdParams p, int* status) {
+                          const __grid_constant__ CUtensorMap tmapDq, BwdParams p, int* status) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kBarOff);
     uint64_t* kvFull = bars;          // [1]
@@ -95,7 +94,7 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
     uint64_t* slotFree = bars + 13;   // every product that reads the step's Q and dO tiles is complete
     uint64_t* dpFull = bars + 14;     // dP^T complete
     uint64_t* epiStaged = bars + 15;  // a gradient tile of the keys is in shared memory (8 warps)
-    uint64_t* epiFree = bars + 16;    // ... and has been read out of it
+    uint64_t* epiFree = bars + 16;    // ... and has been read out of it (8 warps)
     uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 17);
     volatile int* abortFlag = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
@@ -124,12 +123,32 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
     const int firstQ = p.causal ? max(0, k0 - p.oldLen) / kBlk : 0;
     const int steps = max(0, numQBlocks - firstQ);
 
-    if (threadIdx.x == 0) {
+    // The first tiles are requested before anything else is set up: the producer thread initialises the three barriers
+    // they complete on itself (the other roles look at them only after the CTA-wide barrier below).
+    auto loadQdO = [&](int it) {
+        uint8_t* slot = smem + kRingOff + (it & 1) * 2 * kTileBytes;
+        const int q0 = (firstQ + it) * kBlk;
+        mbar_arrive_expect_tx(&qFull[it & 1], 2 * kTileBytes);
+        tma_load_3d(slot, &tmapQ, &qFull[it & 1], h * kD, q0, b);
+        tma_load_3d(slot + kHalfBytes, &tmapQ, &qFull[it & 1], h * kD + 64, q0, b);
+        tma_load_3d(slot + kTileBytes, &tmapDo, &qFull[it & 1], h * kD, q0, b);
+        tma_load_3d(slot + kTileBytes + kHalfBytes, &tmapDo, &qFull[it & 1], h * kD + 64, q0, b);
+    };
+    if (warp == kProducerWarp && steps > 0 && elect_one()) {
         mbar_init(kvFull, 1);
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&qFull[i], 1);
-            mbar_init(&dqStaged[i], kSoftmaxWarps);
-        }
+        mbar_init(&qFull[0], 1);
+        mbar_init(&qFull[1], 1);
+        fence_mbar_init();
+        mbar_arrive_expect_tx(kvFull, 2 * kTileBytes);
+        tma_load_3d(smem + kKOff, &tmapK, kvFull, h * kD, k0, b);
+        tma_load_3d(smem + kKOff + kHalfBytes, &tmapK, kvFull, h * kD + 64, k0, b);
+        tma_load_3d(smem + kVOff, &tmapV, kvFull, h * kD, k0, b);
+        tma_load_3d(smem + kVOff + kHalfBytes, &tmapV, kvFull, h * kD + 64, k0, b);
+        loadQdO(0);
+        if (steps > 1) loadQdO(1);
+    }
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; ++i) mbar_init(&dqStaged[i], kSoftmaxWarps);
         mbar_init(sFull, 1);
         mbar_init(pFull, kSoftmaxWarps);
         mbar_init(dsFull, kSoftmaxWarps);
@@ -139,7 +158,7 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
         mbar_init(slotFree, 1);
         mbar_init(dpFull, 1);
         mbar_init(epiStaged, kSoftmaxWarps);
-        mbar_init(epiFree, 1);
+        mbar_init(epiFree, kSoftmaxWarps);
         mbar_init(&rowFull[0], kSoftmaxWarps);
         mbar_init(&rowFull[1], kSoftmaxWarps);
         *abortFlag = 0;
@@ -149,8 +168,6 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
         tma_prefetch_desc(&tmapV);
         tma_prefetch_desc(&tmapDo);
         tma_prefetch_desc(&tmapDq);
-        tma_prefetch_desc(&tmapDk);
-        tma_prefetch_desc(&tmapDv);
     }
     if (warp == kMmaWarp) {
         tmem_alloc(tmemSlot, 512);
@@ -164,36 +181,23 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
     if (warp == kProducerWarp) {
         // ---------------- TMA producer (one elected thread) ----------------
         if (elect_one() && steps > 0) {
-            mbar_arrive_expect_tx(kvFull, 2 * kTileBytes);
-            tma_load_3d(smem + kKOff, &tmapK, kvFull, h * kD, k0, b);
-            tma_load_3d(smem + kKOff + kHalfBytes, &tmapK, kvFull, h * kD + 64, k0, b);
-            tma_load_3d(smem + kVOff, &tmapV, kvFull, h * kD, k0, b);
-            tma_load_3d(smem + kVOff + kHalfBytes, &tmapV, kvFull, h * kD + 64, k0, b);
-            // Slot (it & 1) receives the Q and dO tiles of step it. Before that, the dQ tile the gradient warps staged
-            // there for step it - 2 is added to global memory; the slot is free again when that tile has been read.
-            for (int it = 0; it < steps + 2; ++it) {
+            // Slot (it & 1) receives the Q and dO tiles of step it (those of steps 0 and 1 were requested above). Before
+            // that, the dQ tile the gradient warps staged there for step it - 2 is added to global memory; the slot is
+            // free again when that tile has been read. The CTA may end once the last tile has been read: the unit
+            // completes the additions by itself.
+            for (int it = 2; it < steps + 2; ++it) {
                 const int stage = it & 1;
                 uint8_t* slot = smem + kRingOff + stage * 2 * kTileBytes;
-                if (it >= 2) {
-                    if (!mbar_wait(&dqStaged[stage], ((it - 2) >> 1) & 1, abortFlag, status, kDevTimeoutStageEmpty)) break;
-                    const int qPrev = (firstQ + it - 2) * kBlk;
+                if (!mbar_wait(&dqStaged[stage], ((it - 2) >> 1) & 1, abortFlag, status, kDevTimeoutStageEmpty)) break;
+                const int qPrev = (firstQ + it - 2) * kBlk;
 #pragma unroll
-                    for (int box = 0; box < 4; ++box) {
-                        tma_reduce_add_3d(&tmapDq, slot + box * (kBlk * 128), h * kD + box * 32, qPrev, b);
-                    }
-                    tma_store_commit();
-                    tma_store_wait_read();
+                for (int box = 0; box < 4; ++box) {
+                    tma_reduce_add_3d(&tmapDq, slot + box * (kBlk * 128), h * kD + box * 32, qPrev, b);
                 }
-                if (it < steps) {
-                    const int q0 = (firstQ + it) * kBlk;
-                    mbar_arrive_expect_tx(&qFull[stage], 2 * kTileBytes);
-                    tma_load_3d(slot, &tmapQ, &qFull[stage], h * kD, q0, b);
-                    tma_load_3d(slot + kHalfBytes, &tmapQ, &qFull[stage], h * kD + 64, q0, b);
-                    tma_load_3d(slot + kTileBytes, &tmapDo, &qFull[stage], h * kD, q0, b);
-                    tma_load_3d(slot + kTileBytes + kHalfBytes, &tmapDo, &qFull[stage], h * kD + 64, q0, b);
-                }
+                tma_store_commit();
+                tma_store_wait_read();
+                if (it < steps) loadQdO(it);
             }
-            tma_store_wait_all();
         }
         __syncwarp();
     } else if (warp == kMmaWarp) {
@@ -447,14 +451,15 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
             for (int i = 0; i < kD; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
         if (alive && steps > 0 && warp_all(mbar_wait(accFull, 0, abortFlag, status, kDevTimeoutAccFull))) {
-            // dV, then dK: a thread owns a key row, so the 64 KB tile is laid into the K and V tiles' shared memory (no
-            // product reads them any more) as four boxes of 32 floats x 128 rows in the 128-byte swizzle, and the TMA
-            // unit writes it: whole lines, and rows past the last key are clipped by the tensor map.
+            // dV, then dK: a thread owns a key row of the accumulator, so the 64 KB tile is laid into the K and V tiles'
+            // shared memory (no product reads them any more; four parts of 32 floats x 128 rows, 16-byte pieces swizzled by
+            // the row) and leaves from there a row per warp instruction: 512 contiguous bytes. (Written by the TMA unit the
+            // two tiles queued behind the last dQ tiles: 1 536 row segments of 128 bytes at about 5 cycles each, 7 500
+            // cycles at the end of every CTA.)
             tc_fence_after();
             uint8_t* stageBase = smem + kKOff;
-            bool ok = true;
 #pragma unroll 1
-            for (int which = 0; which < 2 && ok; ++which) {
+            for (int which = 0; which < 2; ++which) {
                 if (which == 1 && !warp_all(mbar_wait(epiFree, 0, abortFlag, status, kDevTimeoutStageEmpty))) break;
                 const uint32_t tAcc = tmemBase + laneBase + (which == 0 ? 256u : 384u) + static_cast<uint32_t>(half * 64);
 #pragma unroll
@@ -469,26 +474,25 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
                             make_uint4(acc[j * 4], acc[j * 4 + 1], acc[j * 4 + 2], acc[j * 4 + 3]);
                     }
                 }
-                fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(epiStaged);
-                if (warp == 0 && lane == 0) {
-                    if (mbar_wait(epiStaged, static_cast<uint32_t>(which), abortFlag, status, kDevTimeoutOther)) {
-                        const CUtensorMap* map = which == 0 ? &tmapDv : &tmapDk;
-#pragma unroll
-                        for (int box = 0; box < 4; ++box) {
-                            tma_store_3d(map, stageBase + box * (kBlk * 128), h * kD + box * 32, k0, b);
-                        }
-                        tma_store_commit();
-                        if (which == 0) {
-                            tma_store_wait_read();
-                            mbar_arrive(epiFree);
-                        } else {
-                            tma_store_wait_all();
-                        }
-                    }
+                if (!warp_all(mbar_wait(epiStaged, static_cast<uint32_t>(which), abortFlag, status, kDevTimeoutOther))) break;
+                // warp w writes key rows w, w + 8, ...; lane l the floats [4l, 4l + 4) of the row; rows past the last key
+                // are left out
+                const size_t ld = which == 0 ? p.ldDv : p.ldDk;
+                float* dst = (which == 0 ? p.dV : p.dK) + (static_cast<size_t>(b) * p.totalLen + k0) * ld +
+                             static_cast<size_t>(h) * kD + lane * 4;
+                const uint8_t* part = stageBase + (lane >> 3) * (kBlk * 128);
+                const int validRows = min(kBlk, p.totalLen - k0);
+#pragma unroll 4
+                for (int r = warp; r < validRows; r += kSoftmaxWarps) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(part + r * 128 + (((lane & 7) ^ (r & 7)) << 4));
+                    *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * ld) = v;
                 }
-                __syncwarp();
+                if (which == 0) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(epiFree);   // this warp has read its rows of dV out of the tiles
+                }
             }
         }
     }
@@ -666,15 +670,6 @@ void attentionBackward(const AttentionBackwardArgs& a, cudaStream_t stream) {
             uint32_t box[3] = {32u, 128u, 1u};
             encodeTensorMap(&tdq, a.dQ, 4, 3, dims, strides, box);
         }
-        TensorMapStorage tdk, tdv;
-        {
-            uint64_t dims[3] = {static_cast<uint64_t>(dim), static_cast<uint64_t>(a.totalLen), static_cast<uint64_t>(a.batch)};
-            uint32_t box[3] = {32u, 128u, 1u};
-            uint64_t sk[2] = {static_cast<uint64_t>(a.ldDk) * 4, static_cast<uint64_t>(a.ldDk) * 4 * static_cast<uint64_t>(a.totalLen)};
-            uint64_t sv[2] = {static_cast<uint64_t>(a.ldDv) * 4, static_cast<uint64_t>(a.ldDv) * 4 * static_cast<uint64_t>(a.totalLen)};
-            encodeTensorMap(&tdk, a.dK, 4, 3, dims, sk, box);
-            encodeTensorMap(&tdv, a.dV, 4, 3, dims, sv, box);
-        }
         makeMap3(&tq, a.q, dim, a.newLen, a.batch, a.ldQ);
         makeMap3(&tk, a.k, dim, a.totalLen, a.batch, a.ldK);
         makeMap3(&tv, a.v, dim, a.totalLen, a.batch, a.ldV);
@@ -703,8 +698,7 @@ void attentionBackward(const AttentionBackwardArgs& a, cudaStream_t stream) {
         attentionBackwardTcKernel<<<static_cast<unsigned>(blocks), kThreads, kSmemBytes, stream>>>(
             *reinterpret_cast<const CUtensorMap*>(tq.bytes), *reinterpret_cast<const CUtensorMap*>(tk.bytes),
             *reinterpret_cast<const CUtensorMap*>(tv.bytes), *reinterpret_cast<const CUtensorMap*>(tg.bytes),
-            *reinterpret_cast<const CUtensorMap*>(tdq.bytes), *reinterpret_cast<const CUtensorMap*>(tdk.bytes),
-            *reinterpret_cast<const CUtensorMap*>(tdv.bytes), p, a.dStatus);
+            *reinterpret_cast<const CUtensorMap*>(tdq.bytes), p, a.dStatus);
         BFB_LAUNCH_CHECK();
         noteLaunch();
         return;
