@@ -71,6 +71,7 @@ struct BwdParams {
     const float* dTerm;  // [batch, heads, newLen]: sum_d O dO
     int batch, newLen, totalLen, numHeads;
     int64_t ldDq, ldDk, ldDv;
+    int prefetchAhead;     // a block asks for the K and V tiles of the block this many places after it
     float scale, scaleLog2;
     int oldLen, causal, numKvBlocks;
 };
@@ -111,13 +112,17 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
     constexpr int kGroup = 8;
     const int numBh = p.batch * p.numHeads;
     const int perGroup = kGroup * p.numKvBlocks;
-    const int group = static_cast<int>(blockIdx.x) / perGroup;
-    const int inGroup = static_cast<int>(blockIdx.x) - group * perGroup;
-    const int groupSize = min(kGroup, numBh - group * kGroup);
-    const int kvBlock = inGroup / groupSize;
-    const int bh = group * kGroup + inGroup % groupSize;
-    const int b = bh / p.numHeads, h = bh % p.numHeads;
-    const int k0 = kvBlock * kBlk;
+    auto decode = [&](int block, int* bOut, int* hOut) -> int {   // returns the block's first key
+        const int group = block / perGroup;
+        const int inGroup = block - group * perGroup;
+        const int groupSize = min(kGroup, numBh - group * kGroup);
+        const int bh = group * kGroup + inGroup % groupSize;
+        *bOut = bh / p.numHeads;
+        *hOut = bh % p.numHeads;
+        return (inGroup / groupSize) * kBlk;
+    };
+    int b, h;
+    const int k0 = decode(static_cast<int>(blockIdx.x), &b, &h);
     const int numQBlocks = (p.newLen + kBlk - 1) / kBlk;
     // first query block with a row that sees key k0: old_len + i >= k0
     const int firstQ = p.causal ? max(0, k0 - p.oldLen) / kBlk : 0;
@@ -146,6 +151,17 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
         tma_load_3d(smem + kVOff + kHalfBytes, &tmapV, kvFull, h * kD + 64, k0, b);
         loadQdO(0);
         if (steps > 1) loadQdO(1);
+        // A block's K and V tiles are read by that block alone, so they would come from DRAM when it starts: the block
+        // that takes an SM about one CTA from now has them brought into L2 here.
+        const int ahead = static_cast<int>(blockIdx.x) + p.prefetchAhead;
+        if (ahead < static_cast<int>(gridDim.x)) {
+            int b2, h2;
+            const int k2 = decode(ahead, &b2, &h2);
+            tma_prefetch_l2_3d(&tmapK, h2 * kD, k2, b2);
+            tma_prefetch_l2_3d(&tmapK, h2 * kD + 64, k2, b2);
+            tma_prefetch_l2_3d(&tmapV, h2 * kD, k2, b2);
+            tma_prefetch_l2_3d(&tmapV, h2 * kD + 64, k2, b2);
+        }
     }
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) mbar_init(&dqStaged[i], kSoftmaxWarps);
@@ -692,6 +708,7 @@ void attentionBackward(const AttentionBackwardArgs& a, cudaStream_t stream) {
         p.oldLen = static_cast<int>(a.oldLen);
         p.causal = a.causal;
         p.numKvBlocks = static_cast<int>((a.totalLen + kBlk - 1) / kBlk);
+        p.prefetchAhead = smCount();   // one CTA per SM is resident
         const int64_t blocks = static_cast<int64_t>(p.numKvBlocks) * a.batch * a.numHeads;
         require(blocks <= 0x7FFFFFFF, "attention_bwd: too many key blocks for one launch");
         BFB_CUDA(cudaFuncSetAttribute(attentionBackwardTcKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));

@@ -157,6 +157,12 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const void* tmap, uint64_
         ::"r"(smem_u32(dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
+// Brings the tile at the given coordinates into L2 only (no destination, nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_3d(const void* tmap, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(tmap), "r"(c0), "r"(c1),
+                 "r"(c2)
+                 : "memory");
+}
 // ---- TMA tiled store (shared -> global), tracked by the issuing thread's bulk async-group ----------
 // The source tile must be complete in shared memory and published to the async proxy (fence_proxy_async_smem)
 // before the store is issued. Coordinates outside the tensor are clipped, never written.
