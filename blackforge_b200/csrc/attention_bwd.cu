@@ -419,6 +419,14 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(dsFull);
+            // the statistics of the next step, fetched at the top of this one, go to the other buffer: every warp has
+            // left the step that read it (this step's S^T needed all of them to finish the one before)
+            if (it + 1 < steps) {
+                float* nextRows = reinterpret_cast<float*>(smem + kRowOff) + (stage ^ 1) * 256 + half * 128;
+                nextRows[keyRow] = nextStat;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&rowFull[stage ^ 1]);
+            }
             // ---- dQ: lane = query row, columns = head_dim. The tile goes to the slot this step's Q and dO came from, as
             // four boxes of 32 floats x 128 rows in the 128-byte swizzle; the producer thread hands it to the TMA unit.
             if (!warp_all(mbar_wait(dqFull, par, abortFlag, status, kDevTimeoutAccFull))) {
@@ -433,7 +441,10 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(dqFree);       // the columns may take the next step's S^T
-            if (!warp_all(mbar_wait(slotFree, par, abortFlag, status, kDevTimeoutAccFull))) {
+            // The first four warps write over the Q tile, which dK (issued after dQ) still reads; the others write over
+            // the dO tile, whose last reader dV was issued before dQ and is complete with it. They go ahead, and so
+            // reach the next step's exponentials while their scheduler's other warp is still here.
+            if (half == 0 && !warp_all(mbar_wait(slotFree, par, abortFlag, status, kDevTimeoutAccFull))) {
                 alive = false;
                 break;
             }
@@ -450,14 +461,6 @@ attentionBackwardTcKernel(const __grid_constant__ CUtensorMap tmapQ, const __gri
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(&dqStaged[stage]);
-            // the statistics of the next step, fetched at the top of this one, go to the other buffer: every warp
-            // has left the step that read it (this step's S^T needed all of them to finish the one before)
-            if (it + 1 < steps) {
-                float* nextRows = reinterpret_cast<float*>(smem + kRowOff) + (stage ^ 1) * 256 + half * 128;
-                nextRows[keyRow] = nextStat;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&rowFull[stage ^ 1]);
-            }
         }
         // ---- dV (first four warps) and dK (the others) of this CTA's keys; keys that no query row sees get zeros
         if (steps == 0 && keyValid) {
